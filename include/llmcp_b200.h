@@ -1,0 +1,186 @@
+/* C ABI of libllmcp_b200.so: a CUDA (sm_100a) implementation of llmcp's Q8_0 hot path.
+ *
+ * Three groups of entry points:
+ *   1. the AOT ABI v2 symbols that llmcp's runtime resolves with dlsym, so the library can
+ *      be passed to `llmcp-benchmark --aot` / `llmcp-run --aot` in place of a compiled model;
+ *   2. one function per llmcp dialect operator (host pointers in, host pointers out) for
+ *      operator-level parity checks, plus the same operators on device pointers;
+ *   3. an engine handle for callers that want tokens, state and logits to stay on the GPU.
+ *
+ * All functions return 0 on success unless stated otherwise; on failure they return a
+ * non-zero code and leave a message for llmcp_b200_last_error().  Nothing here falls back
+ * to the CPU: without a CUDA device every compute entry fails.
+ *
+ * File paths in the comments are paths inside the llmcp project.
+ */
+#ifndef LLMCP_B200_H
+#define LLMCP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- 1. AOT ABI v2 --------------------------------------------------------------- */
+
+/* Replaces the generated `llmcp_model_abi_version` (lib/Model/ModelBuilder.cpp:528-536,
+ * include/llmcp/Support/AotAbi.h:12); checked by lib/Runtime/AotRuntime.cpp:49-55. */
+int32_t llmcp_model_abi_version(void);
+
+/* Replace the generated `_mlir_ciface_llmcp_model_prefill` / `_decode`
+ * (lib/Model/ModelBuilder.cpp:440-526; resolved at lib/Runtime/AotRuntime.cpp:56-64 and
+ * called at :87-118).  Arguments, in order: tokens memref<?xindex>, cos memref<?x64xf32>,
+ * sin memref<?x64xf32>, start position (index, by value), cache length (index, by value),
+ * arena memref<?xi8>, kv memref<8x2x4x?x256xbf16>, delta memref<24x32x128x128xf32>,
+ * conv memref<24x3x8192xbf16>, logits memref<1x248320xf32>; each memref is a pointer to
+ * {T* base; T* data; int64 offset; int64 sizes[N]; int64 strides[N]}
+ * (include/llmcp/Runtime/AotRuntime.h:52-58).  All buffers are host memory.  The logits row
+ * is always fully written.  The generation state lives on the GPU: it is cleared when a call
+ * starts at position 0 and the host kv/delta/conv buffers are neither read nor written
+ * unless LLMCP_B200_SYNC_STATE=1 is set, in which case they are uploaded before and
+ * downloaded after every call.  On a CUDA failure the row is filled with NaN and the message
+ * is kept for llmcp_b200_last_error(). */
+void _mlir_ciface_llmcp_model_prefill(void *tokens, void *cos, void *sin, void *start_pos, void *cache_length,
+                                      void *arena, void *kv, void *delta, void *conv, void *logits);
+void _mlir_ciface_llmcp_model_decode(void *tokens, void *cos, void *sin, void *start_pos, void *cache_length,
+                                     void *arena, void *kv, void *delta, void *conv, void *logits);
+
+/* Additive: copies the last error message (NUL terminated, truncated to `capacity`) and
+ * returns its length; 0 means no error since the last llmcp_b200_clear_error(). */
+size_t llmcp_b200_last_error(char *buffer, size_t capacity);
+void llmcp_b200_clear_error(void);
+/* Number of visible CUDA devices (0 without a driver or GPU). */
+int llmcp_b200_device_count(void);
+/* Device used by the AOT entries and by the host-pointer operators (default: current). */
+int llmcp_b200_set_device(int device);
+/* Releases every engine created by the AOT entries. */
+void llmcp_b200_release_all(void);
+/* Kernel launches issued by this library since it was loaded. */
+uint64_t llmcp_b200_launch_count(void);
+
+/* ---- 2. operators ------------------------------------------------------------------ */
+/* dtype: 0 = f32, 1 = bf16 (bit patterns in uint16).  activation: 0 none, 1 silu,
+ * 2 sigmoid, 3 softplus (lib/Dialect/LLMCP/Transforms/MatmulLoweringCommon.cpp:78-103). */
+
+/* Activation quantisation used by every Q8 linear (Q8Decode.cpp:83-120,
+ * Q8Matmul.cpp:93-141): q [M,K] int8, scales [M,K/32] f32. */
+int llmcp_op_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales);
+
+/* llmcp.linear with weight_format = "q8_0_p4" (LLMCPOps.td:19-45, LLMCPOps.cpp:46-70;
+ * kernels Q8Decode.cpp:131-225 for M = 1 and Q8Matmul.cpp:143-289 otherwise).
+ * weight: N/4 * K/32 records of 136 bytes.  block_dots, if not NULL, receives the int32
+ * dot product of every (row, column, 32-block): [M, N, K/32].  N % 8 == 0, K % 32 == 0. */
+int llmcp_op_linear_q8(const void *x, int x_dtype, int64_t M, int64_t K, const uint8_t *weight, int64_t N,
+                       void *y, int y_dtype, int activation, int32_t *block_dots);
+
+/* llmcp.lm_head (LLMCPOps.td:103-110, LowerToLinalg.cpp:729-765) followed by the host
+ * argmax of tools/llmcp-benchmark/llmcp-benchmark.cpp:51-54 (first maximum).
+ * hidden: [M, K] bf16; logits: [M, vocab] f32 (may be NULL); argmax: [M] (may be NULL). */
+int llmcp_op_lm_head_q8(const uint16_t *hidden, int64_t M, int64_t K, const uint8_t *table, int64_t vocab,
+                        float *logits, int64_t *argmax);
+
+/* llmcp.embedding on a packed table (LLMCPOps.td:94-101, LowerToLinalg.cpp:435-531). */
+int llmcp_op_embedding_q8(const int64_t *tokens, int64_t S, const uint8_t *table, int64_t vocab, int64_t hidden,
+                          uint16_t *out);
+
+/* llmcp.rms_norm (LLMCPOps.td:47-68, LowerToLinalg.cpp:211-308, DecodeNormalization.cpp:70-145). */
+int llmcp_op_rms_norm(const uint16_t *x, int64_t M, int64_t H, const void *weight, int w_dtype, float eps,
+                      int zero_centered, uint16_t *y);
+
+/* llmcp.add (op 0), llmcp.mul (1), llmcp.silu_mul (2; a = gate, b = up)
+ * (LLMCPOps.td:70-92, LowerToLinalg.cpp:312-427). */
+int llmcp_op_pointwise(const uint16_t *a, const uint16_t *b, int64_t count, int op, uint16_t *y);
+
+/* llmcp.gated_rms_norm (LLMCPOps.td:167-179, LowerToLinalg.cpp:574-727). */
+int llmcp_op_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const void *weight, int w_dtype, int64_t M,
+                            int64_t H, int64_t group, float eps, int gate_activated, uint16_t *y);
+
+/* llmcp.causal_conv1d with SiLU (LLMCPOps.td:112-123, LowerCausalConv1d.cpp:29-189).
+ * x,y: [S, C] bf16; weight: [C, 1, kernel] bf16; state: [kernel-1, C] bf16, updated. */
+int llmcp_op_causal_conv1d(const uint16_t *x, const uint16_t *weight, uint16_t *state, int64_t S, int64_t C,
+                           int64_t kernel, uint16_t *y);
+
+/* llmcp.gated_delta_net (LLMCPOps.td:125-143, LowerGatedDeltaNet.cpp:47-452).
+ * conv: [S, 2*nk*dk + nv*dv] bf16; a,b: [S, nv] bf16; a_log: [nv] f32; dt_bias: [nv] bf16;
+ * state: [nv, dk, dv] f32, updated; out: [S, nv*dv] bf16. */
+int llmcp_op_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b, const float *a_log,
+                             const uint16_t *dt_bias, float *state, int64_t S, int64_t nk, int64_t nv, int64_t dk,
+                             int64_t dv, int b_activated, uint16_t *out);
+
+/* llmcp.attention (LLMCPOps.td:145-165, LowerAttention.cpp:54-607).  qg: [S, nh*2*hd];
+ * k,v: [S, nkv*hd]; q_norm,k_norm: [hd] bf16; cos,sin: [S, rot] f32; cache: one layer
+ * [2, nkv, cap, hd] bf16, updated at rows position .. position+S-1; out: [S, nh*hd]. */
+int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
+                       const uint16_t *k_norm, const float *cos, const float *sin, uint16_t *cache, int64_t position,
+                       int64_t S, int64_t nh, int64_t nkv, int64_t hd, int64_t rot, int64_t cap, uint16_t *out);
+
+/* The same contraction on device pointers, enqueued on `stream` (a cudaStream_t) without
+ * synchronising: for callers that keep weights and activations in HBM.
+ *   llmcp_dev_repack_q8 : arena records -> q [N][K] int8 and d [N][K/32] f16 (device layout).
+ *   llmcp_dev_act_quant : as llmcp_op_act_quant.
+ *   llmcp_dev_gemv_q8   : M = 1 linear on already quantised input (Q8Decode.cpp:131-225).
+ *   llmcp_dev_gemm_q8   : M > 1 linear (Q8Matmul.cpp:143-289).
+ *   llmcp_dev_argmax    : first maximum of n f32 values; scratch: 512 floats + 512 int64. */
+int llmcp_dev_repack_q8(const uint8_t *records, int64_t N, int64_t K, int8_t *q, uint16_t *d, void *stream);
+int llmcp_dev_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales, void *stream);
+int llmcp_dev_gemv_q8(const int8_t *aq, const float *as, int64_t K, const int8_t *wq, const uint16_t *wd, int64_t N,
+                      void *y, int y_dtype, int activation, int rows_per_warp, void *stream);
+int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
+                      int64_t N, void *y, int y_dtype, int activation, void *stream);
+int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *scratch_indices, int64_t *out_index,
+                     void *stream);
+
+/* ---- 3. engine --------------------------------------------------------------------- */
+
+typedef struct llmcp_b200_dims {
+  int64_t hidden, intermediate, vocab, layers, full_interval;
+  int64_t heads, kv_heads, head_dim, rotary;
+  int64_t lin_k_heads, lin_v_heads, lin_k_dim, lin_v_dim, conv_kernel;
+  float eps, rope_theta;
+} llmcp_b200_dims;
+
+/* Qwen3.5-4B text dimensions (docs/model-spec.md:51-76, lib/Runtime/AotRuntime.cpp:41-43). */
+void llmcp_b200_default_dims(llmcp_b200_dims *dims);
+
+/* Container helpers (format of include/llmcp/Support/PackedWeights.h:21-58,
+ * lib/Model/WeightLayout.cpp:96-268, lib/Model/WeightPacker.cpp:126-160).
+ *   llmcp_b200_synthetic_bytes : size of a random-init container for `dims`.
+ *   llmcp_b200_synthetic_fill  : writes it (arena, manifest, header last) from `seed`.
+ *   llmcp_b200_pack_q8_0_p4    : lib/Model/Quantization.cpp:165-214 on an f32 matrix.
+ *   llmcp_b200_validate        : the checks of lib/Runtime/WeightArena.cpp:39-123. */
+uint64_t llmcp_b200_synthetic_bytes(const llmcp_b200_dims *dims);
+int llmcp_b200_synthetic_fill(const llmcp_b200_dims *dims, uint64_t seed, uint8_t *file, uint64_t file_bytes);
+int llmcp_b200_pack_q8_0_p4(const float *values, int64_t rows, int64_t cols, uint8_t *dst);
+int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes);
+/* Rotary cos/sin row of one position, f32 (lib/Runtime/AotRuntime.cpp:22-32). */
+void llmcp_b200_make_cos_sin(int64_t position, int64_t rotary, float theta, float *cos_out, float *sin_out);
+/* Copies the manifest JSON text of a container; returns its length. */
+uint64_t llmcp_b200_manifest(const uint8_t *file, uint64_t file_bytes, char *buffer, uint64_t capacity);
+
+/* Uploads a container (host memory: header, arena, manifest) to `device`, re-laying the
+ * weights out for the GPU, and allocates state for `capacity` positions.  NULL on failure. */
+void *llmcp_b200_engine_create(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims,
+                               int64_t capacity, int device);
+void llmcp_b200_engine_destroy(void *engine);
+int llmcp_b200_engine_reset(void *engine);
+/* One forward over host tokens (the work of lib/Runtime/AotRuntime.cpp:68-120): logits
+ * (vocab f32, may be NULL) and argmax (may be NULL) of the last position. */
+int llmcp_b200_engine_forward(void *engine, const int64_t *tokens, int64_t S, int64_t position, float *logits,
+                              int64_t *argmax);
+/* The decode loop of tools/llmcp-benchmark/llmcp-benchmark.cpp:94-101 kept on the device:
+ * token, argmax and state never leave HBM.  out_tokens: `steps` ids; device_ms: CUDA-event
+ * time of the loop (may be NULL). */
+int llmcp_b200_engine_generate(void *engine, int64_t first_token, int64_t position, int64_t steps,
+                               int64_t *out_tokens, float *device_ms);
+/* State buffers in the layouts of lib/Runtime/AotRuntime.cpp:41-43 (any may be NULL). */
+int llmcp_b200_engine_read_state(void *engine, uint16_t *kv, float *delta, uint16_t *conv);
+/* Final-norm output of the last position (hidden bf16) of the most recent forward. */
+int llmcp_b200_engine_read_hidden(void *engine, uint16_t *hidden);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LLMCP_B200_H */

@@ -1,0 +1,438 @@
+"""Python binding of libllmcp_b200.so and a host-side mirror of llmcp's runtime classes.
+
+``ops``       one function per llmcp dialect operator on numpy arrays (host in, host out);
+``Arena``     the packed weight container (lib/Runtime/WeightArena.cpp);
+``AotRuntime``  the loader that calls the AOT ABI v2 entry points with MLIR memref
+              descriptors exactly as lib/Runtime/AotRuntime.cpp:68-120 does;
+``Engine``    the additive device-resident interface.
+
+Everything computes on the GPU through the shared library.  There is no CPU fallback: if the
+library has not been built, or no CUDA device is present, calls raise.
+"""
+import ctypes as C
+import json
+import mmap
+import os
+import pathlib
+
+import numpy as np
+
+_PACKAGE = pathlib.Path(__file__).resolve().parent
+LIBRARY_PATH = _PACKAGE / "libllmcp_b200.so"
+
+DTYPE_F32, DTYPE_BF16 = 0, 1
+ACTIVATIONS = {"none": 0, "silu": 1, "sigmoid": 2, "softplus": 3}
+
+_lib = None
+
+
+class LlmcpError(RuntimeError):
+    pass
+
+
+class Dims(C.Structure):
+    """llmcp_b200_dims (include/llmcp_b200.h)."""
+    _fields_ = [(n, C.c_int64) for n in (
+        "hidden", "intermediate", "vocab", "layers", "full_interval", "heads", "kv_heads", "head_dim",
+        "rotary", "lin_k_heads", "lin_v_heads", "lin_k_dim", "lin_v_dim", "conv_kernel")] + [
+        ("eps", C.c_float), ("rope_theta", C.c_float)]
+
+    def copy(self, **changes):
+        out = Dims.from_buffer_copy(self)
+        for key, value in changes.items():
+            setattr(out, key, value)
+        return out
+
+    @property
+    def qkv_dim(self):
+        return 2 * self.lin_k_heads * self.lin_k_dim + self.lin_v_heads * self.lin_v_dim
+
+    @property
+    def full_layers(self):
+        return self.layers // self.full_interval
+
+    @property
+    def linear_layers(self):
+        return self.layers - self.full_layers
+
+
+def lib():
+    """Loads the shared library (built by ``python -m llmcp_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not LIBRARY_PATH.exists():
+            raise LlmcpError(f"{LIBRARY_PATH} is missing: run `python -m llmcp_b200.build` (needs nvcc)")
+        handle = C.CDLL(str(LIBRARY_PATH))
+        handle.llmcp_model_abi_version.restype = C.c_int32
+        handle.llmcp_b200_last_error.restype = C.c_size_t
+        handle.llmcp_b200_launch_count.restype = C.c_uint64
+        handle.llmcp_b200_synthetic_bytes.restype = C.c_uint64
+        handle.llmcp_b200_manifest.restype = C.c_uint64
+        handle.llmcp_b200_engine_create.restype = C.c_void_p
+        handle._mlir_ciface_llmcp_model_prefill.restype = None
+        handle._mlir_ciface_llmcp_model_decode.restype = None
+        _lib = handle
+    return _lib
+
+
+def last_error():
+    buf = C.create_string_buffer(4096)
+    lib().llmcp_b200_last_error(buf, C.c_size_t(len(buf)))
+    return buf.value.decode(errors="replace")
+
+
+def _check(code):
+    if code != 0:
+        raise LlmcpError(last_error() or f"llmcp_b200 call failed with code {code}")
+
+
+def device_count():
+    return int(lib().llmcp_b200_device_count())
+
+
+def set_device(index):
+    _check(lib().llmcp_b200_set_device(int(index)))
+
+
+def launch_count():
+    return int(lib().llmcp_b200_launch_count())
+
+
+def default_dims():
+    d = Dims()
+    lib().llmcp_b200_default_dims(C.byref(d))
+    return d
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def _i(v):
+    return C.c_int64(int(v))
+
+
+def _np_dtype(code):
+    return np.uint16 if code == DTYPE_BF16 else np.float32
+
+
+class ops:
+    """The llmcp dialect operators (include/llmcp/Dialect/LLMCP/IR/LLMCPOps.td:19-179)."""
+
+    @staticmethod
+    def act_quant(x, x_bf16=True):
+        x = np.ascontiguousarray(x, dtype=np.uint16 if x_bf16 else np.float32)
+        M, K = x.shape
+        q = np.empty((M, K), dtype=np.int8)
+        s = np.empty((M, K // 32), dtype=np.float32)
+        _check(lib().llmcp_op_act_quant(_p(x), int(x_bf16), _i(M), _i(K), _p(q), _p(s)))
+        return q, s
+
+    @staticmethod
+    def linear_q8(x, packed, N, x_bf16=True, y_bf16=True, activation="none", want_dots=False):
+        x = np.ascontiguousarray(x, dtype=np.uint16 if x_bf16 else np.float32)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        M, K = x.shape
+        if packed.size != N * (K // 32) * 34:
+            raise LlmcpError("packed weight size does not match N * (K + K / 32 * 2)")  # LLMCPOps.cpp:46-70
+        y = np.empty((M, N), dtype=np.uint16 if y_bf16 else np.float32)
+        dots = np.empty((M, N, K // 32), dtype=np.int32) if want_dots else None
+        _check(lib().llmcp_op_linear_q8(_p(x), int(x_bf16), _i(M), _i(K), _p(packed), _i(N), _p(y), int(y_bf16),
+                                        ACTIVATIONS[activation], _p(dots)))
+        return (y, dots) if want_dots else y
+
+    @staticmethod
+    def lm_head_q8(hidden, packed, vocab):
+        hidden = np.ascontiguousarray(hidden, dtype=np.uint16)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        M, K = hidden.shape
+        logits = np.empty((M, vocab), dtype=np.float32)
+        argmax = np.empty(M, dtype=np.int64)
+        _check(lib().llmcp_op_lm_head_q8(_p(hidden), _i(M), _i(K), _p(packed), _i(vocab), _p(logits), _p(argmax)))
+        return logits, argmax
+
+    @staticmethod
+    def embedding_q8(tokens, packed, vocab, hidden):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        out = np.empty((tokens.shape[0], hidden), dtype=np.uint16)
+        _check(lib().llmcp_op_embedding_q8(_p(tokens), _i(tokens.shape[0]), _p(packed), _i(vocab), _i(hidden), _p(out)))
+        return out
+
+    @staticmethod
+    def rms_norm(x, w, eps=1e-6, zero_centered=True, w_bf16=True):
+        x = np.ascontiguousarray(x, dtype=np.uint16)
+        w = np.ascontiguousarray(w, dtype=np.uint16 if w_bf16 else np.float32)
+        M, H = x.shape
+        y = np.empty_like(x)
+        _check(lib().llmcp_op_rms_norm(_p(x), _i(M), _i(H), _p(w), int(w_bf16), C.c_float(eps), int(zero_centered), _p(y)))
+        return y
+
+    @staticmethod
+    def pointwise(a, b, op):
+        a = np.ascontiguousarray(a, dtype=np.uint16)
+        b = np.ascontiguousarray(b, dtype=np.uint16)
+        y = np.empty_like(a)
+        _check(lib().llmcp_op_pointwise(_p(a), _p(b), _i(a.size), {"add": 0, "mul": 1, "silu_mul": 2}[op], _p(y)))
+        return y
+
+    @staticmethod
+    def gated_rms_norm(x, gate, w, group, eps=1e-6, gate_activated=False, w_bf16=False):
+        x = np.ascontiguousarray(x, dtype=np.uint16)
+        gate = np.ascontiguousarray(gate, dtype=np.uint16)
+        w = np.ascontiguousarray(w, dtype=np.uint16 if w_bf16 else np.float32)
+        M, H = x.shape
+        y = np.empty_like(x)
+        _check(lib().llmcp_op_gated_rms_norm(_p(x), _p(gate), _p(w), int(w_bf16), _i(M), _i(H), _i(group),
+                                             C.c_float(eps), int(gate_activated), _p(y)))
+        return y
+
+    @staticmethod
+    def causal_conv1d(x, w, state, kernel):
+        x = np.ascontiguousarray(x, dtype=np.uint16)
+        w = np.ascontiguousarray(w, dtype=np.uint16)
+        state = np.array(state, dtype=np.uint16, copy=True)
+        S, channels = x.shape
+        y = np.empty_like(x)
+        _check(lib().llmcp_op_causal_conv1d(_p(x), _p(w), _p(state), _i(S), _i(channels), _i(kernel), _p(y)))
+        return y, state
+
+    @staticmethod
+    def gated_delta_net(conv, a, b, a_log, dt_bias, state, nk, nv, dk, dv, b_activated=False):
+        conv = np.ascontiguousarray(conv, dtype=np.uint16)
+        a = np.ascontiguousarray(a, dtype=np.uint16)
+        b = np.ascontiguousarray(b, dtype=np.uint16)
+        a_log = np.ascontiguousarray(a_log, dtype=np.float32)
+        dt_bias = np.ascontiguousarray(dt_bias, dtype=np.uint16)
+        state = np.array(state, dtype=np.float32, copy=True)
+        S = conv.shape[0]
+        out = np.empty((S, nv * dv), dtype=np.uint16)
+        _check(lib().llmcp_op_gated_delta_net(_p(conv), _p(a), _p(b), _p(a_log), _p(dt_bias), _p(state), _i(S), _i(nk),
+                                              _i(nv), _i(dk), _i(dv), int(b_activated), _p(out)))
+        return out, state
+
+    @staticmethod
+    def attention(qg, k, v, q_norm, k_norm, cos, sin, cache, position, nh, nkv, hd, rot):
+        qg = np.ascontiguousarray(qg, dtype=np.uint16)
+        k = np.ascontiguousarray(k, dtype=np.uint16)
+        v = np.ascontiguousarray(v, dtype=np.uint16)
+        q_norm = np.ascontiguousarray(q_norm, dtype=np.uint16)
+        k_norm = np.ascontiguousarray(k_norm, dtype=np.uint16)
+        cos = np.ascontiguousarray(cos, dtype=np.float32)
+        sin = np.ascontiguousarray(sin, dtype=np.float32)
+        cache = np.array(cache, dtype=np.uint16, copy=True)
+        S, cap = qg.shape[0], cache.shape[2]
+        out = np.empty((S, nh * hd), dtype=np.uint16)
+        _check(lib().llmcp_op_attention(_p(qg), _p(k), _p(v), _p(q_norm), _p(k_norm), _p(cos), _p(sin), _p(cache),
+                                        _i(position), _i(S), _i(nh), _i(nkv), _i(hd), _i(rot), _i(cap), _p(out)))
+        return out, cache
+
+
+def pack_q8_0_p4(values):
+    """lib/Model/Quantization.cpp:165-214 on an f32 matrix -> packed bytes."""
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    rows, cols = values.shape
+    out = np.empty(rows * (cols // 32) * 34 if cols % 32 == 0 else 0, dtype=np.uint8)
+    _check(lib().llmcp_b200_pack_q8_0_p4(_p(values), _i(rows), _i(cols), _p(out)))
+    return out
+
+
+def synthetic_container(dims, seed):
+    """A random-init, q8_0-packed container for ``dims`` as a numpy uint8 array."""
+    size = int(lib().llmcp_b200_synthetic_bytes(C.byref(dims)))
+    if size == 0:
+        raise LlmcpError(last_error())
+    data = np.empty(size, dtype=np.uint8)
+    _check(lib().llmcp_b200_synthetic_fill(C.byref(dims), C.c_uint64(seed), _p(data), C.c_uint64(size)))
+    return data
+
+
+class Arena:
+    """The packed weight container: header, arena, JSON manifest (lib/Runtime/WeightArena.cpp:27-129).
+
+    ``load`` maps a file, ``from_buffer`` adopts a numpy uint8 array.  A failed load leaves
+    the previously loaded contents in place.
+    """
+
+    def __init__(self):
+        self.data = None
+        self.size = 0
+        self.quantization = "none"
+        self.manifest = None
+        self.weights = {}
+        self._map = None
+
+    def _adopt(self, data, keep):
+        _check(lib().llmcp_b200_validate(_p(data), C.c_uint64(data.size)))
+        length = int(lib().llmcp_b200_manifest(_p(data), C.c_uint64(data.size), None, C.c_uint64(0)))
+        arena_bytes = int.from_bytes(data[16:24].tobytes(), "little")
+        manifest = json.loads(data[arena_bytes:arena_bytes + length].tobytes().decode())
+        self.data, self.size, self._map = data, arena_bytes, keep
+        self.manifest = manifest
+        self.quantization = manifest["quantization"]
+        self.weights = {t["name"]: t for t in manifest["tensors"]}
+
+    def load(self, path):
+        with open(path, "rb") as f:
+            mapped = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
+        data = np.frombuffer(mapped, dtype=np.uint8)
+        if data.size < 64:
+            raise LlmcpError("packed weights file is too small")
+        self._adopt(data, mapped)
+        return self
+
+    def from_buffer(self, data):
+        self._adopt(np.ascontiguousarray(data, dtype=np.uint8), None)
+        return self
+
+    def get(self, name):
+        return self.weights[name]
+
+
+def _memref(rank):
+    class MemRef(C.Structure):
+        _fields_ = [("base", C.c_void_p), ("data", C.c_void_p), ("offset", C.c_int64),
+                    ("sizes", C.c_int64 * rank), ("strides", C.c_int64 * rank)]
+    return MemRef
+
+
+_MemRef1, _MemRef2, _MemRef3, _MemRef4, _MemRef5 = (_memref(r) for r in (1, 2, 3, 4, 5))
+
+
+def _descriptor(cls, array, sizes=None):
+    sizes = list(array.shape if sizes is None else sizes)
+    strides = [1] * len(sizes)
+    for i in range(len(sizes) - 2, -1, -1):
+        strides[i] = strides[i + 1] * sizes[i + 1]
+    d = cls()
+    d.base = d.data = array.ctypes.data
+    d.offset = 0
+    for i, (size, stride) in enumerate(zip(sizes, strides)):
+        d.sizes[i] = size
+        d.strides[i] = stride
+    return d
+
+
+def make_cos_sin(position, rotary=64, theta=1.0e7):
+    """lib/Runtime/AotRuntime.cpp:22-32 (computed by the library's C++ host code, in f32)."""
+    cos = np.empty(rotary, dtype=np.float32)
+    sin = np.empty(rotary, dtype=np.float32)
+    lib().llmcp_b200_make_cos_sin(_i(position), _i(rotary), C.c_float(theta), _p(cos), _p(sin))
+    return cos, sin
+
+
+class AotRuntime:
+    """Mirror of mlir::llmcp::runtime::AotRuntime (lib/Runtime/AotRuntime.cpp:39-120).
+
+    ``init`` loads a shared library that exports the AOT ABI v2 symbols and allocates the
+    host state buffers; ``forward`` marshals memref descriptors and calls the prefill entry
+    for more than one token, else the decode entry.  ``dims`` defaults to the constants the
+    reference hard-codes for Qwen3.5-4B.
+    """
+
+    def __init__(self, dims=None):
+        self.dims = dims or default_dims()
+        self.handle = None
+        self.capacity = 0
+
+    def init(self, path=None, max_sequence=0, cos_sin=None):
+        d = self.dims
+        self.capacity = int(max_sequence)
+        self.kv = np.zeros((d.full_layers, 2, d.kv_heads, self.capacity, d.head_dim), dtype=np.uint16)
+        self.delta = np.zeros((d.linear_layers, d.lin_v_heads, d.lin_k_dim, d.lin_v_dim), dtype=np.float32)
+        self.conv = np.zeros((d.linear_layers, d.conv_kernel - 1, d.qkv_dim), dtype=np.uint16)
+        self._cos_sin = cos_sin or (lambda pos: make_cos_sin(pos, d.rotary, d.rope_theta))
+        try:
+            self.handle = C.CDLL(str(path or LIBRARY_PATH))
+            version = self.handle.llmcp_model_abi_version
+            version.restype = C.c_int32
+            if version() != 2:
+                return False
+            self._prefill = self.handle._mlir_ciface_llmcp_model_prefill
+            self._decode = self.handle._mlir_ciface_llmcp_model_decode
+        except (OSError, AttributeError):
+            return False
+        for fn in (self._prefill, self._decode):
+            fn.restype = None
+            fn.argtypes = [C.c_void_p] * 10
+        return True
+
+    def forward(self, arena, tokens, start_pos, cache_length):
+        d = self.dims
+        sequence = len(tokens)
+        if sequence == 0 or start_pos < 0 or start_pos > self.capacity or sequence > self.capacity - start_pos:
+            return None
+        token_data = np.ascontiguousarray(tokens, dtype=np.int64)
+        cos = np.empty((sequence, d.rotary), dtype=np.float32)
+        sin = np.empty((sequence, d.rotary), dtype=np.float32)
+        for t in range(sequence):
+            cos[t], sin[t] = self._cos_sin(start_pos + t)
+        logits = np.zeros((1, d.vocab), dtype=np.float32)
+        rt = _descriptor(_MemRef1, token_data)
+        rc = _descriptor(_MemRef2, cos)
+        rs = _descriptor(_MemRef2, sin)
+        ra = _descriptor(_MemRef1, arena.data, sizes=[arena.size])
+        rk = _descriptor(_MemRef5, self.kv)
+        rd = _descriptor(_MemRef4, self.delta)
+        rv = _descriptor(_MemRef3, self.conv)
+        ro = _descriptor(_MemRef2, logits)
+        fn = self._prefill if sequence > 1 else self._decode
+        fn(C.addressof(rt), C.addressof(rc), C.addressof(rs), C.c_void_p(start_pos), C.c_void_p(cache_length),
+           C.addressof(ra), C.addressof(rk), C.addressof(rd), C.addressof(rv), C.addressof(ro))
+        return logits[0]
+
+
+class Engine:
+    """Device-resident executor (llmcp_b200_engine_* in include/llmcp_b200.h)."""
+
+    def __init__(self, container, dims=None, capacity=1160, device=0):
+        self.dims = dims or default_dims()
+        self.container = np.ascontiguousarray(container, dtype=np.uint8)
+        self.capacity = capacity
+        self.handle = lib().llmcp_b200_engine_create(_p(self.container), C.c_uint64(self.container.size),
+                                                     C.byref(self.dims), _i(capacity), int(device))
+        if not self.handle:
+            raise LlmcpError(last_error())
+        self.handle = C.c_void_p(self.handle)
+
+    def reset(self):
+        _check(lib().llmcp_b200_engine_reset(self.handle))
+
+    def forward(self, tokens, position, want_logits=True):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        logits = np.empty(self.dims.vocab, dtype=np.float32) if want_logits else None
+        argmax = C.c_int64(-1)
+        _check(lib().llmcp_b200_engine_forward(self.handle, _p(tokens), _i(tokens.shape[0]), _i(position),
+                                               _p(logits), C.byref(argmax)))
+        return logits, int(argmax.value)
+
+    def generate(self, first_token, position, steps):
+        out = np.empty(steps, dtype=np.int64)
+        ms = C.c_float(0)
+        _check(lib().llmcp_b200_engine_generate(self.handle, _i(first_token), _i(position), _i(steps), _p(out),
+                                                C.byref(ms)))
+        return out, float(ms.value)
+
+    def read_state(self):
+        d = self.dims
+        kv = np.empty((d.full_layers, 2, d.kv_heads, self.capacity, d.head_dim), dtype=np.uint16)
+        delta = np.empty((d.linear_layers, d.lin_v_heads, d.lin_k_dim, d.lin_v_dim), dtype=np.float32)
+        conv = np.empty((d.linear_layers, d.conv_kernel - 1, d.qkv_dim), dtype=np.uint16)
+        _check(lib().llmcp_b200_engine_read_state(self.handle, _p(kv), _p(delta), _p(conv)))
+        return {"kv": kv, "delta": delta, "conv": conv}
+
+    def read_hidden(self):
+        out = np.empty(self.dims.hidden, dtype=np.uint16)
+        _check(lib().llmcp_b200_engine_read_hidden(self.handle, _p(out)))
+        return out
+
+    def close(self):
+        if self.handle:
+            lib().llmcp_b200_engine_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

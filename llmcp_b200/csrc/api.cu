@@ -1,0 +1,741 @@
+// extern "C" surface of libllmcp_b200.so (see include/llmcp_b200.h).
+
+#include "../../include/llmcp_b200.h"
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "engine.h"
+#include "kernels.h"
+
+using namespace llmcp_b200;
+
+namespace {
+
+std::mutex g_mutex;
+std::string g_error;
+int g_device = -1; // -1: whatever device is current
+std::atomic<uint64_t> g_launches{0};
+
+void set_error(const std::string &message) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_error = message;
+  std::fprintf(stderr, "llmcp_b200: %s\n", message.c_str());
+}
+
+void require_device() {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    throw std::runtime_error("no CUDA device: this library has no CPU path");
+  }
+  if (g_device >= 0 && cudaSetDevice(g_device) != cudaSuccess)
+    throw std::runtime_error("cudaSetDevice failed");
+}
+
+void cuda_check(cudaError_t e, const char *what) {
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// Device buffer that optionally starts as a copy of host data.
+struct Buf {
+  void *p = nullptr;
+  size_t bytes = 0;
+  Buf() = default;
+  explicit Buf(size_t n, const void *host = nullptr) : bytes(n) {
+    cuda_check(cudaMalloc(&p, n ? n : 1), "cudaMalloc");
+    if (host && n)
+      cuda_check(cudaMemcpy(p, host, n, cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+  }
+  Buf(const Buf &) = delete;
+  Buf &operator=(const Buf &) = delete;
+  ~Buf() {
+    if (p)
+      cudaFree(p);
+  }
+  template <typename T> T *as() const { return static_cast<T *>(p); }
+  void to_host(void *host, size_t n) const {
+    if (n)
+      cuda_check(cudaMemcpy(host, p, n, cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
+  }
+};
+
+size_t elem(int dtype) { return dtype == kBF16 ? 2 : 4; }
+
+template <typename F> int guarded(F &&body) {
+  try {
+    body();
+    cuda_check(cudaDeviceSynchronize(), "kernel execution");
+    return 0;
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return 1;
+  }
+}
+
+template <typename F> int guarded_async(F &&body) {
+  try {
+    body();
+    return 0;
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return 1;
+  }
+}
+
+void check_q8_shape(int64_t N, int64_t K) {
+  if (N <= 0 || K <= 0 || N % 8 != 0 || K % 32 != 0)
+    throw std::runtime_error("packed Q8_0 needs rows % 8 == 0 and cols % 32 == 0"); // Q8PackedLayout.h:38-42
+}
+
+// Uploads packed records and re-lays them out: returns q and d planes.
+struct DeviceQ8 {
+  Buf q, d;
+  DeviceQ8(const uint8_t *records, int64_t N, int64_t K)
+      : q(static_cast<size_t>(N) * K), d(static_cast<size_t>(N) * (K / 32) * 2) {
+    Buf staging(static_cast<size_t>(N) * (K / 32) * 34, records);
+    launch_repack_p4(staging.as<uint8_t>(), N, K, q.as<int8_t>(), d.as<uint16_t>(), nullptr);
+    cuda_check(cudaDeviceSynchronize(), "repack");
+    g_launches += 1;
+  }
+};
+
+void run_linear(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
+                int64_t N, void *y, int y_dtype, int activation, int32_t *dots, int rows_per_warp,
+                cudaStream_t stream) {
+  if (M == 1) {
+    GemvJobs jobs{};
+    jobs.count = 1;
+    jobs.job[0].wq = wq;
+    jobs.job[0].wd = wd;
+    jobs.job[0].y = y;
+    jobs.job[0].N = static_cast<int>(N);
+    jobs.job[0].activation = activation;
+    jobs.job[0].y_dtype = y_dtype;
+    cuda_check(launch_gemv_q8(aq, as, static_cast<int>(K), jobs, dots, stream, rows_per_warp), "gemv");
+  } else {
+    cuda_check(launch_gemm_q8_dp4a(aq, as, static_cast<int>(M), static_cast<int>(K), wq, wd, static_cast<int>(N), y,
+                                   y_dtype, activation, dots, stream), "gemm");
+  }
+  g_launches += 1;
+}
+
+// ---- AOT entry plumbing -------------------------------------------------------------
+template <typename T, int N> struct MemRef {
+  T *base;
+  T *data;
+  int64_t offset;
+  int64_t sizes[N];
+  int64_t strides[N];
+};
+
+struct Session {
+  const uint8_t *arena = nullptr;
+  uint64_t arena_bytes = 0;
+  const void *kv = nullptr, *delta = nullptr, *conv = nullptr;
+  int64_t capacity = 0;
+  std::unique_ptr<Engine> engine;
+};
+
+std::vector<std::unique_ptr<Session>> g_sessions;
+
+bool contiguous(const int64_t *sizes, const int64_t *strides, int rank) {
+  int64_t expect = 1;
+  for (int i = rank - 1; i >= 0; --i) {
+    if (sizes[i] != 1 && strides[i] != expect)
+      return false;
+    expect *= sizes[i];
+  }
+  return true;
+}
+
+void aot_entry(void *tokens_p, void *cos_p, void *sin_p, void *start_pos, void *cache_length, void *arena_p,
+               void *kv_p, void *delta_p, void *conv_p, void *logits_p) {
+  auto *logits = static_cast<MemRef<float, 2> *>(logits_p);
+  float *row = logits->data + logits->offset;
+  const int64_t vocab = logits->sizes[1];
+  try {
+    require_device();
+    auto *tokens = static_cast<MemRef<int64_t, 1> *>(tokens_p);
+    auto *cos = static_cast<MemRef<float, 2> *>(cos_p);
+    auto *sin = static_cast<MemRef<float, 2> *>(sin_p);
+    auto *arena = static_cast<MemRef<uint8_t, 1> *>(arena_p);
+    auto *kv = static_cast<MemRef<uint16_t, 5> *>(kv_p);
+    auto *delta = static_cast<MemRef<float, 4> *>(delta_p);
+    auto *conv = static_cast<MemRef<uint16_t, 3> *>(conv_p);
+    const int64_t position = reinterpret_cast<int64_t>(start_pos);
+    (void)cache_length; // accepted and unused, as in LowerAttention.cpp:408-412
+    const int64_t S = tokens->sizes[0];
+    if (tokens->strides[0] != 1 && S > 1)
+      throw std::runtime_error("tokens must be contiguous");
+    if (!contiguous(cos->sizes, cos->strides, 2) || !contiguous(sin->sizes, sin->strides, 2) ||
+        !contiguous(kv->sizes, kv->strides, 5) || !contiguous(delta->sizes, delta->strides, 4) ||
+        !contiguous(conv->sizes, conv->strides, 3))
+      throw std::runtime_error("cos/sin/kv/delta/conv must be contiguous row-major buffers");
+
+    const uint8_t *base = arena->data + arena->offset;
+    Session *session = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      for (auto &s : g_sessions)
+        if (s->arena == base && s->arena_bytes == static_cast<uint64_t>(arena->sizes[0]) &&
+            s->kv == kv->data && s->delta == delta->data && s->conv == conv->data && s->capacity == kv->sizes[3])
+          session = s.get();
+    }
+    if (!session) {
+      // Dimensions the generated code has baked in come from the descriptors and the
+      // manifest here (AotRuntime.cpp:41-43,87-114).
+      Manifest manifest;
+      const std::string error = parse_container(base, 0, &manifest);
+      if (!error.empty())
+        throw std::runtime_error(error);
+      if (manifest.total_bytes != static_cast<uint64_t>(arena->sizes[0]))
+        throw std::runtime_error("arena descriptor length differs from the container header");
+      const std::string root = "model.language_model.";
+      const TensorEntry *embed = manifest.find(root + "embed_tokens.weight");
+      const TensorEntry *gate = manifest.find(root + "layers.0.mlp.gate_proj.weight");
+      if (!embed || !gate)
+        throw std::runtime_error("manifest lacks embed_tokens / layers.0.mlp.gate_proj");
+      ModelDims d;
+      d.vocab = embed->shape[0];
+      d.hidden = embed->shape[1];
+      d.intermediate = gate->shape[0];
+      int64_t layers = 0;
+      while (manifest.find(root + "layers." + std::to_string(layers) + ".input_layernorm.weight"))
+        ++layers;
+      d.layers = layers;
+      const int64_t full = kv->sizes[0], linear = delta->sizes[0];
+      if (full <= 0 || full + linear != layers || layers % full != 0)
+        throw std::runtime_error("state descriptors do not match the layer count of the manifest");
+      d.full_interval = layers / full;
+      d.kv_heads = kv->sizes[2];
+      d.head_dim = kv->sizes[4];
+      d.rotary = cos->sizes[1];
+      d.lin_v_heads = delta->sizes[1];
+      d.lin_k_dim = delta->sizes[2];
+      d.lin_v_dim = delta->sizes[3];
+      d.conv_kernel = conv->sizes[1] + 1;
+      const int64_t qkv_dim = conv->sizes[2];
+      d.lin_k_heads = (qkv_dim - d.lin_v_heads * d.lin_v_dim) / (2 * d.lin_k_dim);
+      const TensorEntry *q_proj = nullptr;
+      for (int64_t l = 0; l < layers && !q_proj; ++l)
+        q_proj = manifest.find(root + "layers." + std::to_string(l) + ".self_attn.q_proj.weight");
+      if (!q_proj)
+        throw std::runtime_error("manifest lacks a self_attn.q_proj.weight");
+      d.heads = q_proj->shape[0] / (2 * d.head_dim);
+      if (vocab != d.vocab)
+        throw std::runtime_error("logits descriptor width differs from the vocabulary of the arena");
+      int device = g_device;
+      if (device < 0)
+        cuda_check(cudaGetDevice(&device), "cudaGetDevice");
+      auto fresh = std::make_unique<Session>();
+      fresh->arena = base;
+      fresh->arena_bytes = static_cast<uint64_t>(arena->sizes[0]);
+      fresh->kv = kv->data;
+      fresh->delta = delta->data;
+      fresh->conv = conv->data;
+      fresh->capacity = kv->sizes[3];
+      fresh->engine = std::make_unique<Engine>(base, 0, d, kv->sizes[3], device);
+      std::lock_guard<std::mutex> lock(g_mutex);
+      g_sessions.push_back(std::move(fresh));
+      session = g_sessions.back().get();
+    }
+    Engine &engine = *session->engine;
+    static const bool sync_state = std::getenv("LLMCP_B200_SYNC_STATE") && std::atoi(std::getenv("LLMCP_B200_SYNC_STATE")) != 0;
+    if (sync_state)
+      engine.upload_state(kv->data + kv->offset, delta->data + delta->offset, conv->data + conv->offset);
+    else if (position == 0)
+      engine.reset_state();
+    const uint64_t before = engine.launches();
+    engine.forward_host(tokens->data + tokens->offset, S, position, cos->data + cos->offset, sin->data + sin->offset, row);
+    g_launches += engine.launches() - before;
+    if (sync_state)
+      engine.download_state(kv->data + kv->offset, delta->data + delta->offset, conv->data + conv->offset);
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    for (int64_t i = 0; i < vocab; ++i)
+      row[i] = NAN;
+  }
+}
+
+ModelDims to_dims(const llmcp_b200_dims *d) {
+  ModelDims m;
+  if (!d)
+    return m;
+  m.hidden = d->hidden;
+  m.intermediate = d->intermediate;
+  m.vocab = d->vocab;
+  m.layers = d->layers;
+  m.full_interval = d->full_interval;
+  m.heads = d->heads;
+  m.kv_heads = d->kv_heads;
+  m.head_dim = d->head_dim;
+  m.rotary = d->rotary;
+  m.lin_k_heads = d->lin_k_heads;
+  m.lin_v_heads = d->lin_v_heads;
+  m.lin_k_dim = d->lin_k_dim;
+  m.lin_v_dim = d->lin_v_dim;
+  m.conv_kernel = d->conv_kernel;
+  m.eps = d->eps;
+  m.rope_theta = d->rope_theta;
+  return m;
+}
+
+void check_dims(const ModelDims &d) {
+  if (d.hidden <= 0 || d.hidden % 32 || d.intermediate <= 0 || d.intermediate % 32 || d.vocab % 8 || d.layers <= 0 ||
+      d.full_interval <= 0 || d.layers % d.full_interval || d.heads <= 0 || d.kv_heads <= 0 || d.heads % d.kv_heads ||
+      d.head_dim <= 0 || d.rotary % 2 || d.rotary > d.head_dim || d.lin_k_heads <= 0 || d.lin_v_heads % d.lin_k_heads ||
+      d.lin_v_heads % 8 || d.lin_v_dim % 32 || d.value_dim() % 32 || d.attn_dim() % 32 || d.qkv_dim() % 8 ||
+      d.kv_dim() % 8 || d.q_out() % 8 || d.conv_kernel < 2)
+    throw std::runtime_error("unsupported model dimensions");
+}
+
+} // namespace
+
+extern "C" {
+
+int32_t llmcp_model_abi_version(void) { return 2; }
+
+void _mlir_ciface_llmcp_model_prefill(void *tokens, void *cos, void *sin, void *start_pos, void *cache_length,
+                                      void *arena, void *kv, void *delta, void *conv, void *logits) {
+  aot_entry(tokens, cos, sin, start_pos, cache_length, arena, kv, delta, conv, logits);
+}
+
+void _mlir_ciface_llmcp_model_decode(void *tokens, void *cos, void *sin, void *start_pos, void *cache_length,
+                                     void *arena, void *kv, void *delta, void *conv, void *logits) {
+  aot_entry(tokens, cos, sin, start_pos, cache_length, arena, kv, delta, conv, logits);
+}
+
+size_t llmcp_b200_last_error(char *buffer, size_t capacity) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (buffer && capacity) {
+    const size_t n = std::min(capacity - 1, g_error.size());
+    std::memcpy(buffer, g_error.data(), n);
+    buffer[n] = 0;
+  }
+  return g_error.size();
+}
+
+void llmcp_b200_clear_error(void) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_error.clear();
+}
+
+int llmcp_b200_device_count(void) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return count;
+}
+
+int llmcp_b200_set_device(int device) {
+  return guarded_async([&] {
+    if (device < 0 || device >= llmcp_b200_device_count())
+      throw std::runtime_error("no such CUDA device");
+    g_device = device;
+    cuda_check(cudaSetDevice(device), "cudaSetDevice");
+  });
+}
+
+void llmcp_b200_release_all(void) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_sessions.clear();
+}
+
+uint64_t llmcp_b200_launch_count(void) { return g_launches.load(); }
+
+// ---- operators on host pointers ------------------------------------------------------
+int llmcp_op_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales) {
+  return guarded([&] {
+    require_device();
+    if (K % 32 != 0 || M < 0)
+      throw std::runtime_error("K must be a multiple of 32");
+    Buf dx(static_cast<size_t>(M) * K * elem(x_dtype), x), dq(static_cast<size_t>(M) * K), ds(static_cast<size_t>(M) * (K / 32) * 4);
+    launch_act_quant(dx.p, x_dtype, M, K, dq.as<int8_t>(), ds.as<float>(), nullptr);
+    g_launches += 1;
+    cuda_check(cudaDeviceSynchronize(), "act_quant");
+    dq.to_host(q, dq.bytes);
+    ds.to_host(scales, ds.bytes);
+  });
+}
+
+int llmcp_op_linear_q8(const void *x, int x_dtype, int64_t M, int64_t K, const uint8_t *weight, int64_t N, void *y,
+                       int y_dtype, int activation, int32_t *block_dots) {
+  return guarded([&] {
+    require_device();
+    check_q8_shape(N, K);
+    if (M <= 0)
+      return; // an empty input produces an empty output
+    DeviceQ8 w(weight, N, K);
+    Buf dx(static_cast<size_t>(M) * K * elem(x_dtype), x), dq(static_cast<size_t>(M) * K), ds(static_cast<size_t>(M) * (K / 32) * 4);
+    Buf dy(static_cast<size_t>(M) * N * elem(y_dtype));
+    Buf dots(block_dots ? static_cast<size_t>(M) * N * (K / 32) * 4 : 0);
+    launch_act_quant(dx.p, x_dtype, M, K, dq.as<int8_t>(), ds.as<float>(), nullptr);
+    g_launches += 1;
+    run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), N, dy.p, y_dtype, activation,
+               block_dots ? dots.as<int32_t>() : nullptr, 0, nullptr);
+    cuda_check(cudaDeviceSynchronize(), "linear");
+    dy.to_host(y, dy.bytes);
+    if (block_dots)
+      dots.to_host(block_dots, dots.bytes);
+  });
+}
+
+int llmcp_op_lm_head_q8(const uint16_t *hidden, int64_t M, int64_t K, const uint8_t *table, int64_t vocab,
+                        float *logits, int64_t *argmax) {
+  return guarded([&] {
+    require_device();
+    check_q8_shape(vocab, K);
+    if (M <= 0)
+      return;
+    DeviceQ8 w(table, vocab, K);
+    Buf dx(static_cast<size_t>(M) * K * 2, hidden), dq(static_cast<size_t>(M) * K), ds(static_cast<size_t>(M) * (K / 32) * 4);
+    Buf dy(static_cast<size_t>(M) * vocab * 4), sv(kArgmaxParts * 4), si(kArgmaxParts * 8), out(static_cast<size_t>(M) * 8);
+    launch_act_quant(dx.p, kBF16, M, K, dq.as<int8_t>(), ds.as<float>(), nullptr);
+    g_launches += 1;
+    run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), vocab, dy.p, kF32, kNone,
+               nullptr, 0, nullptr);
+    for (int64_t m = 0; m < M; ++m) {
+      launch_argmax(dy.as<float>() + m * vocab, vocab, sv.as<float>(), si.as<int64_t>(), 0, out.as<int64_t>() + m,
+                    nullptr, nullptr);
+      g_launches += 2;
+    }
+    cuda_check(cudaDeviceSynchronize(), "lm_head");
+    if (logits)
+      dy.to_host(logits, dy.bytes);
+    if (argmax)
+      out.to_host(argmax, out.bytes);
+  });
+}
+
+int llmcp_op_embedding_q8(const int64_t *tokens, int64_t S, const uint8_t *table, int64_t vocab, int64_t hidden,
+                          uint16_t *out) {
+  return guarded([&] {
+    require_device();
+    check_q8_shape(vocab, hidden);
+    for (int64_t i = 0; i < S; ++i)
+      if (tokens[i] < 0 || tokens[i] >= vocab)
+        throw std::runtime_error("token id outside the table");
+    if (S <= 0)
+      return;
+    DeviceQ8 w(table, vocab, hidden);
+    Buf dt(static_cast<size_t>(S) * 8, tokens), dy(static_cast<size_t>(S) * hidden * 2);
+    launch_embedding_q8(dt.as<int64_t>(), S, hidden, w.q.as<int8_t>(), w.d.as<uint16_t>(), dy.as<uint16_t>(), nullptr);
+    g_launches += 1;
+    cuda_check(cudaDeviceSynchronize(), "embedding");
+    dy.to_host(out, dy.bytes);
+  });
+}
+
+int llmcp_op_rms_norm(const uint16_t *x, int64_t M, int64_t H, const void *weight, int w_dtype, float eps,
+                      int zero_centered, uint16_t *y) {
+  return guarded([&] {
+    require_device();
+    if (M <= 0 || H <= 0)
+      return;
+    Buf dx(static_cast<size_t>(M) * H * 2, x), dw(static_cast<size_t>(H) * elem(w_dtype), weight), dy(static_cast<size_t>(M) * H * 2);
+    cuda_check(launch_rms_norm(dx.as<uint16_t>(), nullptr, M, static_cast<int>(H), dw.p, w_dtype, eps, zero_centered,
+                               nullptr, dy.as<uint16_t>(), nullptr, nullptr, nullptr), "rms_norm");
+    g_launches += 1;
+    cuda_check(cudaDeviceSynchronize(), "rms_norm");
+    dy.to_host(y, dy.bytes);
+  });
+}
+
+int llmcp_op_pointwise(const uint16_t *a, const uint16_t *b, int64_t count, int op, uint16_t *y) {
+  return guarded([&] {
+    require_device();
+    if (op < 0 || op > 2)
+      throw std::runtime_error("op must be 0 (add), 1 (mul) or 2 (silu_mul)");
+    if (count <= 0)
+      return;
+    Buf da(static_cast<size_t>(count) * 2, a), db(static_cast<size_t>(count) * 2, b), dy(static_cast<size_t>(count) * 2);
+    cuda_check(launch_pointwise(da.as<uint16_t>(), db.as<uint16_t>(), count, op, dy.as<uint16_t>(), nullptr, nullptr, nullptr), "pointwise");
+    g_launches += 1;
+    cuda_check(cudaDeviceSynchronize(), "pointwise");
+    dy.to_host(y, dy.bytes);
+  });
+}
+
+int llmcp_op_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const void *weight, int w_dtype, int64_t M,
+                            int64_t H, int64_t group, float eps, int gate_activated, uint16_t *y) {
+  return guarded([&] {
+    require_device();
+    if (group <= 0 || H % group != 0)
+      throw std::runtime_error("hidden must be a multiple of group_size");
+    if (M <= 0)
+      return;
+    Buf dx(static_cast<size_t>(M) * H * 2, x), dg(static_cast<size_t>(M) * H * 2, gate), dw(static_cast<size_t>(group) * elem(w_dtype), weight),
+        dy(static_cast<size_t>(M) * H * 2);
+    cuda_check(launch_gated_rms_norm(dx.as<uint16_t>(), dg.as<uint16_t>(), dw.p, w_dtype, M, static_cast<int>(H),
+                                     static_cast<int>(group), eps, gate_activated, dy.as<uint16_t>(), nullptr, nullptr, nullptr),
+               "gated_rms_norm");
+    g_launches += 1;
+    cuda_check(cudaDeviceSynchronize(), "gated_rms_norm");
+    dy.to_host(y, dy.bytes);
+  });
+}
+
+int llmcp_op_causal_conv1d(const uint16_t *x, const uint16_t *weight, uint16_t *state, int64_t S, int64_t C,
+                           int64_t kernel, uint16_t *y) {
+  return guarded([&] {
+    require_device();
+    if (kernel <= 1 || C <= 0)
+      throw std::runtime_error("kernel_size must exceed 1");
+    if (S <= 0)
+      return;
+    Buf dx(static_cast<size_t>(S) * C * 2, x), dw(static_cast<size_t>(C) * kernel * 2, weight), ds(static_cast<size_t>(kernel - 1) * C * 2, state),
+        dy(static_cast<size_t>(S) * C * 2);
+    cuda_check(launch_causal_conv1d(dx.as<uint16_t>(), dw.as<uint16_t>(), ds.as<uint16_t>(), S, static_cast<int>(C),
+                                    static_cast<int>(kernel), dy.as<uint16_t>(), nullptr), "causal_conv1d");
+    g_launches += 2;
+    cuda_check(cudaDeviceSynchronize(), "causal_conv1d");
+    dy.to_host(y, dy.bytes);
+    ds.to_host(state, ds.bytes);
+  });
+}
+
+int llmcp_op_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b, const float *a_log,
+                             const uint16_t *dt_bias, float *state, int64_t S, int64_t nk, int64_t nv, int64_t dk,
+                             int64_t dv, int b_activated, uint16_t *out) {
+  return guarded([&] {
+    require_device();
+    if (nk <= 0 || nv <= 0 || dk <= 0 || dv <= 0 || nv % nk != 0)
+      throw std::runtime_error("num_v_heads must be a positive multiple of num_k_heads");
+    if (S <= 0)
+      return;
+    const size_t channels = static_cast<size_t>(2 * nk * dk + nv * dv);
+    Buf dc(static_cast<size_t>(S) * channels * 2, conv), da(static_cast<size_t>(S) * nv * 2, a), db(static_cast<size_t>(S) * nv * 2, b),
+        dl(static_cast<size_t>(nv) * 4, a_log), dt(static_cast<size_t>(nv) * 2, dt_bias), ds(static_cast<size_t>(nv) * dk * dv * 4, state),
+        dout(static_cast<size_t>(S) * nv * dv * 2),
+        scratch(gdn_scratch_floats(S, static_cast<int>(nk), static_cast<int>(nv), static_cast<int>(dk)) * 4);
+    cuda_check(launch_gated_delta_net(dc.as<uint16_t>(), da.as<uint16_t>(), db.as<uint16_t>(), dl.p, kF32, dt.p, kBF16,
+                                      ds.as<float>(), S, static_cast<int>(nk), static_cast<int>(nv), static_cast<int>(dk),
+                                      static_cast<int>(dv), b_activated, scratch.as<float>(), dout.as<uint16_t>(), nullptr),
+               "gated_delta_net");
+    g_launches += 2;
+    cuda_check(cudaDeviceSynchronize(), "gated_delta_net");
+    dout.to_host(out, dout.bytes);
+    ds.to_host(state, ds.bytes);
+  });
+}
+
+int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
+                       const uint16_t *k_norm, const float *cos, const float *sin, uint16_t *cache, int64_t position,
+                       int64_t S, int64_t nh, int64_t nkv, int64_t hd, int64_t rot, int64_t cap, uint16_t *out) {
+  return guarded([&] {
+    require_device();
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || rot < 0 || rot > hd || rot % 2 != 0)
+      throw std::runtime_error("invalid head configuration");
+    if (position < 0 || position + S > cap)
+      throw std::runtime_error("tokens do not fit the KV cache");
+    if (S <= 0)
+      return;
+    Buf dqg(static_cast<size_t>(S) * nh * 2 * hd * 2, qg), dk(static_cast<size_t>(S) * nkv * hd * 2, k), dv(static_cast<size_t>(S) * nkv * hd * 2, v),
+        dqn(static_cast<size_t>(hd) * 2, q_norm), dkn(static_cast<size_t>(hd) * 2, k_norm), dcos(static_cast<size_t>(S) * rot * 4, cos),
+        dsin(static_cast<size_t>(S) * rot * 4, sin), dcache(static_cast<size_t>(2) * nkv * cap * hd * 2, cache),
+        dout(static_cast<size_t>(S) * nh * hd * 2),
+        scratch(attn_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(hd), position));
+    cuda_check(launch_attention(dqg.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(), dqn.as<uint16_t>(),
+                                dkn.as<uint16_t>(), dcos.as<float>(), dsin.as<float>(), dcache.as<uint16_t>(), position, S,
+                                static_cast<int>(nh), static_cast<int>(nkv), static_cast<int>(hd), static_cast<int>(rot), cap,
+                                scratch.p, dout.as<uint16_t>(), nullptr), "attention");
+    g_launches += 3;
+    cuda_check(cudaDeviceSynchronize(), "attention");
+    dout.to_host(out, dout.bytes);
+    dcache.to_host(cache, dcache.bytes);
+  });
+}
+
+// ---- operators on device pointers ------------------------------------------------------
+int llmcp_dev_repack_q8(const uint8_t *records, int64_t N, int64_t K, int8_t *q, uint16_t *d, void *stream) {
+  return guarded_async([&] {
+    check_q8_shape(N, K);
+    launch_repack_p4(records, N, K, q, d, static_cast<cudaStream_t>(stream));
+    g_launches += 1;
+    cuda_check(cudaGetLastError(), "repack");
+  });
+}
+
+int llmcp_dev_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales, void *stream) {
+  return guarded_async([&] {
+    if (K % 32 != 0)
+      throw std::runtime_error("K must be a multiple of 32");
+    launch_act_quant(x, x_dtype, M, K, q, scales, static_cast<cudaStream_t>(stream));
+    g_launches += 1;
+    cuda_check(cudaGetLastError(), "act_quant");
+  });
+}
+
+int llmcp_dev_gemv_q8(const int8_t *aq, const float *as, int64_t K, const int8_t *wq, const uint16_t *wd, int64_t N,
+                      void *y, int y_dtype, int activation, int rows_per_warp, void *stream) {
+  return guarded_async([&] {
+    check_q8_shape(N, K);
+    run_linear(aq, as, 1, K, wq, wd, N, y, y_dtype, activation, nullptr, rows_per_warp, static_cast<cudaStream_t>(stream));
+  });
+}
+
+int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
+                      int64_t N, void *y, int y_dtype, int activation, void *stream) {
+  return guarded_async([&] {
+    check_q8_shape(N, K);
+    if (M < 2)
+      throw std::runtime_error("llmcp_dev_gemm_q8 needs M > 1; use llmcp_dev_gemv_q8 for one row");
+    run_linear(aq, as, M, K, wq, wd, N, y, y_dtype, activation, nullptr, 0, static_cast<cudaStream_t>(stream));
+  });
+}
+
+int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *scratch_indices, int64_t *out_index,
+                     void *stream) {
+  return guarded_async([&] {
+    if (n <= 0)
+      throw std::runtime_error("argmax of an empty vector");
+    launch_argmax(x, n, scratch_values, scratch_indices, 0, out_index, nullptr, static_cast<cudaStream_t>(stream));
+    g_launches += 2;
+    cuda_check(cudaGetLastError(), "argmax");
+  });
+}
+
+// ---- container helpers and engine --------------------------------------------------------
+void llmcp_b200_default_dims(llmcp_b200_dims *d) {
+  const ModelDims m;
+  d->hidden = m.hidden;
+  d->intermediate = m.intermediate;
+  d->vocab = m.vocab;
+  d->layers = m.layers;
+  d->full_interval = m.full_interval;
+  d->heads = m.heads;
+  d->kv_heads = m.kv_heads;
+  d->head_dim = m.head_dim;
+  d->rotary = m.rotary;
+  d->lin_k_heads = m.lin_k_heads;
+  d->lin_v_heads = m.lin_v_heads;
+  d->lin_k_dim = m.lin_k_dim;
+  d->lin_v_dim = m.lin_v_dim;
+  d->conv_kernel = m.conv_kernel;
+  d->eps = m.eps;
+  d->rope_theta = m.rope_theta;
+}
+
+uint64_t llmcp_b200_synthetic_bytes(const llmcp_b200_dims *dims) {
+  try {
+    const ModelDims d = to_dims(dims);
+    check_dims(d);
+    return synthetic_container_bytes(d, nullptr);
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return 0;
+  }
+}
+
+int llmcp_b200_synthetic_fill(const llmcp_b200_dims *dims, uint64_t seed, uint8_t *file, uint64_t file_bytes) {
+  return guarded_async([&] {
+    const ModelDims d = to_dims(dims);
+    check_dims(d);
+    const std::string error = fill_synthetic_container(d, seed, file, file_bytes);
+    if (!error.empty())
+      throw std::runtime_error(error);
+  });
+}
+
+int llmcp_b200_pack_q8_0_p4(const float *values, int64_t rows, int64_t cols, uint8_t *dst) {
+  return guarded_async([&] {
+    if (!pack_q8_0_p4(values, rows, cols, dst))
+      throw std::runtime_error("packed Q8_0 needs rows % 8 == 0 and cols % 32 == 0");
+  });
+}
+
+int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes) {
+  return guarded_async([&] {
+    if (file_bytes < kHeaderBytes)
+      throw std::runtime_error("packed weights file is too small");
+    Manifest m;
+    const std::string error = parse_container(file, file_bytes, &m);
+    if (!error.empty())
+      throw std::runtime_error(error);
+  });
+}
+
+void llmcp_b200_make_cos_sin(int64_t position, int64_t rotary, float theta, float *cos_out, float *sin_out) {
+  make_cos_sin(position, rotary, theta, cos_out, sin_out);
+}
+
+uint64_t llmcp_b200_manifest(const uint8_t *file, uint64_t file_bytes, char *buffer, uint64_t capacity) {
+  uint64_t arena = 0, offset = 0, bytes = 0;
+  const std::string error = read_header(file, file_bytes, &arena, &offset, &bytes);
+  if (!error.empty()) {
+    set_error(error);
+    return 0;
+  }
+  if (buffer && capacity) {
+    const uint64_t n = std::min<uint64_t>(capacity - 1, bytes);
+    std::memcpy(buffer, file + offset, n);
+    buffer[n] = 0;
+  }
+  return bytes;
+}
+
+void *llmcp_b200_engine_create(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims, int64_t capacity,
+                               int device) {
+  try {
+    const ModelDims d = to_dims(dims);
+    check_dims(d);
+    return new Engine(file, file_bytes, d, capacity, device);
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return nullptr;
+  }
+}
+
+void llmcp_b200_engine_destroy(void *engine) { delete static_cast<Engine *>(engine); }
+
+int llmcp_b200_engine_reset(void *engine) {
+  return guarded_async([&] { static_cast<Engine *>(engine)->reset_state(); });
+}
+
+int llmcp_b200_engine_forward(void *engine, const int64_t *tokens, int64_t S, int64_t position, float *logits,
+                              int64_t *argmax) {
+  return guarded_async([&] {
+    Engine &e = *static_cast<Engine *>(engine);
+    const uint64_t before = e.launches();
+    const int64_t token = e.forward_host(tokens, S, position, nullptr, nullptr, logits);
+    g_launches += e.launches() - before;
+    if (argmax)
+      *argmax = token;
+  });
+}
+
+int llmcp_b200_engine_generate(void *engine, int64_t first_token, int64_t position, int64_t steps, int64_t *out_tokens,
+                               float *device_ms) {
+  return guarded_async([&] {
+    Engine &e = *static_cast<Engine *>(engine);
+    const uint64_t before = e.launches();
+    e.generate(first_token, position, steps, out_tokens, device_ms);
+    g_launches += e.launches() - before;
+  });
+}
+
+int llmcp_b200_engine_read_state(void *engine, uint16_t *kv, float *delta, uint16_t *conv) {
+  return guarded_async([&] { static_cast<Engine *>(engine)->download_state(kv, delta, conv); });
+}
+
+int llmcp_b200_engine_read_hidden(void *engine, uint16_t *hidden) {
+  return guarded_async([&] {
+    Engine &e = *static_cast<Engine *>(engine);
+    cuda_check(cudaMemcpy(hidden, e.final_hidden_device(), static_cast<size_t>(e.dims().hidden) * 2, cudaMemcpyDeviceToHost),
+               "read hidden");
+  });
+}
+
+} // extern "C"

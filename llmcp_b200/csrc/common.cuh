@@ -1,0 +1,88 @@
+// Shared device helpers for the llmcp Q8 operator kernels (sm_100a).
+//
+// Numerical contract of every kernel in this library: each f32 multiply, add and
+// divide is a separate IEEE round-to-nearest operation unless __fmaf_rn is written
+// (the library is compiled with -fmad=false), reductions run in the order the
+// reference's lowering runs them, and exp/log are the f32 rounding of the
+// double-precision function.  With that contract the kernels reproduce the
+// reference's f32 results bit for bit, not only within a tolerance.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace llmcp_b200 {
+
+constexpr int kBlock = 32;          // weights per Q8_0 block (Q8PackedLayout.h:21)
+constexpr int kRecordBytes = 136;   // 4 f16 scales + 8 x 16 B (Q8PackedLayout.h:24-35)
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+enum Activation : int { kNone = 0, kSilu = 1, kSigmoid = 2, kSoftplus = 3 };
+
+__host__ __device__ inline float bf16_to_f32(uint16_t v) {
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(static_cast<uint32_t>(v) << 16);
+#else
+  union { uint32_t u; float f; } c;
+  c.u = static_cast<uint32_t>(v) << 16;
+  return c.f;
+#endif
+}
+
+// arith.truncf f32 -> bf16: round to nearest, ties to even.
+__host__ __device__ inline uint16_t f32_to_bf16(float f) {
+#ifdef __CUDA_ARCH__
+  uint32_t bits = __float_as_uint(f);
+#else
+  union { uint32_t u; float f; } c;
+  c.f = f;
+  uint32_t bits = c.u;
+#endif
+  if ((bits & 0x7fffffffu) > 0x7f800000u)
+    return static_cast<uint16_t>((bits >> 16) | 0x40);
+  bits += 0x7fffu + ((bits >> 16) & 1u);
+  return static_cast<uint16_t>(bits >> 16);
+}
+
+__device__ inline float f16_bits_to_f32(uint16_t v) {
+  float f;
+  asm("{ .reg .b16 h; mov.b16 h, %1; cvt.f32.f16 %0, h; }" : "=f"(f) : "h"(v));
+  return f;
+}
+
+__device__ inline float load_as_f32(const void *p, int dtype, int64_t i) {
+  return dtype == kBF16 ? bf16_to_f32(static_cast<const uint16_t *>(p)[i])
+                        : static_cast<const float *>(p)[i];
+}
+
+__device__ inline void store_from_f32(void *p, int dtype, int64_t i, float v) {
+  if (dtype == kBF16)
+    static_cast<uint16_t *>(p)[i] = f32_to_bf16(v);
+  else
+    static_cast<float *>(p)[i] = v;
+}
+
+// exp / log as the f32 rounding of the double-precision function.
+__device__ inline float d_exp(float x) { return static_cast<float>(exp(static_cast<double>(x))); }
+__device__ inline float d_log(float x) { return static_cast<float>(log(static_cast<double>(x))); }
+// math.rsqrt lowers to 1 / sqrt(x).
+__device__ inline float d_rsqrt(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+__device__ inline float d_sigmoid(float v) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, d_exp(-v))); }
+
+// MatmulLoweringCommon.cpp:78-103
+__device__ inline float apply_activation(float v, int activation) {
+  switch (activation) {
+  case kSilu:
+    return __fmul_rn(v, d_sigmoid(v));
+  case kSigmoid:
+    return d_sigmoid(v);
+  case kSoftplus:
+    return d_log(__fadd_rn(1.0f, d_exp(v)));
+  default:
+    return v;
+  }
+}
+
+__device__ inline int dp4a(int a, int b, int c) { return __dp4a(a, b, c); }
+
+} // namespace llmcp_b200

@@ -1,0 +1,436 @@
+#include "engine.h"
+
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+
+#include "kernels.h"
+
+namespace llmcp_b200 {
+
+namespace {
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int dtype_of(const TensorEntry &t) {
+  if (t.dtype == "BF16")
+    return kBF16;
+  if (t.dtype == "F32")
+    return kF32;
+  throw std::runtime_error("tensor " + t.name + " has dtype " + t.dtype + ", expected BF16 or F32");
+}
+
+} // namespace
+
+void Engine::check(cudaError_t e, const char *what) {
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device)
+    : dims_(dims), capacity_(capacity), device_(device) {
+  if (capacity <= 0)
+    throw std::runtime_error("capacity must be positive");
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+    throw std::runtime_error("no CUDA device: this library has no CPU path");
+  check(cudaSetDevice(device), "cudaSetDevice");
+  check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+
+  Manifest manifest;
+  const std::string error = parse_container(base, file_bytes, &manifest);
+  if (!error.empty())
+    throw std::runtime_error(error);
+  if (manifest.quantization != "q8_0")
+    throw std::runtime_error("only q8_0 arenas are supported (quantization = " + manifest.quantization + ")");
+  load_weights(base, manifest);
+
+  const ModelDims &c = dims_;
+  const size_t kv_bytes = static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2;
+  const size_t delta_bytes = static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4;
+  const size_t conv_bytes = static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2;
+  auto alloc = [&](size_t bytes) {
+    void *p = nullptr;
+    check(cudaMalloc(&p, std::max<size_t>(bytes, 256)), "cudaMalloc");
+    allocations_.push_back(p);
+    return p;
+  };
+  kv_ = static_cast<uint16_t *>(alloc(kv_bytes));
+  delta_ = static_cast<float *>(alloc(delta_bytes));
+  conv_ = static_cast<uint16_t *>(alloc(conv_bytes));
+  cos_table_ = static_cast<float *>(alloc(static_cast<size_t>(capacity_) * c.rotary * 4));
+  sin_table_ = static_cast<float *>(alloc(static_cast<size_t>(capacity_) * c.rotary * 4));
+  {
+    std::vector<float> cos_host(static_cast<size_t>(capacity_) * c.rotary), sin_host(cos_host.size());
+    for (int64_t p = 0; p < capacity_; ++p)
+      make_cos_sin(p, c.rotary, c.rope_theta, cos_host.data() + p * c.rotary, sin_host.data() + p * c.rotary);
+    check(cudaMemcpy(cos_table_, cos_host.data(), cos_host.size() * 4, cudaMemcpyHostToDevice), "cos table");
+    check(cudaMemcpy(sin_table_, sin_host.data(), sin_host.size() * 4, cudaMemcpyHostToDevice), "sin table");
+  }
+  final_hidden_ = static_cast<uint16_t *>(alloc(static_cast<size_t>(c.hidden) * 2));
+  logits_ = static_cast<float *>(alloc(static_cast<size_t>(c.vocab) * 4));
+  argmax_v_ = static_cast<float *>(alloc(kArgmaxParts * 4));
+  argmax_i_ = static_cast<int64_t *>(alloc(kArgmaxParts * 8));
+  next_token_ = static_cast<int64_t *>(alloc(8));
+  generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
+  check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
+  check(cudaMallocHost(&token_pinned_, 8), "cudaMallocHost");
+  reset_state();
+  ensure_workspace(1, capacity_ - 1);
+  check(cudaStreamSynchronize(stream_), "engine setup");
+}
+
+Engine::~Engine() {
+  cudaSetDevice(device_);
+  if (stream_)
+    cudaStreamSynchronize(stream_);
+  for (void *p : ws_allocations_)
+    cudaFree(p);
+  for (void *p : allocations_)
+    cudaFree(p);
+  if (logits_pinned_)
+    cudaFreeHost(logits_pinned_);
+  if (token_pinned_)
+    cudaFreeHost(token_pinned_);
+  if (stream_)
+    cudaStreamDestroy(stream_);
+}
+
+void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
+  const ModelDims &c = dims_;
+  const std::string root = "model.language_model.";
+  // One pool for all device weights; a staging buffer for the largest packed tensor.
+  size_t pool_bytes = 0, staging_bytes = 0;
+  for (const TensorEntry &t : manifest.tensors) {
+    if (t.dtype == "Q8_0") {
+      const size_t n = static_cast<size_t>(t.shape[0]), k = static_cast<size_t>(t.shape[1]);
+      pool_bytes += round_up(n * k, 256) + round_up(n * (k / 32) * 2, 256);
+      staging_bytes = std::max<size_t>(staging_bytes, t.size);
+    } else {
+      pool_bytes += round_up(t.size, 256);
+    }
+  }
+  uint8_t *pool = nullptr, *staging = nullptr;
+  check(cudaMalloc(&pool, pool_bytes), "cudaMalloc(weights)");
+  allocations_.push_back(pool);
+  check(cudaMalloc(&staging, std::max<size_t>(staging_bytes, 256)), "cudaMalloc(staging)");
+  size_t cursor = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t *p = pool + cursor;
+    cursor += round_up(bytes, 256);
+    return p;
+  };
+
+  auto q8 = [&](const std::string &name, int64_t rows, int64_t cols) {
+    const TensorEntry *t = manifest.find(name);
+    if (!t)
+      throw std::runtime_error("missing tensor " + name);
+    if (t->dtype != "Q8_0" || t->shape.size() != 2 || t->shape[0] != rows || t->shape[1] != cols)
+      throw std::runtime_error("tensor " + name + " is not Q8_0 [" + std::to_string(rows) + ", " +
+                               std::to_string(cols) + "]");
+    Q8Weight w;
+    w.N = static_cast<int>(rows);
+    w.K = static_cast<int>(cols);
+    w.q = reinterpret_cast<int8_t *>(take(static_cast<size_t>(rows) * cols));
+    w.d = reinterpret_cast<uint16_t *>(take(static_cast<size_t>(rows) * (cols / 32) * 2));
+    check(cudaMemcpyAsync(staging, base + t->offset, t->size, cudaMemcpyHostToDevice, stream_), "upload weights");
+    launch_repack_p4(staging, rows, cols, w.q, w.d, stream_);
+    check(cudaGetLastError(), "repack");
+    return w;
+  };
+  auto small = [&](const std::string &name, int64_t elements) {
+    const TensorEntry *t = manifest.find(name);
+    if (!t)
+      throw std::runtime_error("missing tensor " + name);
+    SmallTensor s;
+    s.dtype = dtype_of(*t);
+    uint64_t count = 1;
+    for (int64_t d : t->shape)
+      count *= static_cast<uint64_t>(d);
+    if (static_cast<int64_t>(count) != elements)
+      throw std::runtime_error("tensor " + name + " has " + std::to_string(count) + " elements, expected " +
+                               std::to_string(elements));
+    s.data = take(t->size);
+    check(cudaMemcpyAsync(s.data, base + t->offset, t->size, cudaMemcpyHostToDevice, stream_), "upload tensor");
+    return s;
+  };
+
+  embed_ = q8(root + "embed_tokens.weight", c.vocab, c.hidden);
+  layers_.resize(static_cast<size_t>(c.layers));
+  for (int64_t l = 0; l < c.layers; ++l) {
+    LayerWeights &L = layers_[static_cast<size_t>(l)];
+    const std::string p = root + "layers." + std::to_string(l) + ".";
+    L.full = c.is_full(l);
+    L.input_norm = small(p + "input_layernorm.weight", c.hidden);
+    L.post_norm = small(p + "post_attention_layernorm.weight", c.hidden);
+    if (!L.full) {
+      L.qkv = q8(p + "linear_attn.in_proj_qkv.weight", c.qkv_dim(), c.hidden);
+      L.z = q8(p + "linear_attn.in_proj_z.weight", c.value_dim(), c.hidden);
+      L.a = q8(p + "linear_attn.in_proj_a.weight", c.lin_v_heads, c.hidden);
+      L.b = q8(p + "linear_attn.in_proj_b.weight", c.lin_v_heads, c.hidden);
+      L.conv = small(p + "linear_attn.conv1d.weight", c.qkv_dim() * c.conv_kernel);
+      if (L.conv.dtype != kBF16)
+        throw std::runtime_error("conv1d.weight must be BF16");
+      L.dt_bias = small(p + "linear_attn.dt_bias", c.lin_v_heads);
+      L.a_log = small(p + "linear_attn.A_log", c.lin_v_heads);
+      L.lin_norm = small(p + "linear_attn.norm.weight", c.lin_v_dim);
+      L.out_proj = q8(p + "linear_attn.out_proj.weight", c.hidden, c.value_dim());
+    } else {
+      L.q_proj = q8(p + "self_attn.q_proj.weight", c.q_out(), c.hidden);
+      L.k_proj = q8(p + "self_attn.k_proj.weight", c.kv_dim(), c.hidden);
+      L.v_proj = q8(p + "self_attn.v_proj.weight", c.kv_dim(), c.hidden);
+      L.o_proj = q8(p + "self_attn.o_proj.weight", c.hidden, c.attn_dim());
+      L.q_norm = small(p + "self_attn.q_norm.weight", c.head_dim);
+      L.k_norm = small(p + "self_attn.k_norm.weight", c.head_dim);
+      if (L.q_norm.dtype != kBF16 || L.k_norm.dtype != kBF16)
+        throw std::runtime_error("q_norm / k_norm must be BF16");
+    }
+    L.gate = q8(p + "mlp.gate_proj.weight", c.intermediate, c.hidden);
+    L.up = q8(p + "mlp.up_proj.weight", c.intermediate, c.hidden);
+    L.down = q8(p + "mlp.down_proj.weight", c.hidden, c.intermediate);
+  }
+  final_norm_ = small(root + "norm.weight", c.hidden);
+  check(cudaStreamSynchronize(stream_), "weight upload");
+  cudaFree(staging);
+}
+
+void Engine::reset_state() {
+  const ModelDims &c = dims_;
+  check(cudaMemsetAsync(kv_, 0, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, stream_), "memset");
+  check(cudaMemsetAsync(delta_, 0, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, stream_), "memset");
+  check(cudaMemsetAsync(conv_, 0, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, stream_), "memset");
+}
+
+void Engine::upload_state(const uint16_t *kv, const float *delta, const uint16_t *conv) {
+  const ModelDims &c = dims_;
+  check(cudaMemcpyAsync(kv_, kv, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, cudaMemcpyHostToDevice, stream_), "upload kv");
+  check(cudaMemcpyAsync(delta_, delta, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, cudaMemcpyHostToDevice, stream_), "upload delta");
+  check(cudaMemcpyAsync(conv_, conv, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, cudaMemcpyHostToDevice, stream_), "upload conv");
+  check(cudaStreamSynchronize(stream_), "upload state");
+}
+
+void Engine::download_state(uint16_t *kv, float *delta, uint16_t *conv) {
+  const ModelDims &c = dims_;
+  if (kv)
+    check(cudaMemcpyAsync(kv, kv_, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, cudaMemcpyDeviceToHost, stream_), "download kv");
+  if (delta)
+    check(cudaMemcpyAsync(delta, delta_, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, cudaMemcpyDeviceToHost, stream_), "download delta");
+  if (conv)
+    check(cudaMemcpyAsync(conv, conv_, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, cudaMemcpyDeviceToHost, stream_), "download conv");
+  check(cudaStreamSynchronize(stream_), "download state");
+}
+
+void Engine::ensure_workspace(int64_t S, int64_t position) {
+  const ModelDims &c = dims_;
+  const size_t need_attn = attn_scratch_bytes(S, static_cast<int>(c.heads), static_cast<int>(c.head_dim), position);
+  if (S <= ws_tokens_ && need_attn <= attn_scratch_bytes_)
+    return;
+  check(cudaStreamSynchronize(stream_), "workspace resize");
+  for (void *p : ws_allocations_)
+    cudaFree(p);
+  ws_allocations_.clear();
+  const int64_t rows = std::max(S, ws_tokens_);
+  auto alloc = [&](size_t bytes) {
+    void *p = nullptr;
+    check(cudaMalloc(&p, std::max<size_t>(bytes, 256)), "cudaMalloc(workspace)");
+    ws_allocations_.push_back(p);
+    return p;
+  };
+  const size_t r = static_cast<size_t>(rows);
+  const size_t max_k = static_cast<size_t>(std::max({c.hidden, c.intermediate, c.value_dim(), c.attn_dim()}));
+  tokens_ = static_cast<int64_t *>(alloc(r * 8));
+  cos_ = static_cast<float *>(alloc(r * c.rotary * 4));
+  sin_ = static_cast<float *>(alloc(r * c.rotary * 4));
+  hidden_[0] = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
+  hidden_[1] = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
+  branch_ = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
+  mlp_out_ = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
+  aq_ = static_cast<int8_t *>(alloc(r * max_k));
+  as_ = static_cast<float *>(alloc(r * (max_k / 32) * 4));
+  qkv_ = static_cast<uint16_t *>(alloc(r * c.qkv_dim() * 2));
+  z_ = static_cast<uint16_t *>(alloc(r * c.value_dim() * 2));
+  a_ = static_cast<uint16_t *>(alloc(r * c.lin_v_heads * 2));
+  b_ = static_cast<uint16_t *>(alloc(r * c.lin_v_heads * 2));
+  convd_ = static_cast<uint16_t *>(alloc(r * c.qkv_dim() * 2));
+  gdn_ = static_cast<uint16_t *>(alloc(r * c.value_dim() * 2));
+  qg_ = static_cast<uint16_t *>(alloc(r * c.q_out() * 2));
+  k_ = static_cast<uint16_t *>(alloc(r * c.kv_dim() * 2));
+  v_ = static_cast<uint16_t *>(alloc(r * c.kv_dim() * 2));
+  attn_ = static_cast<uint16_t *>(alloc(r * c.attn_dim() * 2));
+  gate_ = static_cast<uint16_t *>(alloc(r * c.intermediate * 2));
+  up_ = static_cast<uint16_t *>(alloc(r * c.intermediate * 2));
+  gdn_scratch_ = static_cast<float *>(alloc(
+      gdn_scratch_floats(rows, static_cast<int>(c.lin_k_heads), static_cast<int>(c.lin_v_heads), static_cast<int>(c.lin_k_dim)) * 4));
+  attn_scratch_bytes_ = std::max(need_attn, attn_scratch_bytes_);
+  attn_scratch_ = alloc(attn_scratch_bytes_);
+  ws_tokens_ = rows;
+}
+
+struct LinearJob {
+  const Q8Weight *w;
+  void *y;
+  int y_dtype;
+  int activation;
+};
+
+static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
+                        cudaStream_t stream, uint64_t *launches) {
+  if (S == 1) {
+    GemvJobs g{};
+    g.count = count;
+    for (int i = 0; i < count; ++i) {
+      g.job[i].wq = jobs[i].w->q;
+      g.job[i].wd = jobs[i].w->d;
+      g.job[i].y = jobs[i].y;
+      g.job[i].N = jobs[i].w->N;
+      g.job[i].activation = jobs[i].activation;
+      g.job[i].y_dtype = jobs[i].y_dtype;
+    }
+    cudaError_t e = launch_gemv_q8(aq, as, jobs[0].w->K, g, nullptr, stream);
+    if (e != cudaSuccess)
+      throw std::runtime_error(std::string("gemv: ") + cudaGetErrorString(e));
+    *launches += 1;
+    return;
+  }
+  for (int i = 0; i < count; ++i) {
+    cudaError_t e = launch_gemm_q8_dp4a(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d,
+                                        jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, stream);
+    if (e != cudaSuccess)
+      throw std::runtime_error(std::string("gemm: ") + cudaGetErrorString(e));
+    *launches += 1;
+  }
+}
+
+void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const float *cos_dev, const float *sin_dev) {
+  const ModelDims &c = dims_;
+  const int H = static_cast<int>(c.hidden);
+  if (S <= 0 || position < 0 || position + S > capacity_)
+    throw std::runtime_error("sequence does not fit the cache: position " + std::to_string(position) + " + " +
+                             std::to_string(S) + " > capacity " + std::to_string(capacity_));
+  ensure_workspace(S, position);
+  launch_embedding_q8(tokens_dev, S, H, embed_.q, embed_.d, hidden_[0], stream_);
+  launches_ += 1;
+  int cur = 0;
+  bool pending = false;
+  int64_t lin_index = 0, full_index = 0;
+  for (int64_t l = 0; l < c.layers; ++l) {
+    const LayerWeights &L = layers_[static_cast<size_t>(l)];
+    if (pending) {
+      check(launch_rms_norm(hidden_[cur], mlp_out_, S, H, L.input_norm.data, L.input_norm.dtype, c.eps, 1,
+                            hidden_[cur ^ 1], nullptr, aq_, as_, stream_), "rms_norm");
+      cur ^= 1;
+    } else {
+      check(launch_rms_norm(hidden_[cur], nullptr, S, H, L.input_norm.data, L.input_norm.dtype, c.eps, 1, nullptr,
+                            nullptr, aq_, as_, stream_), "rms_norm");
+    }
+    launches_ += 1;
+    if (!L.full) {
+      const LinearJob jobs[4] = {{&L.qkv, qkv_, kBF16, kNone},
+                                 {&L.z, z_, kBF16, kSilu},
+                                 {&L.a, a_, kBF16, kNone},
+                                 {&L.b, b_, kBF16, kSigmoid}};
+      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_);
+      const int C = static_cast<int>(c.qkv_dim());
+      check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data),
+                                 conv_ + lin_index * (c.conv_kernel - 1) * C, S, C, static_cast<int>(c.conv_kernel),
+                                 convd_, stream_), "causal_conv1d");
+      check(launch_gated_delta_net(convd_, a_, b_, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype,
+                                   delta_ + lin_index * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim, S,
+                                   static_cast<int>(c.lin_k_heads), static_cast<int>(c.lin_v_heads),
+                                   static_cast<int>(c.lin_k_dim), static_cast<int>(c.lin_v_dim), 1, gdn_scratch_, gdn_,
+                                   stream_), "gated_delta_net");
+      check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(c.value_dim()),
+                                  static_cast<int>(c.lin_v_dim), c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
+      launches_ += 5;
+      const LinearJob out = {&L.out_proj, branch_, kBF16, kNone};
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_);
+      ++lin_index;
+    } else {
+      const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
+      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_);
+      check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
+                             static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev,
+                             kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim, position, S,
+                             static_cast<int>(c.heads), static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim),
+                             static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, stream_), "attention");
+      launch_act_quant(attn_, kBF16, S, c.attn_dim(), aq_, as_, stream_);
+      launches_ += 4;
+      const LinearJob out = {&L.o_proj, branch_, kBF16, kNone};
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_);
+      ++full_index;
+    }
+    check(launch_rms_norm(hidden_[cur], branch_, S, H, L.post_norm.data, L.post_norm.dtype, c.eps, 1, hidden_[cur ^ 1],
+                          nullptr, aq_, as_, stream_), "rms_norm");
+    cur ^= 1;
+    const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
+    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_);
+    check(launch_pointwise(gate_, up_, S * c.intermediate, 1, nullptr, aq_, as_, stream_), "mul");
+    launches_ += 2;
+    const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
+    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_);
+    pending = true;
+  }
+  // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
+  const uint16_t *last = hidden_[cur] + (S - 1) * H;
+  check(launch_rms_norm(last, pending ? mlp_out_ + (S - 1) * H : nullptr, 1, H, final_norm_.data, final_norm_.dtype,
+                        c.eps, 1, nullptr, final_hidden_, aq_, as_, stream_), "final rms_norm");
+  const Q8Weight &table = embed_;
+  const LinearJob head = {&table, logits_, kF32, kNone};
+  run_linears(this, aq_, as_, 1, &head, 1, stream_, &launches_);
+  launch_argmax(logits_, c.vocab, argmax_v_, argmax_i_, 0, next_token_, nullptr, stream_);
+  launches_ += 3;
+  check(cudaGetLastError(), "forward");
+}
+
+int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position, const float *cos, const float *sin,
+                             float *logits_host) {
+  const ModelDims &c = dims_;
+  check(cudaSetDevice(device_), "cudaSetDevice");
+  if (S <= 0 || position < 0 || position + S > capacity_)
+    throw std::runtime_error("sequence does not fit the cache");
+  ensure_workspace(S, position);
+  check(cudaMemcpyAsync(tokens_, tokens, static_cast<size_t>(S) * 8, cudaMemcpyHostToDevice, stream_), "tokens");
+  const float *cos_dev = cos_table_ + position * c.rotary, *sin_dev = sin_table_ + position * c.rotary;
+  if (cos && sin) {
+    check(cudaMemcpyAsync(cos_, cos, static_cast<size_t>(S) * c.rotary * 4, cudaMemcpyHostToDevice, stream_), "cos");
+    check(cudaMemcpyAsync(sin_, sin, static_cast<size_t>(S) * c.rotary * 4, cudaMemcpyHostToDevice, stream_), "sin");
+    cos_dev = cos_;
+    sin_dev = sin_;
+  }
+  run(tokens_, S, position, cos_dev, sin_dev);
+  if (logits_host)
+    check(cudaMemcpyAsync(logits_pinned_, logits_, static_cast<size_t>(c.vocab) * 4, cudaMemcpyDeviceToHost, stream_), "logits");
+  check(cudaMemcpyAsync(token_pinned_, next_token_, 8, cudaMemcpyDeviceToHost, stream_), "argmax");
+  check(cudaStreamSynchronize(stream_), "forward");
+  if (logits_host)
+    std::memcpy(logits_host, logits_pinned_, static_cast<size_t>(c.vocab) * 4);
+  return *token_pinned_;
+}
+
+void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int64_t *out_tokens_host, float *device_ms) {
+  const ModelDims &c = dims_;
+  check(cudaSetDevice(device_), "cudaSetDevice");
+  if (steps <= 0 || position < 0 || position + steps > capacity_)
+    throw std::runtime_error("generation does not fit the cache");
+  *token_pinned_ = first_token;
+  check(cudaMemcpyAsync(next_token_, token_pinned_, 8, cudaMemcpyHostToDevice, stream_), "first token");
+  cudaEvent_t begin, end;
+  check(cudaEventCreate(&begin), "event");
+  check(cudaEventCreate(&end), "event");
+  check(cudaEventRecord(begin, stream_), "event");
+  for (int64_t i = 0; i < steps; ++i) {
+    const int64_t p = position + i;
+    run(next_token_, 1, p, cos_table_ + p * c.rotary, sin_table_ + p * c.rotary);
+    check(cudaMemcpyAsync(generated_ + i, next_token_, 8, cudaMemcpyDeviceToDevice, stream_), "record token");
+  }
+  check(cudaEventRecord(end, stream_), "event");
+  check(cudaStreamSynchronize(stream_), "generate");
+  if (device_ms)
+    check(cudaEventElapsedTime(device_ms, begin, end), "event");
+  cudaEventDestroy(begin);
+  cudaEventDestroy(end);
+  if (out_tokens_host)
+    check(cudaMemcpy(out_tokens_host, generated_, static_cast<size_t>(steps) * 8, cudaMemcpyDeviceToHost), "tokens");
+}
+
+} // namespace llmcp_b200

@@ -1,0 +1,128 @@
+// Model executor: owns the device copy of a packed arena (weights re-laid out for the GPU),
+// the device-resident generation state, the activation workspace, and runs the graph of
+// lib/Model/ModelBuilder.cpp:218-526 (after FuseLinearActivations.cpp:27-77) with the kernels
+// of this library.
+#pragma once
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "format.h"
+
+namespace llmcp_b200 {
+
+struct Q8Weight {
+  int8_t *q = nullptr;   // [N][K]
+  uint16_t *d = nullptr; // [N][K/32]
+  int N = 0, K = 0;
+};
+
+struct SmallTensor {
+  void *data = nullptr;
+  int dtype = 0; // DType
+};
+
+struct LayerWeights {
+  bool full = false;
+  SmallTensor input_norm, post_norm;
+  Q8Weight qkv, z, a, b, out_proj;
+  SmallTensor conv, dt_bias, a_log, lin_norm;
+  Q8Weight q_proj, k_proj, v_proj, o_proj;
+  SmallTensor q_norm, k_norm;
+  Q8Weight gate, up, down;
+};
+
+class Engine {
+public:
+  // `base` points at the first byte of a mapped container (header, arena, manifest).
+  // Throws std::runtime_error with a readable message on any failure.
+  Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device);
+  ~Engine();
+  Engine(const Engine &) = delete;
+  Engine &operator=(const Engine &) = delete;
+
+  const ModelDims &dims() const { return dims_; }
+  int64_t capacity() const { return capacity_; }
+  int device() const { return device_; }
+  cudaStream_t stream() const { return stream_; }
+
+  void reset_state();
+  // Host <-> device copies of the three state buffers in the reference's layouts:
+  // kv [full, 2, kv_heads, capacity, head_dim] bf16, delta [linear, v_heads, k_dim, v_dim] f32,
+  // conv [linear, kernel-1, qkv_dim] bf16.
+  void upload_state(const uint16_t *kv, const float *delta, const uint16_t *conv);
+  void download_state(uint16_t *kv, float *delta, uint16_t *conv);
+
+  // One AOT entry call with host buffers: S tokens starting at `position`; writes the last
+  // position's logits (vocab f32) to `logits_host` if not null and returns its argmax.
+  // cos/sin may be null, in which case the rows are computed from the position.
+  int64_t forward_host(const int64_t *tokens, int64_t S, int64_t position, const float *cos, const float *sin,
+                       float *logits_host);
+
+  // Greedy generation that never leaves the device: feeds `first_token` at `position`, then
+  // each step's argmax to the next, for `steps` steps.  out_tokens_host (steps entries) gets
+  // the argmax of every step; device_ms, if not null, the CUDA-event time of the loop.
+  void generate(int64_t first_token, int64_t position, int64_t steps, int64_t *out_tokens_host, float *device_ms);
+
+  // Device pointers for inspection by tests.
+  const float *logits_device() const { return logits_; }
+  const uint16_t *final_hidden_device() const { return final_hidden_; }
+
+  uint64_t launches() const { return launches_; }
+
+private:
+  void load_weights(const uint8_t *base, const Manifest &manifest);
+  void ensure_workspace(int64_t S, int64_t position);
+  // tokens_dev: S ids on the device; cos/sin rows for positions [position, position+S).
+  void run(const int64_t *tokens_dev, int64_t S, int64_t position, const float *cos_dev, const float *sin_dev);
+  void linear(const Q8Weight &w, int64_t S, void *y, int y_dtype, int activation);
+  void check(cudaError_t e, const char *what);
+
+  ModelDims dims_;
+  int64_t capacity_ = 0;
+  int device_ = 0;
+  cudaStream_t stream_ = nullptr;
+  uint64_t launches_ = 0;
+
+  std::vector<void *> allocations_;
+  std::vector<LayerWeights> layers_;
+  Q8Weight embed_;
+  SmallTensor final_norm_;
+
+  // state
+  uint16_t *kv_ = nullptr;
+  float *delta_ = nullptr;
+  uint16_t *conv_ = nullptr;
+  float *cos_table_ = nullptr, *sin_table_ = nullptr; // [capacity, rotary]
+
+  // workspace (sized for ws_tokens_ rows)
+  int64_t ws_tokens_ = 0;
+  size_t attn_scratch_bytes_ = 0;
+  int64_t *tokens_ = nullptr;
+  float *cos_ = nullptr, *sin_ = nullptr;
+  uint16_t *hidden_[2] = {nullptr, nullptr};
+  uint16_t *branch_ = nullptr, *mlp_out_ = nullptr;
+  int8_t *aq_ = nullptr;
+  float *as_ = nullptr;
+  uint16_t *qkv_ = nullptr, *z_ = nullptr, *a_ = nullptr, *b_ = nullptr, *convd_ = nullptr, *gdn_ = nullptr;
+  uint16_t *qg_ = nullptr, *k_ = nullptr, *v_ = nullptr, *attn_ = nullptr;
+  uint16_t *gate_ = nullptr, *up_ = nullptr;
+  float *gdn_scratch_ = nullptr;
+  void *attn_scratch_ = nullptr;
+  std::vector<void *> ws_allocations_;
+
+  // outputs
+  uint16_t *final_hidden_ = nullptr; // [hidden] last row after the final norm
+  float *logits_ = nullptr;          // [vocab]
+  float *argmax_v_ = nullptr;
+  int64_t *argmax_i_ = nullptr;
+  int64_t *next_token_ = nullptr; // device scalar
+  int64_t *generated_ = nullptr;  // device [capacity]
+  float *logits_pinned_ = nullptr;
+  int64_t *token_pinned_ = nullptr;
+};
+
+} // namespace llmcp_b200

@@ -1,0 +1,68 @@
+// Launchers of the llmcp operator kernels.  All pointers are device pointers; every
+// launcher enqueues on `stream` and returns without synchronising.
+#pragma once
+
+#include <algorithm>
+#include <cstddef>
+#include <cstdint>
+
+#include "common.cuh"
+
+namespace llmcp_b200 {
+
+constexpr int kMaxGemvJobs = 4;
+constexpr int kArgmaxParts = 512;
+
+// One weight matrix of a decode GEMV launch; all jobs of a launch share the input row.
+struct GemvJob {
+  const int8_t *wq;   // [N][K] int8
+  const uint16_t *wd; // [N][K/32] f16 bits
+  void *y;            // [N] output
+  int N;
+  int activation;
+  int y_dtype;
+  int warp_begin;  // filled by the launcher
+  int dots_offset; // filled by the launcher
+};
+
+struct GemvJobs {
+  GemvJob job[kMaxGemvJobs];
+  int count;
+};
+
+void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint16_t *d, cudaStream_t stream);
+void launch_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *s, cudaStream_t stream);
+cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
+                           cudaStream_t stream, int rows_per_warp = 0);
+cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K, const int8_t *wq,
+                                const uint16_t *wd, int N, void *y, int y_dtype, int activation,
+                                int32_t *dots_out, cudaStream_t stream);
+void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, const int8_t *wq, const uint16_t *wd,
+                         uint16_t *out, cudaStream_t stream);
+// scratch_v / scratch_i: kArgmaxParts entries each.
+void launch_argmax(const float *x, int64_t n, float *scratch_v, int64_t *scratch_i, int64_t index_base,
+                   int64_t *out_index, float *out_value, cudaStream_t stream);
+
+cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int H, const void *w, int w_dtype,
+                            float eps, int zero_centered, uint16_t *sum_out, uint16_t *y, int8_t *q, float *s,
+                            cudaStream_t stream);
+cudaError_t launch_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const void *w, int w_dtype, int64_t M,
+                                  int H, int group, float eps, int gate_activated, uint16_t *y, int8_t *q,
+                                  float *s, cudaStream_t stream);
+cudaError_t launch_pointwise(const uint16_t *a, const uint16_t *b, int64_t count, int op, uint16_t *y, int8_t *q,
+                             float *s, cudaStream_t stream);
+
+cudaError_t launch_causal_conv1d(const uint16_t *x, const uint16_t *w, uint16_t *state, int64_t S, int C,
+                                 int kernel, uint16_t *y, cudaStream_t stream);
+size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk);
+cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b, const void *a_log,
+                                   int a_log_dtype, const void *dt_bias, int dt_dtype, float *state, int64_t S,
+                                   int nk, int nv, int dk, int dv, int b_activated, float *scratch,
+                                   uint16_t *out, cudaStream_t stream);
+size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t position);
+cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
+                             const uint16_t *k_norm, const float *cos, const float *sin, uint16_t *cache,
+                             int64_t position, int64_t S, int nh, int nkv, int hd, int rot, int64_t cap,
+                             void *scratch, uint16_t *out, cudaStream_t stream);
+
+} // namespace llmcp_b200

@@ -1,0 +1,412 @@
+// Token mixers of the Qwen3.5 layers: causal_conv1d, the gated_delta_net recurrence and
+// the gated GQA attention.  Every reduction keeps the reference's order (see common.cuh),
+// and parallelism comes only from dimensions the reference treats as independent:
+// channels and time for the convolution, value columns and heads for the recurrence,
+// keys (scores) and head-dim lanes (weighted sum) for attention.
+
+#include "kernels.h"
+
+namespace llmcp_b200 {
+
+// ---------------------------------------------------------------------------------
+// causal_conv1d + SiLU (LowerCausalConv1d.cpp:74-182).  state: [kernel-1, C] bf16.
+// ---------------------------------------------------------------------------------
+__global__ void causal_conv1d_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
+                                     const uint16_t *__restrict__ state, int64_t S, int C, int kernel,
+                                     uint16_t *__restrict__ y) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i >= S * C)
+    return;
+  const int64_t t = i / C;
+  const int c = static_cast<int>(i % C);
+  const int state_len = kernel - 1;
+  float acc = 0.0f;
+  for (int k = 0; k < kernel; ++k) {
+    const int64_t src = t + k - state_len;
+    const uint16_t raw = src < 0 ? state[(src + state_len) * C + c] : x[src * C + c];
+    acc = __fadd_rn(acc, __fmul_rn(bf16_to_f32(raw), bf16_to_f32(w[c * kernel + k])));
+  }
+  y[i] = f32_to_bf16(__fmul_rn(acc, d_sigmoid(acc)));
+}
+
+// New state = last kernel-1 rows of [state; x]; one thread per channel walks the rows in
+// ascending order, which is the order the in-place update needs.
+__global__ void conv_state_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ state, int64_t S,
+                                  int C, int kernel) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C)
+    return;
+  const int state_len = kernel - 1;
+  for (int s = 0; s < state_len; ++s) {
+    const int64_t src = S - state_len + s;
+    state[s * C + c] = src < 0 ? state[(src + state_len) * C + c] : x[src * C + c];
+  }
+}
+
+cudaError_t launch_causal_conv1d(const uint16_t *x, const uint16_t *w, uint16_t *state, int64_t S, int C,
+                                 int kernel, uint16_t *y, cudaStream_t stream) {
+  if (S == 0)
+    return cudaSuccess;
+  const int64_t total = S * C;
+  causal_conv1d_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(x, w, state, S, C, kernel, y);
+  conv_state_kernel<<<(C + 255) / 256, 256, 0, stream>>>(x, state, S, C, kernel);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------
+// gated_delta_net (LowerGatedDeltaNet.cpp:129-445).
+//
+// Step 1 (parallel over tokens): L2-normalised q and k per key head, beta and decay per
+// value head.  Step 2 (sequential over tokens, parallel over value columns): one thread
+// owns column v of a head's [dk, dv] state, keeps it in registers across the tokens of the
+// call, and runs the two ascending-k chains of each token.
+// ---------------------------------------------------------------------------------
+__global__ void gdn_prepare_kernel(const uint16_t *__restrict__ conv, const uint16_t *__restrict__ a,
+                                   const uint16_t *__restrict__ b, const void *__restrict__ a_log,
+                                   int a_log_dtype, const void *__restrict__ dt_bias, int dt_dtype,
+                                   int64_t S, int nk, int nv, int dk, int dv, int b_activated,
+                                   float *__restrict__ qn, float *__restrict__ kn,
+                                   float *__restrict__ beta, float *__restrict__ decay) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t channels = 2 * static_cast<int64_t>(nk) * dk + static_cast<int64_t>(nv) * dv;
+  const float q_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(dk)));
+  if (i < S * nk) {
+    const int64_t t = i / nk;
+    const int kh = static_cast<int>(i % nk);
+    const uint16_t *qp = conv + t * channels + kh * dk;
+    const uint16_t *kp = conv + t * channels + static_cast<int64_t>(nk) * dk + kh * dk;
+    float q_sum = 0.0f, k_sum = 0.0f;
+    for (int d = 0; d < dk; ++d) {
+      const float v = bf16_to_f32(qp[d]);
+      q_sum = __fadd_rn(q_sum, __fmul_rn(v, v));
+    }
+    for (int d = 0; d < dk; ++d) {
+      const float v = bf16_to_f32(kp[d]);
+      k_sum = __fadd_rn(k_sum, __fmul_rn(v, v));
+    }
+    const float q_norm_scale = __fmul_rn(d_rsqrt(__fadd_rn(q_sum, 1.0e-6f)), q_scale);
+    const float k_inv = d_rsqrt(__fadd_rn(k_sum, 1.0e-6f));
+    float *qo = qn + (t * nk + kh) * dk;
+    float *ko = kn + (t * nk + kh) * dk;
+    for (int d = 0; d < dk; ++d) {
+      qo[d] = __fmul_rn(bf16_to_f32(qp[d]), q_norm_scale);
+      ko[d] = __fmul_rn(bf16_to_f32(kp[d]), k_inv);
+    }
+  }
+  if (i < S * nv) {
+    const int h = static_cast<int>(i % nv);
+    const float bv = bf16_to_f32(b[i]);
+    beta[i] = b_activated ? bv : d_sigmoid(bv);
+    // dt_bias is widened from bf16, A_log is read as f32 (LowerGatedDeltaNet.cpp:233-246).
+    const float dt = bf16_to_f32(f32_to_bf16(load_as_f32(dt_bias, dt_dtype, h)));
+    const float a_plus_dt = __fadd_rn(bf16_to_f32(a[i]), dt);
+    const float softplus = d_log(__fadd_rn(1.0f, d_exp(a_plus_dt)));
+    const float g = __fmul_rn(-d_exp(load_as_f32(a_log, a_log_dtype, h)), softplus);
+    decay[i] = d_exp(g);
+  }
+}
+
+// DK > 0: state column in registers (DK values).  DK == 0: any dk, state stays in memory.
+template <int DK>
+__global__ void __launch_bounds__(32)
+gdn_recurrence_kernel(const uint16_t *__restrict__ conv, const float *__restrict__ qn,
+                      const float *__restrict__ kn, const float *__restrict__ beta,
+                      const float *__restrict__ decay, float *__restrict__ state, int64_t S, int nk,
+                      int nv, int dk_rt, int dv, uint16_t *__restrict__ out) {
+  const int dk = DK > 0 ? DK : dk_rt;
+  const int h = blockIdx.x;
+  const int v = blockIdx.y * 32 + threadIdx.x;
+  const int kh = h / (nv / nk);
+  const int64_t channels = 2 * static_cast<int64_t>(nk) * dk + static_cast<int64_t>(nv) * dv;
+  const bool active = v < dv;
+  float *col = state + static_cast<int64_t>(h) * dk * dv + (active ? v : 0);
+  extern __shared__ float kq_sm[]; // kn[dk], qn[dk] of the current token
+  float *k_sm = kq_sm, *q_sm = kq_sm + dk;
+
+  float s[DK > 0 ? DK : 1];
+  if (DK > 0) {
+#pragma unroll
+    for (int k = 0; k < DK; ++k)
+      s[k] = active ? col[static_cast<int64_t>(k) * dv] : 0.0f;
+  }
+  for (int64_t t = 0; t < S; ++t) {
+    __syncwarp();
+    for (int d = threadIdx.x; d < dk; d += 32) {
+      k_sm[d] = kn[(t * nk + kh) * dk + d];
+      q_sm[d] = qn[(t * nk + kh) * dk + d];
+    }
+    __syncwarp();
+    const float dc = decay[t * nv + h];
+    const float bt = beta[t * nv + h];
+    const float value = active ? bf16_to_f32(conv[t * channels + 2 * static_cast<int64_t>(nk) * dk + h * dv + v]) : 0.0f;
+    float kv = 0.0f;
+    if (DK > 0) {
+#pragma unroll
+      for (int k = 0; k < DK; ++k)
+        kv = __fadd_rn(kv, __fmul_rn(__fmul_rn(s[k], dc), k_sm[k]));
+    } else if (active) {
+      for (int k = 0; k < dk; ++k)
+        kv = __fadd_rn(kv, __fmul_rn(__fmul_rn(col[static_cast<int64_t>(k) * dv], dc), k_sm[k]));
+    }
+    const float delta = __fmul_rn(__fsub_rn(value, kv), bt);
+    float o = 0.0f;
+    if (DK > 0) {
+#pragma unroll
+      for (int k = 0; k < DK; ++k) {
+        s[k] = __fadd_rn(__fmul_rn(s[k], dc), __fmul_rn(k_sm[k], delta));
+        o = __fadd_rn(o, __fmul_rn(s[k], q_sm[k]));
+      }
+    } else if (active) {
+      for (int k = 0; k < dk; ++k) {
+        const float updated = __fadd_rn(__fmul_rn(col[static_cast<int64_t>(k) * dv], dc), __fmul_rn(k_sm[k], delta));
+        col[static_cast<int64_t>(k) * dv] = updated;
+        o = __fadd_rn(o, __fmul_rn(updated, q_sm[k]));
+      }
+    }
+    if (active)
+      out[t * nv * dv + h * dv + v] = f32_to_bf16(o);
+  }
+  if (DK > 0 && active) {
+#pragma unroll
+    for (int k = 0; k < DK; ++k)
+      col[static_cast<int64_t>(k) * dv] = s[k];
+  }
+}
+
+size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk) {
+  return static_cast<size_t>(S) * (2 * static_cast<size_t>(nk) * dk + 2 * static_cast<size_t>(nv));
+}
+
+cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b,
+                                   const void *a_log, int a_log_dtype, const void *dt_bias, int dt_dtype,
+                                   float *state, int64_t S, int nk, int nv, int dk, int dv,
+                                   int b_activated, float *scratch, uint16_t *out, cudaStream_t stream) {
+  if (S == 0)
+    return cudaSuccess;
+  if (nk <= 0 || nv <= 0 || nv % nk != 0)
+    return cudaErrorInvalidValue;
+  float *qn = scratch;
+  float *kn = qn + S * nk * dk;
+  float *beta = kn + S * nk * dk;
+  float *decay = beta + S * nv;
+  const int64_t threads = S * std::max(nk, nv);
+  gdn_prepare_kernel<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, stream>>>(
+      conv, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, S, nk, nv, dk, dv, b_activated, qn, kn, beta, decay);
+  dim3 grid(nv, (dv + 31) / 32);
+  const size_t smem = 2 * static_cast<size_t>(dk) * sizeof(float);
+  if (dk == 128)
+    gdn_recurrence_kernel<128><<<grid, 32, smem, stream>>>(conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
+  else
+    gdn_recurrence_kernel<0><<<grid, 32, smem, stream>>>(conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------
+// attention (LowerAttention.cpp:160-601).
+//   prepare : per (token, head) zero-centred RMSNorm over head_dim, rotate-half RoPE on
+//             the first `rot` dims, bf16; q -> scratch, k and v -> KV cache.
+//   scores  : s[t, h, j] = (sum_d q[d] * K[j, d]) * scale, ascending d, one thread per key.
+//   combine : per (token, head) online softmax over key tiles of 64 in ascending key order,
+//             one thread per head-dim lane; then divide, sigmoid gate, bf16.
+// cache layout (one layer): [2, nkv, cap, hd] bf16.
+// ---------------------------------------------------------------------------------
+__global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint16_t *__restrict__ k,
+                                    const uint16_t *__restrict__ v, const uint16_t *__restrict__ q_norm,
+                                    const uint16_t *__restrict__ k_norm, const float *__restrict__ cos,
+                                    const float *__restrict__ sin, uint16_t *__restrict__ cache,
+                                    int64_t position, int64_t S, int nh, int nkv, int hd, int rot,
+                                    int64_t cap, uint16_t *__restrict__ qn) {
+  extern __shared__ float prep_sm[]; // per warp: hd values
+  const int lane = threadIdx.x & 31;
+  const int warp_in_cta = threadIdx.x >> 5;
+  const int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + warp_in_cta;
+  const int per_token = nh + nkv;
+  if (item >= S * per_token)
+    return;
+  const int64_t t = item / per_token;
+  const int which = static_cast<int>(item % per_token);
+  const bool is_q = which < nh;
+  const int head = is_q ? which : which - nh;
+  const uint16_t *src = is_q ? qg + t * nh * 2 * hd + static_cast<int64_t>(head) * 2 * hd
+                             : k + t * nkv * hd + static_cast<int64_t>(head) * hd;
+  const uint16_t *weight = is_q ? q_norm : k_norm;
+  uint16_t *dst = is_q ? qn + (t * nh + head) * hd
+                       : cache + ((0 * static_cast<int64_t>(nkv) + head) * cap + position + t) * hd;
+  float *tmp = prep_sm + warp_in_cta * hd;
+  for (int d = lane; d < hd; d += 32) {
+    const float x = bf16_to_f32(src[d]);
+    tmp[d] = __fmul_rn(x, x);
+  }
+  __syncwarp();
+  float inv = 0.0f;
+  if (lane == 0) {
+    float sum = 0.0f;
+    for (int d = 0; d < hd; ++d)
+      sum = __fadd_rn(sum, tmp[d]);
+    inv = d_rsqrt(__fadd_rn(__fmul_rn(sum, __fdiv_rn(1.0f, static_cast<float>(hd))), 1.0e-6f));
+  }
+  inv = __shfl_sync(0xffffffffu, inv, 0);
+  __syncwarp();
+  for (int d = lane; d < hd; d += 32) {
+    const float x = bf16_to_f32(src[d]);
+    const float centered = __fadd_rn(1.0f, bf16_to_f32(weight[d]));
+    tmp[d] = __fmul_rn(__fmul_rn(x, inv), centered);
+  }
+  __syncwarp();
+  const int half = rot / 2;
+  for (int d = lane; d < hd; d += 32) {
+    float r = tmp[d];
+    if (d < rot) {
+      const bool second = d >= half;
+      const float rotated = __fmul_rn(second ? 1.0f : -1.0f, tmp[second ? d - half : d + half]);
+      r = __fadd_rn(__fmul_rn(tmp[d], cos[t * rot + d]), __fmul_rn(rotated, sin[t * rot + d]));
+    }
+    dst[d] = f32_to_bf16(r);
+  }
+  if (!is_q) {
+    uint16_t *vdst = cache + ((1 * static_cast<int64_t>(nkv) + head) * cap + position + t) * hd;
+    const uint16_t *vsrc = v + t * nkv * hd + static_cast<int64_t>(head) * hd;
+    for (int d = lane; d < hd; d += 32)
+      vdst[d] = vsrc[d];
+  }
+}
+
+constexpr int kKeyTile = 64; // LowerAttention.cpp:124
+
+// grid: (key tile, kv head, token); block: group * 64 threads (query head x key).
+__global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
+                                   int64_t position, int nh, int nkv, int hd, int64_t cap,
+                                   int64_t score_stride, float *__restrict__ scores) {
+  extern __shared__ __align__(16) unsigned char att_sm[];
+  const int group = nh / nkv;
+  const int64_t t = blockIdx.z;
+  const int kvh = blockIdx.y;
+  const int64_t query_end = position + t + 1;
+  const int64_t start = static_cast<int64_t>(blockIdx.x) * kKeyTile;
+  if (start >= query_end)
+    return;
+  const int keys = static_cast<int>(min(static_cast<int64_t>(kKeyTile), query_end - start));
+  const int kstride = hd + 1; // floats per key row, odd to spread banks
+  float *k_sm = reinterpret_cast<float *>(att_sm);           // [64][hd+1]
+  float *q_sm = k_sm + kKeyTile * kstride;                   // [group][hd]
+  const uint16_t *kc = cache + (static_cast<int64_t>(kvh) * cap + start) * hd;
+  for (int i = threadIdx.x; i < keys * hd; i += blockDim.x)
+    k_sm[(i / hd) * kstride + (i % hd)] = bf16_to_f32(kc[i]);
+  for (int i = threadIdx.x; i < group * hd; i += blockDim.x)
+    q_sm[i] = bf16_to_f32(qn[(t * nh + kvh * group) * hd + i]);
+  __syncthreads();
+  const int j = threadIdx.x % kKeyTile;
+  const int g = threadIdx.x / kKeyTile;
+  if (j >= keys || g >= group)
+    return;
+  const float *kr = k_sm + j * kstride;
+  const float *qr = q_sm + g * hd;
+  float dot = 0.0f;
+  for (int d = 0; d < hd; ++d)
+    dot = __fadd_rn(dot, __fmul_rn(qr[d], kr[d]));
+  const float scale = __fdiv_rn(1.0f, __fsqrt_rn(static_cast<float>(hd)));
+  scores[(t * nh + kvh * group + g) * score_stride + start + j] = __fmul_rn(dot, scale);
+}
+
+// grid: (head, token); block: hd rounded up to a warp multiple.
+__global__ void attn_combine_kernel(const float *__restrict__ scores, const uint16_t *__restrict__ cache,
+                                    const uint16_t *__restrict__ qg, int64_t position, int nh, int nkv,
+                                    int hd, int64_t cap, int64_t score_stride, uint16_t *__restrict__ out) {
+  __shared__ float p_sm[kKeyTile];
+  __shared__ float max_sm;
+  const int h = blockIdx.x;
+  const int64_t t = blockIdx.y;
+  const int kvh = h / (nh / nkv);
+  const int d = threadIdx.x;
+  const bool active = d < hd;
+  const int64_t query_end = position + t + 1;
+  const float *srow = scores + (t * nh + h) * score_stride;
+  const uint16_t *vc = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd + (active ? d : 0);
+  float acc = 0.0f;
+  float running_max = -1.0e30f;
+  float running_sum = 0.0f;
+  for (int64_t start = 0; start < query_end; start += kKeyTile) {
+    const int keys = static_cast<int>(min(static_cast<int64_t>(kKeyTile), query_end - start));
+    __syncthreads(); // p_sm and max_sm of the previous tile are no longer read
+    if (threadIdx.x < 32) {
+      float m = -1.0e30f;
+      for (int j = threadIdx.x; j < keys; j += 32)
+        m = fmaxf(m, srow[start + j]);
+      for (int o = 16; o > 0; o >>= 1)
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if (threadIdx.x == 0)
+        max_sm = fmaxf(running_max, m);
+    }
+    __syncthreads();
+    const float new_max = max_sm;
+    for (int j = threadIdx.x; j < keys; j += blockDim.x)
+      p_sm[j] = d_exp(__fsub_rn(srow[start + j], new_max));
+    const float correction = d_exp(__fsub_rn(running_max, new_max));
+    __syncthreads();
+    acc = __fmul_rn(acc, correction);
+    float sum = __fmul_rn(running_sum, correction);
+    const uint16_t *vt = vc + start * hd;
+#pragma unroll 4
+    for (int j = 0; j < keys; ++j) {
+      const float p = p_sm[j];
+      sum = __fadd_rn(sum, p);
+      if (active)
+        acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(vt[static_cast<int64_t>(j) * hd])));
+    }
+    running_max = new_max;
+    running_sum = sum;
+  }
+  if (active) {
+    const float gate = bf16_to_f32(qg[t * nh * 2 * hd + static_cast<int64_t>(h) * 2 * hd + hd + d]);
+    const float gated = __fmul_rn(__fdiv_rn(acc, running_sum), d_sigmoid(gate));
+    out[t * nh * hd + static_cast<int64_t>(h) * hd + d] = f32_to_bf16(gated);
+  }
+}
+
+size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t position) {
+  const size_t score_stride = static_cast<size_t>(position + S);
+  return static_cast<size_t>(S) * nh * hd * sizeof(uint16_t) + 256 +
+         static_cast<size_t>(S) * nh * score_stride * sizeof(float);
+}
+
+cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
+                             const uint16_t *q_norm, const uint16_t *k_norm, const float *cos,
+                             const float *sin, uint16_t *cache, int64_t position, int64_t S, int nh,
+                             int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out,
+                             cudaStream_t stream) {
+  if (S == 0)
+    return cudaSuccess;
+  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || rot % 2 != 0 || rot > hd || position + S > cap)
+    return cudaErrorInvalidValue;
+  const int group = nh / nkv;
+  if (group * kKeyTile > 1024 || hd > 1024)
+    return cudaErrorInvalidValue;
+  uint16_t *qn = static_cast<uint16_t *>(scratch);
+  const size_t qn_bytes = (static_cast<size_t>(S) * nh * hd * sizeof(uint16_t) + 255) / 256 * 256;
+  float *scores = reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + qn_bytes);
+  const int64_t score_stride = position + S;
+
+  const int64_t items = S * (nh + nkv);
+  attn_prepare_kernel<<<static_cast<unsigned>((items + 3) / 4), 128, 4 * hd * sizeof(float), stream>>>(
+      qg, k, v, q_norm, k_norm, cos, sin, cache, position, S, nh, nkv, hd, rot, cap, qn);
+
+  const size_t smem = (static_cast<size_t>(kKeyTile) * (hd + 1) + static_cast<size_t>(group) * hd) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess)
+      return e;
+    configured = true;
+  }
+  if (smem > 200 * 1024)
+    return cudaErrorInvalidValue;
+  dim3 sgrid(static_cast<unsigned>((position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
+  attn_scores_kernel<<<sgrid, group * kKeyTile, smem, stream>>>(qn, cache, position, nh, nkv, hd, cap,
+                                                               score_stride, scores);
+  dim3 cgrid(nh, static_cast<unsigned>(S));
+  attn_combine_kernel<<<cgrid, (hd + 31) / 32 * 32, 0, stream>>>(scores, cache, qg, position, nh, nkv, hd,
+                                                                cap, score_stride, out);
+  return cudaGetLastError();
+}
+
+} // namespace llmcp_b200

@@ -1,0 +1,197 @@
+// rms_norm, gated_rms_norm and the bf16 pointwise ops, each optionally emitting the int8
+// activation quantisation that the following Q8 linear needs (so that the linear reads
+// int8 + f32 block scales and no separate quantisation pass runs).
+//
+// Reduction order: the reference sums the squares of a row sequentially in f32
+// (LowerToLinalg.cpp:251-262, DecodeNormalization.cpp:96-105).  In the default, exact
+// mode one thread adds the squares in that order; every other step is elementwise.
+
+#include "kernels.h"
+
+namespace llmcp_b200 {
+
+// Quantises 32 consecutive values held one per lane of a full warp (Q8Decode.cpp:83-120).
+__device__ inline void warp_quant_block(float v, int8_t *q, float *s, int64_t element, int64_t block,
+                                        int lane) {
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = __fdiv_rn(amax, 127.0f);
+  const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
+  q[element] = static_cast<int8_t>(__float2int_rn(__fmul_rn(v, inv)));
+  if (lane == 0)
+    s[block] = scale;
+}
+
+// One CTA per row.  x = bf(a + b) when b is given (the residual add of the layer,
+// LowerToLinalg.cpp:359-374), else x = a.  Outputs (each optional): sum_out = x,
+// y = bf((x * rstd) * (w [+ 1])), and the block quantisation of y.
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, int H,
+                const void *__restrict__ w, int w_dtype, float eps, int zero_centered,
+                uint16_t *__restrict__ sum_out, uint16_t *__restrict__ y, int8_t *__restrict__ q,
+                float *__restrict__ s) {
+  extern __shared__ float row_sm[]; // x values, then their squares
+  float *sq_sm = row_sm + H;
+  __shared__ float rstd_sm;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
+  for (int d = threadIdx.x; d < H; d += blockDim.x) {
+    float v = bf16_to_f32(a[base + d]);
+    if (b) {
+      const uint16_t r = f32_to_bf16(__fadd_rn(v, bf16_to_f32(b[base + d])));
+      if (sum_out)
+        sum_out[base + d] = r;
+      v = bf16_to_f32(r);
+    }
+    row_sm[d] = v;
+    sq_sm[d] = __fmul_rn(v, v);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sum = 0.0f;
+    int d = 0;
+    for (; (H & 3) == 0 && d + 4 <= H; d += 4) {
+      const float4 t = *reinterpret_cast<const float4 *>(sq_sm + d);
+      sum = __fadd_rn(sum, t.x);
+      sum = __fadd_rn(sum, t.y);
+      sum = __fadd_rn(sum, t.z);
+      sum = __fadd_rn(sum, t.w);
+    }
+    for (; d < H; ++d)
+      sum = __fadd_rn(sum, sq_sm[d]);
+    const float mean = __fdiv_rn(sum, static_cast<float>(H));
+    rstd_sm = d_rsqrt(__fadd_rn(mean, eps));
+  }
+  __syncthreads();
+  const float rstd = rstd_sm;
+  const int lane = threadIdx.x & 31;
+  const int64_t nb = H / kBlock;
+  // Whole warps walk consecutive 32-element groups so that a quantisation block sits in
+  // one warp; a ragged tail (H % 32) is only reachable without quantised output.
+  for (int d0 = (threadIdx.x >> 5) * 32; d0 < H; d0 += blockDim.x) {
+    const int d = d0 + lane;
+    float out = 0.0f;
+    if (d < H) {
+      float wt = load_as_f32(w, w_dtype, d);
+      if (zero_centered)
+        wt = __fadd_rn(wt, 1.0f);
+      out = bf16_to_f32(f32_to_bf16(__fmul_rn(__fmul_rn(row_sm[d], rstd), wt)));
+      if (y)
+        y[base + d] = f32_to_bf16(out);
+    }
+    if (q)
+      warp_quant_block(out, q, s, base + d, blockIdx.x * nb + d0 / kBlock, lane);
+  }
+}
+
+cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int H, const void *w,
+                            int w_dtype, float eps, int zero_centered, uint16_t *sum_out, uint16_t *y,
+                            int8_t *q, float *s, cudaStream_t stream) {
+  if (M == 0)
+    return cudaSuccess;
+  if (q && H % kBlock != 0)
+    return cudaErrorInvalidValue;
+  rms_norm_kernel<<<static_cast<unsigned>(M), 256, 2 * H * sizeof(float), stream>>>(
+      a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s);
+  return cudaGetLastError();
+}
+
+// One warp per (row, group).  y = bf(((x * silu(g)) * w) * rstd); with gate_activated the
+// gate already holds silu(g) (LowerToLinalg.cpp:655-718, DecodeNormalization.cpp:118-131).
+__global__ void __launch_bounds__(128)
+gated_rms_norm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ gate,
+                      const void *__restrict__ w, int w_dtype, int64_t groups_total, int group,
+                      float eps, int gate_activated, uint16_t *__restrict__ y, int8_t *__restrict__ q,
+                      float *__restrict__ s) {
+  extern __shared__ float sq_all[];
+  const int lane = threadIdx.x & 31;
+  const int warp_in_cta = threadIdx.x >> 5;
+  const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + warp_in_cta;
+  if (g >= groups_total)
+    return;
+  float *sq = sq_all + warp_in_cta * group;
+  const int64_t base = g * group;
+  for (int d = lane; d < group; d += 32) {
+    const float v = bf16_to_f32(x[base + d]);
+    sq[d] = __fmul_rn(v, v);
+  }
+  __syncwarp();
+  float rstd = 0.0f;
+  if (lane == 0) {
+    float sum = 0.0f;
+    for (int d = 0; d < group; ++d)
+      sum = __fadd_rn(sum, sq[d]);
+    rstd = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(group)), eps));
+  }
+  rstd = __shfl_sync(0xffffffffu, rstd, 0);
+  for (int d0 = 0; d0 < group; d0 += 32) {
+    const int d = d0 + lane;
+    float out = 0.0f;
+    if (d < group) {
+      const float v = bf16_to_f32(x[base + d]);
+      const float gv = bf16_to_f32(gate[base + d]);
+      const float silu = gate_activated ? gv : __fmul_rn(gv, d_sigmoid(gv));
+      float t = __fmul_rn(v, silu);
+      t = __fmul_rn(t, load_as_f32(w, w_dtype, d));
+      t = __fmul_rn(t, rstd);
+      const uint16_t r = f32_to_bf16(t);
+      out = bf16_to_f32(r);
+      if (y)
+        y[base + d] = r;
+    }
+    if (q)
+      warp_quant_block(out, q, s, base + d, (base + d0) / kBlock, lane);
+  }
+}
+
+cudaError_t launch_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const void *w, int w_dtype,
+                                  int64_t M, int H, int group, float eps, int gate_activated,
+                                  uint16_t *y, int8_t *q, float *s, cudaStream_t stream) {
+  if (M == 0)
+    return cudaSuccess;
+  if (group <= 0 || H % group != 0 || (q && group % kBlock != 0))
+    return cudaErrorInvalidValue;
+  const int64_t groups_total = M * (H / group);
+  const unsigned ctas = static_cast<unsigned>((groups_total + 3) / 4);
+  gated_rms_norm_kernel<<<ctas, 128, 4 * group * sizeof(float), stream>>>(
+      x, gate, w, w_dtype, groups_total, group, eps, gate_activated, y, q, s);
+  return cudaGetLastError();
+}
+
+// add / mul / silu_mul on bf16 operands (LowerToLinalg.cpp:312-427).  count is padded to a
+// multiple of 32 by the launcher's grid; quantised output needs count % 32 == 0.
+__global__ void pointwise_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b,
+                                 int64_t count, int op, uint16_t *__restrict__ y, int8_t *__restrict__ q,
+                                 float *__restrict__ s) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  float out = 0.0f;
+  if (i < count) {
+    const float x = bf16_to_f32(a[i]), z = bf16_to_f32(b[i]);
+    float r;
+    if (op == 0)
+      r = __fadd_rn(x, z);
+    else if (op == 1)
+      r = __fmul_rn(x, z);
+    else
+      r = __fmul_rn(__fmul_rn(x, d_sigmoid(x)), z);
+    const uint16_t rb = f32_to_bf16(r);
+    out = bf16_to_f32(rb);
+    if (y)
+      y[i] = rb;
+  }
+  if (q && (i - (threadIdx.x & 31)) < count)
+    warp_quant_block(out, q, s, i, i / kBlock, threadIdx.x & 31);
+}
+
+cudaError_t launch_pointwise(const uint16_t *a, const uint16_t *b, int64_t count, int op, uint16_t *y,
+                             int8_t *q, float *s, cudaStream_t stream) {
+  if (count == 0)
+    return cudaSuccess;
+  if (q && count % kBlock != 0)
+    return cudaErrorInvalidValue;
+  pointwise_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(a, b, count, op, y, q, s);
+  return cudaGetLastError();
+}
+
+} // namespace llmcp_b200

@@ -296,10 +296,13 @@ class Model:
             "conv": np.zeros((self.n_lin, c.conv_kernel - 1, self.qkv_dim), dtype=np.uint16),
         }
 
-    def forward(self, state, tokens, position, theta=1.0e7, want_hidden=False):
+    def forward(self, state, tokens, position, theta=1.0e7, want_hidden=False, cos=None, sin=None):
         tokens = np.ascontiguousarray(tokens, dtype=np.int64)
         S = tokens.shape[0]
-        cos, sin = make_cos_sin(range(position, position + S), self.cfg.rotary, theta)
+        if cos is None:
+            cos, sin = make_cos_sin(range(position, position + S), self.cfg.rotary, theta)
+        cos = np.ascontiguousarray(cos, dtype=np.float32)
+        sin = np.ascontiguousarray(sin, dtype=np.float32)
         logits = np.empty(self.cfg.vocab, dtype=np.float32)
         hidden = np.empty((S, self.cfg.hidden), dtype=np.uint16) if want_hidden else None
         lib().orc_model_forward(self.handle, _p(tokens), _i(S), _p(cos), _p(sin), _i(position),

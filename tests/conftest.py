@@ -11,6 +11,7 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    config.addinivalue_line("markers", "slow: full-size model cases (minutes of CPU oracle time)")
 
 
 @pytest.fixture(scope="session")

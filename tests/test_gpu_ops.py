@@ -1,0 +1,247 @@
+"""Operator parity on a B200: every llmcp operator through the C ABI against the CPU oracle
+and against the vectors taken from the reference's numeric tests.
+
+Bars: int8 quantisation, int32 block dots, indices and state bytes are bit-exact; f32/bf16
+results are required to be bit-identical to the oracle as well (the kernels keep the
+reference's operation order, and exp/log are defined as the f32 rounding of the f64
+function on both sides), which is stricter than the reference's own tolerances; the golden
+cases are checked with the tolerance the reference's harness uses.
+"""
+import numpy as np
+import pytest
+
+import llmcp_b200 as L
+import oracle
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+f = oracle.bf16_to_f32
+
+
+def bf16(a):
+    return oracle.f32_to_bf16(np.asarray(a, dtype=np.float32))
+
+
+def rand_bf16(rng, *shape, scale=1.0):
+    return bf16(rng.standard_normal(shape) * scale)
+
+
+@pytest.mark.parametrize("M,K", [(1, 32), (1, 2560), (3, 96), (19, 288), (64, 9216)])
+@pytest.mark.parametrize("x_bf16", [True, False])
+def test_act_quant(M, K, x_bf16):
+    rng = np.random.default_rng(M * 100 + K)
+    x = rng.standard_normal((M, K)).astype(np.float32) * rng.choice([1e-3, 1.0, 30.0], size=(M, 1)).astype(np.float32)
+    x[0, :32] = 0  # a zero block: scale 0, integers 0 (Q8Decode.cpp:108-114)
+    if x_bf16:
+        x = bf16(x)
+    q, s = L.ops.act_quant(x, x_bf16)
+    oq, os_ = oracle.act_quant(x, x_bf16)
+    assert np.array_equal(q, oq) and np.array_equal(s.view(np.uint32), os_.view(np.uint32))
+    assert s[0, 0] == 0 and not q[0, :32].any()
+
+
+@pytest.mark.parametrize("case", ["linear_q8_p4_decode", "linear_q8_p4_prefill", "linear_q8_p4_prefill_boundaries",
+                                  "linear_q8_p4_decode_boundaries"])
+def test_linear_q8_golden(golden, case):
+    c = golden(case)
+    N = c["w"].shape[0]
+    y, dots = L.ops.linear_q8(c["x"], c["packed"], N, want_dots=True)
+    assert_close(f(y), c["ref"], c["tol"], case)
+    if case.endswith("boundaries"):
+        assert np.array_equal(f(y), c["ref"])
+    q, _ = oracle.act_quant(c["x"])
+    assert np.array_equal(dots, oracle.block_dots(q, c["packed"], N))
+    assert np.array_equal(y, oracle.linear_q8(c["x"], c["packed"], N))
+
+
+@pytest.mark.parametrize("case", ["lm_head_q8_p4", "lm_head_q8_p4_decode"])
+def test_lm_head_golden(golden, case):
+    c = golden(case)
+    logits, argmax = L.ops.lm_head_q8(c["x"], c["packed"], c["w"].shape[0])
+    assert_close(logits, c["ref"], c["tol"], case)
+    want = oracle.linear_q8(c["x"], c["packed"], c["w"].shape[0], y_bf16=False)
+    assert np.array_equal(logits.view(np.uint32), want.view(np.uint32))
+    assert argmax.tolist() == [oracle.argmax(row) for row in want]
+
+
+# (M, N, K): decode and prefill shapes of the model plus ragged tile edges.
+LINEAR_SHAPES = [(1, 9216, 2560), (1, 2560, 9216), (1, 2560, 4096), (1, 32, 2560), (1, 8, 32), (1, 136, 288),
+                 (2, 8, 32), (19, 136, 288), (64, 64, 64), (65, 72, 96), (128, 1024, 2560), (1024, 256, 2560)]
+
+
+@pytest.mark.parametrize("M,N,K", LINEAR_SHAPES)
+def test_linear_q8_bit_exact(M, N, K):
+    rng = np.random.default_rng(N + K + M)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    packed = oracle.pack_q8_0_p4(w)
+    x = rand_bf16(rng, M, K)
+    x[0, :32] = 0
+    for activation, y_bf16 in (("none", True), ("none", False), ("silu", True), ("sigmoid", True), ("softplus", False)):
+        y, dots = L.ops.linear_q8(x, packed, N, y_bf16=y_bf16, activation=activation, want_dots=True)
+        want = oracle.linear_q8(x, packed, N, y_bf16=y_bf16, activation=activation)
+        assert np.array_equal(y.view(np.uint16 if y_bf16 else np.uint32), want.view(np.uint16 if y_bf16 else np.uint32)), \
+            (activation, y_bf16, np.abs(y.astype(np.float64) - want).max())
+        if activation == "none" and y_bf16:
+            q, _ = oracle.act_quant(x)
+            assert np.array_equal(dots, oracle.block_dots(q, packed, N))
+
+
+def test_linear_q8_f32_input_and_rows_per_warp():
+    rng = np.random.default_rng(9)
+    N, K = 512, 2560
+    packed = oracle.pack_q8_0_p4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    y = L.ops.linear_q8(x, packed, N, x_bf16=False, y_bf16=False)
+    assert np.array_equal(y.view(np.uint32), oracle.linear_q8(x, packed, N, x_bf16=False, y_bf16=False).view(np.uint32))
+
+
+def test_linear_q8_rejects_bad_shapes():
+    with pytest.raises(L.LlmcpError):
+        L.ops.linear_q8(np.zeros((1, 32), np.uint16), np.zeros(4 * 34, np.uint8), 4)  # N % 8 (Q8PackedLayout.h:38-42)
+    with pytest.raises(L.LlmcpError):
+        L.ops.linear_q8(np.zeros((1, 32), np.uint16), np.zeros(10, np.uint8), 8)      # size rule (LLMCPOps.cpp:46-70)
+    y = L.ops.linear_q8(np.zeros((0, 32), np.uint16), np.zeros(8 * 34, np.uint8), 8)
+    assert y.shape == (0, 8)
+
+
+def test_lm_head_large_vocab_argmax_first_maximum():
+    rng = np.random.default_rng(4)
+    vocab, K = 31040, 2560  # one shard of the 248320-row table at TP = 8
+    w = (rng.standard_normal((vocab, K)) * 0.02).astype(np.float32)
+    w[20000] = w[777]  # duplicate rows: equal logits, the lower index must win
+    packed = oracle.pack_q8_0_p4(w)
+    h = oracle.rms_norm(rand_bf16(rng, 2, K), np.zeros(K, np.uint16))
+    logits, argmax = L.ops.lm_head_q8(h, packed, vocab)
+    want = oracle.linear_q8(h, packed, vocab, y_bf16=False)
+    assert np.array_equal(logits.view(np.uint32), want.view(np.uint32))
+    assert argmax.tolist() == [oracle.argmax(row) for row in want]
+    boosted = w.copy()
+    boosted[777] *= 0
+    boosted[20000] *= 0
+    boosted[[777, 20000]] += (f(h[0]) / np.abs(f(h[0])).max() * 0.05).astype(np.float32)
+    packed = oracle.pack_q8_0_p4(boosted)
+    logits, argmax = L.ops.lm_head_q8(h[:1], packed, vocab)
+    assert logits[0, 777] == logits[0, 20000] == logits.max() and argmax[0] == 777
+
+
+def test_embedding(golden):
+    c = golden("embedding_q8_p4")
+    out = L.ops.embedding_q8(c["tokens"], c["packed"], *c["table"].shape)
+    assert np.array_equal(f(out), c["ref"])
+    rng = np.random.default_rng(5)
+    packed = oracle.pack_q8_0_p4((rng.standard_normal((512, 2560)) * 0.02).astype(np.float32))
+    tokens = np.array([0, 511, 3, 3, 258], dtype=np.int64)
+    assert np.array_equal(L.ops.embedding_q8(tokens, packed, 512, 2560), oracle.embedding_q8(tokens, packed, 2560))
+    with pytest.raises(L.LlmcpError):
+        L.ops.embedding_q8(np.array([512]), packed, 512, 2560)
+
+
+def test_rms_norm(golden):
+    for case, zc in (("rms_zero_centered", True), ("rms_plain", False)):
+        c = golden(case)
+        assert_close(f(L.ops.rms_norm(c["x"], c["w"], zero_centered=zc)), c["ref"], c["tol"], case)
+    rng = np.random.default_rng(6)
+    for M, H in ((1, 2560), (5, 2560), (1024, 2560), (3, 72), (2, 7)):
+        x = rand_bf16(rng, M, H, scale=3.0)
+        w = rand_bf16(rng, H, scale=0.1)
+        for zc in (True, False):
+            assert np.array_equal(L.ops.rms_norm(x, w, zero_centered=zc), oracle.rms_norm(x, w, zero_centered=zc))
+        wf = rng.standard_normal(H).astype(np.float32)
+        assert np.array_equal(L.ops.rms_norm(x, wf, w_bf16=False), oracle.rms_norm(x, wf, w_bf16=False))
+
+
+def test_pointwise(golden):
+    c = golden("add")
+    assert np.array_equal(f(L.ops.pointwise(c["a"], c["b"], "add")), c["ref"])
+    c = golden("silu_mul")
+    assert_close(f(L.ops.pointwise(c["gate"], c["up"], "silu_mul")), c["ref"], c["tol"])
+    c = golden("mul_silu_mul")
+    product = L.ops.pointwise(c["gate"], c["up"], "mul")
+    assert_close(f(L.ops.pointwise(c["gate"], product, "silu_mul")), c["ref"], c["tol"])
+    rng = np.random.default_rng(7)
+    a, b = rand_bf16(rng, 1024, 96, scale=4.0), rand_bf16(rng, 1024, 96, scale=4.0)
+    for op in ("add", "mul", "silu_mul"):
+        assert np.array_equal(L.ops.pointwise(a, b, op), oracle.pointwise(a, b, op)), op
+
+
+def test_gated_rms_norm(golden):
+    c = golden("gated_rms_norm")
+    assert_close(f(L.ops.gated_rms_norm(c["x"], c["gate"], c["w"], int(c["group"]))), c["ref"], c["tol"])
+    c = golden("gated_rms_norm_activated")
+    assert_close(f(L.ops.gated_rms_norm(c["x"], c["gate"], c["w"], int(c["group"]), gate_activated=True)), c["ref"], c["tol"])
+    rng = np.random.default_rng(8)
+    for M, H, group in ((1, 4096, 128), (33, 4096, 128), (2, 24, 12), (3, 64, 64)):
+        x, g = rand_bf16(rng, M, H, scale=2.0), rand_bf16(rng, M, H, scale=2.0)
+        w = rng.standard_normal(group).astype(np.float32)
+        for activated in (False, True):
+            got = L.ops.gated_rms_norm(x, g, w, group, gate_activated=activated)
+            assert np.array_equal(got, oracle.gated_rms_norm(x, g, w, group, gate_activated=activated))
+        wb = rand_bf16(rng, group)
+        assert np.array_equal(L.ops.gated_rms_norm(x, g, wb, group, w_bf16=True),
+                              oracle.gated_rms_norm(x, g, wb, group, w_bf16=True))
+
+
+def test_causal_conv1d(golden):
+    for case in ("causal_conv1d", "causal_conv1d_decode"):
+        c = golden(case)
+        w = c["w"].reshape(c["w"].shape[0], -1)
+        y, state = L.ops.causal_conv1d(c["x"], w, c["state"], int(c["kernel"]))
+        assert_close(f(y), c["ref"], c["tol"], case)
+        assert np.array_equal(state, c["ref_state"])
+    rng = np.random.default_rng(10)
+    for S, C, kernel in ((1, 8192, 4), (2, 8192, 4), (3, 64, 4), (1024, 8192, 4), (5, 40, 2), (1, 16, 6)):
+        x, w = rand_bf16(rng, S, C), rand_bf16(rng, C, kernel, scale=0.5)
+        state = rand_bf16(rng, kernel - 1, C)
+        y, new_state = L.ops.causal_conv1d(x, w, state, kernel)
+        oy, ostate = oracle.causal_conv1d(x, w, state, kernel)
+        assert np.array_equal(y, oy) and np.array_equal(new_state, ostate), (S, C, kernel)
+
+
+def test_gated_delta_net(golden):
+    for case in [n for n in golden.names() if n.startswith("gated_delta_net")]:
+        c = golden(case)
+        seq, nk, nv, dk, dv = (int(v) for v in c["dims"])
+        out, state = L.ops.gated_delta_net(c["conv"], c["a"], c["b"], c["a_log"], c["dt_bias"], c["state"], nk, nv, dk, dv)
+        assert_close(f(out), c["ref"], c["tol"], case)
+        assert_close(state, c["ref_state"], c["tol"], case + " state")
+        oo, os_ = oracle.gated_delta_net(c["conv"], c["a"], c["b"], c["a_log"], c["dt_bias"], c["state"], nk, nv, dk, dv)
+        assert np.array_equal(out, oo) and np.array_equal(state.view(np.uint32), os_.view(np.uint32)), case
+    rng = np.random.default_rng(11)
+    # BASELINE config 3 uses 16/16 heads, the model 16/32; both, prefill and single steps.
+    for S, nk, nv, dk, dv in ((1, 16, 32, 128, 128), (7, 16, 16, 128, 128), (64, 16, 32, 128, 128), (3, 2, 4, 128, 64)):
+        channels = 2 * nk * dk + nv * dv
+        conv, a = rand_bf16(rng, S, channels), rand_bf16(rng, S, nv)
+        a_log = (rng.standard_normal(nv) * 0.2).astype(np.float32)
+        dt = rand_bf16(rng, nv, scale=0.2)
+        state = (rng.standard_normal((nv, dk, dv)) * 0.1).astype(np.float32)
+        for activated in (False, True):
+            b = rand_bf16(rng, S, nv) if not activated else bf16(1 / (1 + np.exp(-rng.standard_normal((S, nv)))))
+            out, new_state = L.ops.gated_delta_net(conv, a, b, a_log, dt, state, nk, nv, dk, dv, b_activated=activated)
+            oo, os_ = oracle.gated_delta_net(conv, a, b, a_log, dt, state, nk, nv, dk, dv, b_activated=activated)
+            assert np.array_equal(out, oo), (S, nk, nv, activated)
+            assert np.array_equal(new_state.view(np.uint32), os_.view(np.uint32))
+
+
+def test_attention(golden):
+    for case in ("attention", "attention_decode"):
+        c = golden(case)
+        seq, nh, nkv, hd, rot, cap, pos = (int(v) for v in c["dims"])
+        out, cache = L.ops.attention(c["qg"], c["k"], c["v"], c["q_norm"], c["k_norm"], c["cos"], c["sin"], c["cache"],
+                                     pos, nh, nkv, hd, rot)
+        assert_close(f(out), c["ref"], c["tol"], case)
+        assert_close(f(cache), f(c["ref_cache"]), c["tol"], case + " cache")
+    rng = np.random.default_rng(12)
+    nh, nkv, hd, rot = 16, 4, 256, 64
+    q_norm, k_norm = rand_bf16(rng, hd, scale=0.1), rand_bf16(rng, hd, scale=0.1)
+    # prefill at 0; a chunk appended after it; single-token steps at 63/64/65 (tile edges) and 1024.
+    for S, pos, cap in ((70, 0, 80), (5, 64, 80), (1, 63, 80), (1, 64, 80), (1, 65, 80), (1, 1024, 1032), (130, 0, 130)):
+        qg, k, v = rand_bf16(rng, S, nh * 2 * hd), rand_bf16(rng, S, nkv * hd), rand_bf16(rng, S, nkv * hd)
+        cos = np.stack([L.make_cos_sin(pos + t)[0] for t in range(S)])
+        sin = np.stack([L.make_cos_sin(pos + t)[1] for t in range(S)])
+        cache = rand_bf16(rng, 2, nkv, cap, hd)
+        out, new_cache = L.ops.attention(qg, k, v, q_norm, k_norm, cos, sin, cache, pos, nh, nkv, hd, rot)
+        oo, oc = oracle.attention(qg, k, v, q_norm, k_norm, cos, sin, cache, pos, nh, nkv, hd, rot)
+        assert np.array_equal(new_cache, oc), (S, pos)
+        assert np.array_equal(out, oo), (S, pos, np.abs(f(out) - f(oo)).max())
+    with pytest.raises(L.LlmcpError):
+        L.ops.attention(qg, k, v, q_norm, k_norm, cos, sin, cache, cap, nh, nkv, hd, rot)  # past the cache
