@@ -132,6 +132,21 @@ int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, c
 int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *scratch_indices, int64_t *out_index,
                      void *stream);
 
+/* No counterpart in the reference (its generated code allocates with malloc as it goes).
+ * llmcp.gated_delta_net on device pointers for callers that may not allocate GPU memory:
+ * a server that owns the whole GPU through its own pool, or a decode loop that cannot pay
+ * for the synchronisation an allocation can cause.  Arguments as llmcp_op_gated_delta_net,
+ * all of them device pointers; enqueued on `stream` (a cudaStream_t), not synchronised.
+ * The working memory is a 256 KiB array built into the library (resident on every GPU that
+ * loads it): calls with S * (2*nk*dk + 2*nv) > 65536 are refused with code 2 and a message.
+ * All calls on a GPU share that array, so calls that overlap in time on one GPU race; its
+ * old contents need no clearing.  The first call on each device resolves the array's device
+ * address; make it before starting any stream capture.  Calls no cudaMalloc / cudaFree. */
+int llmcp_dev_gated_delta_net_noalloc(const uint16_t *conv, const uint16_t *a, const uint16_t *b,
+                                      const float *a_log, const uint16_t *dt_bias, float *state, int64_t S,
+                                      int64_t nk, int64_t nv, int64_t dk, int64_t dv, int b_activated,
+                                      uint16_t *out, void *stream);
+
 /* ---- 3. engine --------------------------------------------------------------------- */
 
 typedef struct llmcp_b200_dims {

@@ -71,6 +71,14 @@ struct Buf {
 
 size_t elem(int dtype) { return dtype == kBF16 ? 2 : 4; }
 
+} // namespace
+
+namespace llmcp_b200 {
+void report_error(const std::string &message) { set_error(message); }
+} // namespace llmcp_b200
+
+namespace {
+
 template <typename F> int guarded(F &&body) {
   try {
     body();
