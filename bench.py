@@ -156,19 +156,27 @@ def gemv_roofline(L, torch, device):
     ptr = lambda t: C.c_void_p(t.data_ptr())
     assert lib.llmcp_dev_act_quant(ptr(x), 0, C.c_int64(1), C.c_int64(GEMV_K), ptr(aq), ptr(scales), C.c_void_p(stream)) == 0
 
-    def sweep(times):
+    def sweep(times, stream):
         for _ in range(times):
             for r in range(GEMV_RING):
                 rc = lib.llmcp_dev_gemv_q8(ptr(aq), ptr(scales), C.c_int64(GEMV_K), ptr(wq[r]), ptr(wd[r]),
                                            C.c_int64(GEMV_N), ptr(y), 0, 0, 0, C.c_void_p(stream))
                 assert rc == 0, L.last_error()
 
-    sweep(3)
+    sweep(3, stream)
+    torch.cuda.synchronize()
+    # One pass over the ring is captured as a CUDA graph (as the decode step itself is), so the
+    # events time the kernels and not the Python call overhead between launches.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sweep(1, torch.cuda.current_stream().cuda_stream)
+    graph.replay()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
-    begin.record()
     sweeps = 20
-    sweep(sweeps)
+    begin.record()
+    for _ in range(sweeps):
+        graph.replay()
     end.record()
     torch.cuda.synchronize()
     us = begin.elapsed_time(end) * 1e3 / (sweeps * GEMV_RING)

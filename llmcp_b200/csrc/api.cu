@@ -554,9 +554,10 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
         dqn(static_cast<size_t>(hd) * 2, q_norm), dkn(static_cast<size_t>(hd) * 2, k_norm), dcos(static_cast<size_t>(S) * rot * 4, cos),
         dsin(static_cast<size_t>(S) * rot * 4, sin), dcache(static_cast<size_t>(2) * nkv * cap * hd * 2, cache),
         dout(static_cast<size_t>(S) * nh * hd * 2),
-        scratch(attn_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(hd), position));
+        scratch(attn_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(hd), position)), dpos(8, &position);
     cuda_check(launch_attention(dqg.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(), dqn.as<uint16_t>(),
-                                dkn.as<uint16_t>(), dcos.as<float>(), dsin.as<float>(), dcache.as<uint16_t>(), position, S,
+                                dkn.as<uint16_t>(), dcos.as<float>(), dsin.as<float>(), 0, dcache.as<uint16_t>(),
+                                dpos.as<int64_t>(), position, S,
                                 static_cast<int>(nh), static_cast<int>(nkv), static_cast<int>(hd), static_cast<int>(rot), cap,
                                 scratch.p, dout.as<uint16_t>(), nullptr), "attention");
     g_launches += 3;

@@ -1,6 +1,7 @@
 #include "engine.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 
@@ -11,6 +12,28 @@ namespace llmcp_b200 {
 namespace {
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// After a decode step of the device-resident loop: record the token, make it the next input,
+// advance the position and stage the rotary rows of the new position.
+__global__ void advance_kernel(const int64_t *__restrict__ next_token, int64_t *__restrict__ tokens,
+                               int64_t *__restrict__ generated, int64_t *__restrict__ step,
+                               int64_t *__restrict__ position, const float *__restrict__ cos_table,
+                               const float *__restrict__ sin_table, float *__restrict__ cos_row,
+                               float *__restrict__ sin_row, int rotary, int64_t capacity) {
+  const int64_t p = *position + 1;
+  const int i = threadIdx.x;
+  if (p < capacity && i < rotary) {
+    cos_row[i] = cos_table[p * rotary + i];
+    sin_row[i] = sin_table[p * rotary + i];
+  }
+  __syncthreads();
+  if (i == 0) {
+    generated[*step] = *next_token;
+    tokens[0] = *next_token;
+    *step += 1;
+    *position = p;
+  }
+}
 
 int dtype_of(const TensorEntry &t) {
   if (t.dtype == "BF16")
@@ -72,11 +95,22 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   argmax_v_ = static_cast<float *>(alloc(kArgmaxParts * 4));
   argmax_i_ = static_cast<int64_t *>(alloc(kArgmaxParts * 8));
   next_token_ = static_cast<int64_t *>(alloc(8));
+  position_dev_ = static_cast<int64_t *>(alloc(8));
+  step_dev_ = static_cast<int64_t *>(alloc(8));
+  check(cudaMallocHost(&position_pinned_, 8), "cudaMallocHost");
+  if (const char *flag = std::getenv("LLMCP_B200_NO_GRAPH"))
+    use_graph_ = std::atoi(flag) == 0;
   generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
   check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
   check(cudaMallocHost(&token_pinned_, 8), "cudaMallocHost");
   reset_state();
   ensure_workspace(1, capacity_ - 1);
+  // One throw-away decode step loads every kernel and applies its launch attributes, so that
+  // nothing of that kind happens later while a graph is being captured.
+  check(cudaMemsetAsync(tokens_, 0, 8, stream_), "warm-up");
+  set_position(0);
+  run(tokens_, 1, capacity_ - 1, cos_table_, sin_table_, 1);
+  reset_state();
   check(cudaStreamSynchronize(stream_), "engine setup");
 }
 
@@ -92,6 +126,10 @@ Engine::~Engine() {
     cudaFreeHost(logits_pinned_);
   if (token_pinned_)
     cudaFreeHost(token_pinned_);
+  if (position_pinned_)
+    cudaFreeHost(position_pinned_);
+  if (decode_graph_)
+    cudaGraphExecDestroy(decode_graph_);
   if (stream_)
     cudaStreamDestroy(stream_);
 }
@@ -226,6 +264,10 @@ void Engine::ensure_workspace(int64_t S, int64_t position) {
   if (S <= ws_tokens_ && need_attn <= attn_scratch_bytes_)
     return;
   check(cudaStreamSynchronize(stream_), "workspace resize");
+  if (decode_graph_) { // the captured step points into the buffers that are about to move
+    cudaGraphExecDestroy(decode_graph_);
+    decode_graph_ = nullptr;
+  }
   for (void *p : ws_allocations_)
     cudaFree(p);
   ws_allocations_.clear();
@@ -301,7 +343,42 @@ static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, 
   }
 }
 
-void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const float *cos_dev, const float *sin_dev) {
+void Engine::set_position(int64_t position) {
+  // The pinned word is reused: wait until an earlier copy has been consumed.
+  check(cudaStreamSynchronize(stream_), "set_position");
+  *position_pinned_ = position;
+  check(cudaMemcpyAsync(position_dev_, position_pinned_, 8, cudaMemcpyHostToDevice, stream_), "position");
+}
+
+void Engine::decode_step() {
+  if (!use_graph_) {
+    run(tokens_, 1, capacity_ - 1, cos_, sin_, 0);
+    return;
+  }
+  if (!decode_graph_) {
+    cudaGraph_t graph = nullptr;
+    const uint64_t before = launches_;
+    check(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed), "begin capture");
+    try {
+      run(tokens_, 1, capacity_ - 1, cos_, sin_, 0);
+    } catch (...) {
+      cudaStreamEndCapture(stream_, &graph);
+      if (graph)
+        cudaGraphDestroy(graph);
+      throw;
+    }
+    check(cudaStreamEndCapture(stream_, &graph), "end capture");
+    decode_graph_launches_ = launches_ - before;
+    launches_ = before;
+    check(cudaGraphInstantiate(&decode_graph_, graph, 0), "graph instantiate");
+    cudaGraphDestroy(graph);
+  }
+  check(cudaGraphLaunch(decode_graph_, stream_), "graph launch");
+  launches_ += decode_graph_launches_;
+}
+
+void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const float *cos_dev, const float *sin_dev,
+                 int rows_from_position) {
   const ModelDims &c = dims_;
   const int H = static_cast<int>(c.hidden);
   if (S <= 0 || position < 0 || position + S > capacity_)
@@ -349,8 +426,8 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
       run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_);
       check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
-                             static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev,
-                             kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim, position, S,
+                             static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
+                             kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim, position_dev_, position, S,
                              static_cast<int>(c.heads), static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim),
                              static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, stream_), "attention");
       launch_act_quant(attn_, kBF16, S, c.attn_dim(), aq_, as_, stream_);
@@ -389,15 +466,20 @@ int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position,
   if (S <= 0 || position < 0 || position + S > capacity_)
     throw std::runtime_error("sequence does not fit the cache");
   ensure_workspace(S, position);
+  set_position(position);
   check(cudaMemcpyAsync(tokens_, tokens, static_cast<size_t>(S) * 8, cudaMemcpyHostToDevice, stream_), "tokens");
-  const float *cos_dev = cos_table_ + position * c.rotary, *sin_dev = sin_table_ + position * c.rotary;
+  const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
   if (cos && sin) {
-    check(cudaMemcpyAsync(cos_, cos, static_cast<size_t>(S) * c.rotary * 4, cudaMemcpyHostToDevice, stream_), "cos");
-    check(cudaMemcpyAsync(sin_, sin, static_cast<size_t>(S) * c.rotary * 4, cudaMemcpyHostToDevice, stream_), "sin");
-    cos_dev = cos_;
-    sin_dev = sin_;
+    check(cudaMemcpyAsync(cos_, cos, static_cast<size_t>(S) * row_bytes, cudaMemcpyHostToDevice, stream_), "cos");
+    check(cudaMemcpyAsync(sin_, sin, static_cast<size_t>(S) * row_bytes, cudaMemcpyHostToDevice, stream_), "sin");
+  } else {
+    check(cudaMemcpyAsync(cos_, cos_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
+    check(cudaMemcpyAsync(sin_, sin_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
   }
-  run(tokens_, S, position, cos_dev, sin_dev);
+  if (S == 1)
+    decode_step();
+  else
+    run(tokens_, S, position, cos_, sin_, 0);
   if (logits_host)
     check(cudaMemcpyAsync(logits_pinned_, logits_, static_cast<size_t>(c.vocab) * 4, cudaMemcpyDeviceToHost, stream_), "logits");
   check(cudaMemcpyAsync(token_pinned_, next_token_, 8, cudaMemcpyDeviceToHost, stream_), "argmax");
@@ -412,16 +494,25 @@ void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int6
   check(cudaSetDevice(device_), "cudaSetDevice");
   if (steps <= 0 || position < 0 || position + steps > capacity_)
     throw std::runtime_error("generation does not fit the cache");
+  if (c.rotary > 1024)
+    throw std::runtime_error("rotary dimension too large");
+  set_position(position);
   *token_pinned_ = first_token;
-  check(cudaMemcpyAsync(next_token_, token_pinned_, 8, cudaMemcpyHostToDevice, stream_), "first token");
+  check(cudaMemcpyAsync(tokens_, token_pinned_, 8, cudaMemcpyHostToDevice, stream_), "first token");
+  check(cudaMemsetAsync(step_dev_, 0, 8, stream_), "step counter");
+  const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
+  check(cudaMemcpyAsync(cos_, cos_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
+  check(cudaMemcpyAsync(sin_, sin_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
   cudaEvent_t begin, end;
   check(cudaEventCreate(&begin), "event");
   check(cudaEventCreate(&end), "event");
   check(cudaEventRecord(begin, stream_), "event");
+  const int threads = static_cast<int>((c.rotary + 31) / 32 * 32);
   for (int64_t i = 0; i < steps; ++i) {
-    const int64_t p = position + i;
-    run(next_token_, 1, p, cos_table_ + p * c.rotary, sin_table_ + p * c.rotary);
-    check(cudaMemcpyAsync(generated_ + i, next_token_, 8, cudaMemcpyDeviceToDevice, stream_), "record token");
+    decode_step();
+    advance_kernel<<<1, threads, 0, stream_>>>(next_token_, tokens_, generated_, step_dev_, position_dev_, cos_table_,
+                                               sin_table_, cos_, sin_, static_cast<int>(c.rotary), capacity_);
+    launches_ += 1;
   }
   check(cudaEventRecord(end, stream_), "event");
   check(cudaStreamSynchronize(stream_), "generate");

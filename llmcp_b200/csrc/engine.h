@@ -76,8 +76,15 @@ public:
 private:
   void load_weights(const uint8_t *base, const Manifest &manifest);
   void ensure_workspace(int64_t S, int64_t position);
-  // tokens_dev: S ids on the device; cos/sin rows for positions [position, position+S).
-  void run(const int64_t *tokens_dev, int64_t S, int64_t position, const float *cos_dev, const float *sin_dev);
+  // Enqueues one forward over S tokens whose ids are at tokens_dev.  The start position is read
+  // from position_dev_ by the kernels; max_position bounds it (grid and scratch sizing).  cos/sin
+  // are the rows of this call, or tables over all positions when rows_from_position is set.
+  void run(const int64_t *tokens_dev, int64_t S, int64_t max_position, const float *cos_dev, const float *sin_dev,
+           int rows_from_position);
+  void set_position(int64_t position);
+  // The single-token forward over the staging buffers (tokens_, cos_, sin_, position_dev_),
+  // captured once as a CUDA graph and replayed for every decode step.
+  void decode_step();
   void linear(const Q8Weight &w, int64_t S, void *y, int y_dtype, int activation);
   void check(cudaError_t e, const char *what);
 
@@ -123,6 +130,12 @@ private:
   int64_t *generated_ = nullptr;  // device [capacity]
   float *logits_pinned_ = nullptr;
   int64_t *token_pinned_ = nullptr;
+  int64_t *position_dev_ = nullptr; // device scalar: start position of the running call
+  int64_t *step_dev_ = nullptr;     // device scalar: index into generated_
+  int64_t *position_pinned_ = nullptr;
+  cudaGraphExec_t decode_graph_ = nullptr;
+  uint64_t decode_graph_launches_ = 0;
+  bool use_graph_ = true;
 };
 
 } // namespace llmcp_b200

@@ -34,6 +34,10 @@ void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint1
 void launch_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *s, cudaStream_t stream);
 cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
                            cudaStream_t stream, int rows_per_warp = 0);
+// Specialised GEMV for K in {2560, 4096, 9216}; rows_per_group 0 = choose.
+bool gemv_rows_supported(int K);
+cudaError_t launch_gemv_q8_rows(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
+                                cudaStream_t stream, int rows_per_group);
 cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K, const int8_t *wq,
                                 const uint16_t *wd, int N, void *y, int y_dtype, int activation,
                                 int32_t *dots_out, cudaStream_t stream);
@@ -59,10 +63,14 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
                                    int a_log_dtype, const void *dt_bias, int dt_dtype, float *state, int64_t S,
                                    int nk, int nv, int dk, int dv, int b_activated, float *scratch,
                                    uint16_t *out, cudaStream_t stream);
-size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t position);
+// The start position is read from device memory (position_dev) so that a captured launch can be
+// replayed at another position; max_position bounds it (grid and scratch are sized for it).
+// rows_from_position: cos/sin are tables indexed by absolute position instead of the call's rows.
+size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t max_position);
 cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
-                             const uint16_t *k_norm, const float *cos, const float *sin, uint16_t *cache,
-                             int64_t position, int64_t S, int nh, int nkv, int hd, int rot, int64_t cap,
-                             void *scratch, uint16_t *out, cudaStream_t stream);
+                             const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
+                             uint16_t *cache, const int64_t *position_dev, int64_t max_position, int64_t S, int nh,
+                             int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out,
+                             cudaStream_t stream);
 
 } // namespace llmcp_b200

@@ -61,38 +61,54 @@ cudaError_t launch_causal_conv1d(const uint16_t *x, const uint16_t *w, uint16_t 
 // owns column v of a head's [dk, dv] state, keeps it in registers across the tokens of the
 // call, and runs the two ascending-k chains of each token.
 // ---------------------------------------------------------------------------------
-__global__ void gdn_prepare_kernel(const uint16_t *__restrict__ conv, const uint16_t *__restrict__ a,
-                                   const uint16_t *__restrict__ b, const void *__restrict__ a_log,
-                                   int a_log_dtype, const void *__restrict__ dt_bias, int dt_dtype,
-                                   int64_t S, int nk, int nv, int dk, int dv, int b_activated,
-                                   float *__restrict__ qn, float *__restrict__ kn,
-                                   float *__restrict__ beta, float *__restrict__ decay) {
-  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+// One warp per (token, key head) for the two norms (lane 0 adds the q squares in order,
+// lane 1 the k squares), then one thread per (token, value head) for beta and decay.
+__global__ void __launch_bounds__(128)
+gdn_prepare_kernel(const uint16_t *__restrict__ conv, const uint16_t *__restrict__ a,
+                   const uint16_t *__restrict__ b, const void *__restrict__ a_log, int a_log_dtype,
+                   const void *__restrict__ dt_bias, int dt_dtype, int64_t S, int nk, int nv, int dk, int dv,
+                   int b_activated, float *__restrict__ qn, float *__restrict__ kn, float *__restrict__ beta,
+                   float *__restrict__ decay) {
+  extern __shared__ float prep_all[]; // per warp: q squares [dk], k squares [dk]
+  const int lane = threadIdx.x & 31;
+  const int warp_in_cta = threadIdx.x >> 5;
+  const int64_t warp = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + warp_in_cta;
   const int64_t channels = 2 * static_cast<int64_t>(nk) * dk + static_cast<int64_t>(nv) * dv;
-  const float q_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(dk)));
-  if (i < S * nk) {
-    const int64_t t = i / nk;
-    const int kh = static_cast<int>(i % nk);
+  const int64_t norm_items = S * nk;
+  if (warp < norm_items) {
+    const int64_t t = warp / nk;
+    const int kh = static_cast<int>(warp % nk);
     const uint16_t *qp = conv + t * channels + kh * dk;
     const uint16_t *kp = conv + t * channels + static_cast<int64_t>(nk) * dk + kh * dk;
-    float q_sum = 0.0f, k_sum = 0.0f;
-    for (int d = 0; d < dk; ++d) {
-      const float v = bf16_to_f32(qp[d]);
-      q_sum = __fadd_rn(q_sum, __fmul_rn(v, v));
+    float *sq = prep_all + warp_in_cta * 2 * dk;
+    for (int d = lane; d < dk; d += 32) {
+      const float qv = bf16_to_f32(qp[d]), kv = bf16_to_f32(kp[d]);
+      sq[d] = __fmul_rn(qv, qv);
+      sq[dk + d] = __fmul_rn(kv, kv);
     }
-    for (int d = 0; d < dk; ++d) {
-      const float v = bf16_to_f32(kp[d]);
-      k_sum = __fadd_rn(k_sum, __fmul_rn(v, v));
+    __syncwarp();
+    float scale = 0.0f;
+    if (lane < 2) {
+      const float *mine = sq + lane * dk;
+      float sum = 0.0f;
+#pragma unroll 16
+      for (int d = 0; d < dk; ++d)
+        sum = __fadd_rn(sum, mine[d]);
+      scale = d_rsqrt(__fadd_rn(sum, 1.0e-6f));
+      if (lane == 0)
+        scale = __fmul_rn(scale, static_cast<float>(1.0 / sqrt(static_cast<double>(dk))));
     }
-    const float q_norm_scale = __fmul_rn(d_rsqrt(__fadd_rn(q_sum, 1.0e-6f)), q_scale);
-    const float k_inv = d_rsqrt(__fadd_rn(k_sum, 1.0e-6f));
+    const float q_norm_scale = __shfl_sync(0xffffffffu, scale, 0);
+    const float k_inv = __shfl_sync(0xffffffffu, scale, 1);
     float *qo = qn + (t * nk + kh) * dk;
     float *ko = kn + (t * nk + kh) * dk;
-    for (int d = 0; d < dk; ++d) {
+    for (int d = lane; d < dk; d += 32) {
       qo[d] = __fmul_rn(bf16_to_f32(qp[d]), q_norm_scale);
       ko[d] = __fmul_rn(bf16_to_f32(kp[d]), k_inv);
     }
+    return;
   }
+  const int64_t i = (warp - norm_items) * 32 + lane;
   if (i < S * nv) {
     const int h = static_cast<int>(i % nv);
     const float bv = bf16_to_f32(b[i]);
@@ -129,16 +145,44 @@ gdn_recurrence_kernel(const uint16_t *__restrict__ conv, const float *__restrict
     for (int k = 0; k < DK; ++k)
       s[k] = active ? col[static_cast<int64_t>(k) * dv] : 0.0f;
   }
+  // The inputs of token t+1 are fetched while token t is being computed.
+  constexpr int kPre = DK > 0 ? DK / 32 : 1;
+  float k_next[kPre], q_next[kPre];
+  float dc_next = 0.0f, bt_next = 0.0f;
+  uint16_t value_next = 0;
+  auto fetch = [&](int64_t t) {
+    if (DK > 0) {
+#pragma unroll
+      for (int u = 0; u < kPre; ++u) {
+        k_next[u] = kn[(t * nk + kh) * dk + u * 32 + threadIdx.x];
+        q_next[u] = qn[(t * nk + kh) * dk + u * 32 + threadIdx.x];
+      }
+    }
+    dc_next = decay[t * nv + h];
+    bt_next = beta[t * nv + h];
+    value_next = active ? conv[t * channels + 2 * static_cast<int64_t>(nk) * dk + h * dv + v] : static_cast<uint16_t>(0);
+  };
+  fetch(0);
   for (int64_t t = 0; t < S; ++t) {
     __syncwarp();
-    for (int d = threadIdx.x; d < dk; d += 32) {
-      k_sm[d] = kn[(t * nk + kh) * dk + d];
-      q_sm[d] = qn[(t * nk + kh) * dk + d];
+    if (DK > 0) {
+#pragma unroll
+      for (int u = 0; u < kPre; ++u) {
+        k_sm[u * 32 + threadIdx.x] = k_next[u];
+        q_sm[u * 32 + threadIdx.x] = q_next[u];
+      }
+    } else {
+      for (int d = threadIdx.x; d < dk; d += 32) {
+        k_sm[d] = kn[(t * nk + kh) * dk + d];
+        q_sm[d] = qn[(t * nk + kh) * dk + d];
+      }
     }
     __syncwarp();
-    const float dc = decay[t * nv + h];
-    const float bt = beta[t * nv + h];
-    const float value = active ? bf16_to_f32(conv[t * channels + 2 * static_cast<int64_t>(nk) * dk + h * dv + v]) : 0.0f;
+    const float dc = dc_next;
+    const float bt = bt_next;
+    const float value = bf16_to_f32(value_next);
+    if (t + 1 < S)
+      fetch(t + 1);
     float kv = 0.0f;
     if (DK > 0) {
 #pragma unroll
@@ -189,8 +233,8 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
   float *kn = qn + S * nk * dk;
   float *beta = kn + S * nk * dk;
   float *decay = beta + S * nv;
-  const int64_t threads = S * std::max(nk, nv);
-  gdn_prepare_kernel<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, stream>>>(
+  const int64_t warps = S * nk + (S * nv + 31) / 32;
+  gdn_prepare_kernel<<<static_cast<unsigned>((warps + 3) / 4), 128, 4 * 2 * dk * sizeof(float), stream>>>(
       conv, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, S, nk, nv, dk, dv, b_activated, qn, kn, beta, decay);
   dim3 grid(nv, (dv + 31) / 32);
   const size_t smem = 2 * static_cast<size_t>(dk) * sizeof(float);
@@ -214,9 +258,12 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
                                     const uint16_t *__restrict__ v, const uint16_t *__restrict__ q_norm,
                                     const uint16_t *__restrict__ k_norm, const float *__restrict__ cos,
                                     const float *__restrict__ sin, uint16_t *__restrict__ cache,
-                                    int64_t position, int64_t S, int nh, int nkv, int hd, int rot,
-                                    int64_t cap, uint16_t *__restrict__ qn) {
+                                    const int64_t *__restrict__ position_ptr, int rows_from_position, int64_t S,
+                                    int nh, int nkv, int hd, int rot, int64_t cap, uint16_t *__restrict__ qn) {
   extern __shared__ float prep_sm[]; // per warp: hd values
+  const int64_t position = *position_ptr;
+  // cos/sin hold either the rows of this call (row t) or a table over all positions.
+  const int64_t row_base = rows_from_position ? position : 0;
   const int lane = threadIdx.x & 31;
   const int warp_in_cta = threadIdx.x >> 5;
   const int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + warp_in_cta;
@@ -259,7 +306,7 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
     if (d < rot) {
       const bool second = d >= half;
       const float rotated = __fmul_rn(second ? 1.0f : -1.0f, tmp[second ? d - half : d + half]);
-      r = __fadd_rn(__fmul_rn(tmp[d], cos[t * rot + d]), __fmul_rn(rotated, sin[t * rot + d]));
+      r = __fadd_rn(__fmul_rn(tmp[d], cos[(row_base + t) * rot + d]), __fmul_rn(rotated, sin[(row_base + t) * rot + d]));
     }
     dst[d] = f32_to_bf16(r);
   }
@@ -271,13 +318,16 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
   }
 }
 
-constexpr int kKeyTile = 64; // LowerAttention.cpp:124
+constexpr int kKeyTile = 64;     // LowerAttention.cpp:124
+constexpr int kValueTile = 16;   // value rows per shared-memory stage (divides kKeyTile)
+constexpr int kValueStages = 12; // stages in flight: 12 x 16 x 256 x 2 B = 96 KB at head_dim 256
 
 // grid: (key tile, kv head, token); block: group * 64 threads (query head x key).
 __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
-                                   int64_t position, int nh, int nkv, int hd, int64_t cap,
+                                   const int64_t *__restrict__ position_ptr, int nh, int nkv, int hd, int64_t cap,
                                    int64_t score_stride, float *__restrict__ scores) {
   extern __shared__ __align__(16) unsigned char att_sm[];
+  const int64_t position = *position_ptr;
   const int group = nh / nkv;
   const int64_t t = blockIdx.z;
   const int kvh = blockIdx.y;
@@ -290,8 +340,23 @@ __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16
   float *k_sm = reinterpret_cast<float *>(att_sm);           // [64][hd+1]
   float *q_sm = k_sm + kKeyTile * kstride;                   // [group][hd]
   const uint16_t *kc = cache + (static_cast<int64_t>(kvh) * cap + start) * hd;
-  for (int i = threadIdx.x; i < keys * hd; i += blockDim.x)
-    k_sm[(i / hd) * kstride + (i % hd)] = bf16_to_f32(kc[i]);
+  if ((hd & 7) == 0) {
+    const int per_row = hd >> 3; // 16-byte pieces per key
+    for (int i = threadIdx.x; i < keys * per_row; i += blockDim.x) {
+      const int row = i / per_row, piece = i - row * per_row;
+      const uint4 raw = reinterpret_cast<const uint4 *>(kc)[i];
+      float *dst = k_sm + row * kstride + piece * 8;
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        dst[2 * u] = __uint_as_float(w[u] << 16);
+        dst[2 * u + 1] = __uint_as_float(w[u] & 0xffff0000u);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < keys * hd; i += blockDim.x)
+      k_sm[(i / hd) * kstride + (i % hd)] = bf16_to_f32(kc[i]);
+  }
   for (int i = threadIdx.x; i < group * hd; i += blockDim.x)
     q_sm[i] = bf16_to_f32(qn[(t * nh + kvh * group) * hd + i]);
   __syncthreads();
@@ -302,6 +367,7 @@ __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16
   const float *kr = k_sm + j * kstride;
   const float *qr = q_sm + g * hd;
   float dot = 0.0f;
+#pragma unroll 16
   for (int d = 0; d < hd; ++d)
     dot = __fadd_rn(dot, __fmul_rn(qr[d], kr[d]));
   const float scale = __fdiv_rn(1.0f, __fsqrt_rn(static_cast<float>(hd)));
@@ -309,74 +375,155 @@ __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16
 }
 
 // grid: (head, token); block: hd rounded up to a warp multiple.
+// Shared memory: the row's scores (turned into probabilities in place), then per key tile the
+// running maximum and the correction factor.  The maxima, corrections and probabilities are
+// formed tile by tile with the reference's operations but all up front; what is left for the
+// ordered part is  acc = acc * c_tile;  acc += p_j * V[j][d]  in ascending key order.
 __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint16_t *__restrict__ cache,
-                                    const uint16_t *__restrict__ qg, int64_t position, int nh, int nkv,
-                                    int hd, int64_t cap, int64_t score_stride, uint16_t *__restrict__ out) {
-  __shared__ float p_sm[kKeyTile];
-  __shared__ float max_sm;
+                                    const uint16_t *__restrict__ qg, const int64_t *__restrict__ position_ptr,
+                                    int nh, int nkv, int hd, int64_t cap, int64_t score_stride,
+                                    uint16_t *__restrict__ out) {
+  extern __shared__ __align__(16) float comb_sm[];
+  const int64_t position = *position_ptr;
   const int h = blockIdx.x;
   const int64_t t = blockIdx.y;
   const int kvh = h / (nh / nkv);
   const int d = threadIdx.x;
   const bool active = d < hd;
-  const int64_t query_end = position + t + 1;
+  const int total = static_cast<int>(position + t + 1);
+  const int tiles = (total + kKeyTile - 1) / kKeyTile;
+  float *p_sm = comb_sm;
+  float *m_sm = comb_sm + (static_cast<int>(score_stride) + 3) / 4 * 4;
+  float *c_sm = m_sm + (static_cast<int>(score_stride) + kKeyTile - 1) / kKeyTile;
   const float *srow = scores + (t * nh + h) * score_stride;
-  const uint16_t *vc = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd + (active ? d : 0);
-  float acc = 0.0f;
-  float running_max = -1.0e30f;
-  float running_sum = 0.0f;
-  for (int64_t start = 0; start < query_end; start += kKeyTile) {
-    const int keys = static_cast<int>(min(static_cast<int64_t>(kKeyTile), query_end - start));
-    __syncthreads(); // p_sm and max_sm of the previous tile are no longer read
-    if (threadIdx.x < 32) {
-      float m = -1.0e30f;
-      for (int j = threadIdx.x; j < keys; j += 32)
-        m = fmaxf(m, srow[start + j]);
-      for (int o = 16; o > 0; o >>= 1)
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      if (threadIdx.x == 0)
-        max_sm = fmaxf(running_max, m);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+
+  for (int j = threadIdx.x; j < total; j += blockDim.x)
+    p_sm[j] = srow[j];
+  __syncthreads();
+  for (int tile = warp; tile < tiles; tile += warps) {
+    float m = -1.0e30f;
+    for (int j = tile * kKeyTile + lane; j < min(total, (tile + 1) * kKeyTile); j += 32)
+      m = fmaxf(m, p_sm[j]);
+    for (int o = 16; o > 0; o >>= 1)
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0)
+      m_sm[tile] = m;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float running = -1.0e30f;
+    for (int tile = 0; tile < tiles; ++tile) {
+      const float next = fmaxf(running, m_sm[tile]);
+      c_sm[tile] = __fsub_rn(running, next); // exponent of the correction, exp taken below
+      m_sm[tile] = next;
+      running = next;
     }
-    __syncthreads();
-    const float new_max = max_sm;
-    for (int j = threadIdx.x; j < keys; j += blockDim.x)
-      p_sm[j] = d_exp(__fsub_rn(srow[start + j], new_max));
-    const float correction = d_exp(__fsub_rn(running_max, new_max));
-    __syncthreads();
-    acc = __fmul_rn(acc, correction);
-    float sum = __fmul_rn(running_sum, correction);
-    const uint16_t *vt = vc + start * hd;
-#pragma unroll 4
-    for (int j = 0; j < keys; ++j) {
+  }
+  __syncthreads();
+  for (int tile = threadIdx.x; tile < tiles; tile += blockDim.x)
+    c_sm[tile] = d_exp(c_sm[tile]);
+  for (int j = threadIdx.x; j < total; j += blockDim.x)
+    p_sm[j] = d_exp(__fsub_rn(p_sm[j], m_sm[j / kKeyTile]));
+  __syncthreads();
+
+  const uint16_t *vbase = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd;
+  float acc = 0.0f, sum = 0.0f;
+  if ((hd & 7) == 0) {
+    // Value rows stream through a ring of shared-memory stages filled by cp.async, deep enough
+    // that the ordered accumulation (one dependent add per key) never waits for memory.
+    const int used_floats = static_cast<int>(c_sm - comb_sm) + (static_cast<int>(score_stride) + kKeyTile - 1) / kKeyTile;
+    uint16_t *v_sm = reinterpret_cast<uint16_t *>(comb_sm + (used_floats + 3) / 4 * 4);
+    const int stage_elems = kValueTile * hd;
+    const int pieces = stage_elems >> 3; // 16-byte pieces per stage
+    const int value_tiles = (total + kValueTile - 1) / kValueTile;
+    auto issue = [&](int tile) {
+      if (tile < value_tiles) {
+        const int rows = min(kValueTile, total - tile * kValueTile);
+        const uint16_t *src = vbase + static_cast<int64_t>(tile) * stage_elems;
+        uint16_t *dst = v_sm + (tile % kValueStages) * stage_elems;
+        for (int i = threadIdx.x; i < (rows * hd) >> 3; i += blockDim.x) {
+          const uint32_t saddr = static_cast<uint32_t>(__cvta_generic_to_shared(dst + i * 8));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + i * 8) : "memory");
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    (void)pieces;
+    for (int tile = 0; tile < kValueStages - 1; ++tile)
+      issue(tile);
+    for (int tile = 0; tile < value_tiles; ++tile) {
+      asm volatile("cp.async.wait_group %0;" ::"n"(kValueStages - 2) : "memory");
+      __syncthreads(); // stage `tile` has landed for everyone; stage `tile - 1` is free again
+      issue(tile + kValueStages - 1);
+      const uint16_t *rows = v_sm + (tile % kValueStages) * stage_elems + (active ? d : 0);
+      const int first = tile * kValueTile;
+      if ((first & (kKeyTile - 1)) == 0) {
+        const float correction = c_sm[first / kKeyTile];
+        acc = __fmul_rn(acc, correction);
+        sum = __fmul_rn(sum, correction);
+      }
+      const int count = min(kValueTile, total - first);
+      if (count == kValueTile) {
+#pragma unroll
+        for (int u = 0; u < kValueTile; ++u) {
+          const float p = p_sm[first + u];
+          sum = __fadd_rn(sum, p);
+          acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(rows[u * hd])));
+        }
+      } else {
+        for (int u = 0; u < count; ++u) {
+          const float p = p_sm[first + u];
+          sum = __fadd_rn(sum, p);
+          acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(rows[u * hd])));
+        }
+      }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else {
+    const uint16_t *vc = vbase + (active ? d : 0);
+    for (int j = 0; j < total; ++j) {
+      if ((j & (kKeyTile - 1)) == 0) {
+        const float correction = c_sm[j / kKeyTile];
+        acc = __fmul_rn(acc, correction);
+        sum = __fmul_rn(sum, correction);
+      }
       const float p = p_sm[j];
       sum = __fadd_rn(sum, p);
       if (active)
-        acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(vt[static_cast<int64_t>(j) * hd])));
+        acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(vc[static_cast<int64_t>(j) * hd])));
     }
-    running_max = new_max;
-    running_sum = sum;
   }
   if (active) {
     const float gate = bf16_to_f32(qg[t * nh * 2 * hd + static_cast<int64_t>(h) * 2 * hd + hd + d]);
-    const float gated = __fmul_rn(__fdiv_rn(acc, running_sum), d_sigmoid(gate));
+    const float gated = __fmul_rn(__fdiv_rn(acc, sum), d_sigmoid(gate));
     out[t * nh * hd + static_cast<int64_t>(h) * hd + d] = f32_to_bf16(gated);
   }
 }
 
-size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t position) {
-  const size_t score_stride = static_cast<size_t>(position + S);
+static size_t combine_smem_bytes(int64_t score_stride, int hd) {
+  const size_t tiles = static_cast<size_t>((score_stride + kKeyTile - 1) / kKeyTile);
+  size_t bytes = ((static_cast<size_t>(score_stride) + 3) / 4 * 4 + 2 * tiles) * sizeof(float);
+  bytes = (bytes + 15) / 16 * 16;
+  if ((hd & 7) == 0)
+    bytes += static_cast<size_t>(kValueStages) * kValueTile * hd * sizeof(uint16_t);
+  return bytes;
+}
+
+size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t max_position) {
+  const size_t score_stride = static_cast<size_t>(max_position + S);
   return static_cast<size_t>(S) * nh * hd * sizeof(uint16_t) + 256 +
          static_cast<size_t>(S) * nh * score_stride * sizeof(float);
 }
 
 cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
                              const uint16_t *q_norm, const uint16_t *k_norm, const float *cos,
-                             const float *sin, uint16_t *cache, int64_t position, int64_t S, int nh,
-                             int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out,
-                             cudaStream_t stream) {
+                             const float *sin, int rows_from_position, uint16_t *cache,
+                             const int64_t *position_dev, int64_t max_position, int64_t S, int nh, int nkv,
+                             int hd, int rot, int64_t cap, void *scratch, uint16_t *out, cudaStream_t stream) {
   if (S == 0)
     return cudaSuccess;
-  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || rot % 2 != 0 || rot > hd || position + S > cap)
+  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || rot % 2 != 0 || rot > hd || max_position + S > cap)
     return cudaErrorInvalidValue;
   const int group = nh / nkv;
   if (group * kKeyTile > 1024 || hd > 1024)
@@ -384,28 +531,31 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   uint16_t *qn = static_cast<uint16_t *>(scratch);
   const size_t qn_bytes = (static_cast<size_t>(S) * nh * hd * sizeof(uint16_t) + 255) / 256 * 256;
   float *scores = reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + qn_bytes);
-  const int64_t score_stride = position + S;
+  const int64_t score_stride = max_position + S;
 
   const int64_t items = S * (nh + nkv);
   attn_prepare_kernel<<<static_cast<unsigned>((items + 3) / 4), 128, 4 * hd * sizeof(float), stream>>>(
-      qg, k, v, q_norm, k_norm, cos, sin, cache, position, S, nh, nkv, hd, rot, cap, qn);
+      qg, k, v, q_norm, k_norm, cos, sin, cache, position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn);
 
   const size_t smem = (static_cast<size_t>(kKeyTile) * (hd + 1) + static_cast<size_t>(group) * hd) * sizeof(float);
+  const size_t csmem = combine_smem_bytes(score_stride, hd);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess)
       return e;
     configured = true;
   }
-  if (smem > 200 * 1024)
-    return cudaErrorInvalidValue;
-  dim3 sgrid(static_cast<unsigned>((position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
-  attn_scores_kernel<<<sgrid, group * kKeyTile, smem, stream>>>(qn, cache, position, nh, nkv, hd, cap,
+  if (smem > 200 * 1024 || csmem > 200 * 1024)
+    return cudaErrorInvalidValue; // about 50,000 cached positions
+  dim3 sgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
+  attn_scores_kernel<<<sgrid, group * kKeyTile, smem, stream>>>(qn, cache, position_dev, nh, nkv, hd, cap,
                                                                score_stride, scores);
   dim3 cgrid(nh, static_cast<unsigned>(S));
-  attn_combine_kernel<<<cgrid, (hd + 31) / 32 * 32, 0, stream>>>(scores, cache, qg, position, nh, nkv, hd,
-                                                                cap, score_stride, out);
+  attn_combine_kernel<<<cgrid, (hd + 31) / 32 * 32, csmem, stream>>>(scores, cache, qg, position_dev, nh, nkv, hd,
+                                                                    cap, score_stride, out);
   return cudaGetLastError();
 }
 

@@ -51,12 +51,19 @@ rms_norm_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, 
   if (threadIdx.x == 0) {
     float sum = 0.0f;
     int d = 0;
-    for (; (H & 3) == 0 && d + 4 <= H; d += 4) {
-      const float4 t = *reinterpret_cast<const float4 *>(sq_sm + d);
-      sum = __fadd_rn(sum, t.x);
-      sum = __fadd_rn(sum, t.y);
-      sum = __fadd_rn(sum, t.z);
-      sum = __fadd_rn(sum, t.w);
+    // Loads run ahead of the dependent adds: 32 values are fetched, then added in order.
+    for (; (H & 3) == 0 && d + 32 <= H; d += 32) {
+      float4 t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        t[u] = *reinterpret_cast<const float4 *>(sq_sm + d + 4 * u);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        sum = __fadd_rn(sum, t[u].x);
+        sum = __fadd_rn(sum, t[u].y);
+        sum = __fadd_rn(sum, t[u].z);
+        sum = __fadd_rn(sum, t[u].w);
+      }
     }
     for (; d < H; ++d)
       sum = __fadd_rn(sum, sq_sm[d]);
@@ -85,6 +92,106 @@ rms_norm_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, 
   }
 }
 
+// The same operator for H % 32 == 0 with four consecutive elements per thread (8-byte loads
+// and stores, all of a row's loads in flight at once); eight neighbouring lanes hold one
+// quantisation block.
+__global__ void __launch_bounds__(1024)
+rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, int H,
+                     const void *__restrict__ w, int w_dtype, float eps, int zero_centered,
+                     uint16_t *__restrict__ sum_out, uint16_t *__restrict__ y, int8_t *__restrict__ q,
+                     float *__restrict__ s) {
+  extern __shared__ __align__(16) float vrow_sm[]; // squares
+  __shared__ float rstd_sm;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
+  const int quads = H >> 2;
+  const int per_thread = (quads + blockDim.x - 1) / blockDim.x; // 1 for H <= 4096
+  float x[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = r * blockDim.x + threadIdx.x;
+    if (r < per_thread && i < quads) {
+      const uint2 ra = reinterpret_cast<const uint2 *>(a + base)[i];
+      uint32_t words[2] = {ra.x, ra.y};
+      if (b) {
+        const uint2 rb = reinterpret_cast<const uint2 *>(b + base)[i];
+        const uint32_t wb[2] = {rb.x, rb.y};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint16_t lo = f32_to_bf16(__fadd_rn(__uint_as_float(words[u] << 16), __uint_as_float(wb[u] << 16)));
+          const uint16_t hi = f32_to_bf16(__fadd_rn(__uint_as_float(words[u] & 0xffff0000u), __uint_as_float(wb[u] & 0xffff0000u)));
+          words[u] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+        }
+        if (sum_out)
+          reinterpret_cast<uint2 *>(sum_out + base)[i] = make_uint2(words[0], words[1]);
+      }
+      x[r][0] = __uint_as_float(words[0] << 16);
+      x[r][1] = __uint_as_float(words[0] & 0xffff0000u);
+      x[r][2] = __uint_as_float(words[1] << 16);
+      x[r][3] = __uint_as_float(words[1] & 0xffff0000u);
+      reinterpret_cast<float4 *>(vrow_sm)[i] = make_float4(__fmul_rn(x[r][0], x[r][0]), __fmul_rn(x[r][1], x[r][1]),
+                                                            __fmul_rn(x[r][2], x[r][2]), __fmul_rn(x[r][3], x[r][3]));
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sum = 0.0f;
+    for (int d = 0; d < H; d += 32) {
+      float4 t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        t[u] = *reinterpret_cast<const float4 *>(vrow_sm + d + 4 * u);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        sum = __fadd_rn(sum, t[u].x);
+        sum = __fadd_rn(sum, t[u].y);
+        sum = __fadd_rn(sum, t[u].z);
+        sum = __fadd_rn(sum, t[u].w);
+      }
+    }
+    rstd_sm = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(H)), eps));
+  }
+  __syncthreads();
+  const float rstd = rstd_sm;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    if (r >= per_thread)
+      break;
+    const int i = r * blockDim.x + threadIdx.x;
+    const bool live = i < quads;
+    float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (live) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float wt = load_as_f32(w, w_dtype, 4 * i + u);
+        if (zero_centered)
+          wt = __fadd_rn(wt, 1.0f);
+        o[u] = bf16_to_f32(f32_to_bf16(__fmul_rn(__fmul_rn(x[r][u], rstd), wt)));
+      }
+      if (y)
+        reinterpret_cast<uint2 *>(y + base)[i] =
+            make_uint2(static_cast<uint32_t>(f32_to_bf16(o[0])) | (static_cast<uint32_t>(f32_to_bf16(o[1])) << 16),
+                       static_cast<uint32_t>(f32_to_bf16(o[2])) | (static_cast<uint32_t>(f32_to_bf16(o[3])) << 16));
+    }
+    if (q) {
+      float amax = fmaxf(fmaxf(fabsf(o[0]), fabsf(o[1])), fmaxf(fabsf(o[2]), fabsf(o[3])));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      if (live) {
+        const float scale = __fdiv_rn(amax, 127.0f);
+        const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
+        uint32_t packed = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          packed |= (static_cast<uint32_t>(__float2int_rn(__fmul_rn(o[u], inv))) & 0xffu) << (8 * u);
+        reinterpret_cast<uint32_t *>(q + base)[i] = packed;
+        if ((i & 7) == 0)
+          s[(base >> 5) + (i >> 3)] = scale;
+      }
+    }
+  }
+}
+
 cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int H, const void *w,
                             int w_dtype, float eps, int zero_centered, uint16_t *sum_out, uint16_t *y,
                             int8_t *q, float *s, cudaStream_t stream) {
@@ -92,6 +199,12 @@ cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int
     return cudaSuccess;
   if (q && H % kBlock != 0)
     return cudaErrorInvalidValue;
+  if (H % kBlock == 0 && H <= 16384) {
+    const int threads = std::min(1024, (H / 4 + 31) / 32 * 32);
+    rms_norm_vec4_kernel<<<static_cast<unsigned>(M), threads, H * sizeof(float), stream>>>(
+        a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s);
+    return cudaGetLastError();
+  }
   rms_norm_kernel<<<static_cast<unsigned>(M), 256, 2 * H * sizeof(float), stream>>>(
       a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s);
   return cudaGetLastError();

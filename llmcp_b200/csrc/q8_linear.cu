@@ -211,6 +211,10 @@ cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJ
                            int32_t *dots_out, cudaStream_t stream, int rows_per_warp) {
   if (jobs.count < 1 || jobs.count > kMaxGemvJobs || K % kBlock != 0)
     return cudaErrorInvalidValue;
+  if (gemv_rows_supported(K) && rows_per_warp >= 0)
+    return launch_gemv_q8_rows(aq, as, K, jobs, dots_out, stream, rows_per_warp);
+  if (rows_per_warp < 0)
+    rows_per_warp = 0; // negative: force the general kernel
   int total_rows = 0;
   for (int t = 0; t < jobs.count; ++t)
     total_rows += jobs.job[t].N;
