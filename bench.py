@@ -160,7 +160,7 @@ def gemv_roofline(L, torch, device):
         for _ in range(times):
             for r in range(GEMV_RING):
                 rc = lib.llmcp_dev_gemv_q8(ptr(aq), ptr(scales), C.c_int64(GEMV_K), ptr(wq[r]), ptr(wd[r]),
-                                           C.c_int64(GEMV_N), ptr(y), 0, 0, 0, C.c_void_p(stream))
+                                           C.c_int64(GEMV_N), ptr(y), 0, 0, 0, 1, C.c_void_p(stream))
                 assert rc == 0, L.last_error()
 
     sweep(3, stream)

@@ -121,12 +121,16 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
  *   llmcp_dev_repack_q8 : arena records -> q [N][K] int8 and d [N][K/32] f16 (device layout).
  *   llmcp_dev_act_quant : as llmcp_op_act_quant.
  *   llmcp_dev_gemv_q8   : M = 1 linear on already quantised input (Q8Decode.cpp:131-225).
+ *                         rows_per_warp 0 = choose.  flags: 1 = launch as a programmatic
+ *                         dependent of the kernel in front (weights are requested while that
+ *                         kernel still runs; x is read only after it has finished), 2 = also
+ *                         prefetch the whole matrix into L2 first.
  *   llmcp_dev_gemm_q8   : M > 1 linear (Q8Matmul.cpp:143-289).
  *   llmcp_dev_argmax    : first maximum of n f32 values; scratch: 512 floats + 512 int64. */
 int llmcp_dev_repack_q8(const uint8_t *records, int64_t N, int64_t K, int8_t *q, uint16_t *d, void *stream);
 int llmcp_dev_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales, void *stream);
 int llmcp_dev_gemv_q8(const int8_t *aq, const float *as, int64_t K, const int8_t *wq, const uint16_t *wd, int64_t N,
-                      void *y, int y_dtype, int activation, int rows_per_warp, void *stream);
+                      void *y, int y_dtype, int activation, int rows_per_warp, int flags, void *stream);
 int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
                       int64_t N, void *y, int y_dtype, int activation, void *stream);
 int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *scratch_indices, int64_t *out_index,

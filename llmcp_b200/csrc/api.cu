@@ -119,10 +119,11 @@ struct DeviceQ8 {
 
 void run_linear(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
                 int64_t N, void *y, int y_dtype, int activation, int32_t *dots, int rows_per_warp,
-                cudaStream_t stream) {
+                cudaStream_t stream, int flags = 0) {
   if (M == 1) {
     GemvJobs jobs{};
     jobs.count = 1;
+    jobs.flags = flags;
     jobs.job[0].wq = wq;
     jobs.job[0].wd = wd;
     jobs.job[0].y = y;
@@ -559,7 +560,7 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
                                 dkn.as<uint16_t>(), dcos.as<float>(), dsin.as<float>(), 0, dcache.as<uint16_t>(),
                                 dpos.as<int64_t>(), position, S,
                                 static_cast<int>(nh), static_cast<int>(nkv), static_cast<int>(hd), static_cast<int>(rot), cap,
-                                scratch.p, dout.as<uint16_t>(), nullptr), "attention");
+                                scratch.p, dout.as<uint16_t>(), nullptr, nullptr, nullptr), "attention");
     g_launches += 3;
     cuda_check(cudaDeviceSynchronize(), "attention");
     dout.to_host(out, dout.bytes);
@@ -588,10 +589,10 @@ int llmcp_dev_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t
 }
 
 int llmcp_dev_gemv_q8(const int8_t *aq, const float *as, int64_t K, const int8_t *wq, const uint16_t *wd, int64_t N,
-                      void *y, int y_dtype, int activation, int rows_per_warp, void *stream) {
+                      void *y, int y_dtype, int activation, int rows_per_warp, int flags, void *stream) {
   return guarded_async([&] {
     check_q8_shape(N, K);
-    run_linear(aq, as, 1, K, wq, wd, N, y, y_dtype, activation, nullptr, rows_per_warp, static_cast<cudaStream_t>(stream));
+    run_linear(aq, as, 1, K, wq, wd, N, y, y_dtype, activation, nullptr, rows_per_warp, static_cast<cudaStream_t>(stream), flags);
   });
 }
 

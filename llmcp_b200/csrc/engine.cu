@@ -100,6 +100,8 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   check(cudaMallocHost(&position_pinned_, 8), "cudaMallocHost");
   if (const char *flag = std::getenv("LLMCP_B200_NO_GRAPH"))
     use_graph_ = std::atoi(flag) == 0;
+  if (const char *flag = std::getenv("LLMCP_B200_GEMV_FLAGS"))
+    gemv_flags_ = std::atoi(flag);
   generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
   check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
   check(cudaMallocHost(&token_pinned_, 8), "cudaMallocHost");
@@ -316,10 +318,11 @@ struct LinearJob {
 };
 
 static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
-                        cudaStream_t stream, uint64_t *launches) {
+                        cudaStream_t stream, uint64_t *launches, int flags) {
   if (S == 1) {
     GemvJobs g{};
     g.count = count;
+    g.flags = flags;
     for (int i = 0; i < count; ++i) {
       g.job[i].wq = jobs[i].w->q;
       g.job[i].wd = jobs[i].w->d;
@@ -406,7 +409,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_);
+      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags_);
       const int C = static_cast<int>(c.qkv_dim());
       check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data),
                                  conv_ + lin_index * (c.conv_kernel - 1) * C, S, C, static_cast<int>(c.conv_kernel),
@@ -420,31 +423,30 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                   static_cast<int>(c.lin_v_dim), c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
       launches_ += 5;
       const LinearJob out = {&L.out_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_);
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_);
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_);
+      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags_);
       check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                              static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
                              kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim, position_dev_, position, S,
                              static_cast<int>(c.heads), static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim),
-                             static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, stream_), "attention");
-      launch_act_quant(attn_, kBF16, S, c.attn_dim(), aq_, as_, stream_);
-      launches_ += 4;
+                             static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, aq_, as_, stream_), "attention");
+      launches_ += 3;
       const LinearJob out = {&L.o_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_);
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_);
       ++full_index;
     }
     check(launch_rms_norm(hidden_[cur], branch_, S, H, L.post_norm.data, L.post_norm.dtype, c.eps, 1, hidden_[cur ^ 1],
                           nullptr, aq_, as_, stream_), "rms_norm");
     cur ^= 1;
     const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_);
+    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags_);
     check(launch_pointwise(gate_, up_, S * c.intermediate, 1, nullptr, aq_, as_, stream_), "mul");
     launches_ += 2;
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
-    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_);
+    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags_);
     pending = true;
   }
   // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
@@ -453,7 +455,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                         c.eps, 1, nullptr, final_hidden_, aq_, as_, stream_), "final rms_norm");
   const Q8Weight &table = embed_;
   const LinearJob head = {&table, logits_, kF32, kNone};
-  run_linears(this, aq_, as_, 1, &head, 1, stream_, &launches_);
+  run_linears(this, aq_, as_, 1, &head, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious);
   launch_argmax(logits_, c.vocab, argmax_v_, argmax_i_, 0, next_token_, nullptr, stream_);
   launches_ += 3;
   check(cudaGetLastError(), "forward");

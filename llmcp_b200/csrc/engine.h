@@ -136,6 +136,7 @@ private:
   cudaGraphExec_t decode_graph_ = nullptr;
   uint64_t decode_graph_launches_ = 0;
   bool use_graph_ = true;
+  int gemv_flags_ = 3; // kGemvOverlapPrevious | kGemvPrefetchL2
 };
 
 } // namespace llmcp_b200

@@ -30,16 +30,14 @@ __device__ inline Block32 ld_block(const void *p) {
   return r;
 }
 
-constexpr int kWarps = 8;
-
-template <int NB, int RC> constexpr size_t rows_smem_bytes() {
-  return static_cast<size_t>(NB) * 32 + NB * 4 + static_cast<size_t>(kWarps) * RC * (NB + 1) * sizeof(float2);
+template <int NB, int RC> constexpr size_t rows_smem_bytes(int warps) {
+  return static_cast<size_t>(NB) * 32 + NB * 4 + static_cast<size_t>(warps) * RC * (NB + 1) * sizeof(float2);
 }
 
 // NB: blocks per row (K/32).  RC: rows per group (one chain lane each).  RL: rows whose loads
 // are issued together (RC % RL == 0).
 template <int NB, int RC, int RL, bool DOTS>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(256)
 gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const GemvJobs jobs,
                     int total_groups, int32_t *__restrict__ dots_out) {
   constexpr int K = NB * 32;
@@ -50,57 +48,96 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
   float *as_sm = reinterpret_cast<float *>(smem + K);
   float2 *slabs = reinterpret_cast<float2 *>(smem + K + NB * 4);
 
-  for (int i = threadIdx.x; i < 2 * NB; i += kWarps * 32) {
+  const int kWarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int warp_in_cta = threadIdx.x >> 5;
+  float2 *slab = slabs + warp_in_cta * RC * (NB + 1);
+  const int total_warps = gridDim.x * kWarps;
+  const int first_group = blockIdx.x * kWarps + warp_in_cta;
+
+  struct Rows {
+    const int8_t *wq;
+    const uint16_t *wd;
+    void *y;
+    int row0, activation, y_dtype, dots_offset;
+  };
+  // Which matrix and which rows a group stands for; warp_begin holds each matrix's first group.
+  auto resolve = [&](int g) {
+    Rows c{jobs.job[0].wq, jobs.job[0].wd, jobs.job[0].y, 0, jobs.job[0].activation, jobs.job[0].y_dtype, 0};
+    int begin = 0;
+#pragma unroll
+    for (int t = 1; t < kMaxGemvJobs; ++t)
+      if (t < jobs.count && g >= jobs.job[t].warp_begin) {
+        c.wq = jobs.job[t].wq;
+        c.wd = jobs.job[t].wd;
+        c.y = jobs.job[t].y;
+        begin = jobs.job[t].warp_begin;
+        c.activation = jobs.job[t].activation;
+        c.y_dtype = jobs.job[t].y_dtype;
+        c.dots_offset = jobs.job[t].dots_offset;
+      }
+    c.row0 = (g - begin) * RC;
+    return c;
+  };
+  Block32 w[RL][NL];
+  uint16_t dbits[RL][NL];
+  auto load = [&](const Rows &c, int r0) {
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+      const int8_t *wrow = c.wq + static_cast<size_t>(c.row0 + r0 + r) * K + lane * 32;
+      const uint16_t *drow = c.wd + static_cast<size_t>(c.row0 + r0 + r) * NB + lane;
+#pragma unroll
+      for (int i = 0; i < NL; ++i) {
+        if (32 * i + 32 <= NB || lane < NB - 32 * i) {
+          w[r][i] = ld_block(wrow + i * 1024);
+          dbits[r][i] = __ldg(drow + 32 * i);
+        }
+      }
+    }
+  };
+
+  // The weights do not depend on the kernel in front of this one: the first rows are requested
+  // (and, for matrices that fit in L2, the rest is prefetched into L2) before waiting for it.
+  bool preloaded = false;
+  if (first_group < total_groups) {
+    const Rows c = resolve(first_group);
+    load(c, 0);
+    preloaded = true;
+    if ((jobs.flags & kGemvPrefetchL2) && lane == 0) {
+      for (int g = first_group; g < total_groups; g += total_warps) {
+        const Rows p = resolve(g);
+        const int skip = g == first_group ? RL : 0;
+        if (RC - skip > 0) {
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.wq + static_cast<size_t>(p.row0 + skip) * K),
+                       "r"((RC - skip) * K)
+                       : "memory");
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.wd + static_cast<size_t>(p.row0 + skip) * NB),
+                       "r"((RC - skip) * NB * 2)
+                       : "memory");
+        }
+      }
+    }
+  }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  for (int i = threadIdx.x; i < 2 * NB; i += blockDim.x) {
     const uint4 v = reinterpret_cast<const uint4 *>(aq)[i];
     if (i & 1)
       a_hi[i >> 1] = v;
     else
       a_lo[i >> 1] = v;
   }
-  for (int i = threadIdx.x; i < NB; i += kWarps * 32)
+  for (int i = threadIdx.x; i < NB; i += blockDim.x)
     as_sm[i] = as[i];
   __syncthreads();
 
-  const int lane = threadIdx.x & 31;
-  const int warp_in_cta = threadIdx.x >> 5;
-  float2 *slab = slabs + warp_in_cta * RC * (NB + 1);
-  const int total_warps = gridDim.x * kWarps;
-
-  for (int g = blockIdx.x * kWarps + warp_in_cta; g < total_groups; g += total_warps) {
-    // Which matrix, which rows.  warp_begin holds the first group of each matrix.
-    const int8_t *wq = jobs.job[0].wq;
-    const uint16_t *wd = jobs.job[0].wd;
-    void *y = jobs.job[0].y;
-    int begin = 0, activation = jobs.job[0].activation, y_dtype = jobs.job[0].y_dtype, dots_offset = 0;
-#pragma unroll
-    for (int t = 1; t < kMaxGemvJobs; ++t)
-      if (t < jobs.count && g >= jobs.job[t].warp_begin) {
-        wq = jobs.job[t].wq;
-        wd = jobs.job[t].wd;
-        y = jobs.job[t].y;
-        begin = jobs.job[t].warp_begin;
-        activation = jobs.job[t].activation;
-        y_dtype = jobs.job[t].y_dtype;
-        dots_offset = jobs.job[t].dots_offset;
-      }
-    const int row0 = (g - begin) * RC;
-
+  for (int g = first_group; g < total_groups; g += total_warps) {
+    const Rows c = resolve(g);
 #pragma unroll
     for (int r0 = 0; r0 < RC; r0 += RL) {
-      Block32 w[RL][NL];
-      uint16_t dbits[RL][NL];
-#pragma unroll
-      for (int r = 0; r < RL; ++r) {
-        const int8_t *wrow = wq + static_cast<size_t>(row0 + r0 + r) * K + lane * 32;
-        const uint16_t *drow = wd + static_cast<size_t>(row0 + r0 + r) * NB + lane;
-#pragma unroll
-        for (int i = 0; i < NL; ++i) {
-          if (32 * i + 32 <= NB || lane < NB - 32 * i) {
-            w[r][i] = ld_block(wrow + i * 1024);
-            dbits[r][i] = __ldg(drow + 32 * i);
-          }
-        }
-      }
+      if (!(r0 == 0 && preloaded))
+        load(c, r0);
 #pragma unroll
       for (int r = 0; r < RL; ++r) {
 #pragma unroll
@@ -119,11 +156,12 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
             const float factor = __fmul_rn(as_sm[kb], f16_bits_to_f32(dbits[r][i]));
             slab[(r0 + r) * (NB + 1) + kb] = make_float2(static_cast<float>(dot), factor);
             if (DOTS)
-              dots_out[static_cast<size_t>(dots_offset + row0 + r0 + r) * NB + kb] = dot;
+              dots_out[static_cast<size_t>(c.dots_offset + c.row0 + r0 + r) * NB + kb] = dot;
           }
         }
       }
     }
+    preloaded = false;
     __syncwarp();
     if (lane < RC) {
       const float2 *mine = slab + lane * (NB + 1);
@@ -133,7 +171,7 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
         const float2 v = mine[kb];
         acc = __fmaf_rn(v.x, v.y, acc);
       }
-      store_from_f32(y, y_dtype, row0 + lane, apply_activation(acc, activation));
+      store_from_f32(c.y, c.y_dtype, c.row0 + lane, apply_activation(acc, c.activation));
     }
     __syncwarp();
   }
@@ -150,32 +188,52 @@ cudaError_t launch_rows(const int8_t *aq, const float *as, GemvJobs jobs, int32_
     groups += jobs.job[t].N / RC;
     rows += jobs.job[t].N;
   }
-  constexpr size_t smem = rows_smem_bytes<NB, RC>();
-  static int ctas_per_sm = 0;
-  if (ctas_per_sm == 0) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_q8_rows_kernel<NB, RC, RL, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess)
+      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemv_q8_rows_kernel<NB, RC, RL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               200 * 1024);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gemv_q8_rows_kernel<NB, RC, RL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem));
-    if (e == cudaSuccess)
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_q8_rows_kernel<NB, RC, RL, false>,
-                                                        kWarps * 32, smem);
-    if (e != cudaSuccess)
+                               200 * 1024);
+    if (e != cudaSuccess) {
+      sms = 0;
       return e;
-    if (ctas_per_sm < 1)
-      return cudaErrorInvalidConfiguration;
+    }
   }
-  int sms = 148;
-  int device = 0;
-  if (cudaGetDevice(&device) == cudaSuccess)
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  const int ctas = std::min((groups + kWarps - 1) / kWarps, sms * ctas_per_sm);
+  // Eight-warp CTAs, several per SM; with about one group per resident warp every weight byte
+  // of a small matrix is requested in the first microsecond.  More groups than resident warps
+  // (the vocabulary projection) are walked with a grid stride.
+  constexpr int warps = 8;
+  const size_t smem = rows_smem_bytes<NB, RC>(warps);
+  static int ctas_per_sm = 0;
+  if (ctas_per_sm == 0) {
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_q8_rows_kernel<NB, RC, RL, false>,
+                                                                  warps * 32, smem);
+    if (e != cudaSuccess || ctas_per_sm < 1) {
+      ctas_per_sm = 0;
+      return e != cudaSuccess ? e : cudaErrorInvalidConfiguration;
+    }
+  }
+  const int ctas = std::min((groups + warps - 1) / warps, sms * ctas_per_sm);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(ctas);
+  config.blockDim = dim3(warps * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (jobs.flags & kGemvOverlapPrevious) ? 1 : 0;
+  int32_t *no_dots = nullptr;
   if (dots_out)
-    gemv_q8_rows_kernel<NB, RC, RL, true><<<ctas, kWarps * 32, smem, stream>>>(aq, as, jobs, groups, dots_out);
-  else
-    gemv_q8_rows_kernel<NB, RC, RL, false><<<ctas, kWarps * 32, smem, stream>>>(aq, as, jobs, groups, nullptr);
-  return cudaGetLastError();
+    return cudaLaunchKernelEx(&config, gemv_q8_rows_kernel<NB, RC, RL, true>, aq, as, jobs, groups, dots_out);
+  return cudaLaunchKernelEx(&config, gemv_q8_rows_kernel<NB, RC, RL, false>, aq, as, jobs, groups, no_dots);
 }
 
 template <int NI>

@@ -25,9 +25,15 @@ struct GemvJob {
   int dots_offset; // filled by the launcher
 };
 
+// flags of a GEMV launch
+constexpr int kGemvOverlapPrevious = 1; // programmatic dependent launch: start while the kernel in
+                                        // front is still running, wait for it before reading x
+constexpr int kGemvPrefetchL2 = 2;      // prefetch all weights of the launch into L2 up front
+
 struct GemvJobs {
   GemvJob job[kMaxGemvJobs];
   int count;
+  int flags;
 };
 
 void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint16_t *d, cudaStream_t stream);
@@ -66,11 +72,12 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
 // The start position is read from device memory (position_dev) so that a captured launch can be
 // replayed at another position; max_position bounds it (grid and scratch are sized for it).
 // rows_from_position: cos/sin are tables indexed by absolute position instead of the call's rows.
+// q_out / s_out (optional): int8 quantisation of the output for the linear that follows.
 size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t max_position);
 cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
                              const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
                              uint16_t *cache, const int64_t *position_dev, int64_t max_position, int64_t S, int nh,
-                             int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out,
-                             cudaStream_t stream);
+                             int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out,
+                             float *s_out, cudaStream_t stream);
 
 } // namespace llmcp_b200

@@ -319,8 +319,8 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
 }
 
 constexpr int kKeyTile = 64;     // LowerAttention.cpp:124
-constexpr int kValueTile = 16;   // value rows per shared-memory stage (divides kKeyTile)
-constexpr int kValueStages = 12; // stages in flight: 12 x 16 x 256 x 2 B = 96 KB at head_dim 256
+constexpr int kValueTile = 32;  // value rows per shared-memory stage (divides kKeyTile)
+constexpr int kValueStages = 6; // stages in flight: 6 x 32 x 256 x 2 B = 96 KB at head_dim 256
 
 // grid: (key tile, kv head, token); block: group * 64 threads (query head x key).
 __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
@@ -382,8 +382,10 @@ __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16
 __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint16_t *__restrict__ cache,
                                     const uint16_t *__restrict__ qg, const int64_t *__restrict__ position_ptr,
                                     int nh, int nkv, int hd, int64_t cap, int64_t score_stride,
-                                    uint16_t *__restrict__ out) {
+                                    uint16_t *__restrict__ out, int8_t *__restrict__ q_out,
+                                    float *__restrict__ s_out) {
   extern __shared__ __align__(16) float comb_sm[];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t position = *position_ptr;
   const int h = blockIdx.x;
   const int64_t t = blockIdx.y;
@@ -494,10 +496,27 @@ __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint
         acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(vc[static_cast<int64_t>(j) * hd])));
     }
   }
+  float result = 0.0f;
+  const int64_t index = t * nh * hd + static_cast<int64_t>(h) * hd + d;
   if (active) {
     const float gate = bf16_to_f32(qg[t * nh * 2 * hd + static_cast<int64_t>(h) * 2 * hd + hd + d]);
     const float gated = __fmul_rn(__fdiv_rn(acc, sum), d_sigmoid(gate));
-    out[t * nh * hd + static_cast<int64_t>(h) * hd + d] = f32_to_bf16(gated);
+    const uint16_t bits = f32_to_bf16(gated);
+    out[index] = bits;
+    result = bf16_to_f32(bits);
+  }
+  if (q_out) { // the quantisation the following o_proj needs (Q8Decode.cpp:83-120); hd % 32 == 0
+    float amax = fabsf(result);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = __fdiv_rn(amax, 127.0f);
+    const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
+    if (active) {
+      q_out[index] = static_cast<int8_t>(__float2int_rn(__fmul_rn(result, inv)));
+      if (lane == 0)
+        s_out[index >> 5] = scale;
+    }
   }
 }
 
@@ -520,9 +539,12 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
                              const uint16_t *q_norm, const uint16_t *k_norm, const float *cos,
                              const float *sin, int rows_from_position, uint16_t *cache,
                              const int64_t *position_dev, int64_t max_position, int64_t S, int nh, int nkv,
-                             int hd, int rot, int64_t cap, void *scratch, uint16_t *out, cudaStream_t stream) {
+                             int hd, int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out, float *s_out,
+                             cudaStream_t stream) {
   if (S == 0)
     return cudaSuccess;
+  if (q_out && hd % kBlock != 0)
+    return cudaErrorInvalidValue;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || rot % 2 != 0 || rot > hd || max_position + S > cap)
     return cudaErrorInvalidValue;
   const int group = nh / nkv;
@@ -555,7 +577,7 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
                                                                score_stride, scores);
   dim3 cgrid(nh, static_cast<unsigned>(S));
   attn_combine_kernel<<<cgrid, (hd + 31) / 32 * 32, csmem, stream>>>(scores, cache, qg, position_dev, nh, nkv, hd,
-                                                                    cap, score_stride, out);
+                                                                    cap, score_stride, out, q_out, s_out);
   return cudaGetLastError();
 }
 

@@ -102,6 +102,9 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
                      float *__restrict__ s) {
   extern __shared__ __align__(16) float vrow_sm[]; // squares
   __shared__ float rstd_sm;
+  // Lets a following kernel that was launched as a programmatic dependent start its own
+  // input-independent prologue now; it still waits for this kernel to finish before reading.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
   const int quads = H >> 2;
   const int per_thread = (quads + blockDim.x - 1) / blockDim.x; // 1 for H <= 4096
@@ -218,6 +221,7 @@ gated_rms_norm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict
                       float eps, int gate_activated, uint16_t *__restrict__ y, int8_t *__restrict__ q,
                       float *__restrict__ s) {
   extern __shared__ float sq_all[];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int warp_in_cta = threadIdx.x >> 5;
   const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + warp_in_cta;
@@ -277,6 +281,7 @@ cudaError_t launch_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const
 __global__ void pointwise_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b,
                                  int64_t count, int op, uint16_t *__restrict__ y, int8_t *__restrict__ q,
                                  float *__restrict__ s) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   float out = 0.0f;
   if (i < count) {
