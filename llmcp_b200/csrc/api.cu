@@ -107,15 +107,35 @@ void check_q8_shape(int64_t N, int64_t K) {
 
 // Uploads packed records and re-lays them out: returns q and d planes.
 struct DeviceQ8 {
-  Buf q, d;
+  Buf q, d, d32;
   DeviceQ8(const uint8_t *records, int64_t N, int64_t K)
-      : q(static_cast<size_t>(N) * K), d(static_cast<size_t>(N) * (K / 32) * 2) {
+      : q(static_cast<size_t>(N) * K), d(static_cast<size_t>(N) * (K / 32) * 2), d32(static_cast<size_t>(N) * (K / 32) * 4) {
     Buf staging(static_cast<size_t>(N) * (K / 32) * 34, records);
-    launch_repack_p4(staging.as<uint8_t>(), N, K, q.as<int8_t>(), d.as<uint16_t>(), nullptr);
+    launch_repack_p4(staging.as<uint8_t>(), N, K, q.as<int8_t>(), d.as<uint16_t>(), d32.as<float>(), nullptr);
     cuda_check(cudaDeviceSynchronize(), "repack");
     g_launches += 1;
   }
 };
+
+bool tensor_core_gemm_enabled() {
+  const char *flag = std::getenv("LLMCP_B200_GEMM");
+  return !(flag && std::string(flag) == "dp4a");
+}
+
+// Tensor-core GEMM with its status word checked after completion (synchronises).
+void run_gemm_tc(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const float *wd32, int64_t N,
+                 void *y, int y_dtype, int activation, int32_t *dots) {
+  int zero = 0;
+  Buf status(4, &zero);
+  cuda_check(launch_gemm_q8_tc(aq, as, static_cast<int>(M), static_cast<int>(K), wq, wd32, static_cast<int>(N), y, y_dtype,
+                               activation, dots, status.as<int>(), nullptr), "gemm");
+  g_launches += 1;
+  cuda_check(cudaDeviceSynchronize(), "gemm");
+  int raised = 0;
+  status.to_host(&raised, 4);
+  if (raised)
+    throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
+}
 
 void run_linear(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
                 int64_t N, void *y, int y_dtype, int activation, int32_t *dots, int rows_per_warp,
@@ -392,8 +412,12 @@ int llmcp_op_linear_q8(const void *x, int x_dtype, int64_t M, int64_t K, const u
     Buf dots(block_dots ? static_cast<size_t>(M) * N * (K / 32) * 4 : 0);
     launch_act_quant(dx.p, x_dtype, M, K, dq.as<int8_t>(), ds.as<float>(), nullptr);
     g_launches += 1;
-    run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), N, dy.p, y_dtype, activation,
-               block_dots ? dots.as<int32_t>() : nullptr, 0, nullptr);
+    if (M > 1 && tensor_core_gemm_enabled())
+      run_gemm_tc(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d32.as<float>(), N, dy.p, y_dtype, activation,
+                  block_dots ? dots.as<int32_t>() : nullptr);
+    else
+      run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), N, dy.p, y_dtype, activation,
+                 block_dots ? dots.as<int32_t>() : nullptr, 0, nullptr);
     cuda_check(cudaDeviceSynchronize(), "linear");
     dy.to_host(y, dy.bytes);
     if (block_dots)
@@ -413,8 +437,11 @@ int llmcp_op_lm_head_q8(const uint16_t *hidden, int64_t M, int64_t K, const uint
     Buf dy(static_cast<size_t>(M) * vocab * 4), sv(kArgmaxParts * 4), si(kArgmaxParts * 8), out(static_cast<size_t>(M) * 8);
     launch_act_quant(dx.p, kBF16, M, K, dq.as<int8_t>(), ds.as<float>(), nullptr);
     g_launches += 1;
-    run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), vocab, dy.p, kF32, kNone,
-               nullptr, 0, nullptr);
+    if (M > 1 && tensor_core_gemm_enabled())
+      run_gemm_tc(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d32.as<float>(), vocab, dy.p, kF32, kNone, nullptr);
+    else
+      run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), vocab, dy.p, kF32, kNone,
+                 nullptr, 0, nullptr);
     for (int64_t m = 0; m < M; ++m) {
       launch_argmax(dy.as<float>() + m * vocab, vocab, sv.as<float>(), si.as<int64_t>(), 0, out.as<int64_t>() + m,
                     nullptr, nullptr);
@@ -572,7 +599,7 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
 int llmcp_dev_repack_q8(const uint8_t *records, int64_t N, int64_t K, int8_t *q, uint16_t *d, void *stream) {
   return guarded_async([&] {
     check_q8_shape(N, K);
-    launch_repack_p4(records, N, K, q, d, static_cast<cudaStream_t>(stream));
+    launch_repack_p4(records, N, K, q, d, nullptr, static_cast<cudaStream_t>(stream));
     g_launches += 1;
     cuda_check(cudaGetLastError(), "repack");
   });

@@ -102,6 +102,10 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     use_graph_ = std::atoi(flag) == 0;
   if (const char *flag = std::getenv("LLMCP_B200_GEMV_FLAGS"))
     gemv_flags_ = std::atoi(flag);
+  if (const char *flag = std::getenv("LLMCP_B200_GEMM"))
+    use_tensor_cores_ = std::string(flag) != "dp4a";
+  gemm_error_ = static_cast<int *>(alloc(4));
+  check(cudaMemsetAsync(gemm_error_, 0, 4, stream_), "memset");
   generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
   check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
   check(cudaMallocHost(&token_pinned_, 8), "cudaMallocHost");
@@ -144,7 +148,7 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   for (const TensorEntry &t : manifest.tensors) {
     if (t.dtype == "Q8_0") {
       const size_t n = static_cast<size_t>(t.shape[0]), k = static_cast<size_t>(t.shape[1]);
-      pool_bytes += round_up(n * k, 256) + round_up(n * (k / 32) * 2, 256);
+      pool_bytes += round_up(n * k, 256) + round_up(n * (k / 32) * 2, 256) + round_up(n * (k / 32) * 4, 256);
       staging_bytes = std::max<size_t>(staging_bytes, t.size);
     } else {
       pool_bytes += round_up(t.size, 256);
@@ -173,8 +177,9 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
     w.K = static_cast<int>(cols);
     w.q = reinterpret_cast<int8_t *>(take(static_cast<size_t>(rows) * cols));
     w.d = reinterpret_cast<uint16_t *>(take(static_cast<size_t>(rows) * (cols / 32) * 2));
+    w.d32 = reinterpret_cast<float *>(take(static_cast<size_t>(rows) * (cols / 32) * 4));
     check(cudaMemcpyAsync(staging, base + t->offset, t->size, cudaMemcpyHostToDevice, stream_), "upload weights");
-    launch_repack_p4(staging, rows, cols, w.q, w.d, stream_);
+    launch_repack_p4(staging, rows, cols, w.q, w.d, w.d32, stream_);
     check(cudaGetLastError(), "repack");
     return w;
   };
@@ -318,7 +323,7 @@ struct LinearJob {
 };
 
 static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
-                        cudaStream_t stream, uint64_t *launches, int flags) {
+                        cudaStream_t stream, uint64_t *launches, int flags, int *gemm_error = nullptr) {
   if (S == 1) {
     GemvJobs g{};
     g.count = count;
@@ -338,8 +343,12 @@ static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, 
     return;
   }
   for (int i = 0; i < count; ++i) {
-    cudaError_t e = launch_gemm_q8_dp4a(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d,
-                                        jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, stream);
+    cudaError_t e =
+        gemm_error ? launch_gemm_q8_tc(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d32,
+                                       jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, gemm_error,
+                                       stream)
+                   : launch_gemm_q8_dp4a(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d,
+                                         jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, stream);
     if (e != cudaSuccess)
       throw std::runtime_error(std::string("gemm: ") + cudaGetErrorString(e));
     *launches += 1;
@@ -409,7 +418,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags_);
+      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
       const int C = static_cast<int>(c.qkv_dim());
       check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data),
                                  conv_ + lin_index * (c.conv_kernel - 1) * C, S, C, static_cast<int>(c.conv_kernel),
@@ -423,11 +432,11 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                   static_cast<int>(c.lin_v_dim), c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
       launches_ += 5;
       const LinearJob out = {&L.out_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_);
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags_);
+      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
       check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                              static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
                              kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim, position_dev_, position, S,
@@ -435,18 +444,18 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                              static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, aq_, as_, stream_), "attention");
       launches_ += 3;
       const LinearJob out = {&L.o_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_);
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
       ++full_index;
     }
     check(launch_rms_norm(hidden_[cur], branch_, S, H, L.post_norm.data, L.post_norm.dtype, c.eps, 1, hidden_[cur ^ 1],
                           nullptr, aq_, as_, stream_), "rms_norm");
     cur ^= 1;
     const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags_);
+    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
     check(launch_pointwise(gate_, up_, S * c.intermediate, 1, nullptr, aq_, as_, stream_), "mul");
     launches_ += 2;
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
-    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags_);
+    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
     pending = true;
   }
   // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
@@ -485,7 +494,12 @@ int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position,
   if (logits_host)
     check(cudaMemcpyAsync(logits_pinned_, logits_, static_cast<size_t>(c.vocab) * 4, cudaMemcpyDeviceToHost, stream_), "logits");
   check(cudaMemcpyAsync(token_pinned_, next_token_, 8, cudaMemcpyDeviceToHost, stream_), "argmax");
+  check(cudaMemcpyAsync(position_pinned_, gemm_error_, 4, cudaMemcpyDeviceToHost, stream_), "gemm status");
   check(cudaStreamSynchronize(stream_), "forward");
+  if (*reinterpret_cast<int *>(position_pinned_) != 0) {
+    cudaMemsetAsync(gemm_error_, 0, 4, stream_);
+    throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
+  }
   if (logits_host)
     std::memcpy(logits_host, logits_pinned_, static_cast<size_t>(c.vocab) * 4);
   return *token_pinned_;

@@ -16,7 +16,8 @@ namespace llmcp_b200 {
 
 struct Q8Weight {
   int8_t *q = nullptr;   // [N][K]
-  uint16_t *d = nullptr; // [N][K/32]
+  uint16_t *d = nullptr; // [N][K/32] f16 bits
+  float *d32 = nullptr;  // [N][K/32] the same scales as f32 (tensor-core GEMM)
   int N = 0, K = 0;
 };
 
@@ -136,6 +137,8 @@ private:
   cudaGraphExec_t decode_graph_ = nullptr;
   uint64_t decode_graph_launches_ = 0;
   bool use_graph_ = true;
+  bool use_tensor_cores_ = true;
+  int *gemm_error_ = nullptr; // device flag raised by a timed-out wait in the GEMM
   int gemv_flags_ = 3; // kGemvOverlapPrevious | kGemvPrefetchL2
 };
 

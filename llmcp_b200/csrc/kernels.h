@@ -36,7 +36,9 @@ struct GemvJobs {
   int flags;
 };
 
-void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint16_t *d, cudaStream_t stream);
+// d32 (optional): the same scales widened to f32, [N][K/32], for the tensor-core GEMM.
+void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint16_t *d, float *d32,
+                      cudaStream_t stream);
 void launch_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *s, cudaStream_t stream);
 cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
                            cudaStream_t stream, int rows_per_warp = 0);
@@ -47,6 +49,12 @@ cudaError_t launch_gemv_q8_rows(const int8_t *aq, const float *as, int K, const 
 cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K, const int8_t *wq,
                                 const uint16_t *wd, int N, void *y, int y_dtype, int activation,
                                 int32_t *dots_out, cudaStream_t stream);
+// Tensor-core GEMM (tcgen05, sm_100a).  ws: f32 weight scales [N][K/32].  error_flag (device int,
+// optional) is set to 1 if a bounded wait inside the kernel ran out.
+size_t gemm_q8_tc_smem_bytes();
+cudaError_t launch_gemm_q8_tc(const int8_t *aq, const float *as, int M, int K, const int8_t *wq, const float *ws, int N,
+                              void *y, int y_dtype, int activation, int32_t *dots_out, int *error_flag,
+                              cudaStream_t stream);
 void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, const int8_t *wq, const uint16_t *wd,
                          uint16_t *out, cudaStream_t stream);
 // scratch_v / scratch_i: kArgmaxParts entries each.

@@ -17,7 +17,7 @@ namespace llmcp_b200 {
 // Weight re-layout (one-time, at load)
 // ---------------------------------------------------------------------------------
 __global__ void repack_p4_kernel(const uint8_t *__restrict__ src, int64_t N, int64_t K,
-                                 int8_t *__restrict__ q, uint16_t *__restrict__ d) {
+                                 int8_t *__restrict__ q, uint16_t *__restrict__ d, float *__restrict__ d32) {
   const int64_t nb = K / kBlock;
   const int64_t words = N * (K / 4);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -28,16 +28,20 @@ __global__ void repack_p4_kernel(const uint8_t *__restrict__ src, int64_t N, int
     const uint8_t *rec = src + ((row / 4) * nb + b) * kRecordBytes;
     const uint32_t v = *reinterpret_cast<const uint32_t *>(rec + 8 + c * 16 + (row % 4) * 4);
     reinterpret_cast<uint32_t *>(q)[i] = v;
-    if (c == 0)
-      d[row * nb + b] = *reinterpret_cast<const uint16_t *>(rec + (row % 4) * 2);
+    if (c == 0) {
+      const uint16_t bits = *reinterpret_cast<const uint16_t *>(rec + (row % 4) * 2);
+      d[row * nb + b] = bits;
+      if (d32)
+        d32[row * nb + b] = f16_bits_to_f32(bits);
+    }
   }
 }
 
-void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint16_t *d,
+void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint16_t *d, float *d32,
                       cudaStream_t stream) {
   const int64_t words = N * (K / 4);
   const int blocks = static_cast<int>(std::min<int64_t>((words + 255) / 256, 148 * 16));
-  repack_p4_kernel<<<blocks, 256, 0, stream>>>(src, N, K, q, d);
+  repack_p4_kernel<<<blocks, 256, 0, stream>>>(src, N, K, q, d, d32);
 }
 
 // ---------------------------------------------------------------------------------

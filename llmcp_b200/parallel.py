@@ -1,0 +1,117 @@
+"""Multi-GPU pieces of the path: one process per GPU over ``torch.distributed``.
+
+The reference is single-process; what shards naturally here is (a) independent sequences
+(replicas, no collective on the data path) and (b) the 248320-row tied lm_head, whose rows
+split across ranks with one tiny exchange step: a (max, index) reduction that reproduces the
+host argmax of tools/llmcp-benchmark/llmcp-benchmark.cpp:51-54 (the first maximum wins).
+
+``reduce_argmax`` and ``vocab_shard`` are backend-agnostic (gloo on CPU in the tests, NCCL on
+GPUs); ``ShardedLmHead`` runs the shard's GEMV and argmax with the CUDA library.
+"""
+import ctypes as C
+
+import numpy as np
+
+
+def vocab_shard(vocab, world, rank):
+    """Rows [begin, end) of rank ``rank``: equal shards whose size is a multiple of 8 (the packed
+    layout groups rows in eights, include/llmcp/Support/Q8PackedLayout.h:38-42)."""
+    if vocab % (8 * world) != 0:
+        raise ValueError(f"vocabulary {vocab} does not split into {world} shards of whole 8-row groups")
+    rows = vocab // world
+    return rank * rows, (rank + 1) * rows
+
+
+def shard_packed_rows(packed, vocab, hidden, begin, end):
+    """Byte range of rows [begin, end) inside a packed q8_0_p4 table (group-major layout)."""
+    if begin % 4 or end % 4:
+        raise ValueError("shard boundaries must be multiples of 4 rows")
+    record_bytes = (hidden // 32) * 136
+    return packed[(begin // 4) * record_bytes:(end // 4) * record_bytes]
+
+
+def reduce_argmax(local_value, local_index, group=None, device="cpu"):
+    """All ranks contribute their shard's (maximum, global index); every rank gets the global
+    first maximum: the largest value, and among equal values the lowest index."""
+    import torch
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return float(local_value), int(local_index)
+    world = dist.get_world_size(group)
+    # value and index travel as two exact 64-bit words
+    mine = torch.tensor([np.float64(local_value).view(np.int64), int(local_index)], dtype=torch.int64, device=device)
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine, group=group)
+    best_value, best_index = None, None
+    for item in gathered:
+        bits, index = (int(v) for v in item.cpu().tolist())
+        value = float(np.int64(bits).view(np.float64))
+        if best_value is None or value > best_value or (value == best_value and index < best_index):
+            best_value, best_index = value, index
+    return best_value, best_index
+
+
+def max_over_ranks(value, device="cpu", group=None):
+    import torch
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())
+
+
+class ShardedLmHead:
+    """Rows [begin, end) of the tied lm_head on this rank's GPU (LowerToLinalg.cpp:729-765).
+
+    ``packed`` is the full packed table (host numpy uint8) or this rank's slice of it.  ``step``
+    quantises the final hidden row, runs the shard's decode GEMV and argmax on the device and
+    returns the global (value, token) after the cross-rank reduction.
+    """
+
+    def __init__(self, packed_shard, rows, hidden, row_begin, device_index):
+        import torch
+        import llmcp_b200 as L
+        self.torch, self.L, self.lib = torch, L, L.lib()
+        self.rows, self.hidden, self.row_begin = rows, hidden, row_begin
+        self.device = torch.device("cuda", device_index)
+        nb = hidden // 32
+        with torch.cuda.device(self.device):
+            records = torch.from_numpy(np.ascontiguousarray(packed_shard)).to(self.device)
+            self.wq = torch.empty((rows, hidden), dtype=torch.int8, device=self.device)
+            self.wd = torch.empty((rows, nb), dtype=torch.float16, device=self.device)
+            self.aq = torch.empty(hidden, dtype=torch.int8, device=self.device)
+            self.scales = torch.empty(nb, dtype=torch.float32, device=self.device)
+            self.logits = torch.empty(rows, dtype=torch.float32, device=self.device)
+            self.part_v = torch.empty(512, dtype=torch.float32, device=self.device)
+            self.part_i = torch.empty(512, dtype=torch.int64, device=self.device)
+            self.best = torch.empty(1, dtype=torch.int64, device=self.device)
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            self._check(self.lib.llmcp_dev_repack_q8(self._p(records), C.c_int64(rows), C.c_int64(hidden),
+                                                     self._p(self.wq), self._p(self.wd), stream))
+            torch.cuda.synchronize()
+
+    @staticmethod
+    def _p(t):
+        return C.c_void_p(t.data_ptr())
+
+    def _check(self, code):
+        if code != 0:
+            raise self.L.LlmcpError(self.L.last_error())
+
+    def step(self, hidden_bf16_bits, group=None):
+        torch = self.torch
+        with torch.cuda.device(self.device):
+            h = torch.from_numpy(np.ascontiguousarray(hidden_bf16_bits, dtype=np.uint16).view(np.int16)).to(self.device)
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            self._check(self.lib.llmcp_dev_act_quant(self._p(h), 1, C.c_int64(1), C.c_int64(self.hidden),
+                                                     self._p(self.aq), self._p(self.scales), stream))
+            self._check(self.lib.llmcp_dev_gemv_q8(self._p(self.aq), self._p(self.scales), C.c_int64(self.hidden),
+                                                   self._p(self.wq), self._p(self.wd), C.c_int64(self.rows),
+                                                   self._p(self.logits), 0, 0, 0, 0, stream))
+            self._check(self.lib.llmcp_dev_argmax(self._p(self.logits), C.c_int64(self.rows), self._p(self.part_v),
+                                                  self._p(self.part_i), self._p(self.best), stream))
+            torch.cuda.synchronize()
+            index = int(self.best.item())
+            value = float(self.logits[index].item())
+        return reduce_argmax(value, self.row_begin + index, group=group, device=self.device)

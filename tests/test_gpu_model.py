@@ -27,6 +27,7 @@ def oracle_dims(d):
 
 
 def run_both(dims, seed, prompt, steps, capacity):
+    L.lib().llmcp_b200_clear_error()  # a message left by an earlier, deliberately failing call
     data = L.synthetic_container(dims, seed)
     arena = L.Arena().from_buffer(data)
     runtime = L.AotRuntime(dims)
