@@ -136,7 +136,7 @@ gdn_recurrence_kernel(const uint16_t *__restrict__ conv, const float *__restrict
   const int64_t channels = 2 * static_cast<int64_t>(nk) * dk + static_cast<int64_t>(nv) * dv;
   const bool active = v < dv;
   float *col = state + static_cast<int64_t>(h) * dk * dv + (active ? v : 0);
-  extern __shared__ float kq_sm[]; // kn[dk], qn[dk] of the current token
+  extern __shared__ __align__(16) float kq_sm[]; // kn[dk], qn[dk] of the current token
   float *k_sm = kq_sm, *q_sm = kq_sm + dk;
 
   float s[DK > 0 ? DK : 1];
@@ -185,9 +185,17 @@ gdn_recurrence_kernel(const uint16_t *__restrict__ conv, const float *__restrict
       fetch(t + 1);
     float kv = 0.0f;
     if (DK > 0) {
+      // s[k] is replaced by its decayed value here; the update below starts from it.
 #pragma unroll
-      for (int k = 0; k < DK; ++k)
-        kv = __fadd_rn(kv, __fmul_rn(__fmul_rn(s[k], dc), k_sm[k]));
+      for (int k4 = 0; k4 < DK; k4 += 4) {
+        const float4 kk = *reinterpret_cast<const float4 *>(k_sm + k4);
+        const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[k4 + u] = __fmul_rn(s[k4 + u], dc);
+          kv = __fadd_rn(kv, __fmul_rn(s[k4 + u], kv4[u]));
+        }
+      }
     } else if (active) {
       for (int k = 0; k < dk; ++k)
         kv = __fadd_rn(kv, __fmul_rn(__fmul_rn(col[static_cast<int64_t>(k) * dv], dc), k_sm[k]));
@@ -196,9 +204,16 @@ gdn_recurrence_kernel(const uint16_t *__restrict__ conv, const float *__restrict
     float o = 0.0f;
     if (DK > 0) {
 #pragma unroll
-      for (int k = 0; k < DK; ++k) {
-        s[k] = __fadd_rn(__fmul_rn(s[k], dc), __fmul_rn(k_sm[k], delta));
-        o = __fadd_rn(o, __fmul_rn(s[k], q_sm[k]));
+      for (int k4 = 0; k4 < DK; k4 += 4) {
+        const float4 kk = *reinterpret_cast<const float4 *>(k_sm + k4);
+        const float4 qq = *reinterpret_cast<const float4 *>(q_sm + k4);
+        const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+        const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[k4 + u] = __fadd_rn(s[k4 + u], __fmul_rn(kv4[u], delta));
+          o = __fadd_rn(o, __fmul_rn(s[k4 + u], qv4[u]));
+        }
       }
     } else if (active) {
       for (int k = 0; k < dk; ++k) {
