@@ -44,6 +44,10 @@ PREFILL = 1024
 M2_DECODE_TOK_S = 11.39  # published Q8_0 decode tok/s on Apple M2, 4 threads (reference README.md:140)
 GEMV_N, GEMV_K, GEMV_RING = 9216, 2560, 12
 GEMV_BYTES = GEMV_N * (GEMV_K // 32) * 34 + GEMV_K * 4 + GEMV_N * 4  # weights + f32 x + f32 y = 25,114,624
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q8_rows_kernel launch of this shape, from the
+# ncu capture summarised in profiles/gemv_q8_rows_9216x2560.md (the 36,864-byte result stays in L2).
+GEMV_DRAM_TRAFFIC = 25_092_864
+GEMM_M, GEMM_N, GEMM_K = 1024, 9216, 2560  # the gate_proj/up_proj prefill GEMM (BASELINE.json configs[1] shape)
 
 
 def measured_peaks():
@@ -142,13 +146,13 @@ def oracle_decode(arena, steps, warmup, prefill=8):
     return steps / seconds, tokens, oracle.num_threads()
 
 
-def gemv_roofline(L, torch, device):
+def gemv_roofline(L, torch, device, ring=GEMV_RING, sweeps=20):
     """Decode GEMV alone: CUDA events on the launching stream over a ring of weight copies."""
     lib = L.lib()
     stream = torch.cuda.current_stream().cuda_stream
     gen = torch.Generator(device="cuda").manual_seed(SEED)
-    wq = torch.randint(-127, 128, (GEMV_RING, GEMV_N, GEMV_K), dtype=torch.int8, device="cuda", generator=gen)
-    wd = (torch.rand((GEMV_RING, GEMV_N, GEMV_K // 32), device="cuda", generator=gen) * 1e-3).to(torch.float16)
+    wq = torch.randint(-127, 128, (ring, GEMV_N, GEMV_K), dtype=torch.int8, device="cuda", generator=gen)
+    wd = (torch.rand((ring, GEMV_N, GEMV_K // 32), device="cuda", generator=gen) * 1e-3).to(torch.float16)
     x = torch.randn((1, GEMV_K), device="cuda", generator=gen)
     aq = torch.empty(GEMV_K, dtype=torch.int8, device="cuda")
     scales = torch.empty(GEMV_K // 32, dtype=torch.float32, device="cuda")
@@ -158,7 +162,7 @@ def gemv_roofline(L, torch, device):
 
     def sweep(times, stream):
         for _ in range(times):
-            for r in range(GEMV_RING):
+            for r in range(ring):
                 rc = lib.llmcp_dev_gemv_q8(ptr(aq), ptr(scales), C.c_int64(GEMV_K), ptr(wq[r]), ptr(wd[r]),
                                            C.c_int64(GEMV_N), ptr(y), 0, 0, 0, 1, C.c_void_p(stream))
                 assert rc == 0, L.last_error()
@@ -173,14 +177,49 @@ def gemv_roofline(L, torch, device):
     graph.replay()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
-    sweeps = 20
     begin.record()
     for _ in range(sweeps):
         graph.replay()
     end.record()
     torch.cuda.synchronize()
-    us = begin.elapsed_time(end) * 1e3 / (sweeps * GEMV_RING)
-    return GEMV_BYTES / us / 1e3, us, sweeps * GEMV_RING  # GB/s, us per launch, launches
+    us = begin.elapsed_time(end) * 1e3 / (sweeps * ring)
+    return GEMV_BYTES / us / 1e3, us, sweeps * ring  # GB/s, us per launch, launches
+
+
+def gemm_alone(L, torch, repeats=5):
+    """Prefill GEMM alone (tcgen05 kernel) on device buffers: returns (us per launch, int8 TOP/s)."""
+    lib = L.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    nb = GEMM_K // 32
+    wq = torch.randint(-127, 128, (GEMM_N, GEMM_K), dtype=torch.int8, device="cuda", generator=gen)
+    wd = (torch.rand((GEMM_N, nb), device="cuda", generator=gen) * 1e-3).to(torch.float16)
+    x = torch.randn((GEMM_M, GEMM_K), device="cuda", generator=gen)
+    aq = torch.empty((GEMM_M, GEMM_K), dtype=torch.int8, device="cuda")
+    scales = torch.empty((GEMM_M, nb), dtype=torch.float32, device="cuda")
+    wd32 = wd.float().contiguous()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = torch.empty((GEMM_M, GEMM_N), dtype=torch.float32, device="cuda")
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    assert lib.llmcp_dev_act_quant(ptr(x), 0, C.c_int64(GEMM_M), C.c_int64(GEMM_K), ptr(aq), ptr(scales), stream) == 0
+
+    def launch():
+        rc = lib.llmcp_dev_gemm_q8_tc(ptr(aq), ptr(scales), C.c_int64(GEMM_M), C.c_int64(GEMM_K), ptr(wq), ptr(wd32),
+                                      C.c_int64(GEMM_N), ptr(y), 0, 0, ptr(status), stream)
+        assert rc == 0, L.last_error()
+
+    for _ in range(3):
+        launch()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    begin.record()
+    for _ in range(repeats):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    us = begin.elapsed_time(end) * 1e3 / repeats
+    assert int(status.item()) == 0, "a bounded wait inside the GEMM ran out"
+    return us, 2.0 * GEMM_M * GEMM_N * GEMM_K / us / 1e6
 
 
 def main():
@@ -190,6 +229,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--cpu-steps", type=int, default=8, help="decode steps of the CPU baseline sample")
+    parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm"],
+                        help="gemv / gemm: run just that kernel on a small case (what the profiler captures)")
     args = parser.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
@@ -229,6 +270,14 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
     L.set_device(local_rank)
+    if args.only == "gemv":
+        gbs, us, count = gemv_roofline(L, torch, local_rank, ring=6, sweeps=2)
+        print(json.dumps({"only": "gemv", "shape": [1, GEMV_N, GEMV_K], "us_per_launch": us, "gbs": gbs, "launches": count}))
+        return
+    if args.only == "gemm":
+        us, tops = gemm_alone(L, torch)
+        print(json.dumps({"only": "gemm", "shape": [GEMM_M, GEMM_N, GEMM_K], "us_per_launch": us, "int8_tops": tops}))
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
@@ -321,7 +370,7 @@ def main():
         peak, peak_kind = measured_peaks()
         gbs, us, gemv_launches = gemv_roofline(L, torch, local_rank)
         result["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                              "traffic": None, "kernel": "gemv_q8_kernel", "shape": [1, GEMV_N, GEMV_K],
+                              "traffic": GEMV_DRAM_TRAFFIC, "kernel": "gemv_q8_rows_kernel", "shape": [1, GEMV_N, GEMV_K],
                               "us_per_launch": us, "launches_timed": gemv_launches, "peak_kind": f"of {peak_kind}",
                               "algorithmic_bytes_per_launch": GEMV_BYTES,
                               "whole_model_effective_gbs": 4.61e9 / (device_ms / steps / 1e3) / 1e9}

@@ -125,7 +125,11 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
  *                         dependent of the kernel in front (weights are requested while that
  *                         kernel still runs; x is read only after it has finished), 2 = also
  *                         prefetch the whole matrix into L2 first.
- *   llmcp_dev_gemm_q8   : M > 1 linear (Q8Matmul.cpp:143-289).
+ *   llmcp_dev_gemm_q8   : M > 1 linear (Q8Matmul.cpp:143-289), integer dot products on dp4a.
+ *   llmcp_dev_gemm_q8_tc: the same contraction on the tcgen05 tensor cores.  wd32 holds the
+ *                         weight scales widened to f32, [N][K/32].  status (device int, may be
+ *                         null) is set to 1 if a bounded wait inside the kernel ran out; the
+ *                         caller reads it after synchronising.
  *   llmcp_dev_argmax    : first maximum of n f32 values; scratch: 512 floats + 512 int64. */
 int llmcp_dev_repack_q8(const uint8_t *records, int64_t N, int64_t K, int8_t *q, uint16_t *d, void *stream);
 int llmcp_dev_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales, void *stream);
@@ -133,6 +137,8 @@ int llmcp_dev_gemv_q8(const int8_t *aq, const float *as, int64_t K, const int8_t
                       void *y, int y_dtype, int activation, int rows_per_warp, int flags, void *stream);
 int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
                       int64_t N, void *y, int y_dtype, int activation, void *stream);
+int llmcp_dev_gemm_q8_tc(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const float *wd32,
+                         int64_t N, void *y, int y_dtype, int activation, int *status, void *stream);
 int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *scratch_indices, int64_t *out_index,
                      void *stream);
 

@@ -633,6 +633,18 @@ int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, c
   });
 }
 
+int llmcp_dev_gemm_q8_tc(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const float *wd32,
+                         int64_t N, void *y, int y_dtype, int activation, int *status, void *stream) {
+  return guarded_async([&] {
+    check_q8_shape(N, K);
+    if (M < 1)
+      throw std::runtime_error("llmcp_dev_gemm_q8_tc needs M >= 1");
+    cuda_check(launch_gemm_q8_tc(aq, as, static_cast<int>(M), static_cast<int>(K), wq, wd32, static_cast<int>(N), y, y_dtype,
+                                 activation, nullptr, status, static_cast<cudaStream_t>(stream)), "gemm");
+    g_launches += 1;
+  });
+}
+
 int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *scratch_indices, int64_t *out_index,
                      void *stream) {
   return guarded_async([&] {
