@@ -67,21 +67,33 @@ class ClockSampler:
 
     def __init__(self, device):
         self.device = device
-        self.lines = []
+        self.lines = []  # (host time, text)
+        self.windows = []  # [begin, end] host times of the timed regions
         self.proc = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def wait_first_sample(self, seconds=5.0):
+        deadline = time.perf_counter() + seconds
+        while self.proc and not self.lines and time.perf_counter() < deadline:
+            time.sleep(0.01)
+
+    def open_window(self):
+        self.windows.append([time.perf_counter(), None])
+
+    def close_window(self):
+        self.windows[-1][1] = time.perf_counter()
 
     def stop(self):
         if self.proc:
@@ -92,7 +104,10 @@ class ClockSampler:
                 self.proc.kill()
         clocks, max_clock, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        inside = lambda t: any(b <= t <= (e if e is not None else t) for b, e in self.windows)
+        for stamp, line in self.lines:
+            if self.windows and not inside(stamp):
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -105,7 +120,8 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+                "reasons": sorted(reasons), "samples": len(clocks),
+                "sampled": "nvidia-smi every 20 ms, samples inside the two timed loops (device arm and ABI arm)"}
 
 
 def container_path(local_rank, world):
@@ -312,12 +328,14 @@ def main():
     prefill_s = time.perf_counter() - t0
     warm_tokens, _ = engine.generate(first, PREFILL, warmup)
     sampler = ClockSampler(local_rank)
+    sampler.start()
+    sampler.wait_first_sample()
     launches_before = L.launch_count()
     barrier()
-    sampler.start()
+    sampler.open_window()
     tokens, device_ms = engine.generate(int(warm_tokens[-1]), PREFILL + warmup, steps)
     barrier()
-    clocks = sampler.stop()
+    sampler.close_window()
     launches = L.launch_count() - launches_before
     device_ms = max_over_ranks(device_ms)
     value = world * steps / (device_ms / 1e3)
@@ -332,6 +350,7 @@ def main():
         logits = runtime.forward(arena, [int(np.argmax(logits))], pos, pos + 1)
         pos += 1
     barrier()
+    sampler.open_window()
     t0 = time.perf_counter()
     e2e_tokens = []
     for _ in range(steps):
@@ -340,6 +359,8 @@ def main():
         pos += 1
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
+    sampler.close_window()
+    clocks = sampler.stop()
     barrier()
     # e2e prefill: a fresh 1024-token call through the same entry point
     t0 = time.perf_counter()

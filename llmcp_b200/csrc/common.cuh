@@ -85,4 +85,50 @@ __device__ inline float apply_activation(float v, int activation) {
 
 __device__ inline int dp4a(int a, int b, int c) { return __dp4a(a, b, c); }
 
+// Quantises 32 consecutive values held one per lane of a full warp (Q8Decode.cpp:83-120).
+__device__ inline void warp_quant_block(float v, int8_t *q, float *s, int64_t element, int64_t block,
+                                        int lane) {
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = __fdiv_rn(amax, 127.0f);
+  const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
+  q[element] = static_cast<int8_t>(__float2int_rn(__fmul_rn(v, inv)));
+  if (lane == 0)
+    s[block] = scale;
+}
+
+// Every kernel of the forward is launched as a programmatic dependent of the kernel in front of
+// it on the stream: its CTAs may be placed once that kernel's CTAs have exited or released their
+// dependents, and this call, the first statement of the kernel, holds them until that kernel
+// has finished and its writes are visible.  release_early lets the kernel behind this one be
+// placed right away; the kernels in front of a GEMV do that, so that the GEMV requests its
+// weights while they run.  The others release at exit, which bounds the look-ahead to one kernel.
+__device__ __forceinline__ void grid_dependency_sync(bool release_early = false) {
+  if (release_early)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// false when LLMCP_B200_PDL=0: kernels are then launched fully serialised.
+bool overlap_launches_enabled();
+
+// Launch with programmatic stream serialisation (see grid_dependency_sync).
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = overlap_launches_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 } // namespace llmcp_b200

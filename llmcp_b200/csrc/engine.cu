@@ -20,6 +20,7 @@ __global__ void advance_kernel(const int64_t *__restrict__ next_token, int64_t *
                                int64_t *__restrict__ position, const float *__restrict__ cos_table,
                                const float *__restrict__ sin_table, float *__restrict__ cos_row,
                                float *__restrict__ sin_row, int rotary, int64_t capacity) {
+  grid_dependency_sync();
   const int64_t p = *position + 1;
   const int i = threadIdx.x;
   if (p < capacity && i < rotary) {
@@ -102,6 +103,8 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     use_graph_ = std::atoi(flag) == 0;
   if (const char *flag = std::getenv("LLMCP_B200_GEMV_FLAGS"))
     gemv_flags_ = std::atoi(flag);
+  if (const char *flag = std::getenv("LLMCP_B200_FUSE_MIXER"))
+    fuse_decode_mixer_ = std::atoi(flag) != 0;
   if (const char *flag = std::getenv("LLMCP_B200_GEMM"))
     use_tensor_cores_ = std::string(flag) != "dp4a";
   gemm_error_ = static_cast<int *>(alloc(4));
@@ -420,17 +423,25 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.b, b_, kBF16, kSigmoid}};
       run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
       const int C = static_cast<int>(c.qkv_dim());
-      check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data),
-                                 conv_ + lin_index * (c.conv_kernel - 1) * C, S, C, static_cast<int>(c.conv_kernel),
-                                 convd_, stream_), "causal_conv1d");
-      check(launch_gated_delta_net(convd_, a_, b_, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype,
-                                   delta_ + lin_index * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim, S,
-                                   static_cast<int>(c.lin_k_heads), static_cast<int>(c.lin_v_heads),
-                                   static_cast<int>(c.lin_k_dim), static_cast<int>(c.lin_v_dim), 1, gdn_scratch_, gdn_,
-                                   stream_), "gated_delta_net");
-      check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(c.value_dim()),
-                                  static_cast<int>(c.lin_v_dim), c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
-      launches_ += 5;
+      uint16_t *conv_state = conv_ + lin_index * (c.conv_kernel - 1) * C;
+      float *delta_state = delta_ + lin_index * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
+      const int nk = static_cast<int>(c.lin_k_heads), nv = static_cast<int>(c.lin_v_heads);
+      const int dk = static_cast<int>(c.lin_k_dim), dv = static_cast<int>(c.lin_v_dim);
+      if (S == 1 && fuse_decode_mixer_ && gdn_decode_supported(static_cast<int>(c.conv_kernel), nk, nv, dk, dv)) {
+        check(launch_gdn_decode(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, static_cast<int>(c.conv_kernel),
+                                a_, b_, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype, delta_state, nk, nv, dk,
+                                dv, 1, z_, L.lin_norm.data, L.lin_norm.dtype, c.eps, 1, gdn_scratch_, convd_, nullptr, aq_,
+                                as_, stream_), "gated_delta_net (decode)");
+        launches_ += 2;
+      } else {
+        check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, S, C,
+                                   static_cast<int>(c.conv_kernel), convd_, stream_), "causal_conv1d");
+        check(launch_gated_delta_net(convd_, a_, b_, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype,
+                                     delta_state, S, nk, nv, dk, dv, 1, gdn_scratch_, gdn_, stream_), "gated_delta_net");
+        check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(c.value_dim()), dv,
+                                    c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
+        launches_ += 5;
+      }
       const LinearJob out = {&L.out_proj, branch_, kBF16, kNone};
       run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
       ++lin_index;
@@ -526,7 +537,7 @@ void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int6
   const int threads = static_cast<int>((c.rotary + 31) / 32 * 32);
   for (int64_t i = 0; i < steps; ++i) {
     decode_step();
-    advance_kernel<<<1, threads, 0, stream_>>>(next_token_, tokens_, generated_, step_dev_, position_dev_, cos_table_,
+    launch_chained(advance_kernel, dim3(1), dim3(threads), 0, stream_, next_token_, tokens_, generated_, step_dev_, position_dev_, cos_table_,
                                                sin_table_, cos_, sin_, static_cast<int>(c.rotary), capacity_);
     launches_ += 1;
   }

@@ -140,6 +140,7 @@ private:
   bool use_tensor_cores_ = true;
   int *gemm_error_ = nullptr; // device flag raised by a timed-out wait in the GEMM
   int gemv_flags_ = 3; // kGemvOverlapPrevious | kGemvPrefetchL2
+  bool fuse_decode_mixer_ = true; // one-token gated-delta-net layers in two launches instead of five
 };
 
 } // namespace llmcp_b200

@@ -183,6 +183,7 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  grid_dependency_sync(); // barriers and tensor memory are set up; the operands belong to the kernel in front
 
   if (tid < kLoaderThreads) {
     // ---- loaders ------------------------------------------------------------------------
@@ -366,7 +367,7 @@ cudaError_t launch_gemm_q8_tc(const int8_t *aq, const float *as, int M, int K, c
     configured = true;
   }
   dim3 grid((N + kTileN - 1) / kTileN, (M + kTileM - 1) / kTileM);
-  gemm_q8_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(aq, as, M, K, wq, ws, N, y, y_dtype, activation, dots_out,
+  launch_chained(gemm_q8_tc_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, aq, as, M, K, wq, ws, N, y, y_dtype, activation, dots_out,
                                                             error_flag);
   return cudaGetLastError();
 }

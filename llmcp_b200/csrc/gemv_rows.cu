@@ -118,7 +118,8 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
       }
     }
   }
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // No early release here: the kernel behind a GEMV is placed when the GEMV's CTAs exit, which
+  // keeps the look-ahead at one kernel (several matrices prefetching at once thrash L2).
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   for (int i = threadIdx.x; i < 2 * NB; i += blockDim.x) {

@@ -77,6 +77,15 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
                                    int a_log_dtype, const void *dt_bias, int dt_dtype, float *state, int64_t S,
                                    int nk, int nv, int dk, int dv, int b_activated, float *scratch,
                                    uint16_t *out, cudaStream_t stream);
+// One token of causal_conv1d + gated_delta_net + gated_rms_norm (+ quantisation) in two launches;
+// the same values as the three general launchers above produce.  scratch: gdn_scratch_floats(1, ..).
+bool gdn_decode_supported(int kernel, int nk, int nv, int dk, int dv);
+cudaError_t launch_gdn_decode(const uint16_t *qkv, const uint16_t *conv_w, uint16_t *conv_state, int kernel,
+                              const uint16_t *a, const uint16_t *b, const void *a_log, int a_log_dtype,
+                              const void *dt_bias, int dt_dtype, float *state, int nk, int nv, int dk, int dv,
+                              int b_activated, const uint16_t *gate, const void *norm_w, int norm_w_dtype, float eps,
+                              int gate_activated, float *scratch, uint16_t *conv_out, uint16_t *y, int8_t *q_out,
+                              float *s_out, cudaStream_t stream);
 // The start position is read from device memory (position_dev) so that a captured launch can be
 // replayed at another position; max_position bounds it (grid and scratch are sized for it).
 // rows_from_position: cos/sin are tables indexed by absolute position instead of the call's rows.

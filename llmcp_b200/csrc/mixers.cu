@@ -14,6 +14,7 @@ namespace llmcp_b200 {
 __global__ void causal_conv1d_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
                                      const uint16_t *__restrict__ state, int64_t S, int C, int kernel,
                                      uint16_t *__restrict__ y) {
+  grid_dependency_sync();
   const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (i >= S * C)
     return;
@@ -33,6 +34,7 @@ __global__ void causal_conv1d_kernel(const uint16_t *__restrict__ x, const uint1
 // ascending order, which is the order the in-place update needs.
 __global__ void conv_state_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ state, int64_t S,
                                   int C, int kernel) {
+  grid_dependency_sync();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C)
     return;
@@ -48,8 +50,8 @@ cudaError_t launch_causal_conv1d(const uint16_t *x, const uint16_t *w, uint16_t 
   if (S == 0)
     return cudaSuccess;
   const int64_t total = S * C;
-  causal_conv1d_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(x, w, state, S, C, kernel, y);
-  conv_state_kernel<<<(C + 255) / 256, 256, 0, stream>>>(x, state, S, C, kernel);
+  launch_chained(causal_conv1d_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, x, w, state, S, C, kernel, y);
+  launch_chained(conv_state_kernel, dim3((C + 255) / 256), dim3(256), 0, stream, x, state, S, C, kernel);
   return cudaGetLastError();
 }
 
@@ -70,6 +72,7 @@ gdn_prepare_kernel(const uint16_t *__restrict__ conv, const uint16_t *__restrict
                    int b_activated, float *__restrict__ qn, float *__restrict__ kn, float *__restrict__ beta,
                    float *__restrict__ decay) {
   extern __shared__ float prep_all[]; // per warp: q squares [dk], k squares [dk]
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int warp_in_cta = threadIdx.x >> 5;
   const int64_t warp = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + warp_in_cta;
@@ -129,6 +132,7 @@ gdn_recurrence_kernel(const uint16_t *__restrict__ conv, const float *__restrict
                       const float *__restrict__ kn, const float *__restrict__ beta,
                       const float *__restrict__ decay, float *__restrict__ state, int64_t S, int nk,
                       int nv, int dk_rt, int dv, uint16_t *__restrict__ out) {
+  grid_dependency_sync();
   const int dk = DK > 0 ? DK : dk_rt;
   const int h = blockIdx.x;
   const int v = blockIdx.y * 32 + threadIdx.x;
@@ -249,14 +253,223 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
   float *beta = kn + S * nk * dk;
   float *decay = beta + S * nv;
   const int64_t warps = S * nk + (S * nv + 31) / 32;
-  gdn_prepare_kernel<<<static_cast<unsigned>((warps + 3) / 4), 128, 4 * 2 * dk * sizeof(float), stream>>>(
+  launch_chained(gdn_prepare_kernel, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 4 * 2 * dk * sizeof(float), stream, 
       conv, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, S, nk, nv, dk, dv, b_activated, qn, kn, beta, decay);
   dim3 grid(nv, (dv + 31) / 32);
   const size_t smem = 2 * static_cast<size_t>(dk) * sizeof(float);
   if (dk == 128)
-    gdn_recurrence_kernel<128><<<grid, 32, smem, stream>>>(conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
+    launch_chained(gdn_recurrence_kernel<128>, dim3(grid), dim3(32), smem, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
   else
-    gdn_recurrence_kernel<0><<<grid, 32, smem, stream>>>(conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
+    launch_chained(gdn_recurrence_kernel<0>, dim3(grid), dim3(32), smem, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------
+// One-token (decode) form of causal_conv1d + gated_delta_net + gated_rms_norm in two kernels.
+// The arithmetic of every value is that of the general kernels above; only the grouping into
+// launches differs, so that five dependent launches per layer become two.
+// ---------------------------------------------------------------------------------
+constexpr int kMaxConvKernel = 8;
+
+// Convolution of one channel for the single new row, SiLU, bf16 rounding; the channel's state is
+// shifted in place by the same thread (no other thread reads it).
+__device__ __forceinline__ float conv_step(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w,
+                                           uint16_t *__restrict__ state, int C, int kernel, int c) {
+  const int state_len = kernel - 1;
+  uint16_t taps[kMaxConvKernel];
+#pragma unroll
+  for (int k = 0; k < kMaxConvKernel; ++k)
+    if (k < kernel)
+      taps[k] = k < state_len ? state[static_cast<int64_t>(k) * C + c] : x[c];
+  float acc = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kMaxConvKernel; ++k)
+    if (k < kernel)
+      acc = __fadd_rn(acc, __fmul_rn(bf16_to_f32(taps[k]), bf16_to_f32(w[c * kernel + k])));
+#pragma unroll
+  for (int k = 0; k + 1 < kMaxConvKernel; ++k)
+    if (k < state_len)
+      state[static_cast<int64_t>(k) * C + c] = taps[k + 1];
+  return bf16_to_f32(f32_to_bf16(__fmul_rn(acc, d_sigmoid(acc))));
+}
+
+// Warp roles: [0, nk) q heads, [nk, 2 nk) k heads (convolution, then the L2 norm with lane 0
+// adding the squares in order), then one warp per 128 value channels (convolution only), then
+// warps that compute beta and decay, one value head per lane.
+__global__ void __launch_bounds__(128)
+gdn_decode_front_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w, uint16_t *__restrict__ state,
+                        int kernel, const uint16_t *__restrict__ a, const uint16_t *__restrict__ b,
+                        const void *__restrict__ a_log, int a_log_dtype, const void *__restrict__ dt_bias,
+                        int dt_dtype, int nk, int nv, int dk, int dv, int b_activated, float *__restrict__ qn,
+                        float *__restrict__ kn, float *__restrict__ beta, float *__restrict__ decay,
+                        uint16_t *__restrict__ conv_out) {
+  extern __shared__ float front_sm[]; // per warp: dk squares
+  grid_dependency_sync();
+  const int lane = threadIdx.x & 31;
+  const int warp_in_cta = threadIdx.x >> 5;
+  const int warp = blockIdx.x * (blockDim.x >> 5) + warp_in_cta;
+  const int C = 2 * nk * dk + nv * dv;
+  const int value_warps = (nv * dv + 127) / 128;
+  if (warp < 2 * nk) {
+    const bool is_q = warp < nk;
+    const int head = is_q ? warp : warp - nk;
+    const int base = (is_q ? 0 : nk * dk) + head * dk;
+    float *sq = front_sm + warp_in_cta * dk;
+    float v[8]; // dk <= 256
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int d = lane + 32 * u;
+      if (d < dk) {
+        v[u] = conv_step(x, w, state, C, kernel, base + d);
+        sq[d] = __fmul_rn(v[u], v[u]);
+      }
+    }
+    __syncwarp();
+    float scale = 0.0f;
+    if (lane == 0) {
+      float sum = 0.0f;
+#pragma unroll 16
+      for (int d = 0; d < dk; ++d)
+        sum = __fadd_rn(sum, sq[d]);
+      scale = d_rsqrt(__fadd_rn(sum, 1.0e-6f));
+      if (is_q)
+        scale = __fmul_rn(scale, static_cast<float>(1.0 / sqrt(static_cast<double>(dk))));
+    }
+    scale = __shfl_sync(0xffffffffu, scale, 0);
+    float *dst = (is_q ? qn : kn) + head * dk;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int d = lane + 32 * u;
+      if (d < dk)
+        dst[d] = __fmul_rn(v[u], scale);
+    }
+  } else if (warp < 2 * nk + value_warps) {
+    const int first = 2 * nk * dk + (warp - 2 * nk) * 128;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = first + lane + 32 * u;
+      if (c < C)
+        conv_out[c] = f32_to_bf16(conv_step(x, w, state, C, kernel, c));
+    }
+  } else {
+    const int h = (warp - 2 * nk - value_warps) * 32 + lane;
+    if (h < nv) {
+      const float bv = bf16_to_f32(b[h]);
+      beta[h] = b_activated ? bv : d_sigmoid(bv);
+      // dt_bias is widened from bf16, A_log is read as f32 (LowerGatedDeltaNet.cpp:233-246).
+      const float dt = bf16_to_f32(f32_to_bf16(load_as_f32(dt_bias, dt_dtype, h)));
+      const float a_plus_dt = __fadd_rn(bf16_to_f32(a[h]), dt);
+      const float softplus = d_log(__fadd_rn(1.0f, d_exp(a_plus_dt)));
+      const float g = __fmul_rn(-d_exp(load_as_f32(a_log, a_log_dtype, h)), softplus);
+      decay[h] = d_exp(g);
+    }
+  }
+}
+
+// One CTA per value head, one thread per state column: the recurrence step of the token, then
+// the head's gated RMSNorm (thread 0 adds the dv squares in order) and the int8 quantisation of
+// the result for the output projection.  gate holds silu(z) when gate_activated.
+template <int DK>
+__global__ void __launch_bounds__(256)
+gdn_decode_step_kernel(const uint16_t *__restrict__ conv, const float *__restrict__ qn, const float *__restrict__ kn,
+                       const float *__restrict__ beta, const float *__restrict__ decay, float *__restrict__ state,
+                       int nk, int nv, int dv, const uint16_t *__restrict__ gate, const void *__restrict__ norm_w,
+                       int norm_w_dtype, float eps, int gate_activated, uint16_t *__restrict__ y,
+                       int8_t *__restrict__ q_out, float *__restrict__ s_out) {
+  extern __shared__ __align__(16) float step_sm[]; // kn[DK], qn[DK], squares[dv]
+  __shared__ float rstd_sm;
+  grid_dependency_sync(true);
+  float *k_sm = step_sm, *q_sm = step_sm + DK, *sq_sm = step_sm + 2 * DK;
+  const int h = blockIdx.x, v = threadIdx.x;
+  const int kh = h / (nv / nk);
+  float *col = state + static_cast<int64_t>(h) * DK * dv + v;
+  float s[DK];
+#pragma unroll
+  for (int k = 0; k < DK; ++k)
+    s[k] = col[static_cast<int64_t>(k) * dv];
+  for (int d = v; d < DK; d += dv) {
+    k_sm[d] = kn[kh * DK + d];
+    q_sm[d] = qn[kh * DK + d];
+  }
+  const float dc = decay[h], bt = beta[h];
+  const float value = bf16_to_f32(conv[2 * nk * DK + h * dv + v]);
+  __syncthreads();
+  float kv = 0.0f;
+#pragma unroll
+  for (int k4 = 0; k4 < DK; k4 += 4) {
+    const float4 kk = *reinterpret_cast<const float4 *>(k_sm + k4);
+    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s[k4 + u] = __fmul_rn(s[k4 + u], dc);
+      kv = __fadd_rn(kv, __fmul_rn(s[k4 + u], kv4[u]));
+    }
+  }
+  const float delta = __fmul_rn(__fsub_rn(value, kv), bt);
+  float o = 0.0f;
+#pragma unroll
+  for (int k4 = 0; k4 < DK; k4 += 4) {
+    const float4 kk = *reinterpret_cast<const float4 *>(k_sm + k4);
+    const float4 qq = *reinterpret_cast<const float4 *>(q_sm + k4);
+    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+    const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s[k4 + u] = __fadd_rn(s[k4 + u], __fmul_rn(kv4[u], delta));
+      o = __fadd_rn(o, __fmul_rn(s[k4 + u], qv4[u]));
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < DK; ++k)
+    col[static_cast<int64_t>(k) * dv] = s[k];
+  // gated RMSNorm over the head (LowerToLinalg.cpp:655-718, DecodeNormalization.cpp:118-131)
+  const float xo = bf16_to_f32(f32_to_bf16(o));
+  sq_sm[v] = __fmul_rn(xo, xo);
+  __syncthreads();
+  if (v == 0) {
+    float sum = 0.0f;
+#pragma unroll 16
+    for (int d = 0; d < dv; ++d)
+      sum = __fadd_rn(sum, sq_sm[d]);
+    rstd_sm = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(dv)), eps));
+  }
+  __syncthreads();
+  const int64_t element = static_cast<int64_t>(h) * dv + v;
+  const float gv = bf16_to_f32(gate[element]);
+  const float silu = gate_activated ? gv : __fmul_rn(gv, d_sigmoid(gv));
+  float t = __fmul_rn(xo, silu);
+  t = __fmul_rn(t, load_as_f32(norm_w, norm_w_dtype, v));
+  t = __fmul_rn(t, rstd_sm);
+  const uint16_t r = f32_to_bf16(t);
+  if (y)
+    y[element] = r;
+  if (q_out)
+    warp_quant_block(bf16_to_f32(r), q_out, s_out, element, element / kBlock, v & 31);
+}
+
+bool gdn_decode_supported(int kernel, int nk, int nv, int dk, int dv) {
+  return kernel >= 1 && kernel <= kMaxConvKernel && dk == 128 && dv % 32 == 0 && dv >= 32 && dv <= 256 && nk > 0 &&
+         nv % nk == 0;
+}
+
+cudaError_t launch_gdn_decode(const uint16_t *qkv, const uint16_t *conv_w, uint16_t *conv_state, int kernel,
+                              const uint16_t *a, const uint16_t *b, const void *a_log, int a_log_dtype,
+                              const void *dt_bias, int dt_dtype, float *state, int nk, int nv, int dk, int dv,
+                              int b_activated, const uint16_t *gate, const void *norm_w, int norm_w_dtype, float eps,
+                              int gate_activated, float *scratch, uint16_t *conv_out, uint16_t *y, int8_t *q_out,
+                              float *s_out, cudaStream_t stream) {
+  if (!gdn_decode_supported(kernel, nk, nv, dk, dv))
+    return cudaErrorInvalidValue;
+  float *qn = scratch;
+  float *kn = qn + nk * dk;
+  float *beta = kn + nk * dk;
+  float *decay = beta + nv;
+  const int warps = 2 * nk + (nv * dv + 127) / 128 + (nv + 31) / 32;
+  launch_chained(gdn_decode_front_kernel, dim3((warps + 3) / 4), dim3(128), 4 * dk * sizeof(float), stream, qkv, conv_w,
+                 conv_state, kernel, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, nk, nv, dk, dv, b_activated, qn, kn, beta,
+                 decay, conv_out);
+  launch_chained(gdn_decode_step_kernel<128>, dim3(nv), dim3(dv), (2 * 128 + dv) * sizeof(float), stream, conv_out, qn, kn,
+                 beta, decay, state, nk, nv, dv, gate, norm_w, norm_w_dtype, eps, gate_activated, y, q_out, s_out);
   return cudaGetLastError();
 }
 
@@ -276,6 +489,7 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
                                     const int64_t *__restrict__ position_ptr, int rows_from_position, int64_t S,
                                     int nh, int nkv, int hd, int rot, int64_t cap, uint16_t *__restrict__ qn) {
   extern __shared__ float prep_sm[]; // per warp: hd values
+  grid_dependency_sync();
   const int64_t position = *position_ptr;
   // cos/sin hold either the rows of this call (row t) or a table over all positions.
   const int64_t row_base = rows_from_position ? position : 0;
@@ -342,6 +556,7 @@ __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16
                                    const int64_t *__restrict__ position_ptr, int nh, int nkv, int hd, int64_t cap,
                                    int64_t score_stride, float *__restrict__ scores) {
   extern __shared__ __align__(16) unsigned char att_sm[];
+  grid_dependency_sync();
   const int64_t position = *position_ptr;
   const int group = nh / nkv;
   const int64_t t = blockIdx.z;
@@ -400,7 +615,7 @@ __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint
                                     uint16_t *__restrict__ out, int8_t *__restrict__ q_out,
                                     float *__restrict__ s_out) {
   extern __shared__ __align__(16) float comb_sm[];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  grid_dependency_sync(true);
   const int64_t position = *position_ptr;
   const int h = blockIdx.x;
   const int64_t t = blockIdx.y;
@@ -571,7 +786,7 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   const int64_t score_stride = max_position + S;
 
   const int64_t items = S * (nh + nkv);
-  attn_prepare_kernel<<<static_cast<unsigned>((items + 3) / 4), 128, 4 * hd * sizeof(float), stream>>>(
+  launch_chained(attn_prepare_kernel, dim3(static_cast<unsigned>((items + 3) / 4)), dim3(128), 4 * hd * sizeof(float), stream, 
       qg, k, v, q_norm, k_norm, cos, sin, cache, position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn);
 
   const size_t smem = (static_cast<size_t>(kKeyTile) * (hd + 1) + static_cast<size_t>(group) * hd) * sizeof(float);
@@ -588,10 +803,10 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   if (smem > 200 * 1024 || csmem > 200 * 1024)
     return cudaErrorInvalidValue; // about 50,000 cached positions
   dim3 sgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
-  attn_scores_kernel<<<sgrid, group * kKeyTile, smem, stream>>>(qn, cache, position_dev, nh, nkv, hd, cap,
+  launch_chained(attn_scores_kernel, dim3(sgrid), dim3(group * kKeyTile), smem, stream, qn, cache, position_dev, nh, nkv, hd, cap,
                                                                score_stride, scores);
   dim3 cgrid(nh, static_cast<unsigned>(S));
-  attn_combine_kernel<<<cgrid, (hd + 31) / 32 * 32, csmem, stream>>>(scores, cache, qg, position_dev, nh, nkv, hd,
+  launch_chained(attn_combine_kernel, dim3(cgrid), dim3((hd + 31) / 32 * 32), csmem, stream, scores, cache, qg, position_dev, nh, nkv, hd,
                                                                     cap, score_stride, out, q_out, s_out);
   return cudaGetLastError();
 }

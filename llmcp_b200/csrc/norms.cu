@@ -10,20 +10,6 @@
 
 namespace llmcp_b200 {
 
-// Quantises 32 consecutive values held one per lane of a full warp (Q8Decode.cpp:83-120).
-__device__ inline void warp_quant_block(float v, int8_t *q, float *s, int64_t element, int64_t block,
-                                        int lane) {
-  float amax = fabsf(v);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float scale = __fdiv_rn(amax, 127.0f);
-  const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
-  q[element] = static_cast<int8_t>(__float2int_rn(__fmul_rn(v, inv)));
-  if (lane == 0)
-    s[block] = scale;
-}
-
 // One CTA per row.  x = bf(a + b) when b is given (the residual add of the layer,
 // LowerToLinalg.cpp:359-374), else x = a.  Outputs (each optional): sum_out = x,
 // y = bf((x * rstd) * (w [+ 1])), and the block quantisation of y.
@@ -33,6 +19,7 @@ rms_norm_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, 
                 uint16_t *__restrict__ sum_out, uint16_t *__restrict__ y, int8_t *__restrict__ q,
                 float *__restrict__ s) {
   extern __shared__ float row_sm[]; // x values, then their squares
+  grid_dependency_sync();
   float *sq_sm = row_sm + H;
   __shared__ float rstd_sm;
   const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
@@ -102,9 +89,7 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
                      float *__restrict__ s) {
   extern __shared__ __align__(16) float vrow_sm[]; // squares
   __shared__ float rstd_sm;
-  // Lets a following kernel that was launched as a programmatic dependent start its own
-  // input-independent prologue now; it still waits for this kernel to finish before reading.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  grid_dependency_sync(true);
   const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
   const int quads = H >> 2;
   const int per_thread = (quads + blockDim.x - 1) / blockDim.x; // 1 for H <= 4096
@@ -137,6 +122,7 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
   }
   __syncthreads();
   if (threadIdx.x == 0) {
+    // One dependent chain of H adds (the reference's order); 32 squares are fetched, then added.
     float sum = 0.0f;
     for (int d = 0; d < H; d += 32) {
       float4 t[8];
@@ -204,11 +190,11 @@ cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int
     return cudaErrorInvalidValue;
   if (H % kBlock == 0 && H <= 16384) {
     const int threads = std::min(1024, (H / 4 + 31) / 32 * 32);
-    rms_norm_vec4_kernel<<<static_cast<unsigned>(M), threads, H * sizeof(float), stream>>>(
+    launch_chained(rms_norm_vec4_kernel, dim3(static_cast<unsigned>(M)), dim3(threads), H * sizeof(float), stream, 
         a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s);
     return cudaGetLastError();
   }
-  rms_norm_kernel<<<static_cast<unsigned>(M), 256, 2 * H * sizeof(float), stream>>>(
+  launch_chained(rms_norm_kernel, dim3(static_cast<unsigned>(M)), dim3(256), 2 * H * sizeof(float), stream, 
       a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s);
   return cudaGetLastError();
 }
@@ -221,7 +207,7 @@ gated_rms_norm_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict
                       float eps, int gate_activated, uint16_t *__restrict__ y, int8_t *__restrict__ q,
                       float *__restrict__ s) {
   extern __shared__ float sq_all[];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  grid_dependency_sync(true);
   const int lane = threadIdx.x & 31;
   const int warp_in_cta = threadIdx.x >> 5;
   const int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + warp_in_cta;
@@ -271,7 +257,7 @@ cudaError_t launch_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const
     return cudaErrorInvalidValue;
   const int64_t groups_total = M * (H / group);
   const unsigned ctas = static_cast<unsigned>((groups_total + 3) / 4);
-  gated_rms_norm_kernel<<<ctas, 128, 4 * group * sizeof(float), stream>>>(
+  launch_chained(gated_rms_norm_kernel, dim3(ctas), dim3(128), 4 * group * sizeof(float), stream, 
       x, gate, w, w_dtype, groups_total, group, eps, gate_activated, y, q, s);
   return cudaGetLastError();
 }
@@ -281,7 +267,7 @@ cudaError_t launch_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const
 __global__ void pointwise_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b,
                                  int64_t count, int op, uint16_t *__restrict__ y, int8_t *__restrict__ q,
                                  float *__restrict__ s) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  grid_dependency_sync(true);
   const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   float out = 0.0f;
   if (i < count) {
@@ -308,7 +294,7 @@ cudaError_t launch_pointwise(const uint16_t *a, const uint16_t *b, int64_t count
     return cudaSuccess;
   if (q && count % kBlock != 0)
     return cudaErrorInvalidValue;
-  pointwise_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(a, b, count, op, y, q, s);
+  launch_chained(pointwise_kernel, dim3(static_cast<unsigned>((count + 255) / 256)), dim3(256), 0, stream, a, b, count, op, y, q, s);
   return cudaGetLastError();
 }
 

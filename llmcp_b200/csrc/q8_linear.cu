@@ -9,15 +9,26 @@
 // GPU a row-major plane gives 16-byte coalesced loads and is what TMA tiles for the
 // tensor-core path.
 
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace llmcp_b200 {
+
+bool overlap_launches_enabled() {
+  static const bool enabled = [] {
+    const char *flag = std::getenv("LLMCP_B200_PDL");
+    return !(flag && flag[0] == '0');
+  }();
+  return enabled;
+}
 
 // ---------------------------------------------------------------------------------
 // Weight re-layout (one-time, at load)
 // ---------------------------------------------------------------------------------
 __global__ void repack_p4_kernel(const uint8_t *__restrict__ src, int64_t N, int64_t K,
                                  int8_t *__restrict__ q, uint16_t *__restrict__ d, float *__restrict__ d32) {
+  grid_dependency_sync();
   const int64_t nb = K / kBlock;
   const int64_t words = N * (K / 4);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -41,7 +52,7 @@ void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint1
                       cudaStream_t stream) {
   const int64_t words = N * (K / 4);
   const int blocks = static_cast<int>(std::min<int64_t>((words + 255) / 256, 148 * 16));
-  repack_p4_kernel<<<blocks, 256, 0, stream>>>(src, N, K, q, d, d32);
+  launch_chained(repack_p4_kernel, dim3(blocks), dim3(256), 0, stream, src, N, K, q, d, d32);
 }
 
 // ---------------------------------------------------------------------------------
@@ -50,6 +61,7 @@ void launch_repack_p4(const uint8_t *src, int64_t N, int64_t K, int8_t *q, uint1
 // ---------------------------------------------------------------------------------
 __global__ void act_quant_kernel(const void *__restrict__ x, int x_dtype, int64_t blocks_total,
                                  int8_t *__restrict__ q, float *__restrict__ s) {
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
   if (warp >= blocks_total)
@@ -73,7 +85,7 @@ void launch_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *
   if (blocks_total == 0)
     return;
   const int64_t ctas = (blocks_total + 7) / 8;
-  act_quant_kernel<<<static_cast<unsigned>(ctas), 256, 0, stream>>>(x, x_dtype, blocks_total, q, s);
+  launch_chained(act_quant_kernel, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, x, x_dtype, blocks_total, q, s);
 }
 
 // ---------------------------------------------------------------------------------
@@ -102,6 +114,7 @@ __global__ void __launch_bounds__(256)
 gemv_q8_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, int K,
                const GemvJobs jobs, int32_t *__restrict__ dots_out) {
   extern __shared__ __align__(16) unsigned char smem[];
+  grid_dependency_sync();
   const int nb = K / kBlock;
   int8_t *a_sm = reinterpret_cast<int8_t *>(smem);
   float *as_sm = reinterpret_cast<float *>(smem + K);
@@ -207,7 +220,7 @@ static cudaError_t gemv_launch(const int8_t *aq, const float *as, int K, GemvJob
   }
   if (smem > 200 * 1024)
     return cudaErrorInvalidValue;
-  gemv_q8_kernel<RW><<<ctas, kWarps * 32, smem, stream>>>(aq, as, K, jobs, dots_out);
+  launch_chained(gemv_q8_kernel<RW>, dim3(ctas), dim3(kWarps * 32), smem, stream, aq, as, K, jobs, dots_out);
   return cudaGetLastError();
 }
 
@@ -260,6 +273,7 @@ gemm_q8_dp4a_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
   __shared__ __align__(16) uint32_t w_sm[kTile][9];
   __shared__ float as_sm[kTile];
   __shared__ float wd_sm[kTile];
+  grid_dependency_sync();
   const int nb = K / kBlock;
   const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4; // tx -> columns, ty -> rows
@@ -340,7 +354,7 @@ cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K,
                                 const uint16_t *wd, int N, void *y, int y_dtype, int activation,
                                 int32_t *dots_out, cudaStream_t stream) {
   dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile);
-  gemm_q8_dp4a_kernel<<<grid, 256, 0, stream>>>(aq, as, M, K, wq, wd, N, y, y_dtype, activation, dots_out);
+  launch_chained(gemm_q8_dp4a_kernel, dim3(grid), dim3(256), 0, stream, aq, as, M, K, wq, wd, N, y, y_dtype, activation, dots_out);
   return cudaGetLastError();
 }
 
@@ -350,6 +364,7 @@ cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K,
 __global__ void embedding_q8_kernel(const int64_t *__restrict__ tokens, int64_t S, int64_t hidden,
                                     const int8_t *__restrict__ wq, const uint16_t *__restrict__ wd,
                                     uint16_t *__restrict__ out) {
+  grid_dependency_sync();
   const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (i >= S * hidden)
     return;
@@ -362,7 +377,7 @@ __global__ void embedding_q8_kernel(const int64_t *__restrict__ tokens, int64_t 
 void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, const int8_t *wq,
                          const uint16_t *wd, uint16_t *out, cudaStream_t stream) {
   const int64_t total = S * hidden;
-  embedding_q8_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(tokens, S, hidden, wq, wd, out);
+  launch_chained(embedding_q8_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, tokens, S, hidden, wq, wd, out);
 }
 
 // ---------------------------------------------------------------------------------
@@ -379,6 +394,7 @@ __global__ void argmax_partial_kernel(const float *__restrict__ x, int64_t n, fl
                                       int64_t *__restrict__ pi) {
   __shared__ float sv[32];
   __shared__ int64_t si[32];
+  grid_dependency_sync();
   float bv = -INFINITY;
   int64_t bi = INT64_MAX;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -413,6 +429,7 @@ __global__ void argmax_partial_kernel(const float *__restrict__ x, int64_t n, fl
 __global__ void argmax_final_kernel(const float *__restrict__ pv, const int64_t *__restrict__ pi, int parts,
                                     int64_t index_base, int64_t *__restrict__ out_index,
                                     float *__restrict__ out_value) {
+  grid_dependency_sync();
   float bv = -INFINITY;
   int64_t bi = INT64_MAX;
   for (int i = threadIdx.x; i < parts; i += 32)
@@ -432,8 +449,8 @@ __global__ void argmax_final_kernel(const float *__restrict__ pv, const int64_t 
 void launch_argmax(const float *x, int64_t n, float *scratch_v, int64_t *scratch_i, int64_t index_base,
                    int64_t *out_index, float *out_value, cudaStream_t stream) {
   const int parts = static_cast<int>(std::min<int64_t>((n + 1023) / 1024, kArgmaxParts));
-  argmax_partial_kernel<<<parts, 256, 0, stream>>>(x, n, scratch_v, scratch_i);
-  argmax_final_kernel<<<1, 32, 0, stream>>>(scratch_v, scratch_i, parts, index_base, out_index, out_value);
+  launch_chained(argmax_partial_kernel, dim3(parts), dim3(256), 0, stream, x, n, scratch_v, scratch_i);
+  launch_chained(argmax_final_kernel, dim3(1), dim3(32), 0, stream, scratch_v, scratch_i, parts, index_base, out_index, out_value);
 }
 
 } // namespace llmcp_b200

@@ -150,6 +150,58 @@ def test_rms_norm(golden):
         assert np.array_equal(L.ops.rms_norm(x, wf, w_bf16=False), oracle.rms_norm(x, wf, w_bf16=False))
 
 
+def adversarial_rows(rng, M, H):
+    """Rows that stress the order of the sum of squares: wide dynamic range, outliers, growing
+    and repeating magnitudes, many exact rounding ties, zeros in front, all zeros, infinities."""
+    rows = []
+    position = np.arange(H, dtype=np.float64)
+    for r in range(M):
+        kind = r % 12
+        scale = 2.0 ** rng.integers(-30, 30)
+        if kind == 0:
+            x = rng.standard_normal(H)
+        elif kind == 1:
+            x = rng.standard_normal(H) * scale
+        elif kind == 2:
+            x = np.where(rng.random(H) < 0.02, rng.standard_normal(H) * 100.0, rng.standard_normal(H) * 0.1)
+        elif kind == 3:
+            x = 1.01 ** position * 1e-6
+        elif kind == 4:
+            x = rng.integers(0, 8, H) * 0.25
+        elif kind == 5:
+            x = np.where(position % 97 == 0, 0.0, rng.random(H))
+        elif kind == 6:
+            x = 2.0 ** (position % 40 - 20)
+        elif kind == 7:
+            x = np.where(position < 5, 0.0, rng.standard_normal(H) * scale)
+        elif kind == 8:
+            x = 1.0 + rng.integers(0, 3, H) * 0.5
+        elif kind == 9:
+            x = np.zeros(H)
+        elif kind == 10:
+            x = rng.standard_normal(H) * 2.0 ** rng.integers(-8, 8, H)
+        else:
+            x = rng.standard_normal(H)
+            x[rng.integers(0, H)] = np.inf if r % 24 == 11 else 1e30
+        rows.append(x)
+    return bf16(np.stack(rows))
+
+
+@pytest.mark.parametrize("H", [2560, 4096, 1024, 96, 8192])
+def test_rms_norm_sum_order(H):
+    """The sum of squares is taken in the reference's serial order whatever the data."""
+    rng = np.random.default_rng(H)
+    x = adversarial_rows(rng, 600, H)
+    w = rand_bf16(rng, H, scale=0.1)
+    with np.errstate(all="ignore"):
+        want = oracle.rms_norm(x, w)
+        got = L.ops.rms_norm(x, w)
+    # NaN results (rows holding an infinity) are compared as NaN: the payload is the processor's.
+    is_nan = lambda v: (v & 0x7fff) > 0x7f80
+    same = (got == want) | (is_nan(got) & is_nan(want))
+    assert same.all(), np.argwhere(~same.all(axis=1)).ravel()[:10]
+
+
 def test_pointwise(golden):
     c = golden("add")
     assert np.array_equal(f(L.ops.pointwise(c["a"], c["b"], "add")), c["ref"])
