@@ -11,6 +11,11 @@
 // block order:  acc = fma(float(dot), factor, acc)  -- the accumulation order that fixes the f32
 // result bit for bit -- apply the activation and store.  CTAs are persistent: a warp strides
 // over the groups of all matrices of the launch (up to four that share the input row).
+//
+// The weights do not depend on the kernel in front, only the input row does.  Launched as a
+// programmatic dependent, a warp requests the first rows of its first group (registers) and
+// prefetches the rest of its share into L2 before it waits for that kernel; inside the loop the
+// first rows of the next group are requested before the accumulation chain of the current one.
 
 #include "kernels.h"
 
@@ -31,9 +36,8 @@ __device__ inline Block32 ld_block(const void *p) {
 }
 
 template <int NB, int RC> constexpr size_t rows_smem_bytes(int warps) {
-  return static_cast<size_t>(NB) * 32 + NB * 4 + static_cast<size_t>(warps) * RC * (NB + 1) * sizeof(float2);
+  return static_cast<size_t>(NB) * 32 + NB * 4 + static_cast<size_t>(warps) * RC * (NB + 2) * sizeof(float2);
 }
-
 // NB: blocks per row (K/32).  RC: rows per group (one chain lane each).  RL: rows whose loads
 // are issued together (RC % RL == 0).
 template <int NB, int RC, int RL, bool DOTS>
@@ -51,7 +55,8 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
   const int kWarps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int warp_in_cta = threadIdx.x >> 5;
-  float2 *slab = slabs + warp_in_cta * RC * (NB + 1);
+  constexpr int kSlabStride = NB + 2; // float2 units: rows start 16-byte aligned on distinct banks
+  float2 *slab = slabs + warp_in_cta * RC * kSlabStride;
   const int total_warps = gridDim.x * kWarps;
   const int first_group = blockIdx.x * kWarps + warp_in_cta;
 
@@ -97,12 +102,11 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
   };
 
   // The weights do not depend on the kernel in front of this one: the first rows are requested
-  // (and, for matrices that fit in L2, the rest is prefetched into L2) before waiting for it.
-  bool preloaded = false;
+  // (and the rest of the warp's share prefetched into L2) before waiting for it.
+  int preloaded_group = -1; // the group whose first RL rows sit in w / dbits
   if (first_group < total_groups) {
-    const Rows c = resolve(first_group);
-    load(c, 0);
-    preloaded = true;
+    load(resolve(first_group), 0);
+    preloaded_group = first_group;
     if ((jobs.flags & kGemvPrefetchL2) && lane == 0) {
       for (int g = first_group; g < total_groups; g += total_warps) {
         const Rows p = resolve(g);
@@ -133,48 +137,67 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
     as_sm[i] = as[i];
   __syncthreads();
 
+  // One block of one row: exact int32 dot, then (float(dot), a_scale * w_scale) into the slab.
+  auto block_dot = [&](const Rows &c, int row, int kb, const uint32_t (&wv)[8], uint16_t scale_bits) {
+    const uint4 lo = a_lo[kb], hi = a_hi[kb];
+    int dot = dp4a(static_cast<int>(wv[0]), static_cast<int>(lo.x), 0);
+    dot = dp4a(static_cast<int>(wv[1]), static_cast<int>(lo.y), dot);
+    dot = dp4a(static_cast<int>(wv[2]), static_cast<int>(lo.z), dot);
+    dot = dp4a(static_cast<int>(wv[3]), static_cast<int>(lo.w), dot);
+    dot = dp4a(static_cast<int>(wv[4]), static_cast<int>(hi.x), dot);
+    dot = dp4a(static_cast<int>(wv[5]), static_cast<int>(hi.y), dot);
+    dot = dp4a(static_cast<int>(wv[6]), static_cast<int>(hi.z), dot);
+    dot = dp4a(static_cast<int>(wv[7]), static_cast<int>(hi.w), dot);
+    const float factor = __fmul_rn(as_sm[kb], f16_bits_to_f32(scale_bits));
+    slab[row * kSlabStride + kb] = make_float2(static_cast<float>(dot), factor);
+    if (DOTS)
+      dots_out[static_cast<size_t>(c.dots_offset + c.row0 + row) * NB + kb] = dot;
+  };
+  // RC lanes walk their row's pairs in ascending block order: the reference's accumulation.
+  // Sixteen pairs are fetched (eight 16-byte reads), then folded in.
+  auto chain = [&](const Rows &c) {
+    __syncwarp();
+    if (lane < RC) {
+      const float4 *mine = reinterpret_cast<const float4 *>(slab + lane * kSlabStride);
+      float acc = 0.0f;
+      for (int p = 0; p < NB / 2; p += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          t[u] = mine[p + u];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc = __fmaf_rn(t[u].x, t[u].y, acc);
+          acc = __fmaf_rn(t[u].z, t[u].w, acc);
+        }
+      }
+      store_from_f32(c.y, c.y_dtype, c.row0 + lane, apply_activation(acc, c.activation));
+    }
+    __syncwarp();
+  };
+
   for (int g = first_group; g < total_groups; g += total_warps) {
     const Rows c = resolve(g);
 #pragma unroll
     for (int r0 = 0; r0 < RC; r0 += RL) {
-      if (!(r0 == 0 && preloaded))
+      if (!(r0 == 0 && g == preloaded_group))
         load(c, r0);
 #pragma unroll
       for (int r = 0; r < RL; ++r) {
 #pragma unroll
         for (int i = 0; i < NL; ++i) {
-          if (32 * i + 32 <= NB || lane < NB - 32 * i) {
-            const int kb = 32 * i + lane;
-            const uint4 lo = a_lo[kb], hi = a_hi[kb];
-            int dot = dp4a(static_cast<int>(w[r][i].v[0]), static_cast<int>(lo.x), 0);
-            dot = dp4a(static_cast<int>(w[r][i].v[1]), static_cast<int>(lo.y), dot);
-            dot = dp4a(static_cast<int>(w[r][i].v[2]), static_cast<int>(lo.z), dot);
-            dot = dp4a(static_cast<int>(w[r][i].v[3]), static_cast<int>(lo.w), dot);
-            dot = dp4a(static_cast<int>(w[r][i].v[4]), static_cast<int>(hi.x), dot);
-            dot = dp4a(static_cast<int>(w[r][i].v[5]), static_cast<int>(hi.y), dot);
-            dot = dp4a(static_cast<int>(w[r][i].v[6]), static_cast<int>(hi.z), dot);
-            dot = dp4a(static_cast<int>(w[r][i].v[7]), static_cast<int>(hi.w), dot);
-            const float factor = __fmul_rn(as_sm[kb], f16_bits_to_f32(dbits[r][i]));
-            slab[(r0 + r) * (NB + 1) + kb] = make_float2(static_cast<float>(dot), factor);
-            if (DOTS)
-              dots_out[static_cast<size_t>(c.dots_offset + c.row0 + r0 + r) * NB + kb] = dot;
-          }
+          if (32 * i + 32 <= NB || lane < NB - 32 * i)
+            block_dot(c, r0 + r, 32 * i + lane, w[r][i].v, dbits[r][i]);
         }
       }
     }
-    preloaded = false;
-    __syncwarp();
-    if (lane < RC) {
-      const float2 *mine = slab + lane * (NB + 1);
-      float acc = 0.0f;
-#pragma unroll 16
-      for (int kb = 0; kb < NB; ++kb) {
-        const float2 v = mine[kb];
-        acc = __fmaf_rn(v.x, v.y, acc);
-      }
-      store_from_f32(c.y, c.y_dtype, c.row0 + lane, apply_activation(acc, c.activation));
+    // The registers are free: the first rows of the next group are requested now and travel
+    // while the chain below runs.
+    if (g + total_warps < total_groups) {
+      load(resolve(g + total_warps), 0);
+      preloaded_group = g + total_warps;
     }
-    __syncwarp();
+    chain(c);
   }
 }
 
