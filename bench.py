@@ -46,7 +46,7 @@ GEMV_N, GEMV_K, GEMV_RING = 9216, 2560, 12
 GEMV_BYTES = GEMV_N * (GEMV_K // 32) * 34 + GEMV_K * 4 + GEMV_N * 4  # weights + f32 x + f32 y = 25,114,624
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q8_rows_kernel launch of this shape, from the
 # ncu capture summarised in profiles/gemv_q8_rows_9216x2560.md (the 36,864-byte result stays in L2).
-GEMV_DRAM_TRAFFIC = 25_092_864
+GEMV_DRAM_TRAFFIC = 25_097_216
 GEMM_M, GEMM_N, GEMM_K = 1024, 9216, 2560  # the gate_proj/up_proj prefill GEMM (BASELINE.json configs[1] shape)
 
 
@@ -382,7 +382,7 @@ def main():
                    "vs_baseline_is": "per-GPU value / 11.39 tok/s published for Apple M2 (reference README.md:140)"},
         "e2e": {"value": world * steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 8 + 2 * dims.rotary * 4,
                 "d2h_bytes_per_step": dims.vocab * 4, "tokens_match_device_arm": bool(same)},
-        "gpu_launches": int(launches),
+        "gpu_launches": int(launches) * world,
         "clocks": clocks,
         "prefill_tokens_per_second": {"tokens": PREFILL, "engine": PREFILL / prefill_s, "e2e_abi": PREFILL / e2e_prefill_s},
     }
