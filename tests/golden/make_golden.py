@@ -35,7 +35,9 @@ def f32(t):
 
 
 def main():
-    ref_root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of the llmcp project>")
+    ref_root = pathlib.Path(sys.argv[1])
     spec = importlib.util.spec_from_file_location(
         "run_numeric", ref_root / "tests/numeric/run_numeric.py")
     rn = importlib.util.module_from_spec(spec)
