@@ -331,6 +331,7 @@ static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, 
     GemvJobs g{};
     g.count = count;
     g.flags = flags;
+    g.error_flag = gemm_error;
     for (int i = 0; i < count; ++i) {
       g.job[i].wq = jobs[i].w->q;
       g.job[i].wd = jobs[i].w->d;

@@ -46,6 +46,7 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
                     int total_groups, int32_t *__restrict__ dots_out) {
   constexpr int K = NB * 32;
   constexpr int NL = (NB + 31) / 32; // loads per lane per row
+  constexpr bool kInputInRegisters = NB <= 80;
   extern __shared__ __align__(16) unsigned char smem[];
   uint4 *a_lo = reinterpret_cast<uint4 *>(smem);           // bytes 0..15 of every activation block
   uint4 *a_hi = reinterpret_cast<uint4 *>(smem + NB * 16); // bytes 16..31
@@ -126,20 +127,48 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
   // keeps the look-ahead at one kernel (several matrices prefetching at once thrash L2).
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  for (int i = threadIdx.x; i < 2 * NB; i += blockDim.x) {
-    const uint4 v = reinterpret_cast<const uint4 *>(aq)[i];
-    if (i & 1)
-      a_hi[i >> 1] = v;
-    else
-      a_lo[i >> 1] = v;
+  // The input row: for the short rows every lane keeps its own blocks (those it meets in every
+  // row) in registers, read straight from global memory; for longer rows that costs residency,
+  // so the row is staged once per CTA in shared memory instead.
+  uint4 x_lo[kInputInRegisters ? NL : 1], x_hi[kInputInRegisters ? NL : 1];
+  float x_scale[kInputInRegisters ? NL : 1];
+  if (kInputInRegisters) {
+#pragma unroll
+    for (int i = 0; i < NL; ++i) {
+      if (32 * i + 32 <= NB || lane < NB - 32 * i) {
+        const int kb = 32 * i + lane;
+        x_lo[i] = reinterpret_cast<const uint4 *>(aq)[2 * kb];
+        x_hi[i] = reinterpret_cast<const uint4 *>(aq)[2 * kb + 1];
+        x_scale[i] = as[kb];
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < 2 * NB; i += blockDim.x) {
+      const uint4 v = reinterpret_cast<const uint4 *>(aq)[i];
+      if (i & 1)
+        a_hi[i >> 1] = v;
+      else
+        a_lo[i >> 1] = v;
+    }
+    for (int i = threadIdx.x; i < NB; i += blockDim.x)
+      as_sm[i] = as[i];
+    __syncthreads();
   }
-  for (int i = threadIdx.x; i < NB; i += blockDim.x)
-    as_sm[i] = as[i];
-  __syncthreads();
 
   // One block of one row: exact int32 dot, then (float(dot), a_scale * w_scale) into the slab.
-  auto block_dot = [&](const Rows &c, int row, int kb, const uint32_t (&wv)[8], uint16_t scale_bits) {
-    const uint4 lo = a_lo[kb], hi = a_hi[kb];
+  auto block_dot = [&](const Rows &c, int row, int i, const uint32_t (&wv)[8], uint16_t scale_bits) {
+    const int kb = 32 * i + lane;
+    uint4 lo, hi;
+    float a_scale;
+    if (kInputInRegisters) {
+      lo = x_lo[i];
+      hi = x_hi[i];
+      a_scale = x_scale[i];
+    } else {
+      lo = a_lo[kb];
+      hi = a_hi[kb];
+      a_scale = as_sm[kb];
+    }
     int dot = dp4a(static_cast<int>(wv[0]), static_cast<int>(lo.x), 0);
     dot = dp4a(static_cast<int>(wv[1]), static_cast<int>(lo.y), dot);
     dot = dp4a(static_cast<int>(wv[2]), static_cast<int>(lo.z), dot);
@@ -148,7 +177,7 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
     dot = dp4a(static_cast<int>(wv[5]), static_cast<int>(hi.y), dot);
     dot = dp4a(static_cast<int>(wv[6]), static_cast<int>(hi.z), dot);
     dot = dp4a(static_cast<int>(wv[7]), static_cast<int>(hi.w), dot);
-    const float factor = __fmul_rn(as_sm[kb], f16_bits_to_f32(scale_bits));
+    const float factor = __fmul_rn(a_scale, f16_bits_to_f32(scale_bits));
     slab[row * kSlabStride + kb] = make_float2(static_cast<float>(dot), factor);
     if (DOTS)
       dots_out[static_cast<size_t>(c.dots_offset + c.row0 + row) * NB + kb] = dot;
@@ -187,7 +216,7 @@ gemv_q8_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
 #pragma unroll
         for (int i = 0; i < NL; ++i) {
           if (32 * i + 32 <= NB || lane < NB - 32 * i)
-            block_dot(c, r0 + r, 32 * i + lane, w[r][i].v, dbits[r][i]);
+            block_dot(c, r0 + r, i, w[r][i].v, dbits[r][i]);
         }
       }
     }

@@ -29,11 +29,14 @@ struct GemvJob {
 constexpr int kGemvOverlapPrevious = 1; // programmatic dependent launch: start while the kernel in
                                         // front is still running, wait for it before reading x
 constexpr int kGemvPrefetchL2 = 2;      // prefetch all weights of the launch into L2 up front
+constexpr int kGemvRing = 4;            // feed the weights through per-warp shared-memory rings
+                                        // (bulk asynchronous copies), K in {2560, 4096, 9216}
 
 struct GemvJobs {
   GemvJob job[kMaxGemvJobs];
   int count;
   int flags;
+  int *error_flag; // device int (optional): set to 1 if a bounded wait for a copy ran out
 };
 
 // d32 (optional): the same scales widened to f32, [N][K/32], for the tensor-core GEMM.
@@ -46,6 +49,10 @@ cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJ
 bool gemv_rows_supported(int K);
 cudaError_t launch_gemv_q8_rows(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
                                 cudaStream_t stream, int rows_per_group);
+// The same product with the weights streamed through shared-memory rings (gemv_ring.cu).
+bool gemv_ring_supported(int K, const GemvJobs &jobs);
+cudaError_t launch_gemv_q8_ring(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
+                                int *error_flag, cudaStream_t stream);
 cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K, const int8_t *wq,
                                 const uint16_t *wd, int N, void *y, int y_dtype, int activation,
                                 int32_t *dots_out, cudaStream_t stream);
