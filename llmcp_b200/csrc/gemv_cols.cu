@@ -1,0 +1,133 @@
+// Decode GEMV for the long rows (K = 4096, 9216) of a single matrix.  Q8Decode.cpp:131-225.
+//
+// A CTA takes R consecutive rows and has one thread per quantisation block of a row (K/32
+// threads).  Thread t meets the same input block in every row, so it keeps that block and its
+// scale in registers; its R weight blocks (32 bytes each, one 256-bit streaming load per row,
+// a warp reads 1 KB of a row at a time) are all requested before the kernel waits for the kernel
+// in front of it, which makes the whole matrix one round of loads with nothing in shared memory
+// but the (float(dot), a_scale * w_scale) pairs.  After one barrier the first R lanes walk the
+// pairs of their rows in ascending block order,  acc = fma(float(dot), factor, acc)  -- the
+// accumulation order that fixes the f32 result bit for bit -- R chains per instruction instead
+// of one.  R is chosen so that all CTAs of the 2560-row projections are resident at once.
+
+#include "kernels.h"
+
+namespace llmcp_b200 {
+
+namespace {
+
+struct ColsBlock {
+  uint32_t v[8];
+};
+
+__device__ inline ColsBlock ld_cols_block(const void *p) {
+  ColsBlock r;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
+      : "l"(p));
+  return r;
+}
+
+template <int NB, int R, bool DOTS>
+__global__ void __launch_bounds__(NB)
+gemv_q8_cols_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const int8_t *__restrict__ wq,
+                    const uint16_t *__restrict__ wd, void *__restrict__ y, int N, int activation, int y_dtype,
+                    int32_t *__restrict__ dots_out) {
+  constexpr int K = NB * 32;
+  constexpr int kStride = NB + 2; // float2 units: rows start 16-byte aligned on distinct banks
+  __shared__ __align__(16) float2 slab[R * kStride];
+  const int t = threadIdx.x;
+  const int row0 = blockIdx.x * R;
+  const int rows = min(R, N - row0);
+
+  ColsBlock w[R];
+  uint16_t scale_bits[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    if (i < rows) {
+      w[i] = ld_cols_block(wq + static_cast<size_t>(row0 + i) * K + t * 32);
+      scale_bits[i] = __ldg(wd + static_cast<size_t>(row0 + i) * NB + t);
+    }
+  }
+  // The weights are on their way; the input row belongs to the kernel in front.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint4 lo = reinterpret_cast<const uint4 *>(aq)[2 * t];
+  const uint4 hi = reinterpret_cast<const uint4 *>(aq)[2 * t + 1];
+  const float a_scale = as[t];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    if (i < rows) {
+      int dot = dp4a(static_cast<int>(w[i].v[0]), static_cast<int>(lo.x), 0);
+      dot = dp4a(static_cast<int>(w[i].v[1]), static_cast<int>(lo.y), dot);
+      dot = dp4a(static_cast<int>(w[i].v[2]), static_cast<int>(lo.z), dot);
+      dot = dp4a(static_cast<int>(w[i].v[3]), static_cast<int>(lo.w), dot);
+      dot = dp4a(static_cast<int>(w[i].v[4]), static_cast<int>(hi.x), dot);
+      dot = dp4a(static_cast<int>(w[i].v[5]), static_cast<int>(hi.y), dot);
+      dot = dp4a(static_cast<int>(w[i].v[6]), static_cast<int>(hi.z), dot);
+      dot = dp4a(static_cast<int>(w[i].v[7]), static_cast<int>(hi.w), dot);
+      slab[i * kStride + t] = make_float2(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
+      if (DOTS)
+        dots_out[static_cast<size_t>(row0 + i) * NB + t] = dot;
+    }
+  }
+  __syncthreads();
+  if (t < rows) {
+    const float4 *mine = reinterpret_cast<const float4 *>(slab + t * kStride);
+    float acc = 0.0f;
+    for (int p = 0; p < NB / 2; p += 8) {
+      float4 pairs[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        pairs[u] = mine[p + u];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        acc = __fmaf_rn(pairs[u].x, pairs[u].y, acc);
+        acc = __fmaf_rn(pairs[u].z, pairs[u].w, acc);
+      }
+    }
+    store_from_f32(y, y_dtype, row0 + t, apply_activation(acc, activation));
+  }
+}
+
+template <int NB, int R>
+cudaError_t launch_cols(const int8_t *aq, const float *as, const GemvJob &job, int flags, int32_t *dots_out,
+                        cudaStream_t stream) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((job.N + R - 1) / R);
+  config.blockDim = dim3(NB);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (flags & kGemvOverlapPrevious) ? 1 : 0;
+  if (dots_out)
+    return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, true>, aq, as, job.wq, job.wd, job.y, job.N, job.activation,
+                              job.y_dtype, dots_out);
+  int32_t *no_dots = nullptr;
+  return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, false>, aq, as, job.wq, job.wd, job.y, job.N, job.activation,
+                            job.y_dtype, no_dots);
+}
+
+} // namespace
+
+// One matrix, K = 4096 or 9216, few enough rows that one wave of CTAs covers them.
+bool gemv_cols_supported(int K, const GemvJobs &jobs) {
+  if (jobs.count != 1 || (K != 4096 && K != 9216))
+    return false;
+  // resident CTAs per SM by registers: 5 of 128 threads, 2 of 288 threads
+  const int rows_per_cta = K == 4096 ? 8 : 9, resident = K == 4096 ? 148 * 5 : 148 * 2;
+  return (jobs.job[0].N + rows_per_cta - 1) / rows_per_cta <= resident;
+}
+
+cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
+                                cudaStream_t stream) {
+  if (!gemv_cols_supported(K, jobs))
+    return cudaErrorInvalidValue;
+  if (K == 4096)
+    return launch_cols<128, 8>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
+  return launch_cols<288, 9>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
+}
+
+} // namespace llmcp_b200

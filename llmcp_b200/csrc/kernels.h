@@ -29,6 +29,7 @@ struct GemvJob {
 constexpr int kGemvOverlapPrevious = 1; // programmatic dependent launch: start while the kernel in
                                         // front is still running, wait for it before reading x
 constexpr int kGemvPrefetchL2 = 2;      // prefetch all weights of the launch into L2 up front
+constexpr int kGemvNoCols = 8;          // do not use the block-column kernel for long rows
 constexpr int kGemvRing = 4;            // feed the weights through per-warp shared-memory rings
                                         // (bulk asynchronous copies), K in {2560, 4096, 9216}
 
@@ -49,6 +50,10 @@ cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJ
 bool gemv_rows_supported(int K);
 cudaError_t launch_gemv_q8_rows(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
                                 cudaStream_t stream, int rows_per_group);
+// One matrix with long rows (K = 4096, 9216): a thread per block column (gemv_cols.cu).
+bool gemv_cols_supported(int K, const GemvJobs &jobs);
+cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
+                                cudaStream_t stream);
 // The same product with the weights streamed through shared-memory rings (gemv_ring.cu).
 bool gemv_ring_supported(int K, const GemvJobs &jobs);
 cudaError_t launch_gemv_q8_ring(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,

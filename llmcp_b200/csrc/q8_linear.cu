@@ -228,6 +228,8 @@ cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJ
                            int32_t *dots_out, cudaStream_t stream, int rows_per_warp) {
   if (jobs.count < 1 || jobs.count > kMaxGemvJobs || K % kBlock != 0)
     return cudaErrorInvalidValue;
+  if (!(jobs.flags & kGemvNoCols) && rows_per_warp == 0 && gemv_cols_supported(K, jobs))
+    return launch_gemv_q8_cols(aq, as, K, jobs, dots_out, stream);
   if ((jobs.flags & kGemvRing) && rows_per_warp == 0 && gemv_ring_supported(K, jobs))
     return launch_gemv_q8_ring(aq, as, K, jobs, dots_out, jobs.error_flag, stream);
   if (gemv_rows_supported(K) && rows_per_warp >= 0)
