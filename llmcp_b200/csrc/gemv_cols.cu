@@ -110,10 +110,143 @@ cudaError_t launch_cols(const int8_t *aq, const float *as, const GemvJob &job, i
                             job.y_dtype, no_dots);
 }
 
+// K = 2560 (80 blocks per row), up to four matrices that share the input row.  160 threads: thread
+// t meets block t % 80 of every row it handles, and handles rows (t / 80) * 8 .. + 7 of the CTA's
+// set of 16 rows, all requested at once.  CTAs are persistent: the loads of the next set are
+// issued before the 16 chains of the current one run.
+constexpr int kSetRows = 16;
+
+template <bool DOTS>
+__global__ void __launch_bounds__(160, 4)
+gemv_q8_cols80_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const GemvJobs jobs, int total_sets,
+                      int32_t *__restrict__ dots_out) {
+  constexpr int NB = 80, K = 2560, kHalf = kSetRows / 2;
+  constexpr int kStride = NB + 2;
+  __shared__ __align__(16) float2 slab[kSetRows * kStride];
+  const int t = threadIdx.x;
+  const int kb = t % NB, half = t / NB;
+
+  struct Set {
+    const int8_t *wq;
+    const uint16_t *wd;
+    void *y;
+    int row0, activation, y_dtype, dots_offset;
+  };
+  // warp_begin holds each matrix's first set
+  auto resolve = [&](int s) {
+    Set c{jobs.job[0].wq, jobs.job[0].wd, jobs.job[0].y, 0, jobs.job[0].activation, jobs.job[0].y_dtype, 0};
+    int begin = 0;
+#pragma unroll
+    for (int j = 1; j < kMaxGemvJobs; ++j)
+      if (j < jobs.count && s >= jobs.job[j].warp_begin) {
+        c.wq = jobs.job[j].wq;
+        c.wd = jobs.job[j].wd;
+        c.y = jobs.job[j].y;
+        begin = jobs.job[j].warp_begin;
+        c.activation = jobs.job[j].activation;
+        c.y_dtype = jobs.job[j].y_dtype;
+        c.dots_offset = jobs.job[j].dots_offset;
+      }
+    c.row0 = (s - begin) * kSetRows;
+    return c;
+  };
+  ColsBlock w[kHalf];
+  uint16_t scale_bits[kHalf];
+  auto load = [&](const Set &c) {
+#pragma unroll
+    for (int i = 0; i < kHalf; ++i) {
+      const size_t row = static_cast<size_t>(c.row0 + half * kHalf + i);
+      w[i] = ld_cols_block(c.wq + row * K + kb * 32);
+      scale_bits[i] = __ldg(c.wd + row * NB + kb);
+    }
+  };
+
+  int s = blockIdx.x;
+  if (s < total_sets)
+    load(resolve(s));
+  // The weights are on their way; the input row belongs to the kernel in front.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint4 lo = reinterpret_cast<const uint4 *>(aq)[2 * kb];
+  const uint4 hi = reinterpret_cast<const uint4 *>(aq)[2 * kb + 1];
+  const float a_scale = as[kb];
+  for (; s < total_sets; s += gridDim.x) {
+    const Set c = resolve(s);
+#pragma unroll
+    for (int i = 0; i < kHalf; ++i) {
+      int dot = dp4a(static_cast<int>(w[i].v[0]), static_cast<int>(lo.x), 0);
+      dot = dp4a(static_cast<int>(w[i].v[1]), static_cast<int>(lo.y), dot);
+      dot = dp4a(static_cast<int>(w[i].v[2]), static_cast<int>(lo.z), dot);
+      dot = dp4a(static_cast<int>(w[i].v[3]), static_cast<int>(lo.w), dot);
+      dot = dp4a(static_cast<int>(w[i].v[4]), static_cast<int>(hi.x), dot);
+      dot = dp4a(static_cast<int>(w[i].v[5]), static_cast<int>(hi.y), dot);
+      dot = dp4a(static_cast<int>(w[i].v[6]), static_cast<int>(hi.z), dot);
+      dot = dp4a(static_cast<int>(w[i].v[7]), static_cast<int>(hi.w), dot);
+      const int row = half * kHalf + i;
+      slab[row * kStride + kb] = make_float2(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
+      if (DOTS)
+        dots_out[static_cast<size_t>(c.dots_offset + c.row0 + row) * NB + kb] = dot;
+    }
+    __syncthreads();
+    if (s + gridDim.x < total_sets)
+      load(resolve(s + gridDim.x)); // travels while the chains below run
+    if (t < kSetRows) {
+      const float4 *mine = reinterpret_cast<const float4 *>(slab + t * kStride);
+      float acc = 0.0f;
+      for (int p = 0; p < NB / 2; p += 8) {
+        float4 pairs[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          pairs[u] = mine[p + u];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc = __fmaf_rn(pairs[u].x, pairs[u].y, acc);
+          acc = __fmaf_rn(pairs[u].z, pairs[u].w, acc);
+        }
+      }
+      store_from_f32(c.y, c.y_dtype, c.row0 + t, apply_activation(acc, c.activation));
+    }
+    __syncthreads(); // the slab is free again
+  }
+}
+
+cudaError_t launch_cols80(const int8_t *aq, const float *as, GemvJobs jobs, int32_t *dots_out, cudaStream_t stream) {
+  int sets = 0, rows = 0;
+  for (int j = 0; j < jobs.count; ++j) {
+    jobs.job[j].warp_begin = sets;
+    jobs.job[j].dots_offset = rows;
+    sets += jobs.job[j].N / kSetRows;
+    rows += jobs.job[j].N;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(std::min(sets, 148 * 4));
+  config.blockDim = dim3(160);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (jobs.flags & kGemvOverlapPrevious) ? 1 : 0;
+  if (dots_out)
+    return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<true>, aq, as, jobs, sets, dots_out);
+  int32_t *no_dots = nullptr;
+  return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<false>, aq, as, jobs, sets, no_dots);
+}
+
 } // namespace
 
-// One matrix, K = 4096 or 9216, few enough rows that one wave of CTAs covers them.
+// K = 2560: up to four matrices of the layer.  K = 4096 or 9216: one matrix with few enough rows
+// that one wave of CTAs covers them.
 bool gemv_cols_supported(int K, const GemvJobs &jobs) {
+  if (K == 2560) { // the layer projections; the vocabulary projection stays with the row kernel
+    int rows = 0;
+    for (int j = 0; j < jobs.count; ++j) {
+      if (jobs.job[j].N % kSetRows != 0)
+        return false;
+      rows += jobs.job[j].N;
+    }
+    return rows <= 32768;
+  }
   if (jobs.count != 1 || (K != 4096 && K != 9216))
     return false;
   // resident CTAs per SM by registers: 5 of 128 threads, 2 of 288 threads
@@ -125,6 +258,8 @@ cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const 
                                 cudaStream_t stream) {
   if (!gemv_cols_supported(K, jobs))
     return cudaErrorInvalidValue;
+  if (K == 2560)
+    return launch_cols80(aq, as, jobs, dots_out, stream);
   if (K == 4096)
     return launch_cols<128, 8>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
   return launch_cols<288, 9>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
