@@ -304,7 +304,7 @@ gdn_decode_front_kernel(const uint16_t *__restrict__ x, const uint16_t *__restri
                         float *__restrict__ kn, float *__restrict__ beta, float *__restrict__ decay,
                         uint16_t *__restrict__ conv_out) {
   extern __shared__ float front_sm[]; // per warp: dk squares
-  grid_dependency_sync();
+  grid_dependency_sync(true); // the step kernel behind is placed now and fetches its state meanwhile
   const int lane = threadIdx.x & 31;
   const int warp_in_cta = threadIdx.x >> 5;
   const int warp = blockIdx.x * (blockDim.x >> 5) + warp_in_cta;
@@ -378,15 +378,17 @@ gdn_decode_step_kernel(const uint16_t *__restrict__ conv, const float *__restric
                        int8_t *__restrict__ q_out, float *__restrict__ s_out) {
   extern __shared__ __align__(16) float step_sm[]; // kn[DK], qn[DK], squares[dv]
   __shared__ float rstd_sm;
-  grid_dependency_sync(true);
   float *k_sm = step_sm, *q_sm = step_sm + DK, *sq_sm = step_sm + 2 * DK;
   const int h = blockIdx.x, v = threadIdx.x;
   const int kh = h / (nv / nk);
   float *col = state + static_cast<int64_t>(h) * DK * dv + v;
+  // The recurrent state is this kernel's own (written by the same kernel one token earlier, which
+  // finished long ago): it is requested before waiting for the kernel in front.
   float s[DK];
 #pragma unroll
   for (int k = 0; k < DK; ++k)
     s[k] = col[static_cast<int64_t>(k) * dv];
+  grid_dependency_sync(true);
   for (int d = v; d < DK; d += dv) {
     k_sm[d] = kn[kh * DK + d];
     q_sm[d] = qn[kh * DK + d];

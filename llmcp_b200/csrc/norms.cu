@@ -89,10 +89,24 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
                      float *__restrict__ s) {
   extern __shared__ __align__(16) float vrow_sm[]; // squares
   __shared__ float rstd_sm;
-  grid_dependency_sync(true);
   const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
   const int quads = H >> 2;
   const int per_thread = (quads + blockDim.x - 1) / blockDim.x; // 1 for H <= 4096
+  // The norm weights do not depend on the kernel in front: they are fetched before waiting for it.
+  float wt[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = r * blockDim.x + threadIdx.x;
+    if (r < per_thread && i < quads) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        wt[r][u] = load_as_f32(w, w_dtype, 4 * i + u);
+        if (zero_centered)
+          wt[r][u] = __fadd_rn(wt[r][u], 1.0f);
+      }
+    }
+  }
+  grid_dependency_sync(true);
   float x[4][4];
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
@@ -150,12 +164,8 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
     float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (live) {
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        float wt = load_as_f32(w, w_dtype, 4 * i + u);
-        if (zero_centered)
-          wt = __fadd_rn(wt, 1.0f);
-        o[u] = bf16_to_f32(f32_to_bf16(__fmul_rn(__fmul_rn(x[r][u], rstd), wt)));
-      }
+      for (int u = 0; u < 4; ++u)
+        o[u] = bf16_to_f32(f32_to_bf16(__fmul_rn(__fmul_rn(x[r][u], rstd), wt[r][u])));
       if (y)
         reinterpret_cast<uint2 *>(y + base)[i] =
             make_uint2(static_cast<uint32_t>(f32_to_bf16(o[0])) | (static_cast<uint32_t>(f32_to_bf16(o[1])) << 16),
