@@ -44,8 +44,8 @@ PREFILL = 1024
 M2_DECODE_TOK_S = 11.39  # published Q8_0 decode tok/s on Apple M2, 4 threads (reference README.md:140)
 GEMV_N, GEMV_K, GEMV_RING = 9216, 2560, 12
 GEMV_BYTES = GEMV_N * (GEMV_K // 32) * 34 + GEMV_K * 4 + GEMV_N * 4  # weights + f32 x + f32 y = 25,114,624
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q8_rows_kernel launch of this shape, from the
-# ncu capture summarised in profiles/gemv_q8_rows_9216x2560.md (the 36,864-byte result stays in L2).
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q8_cols80_kernel launch of this shape, from the
+# ncu capture summarised in profiles/gemv_q8_cols80_9216x2560.md (the 36,864-byte result stays in L2).
 GEMV_DRAM_TRAFFIC = 25_097_216
 GEMM_M, GEMM_N, GEMM_K = 1024, 9216, 2560  # the gate_proj/up_proj prefill GEMM (BASELINE.json configs[1] shape)
 
@@ -391,7 +391,7 @@ def main():
         peak, peak_kind = measured_peaks()
         gbs, us, gemv_launches = gemv_roofline(L, torch, local_rank)
         result["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                              "traffic": GEMV_DRAM_TRAFFIC, "kernel": "gemv_q8_rows_kernel", "shape": [1, GEMV_N, GEMV_K],
+                              "traffic": GEMV_DRAM_TRAFFIC, "kernel": "gemv_q8_cols80_kernel", "shape": [1, GEMV_N, GEMV_K],
                               "us_per_launch": us, "launches_timed": gemv_launches, "peak_kind": f"of {peak_kind}",
                               "algorithmic_bytes_per_launch": GEMV_BYTES,
                               "whole_model_effective_gbs": 4.61e9 / (device_ms / steps / 1e3) / 1e9}
