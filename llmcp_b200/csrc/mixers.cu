@@ -4,6 +4,8 @@
 // channels and time for the convolution, value columns and heads for the recurrence,
 // keys (scores) and head-dim lanes (weighted sum) for attention.
 
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace llmcp_b200 {
@@ -236,6 +238,129 @@ gdn_recurrence_kernel(const uint16_t *__restrict__ conv, const float *__restrict
   }
 }
 
+// The same recurrence for calls of more than one token, with two tokens in flight.  Token t+1's
+// first chain, kv' = sum_k (s_k * dc') * k'_k, needs the state row k as token t leaves it, and
+// token t's second pass finalises the rows in ascending k: so row k is decayed for token t+1 and
+// folded into kv' right after it has been updated for token t.  Every value is produced by the
+// same operations in the same order as in the kernel above; only the two dependent chains (o of
+// token t, kv of token t+1) now run side by side instead of one after the other.
+template <int DK>
+__global__ void __launch_bounds__(32)
+gdn_recurrence_pipelined_kernel(const uint16_t *__restrict__ conv, const float *__restrict__ qn,
+                                const float *__restrict__ kn, const float *__restrict__ beta,
+                                const float *__restrict__ decay, float *__restrict__ state, int64_t S, int nk,
+                                int nv, int dv, uint16_t *__restrict__ out) {
+  grid_dependency_sync();
+  const int h = blockIdx.x;
+  const int v = blockIdx.y * 32 + threadIdx.x;
+  const int kh = h / (nv / nk);
+  const int64_t channels = 2 * static_cast<int64_t>(nk) * DK + static_cast<int64_t>(nv) * dv;
+  const bool active = v < dv;
+  float *col = state + static_cast<int64_t>(h) * DK * dv + (active ? v : 0);
+  __shared__ __align__(16) float kq_sm[2][2 * DK]; // per token parity: kn[DK], qn[DK]
+
+  float s[DK];
+#pragma unroll
+  for (int k = 0; k < DK; ++k)
+    s[k] = active ? col[static_cast<int64_t>(k) * dv] : 0.0f;
+
+  constexpr int kPre = DK / 32;
+  float k_next[kPre], q_next[kPre];
+  float dc_next = 0.0f, bt_next = 0.0f;
+  uint16_t value_next = 0;
+  auto fetch = [&](int64_t t) { // inputs of token t into registers
+#pragma unroll
+    for (int u = 0; u < kPre; ++u) {
+      k_next[u] = kn[(t * nk + kh) * DK + u * 32 + threadIdx.x];
+      q_next[u] = qn[(t * nk + kh) * DK + u * 32 + threadIdx.x];
+    }
+    dc_next = decay[t * nv + h];
+    bt_next = beta[t * nv + h];
+    value_next = active ? conv[t * channels + 2 * static_cast<int64_t>(nk) * DK + h * dv + v] : static_cast<uint16_t>(0);
+  };
+  auto publish = [&](int parity) { // the fetched token's k and q into shared memory
+#pragma unroll
+    for (int u = 0; u < kPre; ++u) {
+      kq_sm[parity][u * 32 + threadIdx.x] = k_next[u];
+      kq_sm[parity][DK + u * 32 + threadIdx.x] = q_next[u];
+    }
+  };
+
+  // token 0: decay and first chain on their own
+  fetch(0);
+  publish(0);
+  float dc = dc_next, bt = bt_next, value = bf16_to_f32(value_next);
+  if (S > 1)
+    fetch(1);
+  __syncwarp();
+  float kv = 0.0f;
+#pragma unroll
+  for (int k4 = 0; k4 < DK; k4 += 4) {
+    const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[0][k4]);
+    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s[k4 + u] = __fmul_rn(s[k4 + u], dc);
+      kv = __fadd_rn(kv, __fmul_rn(s[k4 + u], kv4[u]));
+    }
+  }
+  for (int64_t t = 0; t < S; ++t) {
+    const int cur = static_cast<int>(t & 1);
+    const float delta = __fmul_rn(__fsub_rn(value, kv), bt);
+    float o = 0.0f;
+    if (t + 1 < S) {
+      // Token t+1 is in the registers: publish it to the other buffer (last read two passes ago)
+      // and start fetching token t+2.
+      publish(cur ^ 1);
+      const float dc1 = dc_next;
+      bt = bt_next;
+      value = bf16_to_f32(value_next);
+      if (t + 2 < S)
+        fetch(t + 2);
+      __syncwarp();
+      float kv1 = 0.0f;
+#pragma unroll
+      for (int k4 = 0; k4 < DK; k4 += 4) {
+        const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[cur][k4]);
+        const float4 qq = *reinterpret_cast<const float4 *>(&kq_sm[cur][DK + k4]);
+        const float4 kn1 = *reinterpret_cast<const float4 *>(&kq_sm[cur ^ 1][k4]);
+        const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+        const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
+        const float kw4[4] = {kn1.x, kn1.y, kn1.z, kn1.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[k4 + u] = __fadd_rn(s[k4 + u], __fmul_rn(kv4[u], delta)); // row k as token t leaves it
+          o = __fadd_rn(o, __fmul_rn(s[k4 + u], qv4[u]));
+          s[k4 + u] = __fmul_rn(s[k4 + u], dc1);                       // decayed for token t+1
+          kv1 = __fadd_rn(kv1, __fmul_rn(s[k4 + u], kw4[u]));
+        }
+      }
+      kv = kv1;
+    } else {
+#pragma unroll
+      for (int k4 = 0; k4 < DK; k4 += 4) {
+        const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[cur][k4]);
+        const float4 qq = *reinterpret_cast<const float4 *>(&kq_sm[cur][DK + k4]);
+        const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+        const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[k4 + u] = __fadd_rn(s[k4 + u], __fmul_rn(kv4[u], delta));
+          o = __fadd_rn(o, __fmul_rn(s[k4 + u], qv4[u]));
+        }
+      }
+    }
+    if (active)
+      out[t * nv * dv + h * dv + v] = f32_to_bf16(o);
+    __syncwarp();
+  }
+  if (active) {
+#pragma unroll
+    for (int k = 0; k < DK; ++k)
+      col[static_cast<int64_t>(k) * dv] = s[k];
+  }
+}
+
 size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk) {
   return static_cast<size_t>(S) * (2 * static_cast<size_t>(nk) * dk + 2 * static_cast<size_t>(nv));
 }
@@ -257,7 +382,13 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
       conv, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, S, nk, nv, dk, dv, b_activated, qn, kn, beta, decay);
   dim3 grid(nv, (dv + 31) / 32);
   const size_t smem = 2 * static_cast<size_t>(dk) * sizeof(float);
-  if (dk == 128)
+  static const bool pipelined = [] {
+    const char *flag = std::getenv("LLMCP_B200_GDN_PIPELINE");
+    return !(flag && flag[0] == '0');
+  }();
+  if (dk == 128 && S > 1 && pipelined)
+    launch_chained(gdn_recurrence_pipelined_kernel<128>, dim3(grid), dim3(32), 0, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dv, out);
+  else if (dk == 128)
     launch_chained(gdn_recurrence_kernel<128>, dim3(grid), dim3(32), smem, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
   else
     launch_chained(gdn_recurrence_kernel<0>, dim3(grid), dim3(32), smem, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);
