@@ -164,6 +164,17 @@ gemv_q8_cols80_kernel(const int8_t *__restrict__ aq, const float *__restrict__ a
   int s = blockIdx.x;
   if (s < total_sets)
     load(resolve(s));
+  // Later sets of this CTA: ask for them in L2 while the kernel in front still runs.
+  if ((jobs.flags & kGemvPrefetchL2) && t < kSetRows) {
+    for (int later = s + gridDim.x; later < total_sets; later += gridDim.x) {
+      const Set c = resolve(later);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(c.wq + static_cast<size_t>(c.row0 + t) * K), "r"(K) : "memory");
+      if (t == 0)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(c.wd + static_cast<size_t>(c.row0) * NB),
+                     "r"(kSetRows * NB * 2)
+                     : "memory");
+    }
+  }
   // The weights are on their way; the input row belongs to the kernel in front.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint4 lo = reinterpret_cast<const uint4 *>(aq)[2 * kb];
