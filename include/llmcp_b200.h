@@ -124,7 +124,10 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
  *                         rows_per_warp 0 = choose.  flags: 1 = launch as a programmatic
  *                         dependent of the kernel in front (weights are requested while that
  *                         kernel still runs; x is read only after it has finished), 2 = also
- *                         prefetch the whole matrix into L2 first.
+ *                         prefetch into L2 what the launch reads after its first round of
+ *                         loads, 4 = feed the weights through shared-memory rings with bulk
+ *                         asynchronous copies (K = 2560, 4096, 9216; slower, for comparison),
+ *                         8 = use the row kernel where a block-column kernel would be chosen.
  *   llmcp_dev_gemm_q8   : M > 1 linear (Q8Matmul.cpp:143-289), integer dot products on dp4a.
  *   llmcp_dev_gemm_q8_tc: the same contraction on the tcgen05 tensor cores.  wd32 holds the
  *                         weight scales widened to f32, [N][K/32].  status (device int, may be
