@@ -297,3 +297,34 @@ def test_attention(golden):
         assert np.array_equal(out, oo), (S, pos, np.abs(f(out) - f(oo)).max())
     with pytest.raises(L.LlmcpError):
         L.ops.attention(qg, k, v, q_norm, k_norm, cos, sin, cache, cap, nh, nkv, hd, rot)  # past the cache
+
+
+@pytest.mark.parametrize("N,K", [(2560, 4096), (2560, 9216), (9216, 2560), (1024, 2560), (248, 4096)])
+def test_gemv_kernel_variants(N, K):
+    """The block-column, row and ring-fed decode GEMV kernels and the oracle agree bit for bit."""
+    import ctypes as C
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(N + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    packed = oracle.pack_q8_0_p4(w)
+    x = rand_bf16(rng, 1, K)
+    want = oracle.linear_q8(x, packed, N, y_bf16=False)[0]
+    lib = L.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    records = torch.from_numpy(packed).cuda()
+    wq = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    wd = torch.empty((N, K // 32), dtype=torch.float16, device="cuda")
+    assert lib.llmcp_dev_repack_q8(ptr(records), C.c_int64(N), C.c_int64(K), ptr(wq), ptr(wd), stream) == 0
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    aq = torch.empty(K, dtype=torch.int8, device="cuda")
+    scales = torch.empty(K // 32, dtype=torch.float32, device="cuda")
+    assert lib.llmcp_dev_act_quant(ptr(xd), 1, C.c_int64(1), C.c_int64(K), ptr(aq), ptr(scales), stream) == 0
+    for flags in (0, 1, 3, 4, 5, 8, 9):  # default kernels, dependent launch, L2 prefetch, ring, row kernel
+        y = torch.full((N,), float("nan"), dtype=torch.float32, device="cuda")
+        rc = lib.llmcp_dev_gemv_q8(ptr(aq), ptr(scales), C.c_int64(K), ptr(wq), ptr(wd), C.c_int64(N), ptr(y), 0, 0, 0,
+                                   flags, stream)
+        assert rc == 0, L.last_error()
+        torch.cuda.synchronize()
+        got = y.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"flags {flags}"
