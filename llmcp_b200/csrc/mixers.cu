@@ -424,67 +424,58 @@ __device__ __forceinline__ float conv_step(const uint16_t *__restrict__ x, const
   return bf16_to_f32(f32_to_bf16(__fmul_rn(acc, d_sigmoid(acc))));
 }
 
-// Warp roles: [0, nk) q heads, [nk, 2 nk) k heads (convolution, then the L2 norm with lane 0
-// adding the squares in order), then one warp per 128 value channels (convolution only), then
-// warps that compute beta and decay, one value head per lane.
-__global__ void __launch_bounds__(128)
+// CTA roles (dk threads each, one channel per thread): [0, nk) q heads, [nk, 2 nk) k heads
+// (convolution, then the L2 norm with thread 0 adding the squares in order), then one CTA per dk
+// value channels (convolution only), then one CTA that computes beta and decay, a value head per
+// thread.
+__global__ void __launch_bounds__(256)
 gdn_decode_front_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w, uint16_t *__restrict__ state,
                         int kernel, const uint16_t *__restrict__ a, const uint16_t *__restrict__ b,
                         const void *__restrict__ a_log, int a_log_dtype, const void *__restrict__ dt_bias,
                         int dt_dtype, int nk, int nv, int dk, int dv, int b_activated, float *__restrict__ qn,
                         float *__restrict__ kn, float *__restrict__ beta, float *__restrict__ decay,
                         uint16_t *__restrict__ conv_out) {
-  extern __shared__ float front_sm[]; // per warp: dk squares
+  extern __shared__ __align__(16) float front_sm[]; // dk squares
+  __shared__ float scale_sm;
   grid_dependency_sync(true); // the step kernel behind is placed now and fetches its state meanwhile
-  const int lane = threadIdx.x & 31;
-  const int warp_in_cta = threadIdx.x >> 5;
-  const int warp = blockIdx.x * (blockDim.x >> 5) + warp_in_cta;
+  const int t = threadIdx.x;
+  const int role = blockIdx.x;
   const int C = 2 * nk * dk + nv * dv;
-  const int value_warps = (nv * dv + 127) / 128;
-  if (warp < 2 * nk) {
-    const bool is_q = warp < nk;
-    const int head = is_q ? warp : warp - nk;
-    const int base = (is_q ? 0 : nk * dk) + head * dk;
-    float *sq = front_sm + warp_in_cta * dk;
-    float v[8]; // dk <= 256
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int d = lane + 32 * u;
-      if (d < dk) {
-        v[u] = conv_step(x, w, state, C, kernel, base + d);
-        sq[d] = __fmul_rn(v[u], v[u]);
-      }
-    }
-    __syncwarp();
-    float scale = 0.0f;
-    if (lane == 0) {
+  const int value_ctas = (nv * dv + dk - 1) / dk;
+  if (role < 2 * nk) {
+    const bool is_q = role < nk;
+    const int head = is_q ? role : role - nk;
+    const float v = conv_step(x, w, state, C, kernel, (is_q ? 0 : nk * dk) + head * dk + t);
+    front_sm[t] = __fmul_rn(v, v);
+    __syncthreads();
+    if (t == 0) {
       float sum = 0.0f;
-#pragma unroll 16
-      for (int d = 0; d < dk; ++d)
-        sum = __fadd_rn(sum, sq[d]);
-      scale = d_rsqrt(__fadd_rn(sum, 1.0e-6f));
+      for (int d = 0; d < dk; d += 16) { // dk % 16 == 0
+        float4 sq[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          sq[u] = *reinterpret_cast<const float4 *>(front_sm + d + 4 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          sum = __fadd_rn(sum, sq[u].x);
+          sum = __fadd_rn(sum, sq[u].y);
+          sum = __fadd_rn(sum, sq[u].z);
+          sum = __fadd_rn(sum, sq[u].w);
+        }
+      }
+      float scale = d_rsqrt(__fadd_rn(sum, 1.0e-6f));
       if (is_q)
         scale = __fmul_rn(scale, static_cast<float>(1.0 / sqrt(static_cast<double>(dk))));
+      scale_sm = scale;
     }
-    scale = __shfl_sync(0xffffffffu, scale, 0);
-    float *dst = (is_q ? qn : kn) + head * dk;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int d = lane + 32 * u;
-      if (d < dk)
-        dst[d] = __fmul_rn(v[u], scale);
-    }
-  } else if (warp < 2 * nk + value_warps) {
-    const int first = 2 * nk * dk + (warp - 2 * nk) * 128;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int c = first + lane + 32 * u;
-      if (c < C)
-        conv_out[c] = f32_to_bf16(conv_step(x, w, state, C, kernel, c));
-    }
+    __syncthreads();
+    (is_q ? qn : kn)[head * dk + t] = __fmul_rn(v, scale_sm);
+  } else if (role < 2 * nk + value_ctas) {
+    const int c = 2 * nk * dk + (role - 2 * nk) * dk + t;
+    if (c < C)
+      conv_out[c] = f32_to_bf16(conv_step(x, w, state, C, kernel, c));
   } else {
-    const int h = (warp - 2 * nk - value_warps) * 32 + lane;
-    if (h < nv) {
+    for (int h = t; h < nv; h += blockDim.x) {
       const float bv = bf16_to_f32(b[h]);
       beta[h] = b_activated ? bv : d_sigmoid(bv);
       // dt_bias is widened from bf16, A_log is read as f32 (LowerGatedDeltaNet.cpp:233-246).
@@ -597,8 +588,8 @@ cudaError_t launch_gdn_decode(const uint16_t *qkv, const uint16_t *conv_w, uint1
   float *kn = qn + nk * dk;
   float *beta = kn + nk * dk;
   float *decay = beta + nv;
-  const int warps = 2 * nk + (nv * dv + 127) / 128 + (nv + 31) / 32;
-  launch_chained(gdn_decode_front_kernel, dim3((warps + 3) / 4), dim3(128), 4 * dk * sizeof(float), stream, qkv, conv_w,
+  const int ctas = 2 * nk + (nv * dv + dk - 1) / dk + 1;
+  launch_chained(gdn_decode_front_kernel, dim3(ctas), dim3(dk), dk * sizeof(float), stream, qkv, conv_w,
                  conv_state, kernel, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, nk, nv, dk, dv, b_activated, qn, kn, beta,
                  decay, conv_out);
   launch_chained(gdn_decode_step_kernel<128>, dim3(nv), dim3(dv), (2 * 128 + dv) * sizeof(float), stream, conv_out, qn, kn,
