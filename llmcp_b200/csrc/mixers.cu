@@ -641,7 +641,17 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
   float inv = 0.0f;
   if (lane == 0) {
     float sum = 0.0f;
-    for (int d = 0; d < hd; ++d)
+    int d = 0;
+    for (; d + 16 <= hd; d += 16) { // sixteen squares are fetched, then added in order
+      float sq[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        sq[u] = tmp[d + u];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        sum = __fadd_rn(sum, sq[u]);
+    }
+    for (; d < hd; ++d)
       sum = __fadd_rn(sum, tmp[d]);
     inv = d_rsqrt(__fadd_rn(__fmul_rn(sum, __fdiv_rn(1.0f, static_cast<float>(hd))), 1.0e-6f));
   }
@@ -910,7 +920,8 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   const int64_t score_stride = max_position + S;
 
   const int64_t items = S * (nh + nkv);
-  launch_chained(attn_prepare_kernel, dim3(static_cast<unsigned>((items + 3) / 4)), dim3(128), 4 * hd * sizeof(float), stream, 
+  const int prepare_warps = items <= 64 ? 1 : 4; // decode: a CTA per head
+  launch_chained(attn_prepare_kernel, dim3(static_cast<unsigned>((items + prepare_warps - 1) / prepare_warps)), dim3(32 * prepare_warps), prepare_warps * hd * sizeof(float), stream, 
       qg, k, v, q_norm, k_norm, cos, sin, cache, position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn);
 
   const size_t smem = (static_cast<size_t>(kKeyTile) * (hd + 1) + static_cast<size_t>(group) * hd) * sizeof(float);
