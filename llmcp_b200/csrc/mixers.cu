@@ -738,6 +738,88 @@ __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16
   scores[(t * nh + kvh * group + g) * score_stride + start + j] = __fmul_rn(dot, scale);
 }
 
+// The same scores for a block of kScoreTokens query tokens per CTA (prefill): the key tile is
+// brought into shared memory once per block instead of once per token, and a thread advances the
+// dot products of four tokens together, reading its key row four values at a time.  Every dot
+// product is still the ascending-d chain  dot = dot + q[d] * k[d]  of the kernel above.
+// grid: (key tile, kv head, token block); block: group * 64 threads (query head x key).
+constexpr int kScoreTokens = 8;
+
+__global__ void __launch_bounds__(256)
+attn_scores_block_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
+                         const int64_t *__restrict__ position_ptr, int64_t S, int nh, int nkv, int hd, int64_t cap,
+                         int64_t score_stride, float *__restrict__ scores) {
+  extern __shared__ __align__(16) unsigned char att_sm[];
+  grid_dependency_sync();
+  const int64_t position = *position_ptr;
+  const int group = nh / nkv;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.z) * kScoreTokens;
+  const int tokens = static_cast<int>(min(static_cast<int64_t>(kScoreTokens), S - t0));
+  const int kvh = blockIdx.y;
+  const int64_t last_end = position + t0 + tokens; // keys the last token of the block sees
+  const int64_t start = static_cast<int64_t>(blockIdx.x) * kKeyTile;
+  if (start >= last_end)
+    return;
+  const int keys = static_cast<int>(min(static_cast<int64_t>(kKeyTile), last_end - start));
+  const int kstride = hd + 4; // floats per key row: 16-byte aligned, four banks apart
+  float *k_sm = reinterpret_cast<float *>(att_sm);  // [64][hd+4]
+  float *q_sm = k_sm + kKeyTile * kstride;          // [tokens][group][hd]
+  const uint16_t *kc = cache + (static_cast<int64_t>(kvh) * cap + start) * hd;
+  const int per_row = hd >> 3; // 16-byte pieces per key (hd % 8 == 0)
+  for (int i = threadIdx.x; i < kKeyTile * per_row; i += blockDim.x) {
+    const int row = i / per_row, piece = i - row * per_row;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (row < keys)
+      raw = reinterpret_cast<const uint4 *>(kc)[i];
+    float *dst = k_sm + row * kstride + piece * 8;
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      dst[2 * u] = __uint_as_float(w[u] << 16);
+      dst[2 * u + 1] = __uint_as_float(w[u] & 0xffff0000u);
+    }
+  }
+  for (int i = threadIdx.x; i < kScoreTokens * group * hd; i += blockDim.x) {
+    const int tb = i / (group * hd), rest = i - tb * group * hd;
+    q_sm[i] = tb < tokens ? bf16_to_f32(qn[((t0 + tb) * nh + kvh * group) * hd + rest]) : 0.0f;
+  }
+  __syncthreads();
+  const int j = threadIdx.x % kKeyTile;
+  const int g = threadIdx.x / kKeyTile;
+  if (g >= group)
+    return;
+  const float4 *kr = reinterpret_cast<const float4 *>(k_sm + j * kstride);
+  const float scale = __fdiv_rn(1.0f, __fsqrt_rn(static_cast<float>(hd)));
+#pragma unroll
+  for (int tb0 = 0; tb0 < kScoreTokens; tb0 += 4) {
+    if (tb0 >= tokens)
+      break;
+    const float4 *q0 = reinterpret_cast<const float4 *>(q_sm + ((tb0 + 0) * group + g) * hd);
+    const float4 *q1 = reinterpret_cast<const float4 *>(q_sm + ((tb0 + 1) * group + g) * hd);
+    const float4 *q2 = reinterpret_cast<const float4 *>(q_sm + ((tb0 + 2) * group + g) * hd);
+    const float4 *q3 = reinterpret_cast<const float4 *>(q_sm + ((tb0 + 3) * group + g) * hd);
+    float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+    for (int d4 = 0; d4 < (hd >> 2); ++d4) {
+      const float4 kv = kr[d4];
+      const float4 qv[4] = {q0[d4], q1[d4], q2[d4], q3[d4]};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        dot[u] = __fadd_rn(dot[u], __fmul_rn(qv[u].x, kv.x));
+        dot[u] = __fadd_rn(dot[u], __fmul_rn(qv[u].y, kv.y));
+        dot[u] = __fadd_rn(dot[u], __fmul_rn(qv[u].z, kv.z));
+        dot[u] = __fadd_rn(dot[u], __fmul_rn(qv[u].w, kv.w));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t t = t0 + tb0 + u;
+      if (tb0 + u < tokens && start + j < position + t + 1)
+        scores[(t * nh + kvh * group + g) * score_stride + start + j] = __fmul_rn(dot[u], scale);
+    }
+  }
+}
+
 // grid: (head, token); block: hd rounded up to a warp multiple.
 // Shared memory: the row's scores (turned into probabilities in place), then per key tile the
 // running maximum and the correction factor.  The maxima, corrections and probabilities are
@@ -937,9 +1019,24 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   }
   if (smem > 200 * 1024 || csmem > 200 * 1024)
     return cudaErrorInvalidValue; // about 50,000 cached positions
-  dim3 sgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
-  launch_chained(attn_scores_kernel, dim3(sgrid), dim3(group * kKeyTile), smem, stream, qn, cache, position_dev, nh, nkv, hd, cap,
-                                                               score_stride, scores);
+  const size_t block_smem = (static_cast<size_t>(kKeyTile) * (hd + 4) + static_cast<size_t>(kScoreTokens) * group * hd) * sizeof(float);
+  if (S >= 4 && (hd & 7) == 0 && group * kKeyTile <= 256 && block_smem <= 200 * 1024) {
+    static bool block_configured = false;
+    if (!block_configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_scores_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess)
+        return e;
+      block_configured = true;
+    }
+    dim3 bgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv,
+               static_cast<unsigned>((S + kScoreTokens - 1) / kScoreTokens));
+    launch_chained(attn_scores_block_kernel, dim3(bgrid), dim3(group * kKeyTile), block_smem, stream, qn, cache, position_dev, S,
+                   nh, nkv, hd, cap, score_stride, scores);
+  } else {
+    dim3 sgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
+    launch_chained(attn_scores_kernel, dim3(sgrid), dim3(group * kKeyTile), smem, stream, qn, cache, position_dev, nh, nkv, hd,
+                   cap, score_stride, scores);
+  }
   dim3 cgrid(nh, static_cast<unsigned>(S));
   launch_chained(attn_combine_kernel, dim3(cgrid), dim3((hd + 31) / 32 * 32), csmem, stream, scores, cache, qg, position_dev, nh, nkv, hd,
                                                                     cap, score_stride, out, q_out, s_out);
