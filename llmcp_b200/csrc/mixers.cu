@@ -966,6 +966,209 @@ __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint
   }
 }
 
+// The same weighted sum for a block of kCombineTokens query tokens of one head per CTA (prefill):
+// a value row is brought into shared memory once per block instead of once per token, and a
+// thread accumulates two head dimensions for all tokens of the block.  hd / 2 threads accumulate;
+// one more warp keeps the softmax denominators (lane tb walks token tb's probabilities in key
+// order, which every dimension thread used to repeat).  Per (token, dimension) the operations and
+// their order are those of the kernel above: correction at every 64-key tile, then
+// acc = acc + p * v key by key.
+constexpr int kCombineTokens = 8;
+constexpr int kBlockStages = 4;
+
+__global__ void __launch_bounds__(160)
+attn_combine_block_kernel(const float *__restrict__ scores, const uint16_t *__restrict__ cache,
+                          const uint16_t *__restrict__ qg, const int64_t *__restrict__ position_ptr, int64_t S, int nh,
+                          int nkv, int hd, int64_t cap, int64_t score_stride, int p_stride, uint16_t *__restrict__ out,
+                          int8_t *__restrict__ q_out, float *__restrict__ s_out) {
+  extern __shared__ __align__(16) float comb_sm[];
+  grid_dependency_sync(true);
+  const int64_t position = *position_ptr;
+  const int h = blockIdx.x;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.y) * kCombineTokens;
+  const int tokens = static_cast<int>(min(static_cast<int64_t>(kCombineTokens), S - t0));
+  const int kvh = h / (nh / nkv);
+  const int total0 = static_cast<int>(position + t0 + 1);       // keys the first token sees
+  const int total_last = total0 + tokens - 1;                   // keys the last token sees
+  const int tiles_max = (total_last + kKeyTile - 1) / kKeyTile;
+  const int tile_slots = (p_stride + kKeyTile - 1) / kKeyTile;
+  float *p_sm = comb_sm;                                         // [tokens][p_stride]
+  float *m_sm = p_sm + kCombineTokens * p_stride;                // [tokens][tile_slots]
+  float *c_sm = m_sm + kCombineTokens * tile_slots;              // [tokens][tile_slots]
+  float *sum_sm = c_sm + kCombineTokens * tile_slots;            // [tokens]
+  uint16_t *v_sm = reinterpret_cast<uint16_t *>(sum_sm + kCombineTokens);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int pairs = hd >> 1;
+  const int d = threadIdx.x;
+  const bool consumer = d < pairs;        // dimensions 2 d and 2 d + 1
+  const bool keeper = d >= pairs && lane < tokens; // the extra warp: lane tb keeps token tb's denominator
+
+  // probabilities of every token of the block (as in the one-token kernel)
+  for (int tb = 0; tb < tokens; ++tb) {
+    const float *srow = scores + ((t0 + tb) * nh + h) * score_stride;
+    for (int j = threadIdx.x; j < total0 + tb; j += blockDim.x)
+      p_sm[tb * p_stride + j] = srow[j];
+  }
+  __syncthreads();
+  for (int item = warp; item < tokens * tiles_max; item += warps) {
+    const int tb = item / tiles_max, tile = item - tb * tiles_max;
+    const int total = total0 + tb;
+    float m = -1.0e30f;
+    for (int j = tile * kKeyTile + lane; j < min(total, (tile + 1) * kKeyTile); j += 32)
+      m = fmaxf(m, p_sm[tb * p_stride + j]);
+    for (int o = 16; o > 0; o >>= 1)
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0)
+      m_sm[tb * tile_slots + tile] = m;
+  }
+  __syncthreads();
+  if (threadIdx.x < tokens) {
+    const int tb = threadIdx.x;
+    const int tiles = (total0 + tb + kKeyTile - 1) / kKeyTile;
+    float running = -1.0e30f;
+    for (int tile = 0; tile < tiles; ++tile) {
+      const float next = fmaxf(running, m_sm[tb * tile_slots + tile]);
+      c_sm[tb * tile_slots + tile] = __fsub_rn(running, next); // exponent of the correction, exp taken below
+      m_sm[tb * tile_slots + tile] = next;
+      running = next;
+    }
+  }
+  __syncthreads();
+  for (int tb = 0; tb < tokens; ++tb) {
+    const int total = total0 + tb;
+    const int tiles = (total + kKeyTile - 1) / kKeyTile;
+    for (int tile = threadIdx.x; tile < tiles; tile += blockDim.x)
+      c_sm[tb * tile_slots + tile] = d_exp(c_sm[tb * tile_slots + tile]);
+    for (int j = threadIdx.x; j < total; j += blockDim.x)
+      p_sm[tb * p_stride + j] = d_exp(__fsub_rn(p_sm[tb * p_stride + j], m_sm[tb * tile_slots + j / kKeyTile]));
+  }
+  __syncthreads();
+
+  const uint16_t *vbase = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd;
+  const int stage_elems = kValueTile * hd;
+  const int value_tiles = (total_last + kValueTile - 1) / kValueTile;
+  auto issue = [&](int tile) {
+    if (tile < value_tiles) {
+      const int rows = min(kValueTile, total_last - tile * kValueTile);
+      const uint16_t *src = vbase + static_cast<int64_t>(tile) * stage_elems;
+      uint16_t *dst = v_sm + (tile % kBlockStages) * stage_elems;
+      for (int i = threadIdx.x; i < (rows * hd) >> 3; i += blockDim.x) {
+        const uint32_t saddr = static_cast<uint32_t>(__cvta_generic_to_shared(dst + i * 8));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + i * 8) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc0[kCombineTokens], acc1[kCombineTokens];
+#pragma unroll
+  for (int tb = 0; tb < kCombineTokens; ++tb)
+    acc0[tb] = acc1[tb] = 0.0f;
+  float sum = 0.0f; // keeper lanes only
+  for (int tile = 0; tile < kBlockStages - 1; ++tile)
+    issue(tile);
+  for (int tile = 0; tile < value_tiles; ++tile) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kBlockStages - 2) : "memory");
+    __syncthreads(); // stage `tile` has landed for everyone; stage `tile - 1` is free again
+    issue(tile + kBlockStages - 1);
+    const int first = tile * kValueTile;
+    const int count = min(kValueTile, total_last - first);
+    if (consumer) {
+      const uint32_t *rows = reinterpret_cast<const uint32_t *>(v_sm + (tile % kBlockStages) * stage_elems) + d;
+      if ((first & (kKeyTile - 1)) == 0) {
+#pragma unroll
+        for (int tb = 0; tb < kCombineTokens; ++tb) {
+          if (tb < tokens && first < total0 + tb) {
+            const float correction = c_sm[tb * tile_slots + first / kKeyTile];
+            acc0[tb] = __fmul_rn(acc0[tb], correction);
+            acc1[tb] = __fmul_rn(acc1[tb], correction);
+          }
+        }
+      }
+      if (first + kValueTile <= total0 && tokens == kCombineTokens) {
+        // every key of the stage is visible to every token of the block
+#pragma unroll 2
+        for (int u4 = 0; u4 < kValueTile; u4 += 4) {
+          float v0[4], v1[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const uint32_t v2 = rows[(u4 + u) * pairs];
+            v0[u] = __uint_as_float(v2 << 16);
+            v1[u] = __uint_as_float(v2 & 0xffff0000u);
+          }
+#pragma unroll
+          for (int tb = 0; tb < kCombineTokens; ++tb) {
+            const float4 p4 = *reinterpret_cast<const float4 *>(p_sm + tb * p_stride + first + u4);
+            const float p[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              acc0[tb] = __fadd_rn(acc0[tb], __fmul_rn(p[u], v0[u]));
+              acc1[tb] = __fadd_rn(acc1[tb], __fmul_rn(p[u], v1[u]));
+            }
+          }
+        }
+      } else {
+        for (int u = 0; u < count; ++u) {
+          const uint32_t v2 = rows[u * pairs];
+          const float v0 = __uint_as_float(v2 << 16), v1 = __uint_as_float(v2 & 0xffff0000u);
+#pragma unroll
+          for (int tb = 0; tb < kCombineTokens; ++tb) {
+            if (tb < tokens && first + u < total0 + tb) {
+              const float p = p_sm[tb * p_stride + first + u];
+              acc0[tb] = __fadd_rn(acc0[tb], __fmul_rn(p, v0));
+              acc1[tb] = __fadd_rn(acc1[tb], __fmul_rn(p, v1));
+            }
+          }
+        }
+      }
+    } else if (keeper) {
+      const int tb = lane, total = total0 + tb;
+      if ((first & (kKeyTile - 1)) == 0 && first < total)
+        sum = __fmul_rn(sum, c_sm[tb * tile_slots + first / kKeyTile]);
+      const int mine = min(count, total - first);
+      for (int u = 0; u < mine; ++u)
+        sum = __fadd_rn(sum, p_sm[tb * p_stride + first + u]);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (keeper)
+    sum_sm[lane] = sum;
+  __syncthreads();
+  // gate, bf16, and the quantisation the following o_proj needs (Q8Decode.cpp:83-120): a 32-wide
+  // block is held by 16 neighbouring accumulating threads.
+#pragma unroll
+  for (int tb = 0; tb < kCombineTokens; ++tb) {
+    if (tb >= tokens)
+      break;
+    const int64_t t = t0 + tb;
+    const int64_t index = t * nh * hd + static_cast<int64_t>(h) * hd + 2 * d;
+    float r0 = 0.0f, r1 = 0.0f;
+    if (consumer) {
+      const float denominator = sum_sm[tb];
+      const uint32_t gate2 = *reinterpret_cast<const uint32_t *>(qg + t * nh * 2 * hd + static_cast<int64_t>(h) * 2 * hd + hd + 2 * d);
+      const uint16_t b0 = f32_to_bf16(__fmul_rn(__fdiv_rn(acc0[tb], denominator), d_sigmoid(__uint_as_float(gate2 << 16))));
+      const uint16_t b1 = f32_to_bf16(__fmul_rn(__fdiv_rn(acc1[tb], denominator), d_sigmoid(__uint_as_float(gate2 & 0xffff0000u))));
+      *reinterpret_cast<uint32_t *>(out + index) = static_cast<uint32_t>(b0) | (static_cast<uint32_t>(b1) << 16);
+      r0 = bf16_to_f32(b0);
+      r1 = bf16_to_f32(b1);
+    }
+    if (q_out) { // hd % 32 == 0
+      float amax = fmaxf(fabsf(r0), fabsf(r1));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float scale = __fdiv_rn(amax, 127.0f);
+      const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
+      if (consumer) {
+        const uint32_t q0 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(r0, inv))) & 0xffu;
+        const uint32_t q1 = static_cast<uint32_t>(__float2int_rn(__fmul_rn(r1, inv))) & 0xffu;
+        *reinterpret_cast<uint16_t *>(q_out + index) = static_cast<uint16_t>(q0 | (q1 << 8));
+        if ((d & 15) == 0)
+          s_out[index >> 5] = scale;
+      }
+    }
+  }
+}
+
 static size_t combine_smem_bytes(int64_t score_stride, int hd) {
   const size_t tiles = static_cast<size_t>((score_stride + kKeyTile - 1) / kKeyTile);
   size_t bytes = ((static_cast<size_t>(score_stride) + 3) / 4 * 4 + 2 * tiles) * sizeof(float);
@@ -1037,9 +1240,27 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
     launch_chained(attn_scores_kernel, dim3(sgrid), dim3(group * kKeyTile), smem, stream, qn, cache, position_dev, nh, nkv, hd,
                    cap, score_stride, scores);
   }
-  dim3 cgrid(nh, static_cast<unsigned>(S));
-  launch_chained(attn_combine_kernel, dim3(cgrid), dim3((hd + 31) / 32 * 32), csmem, stream, scores, cache, qg, position_dev, nh, nkv, hd,
-                                                                    cap, score_stride, out, q_out, s_out);
+  // Prefill: eight tokens of a head per CTA when their probabilities fit in shared memory.
+  const int p_stride = static_cast<int>((score_stride + 3) / 4 * 4);
+  const int tile_slots = (p_stride + kKeyTile - 1) / kKeyTile;
+  const size_t block_csmem = (static_cast<size_t>(kCombineTokens) * (p_stride + 2 * tile_slots + 1)) * sizeof(float) + 16 +
+                             static_cast<size_t>(kBlockStages) * kValueTile * hd * sizeof(uint16_t);
+  if (S >= 4 && hd == 256 && block_csmem <= 200 * 1024) {
+    static bool block_configured = false;
+    if (!block_configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_combine_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess)
+        return e;
+      block_configured = true;
+    }
+    dim3 bgrid(nh, static_cast<unsigned>((S + kCombineTokens - 1) / kCombineTokens));
+    launch_chained(attn_combine_block_kernel, dim3(bgrid), dim3(hd / 2 + 32), block_csmem, stream, scores, cache, qg, position_dev,
+                   S, nh, nkv, hd, cap, score_stride, p_stride, out, q_out, s_out);
+  } else {
+    dim3 cgrid(nh, static_cast<unsigned>(S));
+    launch_chained(attn_combine_kernel, dim3(cgrid), dim3((hd + 31) / 32 * 32), csmem, stream, scores, cache, qg, position_dev, nh,
+                   nkv, hd, cap, score_stride, out, q_out, s_out);
+  }
   return cudaGetLastError();
 }
 
