@@ -199,7 +199,12 @@ cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int
   if (q && H % kBlock != 0)
     return cudaErrorInvalidValue;
   if (H % kBlock == 0 && H <= 16384) {
-    const int threads = std::min(1024, (H / 4 + 31) / 32 * 32);
+    // One row: a thread per four elements.  Many rows (prefill): 256-thread CTAs, so that eight
+    // rows per SM run their serial sums side by side.
+    // (a thread holds at most four quads, so long rows still get more threads)
+    const int quads = H / 4;
+    const int threads = M >= 64 ? std::min(1024, std::max(256, ((quads + 3) / 4 + 31) / 32 * 32))
+                                : std::min(1024, (quads + 31) / 32 * 32);
     launch_chained(rms_norm_vec4_kernel, dim3(static_cast<unsigned>(M)), dim3(threads), H * sizeof(float), stream, 
         a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s);
     return cudaGetLastError();
