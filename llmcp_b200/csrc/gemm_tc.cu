@@ -277,17 +277,20 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
       const int s = (kb / kStageBlocks) % kStages, j = kb % kStageBlocks;
       const float a_scale = Shared::a_scale(base, s)[j * kTileM + row];
       const float4 *w_scale = reinterpret_cast<const float4 *>(Shared::b_scale(base, s) + j * kTileN + half * 64);
+      // Both halves of this thread's columns are requested together and the buffer is handed
+      // back before any arithmetic: the tensor-memory latency is paid once per block and the
+      // MMA of a later block can reuse the buffer while this one is still being folded in.
+      int32_t v[2][32];
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kTileN + half * 64;
+      tmem_load32(taddr, v[0]);
+      tmem_load32(taddr + 32, v[1]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&bars->tempty[buf]);
 #pragma unroll
       for (int chunk = 0; chunk < 2; ++chunk) {
-        int32_t v[32];
-        tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kTileN + half * 64 + chunk * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (chunk == 1) { // both halves of this thread's columns are in registers: release the buffer
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0)
-            mbar_arrive(&bars->tempty[buf]);
-        }
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const float4 w4 = w_scale[chunk * 8 + g];
@@ -295,7 +298,7 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int c = chunk * 32 + g * 4 + u;
-            acc[c] = __fmaf_rn(static_cast<float>(v[g * 4 + u]), __fmul_rn(a_scale, wv[u]), acc[c]);
+            acc[c] = __fmaf_rn(static_cast<float>(v[chunk][g * 4 + u]), __fmul_rn(a_scale, wv[u]), acc[c]);
           }
         }
         if (dots_out && gm < M) {
@@ -303,7 +306,7 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
           for (int u = 0; u < 32; ++u) {
             const int gn = n0 + half * 64 + chunk * 32 + u;
             if (gn < N)
-              dots_out[(static_cast<size_t>(gm) * N + gn) * nb + kb] = v[u];
+              dots_out[(static_cast<size_t>(gm) * N + gn) * nb + kb] = v[chunk][u];
           }
         }
       }
