@@ -7,13 +7,15 @@
 // chain runs on the CUDA cores in ascending block order: the result is bit-identical to the
 // GEMV and to the CPU order of operations.
 //
-// One CTA per 128 x 128 output tile, 384 threads:
+// One CTA per 128 x 128 output tile, 640 threads:
 //   warps 0-2  loaders: cp.async 16-byte pieces of the int8 operands into a ring of
 //              shared-memory stages (4 blocks = 128 bytes of K per row, 128-byte swizzle,
 //              K-major, the layout the MMA's matrix descriptors name), plus the f32 scales;
 //   warp  3    one lane issues the MMAs: block kb of a stage -> tensor-memory buffer kb % 4;
-//   warps 4-11 epilogue: tcgen05.ld the buffer (thread = row, 64 columns each), hand the
-//              buffer back, then cvt / fmul / fma per element.
+//   warps 4-19 epilogue: tcgen05.ld the buffer (thread = row, 32 columns each: four lane
+//              quarters x four column quarters), hand the buffer back, then cvt / fmul / fma per
+//              element.  Sixteen warps rather than eight: the loop is a chain of waits (barrier,
+//              tensor-memory load) and more warps in different phases keep the issue slots busy.
 // Hand-offs are mbarriers; every wait is bounded and a timed-out wait raises an abort flag
 // that all roles observe, so a protocol error ends the kernel with an error code instead of
 // hanging it.  Tensor memory (512 columns) is allocated by warp 0 and always released.
@@ -33,8 +35,8 @@ constexpr int kTmemBuffers = 4;               // 4 x 128 columns
 constexpr int kLoaderThreads = 96;
 constexpr int kMmaWarp = 3;
 constexpr int kEpilogueWarp0 = 4;
-constexpr int kEpilogueThreads = 256;
-constexpr int kThreads = 384;
+constexpr int kEpilogueThreads = 512;
+constexpr int kThreads = 640;
 constexpr uint32_t kSpinLimit = 1u << 26;     // bounded waits (about a second)
 
 constexpr int kOperandBytes = kTileM * kStageK;                 // 16 KB per operand per stage
@@ -140,9 +142,9 @@ namespace {
 
 struct Barriers {
   uint64_t full[kStages];          // stage landed in shared memory (96 loader arrivals)
-  uint64_t empty[kStages];         // stage no longer needed: MMA done (1) + epilogue warps (8)
+  uint64_t empty[kStages];         // stage no longer needed: MMA done (1) + every epilogue warp
   uint64_t tfull[kTmemBuffers];    // a block's dot products are in the tensor-memory buffer
-  uint64_t tempty[kTmemBuffers];   // the buffer has been read by all 8 epilogue warps
+  uint64_t tempty[kTmemBuffers];   // the buffer has been read by all epilogue warps
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -260,12 +262,12 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
   } else if (warp >= kEpilogueWarp0) {
     // ---- epilogue ---------------------------------------------------------------------------
     const int quarter = warp & 3;                   // tensor-memory lanes 32*quarter .. +31
-    const int half = (warp - kEpilogueWarp0) >> 2;  // columns 64*half .. +63
+    const int colq = (warp - kEpilogueWarp0) >> 2;  // columns 32*colq .. +31
     const int row = quarter * 32 + lane;
     const int gm = m0 + row;
-    float acc[64];
+    float acc[32];
 #pragma unroll
-    for (int c = 0; c < 64; ++c)
+    for (int c = 0; c < 32; ++c)
       acc[c] = 0.0f;
     bool ok = true;
     for (int kb = 0; kb < nb && ok; ++kb) {
@@ -276,38 +278,30 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
       tc_fence_after();
       const int s = (kb / kStageBlocks) % kStages, j = kb % kStageBlocks;
       const float a_scale = Shared::a_scale(base, s)[j * kTileM + row];
-      const float4 *w_scale = reinterpret_cast<const float4 *>(Shared::b_scale(base, s) + j * kTileN + half * 64);
-      // Both halves of this thread's columns are requested together and the buffer is handed
-      // back before any arithmetic: the tensor-memory latency is paid once per block and the
-      // MMA of a later block can reuse the buffer while this one is still being folded in.
-      int32_t v[2][32];
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kTileN + half * 64;
-      tmem_load32(taddr, v[0]);
-      tmem_load32(taddr + 32, v[1]);
+      const float4 *w_scale = reinterpret_cast<const float4 *>(Shared::b_scale(base, s) + j * kTileN + colq * 32);
+      // The buffer is handed back before any arithmetic, so that the MMA of a later block can
+      // reuse it while this one is still being folded in.
+      int32_t v[32];
+      tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kTileN + colq * 32, v);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&bars->tempty[buf]);
 #pragma unroll
-      for (int chunk = 0; chunk < 2; ++chunk) {
+      for (int g = 0; g < 8; ++g) {
+        const float4 w4 = w_scale[g];
+        const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 w4 = w_scale[chunk * 8 + g];
-          const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+        for (int u = 0; u < 4; ++u)
+          acc[g * 4 + u] = __fmaf_rn(static_cast<float>(v[g * 4 + u]), __fmul_rn(a_scale, wv[u]), acc[g * 4 + u]);
+      }
+      if (dots_out && gm < M) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = chunk * 32 + g * 4 + u;
-            acc[c] = __fmaf_rn(static_cast<float>(v[chunk][g * 4 + u]), __fmul_rn(a_scale, wv[u]), acc[c]);
-          }
-        }
-        if (dots_out && gm < M) {
-#pragma unroll
-          for (int u = 0; u < 32; ++u) {
-            const int gn = n0 + half * 64 + chunk * 32 + u;
-            if (gn < N)
-              dots_out[(static_cast<size_t>(gm) * N + gn) * nb + kb] = v[chunk][u];
-          }
+        for (int u = 0; u < 32; ++u) {
+          const int gn = n0 + colq * 32 + u;
+          if (gn < N)
+            dots_out[(static_cast<size_t>(gm) * N + gn) * nb + kb] = v[u];
         }
       }
       if (j == kStageBlocks - 1 || kb == nb - 1) { // done with this stage's scales
@@ -318,8 +312,8 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
     }
     if (ok && gm < M) {
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const int gn = n0 + half * 64 + g * 8;
+      for (int g = 0; g < 4; ++g) {
+        const int gn = n0 + colq * 32 + g * 8;
         if (gn < N) { // N is a multiple of 8, so a group of eight is entirely inside or outside
           float o[8];
 #pragma unroll
