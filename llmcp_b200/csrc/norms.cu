@@ -6,7 +6,10 @@
 // (LowerToLinalg.cpp:251-262, DecodeNormalization.cpp:96-105).  In the default, exact
 // mode one thread adds the squares in that order; every other step is elementwise.
 
+#include <cstdlib>
+
 #include "kernels.h"
+#include "ordered_sum.cuh"
 
 namespace llmcp_b200 {
 
@@ -86,9 +89,10 @@ __global__ void __launch_bounds__(1024)
 rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, int H,
                      const void *__restrict__ w, int w_dtype, float eps, int zero_centered,
                      uint16_t *__restrict__ sum_out, uint16_t *__restrict__ y, int8_t *__restrict__ q,
-                     float *__restrict__ s) {
+                     float *__restrict__ s, int block_sum) {
   extern __shared__ __align__(16) float vrow_sm[]; // squares
   __shared__ float rstd_sm;
+  __shared__ OrderedSumScratch sum_scratch;
   const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
   const int quads = H >> 2;
   const int per_thread = (quads + blockDim.x - 1) / blockDim.x; // 1 for H <= 4096
@@ -135,7 +139,22 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (block_sum && per_thread == 1) {
+    // The serial sum of the squares (the reference's order), evaluated by the whole block: the
+    // same value bit for bit, in fewer dependent steps than the chain below.
+    float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    bool bad = false;
+    if (static_cast<int>(threadIdx.x) < quads) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        sq[u] = __fmul_rn(x[0][u], x[0][u]);
+        bad |= !(sq[u] <= 3.402823466e38f); // infinity or NaN
+      }
+    }
+    const float sum = block_ordered_sum(sq, vrow_sm, H, bad, sum_scratch);
+    if (threadIdx.x == 0)
+      rstd_sm = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(H)), eps));
+  } else if (threadIdx.x == 0) {
     // One dependent chain of H adds (the reference's order); 32 squares are fetched, then added.
     float sum = 0.0f;
     for (int d = 0; d < H; d += 32) {
@@ -205,8 +224,15 @@ cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int
     const int quads = H / 4;
     const int threads = M >= 64 ? std::min(1024, std::max(256, ((quads + 3) / 4 + 31) / 32 * 32))
                                 : std::min(1024, (quads + 31) / 32 * 32);
+    // Few rows: the sum of squares is evaluated by the whole block (LLMCP_B200_ORDERED_SUM=0: by
+    // one thread).  Many rows keep the one-thread chain: eight rows per SM hide its latency.
+    static const bool block_sum_enabled = [] {
+      const char *flag = std::getenv("LLMCP_B200_ORDERED_SUM");
+      return !(flag && flag[0] == '0');
+    }();
+    const int block_sum = block_sum_enabled && M < 64 && threads * 4 >= H ? 1 : 0;
     launch_chained(rms_norm_vec4_kernel, dim3(static_cast<unsigned>(M)), dim3(threads), H * sizeof(float), stream, 
-        a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s);
+        a, b, H, w, w_dtype, eps, zero_centered, sum_out, y, q, s, block_sum);
     return cudaGetLastError();
   }
   launch_chained(rms_norm_kernel, dim3(static_cast<unsigned>(M)), dim3(256), 2 * H * sizeof(float), stream, 

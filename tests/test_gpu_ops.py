@@ -189,13 +189,17 @@ def adversarial_rows(rng, M, H):
 
 @pytest.mark.parametrize("H", [2560, 4096, 1024, 96, 8192])
 def test_rms_norm_sum_order(H):
-    """The sum of squares is taken in the reference's serial order whatever the data."""
+    """The sum of squares is the reference's serial sum whatever the data, both from the
+    one-thread chain and from the block-wide evaluation."""
     rng = np.random.default_rng(H)
     x = adversarial_rows(rng, 600, H)
     w = rand_bf16(rng, H, scale=0.1)
     with np.errstate(all="ignore"):
         want = oracle.rms_norm(x, w)
-        got = L.ops.rms_norm(x, w)
+        got = L.ops.rms_norm(x, w)  # many rows: one thread per row adds the squares
+        # few rows per call: the whole block evaluates the same serial sum
+        few = np.concatenate([L.ops.rms_norm(x[i:i + 48], w) for i in range(0, len(x), 48)])
+    assert np.array_equal(few, got), np.argwhere((few != got).any(axis=1)).ravel()[:10]
     # NaN results (rows holding an infinity) are compared as NaN: the payload is the processor's.
     is_nan = lambda v: (v & 0x7fff) > 0x7f80
     same = (got == want) | (is_nan(got) & is_nan(want))
