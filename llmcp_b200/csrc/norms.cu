@@ -139,6 +139,7 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
     }
   }
   __syncthreads();
+  float rstd;
   if (block_sum && per_thread == 1) {
     // The serial sum of the squares (the reference's order), evaluated by the whole block: the
     // same value bit for bit, in fewer dependent steps than the chain below.
@@ -151,29 +152,32 @@ rms_norm_vec4_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
         bad |= !(sq[u] <= 3.402823466e38f); // infinity or NaN
       }
     }
-    const float sum = block_ordered_sum(sq, vrow_sm, H, bad, sum_scratch);
-    if (threadIdx.x == 0)
-      rstd_sm = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(H)), eps));
-  } else if (threadIdx.x == 0) {
-    // One dependent chain of H adds (the reference's order); 32 squares are fetched, then added.
-    float sum = 0.0f;
-    for (int d = 0; d < H; d += 32) {
-      float4 t[8];
+    const float mean_over = static_cast<float>(H);
+    rstd = block_ordered_sum(sq, vrow_sm, H, bad, sum_scratch, [mean_over, eps](float sum) {
+      return d_rsqrt(__fadd_rn(__fdiv_rn(sum, mean_over), eps));
+    });
+  } else {
+    if (threadIdx.x == 0) {
+      // One dependent chain of H adds (the reference's order); 32 squares are fetched, then added.
+      float sum = 0.0f;
+      for (int d = 0; d < H; d += 32) {
+        float4 t[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        t[u] = *reinterpret_cast<const float4 *>(vrow_sm + d + 4 * u);
+        for (int u = 0; u < 8; ++u)
+          t[u] = *reinterpret_cast<const float4 *>(vrow_sm + d + 4 * u);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        sum = __fadd_rn(sum, t[u].x);
-        sum = __fadd_rn(sum, t[u].y);
-        sum = __fadd_rn(sum, t[u].z);
-        sum = __fadd_rn(sum, t[u].w);
+        for (int u = 0; u < 8; ++u) {
+          sum = __fadd_rn(sum, t[u].x);
+          sum = __fadd_rn(sum, t[u].y);
+          sum = __fadd_rn(sum, t[u].z);
+          sum = __fadd_rn(sum, t[u].w);
+        }
       }
+      rstd_sm = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(H)), eps));
     }
-    rstd_sm = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(H)), eps));
+    __syncthreads();
+    rstd = rstd_sm;
   }
-  __syncthreads();
-  const float rstd = rstd_sm;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     if (r >= per_thread)
@@ -220,10 +224,12 @@ cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int
   if (H % kBlock == 0 && H <= 16384) {
     // One row: a thread per four elements.  Many rows (prefill): 256-thread CTAs, so that eight
     // rows per SM run their serial sums side by side.
-    // (a thread holds at most four quads, so long rows still get more threads)
+    // (a thread holds at most four quads, so long rows still get more threads).  Few rows get one
+    // warp more where 1024 threads allow: it holds no elements and adds the head of the sum of
+    // squares while the others scan (block_ordered_sum).
     const int quads = H / 4;
     const int threads = M >= 64 ? std::min(1024, std::max(256, ((quads + 3) / 4 + 31) / 32 * 32))
-                                : std::min(1024, (quads + 31) / 32 * 32);
+                                : std::min(1024, (quads + 31) / 32 * 32 + 32);
     // Few rows: the sum of squares is evaluated by the whole block (LLMCP_B200_ORDERED_SUM=0: by
     // one thread).  Many rows keep the one-thread chain: eight rows per SM hide its latency.
     static const bool block_sum_enabled = [] {

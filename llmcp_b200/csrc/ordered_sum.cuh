@@ -3,23 +3,27 @@
 // reference's rms_norm reduction, DecodeNormalization.cpp:96-105), in fewer dependent steps.
 //
 // While the running sum stays inside one binade [2^e, 2^(e+1)) it is an integer count S of
-// u = 2^(e-23), and  RN(s + p) = u * RNE(S + p/u):  the term contributes floor(p/u), plus one if
-// its remainder is above u/2, plus (on an exact tie) whatever makes the new count even, which
-// depends on the parity of S alone.  A run of terms in one binade is therefore summarised by two
-// integers, its total for an even and for an odd count on entry, and summaries compose
-// associatively.
+// u = 2^(e-23), 2^23 <= S < 2^24, and  RN(s + p) = u * RNE(S + p/u).  What the addition adds to
+// the count depends on S only through its parity (an exact tie goes to the even count).  So a
+// stretch of terms in one binade is summarised by two integers, what it adds for an even and for
+// an odd count on entry, and summaries compose associatively.
+//
+// The two integers of a quad of terms come from floating-point additions themselves: with the
+// terms scaled by 1/u (exact, a power of two), the chain  2^23 + p0/u + p1/u + ...  in f32 makes
+// the same rounding decisions as the real sum from an even count, and the chain from 2^23 + 1
+// those from an odd count, as long as neither reaches 2^24.
 //
 // Which binade the sum is in at each term is predicted from an approximate parallel prefix sum
 // (any order; it differs from the serial sum by far less than the 2^-10 margin used).  Quads of
-// terms that lie safely inside one binade are classified for it and summarised; consecutive
-// quads of one binade are composed by a segmented warp scan into runs.  Quads near a power of
-// two, and the first 64 terms (where the sum still doubles every few additions), stay serial.
-// One thread then stitches the pieces in order: real additions for the serial quads, one integer
-// addition per run.  Every prediction is verified on the way (the sum's exponent at the start of
-// a run, no carry into the next binade at its end); if one fails, or the terms are not all
-// finite, or the sum is zero or subnormal, the plain serial loop produces the result.  The
-// result is therefore the serial sum bit for bit in every case; the prediction only decides how
-// fast it is obtained.
+// terms that lie safely inside one binade are summarised for it; consecutive quads of one binade
+// are composed by a segmented warp scan into runs.  Quads near a power of two, and the first 64
+// terms (where the sum still doubles every few additions), stay serial.  One thread then
+// stitches the pieces in order: four real additions for a serial quad, one integer addition to
+// the sum's bit pattern for a run.  Every prediction is verified on the way (the sum's exponent
+// at the start of a run, no carry into the next binade at its end); if one fails, or the terms
+// are not all finite, or the sum is zero or tiny, the plain serial loop produces the result.
+// The result is therefore the serial sum bit for bit in every case; the prediction only decides
+// how fast it is obtained.
 #pragma once
 
 #include "common.cuh"
@@ -27,52 +31,28 @@
 namespace llmcp_b200 {
 
 constexpr int kOrderedMaxWarps = 32;
-constexpr int kOrderedMaxEntries = 96; // more runs than this: the plain chain is used
+constexpr int kOrderedMaxEntries = 96; // more pieces than this: the plain chain is used
+constexpr int kOrderedChunk = 8;       // entries the stitching thread fetches at a time
 
+// One piece of the sum per entry, in order.  A run of quads in one binade: x = 2^31 | binade
+// (biased exponent), y / z = what it adds to an even / odd count; x = 2^31 alone is padding
+// (adds nothing).  A serial quad: its four terms as f32 bits (sign bit clear).
 struct OrderedSumScratch {
   float warp_total[kOrderedMaxWarps];
   int run_count[kOrderedMaxWarps];
-  uint4 entries[kOrderedMaxEntries]; // flat, in order.  x: binade (biased exponent) or -1 serial quad; y: even; z: odd; w: quad
+  uint4 entries[kOrderedMaxEntries + kOrderedChunk];
   float result;
 };
 
+
 namespace ordered_sum {
 
-constexpr uint32_t kLimit = 1u << 24;
-constexpr uint32_t kSat = 1u << 26;
-constexpr int kHeadQuads = 16; // the first 64 terms are added serially
+constexpr int kHeadQuads = 16;               // the first 64 terms are added serially
+constexpr uint32_t kSat = 1u << 26;          // a total this large fails the carry check anyway
+constexpr uint32_t kRun = 0x80000000u;
+constexpr uint32_t kEvenStart = 0x4b000000u; // 2^23 as f32 bits
+constexpr uint32_t kOddStart = 0x4b000001u;  // 2^23 + 1
 
-struct Term {
-  uint32_t count;
-  int round; // 0 down/exact, 1 up, 2 tie
-};
-
-__device__ __forceinline__ Term classify(float p, int lsb) {
-  const uint32_t b = __float_as_uint(p);
-  const int exponent = static_cast<int>(b >> 23);
-  const bool normal = exponent != 0;
-  const uint32_t m = (b & 0x7fffffu) | (normal ? 0x800000u : 0u);
-  const int p_lsb = normal ? exponent - 150 : -149;
-  const int shift = lsb - p_lsb;
-  // shift <= 0: the term is a multiple of the unit; 1..31: split it; >= 32: it vanishes
-  const int right = min(max(shift, 0), 31), left = min(max(-shift, 0), 3);
-  const uint32_t whole = shift > 0 ? (shift < 32 ? m >> right : 0u) : (left > 2 ? kSat : m << left);
-  const uint32_t rest = (shift > 0 && shift < 32) ? (m & ((1u << right) - 1u)) : 0u;
-  const uint32_t half = (shift > 0 && shift < 32) ? (1u << (right - 1)) : 1u;
-  Term t;
-  t.count = m == 0u ? 0u : whole;
-  t.round = (m == 0u || rest < half) ? 0 : (rest > half ? 1 : 2);
-  return t;
-}
-__device__ __forceinline__ uint32_t increment(Term t, uint32_t parity) {
-  return t.count + (t.round == 1 ? 1u : (t.round == 2 ? ((parity + t.count) & 1u) : 0u));
-}
-__device__ __forceinline__ uint32_t saturate(uint32_t v) { return v < kSat ? v : kSat; }
-__device__ __forceinline__ void compose(uint32_t a_even, uint32_t a_odd, uint32_t b_even, uint32_t b_odd,
-                                        uint32_t &even, uint32_t &odd) {
-  even = saturate(a_even + ((a_even & 1u) ? b_odd : b_even));
-  odd = saturate(a_odd + (((1u + a_odd) & 1u) ? b_odd : b_even));
-}
 __device__ __forceinline__ float serial(const float *p_sm, int from, int to, float s) {
   int i = from;
   for (; i + 32 <= to; i += 32) {
@@ -93,136 +73,160 @@ __device__ __forceinline__ float serial(const float *p_sm, int from, int to, flo
   return s;
 }
 
+// One entry applied to the running sum, without branches: both forms are evaluated and one is
+// kept.  `wrong` collects failed predictions.
+__device__ __forceinline__ float apply(float s, const uint4 e, uint32_t &wrong) {
+  const uint32_t bits = __float_as_uint(s);
+  const uint32_t next = bits + ((bits & 1u) ? e.z : e.y);
+  const float added = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, __uint_as_float(e.x)), __uint_as_float(e.y)),
+                                          __uint_as_float(e.z)), __uint_as_float(e.w));
+  wrong |= e.x > kRun ? (((bits >> 23) ^ (e.x & 0x7fffffffu)) | ((next ^ bits) >> 23)) : 0u;
+  return e.x >= kRun ? __uint_as_float(next) : added;
+}
+
 } // namespace ordered_sum
 
 // Thread t holds terms [4t, 4t+4) in p (zeros beyond n); p_sm holds all n terms (16-byte aligned,
-// visible to the block).  n % 4 == 0, blockDim.x * 4 >= n.  Every thread calls; all get the sum.
+// visible to the block).  n % 4 == 0, blockDim.x * 4 >= n, blockDim.x a multiple of 32.  Every
+// thread calls; all get finish(sum), which one thread evaluates.  If the block's last warp holds
+// no terms it stays out of the other warps' barriers (which then use barrier 1): one of its
+// threads adds the first 64 terms meanwhile, and stitches.  The caller synchronises the block
+// before it reuses `sc`.
+template <typename Finish>
 __device__ float block_ordered_sum(const float (&p)[4], const float *p_sm, int n, bool any_bad,
-                                   OrderedSumScratch &sc) {
+                                   OrderedSumScratch &sc, Finish finish) {
   using namespace ordered_sum;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int warps = (blockDim.x + 31) >> 5;
   const int quads = n >> 2;
-  const bool active = tid < quads;
-  // approximate prefix sums (any order): they only predict where the sum changes binade
-  const float q = active ? (p[0] + p[1]) + (p[2] + p[3]) : 0.0f;
-  float incl = q;
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const float o = __shfl_up_sync(0xffffffffu, incl, d);
-    if (lane >= d)
-      incl += o;
-  }
-  if (lane == 31)
-    sc.warp_total[warp] = incl;
-  const bool serial_only = __syncthreads_or(any_bad ? 1 : 0) != 0;
-  float base;
-  {
-    const float mine = lane < warps ? sc.warp_total[lane] : 0.0f; // warps <= 32
-    float scan = mine;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const float o = __shfl_up_sync(0xffffffffu, scan, d);
-      if (lane >= d)
-        scan += o;
-    }
-    base = __shfl_sync(0xffffffffu, scan - mine, warp);
-  }
-  const float lo = base + (incl - q), hi = base + incl;
-  // kind: -2 head or inactive (no entry), -1 serial quad, else the binade (biased exponent)
-  int key = -2;
-  uint32_t even = 0u, odd = 0u;
-  if (active && tid >= kHeadQuads) {
-    key = -1;
-    const uint32_t e_lo = __float_as_uint(lo * 0.9990234375f) >> 23;  // 1 - 2^-10
-    const uint32_t e_hi = __float_as_uint(hi * 1.0009765625f) >> 23;  // 1 + 2^-10
-    if (lo > 0.0f && e_lo == e_hi && e_lo >= 1u && e_lo < 254u) {
-      key = static_cast<int>(e_lo);
-      const int lsb = key - 150;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const Term t = classify(p[u], lsb);
-        even = saturate(even + increment(t, even & 1u));
-        odd = saturate(odd + increment(t, (1u + odd) & 1u));
-      }
-    }
-  }
-  // runs inside the warp: consecutive clean quads of one binade; every serial quad is its own run
-  const int prev_key = __shfl_up_sync(0xffffffffu, key, 1);
-  const bool starts = key != -2 && (lane == 0 || key == -1 || prev_key != key);
-  const uint32_t start_mask = __ballot_sync(0xffffffffu, starts);
-  const int run = __popc(start_mask & (0xffffffffu >> (31 - lane))) - 1; // index of my run (if key != -2)
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const uint32_t o_even = __shfl_up_sync(0xffffffffu, even, d);
-    const uint32_t o_odd = __shfl_up_sync(0xffffffffu, odd, d);
-    const int o_run = __shfl_up_sync(0xffffffffu, run, d);
-    const int o_key = __shfl_up_sync(0xffffffffu, key, d);
-    if (lane >= d && key >= 0 && o_key == key && o_run == run)
-      compose(o_even, o_odd, even, odd, even, odd);
-  }
-  const int next_run = __shfl_down_sync(0xffffffffu, run, 1);
-  const int next_key = __shfl_down_sync(0xffffffffu, key, 1);
-  const bool tail = key != -2 && (lane == 31 || next_key == -2 || next_run != run);
-  if (lane == 0)
-    sc.run_count[warp] = __popc(start_mask);
-  __syncthreads();
-  // every run's tail lane writes its entry at the run's place in the flat, ordered list
-  int offset, total_runs;
-  {
-    int mine = lane < warps ? sc.run_count[lane] : 0; // warps <= 32
-    int incl = mine;
+  const bool spare = static_cast<int>(blockDim.x) - 32 >= quads;
+  const int workers = static_cast<int>(blockDim.x) - (spare ? 32 : 0); // threads of the parallel part
+  const int worker_warps = workers >> 5;
+  const int stitcher = spare ? workers : 0;
+  const int head = min(kHeadQuads * 4, n);
+  float head_sum = 0.0f;
+  if (tid >= workers) {
+    if (tid == stitcher)
+      head_sum = serial(p_sm, 0, head, 0.0f);
+  } else {
+    const bool active = tid < quads;
+    const bool bad = any_bad || ((__float_as_uint(p[0]) | __float_as_uint(p[1]) | __float_as_uint(p[2]) |
+                                  __float_as_uint(p[3])) >> 31) != 0u;
+    // approximate prefix sums (any order): they only predict where the sum changes binade
+    const float q = active ? (p[0] + p[1]) + (p[2] + p[3]) : 0.0f;
+    float incl = q;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const int o = __shfl_up_sync(0xffffffffu, incl, d);
+      const float o = __shfl_up_sync(0xffffffffu, incl, d);
       if (lane >= d)
         incl += o;
     }
-    total_runs = __shfl_sync(0xffffffffu, incl, 31);
-    offset = __shfl_sync(0xffffffffu, incl - mine, warp);
-  }
-  const bool listed = total_runs <= kOrderedMaxEntries;
-  if (tail && listed)
-    sc.entries[offset + run] = make_uint4(static_cast<uint32_t>(key), even, odd, static_cast<uint32_t>(tid));
-  __syncthreads();
-  if (tid == 0) {
-    const int head = min(kHeadQuads * 4, n);
-    float s = serial(p_sm, 0, head, 0.0f);
-    bool ok = !serial_only && listed;
-    if (ok) {
-      // Eight entries at a time: their loads first, then a chain in registers.  A failed
-      // prediction only clears `ok`; the chain runs on.
-      for (int base_entry = 0; base_entry < total_runs; base_entry += 8) {
-        uint4 e[8];
+    const bool warp_bad = __any_sync(0xffffffffu, bad);
+    if (lane == 31)
+      sc.warp_total[warp] = warp_bad ? __uint_as_float(0x7fc00000u) : incl; // not finite: the plain chain
+    if (spare)
+      asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");
+    else
+      __syncthreads();
+    float base = 0.0f;
+    for (int w = 0; w < warp; ++w)
+      base += sc.warp_total[w];
+    const float lo = base + (incl - q), hi = base + incl;
+    // key: -2 head or inactive (no entry), -1 serial quad, else the binade (biased exponent)
+    int key = -2;
+    uint32_t even = 0u, odd = 0u;
+    if (active && tid >= kHeadQuads) {
+      key = -1;
+      const uint32_t e_lo = __float_as_uint(lo * 0.9990234375f) >> 23; // 1 - 2^-10
+      const uint32_t e_hi = __float_as_uint(hi * 1.0009765625f) >> 23; // 1 + 2^-10
+      if (lo > 0.0f && e_lo == e_hi && e_lo >= 24u && e_lo < 254u) {
+        const float scale = __uint_as_float((277u - e_lo) << 23); // 1/u = 2^(150 - e)
+        float from_even = __uint_as_float(kEvenStart), from_odd = __uint_as_float(kOddStart);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          e[i] = base_entry + i < total_runs ? sc.entries[base_entry + i] : make_uint4(0xfffffffeu, 0u, 0u, 0u);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (e[i].x == 0xffffffffu) { // serial quad
-            const float4 terms = *reinterpret_cast<const float4 *>(p_sm + 4 * e[i].w);
-            s = __fadd_rn(s, terms.x);
-            s = __fadd_rn(s, terms.y);
-            s = __fadd_rn(s, terms.z);
-            s = __fadd_rn(s, terms.w);
-          } else if (e[i].x != 0xfffffffeu) { // a run of clean quads in binade e.x
-            const uint32_t bits = __float_as_uint(s);
-            const uint32_t units = (bits & 0x7fffffu) | 0x800000u;
-            const uint32_t next = units + ((units & 1u) ? e[i].z : e[i].y);
-            ok = ok && (bits >> 23) == e[i].x && next < kLimit;
-            s = __uint_as_float((bits & 0x7f800000u) | (next & 0x7fffffu));
-          }
+        for (int u = 0; u < 4; ++u) {
+          const float scaled = __fmul_rn(p[u], scale);
+          from_even = __fadd_rn(from_even, scaled);
+          from_odd = __fadd_rn(from_odd, scaled);
+        }
+        if (from_even < 16777216.0f && from_odd < 16777216.0f) {
+          key = static_cast<int>(e_lo);
+          even = __float_as_uint(from_even) - kEvenStart;
+          odd = __float_as_uint(from_odd) - kOddStart;
         }
       }
     }
-    if (!ok)
-      s = serial(p_sm, head, n, serial(p_sm, 0, head, 0.0f));
-    sc.result = s;
+    // runs inside the warp: consecutive clean quads of one binade; every serial quad is its own run
+    const int prev_key = __shfl_up_sync(0xffffffffu, key, 1);
+    const bool starts = key != -2 && (lane == 0 || key == -1 || prev_key != key);
+    const uint32_t start_mask = __ballot_sync(0xffffffffu, starts);
+    const uint32_t live_mask = __ballot_sync(0xffffffffu, key != -2);
+    const uint32_t upto = start_mask & (0xffffffffu >> (31 - lane));
+    const int run = __popc(upto) - 1;                           // index of my run (if key != -2)
+    const int reach = key >= 0 ? lane - (31 - __clz(upto)) : 0; // lanes of my run in front of me
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t o_even = __shfl_up_sync(0xffffffffu, even, d);
+      const uint32_t o_odd = __shfl_up_sync(0xffffffffu, odd, d);
+      if (d <= reach) { // the totals stay below 32 * 2^23
+        const uint32_t new_even = o_even + ((o_even & 1u) ? odd : even);
+        const uint32_t new_odd = o_odd + ((o_odd & 1u) ? even : odd);
+        even = new_even;
+        odd = new_odd;
+      }
+    }
+    const bool tail = key != -2 && (lane == 31 || ((start_mask | ~live_mask) >> (lane + 1)) & 1u);
+    if (lane == 0)
+      sc.run_count[warp] = __popc(start_mask);
+    if (spare)
+      asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");
+    else
+      __syncthreads();
+    // every run's tail lane writes its entry at the run's place in the flat, ordered list
+    const int count = lane < worker_warps ? sc.run_count[lane] : 0; // at most 32 warps
+    const int total_runs = __reduce_add_sync(0xffffffffu, count);
+    const int offset = __reduce_add_sync(0xffffffffu, lane < warp ? count : 0);
+    if (total_runs <= kOrderedMaxEntries) {
+      if (tail)
+        sc.entries[offset + run] =
+            key >= 0 ? make_uint4(kRun | static_cast<uint32_t>(key), min(even, kSat), min(odd, kSat), 0u)
+                     : make_uint4(__float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]),
+                                  __float_as_uint(p[3]));
+      if (tid < kOrderedChunk) // padding, so that the stitch fetches whole chunks
+        sc.entries[total_runs + tid] = make_uint4(kRun, 0u, 0u, 0u);
+    }
   }
   __syncthreads();
-  const float result = sc.result;
+  if (warp == (stitcher >> 5)) {
+    const int count = lane < worker_warps ? sc.run_count[lane] : 0;
+    const int total_runs = __reduce_add_sync(0xffffffffu, count);
+    const float total = lane < worker_warps ? sc.warp_total[lane] : 0.0f;
+    const bool serial_only = __any_sync(0xffffffffu, !(fabsf(total) <= 3.402823466e38f));
+    if (tid == stitcher) {
+      if (!spare)
+        head_sum = serial(p_sm, 0, head, 0.0f);
+      float s = head_sum;
+      bool ok = !serial_only && total_runs <= kOrderedMaxEntries;
+      if (ok) {
+        uint32_t wrong = 0u;
+        // a chunk of entries at a time: their loads first, then a chain in registers
+        for (int first = 0; first < total_runs; first += kOrderedChunk) {
+          uint4 e[kOrderedChunk];
+#pragma unroll
+          for (int i = 0; i < kOrderedChunk; ++i)
+            e[i] = sc.entries[first + i];
+#pragma unroll
+          for (int i = 0; i < kOrderedChunk; ++i)
+            s = apply(s, e[i], wrong);
+        }
+        ok = wrong == 0u;
+      }
+      if (!ok)
+        s = serial(p_sm, head, n, head_sum);
+      sc.result = finish(s);
+    }
+    __syncwarp(); // the stitching thread's warp arrives at the barrier as a whole
+  }
   __syncthreads();
-  return result;
+  return sc.result;
 }
 
 } // namespace llmcp_b200
