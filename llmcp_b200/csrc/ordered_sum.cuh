@@ -16,12 +16,14 @@
 // Which binade the sum is in at each term is predicted from an approximate parallel prefix sum
 // (any order; it differs from the serial sum by far less than the 2^-10 margin used).  Quads of
 // terms that lie safely inside one binade are summarised for it; consecutive quads of one binade
-// are composed by a segmented warp scan into runs.  Quads near a power of two, and the first 64
-// terms (where the sum still doubles every few additions), stay serial.  One thread then
-// stitches the pieces in order: four real additions for a serial quad, one integer addition to
-// the sum's bit pattern for a run.  Every prediction is verified on the way (the sum's exponent
-// at the start of a run, no carry into the next binade at its end); if one fails, or the terms
-// are not all finite, or the sum is zero or tiny, the plain serial loop produces the result.
+// are composed by a segmented warp scan into runs.  Quads near a power of two stay serial, and
+// so does the head of the sum (at least 64 terms, where the sum still doubles every few
+// additions; about a sixth of the terms when a spare warp can add them while the others scan).
+// One thread then stitches the pieces in order: four real additions for a serial quad, one
+// integer addition to the sum's bit pattern for a run.  Every prediction is verified on the way
+// (the sum's exponent at the start of a run, no carry into the next binade at its end); if one
+// fails, or the terms are not all finite and non-negative, or the sum is zero or tiny, the plain
+// serial loop produces the result.
 // The result is therefore the serial sum bit for bit in every case; the prediction only decides
 // how fast it is obtained.
 #pragma once
@@ -32,22 +34,23 @@ namespace llmcp_b200 {
 
 constexpr int kOrderedMaxWarps = 32;
 constexpr int kOrderedMaxEntries = 96; // more pieces than this: the plain chain is used
-constexpr int kOrderedChunk = 8;       // entries the stitching thread fetches at a time
+constexpr int kOrderedChunk = 8;       // padding behind the list: the stitch fetches up to seven entries ahead
 
 // One piece of the sum per entry, in order.  A run of quads in one binade: x = 2^31 | binade
-// (biased exponent), y / z = what it adds to an even / odd count; x = 2^31 alone is padding
-// (adds nothing).  A serial quad: its four terms as f32 bits (sign bit clear).
+// (biased exponent), y = what it adds to an even count, z = what it adds to an odd count minus
+// y (-1, 0 or 1), w = binade << 23.  A serial quad: its four terms as f32 bits (sign bit
+// clear); four zeros serve as padding.
 struct OrderedSumScratch {
-  float warp_total[kOrderedMaxWarps];
+  alignas(16) float warp_total[kOrderedMaxWarps];
   int run_count[kOrderedMaxWarps];
   uint4 entries[kOrderedMaxEntries + kOrderedChunk];
   float result;
 };
 
-
 namespace ordered_sum {
 
-constexpr int kHeadQuads = 16;               // the first 64 terms are added serially
+constexpr int kHeadQuads = 16;               // the first 64 terms are always added serially
+constexpr int kHeadShare = 6;                // a spare warp adds about this fraction of the terms serially
 constexpr uint32_t kSat = 1u << 26;          // a total this large fails the carry check anyway
 constexpr uint32_t kRun = 0x80000000u;
 constexpr uint32_t kEvenStart = 0x4b000000u; // 2^23 as f32 bits
@@ -74,14 +77,17 @@ __device__ __forceinline__ float serial(const float *p_sm, int from, int to, flo
 }
 
 // One entry applied to the running sum, without branches: both forms are evaluated and one is
-// kept.  `wrong` collects failed predictions.
+// kept.  `wrong` collects failed predictions: a run must find the sum in its binade and leave it
+// there (e.w holds the binade in the exponent's place).
 __device__ __forceinline__ float apply(float s, const uint4 e, uint32_t &wrong) {
   const uint32_t bits = __float_as_uint(s);
-  const uint32_t next = bits + ((bits & 1u) ? e.z : e.y);
+  const uint32_t next = (bits + e.y) + (bits & 1u) * e.z; // e.z: odd total minus even total
   const float added = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, __uint_as_float(e.x)), __uint_as_float(e.y)),
                                           __uint_as_float(e.z)), __uint_as_float(e.w));
-  wrong |= e.x > kRun ? (((bits >> 23) ^ (e.x & 0x7fffffffu)) | ((next ^ bits) >> 23)) : 0u;
-  return e.x >= kRun ? __uint_as_float(next) : added;
+  const bool run = static_cast<int32_t>(e.x) < 0;
+  const uint32_t checked = static_cast<uint32_t>(static_cast<int32_t>(e.x) >> 31) & 0xff800000u;
+  wrong |= ((bits ^ e.w) | (next ^ e.w)) & checked;
+  return run ? __uint_as_float(next) : added;
 }
 
 } // namespace ordered_sum
@@ -90,7 +96,7 @@ __device__ __forceinline__ float apply(float s, const uint4 e, uint32_t &wrong) 
 // visible to the block).  n % 4 == 0, blockDim.x * 4 >= n, blockDim.x a multiple of 32.  Every
 // thread calls; all get finish(sum), which one thread evaluates.  If the block's last warp holds
 // no terms it stays out of the other warps' barriers (which then use barrier 1): one of its
-// threads adds the first 64 terms meanwhile, and stitches.  The caller synchronises the block
+// threads adds the head of the sum meanwhile, and stitches.  The caller synchronises the block
 // before it reuses `sc`.
 template <typename Finish>
 __device__ float block_ordered_sum(const float (&p)[4], const float *p_sm, int n, bool any_bad,
@@ -102,7 +108,9 @@ __device__ float block_ordered_sum(const float (&p)[4], const float *p_sm, int n
   const int workers = static_cast<int>(blockDim.x) - (spare ? 32 : 0); // threads of the parallel part
   const int worker_warps = workers >> 5;
   const int stitcher = spare ? workers : 0;
-  const int head = min(kHeadQuads * 4, n);
+  // a spare warp has the time of the parallel part for its serial head: a quarter of the terms
+  const int head_quads = min(quads, spare ? max(kHeadQuads, (quads / kHeadShare) & ~31) : kHeadQuads);
+  const int head = head_quads * 4;
   float head_sum = 0.0f;
   if (tid >= workers) {
     if (tid == stitcher)
@@ -127,14 +135,16 @@ __device__ float block_ordered_sum(const float (&p)[4], const float *p_sm, int n
       asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");
     else
       __syncthreads();
-    float base = 0.0f;
-    for (int w = 0; w < warp; ++w)
-      base += sc.warp_total[w];
+    // the sum of the totals of the warps in front (any order will do)
+    float base = lane < warp ? sc.warp_total[lane] : 0.0f;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1)
+      base += __shfl_xor_sync(0xffffffffu, base, d);
     const float lo = base + (incl - q), hi = base + incl;
     // key: -2 head or inactive (no entry), -1 serial quad, else the binade (biased exponent)
     int key = -2;
     uint32_t even = 0u, odd = 0u;
-    if (active && tid >= kHeadQuads) {
+    if (active && tid >= head_quads) {
       key = -1;
       const uint32_t e_lo = __float_as_uint(lo * 0.9990234375f) >> 23; // 1 - 2^-10
       const uint32_t e_hi = __float_as_uint(hi * 1.0009765625f) >> 23; // 1 + 2^-10
@@ -187,11 +197,12 @@ __device__ float block_ordered_sum(const float (&p)[4], const float *p_sm, int n
     if (total_runs <= kOrderedMaxEntries) {
       if (tail)
         sc.entries[offset + run] =
-            key >= 0 ? make_uint4(kRun | static_cast<uint32_t>(key), min(even, kSat), min(odd, kSat), 0u)
+            key >= 0 ? make_uint4(kRun | static_cast<uint32_t>(key), min(even, kSat), min(odd, kSat) - min(even, kSat),
+                                  static_cast<uint32_t>(key) << 23)
                      : make_uint4(__float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]),
                                   __float_as_uint(p[3]));
-      if (tid < kOrderedChunk) // padding, so that the stitch fetches whole chunks
-        sc.entries[total_runs + tid] = make_uint4(kRun, 0u, 0u, 0u);
+      if (tid < kOrderedChunk) // padding: the stitch fetches ahead and works in fours
+        sc.entries[total_runs + tid] = make_uint4(0u, 0u, 0u, 0u); // four zero terms
     }
   }
   __syncthreads();
@@ -207,15 +218,17 @@ __device__ float block_ordered_sum(const float (&p)[4], const float *p_sm, int n
       bool ok = !serial_only && total_runs <= kOrderedMaxEntries;
       if (ok) {
         uint32_t wrong = 0u;
-        // a chunk of entries at a time: their loads first, then a chain in registers
-        for (int first = 0; first < total_runs; first += kOrderedChunk) {
-          uint4 e[kOrderedChunk];
-#pragma unroll
-          for (int i = 0; i < kOrderedChunk; ++i)
-            e[i] = sc.entries[first + i];
-#pragma unroll
-          for (int i = 0; i < kOrderedChunk; ++i)
-            s = apply(s, e[i], wrong);
+        // four entries in flight: each is fetched three entries before it is applied
+        uint4 e0 = sc.entries[0], e1 = sc.entries[1], e2 = sc.entries[2], e3 = sc.entries[3];
+        for (int first = 0; first < total_runs; first += 4) {
+          s = apply(s, e0, wrong);
+          e0 = sc.entries[first + 4];
+          s = apply(s, e1, wrong);
+          e1 = sc.entries[first + 5];
+          s = apply(s, e2, wrong);
+          e2 = sc.entries[first + 6];
+          s = apply(s, e3, wrong);
+          e3 = sc.entries[first + 7];
         }
         ok = wrong == 0u;
       }
