@@ -182,6 +182,21 @@ uint64_t llmcp_b200_synthetic_bytes(const llmcp_b200_dims *dims);
 int llmcp_b200_synthetic_fill(const llmcp_b200_dims *dims, uint64_t seed, uint8_t *file, uint64_t file_bytes);
 int llmcp_b200_pack_q8_0_p4(const float *values, int64_t rows, int64_t cols, uint8_t *dst);
 int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes);
+/* Checkpoint → container, the job of llmcp's offline packer:
+ *   llmcp_b200_parse_config     : model dimensions from the text of config.json, with the
+ *                                 checks of lib/Model/ModelConfig.cpp:78-283.
+ *   llmcp_b200_read_safetensors : header of one safetensors shard (lib/Model/Safetensors.cpp:
+ *                                 61-172) as text, one line per tensor:
+ *                                 name TAB dtype TAB absolute data offset TAB bytes TAB d0,d1,...
+ *                                 Returns the text length, 0 on error.
+ *   llmcp_b200_pack_checkpoint  : `llmcp-pack --model DIR --out FILE --quant none|q8_0
+ *                                 [--dry-run] [--verbose]` (tools/llmcp-pack/llmcp-pack.cpp:44-89,
+ *                                 lib/Model/WeightPacker.cpp:163-274); the three counters are what
+ *                                 its summary line prints.  Host only: no GPU is touched. */
+int llmcp_b200_parse_config(const char *json, uint64_t length, llmcp_b200_dims *dims);
+uint64_t llmcp_b200_read_safetensors(const char *path, char *buffer, uint64_t capacity);
+int llmcp_b200_pack_checkpoint(const char *model_dir, const char *output_path, const char *quant, int dry_run,
+                               int verbose, uint64_t *tensors, uint64_t *source_bytes, uint64_t *arena_bytes);
 /* Rotary cos/sin row of one position, f32 (lib/Runtime/AotRuntime.cpp:22-32). */
 void llmcp_b200_make_cos_sin(int64_t position, int64_t rotary, float theta, float *cos_out, float *sin_out);
 /* Copies the manifest JSON text of a container; returns its length. */

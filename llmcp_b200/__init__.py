@@ -68,6 +68,7 @@ def lib():
         handle.llmcp_b200_launch_count.restype = C.c_uint64
         handle.llmcp_b200_synthetic_bytes.restype = C.c_uint64
         handle.llmcp_b200_manifest.restype = C.c_uint64
+        handle.llmcp_b200_read_safetensors.restype = C.c_uint64
         handle.llmcp_b200_engine_create.restype = C.c_void_p
         handle._mlir_ciface_llmcp_model_prefill.restype = None
         handle._mlir_ciface_llmcp_model_decode.restype = None
@@ -245,6 +246,42 @@ def synthetic_container(dims, seed):
     data = np.empty(size, dtype=np.uint8)
     _check(lib().llmcp_b200_synthetic_fill(C.byref(dims), C.c_uint64(seed), _p(data), C.c_uint64(size)))
     return data
+
+
+def parse_config(text):
+    """Model dimensions from the text of a checkpoint's config.json (lib/Model/ModelConfig.cpp:78-283)."""
+    raw = text.encode() if isinstance(text, str) else bytes(text)
+    d = Dims()
+    _check(lib().llmcp_b200_parse_config(raw, C.c_uint64(len(raw)), C.byref(d)))
+    return d
+
+
+def read_safetensors(path):
+    """Header of one safetensors shard: ``{name: (dtype, absolute data offset, bytes, shape)}``
+    (lib/Model/Safetensors.cpp:137-172).  No tensor data is read."""
+    raw = os.fsencode(str(path))
+    lib().llmcp_b200_clear_error()  # a length of 0 is an error only if one was recorded by this call
+    size = int(lib().llmcp_b200_read_safetensors(raw, None, C.c_uint64(0)))
+    if size == 0 and last_error():
+        raise LlmcpError(last_error())
+    buf = C.create_string_buffer(size + 1)
+    lib().llmcp_b200_read_safetensors(raw, buf, C.c_uint64(size + 1))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, dtype, offset, nbytes, shape = line.split("\t")
+        out[name] = (dtype, int(offset), int(nbytes), tuple(int(v) for v in shape.split(",") if v))
+    return out
+
+
+def pack_checkpoint(model_dir, output_path=None, quant="none", dry_run=False, verbose=False):
+    """``llmcp-pack``: packs ``model_dir`` (config.json + safetensors) into the container file
+    ``output_path`` (tools/llmcp-pack/llmcp-pack.cpp:44-89).  Returns
+    ``(tensors, source_bytes, arena_bytes)``, the figures of the tool's summary line."""
+    counters = [C.c_uint64(0) for _ in range(3)]
+    _check(lib().llmcp_b200_pack_checkpoint(
+        os.fsencode(str(model_dir)), os.fsencode(str(output_path)) if output_path else None, quant.encode(),
+        int(bool(dry_run)), int(bool(verbose)), *[C.byref(c) for c in counters]))
+    return tuple(int(c.value) for c in counters)
 
 
 class Arena:

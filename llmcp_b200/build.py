@@ -17,8 +17,8 @@ ROOT = PACKAGE.parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libllmcp_b200.so"
 
-SOURCES = ["q8_linear.cu", "gemv_rows.cu", "gemv_cols.cu", "gemv_ring.cu", "gemm_tc.cu", "norms.cu", "mixers.cu", "engine.cu", "api.cu", "noalloc.cu", "format.cpp"]
-TOOLS = {"llmcp-benchmark": ["tools/llmcp_benchmark.cpp"]}
+SOURCES = ["q8_linear.cu", "gemv_rows.cu", "gemv_cols.cu", "gemv_ring.cu", "gemm_tc.cu", "norms.cu", "mixers.cu", "engine.cu", "api.cu", "noalloc.cu", "format.cpp", "checkpoint.cpp"]
+TOOLS = {"llmcp-benchmark": ["tools/llmcp_benchmark.cpp"], "llmcp-pack": ["tools/llmcp_pack.cpp"]}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -79,9 +79,9 @@ def build(force=False, verbose=False):
             continue
         target = PACKAGE / "bin" / tool
         target.parent.mkdir(exist_ok=True)
-        if force or _newer(target, [*paths, *headers, CSRC / "format.cpp"]):
+        if force or _newer(target, [*paths, *headers, CSRC / "format.cpp", CSRC / "checkpoint.cpp"]):
             cmd = ["/usr/bin/g++", "-O2", "-std=c++17", "-fopenmp", "-ffp-contract=off", "-o", str(target),
-                   *map(str, paths), str(CSRC / "format.cpp"), "-ldl"]
+                   *map(str, paths), str(CSRC / "format.cpp"), str(CSRC / "checkpoint.cpp"), "-ldl"]
             if verbose:
                 print(" ".join(cmd), flush=True)
             subprocess.run(cmd, check=True, env=env)

@@ -13,6 +13,7 @@
 #include <string>
 #include <vector>
 
+#include "checkpoint.h"
 #include "engine.h"
 #include "kernels.h"
 
@@ -657,8 +658,11 @@ int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *
 }
 
 // ---- container helpers and engine --------------------------------------------------------
-void llmcp_b200_default_dims(llmcp_b200_dims *d) {
-  const ModelDims m;
+static void from_dims(const ModelDims &m, llmcp_b200_dims *d);
+
+void llmcp_b200_default_dims(llmcp_b200_dims *d) { from_dims(ModelDims(), d); }
+
+static void from_dims(const ModelDims &m, llmcp_b200_dims *d) {
   d->hidden = m.hidden;
   d->intermediate = m.intermediate;
   d->vocab = m.vocab;
@@ -713,6 +717,56 @@ int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes) {
     const std::string error = parse_container(file, file_bytes, &m);
     if (!error.empty())
       throw std::runtime_error(error);
+  });
+}
+
+int llmcp_b200_parse_config(const char *json, uint64_t length, llmcp_b200_dims *dims) {
+  return guarded_async([&] {
+    ModelDims d;
+    const std::string error = parse_model_config(json, length, &d);
+    if (!error.empty())
+      throw std::runtime_error(error);
+    from_dims(d, dims);
+  });
+}
+
+uint64_t llmcp_b200_read_safetensors(const char *path, char *buffer, uint64_t capacity) {
+  SourceTensors tensors;
+  const std::string error = read_safetensors_file(path, path, &tensors);
+  if (!error.empty()) {
+    set_error(error);
+    return 0;
+  }
+  std::string text;
+  for (const auto &item : tensors) {
+    const SourceTensor &t = item.second;
+    text += t.name + "\t" + t.dtype + "\t" + std::to_string(t.data_offset) + "\t" + std::to_string(t.data_size) + "\t";
+    for (size_t i = 0; i < t.shape.size(); ++i)
+      text += (i ? "," : "") + std::to_string(t.shape[i]);
+    text += "\n";
+  }
+  if (buffer && capacity) {
+    const uint64_t n = std::min<uint64_t>(capacity - 1, text.size());
+    std::memcpy(buffer, text.data(), n);
+    buffer[n] = 0;
+  }
+  return text.size();
+}
+
+int llmcp_b200_pack_checkpoint(const char *model_dir, const char *output_path, const char *quant, int dry_run,
+                               int verbose, uint64_t *tensors, uint64_t *source_bytes, uint64_t *arena_bytes) {
+  return guarded_async([&] {
+    PackSummary summary;
+    const std::string error = pack_checkpoint(model_dir ? model_dir : "", output_path ? output_path : "",
+                                              quant ? quant : "none", dry_run != 0, verbose != 0, &summary);
+    if (!error.empty())
+      throw std::runtime_error(error);
+    if (tensors)
+      *tensors = summary.tensors;
+    if (source_bytes)
+      *source_bytes = summary.source_bytes;
+    if (arena_bytes)
+      *arena_bytes = summary.arena_bytes;
   });
 }
 

@@ -1,4 +1,5 @@
 #include "format.h"
+#include "json.h"
 
 #include <algorithm>
 #include <cmath>
@@ -131,178 +132,7 @@ std::string read_header(const uint8_t *data, uint64_t file_bytes, uint64_t *aren
   return "";
 }
 
-// ------------------------------------------------------------------------------
-// a small JSON reader (objects, arrays, strings, numbers, true/false/null)
-// ------------------------------------------------------------------------------
-namespace {
-
-struct Json {
-  enum Kind { Null, Bool, Number, String, Array, Object } kind = Null;
-  bool boolean = false;
-  double number = 0;
-  bool integral = false;
-  int64_t integer = 0;
-  std::string text;
-  std::vector<Json> items;
-  std::vector<std::pair<std::string, Json>> members;
-
-  const Json *get(const char *key) const {
-    for (const auto &m : members)
-      if (m.first == key)
-        return &m.second;
-    return nullptr;
-  }
-};
-
-struct JsonReader {
-  const char *p, *end;
-  bool ok = true;
-
-  void skip() {
-    while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r'))
-      ++p;
-  }
-  bool eat(char c) {
-    skip();
-    if (p < end && *p == c) {
-      ++p;
-      return true;
-    }
-    return false;
-  }
-  std::string string() {
-    std::string out;
-    if (!eat('"')) {
-      ok = false;
-      return out;
-    }
-    while (p < end && *p != '"') {
-      if (*p == '\\' && p + 1 < end) {
-        ++p;
-        switch (*p) {
-        case 'n': out += '\n'; break;
-        case 't': out += '\t'; break;
-        case 'r': out += '\r'; break;
-        case 'b': out += '\b'; break;
-        case 'f': out += '\f'; break;
-        case 'u':
-          if (p + 4 < end) {
-            unsigned code = 0;
-            for (int i = 1; i <= 4; ++i) {
-              char c = p[i];
-              code = code * 16 + (c >= '0' && c <= '9' ? c - '0' : (c | 32) >= 'a' && (c | 32) <= 'f' ? (c | 32) - 'a' + 10 : 0);
-            }
-            out += code < 128 ? static_cast<char>(code) : '?';
-            p += 4;
-          } else {
-            ok = false;
-          }
-          break;
-        default: out += *p;
-        }
-        ++p;
-      } else {
-        out += *p++;
-      }
-    }
-    if (p >= end)
-      ok = false;
-    else
-      ++p;
-    return out;
-  }
-  Json value(int depth = 0) {
-    Json v;
-    skip();
-    if (p >= end || depth > 32) {
-      ok = false;
-      return v;
-    }
-    if (*p == '{') {
-      ++p;
-      v.kind = Json::Object;
-      if (eat('}'))
-        return v;
-      do {
-        std::string key = string();
-        if (!ok || !eat(':')) {
-          ok = false;
-          return v;
-        }
-        v.members.emplace_back(std::move(key), value(depth + 1));
-      } while (ok && eat(','));
-      if (!eat('}'))
-        ok = false;
-    } else if (*p == '[') {
-      ++p;
-      v.kind = Json::Array;
-      if (eat(']'))
-        return v;
-      do {
-        v.items.push_back(value(depth + 1));
-      } while (ok && eat(','));
-      if (!eat(']'))
-        ok = false;
-    } else if (*p == '"') {
-      v.kind = Json::String;
-      v.text = string();
-    } else if (end - p >= 4 && !std::strncmp(p, "true", 4)) {
-      v.kind = Json::Bool;
-      v.boolean = true;
-      p += 4;
-    } else if (end - p >= 5 && !std::strncmp(p, "false", 5)) {
-      v.kind = Json::Bool;
-      p += 5;
-    } else if (end - p >= 4 && !std::strncmp(p, "null", 4)) {
-      p += 4;
-    } else {
-      const char *start = p;
-      bool integral = true;
-      if (p < end && (*p == '-' || *p == '+'))
-        ++p;
-      while (p < end && ((*p >= '0' && *p <= '9') || *p == '.' || *p == 'e' || *p == 'E' || *p == '-' || *p == '+')) {
-        if (*p == '.' || *p == 'e' || *p == 'E')
-          integral = false;
-        ++p;
-      }
-      if (p == start) {
-        ok = false;
-        return v;
-      }
-      std::string text(start, p);
-      v.kind = Json::Number;
-      v.number = std::strtod(text.c_str(), nullptr);
-      v.integral = integral && text.size() < 19;
-      if (v.integral)
-        v.integer = std::strtoll(text.c_str(), nullptr, 10);
-    }
-    return v;
-  }
-};
-
-bool as_integer(const Json *j, int64_t *out) {
-  if (!j || j->kind != Json::Number || !j->integral)
-    return false;
-  *out = j->integer;
-  return true;
-}
-
-void append_escaped(std::string &out, const std::string &s) {
-  out += '"';
-  for (char c : s) {
-    if (c == '"' || c == '\\') {
-      out += '\\';
-      out += c;
-    } else if (c == '\n') {
-      out += "\\n";
-    } else {
-      out += c;
-    }
-  }
-  out += '"';
-}
-
-} // namespace
+using namespace detail;
 
 const TensorEntry *Manifest::find(const std::string &name) const {
   for (const auto &t : tensors)
@@ -312,10 +142,14 @@ const TensorEntry *Manifest::find(const std::string &name) const {
 }
 
 std::string Manifest::to_json() const {
-  std::string out = "{\"alignment\":64,\"block_size\":32,\"group_stride\":" + std::to_string(group_stride) +
+  // block_size and quant_layout accompany a quantised arena only (WeightPacker.cpp:126-137).
+  const bool quantised = quantization != "none";
+  std::string out = std::string("{\"alignment\":64,") + (quantised ? "\"block_size\":32," : "") +
+                    "\"group_stride\":" + std::to_string(group_stride) +
                     ",\"header_bytes\":" + std::to_string(header_bytes) + ",\"model\":";
   append_escaped(out, model);
-  out += ",\"num_groups\":" + std::to_string(num_groups) + ",\"quant_layout\":\"q8_0_p4\",\"quantization\":";
+  out += ",\"num_groups\":" + std::to_string(num_groups) + (quantised ? ",\"quant_layout\":\"q8_0_p4\"" : "") +
+         ",\"quantization\":";
   append_escaped(out, quantization);
   out += ",\"tensors\":[";
   for (size_t i = 0; i < tensors.size(); ++i) {
@@ -436,10 +270,16 @@ uint64_t align_up(uint64_t v) { return (v + kTensorAlignment - 1) & ~(kTensorAli
 struct LayoutBuilder {
   Manifest m;
   uint64_t cursor = kHeaderBytes;
+  const SourceTensors *source = nullptr; // checkpoint headers, or null for the synthetic model
+  bool quantize = true;
+  std::string error;
 
-  // `element_bytes` 2 = bf16 source, 4 = f32 source.  2-D bf16/f32 tensors with rows % 8 == 0
-  // and cols % 32 == 0 are stored as Q8_0 (WeightLayout.cpp:72-82).
+  // `element_bytes` 2 = bf16 source, 4 = f32 source (used when there is no checkpoint; with
+  // one, dtype and byte size come from its header and the shape must match).  2-D bf16/f32
+  // tensors with rows % 8 == 0 and cols % 32 == 0 are stored as Q8_0 (WeightLayout.cpp:72-82).
   void add(const std::string &name, std::vector<int64_t> shape, int element_bytes) {
+    if (!error.empty())
+      return;
     TensorEntry e;
     e.name = name;
     e.offset = align_up(cursor);
@@ -447,9 +287,31 @@ struct LayoutBuilder {
     for (int64_t d : shape)
       elements *= static_cast<uint64_t>(d);
     e.source_size = elements * element_bytes;
-    e.size = e.source_size;
     e.dtype = element_bytes == 2 ? "BF16" : "F32";
-    if (shape.size() == 2 && shape[0] % 8 == 0 && shape[1] % 32 == 0) {
+    if (source) {
+      auto it = source->find(name);
+      if (it == source->end()) {
+        error = "missing tensor '" + name + "'";
+        return;
+      }
+      const SourceTensor &t = it->second;
+      if (t.shape.size() != shape.size()) {
+        error = "tensor '" + name + "' has rank " + std::to_string(t.shape.size()) + ", expected " +
+                std::to_string(shape.size());
+        return;
+      }
+      for (size_t i = 0; i < shape.size(); ++i)
+        if (t.shape[i] != shape[i]) {
+          error = "tensor '" + name + "' dimension " + std::to_string(i) + " is " + std::to_string(t.shape[i]) +
+                  ", expected " + std::to_string(shape[i]);
+          return;
+        }
+      e.source_size = t.data_size;
+      e.dtype = t.dtype;
+    }
+    e.size = e.source_size;
+    if (quantize && shape.size() == 2 && shape[0] > 0 && shape[1] > 0 && shape[0] % 8 == 0 && shape[1] % 32 == 0 &&
+        (e.dtype == "BF16" || e.dtype == "F32")) {
       e.size = static_cast<uint64_t>(shape[0]) * (shape[1] / 32) * 34;
       e.dtype = "Q8_0";
     }
@@ -459,10 +321,37 @@ struct LayoutBuilder {
   }
 };
 
+void lay_out_model(const ModelDims &c, LayoutBuilder &b);
+
 } // namespace
 
 Manifest build_layout(const ModelDims &c) {
   LayoutBuilder b;
+  lay_out_model(c, b);
+  b.m.model = "synthetic";
+  return b.m;
+}
+
+std::string plan_layout(const ModelDims &c, const SourceTensors &tensors, bool q8, Manifest *out) {
+  if (c.full_interval <= 0 || c.layers <= 0 || c.layers % c.full_interval != 0)
+    return "num_hidden_layers must be divisible by full_attention_interval";
+  LayoutBuilder b;
+  b.source = &tensors;
+  b.quantize = q8;
+  b.m.quantization = q8 ? "q8_0" : "none";
+  lay_out_model(c, b);
+  if (!b.error.empty())
+    return b.error;
+  *out = std::move(b.m);
+  return "";
+}
+
+namespace {
+
+// Tensor order of the arena (WeightLayout.cpp:96-268): the embedding table, then per group of
+// `full_interval` layers the layer tensors (every group padded to the first one's size), then
+// the final norm.
+void lay_out_model(const ModelDims &c, LayoutBuilder &b) {
   const std::string root = "model.language_model.";
   b.add(root + "embed_tokens.weight", {c.vocab, c.hidden}, 2);
   const int64_t groups = c.layers / c.full_interval;
@@ -498,14 +387,16 @@ Manifest build_layout(const ModelDims &c) {
     const uint64_t group_bytes = align_up(b.cursor - group_start);
     if (g == 0)
       b.m.group_stride = group_bytes;
+    else if (b.m.group_stride != group_bytes && b.error.empty())
+      b.error = "layer groups have different weight sizes";
     b.cursor = group_start + b.m.group_stride;
   }
   b.add(root + "norm.weight", {c.hidden}, 2);
   b.m.total_bytes = align_up(b.cursor);
   b.m.num_groups = groups;
-  b.m.model = "synthetic";
-  return b.m;
 }
+
+} // namespace
 
 // ------------------------------------------------------------------------------
 // Q8_0 quantisation and lane packing

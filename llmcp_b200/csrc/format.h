@@ -10,6 +10,7 @@
 #pragma once
 
 #include <cstdint>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -71,6 +72,21 @@ std::string parse_container(const uint8_t *base, uint64_t file_bytes, Manifest *
 
 // Tensor order, shapes, dtypes and offsets of a Qwen3.5-style model packed with --quant q8_0.
 Manifest build_layout(const ModelDims &dims);
+
+// One tensor of a checkpoint as a safetensors header describes it: `data_offset` is the
+// absolute position of its first byte in the shard file `shard`
+// (include/llmcp/Model/Safetensors.h:24-33).
+struct SourceTensor {
+  std::string name, dtype, shard;
+  std::vector<int64_t> shape;
+  uint64_t data_offset = 0, data_size = 0;
+};
+using SourceTensors = std::map<std::string, SourceTensor>;
+
+// The same layout for a real checkpoint: every tensor must be present with the expected
+// shape; dtype and byte size come from the checkpoint; with `q8` the 2-D bf16/f32 tensors
+// whose shape allows it become Q8_0.  Returns "" or the reason (lib/Model/WeightLayout.cpp:54-268).
+std::string plan_layout(const ModelDims &dims, const SourceTensors &tensors, bool q8, Manifest *out);
 
 // Q8_0: per 32 values d = f16(amax / 127), q = clamp(lround(x / (amax / 127)), -127, 127).
 void quantize_row_q8_0(const float *values, int64_t cols, uint16_t *d, int8_t *qs);

@@ -26,9 +26,10 @@ def oracle_dims(d):
                 lin_v_dim=d.lin_v_dim, conv_kernel=d.conv_kernel)
 
 
-def run_both(dims, seed, prompt, steps, capacity):
+def run_both(dims, seed, prompt, steps, capacity, data=None):
     L.lib().llmcp_b200_clear_error()  # a message left by an earlier, deliberately failing call
-    data = L.synthetic_container(dims, seed)
+    if data is None:
+        data = L.synthetic_container(dims, seed)
     arena = L.Arena().from_buffer(data)
     runtime = L.AotRuntime(dims)
     assert runtime.init(max_sequence=capacity)
@@ -86,6 +87,18 @@ def test_engine_matches_aot_and_oracle_state():
     logits2, token2 = engine.forward(prompt[3:], 3)
     assert token2 == token and np.array_equal(logits2.view(np.uint32), logits.view(np.uint32))
     engine.close()
+
+
+def test_packed_checkpoint_matches_oracle(tmp_path):
+    """A checkpoint packed by this repository's llmcp-pack, with random norm gains, A_log and
+    dt_bias (the synthetic model has them at their neutral values), through the AOT entries."""
+    import test_checkpoint as ck
+    ck.write_checkpoint(tmp_path, seed=11)
+    L.pack_checkpoint(tmp_path, tmp_path / "weights.bin", quant="q8_0")
+    data = np.fromfile(tmp_path / "weights.bin", dtype=np.uint8)
+    d = L.parse_config((tmp_path / "config.json").read_text())
+    assert all(getattr(d, k) == v for k, v in ck.TINY.items())
+    run_both(d, 0, [5, 200, 31, 7, 7, 9], steps=5, capacity=16, data=data)
 
 
 def test_one_token_prompt_uses_decode_entry():
