@@ -344,10 +344,11 @@ def main():
     # ---- end-to-end arm through the AOT ABI ------------------------------------------------
     runtime = L.AotRuntime(dims)
     assert runtime.init(max_sequence=capacity)
-    logits = runtime.forward(arena, prompt, 0, PREFILL)
+    logits = np.zeros(dims.vocab, dtype=np.float32)  # one host row for every call, as llmcp-benchmark.cpp:84-101 keeps
+    runtime.forward(arena, prompt, 0, PREFILL, logits)
     pos = PREFILL
     for _ in range(warmup):
-        logits = runtime.forward(arena, [int(np.argmax(logits))], pos, pos + 1)
+        runtime.forward(arena, [int(np.argmax(logits))], pos, pos + 1, logits)
         pos += 1
     barrier()
     sampler.open_window()
@@ -355,7 +356,7 @@ def main():
     e2e_tokens = []
     for _ in range(steps):
         e2e_tokens.append(int(np.argmax(logits)))
-        logits = runtime.forward(arena, [e2e_tokens[-1]], pos, pos + 1)
+        runtime.forward(arena, [e2e_tokens[-1]], pos, pos + 1, logits)
         pos += 1
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)

@@ -95,10 +95,20 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   logits_ = static_cast<float *>(alloc(static_cast<size_t>(c.vocab) * 4));
   argmax_v_ = static_cast<float *>(alloc(kArgmaxParts * 4));
   argmax_i_ = static_cast<int64_t *>(alloc(kArgmaxParts * 8));
-  next_token_ = static_cast<int64_t *>(alloc(8));
-  position_dev_ = static_cast<int64_t *>(alloc(8));
+  // [next token (8 bytes) | GEMM status word (4)]: one copy brings both back after a call.
+  uint8_t *results = static_cast<uint8_t *>(alloc(16));
+  next_token_ = reinterpret_cast<int64_t *>(results);
+  gemm_error_ = reinterpret_cast<int *>(results + 8);
+  // The inputs of a one-token step, [position | token | cos row | sin row], in one block so
+  // that one copy from the pinned packet of the same layout delivers them all.
+  step_block_bytes_ = 16 + 2 * static_cast<size_t>(c.rotary) * 4;
+  uint8_t *block = static_cast<uint8_t *>(alloc(step_block_bytes_));
+  position_dev_ = reinterpret_cast<int64_t *>(block);
+  dec_tokens_ = reinterpret_cast<int64_t *>(block + 8);
+  dec_cos_ = reinterpret_cast<float *>(block + 16);
+  dec_sin_ = dec_cos_ + c.rotary;
   step_dev_ = static_cast<int64_t *>(alloc(8));
-  check(cudaMallocHost(&position_pinned_, 8), "cudaMallocHost");
+  check(cudaMallocHost(&position_pinned_, step_block_bytes_), "cudaMallocHost");
   if (const char *flag = std::getenv("LLMCP_B200_NO_GRAPH"))
     use_graph_ = std::atoi(flag) == 0;
   if (const char *flag = std::getenv("LLMCP_B200_GEMV_FLAGS"))
@@ -107,11 +117,10 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     fuse_decode_mixer_ = std::atoi(flag) != 0;
   if (const char *flag = std::getenv("LLMCP_B200_GEMM"))
     use_tensor_cores_ = std::string(flag) != "dp4a";
-  gemm_error_ = static_cast<int *>(alloc(4));
   check(cudaMemsetAsync(gemm_error_, 0, 4, stream_), "memset");
   generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
   check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
-  check(cudaMallocHost(&token_pinned_, 8), "cudaMallocHost");
+  check(cudaMallocHost(&token_pinned_, 16), "cudaMallocHost");
   reset_state();
   ensure_workspace(1, capacity_ - 1);
   // One throw-away decode step loads every kernel and applies its launch attributes, so that
@@ -368,7 +377,7 @@ void Engine::set_position(int64_t position) {
 
 void Engine::decode_step() {
   if (!use_graph_) {
-    run(tokens_, 1, capacity_ - 1, cos_, sin_, 0);
+    run(dec_tokens_, 1, capacity_ - 1, dec_cos_, dec_sin_, 0);
     return;
   }
   if (!decode_graph_) {
@@ -376,7 +385,7 @@ void Engine::decode_step() {
     const uint64_t before = launches_;
     check(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed), "begin capture");
     try {
-      run(tokens_, 1, capacity_ - 1, cos_, sin_, 0);
+      run(dec_tokens_, 1, capacity_ - 1, dec_cos_, dec_sin_, 0);
     } catch (...) {
       cudaStreamEndCapture(stream_, &graph);
       if (graph)
@@ -489,26 +498,42 @@ int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position,
   if (S <= 0 || position < 0 || position + S > capacity_)
     throw std::runtime_error("sequence does not fit the cache");
   ensure_workspace(S, position);
-  set_position(position);
-  check(cudaMemcpyAsync(tokens_, tokens, static_cast<size_t>(S) * 8, cudaMemcpyHostToDevice, stream_), "tokens");
   const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
-  if (cos && sin) {
-    check(cudaMemcpyAsync(cos_, cos, static_cast<size_t>(S) * row_bytes, cudaMemcpyHostToDevice, stream_), "cos");
-    check(cudaMemcpyAsync(sin_, sin, static_cast<size_t>(S) * row_bytes, cudaMemcpyHostToDevice, stream_), "sin");
-  } else {
-    check(cudaMemcpyAsync(cos_, cos_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
-    check(cudaMemcpyAsync(sin_, sin_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
-  }
-  if (S == 1)
+  if (S == 1) {
+    // One packet, one copy: position, token and the two rotary rows.
+    check(cudaStreamSynchronize(stream_), "forward"); // the pinned packet is reused
+    uint8_t *packet = reinterpret_cast<uint8_t *>(position_pinned_);
+    std::memcpy(packet, &position, 8);
+    std::memcpy(packet + 8, tokens, 8);
+    size_t bytes = 16;
+    if (cos && sin) {
+      std::memcpy(packet + 16, cos, row_bytes);
+      std::memcpy(packet + 16 + row_bytes, sin, row_bytes);
+      bytes = step_block_bytes_;
+    }
+    check(cudaMemcpyAsync(position_dev_, packet, bytes, cudaMemcpyHostToDevice, stream_), "step inputs");
+    if (!(cos && sin)) {
+      check(cudaMemcpyAsync(dec_cos_, cos_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
+      check(cudaMemcpyAsync(dec_sin_, sin_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
+    }
     decode_step();
-  else
+  } else {
+    set_position(position);
+    check(cudaMemcpyAsync(tokens_, tokens, static_cast<size_t>(S) * 8, cudaMemcpyHostToDevice, stream_), "tokens");
+    if (cos && sin) {
+      check(cudaMemcpyAsync(cos_, cos, static_cast<size_t>(S) * row_bytes, cudaMemcpyHostToDevice, stream_), "cos");
+      check(cudaMemcpyAsync(sin_, sin, static_cast<size_t>(S) * row_bytes, cudaMemcpyHostToDevice, stream_), "sin");
+    } else {
+      check(cudaMemcpyAsync(cos_, cos_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
+      check(cudaMemcpyAsync(sin_, sin_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
+    }
     run(tokens_, S, position, cos_, sin_, 0);
+  }
   if (logits_host)
     check(cudaMemcpyAsync(logits_pinned_, logits_, static_cast<size_t>(c.vocab) * 4, cudaMemcpyDeviceToHost, stream_), "logits");
-  check(cudaMemcpyAsync(token_pinned_, next_token_, 8, cudaMemcpyDeviceToHost, stream_), "argmax");
-  check(cudaMemcpyAsync(position_pinned_, gemm_error_, 4, cudaMemcpyDeviceToHost, stream_), "gemm status");
+  check(cudaMemcpyAsync(token_pinned_, next_token_, 16, cudaMemcpyDeviceToHost, stream_), "argmax and GEMM status");
   check(cudaStreamSynchronize(stream_), "forward");
-  if (*reinterpret_cast<int *>(position_pinned_) != 0) {
+  if (*reinterpret_cast<const int *>(token_pinned_ + 1) != 0) {
     cudaMemsetAsync(gemm_error_, 0, 4, stream_);
     throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
   }
@@ -526,11 +551,11 @@ void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int6
     throw std::runtime_error("rotary dimension too large");
   set_position(position);
   *token_pinned_ = first_token;
-  check(cudaMemcpyAsync(tokens_, token_pinned_, 8, cudaMemcpyHostToDevice, stream_), "first token");
+  check(cudaMemcpyAsync(dec_tokens_, token_pinned_, 8, cudaMemcpyHostToDevice, stream_), "first token");
   check(cudaMemsetAsync(step_dev_, 0, 8, stream_), "step counter");
   const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
-  check(cudaMemcpyAsync(cos_, cos_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
-  check(cudaMemcpyAsync(sin_, sin_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
+  check(cudaMemcpyAsync(dec_cos_, cos_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
+  check(cudaMemcpyAsync(dec_sin_, sin_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
   cudaEvent_t begin, end;
   check(cudaEventCreate(&begin), "event");
   check(cudaEventCreate(&end), "event");
@@ -538,8 +563,8 @@ void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int6
   const int threads = static_cast<int>((c.rotary + 31) / 32 * 32);
   for (int64_t i = 0; i < steps; ++i) {
     decode_step();
-    launch_chained(advance_kernel, dim3(1), dim3(threads), 0, stream_, next_token_, tokens_, generated_, step_dev_, position_dev_, cos_table_,
-                                               sin_table_, cos_, sin_, static_cast<int>(c.rotary), capacity_);
+    launch_chained(advance_kernel, dim3(1), dim3(threads), 0, stream_, next_token_, dec_tokens_, generated_, step_dev_, position_dev_, cos_table_,
+                                               sin_table_, dec_cos_, dec_sin_, static_cast<int>(c.rotary), capacity_);
     launches_ += 1;
   }
   check(cudaEventRecord(end, stream_), "event");

@@ -132,8 +132,12 @@ private:
   float *logits_pinned_ = nullptr;
   int64_t *token_pinned_ = nullptr;
   int64_t *position_dev_ = nullptr; // device scalar: start position of the running call
+  // Inputs of the one-token step behind position_dev_ in one device block: token, cos row, sin row.
+  int64_t *dec_tokens_ = nullptr;
+  float *dec_cos_ = nullptr, *dec_sin_ = nullptr;
+  size_t step_block_bytes_ = 0;
   int64_t *step_dev_ = nullptr;     // device scalar: index into generated_
-  int64_t *position_pinned_ = nullptr;
+  int64_t *position_pinned_ = nullptr; // pinned packet with the layout of the block at position_dev_
   cudaGraphExec_t decode_graph_ = nullptr;
   uint64_t decode_graph_launches_ = 0;
   bool use_graph_ = true;
