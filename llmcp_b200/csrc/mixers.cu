@@ -820,6 +820,21 @@ attn_scores_block_kernel(const uint16_t *__restrict__ qn, const uint16_t *__rest
   }
 }
 
+// Bounded wait for a phase of a value-stage mbarrier; false when the limit ran out.
+__device__ __forceinline__ bool value_wait(uint64_t *bar, uint32_t parity) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(bar));
+  for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+    uint32_t done;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(done)
+                 : "r"(addr), "r"(parity)
+                 : "memory");
+    if (done)
+      return true;
+  }
+  return false;
+}
+
 // grid: (head, token); block: hd rounded up to a warp multiple.
 // Shared memory: the row's scores (turned into probabilities in place), then per key tile the
 // running maximum and the correction factor.  The maxima, corrections and probabilities are
@@ -845,6 +860,38 @@ __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint
   float *c_sm = m_sm + (static_cast<int>(score_stride) + kKeyTile - 1) / kKeyTile;
   const float *srow = scores + (t * nh + h) * score_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+
+  // Value rows (32 keys x hd bf16, contiguous in the cache) stream through a ring of
+  // shared-memory stages, one bulk copy per stage that signals the stage's mbarrier.  The first
+  // stages are requested here, so that they travel while the probabilities are being formed.
+  const bool bulk = (hd & 7) == 0;
+  const uint16_t *vbase = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd;
+  const int used_floats = static_cast<int>(c_sm - comb_sm) + (static_cast<int>(score_stride) + kKeyTile - 1) / kKeyTile;
+  uint16_t *v_sm = reinterpret_cast<uint16_t *>(comb_sm + (used_floats + 3) / 4 * 4);
+  const int stage_elems = kValueTile * hd;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(v_sm + kValueStages * stage_elems);
+  const int value_tiles = (total + kValueTile - 1) / kValueTile;
+  auto request = [&](int tile) {
+    if (threadIdx.x == 0 && tile < value_tiles) {
+      const uint32_t bytes = static_cast<uint32_t>(min(kValueTile, total - tile * kValueTile) * hd * 2);
+      const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(bars + tile % kValueStages));
+      const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(v_sm + (tile % kValueStages) * stage_elems));
+      // generic-proxy reads of the stage (before the barrier in front of this call) stay ahead of the copy
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                   "l"(vbase + static_cast<int64_t>(tile) * stage_elems), "r"(bytes), "r"(bar)
+                   : "memory");
+    }
+  };
+  if (bulk && threadIdx.x == 0) {
+    for (int s = 0; s < kValueStages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(bars + s)))
+                   : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int tile = 0; tile < kValueStages - 1; ++tile)
+      request(tile);
+  }
 
   for (int j = threadIdx.x; j < total; j += blockDim.x)
     p_sm[j] = srow[j];
@@ -875,59 +922,83 @@ __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint
     p_sm[j] = d_exp(__fsub_rn(p_sm[j], m_sm[j / kKeyTile]));
   __syncthreads();
 
-  const uint16_t *vbase = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd;
   float acc = 0.0f, sum = 0.0f;
-  if ((hd & 7) == 0) {
-    // Value rows stream through a ring of shared-memory stages filled by cp.async, deep enough
-    // that the ordered accumulation (one dependent add per key) never waits for memory.
-    const int used_floats = static_cast<int>(c_sm - comb_sm) + (static_cast<int>(score_stride) + kKeyTile - 1) / kKeyTile;
-    uint16_t *v_sm = reinterpret_cast<uint16_t *>(comb_sm + (used_floats + 3) / 4 * 4);
-    const int stage_elems = kValueTile * hd;
-    const int pieces = stage_elems >> 3; // 16-byte pieces per stage
-    const int value_tiles = (total + kValueTile - 1) / kValueTile;
-    auto issue = [&](int tile) {
-      if (tile < value_tiles) {
-        const int rows = min(kValueTile, total - tile * kValueTile);
-        const uint16_t *src = vbase + static_cast<int64_t>(tile) * stage_elems;
-        uint16_t *dst = v_sm + (tile % kValueStages) * stage_elems;
-        for (int i = threadIdx.x; i < (rows * hd) >> 3; i += blockDim.x) {
-          const uint32_t saddr = static_cast<uint32_t>(__cvta_generic_to_shared(dst + i * 8));
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + i * 8) : "memory");
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    (void)pieces;
-    for (int tile = 0; tile < kValueStages - 1; ++tile)
-      issue(tile);
-    for (int tile = 0; tile < value_tiles; ++tile) {
-      asm volatile("cp.async.wait_group %0;" ::"n"(kValueStages - 2) : "memory");
-      __syncthreads(); // stage `tile` has landed for everyone; stage `tile - 1` is free again
-      issue(tile + kValueStages - 1);
-      const uint16_t *rows = v_sm + (tile % kValueStages) * stage_elems + (active ? d : 0);
+  if (bulk) {
+    // Shared memory serves one wavefront per cycle, and with a thread per dimension every key
+    // cost sixteen of them (eight warps, a probability and a 64-byte value piece each).  So the
+    // first hd / 2 threads take two neighbouring dimensions each (one 32-bit load per key, a
+    // full 128-byte wavefront per warp) and read the probabilities four at a time; the last
+    // thread of the block keeps the denominator, which every thread used to repeat.  Per
+    // dimension the operations and their order are unchanged.
+    const int pair_threads = hd >> 1;
+    const bool accumulates = static_cast<int>(threadIdx.x) < pair_threads;
+    const bool sums = threadIdx.x == blockDim.x - 1; // blockDim.x >= hd, so never an accumulating thread
+    float acc0 = 0.0f, acc1 = 0.0f;
+    bool ok = true;
+    int tile = 0;
+    for (; tile < value_tiles; ++tile) {
+      ok = value_wait(&bars[tile % kValueStages], (tile / kValueStages) & 1);
+      // Stage `tile` has landed; after the barrier everyone has left stage `tile - 1`, which
+      // the copy of tile + kValueStages - 1 may then overwrite.
+      ok = __syncthreads_and(ok);
+      if (!ok)
+        break;
+      request(tile + kValueStages - 1);
       const int first = tile * kValueTile;
-      if ((first & (kKeyTile - 1)) == 0) {
-        const float correction = c_sm[first / kKeyTile];
-        acc = __fmul_rn(acc, correction);
-        sum = __fmul_rn(sum, correction);
-      }
+      const bool corrected = (first & (kKeyTile - 1)) == 0;
+      const float correction = corrected ? c_sm[first / kKeyTile] : 1.0f;
       const int count = min(kValueTile, total - first);
-      if (count == kValueTile) {
+      if (accumulates) {
+        const uint32_t *rows =
+            reinterpret_cast<const uint32_t *>(v_sm + (tile % kValueStages) * stage_elems) + threadIdx.x;
+        if (corrected) {
+          acc0 = __fmul_rn(acc0, correction);
+          acc1 = __fmul_rn(acc1, correction);
+        }
+        if (count == kValueTile) {
 #pragma unroll
-        for (int u = 0; u < kValueTile; ++u) {
-          const float p = p_sm[first + u];
-          sum = __fadd_rn(sum, p);
-          acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(rows[u * hd])));
+          for (int q = 0; q < kValueTile / 4; ++q) {
+            const float4 p4 = *reinterpret_cast<const float4 *>(p_sm + first + 4 * q);
+            const float pv[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const uint32_t pair = rows[(4 * q + u) * pair_threads];
+              acc0 = __fadd_rn(acc0, __fmul_rn(pv[u], __uint_as_float(pair << 16)));
+              acc1 = __fadd_rn(acc1, __fmul_rn(pv[u], __uint_as_float(pair & 0xffff0000u)));
+            }
+          }
+        } else {
+          for (int u = 0; u < count; ++u) {
+            const float p = p_sm[first + u];
+            const uint32_t pair = rows[u * pair_threads];
+            acc0 = __fadd_rn(acc0, __fmul_rn(p, __uint_as_float(pair << 16)));
+            acc1 = __fadd_rn(acc1, __fmul_rn(p, __uint_as_float(pair & 0xffff0000u)));
+          }
         }
-      } else {
-        for (int u = 0; u < count; ++u) {
-          const float p = p_sm[first + u];
-          sum = __fadd_rn(sum, p);
-          acc = __fadd_rn(acc, __fmul_rn(p, bf16_to_f32(rows[u * hd])));
-        }
+      } else if (sums) {
+        if (corrected)
+          sum = __fmul_rn(sum, correction);
+        for (int u = 0; u < count; ++u)
+          sum = __fadd_rn(sum, p_sm[first + u]);
       }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (!ok) {
+      // A copy did not arrive within the limit: give the copies still in flight one more
+      // bounded chance to land before the CTA leaves, and report through the result.
+      for (int pending = tile; pending < min(value_tiles, tile + kValueStages - 1); ++pending)
+        value_wait(&bars[pending % kValueStages], (pending / kValueStages) & 1);
+      acc0 = acc1 = sum = __int_as_float(0x7fc00000);
+    }
+    __syncthreads(); // probabilities and value stages are dead: their space carries the results across
+    if (accumulates) {
+      comb_sm[2 * threadIdx.x] = acc0;
+      comb_sm[2 * threadIdx.x + 1] = acc1;
+    }
+    if (sums)
+      comb_sm[hd] = sum;
+    __syncthreads();
+    acc = comb_sm[active ? d : 0];
+    sum = comb_sm[hd];
   } else {
     const uint16_t *vc = vbase + (active ? d : 0);
     for (int j = 0; j < total; ++j) {
@@ -1174,7 +1245,7 @@ static size_t combine_smem_bytes(int64_t score_stride, int hd) {
   size_t bytes = ((static_cast<size_t>(score_stride) + 3) / 4 * 4 + 2 * tiles) * sizeof(float);
   bytes = (bytes + 15) / 16 * 16;
   if ((hd & 7) == 0)
-    bytes += static_cast<size_t>(kValueStages) * kValueTile * hd * sizeof(uint16_t);
+    bytes += static_cast<size_t>(kValueStages) * kValueTile * hd * sizeof(uint16_t) + kValueStages * sizeof(uint64_t);
   return bytes;
 }
 
