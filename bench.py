@@ -238,6 +238,29 @@ def gemm_alone(L, torch, repeats=5):
     return us, 2.0 * GEMM_M * GEMM_N * GEMM_K / us / 1e6
 
 
+def attention_alone(L, repeats=4, position=1030):
+    """One-token attention of a full-attention layer (16 query heads, 4 KV heads, head_dim 256)
+    against `position` cached keys, through the operator entry point with host buffers: the small
+    case the profiler captures for the decode attention kernels.  Returns the last output row."""
+    rng = np.random.default_rng(SEED)
+    nh, nkv, hd, rot, cap = 16, 4, 256, 64, position + 70
+
+    def bf16(a):
+        bits = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+        return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+
+    qg = bf16(rng.standard_normal((1, nh * 2 * hd)))
+    k = bf16(rng.standard_normal((1, nkv * hd)))
+    v = bf16(rng.standard_normal((1, nkv * hd)))
+    norm = np.zeros(hd, dtype=np.uint16)
+    cos, sin = L.make_cos_sin(position, rot, 1e7)
+    cache = bf16(rng.standard_normal((2, nkv, cap, hd)))
+    out = None
+    for _ in range(repeats):
+        out, _ = L.ops.attention(qg, k, v, norm, norm, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
+    return out[0]
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -245,8 +268,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--cpu-steps", type=int, default=8, help="decode steps of the CPU baseline sample")
-    parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm"],
-                        help="gemv / gemm: run just that kernel on a small case (what the profiler captures)")
+    parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm", "attn"],
+                        help="gemv / gemm / attn: run just that kernel on a small case (what the profiler captures)")
     args = parser.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
@@ -289,6 +312,11 @@ def main():
     if args.only == "gemv":
         gbs, us, count = gemv_roofline(L, torch, local_rank, ring=6, sweeps=2)
         print(json.dumps({"only": "gemv", "shape": [1, GEMV_N, GEMV_K], "us_per_launch": us, "gbs": gbs, "launches": count}))
+        return
+    if args.only == "attn":
+        row = attention_alone(L)
+        print(json.dumps({"only": "attn", "shape": {"heads": 16, "kv_heads": 4, "head_dim": 256, "keys": 1031},
+                          "checksum": int(row.astype(np.int64).sum())}))
         return
     if args.only == "gemm":
         us, tops = gemm_alone(L, torch)

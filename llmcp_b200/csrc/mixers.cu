@@ -738,6 +738,90 @@ __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16
   scores[(t * nh + kvh * group + g) * score_stride + start + j] = __fmul_rn(dot, scale);
 }
 
+// The scores of one query token against 32 keys per CTA, for head dimensions that are a multiple
+// of eight (the one-token step).  Compared with the kernel above: half the keys per CTA, so twice
+// as many SMs fetch key rows; a thread's 16-byte pieces of the tile are all requested before the
+// first is converted; rows are hd + 4 floats apart, so that keys and queries are read four
+// dimensions at a time (a quarter warp's eight rows fall on distinct banks).  The dot product
+// is the same ascending-d chain  dot = dot + q[d] * k[d].
+// grid: (32-key tile, kv head, token); block: group * 32 threads (query head x key).
+constexpr int kScoreKeys = 32;
+
+__global__ void __launch_bounds__(256)
+attn_scores_keys32_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
+                          const int64_t *__restrict__ position_ptr, int nh, int nkv, int hd, int64_t cap,
+                          int64_t score_stride, float *__restrict__ scores) {
+  extern __shared__ __align__(16) unsigned char att_sm[];
+  grid_dependency_sync();
+  const int64_t position = *position_ptr;
+  const int group = nh / nkv;
+  const int64_t t = blockIdx.z;
+  const int kvh = blockIdx.y;
+  const int64_t query_end = position + t + 1;
+  const int64_t start = static_cast<int64_t>(blockIdx.x) * kScoreKeys;
+  if (start >= query_end)
+    return;
+  const int keys = static_cast<int>(min(static_cast<int64_t>(kScoreKeys), query_end - start));
+  const int kstride = hd + 4;
+  float *k_sm = reinterpret_cast<float *>(att_sm); // [32][hd + 4]
+  float *q_sm = k_sm + kScoreKeys * kstride;       // [group][hd]
+  const uint4 *kc = reinterpret_cast<const uint4 *>(cache + (static_cast<int64_t>(kvh) * cap + start) * hd);
+  const int per_row = hd >> 3; // 16-byte pieces per key
+  const int pieces = keys * per_row;
+  auto unpack = [](float *dst, const uint4 &raw) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float4 lo, hi;
+    lo.x = __uint_as_float(w[0] << 16);
+    lo.y = __uint_as_float(w[0] & 0xffff0000u);
+    lo.z = __uint_as_float(w[1] << 16);
+    lo.w = __uint_as_float(w[1] & 0xffff0000u);
+    hi.x = __uint_as_float(w[2] << 16);
+    hi.y = __uint_as_float(w[2] & 0xffff0000u);
+    hi.z = __uint_as_float(w[3] << 16);
+    hi.w = __uint_as_float(w[3] & 0xffff0000u);
+    reinterpret_cast<float4 *>(dst)[0] = lo;
+    reinterpret_cast<float4 *>(dst)[1] = hi;
+  };
+  for (int base = 0; base < pieces; base += 8 * blockDim.x) {
+    uint4 raw[8];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int i = base + n * blockDim.x + threadIdx.x;
+      if (i < pieces)
+        raw[n] = kc[i];
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int i = base + n * blockDim.x + threadIdx.x;
+      if (i < pieces) {
+        const int row = i / per_row, piece = i - row * per_row;
+        unpack(k_sm + row * kstride + piece * 8, raw[n]);
+      }
+    }
+  }
+  const uint4 *qc = reinterpret_cast<const uint4 *>(qn + (t * nh + kvh * group) * hd);
+  for (int i = threadIdx.x; i < group * per_row; i += blockDim.x)
+    unpack(q_sm + i * 8, qc[i]);
+  __syncthreads();
+  const int j = threadIdx.x % kScoreKeys;
+  const int g = threadIdx.x / kScoreKeys;
+  if (j >= keys || g >= group)
+    return;
+  const float4 *kr = reinterpret_cast<const float4 *>(k_sm + j * kstride);
+  const float4 *qr = reinterpret_cast<const float4 *>(q_sm + g * hd);
+  float dot = 0.0f;
+#pragma unroll 8
+  for (int d4 = 0; d4 < (hd >> 2); ++d4) {
+    const float4 kv = kr[d4], qv = qr[d4];
+    dot = __fadd_rn(dot, __fmul_rn(qv.x, kv.x));
+    dot = __fadd_rn(dot, __fmul_rn(qv.y, kv.y));
+    dot = __fadd_rn(dot, __fmul_rn(qv.z, kv.z));
+    dot = __fadd_rn(dot, __fmul_rn(qv.w, kv.w));
+  }
+  const float scale = __fdiv_rn(1.0f, __fsqrt_rn(static_cast<float>(hd)));
+  scores[(t * nh + kvh * group + g) * score_stride + start + j] = __fmul_rn(dot, scale);
+}
+
 // The same scores for a block of kScoreTokens query tokens per CTA (prefill): the key tile is
 // brought into shared memory once per block instead of once per token, and a thread advances the
 // dot products of four tokens together, reading its key row four values at a time.  Every dot
@@ -1306,6 +1390,11 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
                static_cast<unsigned>((S + kScoreTokens - 1) / kScoreTokens));
     launch_chained(attn_scores_block_kernel, dim3(bgrid), dim3(group * kKeyTile), block_smem, stream, qn, cache, position_dev, S,
                    nh, nkv, hd, cap, score_stride, scores);
+  } else if ((hd & 7) == 0 && group * kScoreKeys <= 256 && (static_cast<size_t>(kScoreKeys) * (hd + 4) + static_cast<size_t>(group) * hd) * sizeof(float) <= 48 * 1024) {
+    const size_t keys32_smem = (static_cast<size_t>(kScoreKeys) * (hd + 4) + static_cast<size_t>(group) * hd) * sizeof(float);
+    dim3 sgrid(static_cast<unsigned>((max_position + S + kScoreKeys - 1) / kScoreKeys), nkv, static_cast<unsigned>(S));
+    launch_chained(attn_scores_keys32_kernel, dim3(sgrid), dim3(group * kScoreKeys), keys32_smem, stream, qn, cache, position_dev, nh,
+                   nkv, hd, cap, score_stride, scores);
   } else {
     dim3 sgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
     launch_chained(attn_scores_kernel, dim3(sgrid), dim3(group * kKeyTile), smem, stream, qn, cache, position_dev, nh, nkv, hd,
