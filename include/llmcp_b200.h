@@ -212,6 +212,12 @@ int llmcp_b200_engine_reset(void *engine);
  * (vocab f32, may be NULL) and argmax (may be NULL) of the last position. */
 int llmcp_b200_engine_forward(void *engine, const int64_t *tokens, int64_t S, int64_t position, float *logits,
                               int64_t *argmax);
+/* The same forward with the logits of every position: `logits` holds S x vocab f32, row s for
+ * token s.  This is the result of the tensor-returning `llmcp_model` function that the
+ * reference builds beside the two AOT entries (lib/Model/ModelBuilder.cpp:406-438; its runtime
+ * never resolves it): final norm over all rows, then an S x vocab x hidden Q8 contraction on
+ * the tensor cores.  Generation state advances as in llmcp_b200_engine_forward. */
+int llmcp_b200_engine_forward_all(void *engine, const int64_t *tokens, int64_t S, int64_t position, float *logits);
 /* The decode loop of tools/llmcp-benchmark/llmcp-benchmark.cpp:94-101 kept on the device:
  * token, argmax and state never leave HBM.  out_tokens: `steps` ids; device_ms: CUDA-event
  * time of the loop (may be NULL). */

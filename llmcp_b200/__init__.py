@@ -471,6 +471,14 @@ class Engine:
                                                _p(logits), C.byref(argmax)))
         return logits, int(argmax.value)
 
+    def forward_all(self, tokens, position):
+        """Logits of every position, ``[len(tokens), vocab]`` float32 (llmcp_b200_engine_forward_all)."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        logits = np.empty((tokens.shape[0], self.dims.vocab), dtype=np.float32)
+        _check(lib().llmcp_b200_engine_forward_all(self.handle, _p(tokens), _i(tokens.shape[0]), _i(position),
+                                                   _p(logits)))
+        return logits
+
     def generate(self, first_token, position, steps):
         out = np.empty(steps, dtype=np.int64)
         ms = C.c_float(0)

@@ -819,6 +819,15 @@ int llmcp_b200_engine_forward(void *engine, const int64_t *tokens, int64_t S, in
   });
 }
 
+int llmcp_b200_engine_forward_all(void *engine, const int64_t *tokens, int64_t S, int64_t position, float *logits) {
+  return guarded_async([&] {
+    Engine &e = *static_cast<Engine *>(engine);
+    const uint64_t before = e.launches();
+    e.forward_all_host(tokens, S, position, logits);
+    g_launches += e.launches() - before;
+  });
+}
+
 int llmcp_b200_engine_generate(void *engine, int64_t first_token, int64_t position, int64_t steps, int64_t *out_tokens,
                                float *device_ms) {
   return guarded_async([&] {

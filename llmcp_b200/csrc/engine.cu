@@ -479,6 +479,16 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
     pending = true;
   }
+  if (all_logits_) {
+    // Every position's logits, what the tensor-returning `llmcp_model` function computes
+    // (ModelBuilder.cpp:406-438): final norm over all rows, then one S x vocab x hidden contraction.
+    check(launch_rms_norm(hidden_[cur], pending ? mlp_out_ : nullptr, S, H, final_norm_.data, final_norm_.dtype, c.eps, 1,
+                          nullptr, branch_, aq_, as_, stream_), "final rms_norm, all rows");
+    const LinearJob all = {&embed_, all_logits_, kF32, kNone};
+    run_linears(this, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious,
+                S > 1 && use_tensor_cores_ ? gemm_error_ : nullptr);
+    launches_ += 1;
+  }
   // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
   const uint16_t *last = hidden_[cur] + (S - 1) * H;
   check(launch_rms_norm(last, pending ? mlp_out_ + (S - 1) * H : nullptr, 1, H, final_norm_.data, final_norm_.dtype,
@@ -540,6 +550,42 @@ int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position,
   if (logits_host)
     std::memcpy(logits_host, logits_pinned_, static_cast<size_t>(c.vocab) * 4);
   return *token_pinned_;
+}
+
+void Engine::forward_all_host(const int64_t *tokens, int64_t S, int64_t position, float *logits_host) {
+  const ModelDims &c = dims_;
+  check(cudaSetDevice(device_), "cudaSetDevice");
+  if (S <= 0 || position < 0 || position + S > capacity_)
+    throw std::runtime_error("sequence does not fit the cache");
+  if (!logits_host)
+    throw std::runtime_error("forward_all needs a logits buffer of S x vocab floats");
+  ensure_workspace(S, position);
+  const size_t bytes = static_cast<size_t>(S) * c.vocab * sizeof(float);
+  float *device_rows = nullptr;
+  check(cudaMalloc(&device_rows, bytes), "cudaMalloc(all-position logits)");
+  try {
+    set_position(position);
+    check(cudaMemcpyAsync(tokens_, tokens, static_cast<size_t>(S) * 8, cudaMemcpyHostToDevice, stream_), "tokens");
+    const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
+    check(cudaMemcpyAsync(cos_, cos_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
+    check(cudaMemcpyAsync(sin_, sin_table_ + position * c.rotary, static_cast<size_t>(S) * row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
+    all_logits_ = device_rows;
+    run(tokens_, S, position, cos_, sin_, 0);
+    all_logits_ = nullptr;
+    check(cudaMemcpyAsync(logits_host, device_rows, bytes, cudaMemcpyDeviceToHost, stream_), "all-position logits");
+    check(cudaMemcpyAsync(token_pinned_, next_token_, 16, cudaMemcpyDeviceToHost, stream_), "argmax and GEMM status");
+    check(cudaStreamSynchronize(stream_), "forward_all");
+  } catch (...) {
+    all_logits_ = nullptr;
+    cudaStreamSynchronize(stream_);
+    cudaFree(device_rows);
+    throw;
+  }
+  cudaFree(device_rows);
+  if (*reinterpret_cast<const int *>(token_pinned_ + 1) != 0) {
+    cudaMemsetAsync(gemm_error_, 0, 4, stream_);
+    throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
+  }
 }
 
 void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int64_t *out_tokens_host, float *device_ms) {

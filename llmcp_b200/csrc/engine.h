@@ -63,6 +63,11 @@ public:
   int64_t forward_host(const int64_t *tokens, int64_t S, int64_t position, const float *cos, const float *sin,
                        float *logits_host);
 
+  // The same forward, but the logits of every position are written: logits_host holds
+  // S x vocab floats (the result of the reference's tensor-returning `llmcp_model`,
+  // lib/Model/ModelBuilder.cpp:406-438).  State advances exactly as in forward_host.
+  void forward_all_host(const int64_t *tokens, int64_t S, int64_t position, float *logits_host);
+
   // Greedy generation that never leaves the device: feeds `first_token` at `position`, then
   // each step's argmax to the next, for `steps` steps.  out_tokens_host (steps entries) gets
   // the argmax of every step; device_ms, if not null, the CUDA-event time of the loop.
@@ -125,6 +130,7 @@ private:
   // outputs
   uint16_t *final_hidden_ = nullptr; // [hidden] last row after the final norm
   float *logits_ = nullptr;          // [vocab]
+  float *all_logits_ = nullptr;      // [S, vocab] while forward_all_host runs, else null
   float *argmax_v_ = nullptr;
   int64_t *argmax_i_ = nullptr;
   int64_t *next_token_ = nullptr; // device scalar

@@ -101,6 +101,29 @@ def test_packed_checkpoint_matches_oracle(tmp_path):
     run_both(d, 0, [5, 200, 31, 7, 7, 9], steps=5, capacity=16, data=data)
 
 
+def test_all_position_logits_match_oracle():
+    """llmcp_b200_engine_forward_all: row s equals the oracle's logits for the prefix of s + 1
+    tokens, bit for bit (the S x vocab contraction runs on the tensor cores, the oracle's last
+    row is a GEMV); a one-token call continues the sequence through the GEMV path."""
+    d = L.default_dims().copy(**SMALL)
+    data = L.synthetic_container(d, 5)
+    arena = L.Arena().from_buffer(data)
+    model = oracle.Model(data, arena.manifest, oracle_dims(d))
+    prompt = [17, 5, 900, 2047, 0, 33, 33, 1200, 64]
+    engine = L.Engine(data, d, capacity=16)
+    rows = engine.forward_all(prompt, 0)
+    assert rows.shape == (len(prompt), d.vocab) and np.isfinite(rows).all()
+    for s in range(len(prompt)):
+        want = model.forward(model.new_state(16), prompt[:s + 1], 0)
+        assert np.array_equal(rows[s].view(np.uint32), want.view(np.uint32)), s
+    state = model.new_state(16)
+    model.forward(state, prompt, 0)
+    want = model.forward(state, [77], len(prompt))
+    step = engine.forward_all([77], len(prompt))
+    assert np.array_equal(step[0].view(np.uint32), want.view(np.uint32))
+    engine.close()
+
+
 def test_one_token_prompt_uses_decode_entry():
     d = L.default_dims().copy(**TINY)
     run_both(d, 3, [7], steps=3, capacity=8)  # AotRuntime.cpp:116: sequence == 1 -> decode entry
