@@ -850,22 +850,47 @@ attn_scores_block_kernel(const uint16_t *__restrict__ qn, const uint16_t *__rest
   float *q_sm = k_sm + kKeyTile * kstride;          // [tokens][group][hd]
   const uint16_t *kc = cache + (static_cast<int64_t>(kvh) * cap + start) * hd;
   const int per_row = hd >> 3; // 16-byte pieces per key (hd % 8 == 0)
-  for (int i = threadIdx.x; i < kKeyTile * per_row; i += blockDim.x) {
-    const int row = i / per_row, piece = i - row * per_row;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (row < keys)
-      raw = reinterpret_cast<const uint4 *>(kc)[i];
-    float *dst = k_sm + row * kstride + piece * 8;
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  auto unpack = [](float *dst, const uint4 &raw) {
+    float4 lo, hi;
+    lo.x = __uint_as_float(raw.x << 16);
+    lo.y = __uint_as_float(raw.x & 0xffff0000u);
+    lo.z = __uint_as_float(raw.y << 16);
+    lo.w = __uint_as_float(raw.y & 0xffff0000u);
+    hi.x = __uint_as_float(raw.z << 16);
+    hi.y = __uint_as_float(raw.z & 0xffff0000u);
+    hi.z = __uint_as_float(raw.w << 16);
+    hi.w = __uint_as_float(raw.w & 0xffff0000u);
+    reinterpret_cast<float4 *>(dst)[0] = lo;
+    reinterpret_cast<float4 *>(dst)[1] = hi;
+  };
+  // A thread's pieces are all requested before the first is converted: one round trip to
+  // memory for the tile instead of one per piece.
+  const int key_pieces = kKeyTile * per_row;
+  for (int base = 0; base < key_pieces; base += 8 * blockDim.x) {
+    uint4 raw[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      dst[2 * u] = __uint_as_float(w[u] << 16);
-      dst[2 * u + 1] = __uint_as_float(w[u] & 0xffff0000u);
+    for (int n = 0; n < 8; ++n) {
+      const int i = base + n * blockDim.x + threadIdx.x;
+      raw[n] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < key_pieces && i / per_row < keys)
+        raw[n] = reinterpret_cast<const uint4 *>(kc)[i];
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int i = base + n * blockDim.x + threadIdx.x;
+      if (i < key_pieces) {
+        const int row = i / per_row, piece = i - row * per_row;
+        unpack(k_sm + row * kstride + piece * 8, raw[n]);
+      }
     }
   }
-  for (int i = threadIdx.x; i < kScoreTokens * group * hd; i += blockDim.x) {
-    const int tb = i / (group * hd), rest = i - tb * group * hd;
-    q_sm[i] = tb < tokens ? bf16_to_f32(qn[((t0 + tb) * nh + kvh * group) * hd + rest]) : 0.0f;
+  const int token_pieces = group * per_row; // 16-byte pieces of one token's query heads
+  for (int i = threadIdx.x; i < kScoreTokens * token_pieces; i += blockDim.x) {
+    const int tb = i / token_pieces, rest = i - tb * token_pieces;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (tb < tokens)
+      raw = reinterpret_cast<const uint4 *>(qn + ((t0 + tb) * nh + kvh * group) * hd)[rest];
+    unpack(q_sm + i * 8, raw);
   }
   __syncthreads();
   const int j = threadIdx.x % kKeyTile;
@@ -1158,6 +1183,34 @@ attn_combine_block_kernel(const float *__restrict__ scores, const uint16_t *__re
   const bool consumer = d < pairs;        // dimensions 2 d and 2 d + 1
   const bool keeper = d >= pairs && lane < tokens; // the extra warp: lane tb keeps token tb's denominator
 
+  // Value rows arrive by one bulk copy per 32-key stage (see the one-token kernel); the first
+  // stages are requested before the probabilities are formed.  The first lane of the extra
+  // warp issues the requests.
+  const uint16_t *vbase = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd;
+  const int stage_elems = kValueTile * hd;
+  const int value_tiles = (total_last + kValueTile - 1) / kValueTile;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(v_sm + kBlockStages * stage_elems);
+  auto request = [&](int tile) {
+    if (d == pairs && tile < value_tiles) {
+      const uint32_t bytes = static_cast<uint32_t>(min(kValueTile, total_last - tile * kValueTile) * hd * 2);
+      const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(bars + tile % kBlockStages));
+      const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(v_sm + (tile % kBlockStages) * stage_elems));
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                   "l"(vbase + static_cast<int64_t>(tile) * stage_elems), "r"(bytes), "r"(bar)
+                   : "memory");
+    }
+  };
+  if (d == pairs) {
+    for (int s = 0; s < kBlockStages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(bars + s)))
+                   : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int tile = 0; tile < kBlockStages - 1; ++tile)
+      request(tile);
+  }
+
   // probabilities of every token of the block (as in the one-token kernel)
   for (int tb = 0; tb < tokens; ++tb) {
     const float *srow = scores + ((t0 + tb) * nh + h) * score_stride;
@@ -1199,32 +1252,20 @@ attn_combine_block_kernel(const float *__restrict__ scores, const uint16_t *__re
   }
   __syncthreads();
 
-  const uint16_t *vbase = cache + ((static_cast<int64_t>(nkv) + kvh) * cap) * hd;
-  const int stage_elems = kValueTile * hd;
-  const int value_tiles = (total_last + kValueTile - 1) / kValueTile;
-  auto issue = [&](int tile) {
-    if (tile < value_tiles) {
-      const int rows = min(kValueTile, total_last - tile * kValueTile);
-      const uint16_t *src = vbase + static_cast<int64_t>(tile) * stage_elems;
-      uint16_t *dst = v_sm + (tile % kBlockStages) * stage_elems;
-      for (int i = threadIdx.x; i < (rows * hd) >> 3; i += blockDim.x) {
-        const uint32_t saddr = static_cast<uint32_t>(__cvta_generic_to_shared(dst + i * 8));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + i * 8) : "memory");
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
   float acc0[kCombineTokens], acc1[kCombineTokens];
 #pragma unroll
   for (int tb = 0; tb < kCombineTokens; ++tb)
     acc0[tb] = acc1[tb] = 0.0f;
   float sum = 0.0f; // keeper lanes only
-  for (int tile = 0; tile < kBlockStages - 1; ++tile)
-    issue(tile);
-  for (int tile = 0; tile < value_tiles; ++tile) {
-    asm volatile("cp.async.wait_group %0;" ::"n"(kBlockStages - 2) : "memory");
-    __syncthreads(); // stage `tile` has landed for everyone; stage `tile - 1` is free again
-    issue(tile + kBlockStages - 1);
+  bool ok = true;
+  int tile = 0;
+  for (; tile < value_tiles; ++tile) {
+    ok = value_wait(&bars[tile % kBlockStages], (tile / kBlockStages) & 1);
+    // stage `tile` has landed; after the barrier stage `tile - 1` is free for the next copy
+    ok = __syncthreads_and(ok);
+    if (!ok)
+      break;
+    request(tile + kBlockStages - 1);
     const int first = tile * kValueTile;
     const int count = min(kValueTile, total_last - first);
     if (consumer) {
@@ -1284,7 +1325,13 @@ attn_combine_block_kernel(const float *__restrict__ scores, const uint16_t *__re
         sum = __fadd_rn(sum, p_sm[tb * p_stride + first + u]);
     }
   }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (!ok) {
+    // A copy did not arrive within the limit: one more bounded chance for the copies still in
+    // flight to land before the CTA leaves; the result reports it as NaN.
+    for (int pending = tile; pending < min(value_tiles, tile + kBlockStages - 1); ++pending)
+      value_wait(&bars[pending % kBlockStages], (pending / kBlockStages) & 1);
+    sum = __int_as_float(0x7fc00000);
+  }
   if (keeper)
     sum_sm[lane] = sum;
   __syncthreads();
@@ -1404,7 +1451,8 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   const int p_stride = static_cast<int>((score_stride + 3) / 4 * 4);
   const int tile_slots = (p_stride + kKeyTile - 1) / kKeyTile;
   const size_t block_csmem = (static_cast<size_t>(kCombineTokens) * (p_stride + 2 * tile_slots + 1)) * sizeof(float) + 16 +
-                             static_cast<size_t>(kBlockStages) * kValueTile * hd * sizeof(uint16_t);
+                             static_cast<size_t>(kBlockStages) * kValueTile * hd * sizeof(uint16_t) +
+                             kBlockStages * sizeof(uint64_t);
   if (S >= 4 && hd == 256 && block_csmem <= 200 * 1024) {
     static bool block_configured = false;
     if (!block_configured) {

@@ -290,7 +290,8 @@ def test_attention(golden):
     nh, nkv, hd, rot = 16, 4, 256, 64
     q_norm, k_norm = rand_bf16(rng, hd, scale=0.1), rand_bf16(rng, hd, scale=0.1)
     # prefill at 0; a chunk appended after it; single-token steps at 63/64/65 (tile edges) and 1024.
-    for S, pos, cap in ((70, 0, 80), (5, 64, 80), (1, 63, 80), (1, 64, 80), (1, 65, 80), (1, 1024, 1032), (130, 0, 130)):
+    for S, pos, cap in ((70, 0, 80), (5, 64, 80), (1, 63, 80), (1, 64, 80), (1, 65, 80), (1, 1024, 1032), (130, 0, 130),
+                        (300, 0, 300)):  # 300 keys: the value ring of the prefill kernel wraps twice
         qg, k, v = rand_bf16(rng, S, nh * 2 * hd), rand_bf16(rng, S, nkv * hd), rand_bf16(rng, S, nkv * hd)
         cos = np.stack([L.make_cos_sin(pos + t)[0] for t in range(S)])
         sin = np.stack([L.make_cos_sin(pos + t)[1] for t in range(S)])
