@@ -510,7 +510,10 @@ gdn_decode_step_kernel(const uint16_t *__restrict__ conv, const float *__restric
 #pragma unroll
   for (int k = 0; k < DK; ++k)
     s[k] = col[static_cast<int64_t>(k) * dv];
+  const float norm_weight = load_as_f32(norm_w, norm_w_dtype, v); // a weight: no need to wait for it either
   grid_dependency_sync(true);
+  // The gate is needed only after both chains: requested now, it arrives while they run.
+  const float gv = bf16_to_f32(gate[static_cast<int64_t>(h) * dv + v]);
   for (int d = v; d < DK; d += dv) {
     k_sm[d] = kn[kh * DK + d];
     q_sm[d] = qn[kh * DK + d];
@@ -559,10 +562,9 @@ gdn_decode_step_kernel(const uint16_t *__restrict__ conv, const float *__restric
   }
   __syncthreads();
   const int64_t element = static_cast<int64_t>(h) * dv + v;
-  const float gv = bf16_to_f32(gate[element]);
   const float silu = gate_activated ? gv : __fmul_rn(gv, d_sigmoid(gv));
   float t = __fmul_rn(xo, silu);
-  t = __fmul_rn(t, load_as_f32(norm_w, norm_w_dtype, v));
+  t = __fmul_rn(t, norm_weight);
   t = __fmul_rn(t, rstd_sm);
   const uint16_t r = f32_to_bf16(t);
   if (y)
@@ -633,6 +635,30 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
   uint16_t *dst = is_q ? qn + (t * nh + head) * hd
                        : cache + ((0 * static_cast<int64_t>(nkv) + head) * cap + position + t) * hd;
   float *tmp = prep_sm + warp_in_cta * hd;
+  // Everything the later passes read from memory (norm weight, rotary rows, the value row to be
+  // copied) is requested here, beside the input row, instead of after the serial sum.
+  constexpr int kPerLane = 8; // head dimensions up to 256
+  const bool prefetched = hd <= 32 * kPerLane;
+  const uint16_t *vsrc = v + t * nkv * hd + static_cast<int64_t>(head) * hd;
+  float w_reg[kPerLane], cos_reg[kPerLane], sin_reg[kPerLane];
+  uint16_t v_reg[kPerLane];
+  if (prefetched) {
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int d = lane + 32 * i;
+      w_reg[i] = cos_reg[i] = sin_reg[i] = 0.0f;
+      v_reg[i] = 0;
+      if (d < hd) {
+        w_reg[i] = bf16_to_f32(weight[d]);
+        if (!is_q)
+          v_reg[i] = vsrc[d];
+        if (d < rot) {
+          cos_reg[i] = cos[(row_base + t) * rot + d];
+          sin_reg[i] = sin[(row_base + t) * rot + d];
+        }
+      }
+    }
+  }
   for (int d = lane; d < hd; d += 32) {
     const float x = bf16_to_f32(src[d]);
     tmp[d] = __fmul_rn(x, x);
@@ -657,13 +683,43 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
   }
   inv = __shfl_sync(0xffffffffu, inv, 0);
   __syncwarp();
-  for (int d = lane; d < hd; d += 32) {
-    const float x = bf16_to_f32(src[d]);
-    const float centered = __fadd_rn(1.0f, bf16_to_f32(weight[d]));
-    tmp[d] = __fmul_rn(__fmul_rn(x, inv), centered);
+  if (prefetched) {
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) {
+        const float x = bf16_to_f32(src[d]);
+        tmp[d] = __fmul_rn(__fmul_rn(x, inv), __fadd_rn(1.0f, w_reg[i]));
+      }
+    }
+  } else {
+    for (int d = lane; d < hd; d += 32) {
+      const float x = bf16_to_f32(src[d]);
+      const float centered = __fadd_rn(1.0f, bf16_to_f32(weight[d]));
+      tmp[d] = __fmul_rn(__fmul_rn(x, inv), centered);
+    }
   }
   __syncwarp();
   const int half = rot / 2;
+  uint16_t *vdst = cache + ((1 * static_cast<int64_t>(nkv) + head) * cap + position + t) * hd;
+  if (prefetched) {
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) {
+        float r = tmp[d];
+        if (d < rot) {
+          const bool second = d >= half;
+          const float rotated = __fmul_rn(second ? 1.0f : -1.0f, tmp[second ? d - half : d + half]);
+          r = __fadd_rn(__fmul_rn(tmp[d], cos_reg[i]), __fmul_rn(rotated, sin_reg[i]));
+        }
+        dst[d] = f32_to_bf16(r);
+        if (!is_q)
+          vdst[d] = v_reg[i];
+      }
+    }
+    return;
+  }
   for (int d = lane; d < hd; d += 32) {
     float r = tmp[d];
     if (d < rot) {
@@ -674,8 +730,6 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
     dst[d] = f32_to_bf16(r);
   }
   if (!is_q) {
-    uint16_t *vdst = cache + ((1 * static_cast<int64_t>(nkv) + head) * cap + position + t) * hd;
-    const uint16_t *vsrc = v + t * nkv * hd + static_cast<int64_t>(head) * hd;
     for (int d = lane; d < hd; d += 32)
       vdst[d] = vsrc[d];
   }
