@@ -5,8 +5,14 @@ The reference is single-process; what shards naturally here is (a) independent s
 split across ranks with one tiny exchange step: a (max, index) reduction that reproduces the
 host argmax of tools/llmcp-benchmark/llmcp-benchmark.cpp:51-54 (the first maximum wins).
 
-``reduce_argmax`` and ``vocab_shard`` are backend-agnostic (gloo on CPU in the tests, NCCL on
-GPUs); ``ShardedLmHead`` runs the shard's GEMV and argmax with the CUDA library.
+``reduce_argmax``, ``gather_rows`` and ``vocab_shard`` are backend-agnostic (gloo on CPU in the
+tests, NCCL on GPUs); ``ShardedLmHead`` runs the shard's GEMV and argmax with the CUDA library.
+
+(c) Any Q8 ``linear`` splits the same way by output rows (``ColumnParallelLinear``): a shard is a
+contiguous byte range of the packed weight, every output element is computed by one rank with
+the unsharded arithmetic, and one all-gather assembles the row, so the result is bit-identical
+to the single-GPU product.  A split along K would change the order of the f32 additions and is
+not offered.
 """
 import ctypes as C
 
@@ -115,3 +121,72 @@ class ShardedLmHead:
             index = int(self.best.item())
             value = float(self.logits[index].item())
         return reduce_argmax(value, self.row_begin + index, group=group, device=self.device)
+
+
+def gather_rows(local, group=None):
+    """All-gather of equally sized 1-D shards (a torch tensor per rank, CPU with gloo or CUDA with
+    NCCL) into the full row, in rank order."""
+    import torch
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local
+    world = dist.get_world_size(group)
+    # Moved as bytes: nothing is computed on the way, and NCCL has no 16-bit integer type for
+    # the bf16 bit patterns.
+    raw = local.contiguous().view(torch.uint8)
+    out = torch.empty(world * raw.numel(), dtype=torch.uint8, device=local.device)
+    dist.all_gather_into_tensor(out, raw, group=group)
+    return out.view(local.dtype)
+
+
+class ColumnParallelLinear:
+    """Rows [begin, end) of a Q8 ``linear`` on this rank's GPU (one-token form, Q8Decode.cpp:131-225).
+
+    ``packed_shard`` is this rank's slice of the packed weight (``shard_packed_rows``).  ``local``
+    quantises the input row and runs the shard's GEMV with the fused epilogue; ``forward`` adds the
+    all-gather.  Outputs are bf16 bit patterns (int16 tensors) or float32.
+    """
+
+    def __init__(self, packed_shard, rows, K, device_index, y_bf16=True, activation="none"):
+        import torch
+        import llmcp_b200 as L
+        self.torch, self.L, self.lib = torch, L, L.lib()
+        self.rows, self.K, self.y_bf16 = rows, K, y_bf16
+        self.activation = L.ACTIVATIONS[activation]
+        self.device = torch.device("cuda", device_index)
+        nb = K // 32
+        with torch.cuda.device(self.device):
+            records = torch.from_numpy(np.ascontiguousarray(packed_shard)).to(self.device)
+            self.wq = torch.empty((rows, K), dtype=torch.int8, device=self.device)
+            self.wd = torch.empty((rows, nb), dtype=torch.float16, device=self.device)
+            self.aq = torch.empty(K, dtype=torch.int8, device=self.device)
+            self.scales = torch.empty(nb, dtype=torch.float32, device=self.device)
+            self.y = torch.empty(rows, dtype=torch.int16 if y_bf16 else torch.float32, device=self.device)
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            self._check(self.lib.llmcp_dev_repack_q8(self._p(records), C.c_int64(rows), C.c_int64(K),
+                                                     self._p(self.wq), self._p(self.wd), stream))
+            torch.cuda.synchronize()
+
+    @staticmethod
+    def _p(t):
+        return C.c_void_p(t.data_ptr())
+
+    def _check(self, code):
+        if code != 0:
+            raise self.L.LlmcpError(self.L.last_error())
+
+    def local(self, x_bf16_bits):
+        torch = self.torch
+        with torch.cuda.device(self.device):
+            x = torch.from_numpy(np.ascontiguousarray(x_bf16_bits, dtype=np.uint16).view(np.int16)).to(self.device)
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            self._check(self.lib.llmcp_dev_act_quant(self._p(x), 1, C.c_int64(1), C.c_int64(self.K), self._p(self.aq),
+                                                     self._p(self.scales), stream))
+            self._check(self.lib.llmcp_dev_gemv_q8(self._p(self.aq), self._p(self.scales), C.c_int64(self.K),
+                                                   self._p(self.wq), self._p(self.wd), C.c_int64(self.rows),
+                                                   self._p(self.y), int(self.y_bf16), self.activation, 0, 0, stream))
+            torch.cuda.synchronize()
+        return self.y
+
+    def forward(self, x_bf16_bits, group=None):
+        return gather_rows(self.local(x_bf16_bits), group=group)

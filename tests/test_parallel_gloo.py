@@ -37,7 +37,13 @@ def _worker(rank, world, port, results):
         value, token = parallel.reduce_argmax(local[index], begin + index)
         full = oracle.linear_q8(h, packed, vocab, y_bf16=False)[0]
         slowest = parallel.max_over_ranks(float(rank + 1))
-        results[rank] = (value, token, float(full.max()), oracle.argmax(full), np.array_equal(local, full[begin:end]), slowest)
+        # a column-parallel linear: every rank's rows, gathered in rank order, are the unsharded row
+        row = parallel.gather_rows(torch.from_numpy(local.copy())).numpy()
+        bits = torch.from_numpy(oracle.f32_to_bf16(local).view(np.int16).copy())  # bf16 bit patterns travel as int16
+        row16 = parallel.gather_rows(bits).numpy().view(np.uint16)
+        gathered = np.array_equal(row, full) and np.array_equal(row16, oracle.f32_to_bf16(full))
+        results[rank] = (value, token, float(full.max()), oracle.argmax(full),
+                         np.array_equal(local, full[begin:end]) and gathered, slowest)
     finally:
         dist.destroy_process_group()
 
@@ -64,3 +70,5 @@ def test_vocab_shard_boundaries():
     with pytest.raises(ValueError):
         parallel.vocab_shard(248320, 3, 0)
     assert parallel.reduce_argmax(1.5, 7) == (1.5, 7)  # no process group: identity
+    one = torch.arange(4.0)
+    assert parallel.gather_rows(one) is one
