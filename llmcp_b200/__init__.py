@@ -379,6 +379,8 @@ class AotRuntime:
         self.delta = np.zeros((d.linear_layers, d.lin_v_heads, d.lin_k_dim, d.lin_v_dim), dtype=np.float32)
         self.conv = np.zeros((d.linear_layers, d.conv_kernel - 1, d.qkv_dim), dtype=np.uint16)
         self._cos_sin = cos_sin or (lambda pos: make_cos_sin(pos, d.rotary, d.rope_theta))
+        for cached in ("_fixed", "_one", "_out"):  # descriptors of the buffers just replaced
+            self.__dict__.pop(cached, None)
         try:
             self.handle = C.CDLL(str(path or LIBRARY_PATH))
             version = self.handle.llmcp_model_abi_version
