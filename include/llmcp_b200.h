@@ -194,6 +194,11 @@ int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes);
  *                                 lib/Model/WeightPacker.cpp:163-274); the three counters are what
  *                                 its summary line prints.  Host only: no GPU is touched. */
 int llmcp_b200_parse_config(const char *json, uint64_t length, llmcp_b200_dims *dims);
+/* A random-init checkpoint directory (config.json, one safetensors shard and its index) holding
+ * the tensors llmcp_b200_synthetic_fill draws for (dims, seed): what llmcp-pack, the reference's
+ * or this repository's, turns into that container.  Stands in for the real checkpoint
+ * (docs/model-spec.md:51-76), which is not distributed with either project. */
+int llmcp_b200_synthetic_checkpoint(const llmcp_b200_dims *dims, uint64_t seed, const char *model_dir);
 uint64_t llmcp_b200_read_safetensors(const char *path, char *buffer, uint64_t capacity);
 int llmcp_b200_pack_checkpoint(const char *model_dir, const char *output_path, const char *quant, int dry_run,
                                int verbose, uint64_t *tensors, uint64_t *source_bytes, uint64_t *arena_bytes);

@@ -273,6 +273,12 @@ def read_safetensors(path):
     return out
 
 
+def synthetic_checkpoint(dims, seed, model_dir):
+    """Writes a random-init checkpoint directory (config.json + safetensors) with the tensors of
+    ``synthetic_container(dims, seed)`` before quantisation."""
+    _check(lib().llmcp_b200_synthetic_checkpoint(C.byref(dims), C.c_uint64(seed), os.fsencode(str(model_dir))))
+
+
 def pack_checkpoint(model_dir, output_path=None, quant="none", dry_run=False, verbose=False):
     """``llmcp-pack``: packs ``model_dir`` (config.json + safetensors) into the container file
     ``output_path`` (tools/llmcp-pack/llmcp-pack.cpp:44-89).  Returns

@@ -753,6 +753,16 @@ uint64_t llmcp_b200_read_safetensors(const char *path, char *buffer, uint64_t ca
   return text.size();
 }
 
+int llmcp_b200_synthetic_checkpoint(const llmcp_b200_dims *dims, uint64_t seed, const char *model_dir) {
+  return guarded_async([&] {
+    const ModelDims d = to_dims(dims);
+    check_dims(d);
+    const std::string error = write_synthetic_checkpoint(d, seed, model_dir ? model_dir : "");
+    if (!error.empty())
+      throw std::runtime_error(error);
+  });
+}
+
 int llmcp_b200_pack_checkpoint(const char *model_dir, const char *output_path, const char *quant, int dry_run,
                                int verbose, uint64_t *tensors, uint64_t *source_bytes, uint64_t *arena_bytes) {
   return guarded_async([&] {

@@ -304,6 +304,126 @@ std::string read_checkpoint_tensors(const std::string &model_dir, SourceTensors 
 }
 
 // ------------------------------------------------------------------------------
+// synthetic checkpoint
+// ------------------------------------------------------------------------------
+namespace {
+
+std::string format_double(double v) {
+  char text[40];
+  std::snprintf(text, sizeof text, "%.17g", v);
+  return text;
+}
+
+std::string config_json(const ModelDims &d) {
+  std::string layer_types;
+  for (int64_t i = 0; i < d.layers; ++i)
+    layer_types += std::string(i ? "," : "") + (d.is_full(i) ? "\"full_attention\"" : "\"linear_attention\"");
+  std::string out = "{\"architectures\":[\"Qwen3_5ForConditionalGeneration\"],\"tie_word_embeddings\":true,\"text_config\":{";
+  auto integer = [&](const char *key, int64_t v) { out += std::string("\"") + key + "\":" + std::to_string(v) + ","; };
+  out += "\"attention_bias\":false,\"attn_output_gate\":true,\"hidden_act\":\"silu\",";
+  integer("head_dim", d.head_dim);
+  integer("hidden_size", d.hidden);
+  integer("intermediate_size", d.intermediate);
+  integer("full_attention_interval", d.full_interval);
+  out += "\"layer_types\":[" + layer_types + "],";
+  integer("linear_conv_kernel_dim", d.conv_kernel);
+  integer("linear_key_head_dim", d.lin_k_dim);
+  integer("linear_num_key_heads", d.lin_k_heads);
+  integer("linear_num_value_heads", d.lin_v_heads);
+  integer("linear_value_head_dim", d.lin_v_dim);
+  integer("num_attention_heads", d.heads);
+  integer("num_hidden_layers", d.layers);
+  integer("num_key_value_heads", d.kv_heads);
+  out += "\"rms_norm_eps\":" + format_double(static_cast<double>(d.eps)) + ",";
+  out += "\"rope_parameters\":{\"partial_rotary_factor\":" +
+         format_double(static_cast<double>(d.rotary) / static_cast<double>(d.head_dim)) +
+         ",\"rope_theta\":" + format_double(static_cast<double>(d.rope_theta)) + ",\"rope_type\":\"default\"},";
+  out += "\"tie_word_embeddings\":true,\"vocab_size\":" + std::to_string(d.vocab) + "}}\n";
+  return out;
+}
+
+bool write_text(const std::string &path, const std::string &text) {
+  FILE *f = std::fopen(path.c_str(), "wb");
+  if (!f)
+    return false;
+  const bool ok = std::fwrite(text.data(), 1, text.size(), f) == text.size();
+  return std::fclose(f) == 0 && ok;
+}
+
+} // namespace
+
+std::string write_synthetic_checkpoint(const ModelDims &dims, uint64_t seed, const std::string &model_dir) {
+  // The tensors, their order and their value streams are those of fill_synthetic_container, so
+  // that packing this checkpoint reproduces that container byte for byte.
+  const Manifest layout = build_layout(dims);
+  struct Source {
+    const TensorEntry *entry;
+    bool f32;
+    uint64_t elements, begin;
+  };
+  std::vector<Source> sources;
+  uint64_t cursor = 0;
+  std::string header = "{\"__metadata__\":{\"format\":\"pt\"}";
+  std::string weight_map;
+  for (const TensorEntry &t : layout.tensors) {
+    uint64_t elements = 1;
+    for (int64_t dim : t.shape)
+      elements *= static_cast<uint64_t>(dim);
+    const bool f32 = t.source_size == elements * 4;
+    sources.push_back({&t, f32, elements, cursor});
+    std::string shape;
+    for (size_t i = 0; i < t.shape.size(); ++i)
+      shape += (i ? "," : "") + std::to_string(t.shape[i]);
+    header += ",\"" + t.name + "\":{\"dtype\":\"" + (f32 ? "F32" : "BF16") + "\",\"shape\":[" + shape +
+              "],\"data_offsets\":[" + std::to_string(cursor) + "," + std::to_string(cursor + t.source_size) + "]}";
+    weight_map += std::string(weight_map.empty() ? "" : ",") + "\"" + t.name + "\":\"model.safetensors\"";
+    cursor += t.source_size;
+  }
+  header += "}";
+  while (header.size() % 8 != 0) // the data section starts 8-byte aligned, as writers of the format do
+    header += ' ';
+
+  FILE *f = std::fopen((model_dir + "/model.safetensors").c_str(), "wb");
+  if (!f)
+    return "cannot create '" + model_dir + "/model.safetensors'";
+  std::unique_ptr<FILE, int (*)(FILE *)> closer(f, std::fclose);
+  unsigned char size_bytes[8];
+  for (int i = 0; i < 8; ++i)
+    size_bytes[i] = static_cast<unsigned char>(static_cast<uint64_t>(header.size()) >> (8 * i));
+  if (std::fwrite(size_bytes, 1, 8, f) != 8 || std::fwrite(header.data(), 1, header.size(), f) != header.size())
+    return "cannot write the safetensors header";
+  for (size_t index = 0; index < sources.size(); ++index) {
+    const Source &src = sources[index];
+    const TensorEntry &t = *src.entry;
+    const uint64_t chunk = 1u << 20;
+    std::vector<uint8_t> buffer;
+    for (uint64_t first = 0; first < src.elements; first += chunk) {
+      const uint64_t count = std::min(chunk, src.elements - first);
+      buffer.assign(count * (src.f32 ? 4 : 2), 0);
+      if (t.dtype == "Q8_0" || has_suffix(t.name, "conv1d.weight")) {
+        const float gain = t.dtype == "Q8_0" ? 0.02f : 0.5f;
+        uint16_t *out = reinterpret_cast<uint16_t *>(buffer.data());
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < static_cast<int64_t>(count); ++i)
+          out[i] = f32_to_bf16_bits(gain * synthetic_normal(seed, index, first + static_cast<uint64_t>(i)));
+      } else if (has_suffix(t.name, "linear_attn.norm.weight")) {
+        float *out = reinterpret_cast<float *>(buffer.data());
+        for (uint64_t i = 0; i < count; ++i)
+          out[i] = 1.0f;
+      } // zero-centred gains, A_log and dt_bias stay zero
+      if (std::fwrite(buffer.data(), 1, buffer.size(), f) != buffer.size())
+        return "cannot write tensor data of " + t.name;
+    }
+  }
+  closer.reset();
+  if (!write_text(model_dir + "/model.safetensors.index.json",
+                  "{\"metadata\":{\"total_size\":" + std::to_string(cursor) + "},\"weight_map\":{" + weight_map + "}}\n") ||
+      !write_text(model_dir + "/config.json", config_json(dims)))
+    return "cannot write config.json / model.safetensors.index.json in '" + model_dir + "'";
+  return "";
+}
+
+// ------------------------------------------------------------------------------
 // packing
 // ------------------------------------------------------------------------------
 namespace {

@@ -32,6 +32,12 @@ std::string read_safetensors_file(const std::string &path, const std::string &sh
 // without an index, every *.safetensors file of the directory in name order.
 std::string read_checkpoint_tensors(const std::string &model_dir, SourceTensors *out);
 
+// Writes a random-init checkpoint directory (config.json, model.safetensors,
+// model.safetensors.index.json) whose tensors are the values fill_synthetic_container draws for
+// (`dims`, `seed`): packing it with --quant q8_0 gives that container byte for byte, apart from
+// the manifest's model field.  The 4B-shaped model is 8.4 GB of bf16.
+std::string write_synthetic_checkpoint(const ModelDims &dims, uint64_t seed, const std::string &model_dir);
+
 struct PackSummary {
   uint64_t tensors = 0, source_bytes = 0, arena_bytes = 0;
 };

@@ -304,3 +304,28 @@ def test_llmcp_pack_tool(tmp_path):  # tools/llmcp-pack/llmcp-pack.cpp:44-89
     assert run.returncode == 0 and run.stdout.startswith("validated 55 tensors, ")
     run = subprocess.run([str(tool), "--model", str(tmp_path)], capture_output=True, text=True)
     assert run.returncode == 1 and "--out is required unless --dry-run is set" in run.stderr
+
+
+def test_packed_synthetic_checkpoint_is_the_synthetic_container(tmp_path):
+    """The random-init checkpoint written as safetensors, packed by llmcp-pack, is byte for byte
+    the container the synthetic generator writes directly: both routes to a weights file agree."""
+    dims = L.default_dims().copy(**TINY)
+    L.synthetic_checkpoint(dims, 9, tmp_path)
+    parsed = L.parse_config((tmp_path / "config.json").read_text())
+    assert all(getattr(parsed, k) == v for k, v in TINY.items())
+    assert abs(parsed.eps - dims.eps) < 1e-12 and parsed.rope_theta == dims.rope_theta
+    headers = L.read_safetensors(tmp_path / "model.safetensors")
+    assert len(headers) == 55 and headers["model.language_model.layers.0.linear_attn.A_log"][0] == "F32"
+    out = tmp_path / "weights.bin"
+    L.pack_checkpoint(tmp_path, out, quant="q8_0")
+    packed = np.fromfile(out, dtype=np.uint8)
+    direct = L.synthetic_container(dims, 9)
+    arena_bytes = int.from_bytes(direct[16:24].tobytes(), "little")
+    assert int.from_bytes(packed[16:24].tobytes(), "little") == arena_bytes
+    assert np.array_equal(packed[64:arena_bytes], direct[64:arena_bytes])
+    a, b = json.loads(packed[arena_bytes:].tobytes()), json.loads(direct[arena_bytes:].tobytes())
+    assert a.pop("model") == str(tmp_path) and b.pop("model") == "synthetic"
+    assert a == b
+    # a different seed gives different weights
+    other = L.synthetic_container(dims, 10)
+    assert not np.array_equal(other[64:arena_bytes], direct[64:arena_bytes])
