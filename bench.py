@@ -409,8 +409,9 @@ def main():
                    "seed": SEED, "parallelism": f"replica x{world}" if world > 1 else "single GPU",
                    "l2": "each step streams the 4.47 GB arena, far larger than L2; no flush needed",
                    "vs_baseline_is": "per-GPU value / 11.39 tok/s published for Apple M2 (reference README.md:140)"},
-        "e2e": {"value": world * steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 8 + 2 * dims.rotary * 4,
-                "d2h_bytes_per_step": dims.vocab * 4, "tokens_match_device_arm": bool(same)},
+        "e2e": {"value": world * steps / e2e_s, "unit": "tokens/s", # one packet in: position, token, cos row, sin row; logits row, token and status word back
+                "h2d_bytes_per_step": 16 + 2 * dims.rotary * 4,
+                "d2h_bytes_per_step": dims.vocab * 4 + 16, "tokens_match_device_arm": bool(same)},
         "gpu_launches": int(launches) * world,
         "clocks": clocks,
         "prefill_tokens_per_second": {"tokens": PREFILL, "engine": PREFILL / prefill_s, "e2e_abi": PREFILL / e2e_prefill_s},
