@@ -1,26 +1,33 @@
 #!/usr/bin/env python3
 """Benchmark of the llmcp Q8_0 hot path on B200.
 
-Workload (BASELINE.json configs[4], batch 1): a random-init Qwen3.5-4B-architecture model
-packed with --quant q8_0 (seeded synthetic weights with the real shapes and dtypes; the real
-checkpoint is not available offline), 1024 x token 9419 prefill, then greedy decode.  One
-"step" is one decode step of the whole model: every weight byte of the arena streams from HBM
-once (4.47 GB, far more than the 126 MB L2, so no cache flush is needed between steps).
+Workload (the whole-model configuration of the benchmark list, batch 1): a random-init
+Qwen3.5-4B-architecture model packed with --quant q8_0 (seeded synthetic weights with the real
+shapes and dtypes; the real checkpoint is not available offline), 1024 x token 9419 prefill, then
+greedy decode.  One "step" is one decode step of the whole model: every weight byte of the arena
+streams from HBM once (4.47 GB, far more than the 126 MB L2, so no cache flush is needed
+between steps).
 
   value  decode tokens/s with token, state and logits resident in HBM (engine interface),
-         timed with CUDA events on the launching stream, max over ranks;
+         timed with CUDA events on the launching stream, max over ranks.  It is measured in
+         the fast arithmetic mode (config.mode); the exact mode, whose every f32 result is
+         bit-identical to the reference's order of operations, is timed beside it (exact_mode);
   e2e    the same steps through the reference-facing AOT ABI entry point with host buffers:
          token, cos and sin rows go host -> device, the 248320-float logits row comes back
          and the argmax is taken on the host, as tools/llmcp-benchmark does;
-  roofline  the decode GEMV (N=9216, K=2560, the gate_proj/up_proj shape; BASELINE.json
-         configs[0]) timed alone with CUDA events over a ring of 12 weight copies (301 MB);
+  roofline  the decode GEMV (N=9216, K=2560, the gate_proj/up_proj shape) timed alone with
+         CUDA events over a ring of 12 weight copies (301 MB);
+  roofline_gemm  the prefill GEMM (1024 x 9216 x 2560) on the tcgen05 tensor cores, alone;
   cpu_baseline  the CPU oracle (a restatement of the reference's arithmetic; the reference's
-         own AOT build needs an MLIR toolchain that is not installed) on the host cores.
+         own AOT build needs an MLIR toolchain that is not installed) on all host cores, on
+         the same 1024-token context; its greedy tokens and logits are also what the GPU arm's
+         are compared with (tokens_match_oracle, max_abs_logit_diff, min_top2_margin).
 
 N > 1 (torchrun): every rank holds a full replica and decodes its own sequence; no collective
 on the data path, so scaling is "weak" and value is the sum over ranks.
 
-`--impl reference` times the CPU oracle alone on the same workload and prints the same line.
+`--impl reference` times the CPU oracle alone on the same workload and prints the same line; that
+arm loads no CUDA library.
 """
 import argparse
 import ctypes as C
@@ -44,22 +51,28 @@ PREFILL = 1024
 M2_DECODE_TOK_S = 11.39  # published Q8_0 decode tok/s on Apple M2, 4 threads (reference README.md:140)
 GEMV_N, GEMV_K, GEMV_RING = 9216, 2560, 12
 GEMV_BYTES = GEMV_N * (GEMV_K // 32) * 34 + GEMV_K * 4 + GEMV_N * 4  # weights + f32 x + f32 y = 25,114,624
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q8_cols80_kernel launch of this shape, from the
-# ncu capture summarised in profiles/gemv_q8_cols80_9216x2560.md (the 36,864-byte result stays in L2).
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q8_cols80_kernel launch of this shape, from an ncu
+# capture of `bench.py --only gemv` (not measured in this run; the 36,864-byte result stays in L2).
 GEMV_DRAM_TRAFFIC = 25_097_216
-GEMM_M, GEMM_N, GEMM_K = 1024, 9216, 2560  # the gate_proj/up_proj prefill GEMM (BASELINE.json configs[1] shape)
+GEMM_M, GEMM_N, GEMM_K = 1024, 9216, 2560  # the gate_proj/up_proj prefill GEMM
 
 
 def measured_peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s burst, "measured" | "fallback")."""
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         data = json.loads(path.read_text())
-        return float(data["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(data["hbm_gbs"]), float(data["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed regions run.
+
+    NVML is read directly (queries only) every millisecond from a thread, so that a timed region
+    of a few tens of milliseconds still holds tens of samples; if the NVML binding is missing,
+    `nvidia-smi -lms 20` is read instead.
+    """
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -67,26 +80,58 @@ class ClockSampler:
 
     def __init__(self, device):
         self.device = device
-        self.lines = []  # (host time, text)
+        self.samples = []  # (host time, sm MHz, reasons bitmask or None, nvidia-smi text or None)
         self.windows = []  # [begin, end] host times of the timed regions
         self.proc = None
+        self.nvml = None
+        self.max_clock = None
+        self.running = False
+        self.how = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            index = self.device
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if visible and all(v.strip().isdigit() for v in visible.split(",")):
+                index = int(visible.split(",")[self.device])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.running = True
+            self.how = "NVML queries every ms from a thread"
+            threading.Thread(target=self._poll, daemon=True).start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.how = "nvidia-smi every 20 ms"
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        while self.running:
+            try:
+                clock = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                reasons = int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                self.samples.append((time.perf_counter(), clock, reasons, None))
+            except Exception:
+                pass
+            time.sleep(0.001)
+
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append((time.perf_counter(), line.strip()))
+            self.samples.append((time.perf_counter(), None, None, line.strip()))
 
     def wait_first_sample(self, seconds=5.0):
         deadline = time.perf_counter() + seconds
-        while self.proc and not self.lines and time.perf_counter() < deadline:
+        while (self.proc or self.running) and not self.samples and time.perf_counter() < deadline:
             time.sleep(0.01)
 
     def open_window(self):
@@ -96,19 +141,30 @@ class ClockSampler:
         self.windows[-1][1] = time.perf_counter()
 
     def stop(self):
+        self.running = False
         if self.proc:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
-        clocks, max_clock, reasons = [], None, set()
+        clocks, max_clock, reasons = [], self.max_clock, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         inside = lambda t: any(b <= t <= (e if e is not None else t) for b, e in self.windows)
-        for stamp, line in self.lines:
+        for stamp, clock, mask, text in list(self.samples):
             if self.windows and not inside(stamp):
                 continue
-            parts = [p.strip() for p in line.split(",")]
+            if text is None:
+                clocks.append(clock)
+                n = self.nvml
+                for name, bit in (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown),
+                                  ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
+                                  ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown),
+                                  ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap)):
+                    if mask & int(bit):
+                        reasons.add(name)
+                continue
+            parts = [p.strip() for p in text.split(",")]
             if len(parts) < 9:
                 continue
             try:
@@ -121,45 +177,72 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
                 "reasons": sorted(reasons), "samples": len(clocks),
-                "sampled": "nvidia-smi every 20 ms, samples inside the two timed loops (device arm and ABI arm)"}
+                "sampled": f"{self.how}; samples inside the timed loops (device arm, both modes, and ABI arm)"}
 
 
-def container_path(local_rank, world):
-    """One synthetic container per node in /dev/shm, written by local rank 0."""
-    import llmcp_b200 as L
-    path = pathlib.Path("/dev/shm") / f"llmcp_b200_synth_{SEED}.bin"
-    if local_rank == 0 and not path.exists():
-        data = L.synthetic_container(L.default_dims(), SEED)
-        tmp = path.with_suffix(f".{os.getpid()}.tmp")
-        data.tofile(tmp)
-        os.replace(tmp, path)
-        del data
-    return path
+CONTAINER = pathlib.Path("/dev/shm") / f"llmcp_b200_synth_{SEED}.bin"
 
 
-def oracle_decode(arena, steps, warmup, prefill=8):
-    """Greedy decode with the CPU oracle: returns (tokens/s, tokens, threads)."""
-    import llmcp_b200 as L
-    import oracle
-    d = L.default_dims()
-    model = oracle.Model(arena.data, arena.manifest, dict(
-        full_interval=d.full_interval, heads=d.heads, kv_heads=d.kv_heads, head_dim=d.head_dim, rotary=d.rotary,
-        lin_k_heads=d.lin_k_heads, lin_v_heads=d.lin_v_heads, lin_k_dim=d.lin_k_dim, lin_v_dim=d.lin_v_dim,
-        conv_kernel=d.conv_kernel))
-    state = model.new_state(prefill + warmup + steps + 1)
-    logits = model.forward(state, [TOKEN] * prefill, 0)  # also unpacks the weights once
-    pos, tokens = prefill, []
-    for _ in range(warmup):
-        logits = model.forward(state, [oracle.argmax(logits)], pos)
-        pos += 1
-    begin = time.perf_counter()
-    for _ in range(steps):
-        tokens.append(oracle.argmax(logits))
-        logits = model.forward(state, [tokens[-1]], pos)
-        pos += 1
-    seconds = time.perf_counter() - begin
-    model.close()
-    return steps / seconds, tokens, oracle.num_threads()
+def ensure_container(local_rank):
+    """One synthetic container per node in /dev/shm, written by local rank 0 with the host-only
+    packer binary (no CUDA library is involved)."""
+    if local_rank == 0 and not CONTAINER.exists():
+        tool = ROOT / "llmcp_b200" / "bin" / "llmcp-pack"
+        if not tool.exists():
+            raise SystemExit(f"{tool} is missing: run `python -m llmcp_b200.build`")
+        tmp = CONTAINER.with_suffix(f".{os.getpid()}.part")
+        subprocess.run([str(tool), "--synthetic", str(SEED), "--out", str(tmp)], check=True, stdout=subprocess.DEVNULL)
+        os.replace(tmp, CONTAINER)
+    while not CONTAINER.exists():
+        time.sleep(0.2)
+    return CONTAINER
+
+
+def read_container(path):
+    """(bytes as a numpy array over a read-only map, manifest dict) without the CUDA library:
+    the header holds the arena length at byte 16, the JSON manifest follows the arena."""
+    import mmap
+    with open(path, "rb") as f:
+        mapped = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
+    data = np.frombuffer(mapped, dtype=np.uint8)
+    arena_bytes = int.from_bytes(data[16:24].tobytes(), "little")
+    manifest = json.loads(data[arena_bytes:].tobytes().decode().rstrip("\0"))
+    return data, manifest
+
+
+ORACLE_DIMS = dict(full_interval=4, heads=16, kv_heads=4, head_dim=256, rotary=64, lin_k_heads=16, lin_v_heads=32,
+                   lin_k_dim=128, lin_v_dim=128, conv_kernel=4)  # Qwen3.5-4B text (lib/Runtime/AotRuntime.cpp:41-43)
+
+
+class OracleRun:
+    """The CPU oracle on the benchmark's context: 1024 x token 9419, then greedy steps."""
+
+    def __init__(self, data, manifest, steps):
+        import oracle
+        self.oracle = oracle
+        self.threads = oracle.set_num_threads()  # every host core, whatever OMP_NUM_THREADS was inherited
+        self.model = oracle.Model(data, manifest, ORACLE_DIMS)
+        self.state = self.model.new_state(PREFILL + steps + 2)
+        begin = time.perf_counter()
+        self.logits = [self.model.forward(self.state, [TOKEN] * PREFILL, 0)]
+        self.prefill_s = time.perf_counter() - begin
+        self.tokens = [oracle.argmax(self.logits[0])]
+        self.position = PREFILL
+
+    def decode(self, steps, keep_logits=True):
+        """`steps` greedy steps; returns tokens/s of the loop (forward + host argmax, as
+        tools/llmcp-benchmark times it)."""
+        begin = time.perf_counter()
+        for _ in range(steps):
+            logits = self.model.forward(self.state, [self.tokens[-1]], self.position)
+            self.position += 1
+            self.tokens.append(self.oracle.argmax(logits))
+            if keep_logits:
+                self.logits.append(logits)
+        return steps / (time.perf_counter() - begin)
+
+    def close(self):
+        self.model.close()
 
 
 def gemv_roofline(L, torch, device, ring=GEMV_RING, sweeps=20):
@@ -267,7 +350,8 @@ def main():
     parser.add_argument("--steps", type=int, default=128)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--cpu-steps", type=int, default=8, help="decode steps of the CPU baseline sample")
+    parser.add_argument("--cpu-steps", type=int, default=16, help="decode steps of the CPU baseline sample")
+    parser.add_argument("--mode", default="fast", choices=["fast", "exact"], help="arithmetic mode `value` is measured in")
     parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm", "attn"],
                         help="gemv / gemm / attn: run just that kernel on a small case (what the profiler captures)")
     args = parser.parse_args()
@@ -276,32 +360,35 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-
-    import llmcp_b200 as L
+    workload = ("whole model, Qwen3.5-4B architecture, Q8_0, batch 1 per GPU: greedy decode after a 1024-token "
+                "prefill of token 9419")
 
     if args.impl == "reference":
-        # The reference's own CPU implementation needs MLIR/LLVM 20 to exist at all; the CPU
-        # oracle restates it.  Rank 0 alone runs; each step is one greedy decode step of the
-        # whole model (a short 8-token context keeps the run within minutes; decode cost is
-        # dominated by the 4.47 GB of weights and barely depends on the context length).
+        # The reference's own CPU implementation needs MLIR/LLVM 20 to exist at all; the CPU oracle
+        # restates it.  Rank 0 alone runs, on every host core, on the same 1024-token context as the
+        # GPU arm; each step is one greedy decode step of the whole model.  No CUDA library is loaded.
         if rank != 0:
             return
-        arena = L.Arena().load(container_path(0, 1))
-        ref_steps = min(steps, 32)
-        tok_s, tokens, threads = oracle_decode(arena, ref_steps, min(warmup, 3))
+        data, manifest = read_container(ensure_container(0))
+        ref_steps, ref_warmup = min(steps, 32), min(warmup, 3)
+        run = OracleRun(data, manifest, ref_steps + ref_warmup)
+        run.decode(ref_warmup, keep_logits=False)
+        tok_s = run.decode(ref_steps, keep_logits=False)
+        run.close()
         print(json.dumps({
             "impl": "reference", "metric": "decode_tokens_per_second", "value": tok_s, "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": ref_steps, "warmup": min(warmup, 3), "ms_per_step": 1e3 / tok_s,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": tok_s / M2_DECODE_TOK_S, "dtype": "int8xint8->int32, f32 accumulate",
-            "data": "synthetic",
-            "config": {"workload": "configs[4]: Qwen3.5-4B-architecture Q8_0 whole model, batch 1, greedy decode",
-                       "context": "8-token prefill (bounded sample)", "seed": SEED},
-            "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
-                             "sample": f"{ref_steps} greedy decode steps after an 8-token prefill, all host threads"},
+            "n_gpus": args.gpus, "steps": ref_steps, "warmup": ref_warmup, "ms_per_step": 1e3 / tok_s,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": tok_s / M2_DECODE_TOK_S,
+            "dtype": "int8xint8->int32, f32 accumulate", "data": "synthetic",
+            "config": {"workload": workload, "seed": SEED, "mode": "cpu oracle, fma accumulate"},
+            "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": run.threads, "kind": "port",
+                             "sample": f"{ref_steps} greedy decode steps after the 1024-token prefill, all host threads",
+                             "prefill_tokens_per_second": PREFILL / run.prefill_s},
             "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
         return
 
+    import llmcp_b200 as L
     import torch
     import torch.distributed as dist
 
@@ -310,10 +397,11 @@ def main():
     torch.cuda.set_device(local_rank)
     L.set_device(local_rank)
     if args.only == "gemv":
-        gbs, us, count = gemv_roofline(L, torch, local_rank, ring=6, sweeps=2)
+        gbs, us, count = gemv_roofline(L, torch, local_rank, ring=6, sweeps=2, flags=19 if args.mode == "fast" else 3)
         print(json.dumps({"only": "gemv", "shape": [1, GEMV_N, GEMV_K], "us_per_launch": us, "gbs": gbs, "launches": count}))
         return
     if args.only == "attn":
+        L.set_mode(args.mode)
         row = attention_alone(L)
         print(json.dumps({"only": "attn", "shape": {"heads": 16, "kv_heads": 4, "head_dim": 256, "keys": 1031},
                           "checksum": int(row.astype(np.int64).sum())}))
@@ -337,39 +425,78 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    path = container_path(local_rank, world)
+    path = ensure_container(local_rank)
     barrier()
-    while not path.exists():
-        time.sleep(0.2)
     arena = L.Arena().load(path)
     dims = L.default_dims()
     capacity = PREFILL + 2 * (warmup + steps) + 16
-
-    # ---- device-resident arm --------------------------------------------------------------
-    engine = L.Engine(arena.data, dims, capacity=capacity, device=local_rank)
     prompt = [TOKEN] * PREFILL
-    engine.forward(prompt, 0, want_logits=False)  # warm-up prefill (allocates the workspace)
-    engine.reset()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    _, first = engine.forward(prompt, 0, want_logits=False)
-    prefill_s = time.perf_counter() - t0
-    warm_tokens, _ = engine.generate(first, PREFILL, warmup)
     sampler = ClockSampler(local_rank)
     sampler.start()
     sampler.wait_first_sample()
-    launches_before = L.launch_count()
-    barrier()
-    sampler.open_window()
-    tokens, device_ms = engine.generate(int(warm_tokens[-1]), PREFILL + warmup, steps)
-    barrier()
-    sampler.close_window()
-    launches = L.launch_count() - launches_before
-    device_ms = max_over_ranks(device_ms)
-    value = world * steps / (device_ms / 1e3)
-    engine.close()
 
-    # ---- end-to-end arm through the AOT ABI ------------------------------------------------
+    # ---- device-resident arm, once per arithmetic mode ---------------------------------------
+    def device_arm(mode):
+        engine = L.Engine(arena.data, dims, capacity=capacity, device=local_rank, mode=mode)
+        engine.forward(prompt, 0, want_logits=False)  # warm-up prefill (allocates the workspace)
+        engine.reset()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        first_logits, first = engine.forward(prompt, 0)
+        prefill_s = time.perf_counter() - t0
+        warm_tokens, _ = engine.generate(first, PREFILL, warmup)
+        before = L.launch_count()
+        barrier()
+        sampler.open_window()
+        tokens, device_ms = engine.generate(int(warm_tokens[-1]), PREFILL + warmup, steps)
+        barrier()
+        sampler.close_window()
+        launches = L.launch_count() - before
+        return {"ms": max_over_ranks(device_ms), "launches": launches, "prefill_s": prefill_s,
+                "tokens": [first] + warm_tokens.tolist() + tokens.tolist(), "first_logits": first_logits, "engine": engine}
+
+    other = "exact" if args.mode == "fast" else "fast"
+    main_arm = device_arm(args.mode)
+    side_arm = device_arm(other)
+    side_arm.pop("engine").close()
+    device_ms, launches = main_arm["ms"], main_arm["launches"]
+    value = world * steps / (device_ms / 1e3)
+
+    # ---- against the CPU oracle on the same context (rank 0 of a one-GPU run) ----------------
+    # The oracle's greedy chain from the same prompt, its logits at every position of the chain and
+    # its top-1/top-2 margins; the GPU engine is fed the oracle's tokens (teacher forcing), so one
+    # low-margin position cannot derail the comparison of the positions behind it.
+    check, cpu_baseline = None, None
+    if rank == 0 and world == 1:
+        run = OracleRun(arena.data, arena.manifest, args.cpu_steps)
+        tok_s = run.decode(args.cpu_steps)
+        margins = [run.oracle.top2_margin(row) for row in run.logits]
+        engine = main_arm["engine"]
+        engine.reset()
+        logits, token = engine.forward(prompt, 0)
+        worst = float(np.abs(logits - run.logits[0]).max())
+        same = [token == run.tokens[0]]
+        for i in range(args.cpu_steps):
+            logits, token = engine.forward([run.tokens[i]], PREFILL + i)
+            worst = max(worst, float(np.abs(logits - run.logits[i + 1]).max()))
+            same.append(token == run.tokens[i + 1])
+        n = args.cpu_steps + 1
+        exact_tokens = side_arm["tokens"] if other == "exact" else main_arm["tokens"]
+        check = {"positions": n, "tokens_match_oracle": bool(all(same)), "tokens_equal": int(sum(same)),
+                 "max_abs_logit_diff": worst, "min_top2_margin": float(min(margins)),
+                 "median_top2_margin": float(np.median(margins)),
+                 "exact_mode_tokens_match_oracle": exact_tokens[:n] == run.tokens[:n],
+                 "how": "engine fed the oracle's greedy tokens (1024-token prompt + cpu-steps positions); logits compared "
+                        "position by position; exact mode: its own greedy chain against the oracle's"}
+        cpu_baseline = {"value": tok_s, "unit": "tokens/s", "cores": run.threads, "kind": "port",
+                        "sample": f"{args.cpu_steps} greedy decode steps after the same 1024-token prefill, CPU oracle "
+                                  "(OpenMP, all host threads)",
+                        "prefill_tokens_per_second": PREFILL / run.prefill_s}
+        run.close()
+    main_arm.pop("engine").close()
+
+    # ---- end-to-end arm through the AOT ABI --------------------------------------------------
+    L.set_mode(args.mode)
     runtime = L.AotRuntime(dims)
     assert runtime.init(max_sequence=capacity)
     logits = np.zeros(dims.vocab, dtype=np.float32)  # one host row for every call, as llmcp-benchmark.cpp:84-101 keeps
@@ -398,38 +525,61 @@ def main():
     L.lib().llmcp_b200_release_all()
     if L.last_error():
         raise SystemExit("library error: " + L.last_error())
-    same = e2e_tokens[1:] == tokens.tolist()[:steps - 1]
+    same = e2e_tokens == main_arm["tokens"][warmup:warmup + steps]
 
+    bytes_per_step = 4.61e9  # weights 4.468 GB + recurrent state 0.101 GB + KV and logits
     result = {
         "metric": "decode_tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": device_ms / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": value / world / M2_DECODE_TOK_S, "dtype": "int8xint8->int32, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "configs[4]: Qwen3.5-4B-architecture Q8_0 whole model, batch 1 per GPU, greedy decode "
-                               "after a 1024-token prefill of token 9419",
+        "config": {"workload": workload, "mode": args.mode,
                    "seed": SEED, "parallelism": f"replica x{world}" if world > 1 else "single GPU",
                    "l2": "each step streams the 4.47 GB arena, far larger than L2; no flush needed",
                    "vs_baseline_is": "per-GPU value / 11.39 tok/s published for Apple M2 (reference README.md:140)"},
+        f"{other}_mode": {"value": world * steps / (side_arm["ms"] / 1e3), "unit": "tokens/s",
+                          "ms_per_step": side_arm["ms"] / steps,
+                          "prefill_tokens_per_second": PREFILL / side_arm["prefill_s"]},
         "e2e": {"value": world * steps / e2e_s, "unit": "tokens/s", # one packet in: position, token, cos row, sin row; logits row, token and status word back
                 "h2d_bytes_per_step": 16 + 2 * dims.rotary * 4,
                 "d2h_bytes_per_step": dims.vocab * 4 + 16, "tokens_match_device_arm": bool(same)},
         "gpu_launches": int(launches) * world,
         "clocks": clocks,
-        "prefill_tokens_per_second": {"tokens": PREFILL, "engine": PREFILL / prefill_s, "e2e_abi": PREFILL / e2e_prefill_s},
+        "prefill_tokens_per_second": {"tokens": PREFILL, "engine": PREFILL / main_arm["prefill_s"],
+                                      "e2e_abi": PREFILL / e2e_prefill_s},
+        "whole_step_roofline": {"bytes_per_step": bytes_per_step,
+                                "achieved_gbs": bytes_per_step / (device_ms / steps / 1e3) / 1e9},
     }
+    if check:
+        result["parity"] = check
+        result["tokens_match_oracle"] = check["tokens_match_oracle"]
+        result["min_top2_margin"] = check["min_top2_margin"]
 
     if rank == 0:
-        peak, peak_kind = measured_peaks()
-        gbs, us, gemv_launches = gemv_roofline(L, torch, local_rank)
+        peak, tensor_peak, peak_kind = measured_peaks()
+        fast = args.mode == "fast"
+        gbs, us, gemv_launches = gemv_roofline(L, torch, local_rank, flags=19 if fast else 3)
+        gbs_other, us_other, _ = gemv_roofline(L, torch, local_rank, flags=3 if fast else 19)
         result["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                              "traffic": GEMV_DRAM_TRAFFIC, "kernel": "gemv_q8_cols80_kernel", "shape": [1, GEMV_N, GEMV_K],
+                              "traffic": GEMV_DRAM_TRAFFIC, "traffic_source": "ncu capture of `bench.py --only gemv`, not this run",
+                              "kernel": "gemv_q8_cols80_kernel" + ("<fast>" if fast else ""), "shape": [1, GEMV_N, GEMV_K],
                               "us_per_launch": us, "launches_timed": gemv_launches, "peak_kind": f"of {peak_kind}",
                               "algorithmic_bytes_per_launch": GEMV_BYTES,
-                              "whole_model_effective_gbs": 4.61e9 / (device_ms / steps / 1e3) / 1e9}
-    if rank == 0 and world == 1:
-        tok_s, cpu_tokens, threads = oracle_decode(arena, args.cpu_steps, 1)
-        result["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                  "sample": f"{args.cpu_steps} greedy decode steps after an 8-token prefill of the same "
-                                            "model with the CPU oracle (OpenMP, all host threads)"}
+                              f"{other}_mode": {"achieved": gbs_other, "frac": gbs_other / peak, "us_per_launch": us_other}}
+        result["whole_step_roofline"]["frac"] = result["whole_step_roofline"]["achieved_gbs"] / peak
+        gemm_us, tops = gemm_alone(L, torch)
+        int8_peak = 2.0 * tensor_peak  # no int8 peak is on file: twice the measured dense bf16 burst
+        # The f32 accumulation per 32-block (convert, scale product, fma) runs on the CUDA cores:
+        # 3 operations per (row, column, block) on 148 SMs x 128 lanes at the sampled SM clock.
+        sm_mhz = clocks.get("sm_mhz") or clocks.get("sm_max_mhz") or 1965.0
+        epilogue_us = GEMM_M * GEMM_N * (GEMM_K // 32) * 3 / (148 * 128 * sm_mhz)
+        result["roofline_gemm"] = {"bound": "tensor", "kernel": "gemm_q8_tc_kernel", "shape": [GEMM_M, GEMM_N, GEMM_K],
+                                   "us_per_launch": gemm_us, "achieved": tops, "unit": "int8 TOP/s", "peak": int8_peak,
+                                   "peak_kind": f"2 x bf16 burst, of {peak_kind}", "frac": tops / int8_peak,
+                                   "epilogue_bound_us": epilogue_us,
+                                   "epilogue_bound_tops": 2.0 * GEMM_M * GEMM_N * GEMM_K / epilogue_us / 1e6,
+                                   "frac_of_epilogue_bound": epilogue_us / gemm_us}
+    if cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline
     if rank == 0:
         print(json.dumps(result))
     if world > 1:

@@ -59,6 +59,19 @@ int llmcp_b200_set_device(int device);
 void llmcp_b200_release_all(void);
 /* Kernel launches issued by this library since it was loaded. */
 uint64_t llmcp_b200_launch_count(void);
+/* Arithmetic mode (no counterpart in the reference, which has one order of operations).
+ *   0 exact: every f32 result is bit-identical to the reference's order (default);
+ *   1 fast : integer block dots, quantisation and bf16 rounding points unchanged; the reductions
+ *            whose order only moves f32 rounding (rms_norm's sum of squares, a decode GEMV row's sum
+ *            over its blocks, the one-token attention softmax over keys, the one-token
+ *            gated-delta-net sums over the key dimension) run as parallel trees.  Bars: logits
+ *            within 1e-2 of the exact mode, greedy tokens equal wherever the top-2 margin exceeds
+ *            the logit difference.
+ * The mode applies to engines created afterwards (the AOT entries create theirs at the first
+ * call for a given arena and state) and to the host-pointer operators of group 2.
+ * LLMCP_B200_MODE=fast|exact in the environment sets the initial value. */
+int llmcp_b200_set_mode(int mode);
+int llmcp_b200_get_mode(void);
 
 /* ---- 2. operators ------------------------------------------------------------------ */
 /* dtype: 0 = f32, 1 = bf16 (bit patterns in uint16).  activation: 0 none, 1 silu,
@@ -125,9 +138,9 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
  *                         dependent of the kernel in front (weights are requested while that
  *                         kernel still runs; x is read only after it has finished), 2 = also
  *                         prefetch into L2 what the launch reads after its first round of
- *                         loads, 4 = feed the weights through shared-memory rings with bulk
- *                         asynchronous copies (K = 2560, 4096, 9216; slower, for comparison),
- *                         8 = use the row kernel where a block-column kernel would be chosen.
+ *                         loads, 8 = use the row kernel where a block-column kernel would be
+ *                         chosen, 16 = fast mode: a row's block products are added by a parallel
+ *                         tree instead of the reference's ascending fma chain.
  *   llmcp_dev_gemm_q8   : M > 1 linear (Q8Matmul.cpp:143-289), integer dot products on dp4a.
  *   llmcp_dev_gemm_q8_tc: the same contraction on the tcgen05 tensor cores.  wd32 holds the
  *                         weight scales widened to f32, [N][K/32].  status (device int, may be
@@ -211,6 +224,9 @@ uint64_t llmcp_b200_manifest(const uint8_t *file, uint64_t file_bytes, char *buf
  * weights out for the GPU, and allocates state for `capacity` positions.  NULL on failure. */
 void *llmcp_b200_engine_create(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims,
                                int64_t capacity, int device);
+/* The same with an explicit arithmetic mode (see llmcp_b200_set_mode). */
+void *llmcp_b200_engine_create_mode(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims,
+                                    int64_t capacity, int device, int mode);
 void llmcp_b200_engine_destroy(void *engine);
 int llmcp_b200_engine_reset(void *engine);
 /* One forward over host tokens (the work of lib/Runtime/AotRuntime.cpp:68-120): logits

@@ -70,6 +70,7 @@ def lib():
         handle.llmcp_b200_manifest.restype = C.c_uint64
         handle.llmcp_b200_read_safetensors.restype = C.c_uint64
         handle.llmcp_b200_engine_create.restype = C.c_void_p
+        handle.llmcp_b200_engine_create_mode.restype = C.c_void_p
         handle._mlir_ciface_llmcp_model_prefill.restype = None
         handle._mlir_ciface_llmcp_model_decode.restype = None
         _lib = handle
@@ -97,6 +98,20 @@ def set_device(index):
 
 def launch_count():
     return int(lib().llmcp_b200_launch_count())
+
+
+MODES = {"exact": 0, "fast": 1}
+
+
+def set_mode(mode):
+    """Arithmetic mode of engines created afterwards and of the host-pointer operators:
+    ``"exact"`` (bit-identical to the reference's order of operations) or ``"fast"``
+    (parallel-tree reductions; see llmcp_b200_set_mode in include/llmcp_b200.h)."""
+    _check(lib().llmcp_b200_set_mode(MODES[mode] if isinstance(mode, str) else int(mode)))
+
+
+def get_mode():
+    return {v: k for k, v in MODES.items()}[int(lib().llmcp_b200_get_mode())]
 
 
 def default_dims():
@@ -458,12 +473,17 @@ class AotRuntime:
 class Engine:
     """Device-resident executor (llmcp_b200_engine_* in include/llmcp_b200.h)."""
 
-    def __init__(self, container, dims=None, capacity=1160, device=0):
+    def __init__(self, container, dims=None, capacity=1160, device=0, mode=None):
         self.dims = dims or default_dims()
         self.container = np.ascontiguousarray(container, dtype=np.uint8)
         self.capacity = capacity
-        self.handle = lib().llmcp_b200_engine_create(_p(self.container), C.c_uint64(self.container.size),
-                                                     C.byref(self.dims), _i(capacity), int(device))
+        if mode is None:
+            self.handle = lib().llmcp_b200_engine_create(_p(self.container), C.c_uint64(self.container.size),
+                                                         C.byref(self.dims), _i(capacity), int(device))
+        else:
+            self.handle = lib().llmcp_b200_engine_create_mode(
+                _p(self.container), C.c_uint64(self.container.size), C.byref(self.dims), _i(capacity), int(device),
+                MODES[mode] if isinstance(mode, str) else int(mode))
         if not self.handle:
             raise LlmcpError(last_error())
         self.handle = C.c_void_p(self.handle)

@@ -385,6 +385,17 @@ void llmcp_b200_release_all(void) {
 
 uint64_t llmcp_b200_launch_count(void) { return g_launches.load(); }
 
+int llmcp_b200_set_mode(int mode) {
+  if (mode != kModeExact && mode != kModeFast) {
+    set_error("mode must be 0 (exact) or 1 (fast)");
+    return 1;
+  }
+  set_default_mode(mode);
+  return 0;
+}
+
+int llmcp_b200_get_mode(void) { return default_mode(); }
+
 // ---- operators on host pointers ------------------------------------------------------
 int llmcp_op_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales) {
   return guarded([&] {
@@ -418,7 +429,8 @@ int llmcp_op_linear_q8(const void *x, int x_dtype, int64_t M, int64_t K, const u
                   block_dots ? dots.as<int32_t>() : nullptr);
     else
       run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), N, dy.p, y_dtype, activation,
-                 block_dots ? dots.as<int32_t>() : nullptr, 0, nullptr);
+                 block_dots ? dots.as<int32_t>() : nullptr, 0, nullptr,
+                 default_mode() == kModeFast && !block_dots ? kGemvFast : 0);
     cuda_check(cudaDeviceSynchronize(), "linear");
     dy.to_host(y, dy.bytes);
     if (block_dots)
@@ -468,7 +480,8 @@ int llmcp_op_embedding_q8(const int64_t *tokens, int64_t S, const uint8_t *table
       return;
     DeviceQ8 w(table, vocab, hidden);
     Buf dt(static_cast<size_t>(S) * 8, tokens), dy(static_cast<size_t>(S) * hidden * 2);
-    launch_embedding_q8(dt.as<int64_t>(), S, hidden, w.q.as<int8_t>(), w.d.as<uint16_t>(), dy.as<uint16_t>(), nullptr);
+    launch_embedding_q8(dt.as<int64_t>(), S, hidden, vocab, w.q.as<int8_t>(), w.d.as<uint16_t>(), dy.as<uint16_t>(), nullptr,
+                        nullptr);
     g_launches += 1;
     cuda_check(cudaDeviceSynchronize(), "embedding");
     dy.to_host(out, dy.bytes);
@@ -482,8 +495,14 @@ int llmcp_op_rms_norm(const uint16_t *x, int64_t M, int64_t H, const void *weigh
     if (M <= 0 || H <= 0)
       return;
     Buf dx(static_cast<size_t>(M) * H * 2, x), dw(static_cast<size_t>(H) * elem(w_dtype), weight), dy(static_cast<size_t>(M) * H * 2);
-    cuda_check(launch_rms_norm(dx.as<uint16_t>(), nullptr, M, static_cast<int>(H), dw.p, w_dtype, eps, zero_centered,
-                               nullptr, dy.as<uint16_t>(), nullptr, nullptr, nullptr), "rms_norm");
+    cudaError_t e = cudaErrorNotSupported;
+    if (default_mode() == kModeFast)
+      e = launch_rms_norm_fast(dx.as<uint16_t>(), nullptr, M, static_cast<int>(H), dw.p, w_dtype, eps, zero_centered, nullptr,
+                               dy.as<uint16_t>(), nullptr, nullptr, nullptr);
+    if (e == cudaErrorNotSupported)
+      e = launch_rms_norm(dx.as<uint16_t>(), nullptr, M, static_cast<int>(H), dw.p, w_dtype, eps, zero_centered, nullptr,
+                          dy.as<uint16_t>(), nullptr, nullptr, nullptr);
+    cuda_check(e, "rms_norm");
     g_launches += 1;
     cuda_check(cudaDeviceSynchronize(), "rms_norm");
     dy.to_host(y, dy.bytes);
@@ -583,7 +602,17 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
         dqn(static_cast<size_t>(hd) * 2, q_norm), dkn(static_cast<size_t>(hd) * 2, k_norm), dcos(static_cast<size_t>(S) * rot * 4, cos),
         dsin(static_cast<size_t>(S) * rot * 4, sin), dcache(static_cast<size_t>(2) * nkv * cap * hd * 2, cache),
         dout(static_cast<size_t>(S) * nh * hd * 2),
-        scratch(attn_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(hd), position)), dpos(8, &position);
+        scratch(std::max(attn_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(hd), position),
+                         attn_fast_scratch_bytes(static_cast<int>(nh), static_cast<int>(hd), position + S - 1))),
+        dpos(8, &position);
+    if (default_mode() == kModeFast && S == 1 &&
+        attention_decode_fast_supported(static_cast<int>(nh), static_cast<int>(nkv), static_cast<int>(hd))) {
+      cuda_check(launch_attention_decode_fast(dqg.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(), dqn.as<uint16_t>(),
+                                              dkn.as<uint16_t>(), dcos.as<float>(), dsin.as<float>(), 0, dcache.as<uint16_t>(),
+                                              dpos.as<int64_t>(), position, static_cast<int>(nh), static_cast<int>(nkv),
+                                              static_cast<int>(hd), static_cast<int>(rot), cap, scratch.p, dout.as<uint16_t>(),
+                                              nullptr, nullptr, nullptr), "attention (fast)");
+    } else
     cuda_check(launch_attention(dqg.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(), dqn.as<uint16_t>(),
                                 dkn.as<uint16_t>(), dcos.as<float>(), dsin.as<float>(), 0, dcache.as<uint16_t>(),
                                 dpos.as<int64_t>(), position, S,
@@ -805,6 +834,20 @@ void *llmcp_b200_engine_create(const uint8_t *file, uint64_t file_bytes, const l
     const ModelDims d = to_dims(dims);
     check_dims(d);
     return new Engine(file, file_bytes, d, capacity, device);
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return nullptr;
+  }
+}
+
+void *llmcp_b200_engine_create_mode(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims, int64_t capacity,
+                                    int device, int mode) {
+  try {
+    const ModelDims d = to_dims(dims);
+    check_dims(d);
+    if (mode != kModeExact && mode != kModeFast)
+      throw std::runtime_error("mode must be 0 (exact) or 1 (fast)");
+    return new Engine(file, file_bytes, d, capacity, device, mode);
   } catch (const std::exception &e) {
     set_error(e.what());
     return nullptr;

@@ -11,6 +11,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <set>
+#include <utility>
+
 namespace llmcp_b200 {
 
 constexpr int kBlock = 32;          // weights per Q8_0 block (Q8PackedLayout.h:21)
@@ -109,6 +113,34 @@ __device__ __forceinline__ void grid_dependency_sync(bool release_early = false)
   if (release_early)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device).  The attribute belongs
+// to the device that is current when it is set, so a process that drives several GPUs has to make
+// the opt-in on each of them; the record of what has been done is guarded by a mutex.
+inline cudaError_t opt_in_shared_memory(const void *kernel, size_t bytes) {
+  static std::mutex mutex;
+  static std::set<std::pair<const void *, int>> done;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess)
+    return e;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (done.count({kernel, device}))
+    return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e == cudaSuccess)
+    done.insert({kernel, device});
+  return e;
+}
+
+// Number of SMs of the current device.
+inline cudaError_t current_sm_count(int *sms) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e == cudaSuccess)
+    e = cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, device);
+  return e;
 }
 
 // false when LLMCP_B200_PDL=0: kernels are then launched fully serialised.

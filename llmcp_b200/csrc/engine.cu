@@ -1,5 +1,6 @@
 #include "engine.h"
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -44,21 +45,37 @@ int dtype_of(const TensorEntry &t) {
   throw std::runtime_error("tensor " + t.name + " has dtype " + t.dtype + ", expected BF16 or F32");
 }
 
+std::atomic<int> g_default_mode{-1};
+
 } // namespace
+
+int default_mode() {
+  const int stored = g_default_mode.load();
+  if (stored >= 0)
+    return stored;
+  if (const char *flag = std::getenv("LLMCP_B200_MODE"))
+    return (std::string(flag) == "fast" || std::string(flag) == "1") ? kModeFast : kModeExact;
+  return kModeExact;
+}
+
+void set_default_mode(int mode) { g_default_mode.store(mode == kModeFast ? kModeFast : kModeExact); }
 
 void Engine::check(cudaError_t e, const char *what) {
   if (e != cudaSuccess)
     throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device)
-    : dims_(dims), capacity_(capacity), device_(device) {
+Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode)
+    : dims_(dims), capacity_(capacity), device_(device), mode_(mode < 0 ? default_mode() : (mode == kModeFast ? kModeFast : kModeExact)) {
   if (capacity <= 0)
     throw std::runtime_error("capacity must be positive");
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
     throw std::runtime_error("no CUDA device: this library has no CPU path");
   check(cudaSetDevice(device), "cudaSetDevice");
+  // A constructor that throws does not run the destructor: everything acquired so far is released
+  // here, so that a failed create leaves no device or pinned memory behind.
+  try {
   check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
 
   Manifest manifest;
@@ -130,26 +147,71 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   run(tokens_, 1, capacity_ - 1, cos_table_, sin_table_, 1);
   reset_state();
   check(cudaStreamSynchronize(stream_), "engine setup");
+  } catch (...) {
+    release();
+    throw;
+  }
 }
 
-Engine::~Engine() {
+Engine::~Engine() { release(); }
+
+void Engine::release() noexcept {
   cudaSetDevice(device_);
   if (stream_)
     cudaStreamSynchronize(stream_);
+  if (decode_graph_)
+    cudaGraphExecDestroy(decode_graph_);
+  decode_graph_ = nullptr;
   for (void *p : ws_allocations_)
     cudaFree(p);
+  ws_allocations_.clear();
   for (void *p : allocations_)
     cudaFree(p);
+  allocations_.clear();
   if (logits_pinned_)
     cudaFreeHost(logits_pinned_);
   if (token_pinned_)
     cudaFreeHost(token_pinned_);
   if (position_pinned_)
     cudaFreeHost(position_pinned_);
-  if (decode_graph_)
-    cudaGraphExecDestroy(decode_graph_);
+  logits_pinned_ = nullptr;
+  token_pinned_ = nullptr;
+  position_pinned_ = nullptr;
   if (stream_)
     cudaStreamDestroy(stream_);
+  stream_ = nullptr;
+  cudaGetLastError();
+}
+
+void Engine::validate_tokens(const int64_t *tokens, int64_t S) const {
+  for (int64_t i = 0; i < S; ++i)
+    if (tokens[i] < 0 || tokens[i] >= dims_.vocab)
+      throw std::runtime_error("token id " + std::to_string(tokens[i]) + " at index " + std::to_string(i) +
+                               " is outside the vocabulary [0, " + std::to_string(dims_.vocab) + ")");
+}
+
+void Engine::check_status() {
+  const int status = *reinterpret_cast<const int *>(token_pinned_ + 1);
+  if (status == 0)
+    return;
+  cudaMemsetAsync(gemm_error_, 0, 4, stream_);
+  if (status & 2)
+    throw std::runtime_error("a token id outside the vocabulary reached the embedding kernel");
+  throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
+}
+
+// rms_norm of the forward (zero-centred weight, fused residual add and quantisation); the fast
+// mode takes the tree-reduced kernel where the row length allows.
+void Engine::rms_norm(const uint16_t *a, const uint16_t *b, int64_t S, const SmallTensor &w, uint16_t *sum_out, uint16_t *y) {
+  const int H = static_cast<int>(dims_.hidden);
+  if (mode_ == kModeFast) {
+    const cudaError_t e = launch_rms_norm_fast(a, b, S, H, w.data, w.dtype, dims_.eps, 1, sum_out, y, aq_, as_, stream_);
+    if (e == cudaSuccess)
+      return;
+    if (e != cudaErrorNotSupported)
+      check(e, "rms_norm (fast)");
+  }
+  check(launch_rms_norm(a, b, S, H, w.data, w.dtype, dims_.eps, 1, sum_out, y, aq_, as_, stream_), "rms_norm");
 }
 
 void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
@@ -170,6 +232,7 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   check(cudaMalloc(&pool, pool_bytes), "cudaMalloc(weights)");
   allocations_.push_back(pool);
   check(cudaMalloc(&staging, std::max<size_t>(staging_bytes, 256)), "cudaMalloc(staging)");
+  allocations_.push_back(staging); // released with the rest if loading throws
   size_t cursor = 0;
   auto take = [&](size_t bytes) {
     uint8_t *p = pool + cursor;
@@ -248,6 +311,7 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   }
   final_norm_ = small(root + "norm.weight", c.hidden);
   check(cudaStreamSynchronize(stream_), "weight upload");
+  allocations_.pop_back();
   cudaFree(staging);
 }
 
@@ -279,7 +343,9 @@ void Engine::download_state(uint16_t *kv, float *delta, uint16_t *conv) {
 
 void Engine::ensure_workspace(int64_t S, int64_t position) {
   const ModelDims &c = dims_;
-  const size_t need_attn = attn_scratch_bytes(S, static_cast<int>(c.heads), static_cast<int>(c.head_dim), position);
+  const size_t need_attn =
+      std::max(attn_scratch_bytes(S, static_cast<int>(c.heads), static_cast<int>(c.head_dim), position),
+               attn_fast_scratch_bytes(static_cast<int>(c.heads), static_cast<int>(c.head_dim), position + S - 1));
   if (S <= ws_tokens_ && need_attn <= attn_scratch_bytes_)
     return;
   check(cudaStreamSynchronize(stream_), "workspace resize");
@@ -410,20 +476,19 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     throw std::runtime_error("sequence does not fit the cache: position " + std::to_string(position) + " + " +
                              std::to_string(S) + " > capacity " + std::to_string(capacity_));
   ensure_workspace(S, position);
-  launch_embedding_q8(tokens_dev, S, H, embed_.q, embed_.d, hidden_[0], stream_);
+  launch_embedding_q8(tokens_dev, S, H, c.vocab, embed_.q, embed_.d, hidden_[0], gemm_error_, stream_);
   launches_ += 1;
+  const int gemv_flags = gemv_flags_ | (mode_ == kModeFast ? kGemvFast : 0);
   int cur = 0;
   bool pending = false;
   int64_t lin_index = 0, full_index = 0;
   for (int64_t l = 0; l < c.layers; ++l) {
     const LayerWeights &L = layers_[static_cast<size_t>(l)];
     if (pending) {
-      check(launch_rms_norm(hidden_[cur], mlp_out_, S, H, L.input_norm.data, L.input_norm.dtype, c.eps, 1,
-                            hidden_[cur ^ 1], nullptr, aq_, as_, stream_), "rms_norm");
+      rms_norm(hidden_[cur], mlp_out_, S, L.input_norm, hidden_[cur ^ 1], nullptr);
       cur ^= 1;
     } else {
-      check(launch_rms_norm(hidden_[cur], nullptr, S, H, L.input_norm.data, L.input_norm.dtype, c.eps, 1, nullptr,
-                            nullptr, aq_, as_, stream_), "rms_norm");
+      rms_norm(hidden_[cur], nullptr, S, L.input_norm, nullptr, nullptr);
     }
     launches_ += 1;
     if (!L.full) {
@@ -431,7 +496,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
+      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
       const int C = static_cast<int>(c.qkv_dim());
       uint16_t *conv_state = conv_ + lin_index * (c.conv_kernel - 1) * C;
       float *delta_state = delta_ + lin_index * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
@@ -453,46 +518,54 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
         launches_ += 5;
       }
       const LinearJob out = {&L.out_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
-      check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
-                             static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
-                             kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim, position_dev_, position, S,
-                             static_cast<int>(c.heads), static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim),
-                             static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, aq_, as_, stream_), "attention");
+      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+      uint16_t *cache = kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim;
+      if (mode_ == kModeFast && S == 1 &&
+          attention_decode_fast_supported(static_cast<int>(c.heads), static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim))) {
+        check(launch_attention_decode_fast(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
+                                           static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
+                                           cache, position_dev_, position, static_cast<int>(c.heads),
+                                           static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim),
+                                           static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, aq_, as_, stream_),
+              "attention (fast)");
+      } else {
+        check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
+                               static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position, cache,
+                               position_dev_, position, S, static_cast<int>(c.heads), static_cast<int>(c.kv_heads),
+                               static_cast<int>(c.head_dim), static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, aq_,
+                               as_, stream_), "attention");
+      }
       launches_ += 3;
       const LinearJob out = {&L.o_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
+      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
       ++full_index;
     }
-    check(launch_rms_norm(hidden_[cur], branch_, S, H, L.post_norm.data, L.post_norm.dtype, c.eps, 1, hidden_[cur ^ 1],
-                          nullptr, aq_, as_, stream_), "rms_norm");
+    rms_norm(hidden_[cur], branch_, S, L.post_norm, hidden_[cur ^ 1], nullptr);
     cur ^= 1;
     const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
+    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
     check(launch_pointwise(gate_, up_, S * c.intermediate, 1, nullptr, aq_, as_, stream_), "mul");
     launches_ += 2;
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
-    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags_, use_tensor_cores_ ? gemm_error_ : nullptr);
+    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
     pending = true;
   }
   if (all_logits_) {
     // Every position's logits, what the tensor-returning `llmcp_model` function computes
     // (ModelBuilder.cpp:406-438): final norm over all rows, then one S x vocab x hidden contraction.
-    check(launch_rms_norm(hidden_[cur], pending ? mlp_out_ : nullptr, S, H, final_norm_.data, final_norm_.dtype, c.eps, 1,
-                          nullptr, branch_, aq_, as_, stream_), "final rms_norm, all rows");
+    rms_norm(hidden_[cur], pending ? mlp_out_ : nullptr, S, final_norm_, nullptr, branch_);
     const LinearJob all = {&embed_, all_logits_, kF32, kNone};
-    run_linears(this, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious,
+    run_linears(this, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags & kGemvOverlapPrevious,
                 S > 1 && use_tensor_cores_ ? gemm_error_ : nullptr);
     launches_ += 1;
   }
   // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
   const uint16_t *last = hidden_[cur] + (S - 1) * H;
-  check(launch_rms_norm(last, pending ? mlp_out_ + (S - 1) * H : nullptr, 1, H, final_norm_.data, final_norm_.dtype,
-                        c.eps, 1, nullptr, final_hidden_, aq_, as_, stream_), "final rms_norm");
+  rms_norm(last, pending ? mlp_out_ + (S - 1) * H : nullptr, 1, final_norm_, nullptr, final_hidden_);
   const Q8Weight &table = embed_;
   const LinearJob head = {&table, logits_, kF32, kNone};
   run_linears(this, aq_, as_, 1, &head, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious);
@@ -507,6 +580,7 @@ int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position,
   check(cudaSetDevice(device_), "cudaSetDevice");
   if (S <= 0 || position < 0 || position + S > capacity_)
     throw std::runtime_error("sequence does not fit the cache");
+  validate_tokens(tokens, S); // before any copy or launch
   ensure_workspace(S, position);
   const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
   if (S == 1) {
@@ -543,10 +617,7 @@ int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position,
     check(cudaMemcpyAsync(logits_pinned_, logits_, static_cast<size_t>(c.vocab) * 4, cudaMemcpyDeviceToHost, stream_), "logits");
   check(cudaMemcpyAsync(token_pinned_, next_token_, 16, cudaMemcpyDeviceToHost, stream_), "argmax and GEMM status");
   check(cudaStreamSynchronize(stream_), "forward");
-  if (*reinterpret_cast<const int *>(token_pinned_ + 1) != 0) {
-    cudaMemsetAsync(gemm_error_, 0, 4, stream_);
-    throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
-  }
+  check_status();
   if (logits_host)
     std::memcpy(logits_host, logits_pinned_, static_cast<size_t>(c.vocab) * 4);
   return *token_pinned_;
@@ -559,6 +630,7 @@ void Engine::forward_all_host(const int64_t *tokens, int64_t S, int64_t position
     throw std::runtime_error("sequence does not fit the cache");
   if (!logits_host)
     throw std::runtime_error("forward_all needs a logits buffer of S x vocab floats");
+  validate_tokens(tokens, S);
   ensure_workspace(S, position);
   const size_t bytes = static_cast<size_t>(S) * c.vocab * sizeof(float);
   float *device_rows = nullptr;
@@ -582,10 +654,7 @@ void Engine::forward_all_host(const int64_t *tokens, int64_t S, int64_t position
     throw;
   }
   cudaFree(device_rows);
-  if (*reinterpret_cast<const int *>(token_pinned_ + 1) != 0) {
-    cudaMemsetAsync(gemm_error_, 0, 4, stream_);
-    throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
-  }
+  check_status();
 }
 
 void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int64_t *out_tokens_host, float *device_ms) {
@@ -595,6 +664,7 @@ void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int6
     throw std::runtime_error("generation does not fit the cache");
   if (c.rotary > 1024)
     throw std::runtime_error("rotary dimension too large");
+  validate_tokens(&first_token, 1);
   set_position(position);
   *token_pinned_ = first_token;
   check(cudaMemcpyAsync(dec_tokens_, token_pinned_, 8, cudaMemcpyHostToDevice, stream_), "first token");
@@ -602,21 +672,29 @@ void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int6
   const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
   check(cudaMemcpyAsync(dec_cos_, cos_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "cos");
   check(cudaMemcpyAsync(dec_sin_, sin_table_ + position * c.rotary, row_bytes, cudaMemcpyDeviceToDevice, stream_), "sin");
-  cudaEvent_t begin, end;
-  check(cudaEventCreate(&begin), "event");
-  check(cudaEventCreate(&end), "event");
-  check(cudaEventRecord(begin, stream_), "event");
-  const int threads = static_cast<int>((c.rotary + 31) / 32 * 32);
-  for (int64_t i = 0; i < steps; ++i) {
-    decode_step();
-    launch_chained(advance_kernel, dim3(1), dim3(threads), 0, stream_, next_token_, dec_tokens_, generated_, step_dev_, position_dev_, cos_table_,
-                                               sin_table_, dec_cos_, dec_sin_, static_cast<int>(c.rotary), capacity_);
-    launches_ += 1;
+  cudaEvent_t begin = nullptr, end = nullptr;
+  try {
+    check(cudaEventCreate(&begin), "event");
+    check(cudaEventCreate(&end), "event");
+    check(cudaEventRecord(begin, stream_), "event");
+    const int threads = static_cast<int>((c.rotary + 31) / 32 * 32);
+    for (int64_t i = 0; i < steps; ++i) {
+      decode_step();
+      launch_chained(advance_kernel, dim3(1), dim3(threads), 0, stream_, next_token_, dec_tokens_, generated_, step_dev_,
+                     position_dev_, cos_table_, sin_table_, dec_cos_, dec_sin_, static_cast<int>(c.rotary), capacity_);
+      launches_ += 1;
+    }
+    check(cudaEventRecord(end, stream_), "event");
+    check(cudaStreamSynchronize(stream_), "generate");
+    if (device_ms)
+      check(cudaEventElapsedTime(device_ms, begin, end), "event");
+  } catch (...) {
+    if (begin)
+      cudaEventDestroy(begin);
+    if (end)
+      cudaEventDestroy(end);
+    throw;
   }
-  check(cudaEventRecord(end, stream_), "event");
-  check(cudaStreamSynchronize(stream_), "generate");
-  if (device_ms)
-    check(cudaEventElapsedTime(device_ms, begin, end), "event");
   cudaEventDestroy(begin);
   cudaEventDestroy(end);
   if (out_tokens_host)

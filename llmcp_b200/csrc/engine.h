@@ -36,11 +36,24 @@ struct LayerWeights {
   Q8Weight gate, up, down;
 };
 
+// Arithmetic mode of an engine.
+//   kModeExact: every f32 result is bit-identical to the reference's order of operations.
+//   kModeFast : the integer block dots, the quantisation and the rounding points are unchanged, but
+//               reductions whose order only affects f32 rounding (rms_norm's sum of squares, a GEMV
+//               row's sum over blocks, the attention softmax over keys of the one-token step) are
+//               evaluated as parallel trees.  Logits agree with the exact mode within 1e-2.
+enum Mode : int { kModeExact = 0, kModeFast = 1 };
+// Mode of engines created without an explicit one: LLMCP_B200_MODE=fast|exact in the environment,
+// else what set_default_mode() last stored, else exact.
+int default_mode();
+void set_default_mode(int mode);
+
 class Engine {
 public:
   // `base` points at the first byte of a mapped container (header, arena, manifest).
+  // mode: kModeExact, kModeFast, or -1 for default_mode().
   // Throws std::runtime_error with a readable message on any failure.
-  Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device);
+  Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode = -1);
   ~Engine();
   Engine(const Engine &) = delete;
   Engine &operator=(const Engine &) = delete;
@@ -48,6 +61,7 @@ public:
   const ModelDims &dims() const { return dims_; }
   int64_t capacity() const { return capacity_; }
   int device() const { return device_; }
+  int mode() const { return mode_; }
   cudaStream_t stream() const { return stream_; }
 
   void reset_state();
@@ -80,6 +94,10 @@ public:
   uint64_t launches() const { return launches_; }
 
 private:
+  void release() noexcept; // frees everything the engine holds; safe on a half-built engine
+  void validate_tokens(const int64_t *tokens, int64_t S) const;
+  void check_status(); // throws if the device status word copied to token_pinned_ is non-zero
+  void rms_norm(const uint16_t *a, const uint16_t *b, int64_t S, const SmallTensor &w, uint16_t *sum_out, uint16_t *y);
   void load_weights(const uint8_t *base, const Manifest &manifest);
   void ensure_workspace(int64_t S, int64_t position);
   // Enqueues one forward over S tokens whose ids are at tokens_dev.  The start position is read
@@ -97,6 +115,7 @@ private:
   ModelDims dims_;
   int64_t capacity_ = 0;
   int device_ = 0;
+  int mode_ = kModeExact;
   cudaStream_t stream_ = nullptr;
   uint64_t launches_ = 0;
 

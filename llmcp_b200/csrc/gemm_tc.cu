@@ -355,14 +355,8 @@ cudaError_t launch_gemm_q8_tc(const int8_t *aq, const float *as, int M, int K, c
                               cudaStream_t stream) {
   if (M <= 0 || N % 8 != 0 || K % kBlock != 0)
     return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_q8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kSmemBytes));
-    if (e != cudaSuccess)
-      return e;
-    configured = true;
-  }
+  if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(gemm_q8_tc_kernel), kSmemBytes); e != cudaSuccess)
+    return e;
   dim3 grid((N + kTileN - 1) / kTileN, (M + kTileM - 1) / kTileM);
   launch_chained(gemm_q8_tc_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, aq, as, M, K, wq, ws, N, y, y_dtype, activation, dots_out,
                                                             error_flag);

@@ -28,7 +28,9 @@ __device__ inline ColsBlock ld_cols_block(const void *p) {
   return r;
 }
 
-template <int NB, int R, bool DOTS>
+// FAST: the row's block products  float(dot) * (a_scale * w_scale)  are added by a warp (lane-strided
+// partial sums, then shuffles) instead of the ascending fma chain.
+template <int NB, int R, bool DOTS, bool FAST>
 __global__ void __launch_bounds__(NB)
 gemv_q8_cols_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const int8_t *__restrict__ wq,
                     const uint16_t *__restrict__ wd, void *__restrict__ y, int N, int activation, int y_dtype,
@@ -65,12 +67,32 @@ gemv_q8_cols_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
       dot = dp4a(static_cast<int>(w[i].v[5]), static_cast<int>(hi.y), dot);
       dot = dp4a(static_cast<int>(w[i].v[6]), static_cast<int>(hi.z), dot);
       dot = dp4a(static_cast<int>(w[i].v[7]), static_cast<int>(hi.w), dot);
-      slab[i * kStride + t] = make_float2(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
+      if (FAST)
+        reinterpret_cast<float *>(slab)[i * (NB + 1) + t] =
+            __fmul_rn(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
+      else
+        slab[i * kStride + t] = make_float2(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
       if (DOTS)
         dots_out[static_cast<size_t>(row0 + i) * NB + t] = dot;
     }
   }
   __syncthreads();
+  if (FAST) {
+    const int lane = t & 31;
+    for (int r = t >> 5; r < rows; r += NB / 32) {
+      const float *mine = reinterpret_cast<const float *>(slab) + r * (NB + 1);
+      float acc = 0.0f;
+#pragma unroll
+      for (int p = 0; p < NB / 32; ++p)
+        acc = __fadd_rn(acc, mine[lane + 32 * p]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+      if (lane == 0)
+        store_from_f32(y, y_dtype, row0 + r, apply_activation(acc, activation));
+    }
+    return;
+  }
   if (t < rows) {
     const float4 *mine = reinterpret_cast<const float4 *>(slab + t * kStride);
     float acc = 0.0f;
@@ -103,11 +125,14 @@ cudaError_t launch_cols(const int8_t *aq, const float *as, const GemvJob &job, i
   config.attrs = attribute;
   config.numAttrs = (flags & kGemvOverlapPrevious) ? 1 : 0;
   if (dots_out)
-    return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, true>, aq, as, job.wq, job.wd, job.y, job.N, job.activation,
-                              job.y_dtype, dots_out);
+    return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, true, false>, aq, as, job.wq, job.wd, job.y, job.N,
+                              job.activation, job.y_dtype, dots_out);
   int32_t *no_dots = nullptr;
-  return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, false>, aq, as, job.wq, job.wd, job.y, job.N, job.activation,
-                            job.y_dtype, no_dots);
+  if (flags & kGemvFast)
+    return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, false, true>, aq, as, job.wq, job.wd, job.y, job.N,
+                              job.activation, job.y_dtype, no_dots);
+  return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, false, false>, aq, as, job.wq, job.wd, job.y, job.N,
+                            job.activation, job.y_dtype, no_dots);
 }
 
 // K = 2560 (80 blocks per row), up to four matrices that share the input row.  160 threads: thread
@@ -116,12 +141,14 @@ cudaError_t launch_cols(const int8_t *aq, const float *as, const GemvJob &job, i
 // issued before the 16 chains of the current one run.
 constexpr int kSetRows = 16;
 
-template <bool DOTS>
+// FAST: eight threads per row add ten block products each, then three shuffles, instead of the chain.
+template <bool DOTS, bool FAST>
 __global__ void __launch_bounds__(160, 4)
 gemv_q8_cols80_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const GemvJobs jobs, int total_sets,
                       int32_t *__restrict__ dots_out) {
   constexpr int NB = 80, K = 2560, kHalf = kSetRows / 2;
   constexpr int kStride = NB + 2;
+  constexpr int kFastStride = 88; // floats: the four rows a warp sums start on banks 0, 24, 16, 8
   __shared__ __align__(16) float2 slab[kSetRows * kStride];
   const int t = threadIdx.x;
   const int kb = t % NB, half = t / NB;
@@ -193,14 +220,32 @@ gemv_q8_cols80_kernel(const int8_t *__restrict__ aq, const float *__restrict__ a
       dot = dp4a(static_cast<int>(w[i].v[6]), static_cast<int>(hi.z), dot);
       dot = dp4a(static_cast<int>(w[i].v[7]), static_cast<int>(hi.w), dot);
       const int row = half * kHalf + i;
-      slab[row * kStride + kb] = make_float2(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
+      if (FAST)
+        reinterpret_cast<float *>(slab)[row * kFastStride + kb] =
+            __fmul_rn(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
+      else
+        slab[row * kStride + kb] = make_float2(static_cast<float>(dot), __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i])));
       if (DOTS)
         dots_out[static_cast<size_t>(c.dots_offset + c.row0 + row) * NB + kb] = dot;
     }
     __syncthreads();
     if (s + gridDim.x < total_sets)
-      load(resolve(s + gridDim.x)); // travels while the chains below run
-    if (t < kSetRows) {
+      load(resolve(s + gridDim.x)); // travels while the sums below run
+    if (FAST) {
+      if (t < kSetRows * 8) {
+        const int row = t >> 3, j = t & 7;
+        const float *mine = reinterpret_cast<const float *>(slab) + row * kFastStride + j;
+        float acc = 0.0f;
+#pragma unroll
+        for (int p = 0; p < NB / 8; ++p)
+          acc = __fadd_rn(acc, mine[8 * p]);
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+        if (j == 0)
+          store_from_f32(c.y, c.y_dtype, c.row0 + row, apply_activation(acc, c.activation));
+      }
+    } else if (t < kSetRows) {
       const float4 *mine = reinterpret_cast<const float4 *>(slab + t * kStride);
       float acc = 0.0f;
       for (int p = 0; p < NB / 2; p += 8) {
@@ -239,9 +284,11 @@ cudaError_t launch_cols80(const int8_t *aq, const float *as, GemvJobs jobs, int3
   config.attrs = attribute;
   config.numAttrs = (jobs.flags & kGemvOverlapPrevious) ? 1 : 0;
   if (dots_out)
-    return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<true>, aq, as, jobs, sets, dots_out);
+    return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<true, false>, aq, as, jobs, sets, dots_out);
   int32_t *no_dots = nullptr;
-  return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<false>, aq, as, jobs, sets, no_dots);
+  if (jobs.flags & kGemvFast)
+    return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<false, true>, aq, as, jobs, sets, no_dots);
+  return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<false, false>, aq, as, jobs, sets, no_dots);
 }
 
 } // namespace

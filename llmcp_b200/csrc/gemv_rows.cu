@@ -241,23 +241,14 @@ cudaError_t launch_rows(const int8_t *aq, const float *as, GemvJobs jobs, int32_
     groups += jobs.job[t].N / RC;
     rows += jobs.job[t].N;
   }
-  static int sms = 0;
-  if (sms == 0) {
-    int device = 0;
-    cudaError_t e = cudaGetDevice(&device);
-    if (e == cudaSuccess)
-      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemv_q8_rows_kernel<NB, RC, RL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               200 * 1024);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemv_q8_rows_kernel<NB, RC, RL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               200 * 1024);
-    if (e != cudaSuccess) {
-      sms = 0;
-      return e;
-    }
-  }
+  int sms = 0;
+  cudaError_t e = current_sm_count(&sms);
+  if (e == cudaSuccess)
+    e = opt_in_shared_memory(reinterpret_cast<const void *>(gemv_q8_rows_kernel<NB, RC, RL, false>), 200 * 1024);
+  if (e == cudaSuccess)
+    e = opt_in_shared_memory(reinterpret_cast<const void *>(gemv_q8_rows_kernel<NB, RC, RL, true>), 200 * 1024);
+  if (e != cudaSuccess)
+    return e;
   // Eight-warp CTAs, several per SM; with about one group per resident warp every weight byte
   // of a small matrix is requested in the first microsecond.  More groups than resident warps
   // (the vocabulary projection) are walked with a grid stride.
@@ -265,8 +256,8 @@ cudaError_t launch_rows(const int8_t *aq, const float *as, GemvJobs jobs, int32_
   const size_t smem = rows_smem_bytes<NB, RC>(warps);
   static int ctas_per_sm = 0;
   if (ctas_per_sm == 0) {
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_q8_rows_kernel<NB, RC, RL, false>,
-                                                                  warps * 32, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, gemv_q8_rows_kernel<NB, RC, RL, false>, warps * 32,
+                                                      smem);
     if (e != cudaSuccess || ctas_per_sm < 1) {
       ctas_per_sm = 0;
       return e != cudaSuccess ? e : cudaErrorInvalidConfiguration;

@@ -30,8 +30,9 @@ constexpr int kGemvOverlapPrevious = 1; // programmatic dependent launch: start 
                                         // front is still running, wait for it before reading x
 constexpr int kGemvPrefetchL2 = 2;      // prefetch all weights of the launch into L2 up front
 constexpr int kGemvNoCols = 8;          // do not use the block-column kernel for long rows
-constexpr int kGemvRing = 4;            // feed the weights through per-warp shared-memory rings
-                                        // (bulk asynchronous copies), K in {2560, 4096, 9216}
+constexpr int kGemvFast = 16;           // fast mode: a row's block products are added by a parallel tree
+                                        // instead of the reference's ascending fma chain (the int32 block
+                                        // dots are unchanged; the f32 sum differs by rounding only)
 
 struct GemvJobs {
   GemvJob job[kMaxGemvJobs];
@@ -54,10 +55,6 @@ cudaError_t launch_gemv_q8_rows(const int8_t *aq, const float *as, int K, const 
 bool gemv_cols_supported(int K, const GemvJobs &jobs);
 cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
                                 cudaStream_t stream);
-// The same product with the weights streamed through shared-memory rings (gemv_ring.cu).
-bool gemv_ring_supported(int K, const GemvJobs &jobs);
-cudaError_t launch_gemv_q8_ring(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
-                                int *error_flag, cudaStream_t stream);
 cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K, const int8_t *wq,
                                 const uint16_t *wd, int N, void *y, int y_dtype, int activation,
                                 int32_t *dots_out, cudaStream_t stream);
@@ -67,8 +64,10 @@ size_t gemm_q8_tc_smem_bytes();
 cudaError_t launch_gemm_q8_tc(const int8_t *aq, const float *as, int M, int K, const int8_t *wq, const float *ws, int N,
                               void *y, int y_dtype, int activation, int32_t *dots_out, int *error_flag,
                               cudaStream_t stream);
-void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, const int8_t *wq, const uint16_t *wd,
-                         uint16_t *out, cudaStream_t stream);
+// status (device int, optional): bit 1 is raised when a token id lies outside [0, vocab); such a
+// row is written as zeros and the table is not read.
+void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, int64_t vocab, const int8_t *wq,
+                         const uint16_t *wd, uint16_t *out, int *status, cudaStream_t stream);
 // scratch_v / scratch_i: kArgmaxParts entries each.
 void launch_argmax(const float *x, int64_t n, float *scratch_v, int64_t *scratch_i, int64_t index_base,
                    int64_t *out_index, float *out_value, cudaStream_t stream);
@@ -76,6 +75,12 @@ void launch_argmax(const float *x, int64_t n, float *scratch_v, int64_t *scratch
 cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int H, const void *w, int w_dtype,
                             float eps, int zero_centered, uint16_t *sum_out, uint16_t *y, int8_t *q, float *s,
                             cudaStream_t stream);
+// Fast mode of rms_norm: the sum of squares is a tree reduction (warp shuffles), not the
+// reference's serial order, so the result can differ from launch_rms_norm in the last bit of rstd.
+// Rows with H % 8 == 0 and H <= 8192; cudaErrorNotSupported otherwise (nothing is launched).
+cudaError_t launch_rms_norm_fast(const uint16_t *a, const uint16_t *b, int64_t M, int H, const void *w, int w_dtype,
+                                 float eps, int zero_centered, uint16_t *sum_out, uint16_t *y, int8_t *q, float *s,
+                                 cudaStream_t stream);
 cudaError_t launch_gated_rms_norm(const uint16_t *x, const uint16_t *gate, const void *w, int w_dtype, int64_t M,
                                   int H, int group, float eps, int gate_activated, uint16_t *y, int8_t *q,
                                   float *s, cudaStream_t stream);
@@ -108,5 +113,25 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
                              uint16_t *cache, const int64_t *position_dev, int64_t max_position, int64_t S, int nh,
                              int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out,
                              float *s_out, cudaStream_t stream);
+
+// The first of the three attention launches alone: q/k RMSNorm, partial RoPE, q -> qn scratch
+// (bf16 [S, nh, hd]), k and v -> cache rows position .. position + S - 1.
+cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
+                                     const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
+                                     uint16_t *cache, const int64_t *position_dev, int64_t S, int nh, int nkv, int hd,
+                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream);
+// Fast mode of the one-token attention: after the same prepare kernel, the key range is split
+// over CTAs (each keeps a running maximum, denominator and weighted value sum for the query
+// heads of one KV head) and a second kernel merges the splits, applies the sigmoid gate and
+// quantises for o_proj.  The softmax is the same function as the reference's tile-ordered one
+// but sums in another order, so results agree to f32 rounding, not bit for bit.
+bool attention_decode_fast_supported(int nh, int nkv, int hd);
+size_t attn_fast_scratch_bytes(int nh, int hd, int64_t max_position);
+cudaError_t launch_attention_decode_fast(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
+                                         const uint16_t *q_norm, const uint16_t *k_norm, const float *cos,
+                                         const float *sin, int rows_from_position, uint16_t *cache,
+                                         const int64_t *position_dev, int64_t max_position, int nh, int nkv, int hd,
+                                         int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out,
+                                         float *s_out, cudaStream_t stream);
 
 } // namespace llmcp_b200

@@ -1440,6 +1440,18 @@ size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t max_position) {
          static_cast<size_t>(S) * nh * score_stride * sizeof(float);
 }
 
+cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
+                                     const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
+                                     uint16_t *cache, const int64_t *position_dev, int64_t S, int nh, int nkv, int hd,
+                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream) {
+  const int64_t items = S * (nh + nkv);
+  const int prepare_warps = items <= 64 ? 1 : 4; // decode: a CTA per head
+  launch_chained(attn_prepare_kernel, dim3(static_cast<unsigned>((items + prepare_warps - 1) / prepare_warps)),
+                 dim3(32 * prepare_warps), prepare_warps * hd * sizeof(float), stream, qg, k, v, q_norm, k_norm, cos, sin, cache,
+                 position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
                              const uint16_t *q_norm, const uint16_t *k_norm, const float *cos,
                              const float *sin, int rows_from_position, uint16_t *cache,
@@ -1460,33 +1472,26 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   float *scores = reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + qn_bytes);
   const int64_t score_stride = max_position + S;
 
-  const int64_t items = S * (nh + nkv);
-  const int prepare_warps = items <= 64 ? 1 : 4; // decode: a CTA per head
-  launch_chained(attn_prepare_kernel, dim3(static_cast<unsigned>((items + prepare_warps - 1) / prepare_warps)), dim3(32 * prepare_warps), prepare_warps * hd * sizeof(float), stream, 
-      qg, k, v, q_norm, k_norm, cos, sin, cache, position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn);
+  if (cudaError_t e = launch_attention_prepare(qg, k, v, q_norm, k_norm, cos, sin, rows_from_position, cache, position_dev, S,
+                                               nh, nkv, hd, rot, cap, qn, stream);
+      e != cudaSuccess)
+    return e;
 
   const size_t smem = (static_cast<size_t>(kKeyTile) * (hd + 1) + static_cast<size_t>(group) * hd) * sizeof(float);
   const size_t csmem = combine_smem_bytes(score_stride, hd);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  {
+    cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(attn_scores_kernel), 200 * 1024);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      e = opt_in_shared_memory(reinterpret_cast<const void *>(attn_combine_kernel), 200 * 1024);
     if (e != cudaSuccess)
       return e;
-    configured = true;
   }
   if (smem > 200 * 1024 || csmem > 200 * 1024)
     return cudaErrorInvalidValue; // about 50,000 cached positions
   const size_t block_smem = (static_cast<size_t>(kKeyTile) * (hd + 4) + static_cast<size_t>(kScoreTokens) * group * hd) * sizeof(float);
   if (S >= 4 && (hd & 7) == 0 && group * kKeyTile <= 256 && block_smem <= 200 * 1024) {
-    static bool block_configured = false;
-    if (!block_configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_scores_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      if (e != cudaSuccess)
-        return e;
-      block_configured = true;
-    }
+    if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(attn_scores_block_kernel), 200 * 1024); e != cudaSuccess)
+      return e;
     dim3 bgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv,
                static_cast<unsigned>((S + kScoreTokens - 1) / kScoreTokens));
     launch_chained(attn_scores_block_kernel, dim3(bgrid), dim3(group * kKeyTile), block_smem, stream, qn, cache, position_dev, S,
@@ -1508,13 +1513,8 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
                              static_cast<size_t>(kBlockStages) * kValueTile * hd * sizeof(uint16_t) +
                              kBlockStages * sizeof(uint64_t);
   if (S >= 4 && hd == 256 && block_csmem <= 200 * 1024) {
-    static bool block_configured = false;
-    if (!block_configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_combine_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      if (e != cudaSuccess)
-        return e;
-      block_configured = true;
-    }
+    if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(attn_combine_block_kernel), 200 * 1024); e != cudaSuccess)
+      return e;
     dim3 bgrid(nh, static_cast<unsigned>((S + kCombineTokens - 1) / kCombineTokens));
     launch_chained(attn_combine_block_kernel, dim3(bgrid), dim3(hd / 2 + 32), block_csmem, stream, scores, cache, qg, position_dev,
                    S, nh, nkv, hd, cap, score_stride, p_stride, out, q_out, s_out);

@@ -210,14 +210,8 @@ static cudaError_t gemv_launch(const int8_t *aq, const float *as, int K, GemvJob
   }
   const int ctas = (warp + kWarps - 1) / kWarps;
   const size_t smem = gemv_smem_bytes(K, RW, kWarps);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_q8_kernel<RW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         200 * 1024);
-    if (e != cudaSuccess)
-      return e;
-    configured = true;
-  }
+  if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(gemv_q8_kernel<RW>), 200 * 1024); e != cudaSuccess)
+    return e;
   if (smem > 200 * 1024)
     return cudaErrorInvalidValue;
   launch_chained(gemv_q8_kernel<RW>, dim3(ctas), dim3(kWarps * 32), smem, stream, aq, as, K, jobs, dots_out);
@@ -230,8 +224,6 @@ cudaError_t launch_gemv_q8(const int8_t *aq, const float *as, int K, const GemvJ
     return cudaErrorInvalidValue;
   if (!(jobs.flags & kGemvNoCols) && rows_per_warp == 0 && gemv_cols_supported(K, jobs))
     return launch_gemv_q8_cols(aq, as, K, jobs, dots_out, stream);
-  if ((jobs.flags & kGemvRing) && rows_per_warp == 0 && gemv_ring_supported(K, jobs))
-    return launch_gemv_q8_ring(aq, as, K, jobs, dots_out, jobs.error_flag, stream);
   if (gemv_rows_supported(K) && rows_per_warp >= 0)
     return launch_gemv_q8_rows(aq, as, K, jobs, dots_out, stream, rows_per_warp);
   if (rows_per_warp < 0)
@@ -365,23 +357,32 @@ cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K,
 // ---------------------------------------------------------------------------------
 // Embedding gather (LowerToLinalg.cpp:435-531): bf16(float(q) * float(f16 scale)).
 // ---------------------------------------------------------------------------------
-__global__ void embedding_q8_kernel(const int64_t *__restrict__ tokens, int64_t S, int64_t hidden,
+// A token id outside [0, vocab) reads nothing: its row is written as zeros and bit 1 of *status
+// (optional) is raised, which the host turns into an error after the call.
+__global__ void embedding_q8_kernel(const int64_t *__restrict__ tokens, int64_t S, int64_t hidden, int64_t vocab,
                                     const int8_t *__restrict__ wq, const uint16_t *__restrict__ wd,
-                                    uint16_t *__restrict__ out) {
+                                    uint16_t *__restrict__ out, int *__restrict__ status) {
   grid_dependency_sync();
   const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (i >= S * hidden)
     return;
   const int64_t r = i / hidden, c = i % hidden;
   const int64_t token = tokens[r];
+  if (token < 0 || token >= vocab) {
+    out[i] = 0;
+    if (status && c == 0)
+      atomicOr(status, 2);
+    return;
+  }
   const float scale = f16_bits_to_f32(wd[token * (hidden / kBlock) + c / kBlock]);
   out[i] = f32_to_bf16(__fmul_rn(static_cast<float>(wq[token * hidden + c]), scale));
 }
 
-void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, const int8_t *wq,
-                         const uint16_t *wd, uint16_t *out, cudaStream_t stream) {
+void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, int64_t vocab, const int8_t *wq,
+                         const uint16_t *wd, uint16_t *out, int *status, cudaStream_t stream) {
   const int64_t total = S * hidden;
-  launch_chained(embedding_q8_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, tokens, S, hidden, wq, wd, out);
+  launch_chained(embedding_q8_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, tokens, S, hidden,
+                 vocab, wq, wd, out, status);
 }
 
 // ---------------------------------------------------------------------------------

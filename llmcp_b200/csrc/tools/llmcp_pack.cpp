@@ -5,17 +5,24 @@
 //   llmcp-pack --model DIR [--out weights.bin] [--quant none|q8_0] [--dry-run] [--verbose]
 //
 // Both `--name value` and `--name=value` are accepted, with one or two dashes.
+//
+// Additive (not in the reference's tool): `llmcp-pack --synthetic SEED --out weights.bin` writes
+// the q8_0 container of a random-init model with the Qwen3.5-4B text dimensions, the stand-in
+// for the real checkpoint that benchmarks and tests use.  Host code only.
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "../checkpoint.h"
+#include "../format.h"
 
 using namespace llmcp_b200;
 
 int main(int argc, char **argv) {
-  std::string model, out, quant = "none";
+  std::string model, out, quant = "none", synthetic;
   bool dry_run = false, verbose = false;
   for (int i = 1; i < argc; ++i) {
     std::string arg = argv[i];
@@ -46,6 +53,9 @@ int main(int argc, char **argv) {
     } else if (arg == "out") {
       if (!take(&out))
         return 1;
+    } else if (arg == "synthetic") {
+      if (!take(&synthetic))
+        return 1;
     } else if (arg == "quant") {
       if (!take(&quant))
         return 1;
@@ -57,6 +67,29 @@ int main(int argc, char **argv) {
       std::fprintf(stderr, "llmcp-pack: unknown option '%s'\n", argv[i]);
       return 1;
     }
+  }
+  if (!synthetic.empty()) {
+    if (out.empty()) {
+      std::fprintf(stderr, "llmcp-pack: --synthetic needs --out\n");
+      return 1;
+    }
+    const ModelDims dims;
+    const uint64_t bytes = synthetic_container_bytes(dims, nullptr);
+    std::vector<uint8_t> file(bytes);
+    const std::string error = fill_synthetic_container(dims, std::strtoull(synthetic.c_str(), nullptr, 10), file.data(), bytes);
+    if (!error.empty()) {
+      std::fprintf(stderr, "llmcp-pack: %s\n", error.c_str());
+      return 1;
+    }
+    const std::string tmp = out + ".tmp";
+    FILE *f = std::fopen(tmp.c_str(), "wb");
+    if (!f || std::fwrite(file.data(), 1, bytes, f) != bytes || std::fclose(f) != 0 || std::rename(tmp.c_str(), out.c_str()) != 0) {
+      std::fprintf(stderr, "llmcp-pack: cannot write %s\n", out.c_str());
+      return 1;
+    }
+    std::printf("synthetic container, seed %s, %llu bytes -> %s\n", synthetic.c_str(), static_cast<unsigned long long>(bytes),
+                out.c_str());
+    return 0;
   }
   if (model.empty()) {
     std::fprintf(stderr, "llmcp-pack: --model is required\n");

@@ -76,6 +76,14 @@ def num_threads():
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(threads=None):
+    """Use ``threads`` OpenMP threads (default: every core this process may run on) for the calls
+    that follow, overriding an OMP_NUM_THREADS inherited from a launcher.  Returns the count."""
+    if threads is None:
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return int(lib().orc_set_num_threads(int(threads)))
+
+
 def pack_q8_0_p4(w, src_bf16=False):
     """[rows, cols] f32 (or bf16 bits) -> packed q8_0_p4 bytes."""
     w = np.ascontiguousarray(w, dtype=np.uint16 if src_bf16 else np.float32)
@@ -217,6 +225,14 @@ def make_cos_sin(positions, rotary=64, theta=1.0e7):
 def argmax(values):
     values = np.ascontiguousarray(values, dtype=np.float32)
     return int(lib().orc_argmax(_p(values), _i(values.size)))
+
+
+def top2_margin(logits):
+    """Difference between the largest and the second largest logit of a row: a greedy token is
+    only pinned by a comparison whose logit error stays below half of this."""
+    row = np.asarray(logits, dtype=np.float32).ravel()
+    top = np.partition(row, row.size - 2)[-2:]
+    return float(top[1] - top[0])
 
 
 class ModelConfig(C.Structure):

@@ -514,6 +514,21 @@ int orc_num_threads() {
 #endif
 }
 
+// Number of OpenMP threads of the following calls, whatever OMP_NUM_THREADS said when the
+// process started (launchers such as torchrun export OMP_NUM_THREADS=1).  Returns the new count.
+int orc_set_num_threads(int threads) {
+#if defined(_OPENMP)
+  if (threads > 0) {
+    omp_set_dynamic(0);
+    omp_set_num_threads(threads);
+  }
+  return omp_get_max_threads();
+#else
+  (void)threads;
+  return 1;
+#endif
+}
+
 // ---- a1: weight quantisation and packing ----------------------------------
 // lib/Model/Quantization.cpp:92-116.  d: [cols/32] f16 bits, qs: [cols].
 void orc_quantize_row_q8_0(const float *values, int64_t cols, uint16_t *d,

@@ -1,0 +1,201 @@
+"""Fast mode on a B200: the kernels that replace an ordered f32 reduction by a parallel tree,
+checked against the CPU oracle (which keeps the reference's order) with a tolerance.
+
+What must stay exact in fast mode and is checked as such: int8 quantisation given the same
+input, cache and state bytes written by unchanged kernels, the argmax rule.  What may move by
+f32 rounding: rms_norm's rstd, a GEMV row's sum over blocks, the attention softmax sums.  Bars
+(the north-star ones): logits within max_abs 1e-2 of the oracle, greedy tokens identical
+wherever the oracle's top-1/top-2 margin exceeds the observed logit difference.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import llmcp_b200 as L
+import oracle
+
+pytestmark = pytest.mark.gpu
+f = oracle.bf16_to_f32
+
+
+def bf16(a):
+    return oracle.f32_to_bf16(np.asarray(a, dtype=np.float32))
+
+
+@pytest.fixture
+def fast_mode():
+    L.set_mode("fast")
+    yield
+    L.set_mode("exact")
+
+
+def bf16_ulps(got, want):
+    """Distance in bf16 steps between two arrays of bf16 bit patterns (same sign assumed near zero)."""
+    g = got.astype(np.int32)
+    w = want.astype(np.int32)
+    g = np.where(g & 0x8000, 0x8000 - g, g)
+    w = np.where(w & 0x8000, 0x8000 - w, w)
+    return np.abs(g - w)
+
+
+@pytest.mark.parametrize("M,H", [(1, 2560), (3, 2560), (1, 64), (5, 4096), (2, 8192)])
+def test_rms_norm_fast(fast_mode, M, H):
+    rng = np.random.default_rng(H + M)
+    x = bf16(rng.standard_normal((M, H)) * rng.choice([0.01, 1.0, 50.0], size=(M, 1)))
+    w = bf16(rng.standard_normal(H) * 0.1)
+    got = L.ops.rms_norm(x, w)
+    want = oracle.rms_norm(x, w)
+    ulps = bf16_ulps(got, want)
+    # rstd may differ in its last f32 bit, which moves a bf16 rounding only on a near-tie
+    assert ulps.max() <= 1 and (ulps != 0).mean() < 0.01, (ulps.max(), (ulps != 0).mean())
+
+
+@pytest.mark.parametrize("N,K", [(9216, 2560), (2560, 9216), (2560, 4096), (12352 // 16 * 16, 2560), (1024, 2560), (248, 4096)])
+def test_gemv_fast_reduction(N, K):
+    """flags 16: tree-reduced row sums; against the oracle's ascending fma chain."""
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(N + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    packed = oracle.pack_q8_0_p4(w)
+    x = bf16(rng.standard_normal((1, K)))
+    want = oracle.linear_q8(x, packed, N, y_bf16=False)[0]
+    lib = L.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    records = torch.from_numpy(packed).cuda()
+    wq = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    wd = torch.empty((N, K // 32), dtype=torch.float16, device="cuda")
+    assert lib.llmcp_dev_repack_q8(ptr(records), C.c_int64(N), C.c_int64(K), ptr(wq), ptr(wd), stream) == 0
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    aq = torch.empty(K, dtype=torch.int8, device="cuda")
+    scales = torch.empty(K // 32, dtype=torch.float32, device="cuda")
+    assert lib.llmcp_dev_act_quant(ptr(xd), 1, C.c_int64(1), C.c_int64(K), ptr(aq), ptr(scales), stream) == 0
+    bound = 4e-6 * float(np.abs(want).max()) + 1e-7  # a few f32 roundings of the largest term
+    for flags in (16, 17, 19):
+        y = torch.full((N,), float("nan"), dtype=torch.float32, device="cuda")
+        rc = lib.llmcp_dev_gemv_q8(ptr(aq), ptr(scales), C.c_int64(K), ptr(wq), ptr(wd), C.c_int64(N), ptr(y), 0, 0, 0,
+                                   flags, stream)
+        assert rc == 0, L.last_error()
+        torch.cuda.synchronize()
+        got = y.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert np.abs(got - want).max() <= bound, (flags, np.abs(got - want).max(), bound)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,position", [(16, 4, 256, 0), (16, 4, 256, 31), (16, 4, 256, 32), (16, 4, 256, 1030),
+                                               (4, 2, 256, 77), (8, 4, 128, 200), (4, 4, 128, 65)])
+def test_attention_decode_fast(fast_mode, nh, nkv, hd, position):
+    rng = np.random.default_rng(position + nh)
+    rot, cap = 64, position + 9
+    qg = bf16(rng.standard_normal((1, nh * 2 * hd)))
+    k = bf16(rng.standard_normal((1, nkv * hd)))
+    v = bf16(rng.standard_normal((1, nkv * hd)))
+    qn = bf16(rng.standard_normal(hd) * 0.1)
+    kn = bf16(rng.standard_normal(hd) * 0.1)
+    cos, sin = L.make_cos_sin(position, rot, 1e7)
+    cache = bf16(rng.standard_normal((2, nkv, cap, hd)))
+    got, got_cache = L.ops.attention(qg, k, v, qn, kn, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
+    want, want_cache = oracle.attention(qg, k, v, qn, kn, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
+    assert np.array_equal(got_cache, want_cache)  # the prepare kernel is the exact one
+    ulps = bf16_ulps(got, want)
+    assert np.isfinite(f(got)).all()
+    assert ulps.max() <= 2 and (ulps != 0).mean() < 0.05, (ulps.max(), (ulps != 0).mean())
+
+
+def test_attention_decode_fast_long_context(fast_mode):
+    """8192 cached keys (BASELINE config 4): several 32-key tiles per split."""
+    rng = np.random.default_rng(8192)
+    nh, nkv, hd, rot, position = 16, 4, 256, 64, 8192
+    cap = position + 1
+    qg = bf16(rng.standard_normal((1, nh * 2 * hd)))
+    k = bf16(rng.standard_normal((1, nkv * hd)))
+    v = bf16(rng.standard_normal((1, nkv * hd)))
+    norm = np.zeros(hd, np.uint16)
+    cos, sin = L.make_cos_sin(position, rot, 1e7)
+    cache = bf16(rng.standard_normal((2, nkv, cap, hd)))
+    got, _ = L.ops.attention(qg, k, v, norm, norm, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
+    want, _ = oracle.attention(qg, k, v, norm, norm, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
+    ulps = bf16_ulps(got, want)
+    assert ulps.max() <= 2 and (ulps != 0).mean() < 0.05, (ulps.max(), (ulps != 0).mean())
+
+
+SMALL = dict(hidden=256, intermediate=512, vocab=2048, layers=8, full_interval=4, heads=4, kv_heads=2,
+             head_dim=256, rotary=64, lin_k_heads=2, lin_v_heads=8, lin_k_dim=128, lin_v_dim=128, conv_kernel=4)
+
+
+def oracle_dims(d):
+    return dict(full_interval=d.full_interval, heads=d.heads, kv_heads=d.kv_heads, head_dim=d.head_dim,
+                rotary=d.rotary, lin_k_heads=d.lin_k_heads, lin_v_heads=d.lin_v_heads, lin_k_dim=d.lin_k_dim,
+                lin_v_dim=d.lin_v_dim, conv_kernel=d.conv_kernel)
+
+
+def compare_fast_with_oracle(dims, seed, prompt, steps, capacity):
+    """Teacher-forced comparison: both sides are fed the oracle's greedy tokens, so one flipped
+    token does not derail the rest; returns (max |dlogit|, min margin, tokens that differed)."""
+    data = L.synthetic_container(dims, seed)
+    arena = L.Arena().from_buffer(data)
+    model = oracle.Model(data, arena.manifest, oracle_dims(dims))
+    state = model.new_state(capacity)
+    engine = L.Engine(data, dims, capacity=capacity, mode="fast")
+    exact = L.Engine(data, dims, capacity=capacity, mode="exact")
+    tokens, pos = list(prompt), 0
+    worst, margins, flips = 0.0, [], []
+    for step in range(steps + 1):
+        got, got_token = engine.forward(tokens, pos)
+        ref, ref_token = exact.forward(tokens, pos)
+        want = model.forward(state, tokens, pos)
+        assert np.array_equal(ref.view(np.uint32), want.view(np.uint32)), "exact mode must still match bit for bit"
+        assert np.isfinite(got).all()
+        diff = float(np.abs(got - want).max())
+        worst = max(worst, diff)
+        margin = oracle.top2_margin(want)
+        margins.append(margin)
+        want_token = oracle.argmax(want)
+        if got_token != want_token:
+            flips.append((step, margin, diff))
+            assert margin <= 2 * diff, f"token differs at step {step} although margin {margin} > 2 x {diff}"
+        pos += len(tokens)
+        tokens = [want_token]
+    engine.close()
+    exact.close()
+    model.close()
+    return worst, min(margins), flips
+
+
+def test_fast_model_matches_oracle_within_tolerance():
+    d = L.default_dims().copy(**SMALL)
+    worst, margin, flips = compare_fast_with_oracle(d, 20261125, [17, 5, 900, 2047, 0, 33, 33, 1200], steps=24, capacity=40)
+    print(f"fast vs oracle: max |dlogit| {worst:.3e}, min top-2 margin {margin:.3e}, flips {flips}")
+    assert worst <= 1e-2
+
+
+def test_fast_generate_is_deterministic_and_matches_forward():
+    """The device-resident loop (CUDA graph) and the call-by-call path of a fast engine agree bit
+    for bit with each other: the mode changes the order of additions, not their determinism."""
+    d = L.default_dims().copy(**SMALL)
+    data = L.synthetic_container(d, 3)
+    a = L.Engine(data, d, capacity=40, mode="fast")
+    b = L.Engine(data, d, capacity=40, mode="fast")
+    prompt = [1, 2, 3, 4, 5]
+    _, first = a.forward(prompt, 0)
+    _, first_b = b.forward(prompt, 0)
+    assert first == first_b
+    generated, _ = a.generate(first, len(prompt), 12)
+    tokens, pos, token = [], len(prompt), first
+    for _ in range(12):
+        _, token = b.forward([token], pos)
+        tokens.append(token)
+        pos += 1
+    assert generated.tolist() == tokens
+    a.close()
+    b.close()
+
+
+@pytest.mark.slow
+def test_fast_full_size_model():
+    """Qwen3.5-4B dimensions: 24-token prefill and 6 teacher-forced steps in fast mode."""
+    d = L.default_dims()
+    worst, margin, flips = compare_fast_with_oracle(d, 20261125, [9419] * 24, steps=6, capacity=40)
+    print(f"full size, fast vs oracle: max |dlogit| {worst:.3e}, min top-2 margin {margin:.3e}, flips {flips}")
+    assert worst <= 1e-2

@@ -147,3 +147,88 @@ def test_full_size_model_short_run():
     d = L.default_dims()
     prompt = [9419] * 16
     run_both(d, 20261125, prompt, steps=4, capacity=32)
+
+
+def test_bad_token_ids_are_refused_before_any_launch():
+    """A token id outside [0, vocab) (a -1 pad, an id of another vocabulary) is an error, not an
+    out-of-bounds read of the embedding table: nothing is copied or launched."""
+    d = L.default_dims().copy(**TINY)
+    data = L.synthetic_container(d, 1)
+    engine = L.Engine(data, d, capacity=8)
+    for bad in ([-1], [3, d.vocab], [2 ** 40]):
+        before = L.launch_count()
+        with pytest.raises(L.LlmcpError, match="outside the vocabulary"):
+            engine.forward(bad, 0)
+        with pytest.raises(L.LlmcpError, match="outside the vocabulary"):
+            engine.forward_all(bad, 0)
+        assert L.launch_count() == before
+    with pytest.raises(L.LlmcpError, match="outside the vocabulary"):
+        engine.generate(-5, 0, 2)
+    logits, token = engine.forward([1, 2, 3], 0)  # the engine is still usable
+    assert np.isfinite(logits).all() and 0 <= token < d.vocab
+    engine.close()
+    # the AOT entry reports through NaN logits and the error message (the ABI returns void)
+    runtime = L.AotRuntime(d)
+    assert runtime.init(max_sequence=8)
+    L.lib().llmcp_b200_clear_error()
+    row = runtime.forward(L.Arena().from_buffer(data), [d.vocab + 7], 0, 1)
+    assert np.isnan(row).all() and "outside the vocabulary" in L.last_error()
+    L.lib().llmcp_b200_clear_error()
+    L.lib().llmcp_b200_release_all()
+
+
+def test_engines_on_two_devices_in_one_process():
+    """Kernel attributes (the dynamic shared-memory opt-in) are per device: a second engine on
+    another GPU of the same process must run its prefill (tensor-core GEMM, attention) too."""
+    if L.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    d = L.default_dims().copy(**SMALL)
+    data = L.synthetic_container(d, 9)
+    prompt = [5, 6, 7, 8, 9, 10, 11, 12]
+    results = []
+    for device in (0, 1):
+        engine = L.Engine(data, d, capacity=16, device=device)
+        logits, token = engine.forward(prompt, 0)
+        generated, _ = engine.generate(token, len(prompt), 3)
+        results.append((logits, token, generated.tolist()))
+        engine.close()
+    L.set_device(0)
+    assert np.array_equal(results[0][0].view(np.uint32), results[1][0].view(np.uint32))
+    assert results[0][1:] == results[1][1:]
+
+
+@pytest.mark.slow
+def test_llmcp_benchmark_binary_against_oracle(tmp_path):
+    """The C++ driver (same options and output lines as the reference's llmcp-benchmark) on the
+    full-size synthetic container through libllmcp_b200.so: seven `key: value` lines, and with
+    --verbose the generated ids, which must be the oracle's greedy tokens."""
+    import pathlib
+    import subprocess
+    tool = L._PACKAGE / "bin" / "llmcp-benchmark"
+    assert tool.exists(), "run python -m llmcp_b200.build"
+    weights = pathlib.Path("/dev/shm") / "llmcp_b200_synth_20261125.bin"
+    run = subprocess.run([str(tool), "--weights", str(weights), "--aot", str(L.LIBRARY_PATH), "--prefill-tokens", "32",
+                          "--decode-tokens", "6", "--token", "9419", "--verbose", "--synthetic", "20261125"],
+                         capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stderr
+    lines = dict(line.split(": ", 1) if ": " in line else (line.split(":")[0], line.split(":", 1)[1])
+                 for line in run.stdout.strip().splitlines())
+    for key in ("prefill_tokens", "decode_tokens", "prefill_seconds", "decode_seconds", "total_seconds",
+                "prefill_tokens_per_second", "decode_tokens_per_second"):
+        assert key in lines, run.stdout
+    assert int(lines["prefill_tokens"]) == 32 and int(lines["decode_tokens"]) == 6
+    assert float(lines["decode_tokens_per_second"]) > 0
+    generated = [int(v) for v in lines["generated_tokens"].split()]
+    d = L.default_dims()
+    data = np.fromfile(weights, dtype=np.uint8)
+    arena = L.Arena().from_buffer(data)
+    model = oracle.Model(data, arena.manifest, oracle_dims(d))
+    state = model.new_state(48)
+    logits = model.forward(state, [9419] * 32, 0)
+    want, pos = [], 32
+    for _ in range(len(generated)):
+        want.append(oracle.argmax(logits))
+        logits = model.forward(state, [want[-1]], pos)
+        pos += 1
+    assert generated == want
+    model.close()
