@@ -217,11 +217,11 @@ ORACLE_DIMS = dict(full_interval=4, heads=16, kv_heads=4, head_dim=256, rotary=6
 class OracleRun:
     """The CPU oracle on the benchmark's context: 1024 x token 9419, then greedy steps."""
 
-    def __init__(self, data, manifest, steps):
+    def __init__(self, data, manifest, steps, mode="fma"):
         import oracle
         self.oracle = oracle
         self.threads = oracle.set_num_threads()  # every host core, whatever OMP_NUM_THREADS was inherited
-        self.model = oracle.Model(data, manifest, ORACLE_DIMS)
+        self.model = oracle.Model(data, manifest, ORACLE_DIMS, mode=mode)
         self.state = self.model.new_state(PREFILL + steps + 2)
         begin = time.perf_counter()
         self.logits = [self.model.forward(self.state, [TOKEN] * PREFILL, 0)]
@@ -241,12 +241,21 @@ class OracleRun:
                 self.logits.append(logits)
         return steps / (time.perf_counter() - begin)
 
+    def forced(self, tokens):
+        """Logits of every position when fed `tokens` (another run's greedy chain) after the prompt."""
+        rows = [self.logits[0]]
+        for token in tokens:
+            rows.append(self.model.forward(self.state, [token], self.position))
+            self.position += 1
+        return rows
+
     def close(self):
         self.model.close()
 
 
-def gemv_roofline(L, torch, device, ring=GEMV_RING, sweeps=20):
-    """Decode GEMV alone: CUDA events on the launching stream over a ring of weight copies."""
+def gemv_roofline(L, torch, device, ring=GEMV_RING, sweeps=20, flags=3):
+    """Decode GEMV alone: CUDA events on the launching stream over a ring of weight copies.
+    flags: 1 dependent launch, 2 L2 prefetch of later sets, 16 tree-reduced row sums (fast mode)."""
     lib = L.lib()
     stream = torch.cuda.current_stream().cuda_stream
     gen = torch.Generator(device="cuda").manual_seed(SEED)
@@ -263,7 +272,7 @@ def gemv_roofline(L, torch, device, ring=GEMV_RING, sweeps=20):
         for _ in range(times):
             for r in range(ring):
                 rc = lib.llmcp_dev_gemv_q8(ptr(aq), ptr(scales), C.c_int64(GEMV_K), ptr(wq[r]), ptr(wd[r]),
-                                           C.c_int64(GEMV_N), ptr(y), 0, 0, 0, 1, C.c_void_p(stream))
+                                           C.c_int64(GEMV_N), ptr(y), 0, 0, 0, flags, C.c_void_p(stream))
                 assert rc == 0, L.last_error()
 
     sweep(3, stream)
@@ -488,6 +497,13 @@ def main():
                  "exact_mode_tokens_match_oracle": exact_tokens[:n] == run.tokens[:n],
                  "how": "engine fed the oracle's greedy tokens (1024-token prompt + cpu-steps positions); logits compared "
                         "position by position; exact mode: its own greedy chain against the oracle's"}
+        # The same positions through the reference's other accumulate variant (multiply-then-add,
+        # Q8Scalar.cpp:192-199): how far two orders of f32 rounding that the reference itself
+        # ships move the logits of this random-init model.
+        alt = OracleRun(arena.data, arena.manifest, args.cpu_steps, mode="muladd")
+        alt_rows = alt.forced(run.tokens[:args.cpu_steps])
+        check["reference_fma_vs_muladd_max_abs"] = float(max(np.abs(a - b).max() for a, b in zip(alt_rows, run.logits)))
+        alt.close()
         cpu_baseline = {"value": tok_s, "unit": "tokens/s", "cores": run.threads, "kind": "port",
                         "sample": f"{args.cpu_steps} greedy decode steps after the same 1024-token prefill, CPU oracle "
                                   "(OpenMP, all host threads)",
