@@ -316,7 +316,7 @@ cudaError_t launch_attention_decode_fast(const uint16_t *qg, const uint16_t *k, 
   float *part_acc = reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + qn_bytes);
   float *part_ml = part_acc + static_cast<size_t>(nh) * splits * hd;
   if (cudaError_t e = launch_attention_prepare(qg, k, v, q_norm, k_norm, cos, sin, rows_from_position, cache, position_dev, 1,
-                                               nh, nkv, hd, rot, cap, qn, stream);
+                                               nh, nkv, hd, rot, cap, qn, stream, 1);
       e != cudaSuccess)
     return e;
   const int group = nh / nkv;

@@ -115,11 +115,12 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
                              float *s_out, cudaStream_t stream);
 
 // The first of the three attention launches alone: q/k RMSNorm, partial RoPE, q -> qn scratch
-// (bf16 [S, nh, hd]), k and v -> cache rows position .. position + S - 1.
+// (bf16 [S, nh, hd]), k and v -> cache rows position .. position + S - 1.  tree_sum (fast mode):
+// the sums of squares of the two norms are shuffle trees instead of the reference's serial sums.
 cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
                                      const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
                                      uint16_t *cache, const int64_t *position_dev, int64_t S, int nh, int nkv, int hd,
-                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream);
+                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream, int tree_sum = 0);
 // Fast mode of the one-token attention: after the same prepare kernel, the key range is split
 // over CTAs (each keeps a running maximum, denominator and weighted value sum for the query
 // heads of one KV head) and a second kernel merges the splits, applies the sigmoid gate and

@@ -613,7 +613,7 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
                                     const uint16_t *__restrict__ k_norm, const float *__restrict__ cos,
                                     const float *__restrict__ sin, uint16_t *__restrict__ cache,
                                     const int64_t *__restrict__ position_ptr, int rows_from_position, int64_t S,
-                                    int nh, int nkv, int hd, int rot, int64_t cap, uint16_t *__restrict__ qn) {
+                                    int nh, int nkv, int hd, int rot, int64_t cap, uint16_t *__restrict__ qn, int tree_sum) {
   extern __shared__ float prep_sm[]; // per warp: hd values
   grid_dependency_sync();
   const int64_t position = *position_ptr;
@@ -665,7 +665,15 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
   }
   __syncwarp();
   float inv = 0.0f;
-  if (lane == 0) {
+  if (tree_sum) { // fast mode: lane partial sums, then a shuffle tree (another order than the reference's)
+    float sum = 0.0f;
+    for (int d = lane; d < hd; d += 32)
+      sum = __fadd_rn(sum, tmp[d]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+    inv = d_rsqrt(__fadd_rn(__fmul_rn(sum, __fdiv_rn(1.0f, static_cast<float>(hd))), 1.0e-6f));
+  } else if (lane == 0) {
     float sum = 0.0f;
     int d = 0;
     for (; d + 16 <= hd; d += 16) { // sixteen squares are fetched, then added in order
@@ -681,7 +689,8 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
       sum = __fadd_rn(sum, tmp[d]);
     inv = d_rsqrt(__fadd_rn(__fmul_rn(sum, __fdiv_rn(1.0f, static_cast<float>(hd))), 1.0e-6f));
   }
-  inv = __shfl_sync(0xffffffffu, inv, 0);
+  if (!tree_sum)
+    inv = __shfl_sync(0xffffffffu, inv, 0);
   __syncwarp();
   if (prefetched) {
 #pragma unroll
@@ -1443,12 +1452,12 @@ size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t max_position) {
 cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
                                      const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
                                      uint16_t *cache, const int64_t *position_dev, int64_t S, int nh, int nkv, int hd,
-                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream) {
+                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream, int tree_sum) {
   const int64_t items = S * (nh + nkv);
   const int prepare_warps = items <= 64 ? 1 : 4; // decode: a CTA per head
   launch_chained(attn_prepare_kernel, dim3(static_cast<unsigned>((items + prepare_warps - 1) / prepare_warps)),
                  dim3(32 * prepare_warps), prepare_warps * hd * sizeof(float), stream, qg, k, v, q_norm, k_norm, cos, sin, cache,
-                 position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn);
+                 position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn, tree_sum);
   return cudaGetLastError();
 }
 

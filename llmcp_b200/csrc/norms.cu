@@ -246,74 +246,93 @@ cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int
   return cudaGetLastError();
 }
 
-// Fast mode.  The same operator with eight consecutive elements per thread (16-byte loads) and
-// the sum of squares reduced by warp shuffles and one shared-memory table, i.e. in another order
-// than the reference's serial sum: rstd can differ in its last bit, every other step is unchanged.
-// H % 8 == 0, at most 1024 threads (H <= 8192); four neighbouring lanes hold a quantisation block.
+// Fast mode.  The same operator with EPT (4 or 8) consecutive elements per thread and the sum of
+// squares reduced by warp shuffles and one shared-memory table, i.e. in another order than the
+// reference's serial sum: rstd can differ in its last bit, every other step is unchanged.
+// Four elements per thread for rows up to 4096 (more warps, shorter dependent chains: the kernel
+// is a chain of latencies, not of throughput), eight beyond; 32 / EPT neighbouring lanes hold a
+// quantisation block.  bf16 roundings use the conversion instruction.
+template <int EPT>
 __global__ void __launch_bounds__(1024)
 rms_norm_fast_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, int H,
                      const void *__restrict__ w, int w_dtype, float eps, int zero_centered,
                      uint16_t *__restrict__ sum_out, uint16_t *__restrict__ y, int8_t *__restrict__ q,
                      float *__restrict__ s) {
+  constexpr int W = EPT / 2; // 32-bit words of bf16 pairs per thread
   __shared__ float warp_sums[32];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * H;
   const int i = threadIdx.x;
-  const bool live = i < (H >> 3);
+  const bool live = i < H / EPT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  auto load_words = [&](const uint16_t *p, uint32_t *dst) {
+    if (EPT == 8) {
+      const uint4 r = reinterpret_cast<const uint4 *>(p)[i];
+      dst[0] = r.x, dst[1] = r.y, dst[W - 2] = r.z, dst[W - 1] = r.w;
+    } else {
+      const uint2 r = reinterpret_cast<const uint2 *>(p)[i];
+      dst[0] = r.x, dst[1] = r.y;
+    }
+  };
+  auto store_words = [&](uint16_t *p, const uint32_t *src) {
+    if (EPT == 8)
+      reinterpret_cast<uint4 *>(p)[i] = make_uint4(src[0], src[1], src[W - 2], src[W - 1]);
+    else
+      reinterpret_cast<uint2 *>(p)[i] = make_uint2(src[0], src[1]);
+  };
   // The norm weights do not depend on the kernel in front: they are fetched before waiting for it.
-  float wt[8];
+  float wt[EPT];
 #pragma unroll
-  for (int u = 0; u < 8; ++u)
+  for (int u = 0; u < EPT; ++u)
     wt[u] = 0.0f;
   if (live) {
     if (w_dtype == kBF16) {
-      const uint4 rw = reinterpret_cast<const uint4 *>(w)[i];
-      const uint32_t ww[4] = {rw.x, rw.y, rw.z, rw.w};
+      uint32_t ww[W];
+      load_words(static_cast<const uint16_t *>(w), ww);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < W; ++u) {
         wt[2 * u] = __uint_as_float(ww[u] << 16);
         wt[2 * u + 1] = __uint_as_float(ww[u] & 0xffff0000u);
       }
     } else {
-      const float4 w0 = reinterpret_cast<const float4 *>(w)[2 * i], w1 = reinterpret_cast<const float4 *>(w)[2 * i + 1];
-      wt[0] = w0.x, wt[1] = w0.y, wt[2] = w0.z, wt[3] = w0.w;
-      wt[4] = w1.x, wt[5] = w1.y, wt[6] = w1.z, wt[7] = w1.w;
+#pragma unroll
+      for (int v = 0; v < EPT / 4; ++v) {
+        const float4 w4 = reinterpret_cast<const float4 *>(w)[(EPT / 4) * i + v];
+        wt[4 * v] = w4.x, wt[4 * v + 1] = w4.y, wt[4 * v + 2] = w4.z, wt[4 * v + 3] = w4.w;
+      }
     }
     if (zero_centered) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
+      for (int u = 0; u < EPT; ++u)
         wt[u] = __fadd_rn(wt[u], 1.0f);
     }
   }
   grid_dependency_sync(true);
-  float x[8];
+  float x[EPT];
 #pragma unroll
-  for (int u = 0; u < 8; ++u)
+  for (int u = 0; u < EPT; ++u)
     x[u] = 0.0f;
   if (live) {
-    const uint4 ra = reinterpret_cast<const uint4 *>(a + base)[i];
-    uint32_t words[4] = {ra.x, ra.y, ra.z, ra.w};
+    uint32_t words[W];
+    load_words(a + base, words);
     if (b) {
-      const uint4 rb = reinterpret_cast<const uint4 *>(b + base)[i];
-      const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
+      uint32_t wb[W];
+      load_words(b + base, wb);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const uint16_t lo = f32_to_bf16(__fadd_rn(__uint_as_float(words[u] << 16), __uint_as_float(wb[u] << 16)));
-        const uint16_t hi = f32_to_bf16(__fadd_rn(__uint_as_float(words[u] & 0xffff0000u), __uint_as_float(wb[u] & 0xffff0000u)));
-        words[u] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-      }
+      for (int u = 0; u < W; ++u)
+        words[u] = f32x2_to_bf16x2_hw(__fadd_rn(__uint_as_float(words[u] << 16), __uint_as_float(wb[u] << 16)),
+                                      __fadd_rn(__uint_as_float(words[u] & 0xffff0000u), __uint_as_float(wb[u] & 0xffff0000u)));
       if (sum_out)
-        reinterpret_cast<uint4 *>(sum_out + base)[i] = make_uint4(words[0], words[1], words[2], words[3]);
+        store_words(sum_out + base, words);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < W; ++u) {
       x[2 * u] = __uint_as_float(words[u] << 16);
       x[2 * u + 1] = __uint_as_float(words[u] & 0xffff0000u);
     }
   }
   float part = 0.0f;
 #pragma unroll
-  for (int u = 0; u < 8; ++u)
+  for (int u = 0; u < EPT; ++u)
     part = __fmaf_rn(x[u], x[u], part);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1)
@@ -321,38 +340,48 @@ rms_norm_fast_kernel(const uint16_t *__restrict__ a, const uint16_t *__restrict_
   if (lane == 0)
     warp_sums[warp] = part;
   __syncthreads();
-  float sum = 0.0f;
-  for (int k = 0; k < warps; ++k) // every thread adds the table in the same order
-    sum = __fadd_rn(sum, warp_sums[k]);
+  // Every thread adds the table in the same order: lane k takes entry k, then one shuffle tree.
+  float sum = lane < warps ? warp_sums[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
   const float rstd = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(H)), eps));
-  float o[8];
+  uint32_t wo[W];
+  float o[EPT];
 #pragma unroll
-  for (int u = 0; u < 8; ++u)
-    o[u] = bf16_to_f32(f32_to_bf16(__fmul_rn(__fmul_rn(x[u], rstd), wt[u])));
-  if (live && y) {
-    uint32_t words[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      words[u] = static_cast<uint32_t>(f32_to_bf16(o[2 * u])) | (static_cast<uint32_t>(f32_to_bf16(o[2 * u + 1])) << 16);
-    reinterpret_cast<uint4 *>(y + base)[i] = make_uint4(words[0], words[1], words[2], words[3]);
+  for (int u = 0; u < W; ++u) {
+    wo[u] = f32x2_to_bf16x2_hw(__fmul_rn(__fmul_rn(x[2 * u], rstd), wt[2 * u]), __fmul_rn(__fmul_rn(x[2 * u + 1], rstd), wt[2 * u + 1]));
+    o[2 * u] = __uint_as_float(wo[u] << 16);
+    o[2 * u + 1] = __uint_as_float(wo[u] & 0xffff0000u);
   }
-  if (q) { // H % 32 == 0: whole groups of four lanes are live or not
+  if (live && y)
+    store_words(y + base, wo);
+  if (q) { // H % 32 == 0: whole groups of 32 / EPT lanes are live or not
     float amax = 0.0f;
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
+    for (int u = 0; u < EPT; ++u)
       amax = fmaxf(amax, fabsf(o[u]));
+    if (EPT == 4)
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     if (live) {
       const float scale = __fdiv_rn(amax, 127.0f);
       const float inv = amax == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
-      uint32_t packed[2] = {0u, 0u};
+      uint32_t packed[EPT / 4];
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        packed[u >> 2] |= (static_cast<uint32_t>(__float2int_rn(__fmul_rn(o[u], inv))) & 0xffu) << (8 * (u & 3));
-      reinterpret_cast<uint2 *>(q + base)[i] = make_uint2(packed[0], packed[1]);
-      if ((i & 3) == 0)
-        s[(base >> 5) + (i >> 2)] = scale;
+      for (int v = 0; v < EPT / 4; ++v) {
+        packed[v] = 0u;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          packed[v] |= (static_cast<uint32_t>(__float2int_rn(__fmul_rn(o[4 * v + u], inv))) & 0xffu) << (8 * u);
+      }
+      if (EPT == 8)
+        reinterpret_cast<uint2 *>(q + base)[i] = make_uint2(packed[0], packed[EPT / 4 - 1]);
+      else
+        reinterpret_cast<uint32_t *>(q + base)[i] = packed[0];
+      if ((i & (32 / EPT - 1)) == 0)
+        s[(base >> 5) + i / (32 / EPT)] = scale;
     }
   }
 }
@@ -364,9 +393,15 @@ cudaError_t launch_rms_norm_fast(const uint16_t *a, const uint16_t *b, int64_t M
     return cudaSuccess;
   if (H % 8 != 0 || H > 8192 || (q && H % kBlock != 0))
     return cudaErrorNotSupported;
-  const int threads = ((H >> 3) + 31) / 32 * 32;
-  launch_chained(rms_norm_fast_kernel, dim3(static_cast<unsigned>(M)), dim3(threads), 0, stream, a, b, H, w, w_dtype, eps,
-                 zero_centered, sum_out, y, q, s);
+  if (H <= 4096) {
+    const int threads = (H / 4 + 31) / 32 * 32;
+    launch_chained(rms_norm_fast_kernel<4>, dim3(static_cast<unsigned>(M)), dim3(threads), 0, stream, a, b, H, w, w_dtype, eps,
+                   zero_centered, sum_out, y, q, s);
+  } else {
+    const int threads = (H / 8 + 31) / 32 * 32;
+    launch_chained(rms_norm_fast_kernel<8>, dim3(static_cast<unsigned>(M)), dim3(threads), 0, stream, a, b, H, w, w_dtype, eps,
+                   zero_centered, sum_out, y, q, s);
+  }
   return cudaGetLastError();
 }
 

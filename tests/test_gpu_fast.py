@@ -106,7 +106,12 @@ def test_attention_decode_fast(fast_mode, nh, nkv, hd, position):
     cache = bf16(rng.standard_normal((2, nkv, cap, hd)))
     got, got_cache = L.ops.attention(qg, k, v, qn, kn, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
     want, want_cache = oracle.attention(qg, k, v, qn, kn, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
-    assert np.array_equal(got_cache, want_cache)  # the prepare kernel is the exact one
+    # cached rows other than the new one are untouched; the new key row may move by a bf16 step on
+    # a near-tie (tree-summed norm), the new value row is a copy
+    cache_ulps = bf16_ulps(got_cache, want_cache)
+    assert cache_ulps.max() <= 1 and np.count_nonzero(cache_ulps) <= nkv * hd // 20
+    assert np.array_equal(got_cache[1], want_cache[1])
+    assert np.array_equal(np.delete(got_cache[0], position, axis=1), np.delete(want_cache[0], position, axis=1))
     ulps = bf16_ulps(got, want)
     assert np.isfinite(f(got)).all()
     assert ulps.max() <= 2 and (ulps != 0).mean() < 0.05, (ulps.max(), (ulps != 0).mean())
