@@ -55,6 +55,7 @@ GEMV_BYTES = GEMV_N * (GEMV_K // 32) * 34 + GEMV_K * 4 + GEMV_N * 4  # weights +
 # capture of `bench.py --only gemv` (not measured in this run; the 36,864-byte result stays in L2).
 GEMV_DRAM_TRAFFIC = 25_097_216
 GEMM_M, GEMM_N, GEMM_K = 1024, 9216, 2560  # the gate_proj/up_proj prefill GEMM
+GEMM_FORM = 1  # the engine's default form of the TMA-fed tensor-core GEMM (int8 planes, packed f32x2 arithmetic)
 
 
 def measured_peaks():
@@ -294,8 +295,10 @@ def gemv_roofline(L, torch, device, ring=GEMV_RING, sweeps=20, flags=3):
     return GEMV_BYTES / us / 1e3, us, sweeps * ring  # GB/s, us per launch, launches
 
 
-def gemm_alone(L, torch, repeats=5):
-    """Prefill GEMM alone (tcgen05 kernel) on device buffers: returns (us per launch, int8 TOP/s)."""
+def gemm_alone(L, torch, repeats=5, form=GEMM_FORM):
+    """Prefill GEMM alone (tcgen05 kernel, f16-valued operand planes) on device buffers: returns
+    (us per launch, int8 TOP/s).  The planes are made once, as the engine makes the weight planes
+    at load; the timed launches are the GEMM only."""
     lib = L.lib()
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     gen = torch.Generator(device="cuda").manual_seed(SEED)
@@ -305,15 +308,23 @@ def gemm_alone(L, torch, repeats=5):
     x = torch.randn((GEMM_M, GEMM_K), device="cuda", generator=gen)
     aq = torch.empty((GEMM_M, GEMM_K), dtype=torch.int8, device="cuda")
     scales = torch.empty((GEMM_M, nb), dtype=torch.float32, device="cuda")
-    wd32 = wd.float().contiguous()
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     y = torch.empty((GEMM_M, GEMM_N), dtype=torch.float32, device="cuda")
     ptr = lambda t: C.c_void_p(t.data_ptr())
     assert lib.llmcp_dev_act_quant(ptr(x), 0, C.c_int64(GEMM_M), C.c_int64(GEMM_K), ptr(aq), ptr(scales), stream) == 0
+    lib.llmcp_dev_gemm_q8_tma_scale_pitch.restype = C.c_int64
+    pitch = int(lib.llmcp_dev_gemm_q8_tma_scale_pitch(C.c_int64(GEMM_M)))
+    ah = torch.empty((GEMM_M, GEMM_K), dtype=torch.float16, device="cuda")
+    ast = torch.zeros((nb, pitch), dtype=torch.float32, device="cuda")
+    wh = torch.empty((GEMM_N, GEMM_K), dtype=torch.float16, device="cuda")
+    wst = torch.empty((nb, GEMM_N), dtype=torch.float32, device="cuda")
+    assert lib.llmcp_dev_q8_gemm_planes(ptr(aq), ptr(scales), 0, C.c_int64(GEMM_M), C.c_int64(GEMM_K), ptr(ah), ptr(ast), stream) == 0
+    assert lib.llmcp_dev_q8_gemm_planes(ptr(wq), ptr(wd), 1, C.c_int64(GEMM_N), C.c_int64(GEMM_K), ptr(wh), ptr(wst), stream) == 0
 
     def launch():
-        rc = lib.llmcp_dev_gemm_q8_tc(ptr(aq), ptr(scales), C.c_int64(GEMM_M), C.c_int64(GEMM_K), ptr(wq), ptr(wd32),
-                                      C.c_int64(GEMM_N), ptr(y), 0, 0, ptr(status), stream)
+        a, w = (ah, wh) if form >= 2 else (aq, wq)
+        rc = lib.llmcp_dev_gemm_q8_tma(form, ptr(a), ptr(ast), C.c_int64(GEMM_M), C.c_int64(GEMM_K), ptr(w), ptr(wst),
+                                       C.c_int64(GEMM_N), ptr(y), 0, 0, ptr(status), C.c_uint32(0), 0, stream)
         assert rc == 0, L.last_error()
 
     for _ in range(3):
@@ -588,7 +599,7 @@ def main():
         # 3 operations per (row, column, block) on 148 SMs x 128 lanes at the sampled SM clock.
         sm_mhz = clocks.get("sm_mhz") or clocks.get("sm_max_mhz") or 1965.0
         epilogue_us = GEMM_M * GEMM_N * (GEMM_K // 32) * 3 / (148 * 128 * sm_mhz)
-        result["roofline_gemm"] = {"bound": "tensor", "kernel": "gemm_q8_tc_kernel", "shape": [GEMM_M, GEMM_N, GEMM_K],
+        result["roofline_gemm"] = {"bound": "tensor", "kernel": "gemm_q8_tma_kernel", "shape": [GEMM_M, GEMM_N, GEMM_K],
                                    "us_per_launch": gemm_us, "achieved": tops, "unit": "int8 TOP/s", "peak": int8_peak,
                                    "peak_kind": f"2 x bf16 burst, of {peak_kind}", "frac": tops / int8_peak,
                                    "epilogue_bound_us": epilogue_us,

@@ -146,6 +146,22 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
  *                         weight scales widened to f32, [N][K/32].  status (device int, may be
  *                         null) is set to 1 if a bounded wait inside the kernel ran out; the
  *                         caller reads it after synchronising.
+ *   llmcp_dev_gemm_q8_tma: the M > 1 linear on the tensor cores with operands fetched by TMA
+ *                         (cp.async.bulk.tensor, no multicast).  form: 0 int8 operand planes,
+ *                         tcgen05 kind::i8, int32 dots converted in the epilogue; 2 the same integers
+ *                         held as f16 values, kind::f16 (an f16 x f16 block dot of int8-valued operands
+ *                         is an exact integer in f32, so the result is the same bit for bit and the
+ *                         conversion disappears); 1 and 3: the same with two-lane f32x2 multiplies and
+ *                         fmas.  a / w: [rows][K] int8 (forms 0, 1) or f16 (2, 3); a_scales / w_scales:
+ *                         block-major f32 [K/32][pitch], pitch = llmcp_dev_gemm_q8_tma_scale_pitch(M)
+ *                         (M rounded up to 4) for activations and N for weights.  status as above.
+ *                         spin_limit: polls before a wait inside the kernel gives up (0 = default,
+ *                         about a second).  fault: 0; 1 is a test hook that withholds the first
+ *                         stage's copies so that the bounded waits run out (status becomes 1, y is
+ *                         left unwritten, tensor memory is released).
+ *   llmcp_dev_q8_gemm_planes: those planes from int8 values [rows][K] and their scales
+ *                         [rows][K/32] (f32 for activations, f16 bits for weights when
+ *                         scales_are_f16): scales_block_major always, values_f16 if not null.
  *   llmcp_dev_argmax    : first maximum of n f32 values; scratch: 512 floats + 512 int64. */
 int llmcp_dev_repack_q8(const uint8_t *records, int64_t N, int64_t K, int8_t *q, uint16_t *d, void *stream);
 int llmcp_dev_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales, void *stream);
@@ -155,6 +171,12 @@ int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, c
                       int64_t N, void *y, int y_dtype, int activation, void *stream);
 int llmcp_dev_gemm_q8_tc(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const float *wd32,
                          int64_t N, void *y, int y_dtype, int activation, int *status, void *stream);
+int llmcp_dev_q8_gemm_planes(const int8_t *q, const void *scales, int scales_are_f16, int64_t rows, int64_t K, void *values_f16,
+                             float *scales_block_major, void *stream);
+int64_t llmcp_dev_gemm_q8_tma_scale_pitch(int64_t M);
+int llmcp_dev_gemm_q8_tma(int form, const void *a, const float *a_scales, int64_t M, int64_t K, const void *w,
+                          const float *w_scales, int64_t N, void *y, int y_dtype, int activation, int *status,
+                          uint32_t spin_limit, int fault, void *stream);
 int llmcp_dev_argmax(const float *x, int64_t n, float *scratch_values, int64_t *scratch_indices, int64_t *out_index,
                      void *stream);
 

@@ -107,29 +107,69 @@ void check_q8_shape(int64_t N, int64_t K) {
 }
 
 // Uploads packed records and re-lays them out: returns q and d planes.
+int gemm_kind() {
+  const char *flag = std::getenv("LLMCP_B200_GEMM");
+  return flag ? gemm_kind_from_name(flag) : kDefaultGemmKind;
+}
+
+bool tensor_core_gemm_enabled() { return gemm_kind() != 0; }
+
 struct DeviceQ8 {
   Buf q, d, d32;
+  std::unique_ptr<Buf> h, d32t; // planes of the f16-form GEMM, made on demand
+  int64_t N, K;
   DeviceQ8(const uint8_t *records, int64_t N, int64_t K)
-      : q(static_cast<size_t>(N) * K), d(static_cast<size_t>(N) * (K / 32) * 2), d32(static_cast<size_t>(N) * (K / 32) * 4) {
+      : q(static_cast<size_t>(N) * K), d(static_cast<size_t>(N) * (K / 32) * 2), d32(static_cast<size_t>(N) * (K / 32) * 4), N(N),
+        K(K) {
     Buf staging(static_cast<size_t>(N) * (K / 32) * 34, records);
     launch_repack_p4(staging.as<uint8_t>(), N, K, q.as<int8_t>(), d.as<uint16_t>(), d32.as<float>(), nullptr);
     cuda_check(cudaDeviceSynchronize(), "repack");
     g_launches += 1;
   }
+  // Planes of the TMA-fed GEMM forms: block-major f32 scales, and for the f16 forms the f16-valued integers.
+  void make_tma_planes(bool f16) {
+    if (!d32t) {
+      d32t = std::make_unique<Buf>(static_cast<size_t>(N) * (K / 32) * 4);
+      launch_scales_block_major(d.as<uint16_t>(), 1, N, static_cast<int>(K), N, d32t->as<float>(), nullptr);
+      g_launches += 1;
+    }
+    if (f16 && !h) {
+      h = std::make_unique<Buf>(static_cast<size_t>(N) * K * 2);
+      launch_weights_to_f16(q.as<int8_t>(), d.as<uint16_t>(), N, static_cast<int>(K), h->p, d32t->as<float>(), nullptr);
+      g_launches += 1;
+    }
+    cuda_check(cudaDeviceSynchronize(), "GEMM planes");
+  }
 };
 
-bool tensor_core_gemm_enabled() {
-  const char *flag = std::getenv("LLMCP_B200_GEMM");
-  return !(flag && std::string(flag) == "dp4a");
-}
-
 // Tensor-core GEMM with its status word checked after completion (synchronises).
-void run_gemm_tc(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const float *wd32, int64_t N,
-                 void *y, int y_dtype, int activation, int32_t *dots) {
+void run_gemm_tc(const int8_t *aq, const float *as, int64_t M, int64_t K, DeviceQ8 &w, int64_t N, void *y, int y_dtype,
+                 int activation, int32_t *dots) {
   int zero = 0;
   Buf status(4, &zero);
-  cuda_check(launch_gemm_q8_tc(aq, as, static_cast<int>(M), static_cast<int>(K), wq, wd32, static_cast<int>(N), y, y_dtype,
-                               activation, dots, status.as<int>(), nullptr), "gemm");
+  if (gemm_kind() >= 2) {
+    const int form = gemm_kind() - 2;
+    const bool f16 = form >= kGemmF16;
+    w.make_tma_planes(f16);
+    Buf ah(f16 ? static_cast<size_t>(M) * K * 2 : 0), ast(static_cast<size_t>(gemm_tc16_scale_pitch(M)) * (K / 32) * 4);
+    if (f16)
+      launch_act_to_f16(aq, as, M, static_cast<int>(K), ah.p, ast.as<float>(), nullptr);
+    else
+      launch_scales_block_major(as, 0, M, static_cast<int>(K), gemm_tc16_scale_pitch(M), ast.as<float>(), nullptr);
+    g_launches += 1;
+    cuda_check(launch_gemm_q8_tma(form, f16 ? ah.p : static_cast<const void *>(aq), ast.as<float>(), static_cast<int>(M),
+                                  static_cast<int>(K), f16 ? w.h->p : w.q.p, w.d32t->as<float>(), static_cast<int>(N), y, y_dtype,
+                                  activation, dots, status.as<int>(), nullptr), "gemm");
+    g_launches += 1;
+    cuda_check(cudaDeviceSynchronize(), "gemm");
+    int raised = 0;
+    status.to_host(&raised, 4);
+    if (raised)
+      throw std::runtime_error("tensor-core GEMM: a bounded wait ran out (pipeline protocol error)");
+    return;
+  }
+  cuda_check(launch_gemm_q8_tc(aq, as, static_cast<int>(M), static_cast<int>(K), w.q.as<int8_t>(), w.d32.as<float>(),
+                               static_cast<int>(N), y, y_dtype, activation, dots, status.as<int>(), nullptr), "gemm");
   g_launches += 1;
   cuda_check(cudaDeviceSynchronize(), "gemm");
   int raised = 0;
@@ -425,7 +465,7 @@ int llmcp_op_linear_q8(const void *x, int x_dtype, int64_t M, int64_t K, const u
     launch_act_quant(dx.p, x_dtype, M, K, dq.as<int8_t>(), ds.as<float>(), nullptr);
     g_launches += 1;
     if (M > 1 && tensor_core_gemm_enabled())
-      run_gemm_tc(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d32.as<float>(), N, dy.p, y_dtype, activation,
+      run_gemm_tc(dq.as<int8_t>(), ds.as<float>(), M, K, w, N, dy.p, y_dtype, activation,
                   block_dots ? dots.as<int32_t>() : nullptr);
     else
       run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), N, dy.p, y_dtype, activation,
@@ -451,7 +491,7 @@ int llmcp_op_lm_head_q8(const uint16_t *hidden, int64_t M, int64_t K, const uint
     launch_act_quant(dx.p, kBF16, M, K, dq.as<int8_t>(), ds.as<float>(), nullptr);
     g_launches += 1;
     if (M > 1 && tensor_core_gemm_enabled())
-      run_gemm_tc(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d32.as<float>(), vocab, dy.p, kF32, kNone, nullptr);
+      run_gemm_tc(dq.as<int8_t>(), ds.as<float>(), M, K, w, vocab, dy.p, kF32, kNone, nullptr);
     else
       run_linear(dq.as<int8_t>(), ds.as<float>(), M, K, w.q.as<int8_t>(), w.d.as<uint16_t>(), vocab, dy.p, kF32, kNone,
                  nullptr, 0, nullptr);
@@ -671,6 +711,42 @@ int llmcp_dev_gemm_q8_tc(const int8_t *aq, const float *as, int64_t M, int64_t K
       throw std::runtime_error("llmcp_dev_gemm_q8_tc needs M >= 1");
     cuda_check(launch_gemm_q8_tc(aq, as, static_cast<int>(M), static_cast<int>(K), wq, wd32, static_cast<int>(N), y, y_dtype,
                                  activation, nullptr, status, static_cast<cudaStream_t>(stream)), "gemm");
+    g_launches += 1;
+  });
+}
+
+int llmcp_dev_q8_gemm_planes(const int8_t *q, const void *scales, int scales_are_f16, int64_t rows, int64_t K, void *values_f16,
+                             float *scales_block_major, void *stream) {
+  return guarded_async([&] {
+    if (rows <= 0 || K <= 0 || K % 32 != 0 || !scales_block_major)
+      throw std::runtime_error("rows > 0, K % 32 == 0 and a scale plane are required");
+    const int64_t pitch = scales_are_f16 ? rows : gemm_tc16_scale_pitch(rows);
+    if (!values_f16)
+      launch_scales_block_major(scales, scales_are_f16, rows, static_cast<int>(K), pitch, scales_block_major,
+                                static_cast<cudaStream_t>(stream));
+    else if (scales_are_f16)
+      launch_weights_to_f16(q, static_cast<const uint16_t *>(scales), rows, static_cast<int>(K), values_f16, scales_block_major,
+                            static_cast<cudaStream_t>(stream));
+    else
+      launch_act_to_f16(q, static_cast<const float *>(scales), rows, static_cast<int>(K), values_f16, scales_block_major,
+                        static_cast<cudaStream_t>(stream));
+    g_launches += 1;
+    cuda_check(cudaGetLastError(), "GEMM planes");
+  });
+}
+
+int64_t llmcp_dev_gemm_q8_tma_scale_pitch(int64_t M) { return gemm_tc16_scale_pitch(M); }
+
+int llmcp_dev_gemm_q8_tma(int form, const void *a, const float *a_scales, int64_t M, int64_t K, const void *w,
+                          const float *w_scales, int64_t N, void *y, int y_dtype, int activation, int *status,
+                          uint32_t spin_limit, int fault, void *stream) {
+  return guarded_async([&] {
+    check_q8_shape(N, K);
+    if (M < 1)
+      throw std::runtime_error("llmcp_dev_gemm_q8_tma needs M >= 1");
+    cuda_check(launch_gemm_q8_tma(form, a, a_scales, static_cast<int>(M), static_cast<int>(K), w, w_scales, static_cast<int>(N), y,
+                                  y_dtype, activation, nullptr, status, static_cast<cudaStream_t>(stream), spin_limit, fault),
+               "gemm");
     g_launches += 1;
   });
 }

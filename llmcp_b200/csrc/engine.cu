@@ -49,6 +49,25 @@ std::atomic<int> g_default_mode{-1};
 
 } // namespace
 
+// Names of the prefill GEMM forms (LLMCP_B200_GEMM): the value is 0 for the CUDA-core kernel, 1 for
+// the cp.async-fed tcgen05 kernel, 2 + GemmForm for the TMA-fed ones.
+int gemm_kind_from_name(const char *name) {
+  const std::string kind = name ? name : "";
+  if (kind == "dp4a")
+    return 0;
+  if (kind == "i8-cpasync")
+    return 1;
+  if (kind == "i8")
+    return 2 + kGemmI8;
+  if (kind == "i8x2")
+    return 2 + kGemmI8Packed;
+  if (kind == "f16")
+    return 2 + kGemmF16;
+  if (kind == "f16x2")
+    return 2 + kGemmF16Packed;
+  return kDefaultGemmKind;
+}
+
 int default_mode() {
   const int stored = g_default_mode.load();
   if (stored >= 0)
@@ -78,6 +97,11 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   try {
   check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
 
+  // Prefill GEMM form: decides which weight planes load_weights() builds.
+  if (const char *flag = std::getenv("LLMCP_B200_GEMM")) {
+    gemm_kind_ = gemm_kind_from_name(flag);
+    use_tensor_cores_ = gemm_kind_ != 0;
+  }
   Manifest manifest;
   const std::string error = parse_container(base, file_bytes, &manifest);
   if (!error.empty())
@@ -132,8 +156,6 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     gemv_flags_ = std::atoi(flag);
   if (const char *flag = std::getenv("LLMCP_B200_FUSE_MIXER"))
     fuse_decode_mixer_ = std::atoi(flag) != 0;
-  if (const char *flag = std::getenv("LLMCP_B200_GEMM"))
-    use_tensor_cores_ = std::string(flag) != "dp4a";
   check(cudaMemsetAsync(gemm_error_, 0, 4, stream_), "memset");
   generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
   check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
@@ -222,7 +244,11 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   for (const TensorEntry &t : manifest.tensors) {
     if (t.dtype == "Q8_0") {
       const size_t n = static_cast<size_t>(t.shape[0]), k = static_cast<size_t>(t.shape[1]);
-      pool_bytes += round_up(n * k, 256) + round_up(n * (k / 32) * 2, 256) + round_up(n * (k / 32) * 4, 256);
+      pool_bytes += round_up(n * k, 256) + round_up(n * (k / 32) * 2, 256);
+      if (gemm_kind_ >= 1)
+        pool_bytes += round_up(n * (k / 32) * 4, 256); // f32 scales, row-major or block-major
+      if (gemm_kind_ >= 2 + kGemmF16)
+        pool_bytes += round_up(n * k * 2, 256);
       staging_bytes = std::max<size_t>(staging_bytes, t.size);
     } else {
       pool_bytes += round_up(t.size, 256);
@@ -252,10 +278,21 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
     w.K = static_cast<int>(cols);
     w.q = reinterpret_cast<int8_t *>(take(static_cast<size_t>(rows) * cols));
     w.d = reinterpret_cast<uint16_t *>(take(static_cast<size_t>(rows) * (cols / 32) * 2));
-    w.d32 = reinterpret_cast<float *>(take(static_cast<size_t>(rows) * (cols / 32) * 4));
+    if (gemm_kind_ == 1)
+      w.d32 = reinterpret_cast<float *>(take(static_cast<size_t>(rows) * (cols / 32) * 4));
     check(cudaMemcpyAsync(staging, base + t->offset, t->size, cudaMemcpyHostToDevice, stream_), "upload weights");
     launch_repack_p4(staging, rows, cols, w.q, w.d, w.d32, stream_);
     check(cudaGetLastError(), "repack");
+    if (gemm_kind_ >= 2) { // TMA-fed forms: block-major scales, and for the f16 forms the f16-valued plane
+      w.d32t = reinterpret_cast<float *>(take(static_cast<size_t>(rows) * (cols / 32) * 4));
+      if (gemm_kind_ >= 2 + kGemmF16) {
+        w.h = take(static_cast<size_t>(rows) * cols * 2);
+        launch_weights_to_f16(w.q, w.d, rows, static_cast<int>(cols), w.h, w.d32t, stream_);
+      } else {
+        launch_scales_block_major(w.d, 1, rows, static_cast<int>(cols), rows, w.d32t, stream_);
+      }
+      check(cudaGetLastError(), "GEMM planes");
+    }
     return w;
   };
   auto small = [&](const std::string &name, int64_t elements) {
@@ -374,6 +411,13 @@ void Engine::ensure_workspace(int64_t S, int64_t position) {
   mlp_out_ = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
   aq_ = static_cast<int8_t *>(alloc(r * max_k));
   as_ = static_cast<float *>(alloc(r * (max_k / 32) * 4));
+  ah_ = nullptr;
+  ast_ = nullptr;
+  if (gemm_kind_ >= 2 && rows > 1) {
+    if (gemm_kind_ >= 2 + kGemmF16)
+      ah_ = alloc(r * max_k * 2);
+    ast_ = static_cast<float *>(alloc(static_cast<size_t>(gemm_tc16_scale_pitch(rows)) * (max_k / 32) * 4));
+  }
   qkv_ = static_cast<uint16_t *>(alloc(r * c.qkv_dim() * 2));
   z_ = static_cast<uint16_t *>(alloc(r * c.value_dim() * 2));
   a_ = static_cast<uint16_t *>(alloc(r * c.lin_v_heads * 2));
@@ -400,7 +444,14 @@ struct LinearJob {
   int activation;
 };
 
-static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
+// Buffers of the f16-form GEMM input (null: not in use).
+struct F16Planes {
+  void *ah;
+  float *ast;
+  int form; // GemmForm, or -1: not a TMA-fed form
+};
+
+static void run_linears(const F16Planes &planes, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
                         cudaStream_t stream, uint64_t *launches, int flags, int *gemm_error = nullptr) {
   if (S == 1) {
     GemvJobs g{};
@@ -421,13 +472,25 @@ static void run_linears(Engine *, const int8_t *aq, const float *as, int64_t S, 
     *launches += 1;
     return;
   }
+  const bool tma = gemm_error && planes.form >= 0 && planes.ast && jobs[0].w->d32t;
+  const bool f16 = tma && planes.form >= kGemmF16;
+  if (tma) { // the shared input once: scales block-major, and for the f16 forms the int8 values as f16
+    if (f16)
+      launch_act_to_f16(aq, as, S, jobs[0].w->K, planes.ah, planes.ast, stream);
+    else
+      launch_scales_block_major(as, 0, S, jobs[0].w->K, gemm_tc16_scale_pitch(S), planes.ast, stream);
+    *launches += 1;
+  }
   for (int i = 0; i < count; ++i) {
     cudaError_t e =
-        gemm_error ? launch_gemm_q8_tc(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d32,
-                                       jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, gemm_error,
-                                       stream)
-                   : launch_gemm_q8_dp4a(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d,
-                                         jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, stream);
+        tma ? launch_gemm_q8_tma(planes.form, f16 ? planes.ah : static_cast<const void *>(aq), planes.ast, static_cast<int>(S),
+                                 jobs[i].w->K, f16 ? jobs[i].w->h : static_cast<const void *>(jobs[i].w->q), jobs[i].w->d32t,
+                                 jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, gemm_error, stream)
+        : gemm_error ? launch_gemm_q8_tc(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d32,
+                                         jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, gemm_error,
+                                         stream)
+                     : launch_gemm_q8_dp4a(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d,
+                                           jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, stream);
     if (e != cudaSuccess)
       throw std::runtime_error(std::string("gemm: ") + cudaGetErrorString(e));
     *launches += 1;
@@ -479,6 +542,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
   launch_embedding_q8(tokens_dev, S, H, c.vocab, embed_.q, embed_.d, hidden_[0], gemm_error_, stream_);
   launches_ += 1;
   const int gemv_flags = gemv_flags_ | (mode_ == kModeFast ? kGemvFast : 0);
+  const F16Planes planes = {ah_, ast_, gemm_kind_ >= 2 ? gemm_kind_ - 2 : -1};
   int cur = 0;
   bool pending = false;
   int64_t lin_index = 0, full_index = 0;
@@ -496,7 +560,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(this, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
       const int C = static_cast<int>(c.qkv_dim());
       uint16_t *conv_state = conv_ + lin_index * (c.conv_kernel - 1) * C;
       float *delta_state = delta_ + lin_index * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
@@ -518,11 +582,11 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
         launches_ += 5;
       }
       const LinearJob out = {&L.out_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+      run_linears(planes, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(this, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
       uint16_t *cache = kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim;
       if (mode_ == kModeFast && S == 1 &&
           attention_decode_fast_supported(static_cast<int>(c.heads), static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim))) {
@@ -541,17 +605,17 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       }
       launches_ += 3;
       const LinearJob out = {&L.o_proj, branch_, kBF16, kNone};
-      run_linears(this, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+      run_linears(planes, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
       ++full_index;
     }
     rms_norm(hidden_[cur], branch_, S, L.post_norm, hidden_[cur ^ 1], nullptr);
     cur ^= 1;
     const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-    run_linears(this, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+    run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
     check(launch_pointwise(gate_, up_, S * c.intermediate, 1, nullptr, aq_, as_, stream_), "mul");
     launches_ += 2;
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
-    run_linears(this, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+    run_linears(planes, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
     pending = true;
   }
   if (all_logits_) {
@@ -559,7 +623,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     // (ModelBuilder.cpp:406-438): final norm over all rows, then one S x vocab x hidden contraction.
     rms_norm(hidden_[cur], pending ? mlp_out_ : nullptr, S, final_norm_, nullptr, branch_);
     const LinearJob all = {&embed_, all_logits_, kF32, kNone};
-    run_linears(this, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags & kGemvOverlapPrevious,
+    run_linears(planes, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags & kGemvOverlapPrevious,
                 S > 1 && use_tensor_cores_ ? gemm_error_ : nullptr);
     launches_ += 1;
   }
@@ -568,7 +632,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
   rms_norm(last, pending ? mlp_out_ + (S - 1) * H : nullptr, 1, final_norm_, nullptr, final_hidden_);
   const Q8Weight &table = embed_;
   const LinearJob head = {&table, logits_, kF32, kNone};
-  run_linears(this, aq_, as_, 1, &head, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious);
+  run_linears(planes, aq_, as_, 1, &head, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious);
   launch_argmax(logits_, c.vocab, argmax_v_, argmax_i_, 0, next_token_, nullptr, stream_);
   launches_ += 3;
   check(cudaGetLastError(), "forward");

@@ -17,7 +17,9 @@ namespace llmcp_b200 {
 struct Q8Weight {
   int8_t *q = nullptr;   // [N][K]
   uint16_t *d = nullptr; // [N][K/32] f16 bits
-  float *d32 = nullptr;  // [N][K/32] the same scales as f32 (tensor-core GEMM)
+  float *d32 = nullptr;  // [N][K/32] the same scales as f32 (tensor-core GEMM, int8 form)
+  void *h = nullptr;     // [N][K] the integers as f16 values (tensor-core GEMM, f16 form)
+  float *d32t = nullptr; // [K/32][N] the scales as f32, block-major (tensor-core GEMM, f16 form)
   int N = 0, K = 0;
 };
 
@@ -35,6 +37,10 @@ struct LayerWeights {
   SmallTensor q_norm, k_norm;
   Q8Weight gate, up, down;
 };
+
+// Prefill GEMM forms by name ("dp4a", "i8-cpasync", "i8", "i8x2", "f16", "f16x2"; see kernels.h GemmForm).
+constexpr int kDefaultGemmKind = 2 + 1; // TMA-fed int8 planes (nothing beside the GEMV's planes), packed arithmetic
+int gemm_kind_from_name(const char *name);
 
 // Arithmetic mode of an engine.
 //   kModeExact: every f32 result is bit-identical to the reference's order of operations.
@@ -167,6 +173,9 @@ private:
   uint64_t decode_graph_launches_ = 0;
   bool use_graph_ = true;
   bool use_tensor_cores_ = true;
+  int gemm_kind_ = kDefaultGemmKind; // prefill GEMM form, see gemm_kind_from_name()
+  void *ah_ = nullptr;    // [rows][max K] activations as f16 values (GEMM kind 2)
+  float *ast_ = nullptr;  // [max K / 32][pitch] their scales, block-major
   int *gemm_error_ = nullptr; // device flag raised by a timed-out wait in the GEMM
   int gemv_flags_ = 3; // kGemvOverlapPrevious | kGemvPrefetchL2
   bool fuse_decode_mixer_ = true; // one-token gated-delta-net layers in two launches instead of five

@@ -66,6 +66,35 @@ cudaError_t launch_gemm_q8_tc(const int8_t *aq, const float *as, int M, int K, c
                               cudaStream_t stream);
 // status (device int, optional): bit 1 is raised when a token id lies outside [0, vocab); such a
 // row is written as zeros and the table is not read.
+// Tensor-core GEMM with TMA-fed operands (gemm_tma.cu).  Operand planes are [rows][K] and scale
+// planes block-major f32, [K/32][pitch] (pitch = gemm_tc16_scale_pitch(M) for activations, N for
+// weights); `form` says what the operand planes hold and how the epilogue multiplies:
+//   kGemmI8  / kGemmI8Packed : int8 values, tcgen05 kind::i8, int32 dots converted in the epilogue;
+//   kGemmF16 / kGemmF16Packed: the same integers as f16 values, kind::f16, exact f32 dots;
+//   *Packed: two-lane f32x2 multiplies and fmas.
+// spin_limit 0 = default (about a second); fault: test hook, see the kernel.
+enum GemmForm : int { kGemmI8 = 0, kGemmI8Packed = 1, kGemmF16 = 2, kGemmF16Packed = 3 };
+int64_t gemm_tc16_scale_pitch(int64_t M);
+void launch_act_to_f16(const int8_t *aq, const float *as, int64_t M, int K, void *ah, float *ast, cudaStream_t stream);
+void launch_weights_to_f16(const int8_t *wq, const uint16_t *wd, int64_t N, int K, void *wh, float *wst, cudaStream_t stream);
+void launch_scales_block_major(const void *scales, int scales_are_f16, int64_t rows, int K, int64_t ld, float *out,
+                               cudaStream_t stream);
+cudaError_t launch_gemm_q8_tma(int form, const void *a, const float *ast, int M, int K, const void *w, const float *wst, int N,
+                               void *y, int y_dtype, int activation, int32_t *dots_out, int *error_flag, cudaStream_t stream,
+                               uint32_t spin_limit = 0, int fault = 0);
+// status (device int, optional): bit 1 is raised when a token id lies outside [0, vocab); such a
+// row is written as zeros and the table is not read.
+// Second form of the tensor-core GEMM (gemm_tma.cu): the int8 operands held as f16 values and the
+// scales as block-major f32 planes, tcgen05 kind::f16 with exact f32 block dots, TMA loads.
+//   ah  [M][K] f16, ast [K/32][pitch] f32 with pitch = gemm_tc16_scale_pitch(M)  (launch_act_to_f16)
+//   wh  [N][K] f16, wst [K/32][N] f32                                          (launch_weights_to_f16)
+// spin_limit 0 = default (about a second); fault: test hook, see the kernel.
+int64_t gemm_tc16_scale_pitch(int64_t M);
+void launch_act_to_f16(const int8_t *aq, const float *as, int64_t M, int K, void *ah, float *ast, cudaStream_t stream);
+void launch_weights_to_f16(const int8_t *wq, const uint16_t *wd, int64_t N, int K, void *wh, float *wst, cudaStream_t stream);
+cudaError_t launch_gemm_q8_tc16(const void *ah, const float *ast, int M, int K, const void *wh, const float *wst, int N, void *y,
+                                int y_dtype, int activation, int32_t *dots_out, int *error_flag, cudaStream_t stream,
+                                uint32_t spin_limit = 0, int fault = 0);
 void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, int64_t vocab, const int8_t *wq,
                          const uint16_t *wd, uint16_t *out, int *status, cudaStream_t stream);
 // scratch_v / scratch_i: kArgmaxParts entries each.

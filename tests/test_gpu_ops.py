@@ -333,3 +333,102 @@ def test_gemv_kernel_variants(N, K):
         torch.cuda.synchronize()
         got = y.cpu().numpy()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"flags {flags}"
+
+
+def _tma_gemm_setup(torch, M, N, K, seed):
+    """Operand and scale planes of the TMA-fed tensor-core GEMM on the device, and the oracle's result."""
+    import ctypes as C
+    rng = np.random.default_rng(seed)
+    packed = oracle.pack_q8_0_p4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    x = rand_bf16(rng, M, K)
+    want = oracle.linear_q8(x, packed, N, y_bf16=False)
+    lib = L.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    records = torch.from_numpy(packed).cuda()
+    wq = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    wd = torch.empty((N, K // 32), dtype=torch.float16, device="cuda")
+    assert lib.llmcp_dev_repack_q8(ptr(records), C.c_int64(N), C.c_int64(K), ptr(wq), ptr(wd), stream) == 0
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    aq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+    scales = torch.empty((M, K // 32), dtype=torch.float32, device="cuda")
+    assert lib.llmcp_dev_act_quant(ptr(xd), 1, C.c_int64(M), C.c_int64(K), ptr(aq), ptr(scales), stream) == 0
+    lib.llmcp_dev_gemm_q8_tma_scale_pitch.restype = C.c_int64
+    pitch = int(lib.llmcp_dev_gemm_q8_tma_scale_pitch(C.c_int64(M)))
+    ah = torch.empty((M, K), dtype=torch.float16, device="cuda")
+    ast = torch.zeros((K // 32, pitch), dtype=torch.float32, device="cuda")
+    wh = torch.empty((N, K), dtype=torch.float16, device="cuda")
+    wst = torch.empty((K // 32, N), dtype=torch.float32, device="cuda")
+    assert lib.llmcp_dev_q8_gemm_planes(ptr(aq), ptr(scales), 0, C.c_int64(M), C.c_int64(K), ptr(ah), ptr(ast), stream) == 0
+    assert lib.llmcp_dev_q8_gemm_planes(ptr(wq), ptr(wd), 1, C.c_int64(N), C.c_int64(K), ptr(wh), ptr(wst), stream) == 0
+    torch.cuda.synchronize()
+    # the planes hold the same integers and the same scale values
+    assert torch.equal(ah.to(torch.int8), aq) and torch.equal(wh.to(torch.int8), wq)
+    assert torch.equal(ast[:, :M].t().contiguous(), scales) and torch.equal(wst.t().contiguous(), wd.float())
+    # the scale planes alone (the int8 forms need nothing else)
+    ast2, wst2 = torch.zeros_like(ast), torch.zeros_like(wst)
+    assert lib.llmcp_dev_q8_gemm_planes(None, ptr(scales), 0, C.c_int64(M), C.c_int64(K), None, ptr(ast2), stream) == 0
+    assert lib.llmcp_dev_q8_gemm_planes(None, ptr(wd), 1, C.c_int64(N), C.c_int64(K), None, ptr(wst2), stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(ast2, ast) and torch.equal(wst2, wst)
+    return lib, stream, ptr, {"aq": aq, "wq": wq, "ah": ah, "wh": wh, "ast": ast, "wst": wst}, want
+
+
+def _tma_gemm(lib, stream, ptr, planes, form, M, N, K, y, status, spin_limit=0, fault=0):
+    import ctypes as C
+    a, w = (planes["ah"], planes["wh"]) if form >= 2 else (planes["aq"], planes["wq"])
+    rc = lib.llmcp_dev_gemm_q8_tma(form, ptr(a), ptr(planes["ast"]), C.c_int64(M), C.c_int64(K), ptr(w), ptr(planes["wst"]),
+                                   C.c_int64(N), ptr(y), 0, 0, ptr(status), C.c_uint32(spin_limit), fault, stream)
+    assert rc == 0, L.last_error()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 2560), (300, 136, 288), (2, 8, 32), (1024, 1024, 4096)])
+def test_gemm_tma_device_entry(M, N, K):
+    """llmcp_dev_gemm_q8_tma on device planes, all four forms: bit-identical to the oracle."""
+    torch = pytest.importorskip("torch")
+    lib, stream, ptr, planes, want = _tma_gemm_setup(torch, M, N, K, M + N + K)
+    for form in range(4):
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        _tma_gemm(lib, stream, ptr, planes, form, M, N, K, y, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32)), form
+
+
+@pytest.mark.parametrize("form", [1, 3])
+def test_gemm_tma_bounded_wait_runs_out_and_recovers(form):
+    """The test hook withholds the first stage's copies: every wait behind it must give up after its
+    bounded number of polls, the kernel must report through the status word, write nothing, free
+    its tensor memory and leave the context usable: the next launch is correct."""
+    torch = pytest.importorskip("torch")
+    M, N, K = 256, 384, 2560
+    lib, stream, ptr, planes, want = _tma_gemm_setup(torch, M, N, K, 99)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = torch.full((M, N), 7.0, dtype=torch.float32, device="cuda")
+    _tma_gemm(lib, stream, ptr, planes, form, M, N, K, y, status, spin_limit=1 << 12, fault=1)
+    torch.cuda.synchronize()  # returns: nothing hangs
+    assert int(status.item()) == 1
+    assert bool((y == 7.0).all()), "a tile that gave up writes no output"
+    status.zero_()
+    for _ in range(3):  # tensor memory was released: full-occupancy launches still fit
+        _tma_gemm(lib, stream, ptr, planes, form, M, N, K, y, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_linear_q8_every_gemm_form(monkeypatch):
+    """Every prefill GEMM form stays selectable and exact, int32 block dots included."""
+    rng = np.random.default_rng(21)
+    M, N, K = 130, 264, 2560
+    packed = oracle.pack_q8_0_p4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    x = rand_bf16(rng, M, K)
+    want = oracle.linear_q8(x, packed, N, y_bf16=False)
+    q, _ = oracle.act_quant(x)
+    want_dots = oracle.block_dots(q, packed, N)
+    for form in ("i8-cpasync", "dp4a", "i8", "i8x2", "f16", "f16x2"):
+        monkeypatch.setenv("LLMCP_B200_GEMM", form)
+        y, dots = L.ops.linear_q8(x, packed, N, y_bf16=False, want_dots=True)
+        assert np.array_equal(y.view(np.uint32), want.view(np.uint32)), form
+        assert np.array_equal(dots, want_dots), form
