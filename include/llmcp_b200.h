@@ -249,6 +249,37 @@ void *llmcp_b200_engine_create(const uint8_t *file, uint64_t file_bytes, const l
 /* The same with an explicit arithmetic mode (see llmcp_b200_set_mode). */
 void *llmcp_b200_engine_create_mode(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims,
                                     int64_t capacity, int device, int mode);
+/* Tensor parallelism over the GPUs of one node (no counterpart in the reference, which is one
+ * process on one device; what is split are the output rows of the linears that
+ * lib/Model/ModelBuilder.cpp:218-319 builds, on the 8-row boundaries of
+ * include/llmcp/Support/Q8PackedLayout.h:38-42).  One process per GPU.  Every linear is split by
+ * output rows only, so each output element is computed by one rank with the unsplit arithmetic and
+ * the results equal the single-GPU engine's bit for bit; recurrent and attention heads and their
+ * state are split by head; the vocabulary projection by rows, with a (maximum, index) exchange
+ * that keeps the first-maximum rule.  The exchange is this library's own kernel: every rank stores
+ * its piece into buffers of its peers that are mapped through CUDA IPC and waits, bounded, for
+ * their flags (no NCCL, no host round trip; part of the captured decode step).
+ *   llmcp_b200_tp_slot_bytes : bytes per exchange slot for calls of up to max_tokens tokens.
+ *   llmcp_b200_tp_create     : allocates this rank's exchange buffer on `device`; handle_out
+ *                              receives 64 bytes to hand to the other ranks (any channel).
+ *   llmcp_b200_tp_attach     : maps the peers' buffers; handles = size x 64 bytes in rank order.
+ *   llmcp_b200_tp_all_gather : the exchange alone: this rank's [rows][row_bytes] piece -> slot
+ *                              `slot` (0..2) of every rank, rows of size x row_bytes bytes; copied to
+ *                              dst if not null.  Consecutive calls must name different slots.
+ *                              status (device int, may be null): bit 2 is raised if a peer's flag did
+ *                              not arrive within the wait limit.
+ *   llmcp_b200_engine_create_tp: an engine that holds rank's share; every rank must then make the
+ *                              same forward / generate calls.  llmcp_b200_engine_read_state returns
+ *                              this rank's heads (llmcp_b200_engine_local_dims tells which). */
+uint64_t llmcp_b200_tp_slot_bytes(const llmcp_b200_dims *dims, int64_t max_tokens);
+void *llmcp_b200_tp_create(int rank, int size, uint64_t slot_bytes, int device, uint8_t *handle_out);
+int llmcp_b200_tp_attach(void *tp, const uint8_t *handles);
+void llmcp_b200_tp_destroy(void *tp);
+int llmcp_b200_tp_all_gather(void *tp, const void *src, uint64_t row_bytes, uint64_t rows, int slot, void *dst, int *status,
+                             void *stream);
+void *llmcp_b200_engine_create_tp(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims, int64_t capacity,
+                                  int device, int mode, void *tp, int64_t max_tokens);
+int llmcp_b200_engine_local_dims(void *engine, llmcp_b200_dims *dims, int64_t *kv_head0);
 void llmcp_b200_engine_destroy(void *engine);
 int llmcp_b200_engine_reset(void *engine);
 /* One forward over host tokens (the work of lib/Runtime/AotRuntime.cpp:68-120): logits

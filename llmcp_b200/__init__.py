@@ -71,6 +71,9 @@ def lib():
         handle.llmcp_b200_read_safetensors.restype = C.c_uint64
         handle.llmcp_b200_engine_create.restype = C.c_void_p
         handle.llmcp_b200_engine_create_mode.restype = C.c_void_p
+        handle.llmcp_b200_engine_create_tp.restype = C.c_void_p
+        handle.llmcp_b200_tp_create.restype = C.c_void_p
+        handle.llmcp_b200_tp_slot_bytes.restype = C.c_uint64
         handle._mlir_ciface_llmcp_model_prefill.restype = None
         handle._mlir_ciface_llmcp_model_decode.restype = None
         _lib = handle
@@ -473,11 +476,19 @@ class AotRuntime:
 class Engine:
     """Device-resident executor (llmcp_b200_engine_* in include/llmcp_b200.h)."""
 
-    def __init__(self, container, dims=None, capacity=1160, device=0, mode=None):
+    def __init__(self, container, dims=None, capacity=1160, device=0, mode=None, tp=None, max_tokens=1024):
+        """``tp``: a ``parallel.TensorParallel`` group; the engine then holds this rank's share of
+        the model and every rank has to make the same calls (see llmcp_b200_engine_create_tp)."""
         self.dims = dims or default_dims()
         self.container = np.ascontiguousarray(container, dtype=np.uint8)
         self.capacity = capacity
-        if mode is None:
+        self.tp = tp
+        if tp is not None:
+            mode_code = get_mode() if mode is None else mode
+            self.handle = lib().llmcp_b200_engine_create_tp(
+                _p(self.container), C.c_uint64(self.container.size), C.byref(self.dims), _i(capacity), int(device),
+                MODES[mode_code] if isinstance(mode_code, str) else int(mode_code), tp.handle, _i(max_tokens))
+        elif mode is None:
             self.handle = lib().llmcp_b200_engine_create(_p(self.container), C.c_uint64(self.container.size),
                                                          C.byref(self.dims), _i(capacity), int(device))
         else:
@@ -514,8 +525,16 @@ class Engine:
                                                 C.byref(ms)))
         return out, float(ms.value)
 
+    def local_dims(self):
+        """(dims of this rank's share, its first KV head): head counts divided by the group size."""
+        d = Dims()
+        first = C.c_int64(0)
+        _check(lib().llmcp_b200_engine_local_dims(self.handle, C.byref(d), C.byref(first)))
+        return d, int(first.value)
+
     def read_state(self):
-        d = self.dims
+        """The state buffers in the reference's layouts; under tensor parallelism this rank's heads."""
+        d = self.local_dims()[0] if self.tp is not None else self.dims
         kv = np.empty((d.full_layers, 2, d.kv_heads, self.capacity, d.head_dim), dtype=np.uint16)
         delta = np.empty((d.linear_layers, d.lin_v_heads, d.lin_k_dim, d.lin_v_dim), dtype=np.float32)
         conv = np.empty((d.linear_layers, d.conv_kernel - 1, d.qkv_dim), dtype=np.uint16)

@@ -16,6 +16,7 @@
 #include "checkpoint.h"
 #include "engine.h"
 #include "kernels.h"
+#include "tp_comm.h"
 
 using namespace llmcp_b200;
 
@@ -928,6 +929,62 @@ void *llmcp_b200_engine_create_mode(const uint8_t *file, uint64_t file_bytes, co
     set_error(e.what());
     return nullptr;
   }
+}
+
+uint64_t llmcp_b200_tp_slot_bytes(const llmcp_b200_dims *dims, int64_t max_tokens) {
+  return Engine::tp_slot_bytes(to_dims(dims), max_tokens);
+}
+
+void *llmcp_b200_tp_create(int rank, int size, uint64_t slot_bytes, int device, uint8_t *handle_out) {
+  try {
+    cuda_check(cudaSetDevice(device), "cudaSetDevice");
+    return new TpComm(rank, size, slot_bytes, handle_out);
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return nullptr;
+  }
+}
+
+int llmcp_b200_tp_attach(void *tp, const uint8_t *handles) {
+  return guarded_async([&] { static_cast<TpComm *>(tp)->attach(handles); });
+}
+
+void llmcp_b200_tp_destroy(void *tp) { delete static_cast<TpComm *>(tp); }
+
+int llmcp_b200_tp_all_gather(void *tp, const void *src, uint64_t row_bytes, uint64_t rows, int slot, void *dst, int *status,
+                             void *stream) {
+  return guarded_async([&] {
+    TpComm &comm = *static_cast<TpComm *>(tp);
+    const TpSegment segment = {src, static_cast<size_t>(row_bytes), static_cast<size_t>(rows), 0};
+    cuda_check(comm.all_gather(&segment, 1, slot, status, static_cast<cudaStream_t>(stream)), "all-gather");
+    g_launches += 1;
+    if (dst)
+      cuda_check(cudaMemcpyAsync(dst, comm.slot(slot), static_cast<size_t>(row_bytes) * rows * comm.size(), cudaMemcpyDeviceToDevice,
+                                 static_cast<cudaStream_t>(stream)), "copy out of the slot");
+  });
+}
+
+void *llmcp_b200_engine_create_tp(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims, int64_t capacity,
+                                  int device, int mode, void *tp, int64_t max_tokens) {
+  try {
+    const ModelDims d = to_dims(dims);
+    check_dims(d);
+    if (mode != kModeExact && mode != kModeFast)
+      throw std::runtime_error("mode must be 0 (exact) or 1 (fast)");
+    return new Engine(file, file_bytes, d, capacity, device, mode, static_cast<TpComm *>(tp), max_tokens);
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return nullptr;
+  }
+}
+
+int llmcp_b200_engine_local_dims(void *engine, llmcp_b200_dims *dims, int64_t *kv_head0) {
+  return guarded_async([&] {
+    Engine &e = *static_cast<Engine *>(engine);
+    from_dims(e.local_dims(), dims);
+    if (kv_head0)
+      *kv_head0 = e.kv_head0();
+  });
 }
 
 void llmcp_b200_engine_destroy(void *engine) { delete static_cast<Engine *>(engine); }

@@ -7,6 +7,7 @@
 #include <stdexcept>
 
 #include "kernels.h"
+#include "tp_comm.h"
 
 namespace llmcp_b200 {
 
@@ -84,10 +85,62 @@ void Engine::check(cudaError_t e, const char *what) {
     throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode)
-    : dims_(dims), capacity_(capacity), device_(device), mode_(mode < 0 ? default_mode() : (mode == kModeFast ? kModeFast : kModeExact)) {
+std::string Engine::tp_unsupported(const ModelDims &d, int size) {
+  if (size < 1 || size > kTpMaxRanks)
+    return "tensor parallel group size must be 1 .. 8";
+  if (size == 1)
+    return "";
+  if (d.lin_k_heads % size || d.lin_v_heads % size || d.heads % size)
+    return "head counts do not divide by the group size";
+  if (d.kv_heads % size && size % d.kv_heads)
+    return "KV heads neither divide by the group size nor divide it";
+  if (d.hidden % (size * 8) || d.vocab % (size * 8))
+    return "hidden / vocabulary rows do not split into whole groups of 8 rows";
+  if (d.intermediate % (size * 128) || (d.lin_v_heads / size * d.lin_v_dim) % 128 || (d.heads / size * d.head_dim) % 128)
+    return "a rank's share of intermediate / value / attention width must be a multiple of 128";
+  return "";
+}
+
+size_t Engine::tp_slot_bytes(const ModelDims &d, int64_t max_tokens) {
+  const size_t rows = static_cast<size_t>(std::max<int64_t>(1, max_tokens));
+  const size_t widest = static_cast<size_t>(std::max({d.intermediate, d.value_dim(), d.attn_dim()}));
+  const size_t quant = round_up(rows * widest, 256) + round_up(rows * (widest / 32) * 4, 256);
+  const size_t rows_bf16 = round_up(rows * static_cast<size_t>(d.hidden) * 2, 256);
+  const size_t logits = round_up(static_cast<size_t>(d.vocab) * 4, 256);
+  return std::max({quant, rows_bf16, logits}) + 256;
+}
+
+Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode,
+               TpComm *tp, int64_t max_tokens)
+    : dims_(dims), local_(dims), tp_(tp), max_tokens_(max_tokens), capacity_(capacity), device_(device),
+      mode_(mode < 0 ? default_mode() : (mode == kModeFast ? kModeFast : kModeExact)) {
   if (capacity <= 0)
     throw std::runtime_error("capacity must be positive");
+  if (tp && tp->size() > 1) {
+    tp_rank_ = tp->rank();
+    tp_size_ = tp->size();
+    const std::string why = tp_unsupported(dims, tp_size_);
+    if (!why.empty())
+      throw std::runtime_error("tensor parallel: " + why);
+    if (tp->slot_bytes() < tp_slot_bytes(dims, max_tokens))
+      throw std::runtime_error("tensor parallel: the exchange slots are smaller than Engine::tp_slot_bytes()");
+    local_.lin_k_heads = dims.lin_k_heads / tp_size_;
+    local_.lin_v_heads = dims.lin_v_heads / tp_size_;
+    local_.heads = dims.heads / tp_size_;
+    if (dims.kv_heads >= tp_size_) {
+      local_.kv_heads = dims.kv_heads / tp_size_;
+      kv_head0_ = tp_rank_ * local_.kv_heads;
+    } else { // more ranks than KV heads: every KV head lives on size / kv_heads ranks
+      local_.kv_heads = 1;
+      kv_head0_ = tp_rank_ / (tp_size_ / dims.kv_heads);
+    }
+  } else {
+    tp_ = nullptr;
+  }
+  hidden_rows_ = dims.hidden / tp_size_;
+  inter_rows_ = dims.intermediate / tp_size_;
+  vocab_rows_ = dims.vocab / tp_size_;
+  vocab_row0_ = tp_rank_ * vocab_rows_;
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
     throw std::runtime_error("no CUDA device: this library has no CPU path");
@@ -110,7 +163,7 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     throw std::runtime_error("only q8_0 arenas are supported (quantization = " + manifest.quantization + ")");
   load_weights(base, manifest);
 
-  const ModelDims &c = dims_;
+  const ModelDims &c = local_; // state is per rank: this rank's heads
   const size_t kv_bytes = static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2;
   const size_t delta_bytes = static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4;
   const size_t conv_bytes = static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2;
@@ -136,6 +189,7 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   logits_ = static_cast<float *>(alloc(static_cast<size_t>(c.vocab) * 4));
   argmax_v_ = static_cast<float *>(alloc(kArgmaxParts * 4));
   argmax_i_ = static_cast<int64_t *>(alloc(kArgmaxParts * 8));
+  argmax_pair_ = static_cast<uint8_t *>(alloc(16));
   // [next token (8 bytes) | GEMM status word (4)]: one copy brings both back after a call.
   uint8_t *results = static_cast<uint8_t *>(alloc(16));
   next_token_ = reinterpret_cast<int64_t *>(results);
@@ -238,17 +292,33 @@ void Engine::rms_norm(const uint16_t *a, const uint16_t *b, int64_t S, const Sma
 
 void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   const ModelDims &c = dims_;
+  const ModelDims &m = local_;
   const std::string root = "model.language_model.";
-  // One pool for all device weights; a staging buffer for the largest packed tensor.
+  struct Rows { // rows [row0, row0 + rows) of a tensor's first dimension
+    int64_t row0, rows;
+  };
+  const int G = tp_size_, r = tp_rank_;
+  // One pool for all device weights; a staging buffer for the largest packed tensor.  A rank of a
+  // tensor-parallel group keeps 1 / size of every projection (the tied table and the 2 x heads rows of
+  // a / b stay whole), so the pool is sized by the rows actually taken.
   size_t pool_bytes = 0, staging_bytes = 0;
+  auto q8_bytes = [&](size_t n, size_t k) {
+    size_t bytes = round_up(n * k, 256) + round_up(n * (k / 32) * 2, 256);
+    if (gemm_kind_ >= 1)
+      bytes += round_up(n * (k / 32) * 4, 256); // f32 scales, row-major or block-major
+    if (gemm_kind_ >= 2 + kGemmF16)
+      bytes += round_up(n * k * 2, 256);
+    return bytes;
+  };
   for (const TensorEntry &t : manifest.tensors) {
     if (t.dtype == "Q8_0") {
       const size_t n = static_cast<size_t>(t.shape[0]), k = static_cast<size_t>(t.shape[1]);
-      pool_bytes += round_up(n * k, 256) + round_up(n * (k / 32) * 2, 256);
-      if (gemm_kind_ >= 1)
-        pool_bytes += round_up(n * (k / 32) * 4, 256); // f32 scales, row-major or block-major
-      if (gemm_kind_ >= 2 + kGemmF16)
-        pool_bytes += round_up(n * k * 2, 256);
+      const bool whole = G == 1 || t.name.find("embed_tokens") != std::string::npos ||
+                         t.name.find("in_proj_a") != std::string::npos || t.name.find("in_proj_b") != std::string::npos;
+      size_t rows = whole ? n : n / G + 8;
+      if (!whole && (t.name.find("k_proj") != std::string::npos || t.name.find("v_proj") != std::string::npos))
+        rows = static_cast<size_t>(m.kv_dim()); // KV heads are duplicated when the group is larger than their number
+      pool_bytes += q8_bytes(rows, k);
       staging_bytes = std::max<size_t>(staging_bytes, t.size);
     } else {
       pool_bytes += round_up(t.size, 256);
@@ -263,56 +333,105 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   auto take = [&](size_t bytes) {
     uint8_t *p = pool + cursor;
     cursor += round_up(bytes, 256);
+    if (cursor > pool_bytes)
+      throw std::runtime_error("weight pool overflow");
     return p;
   };
 
-  auto q8 = [&](const std::string &name, int64_t rows, int64_t cols) {
+  // A Q8 tensor [rows, cols] of which this rank keeps the given row ranges (whole 8-row groups), in
+  // that order.  A range is a contiguous byte range of the packed records (group-major layout).
+  auto q8 = [&](const std::string &name, int64_t rows, int64_t cols, std::vector<Rows> keep = {}) {
     const TensorEntry *t = manifest.find(name);
     if (!t)
       throw std::runtime_error("missing tensor " + name);
     if (t->dtype != "Q8_0" || t->shape.size() != 2 || t->shape[0] != rows || t->shape[1] != cols)
       throw std::runtime_error("tensor " + name + " is not Q8_0 [" + std::to_string(rows) + ", " +
                                std::to_string(cols) + "]");
+    if (keep.empty())
+      keep.push_back({0, rows});
+    int64_t kept = 0;
+    for (const Rows &range : keep) {
+      if (range.row0 % 8 || range.rows % 8 || range.row0 + range.rows > rows)
+        throw std::runtime_error("tensor " + name + ": a rank's rows must be whole groups of 8");
+      kept += range.rows;
+    }
+    const int64_t nb = cols / 32;
     Q8Weight w;
-    w.N = static_cast<int>(rows);
+    w.N = static_cast<int>(kept);
     w.K = static_cast<int>(cols);
-    w.q = reinterpret_cast<int8_t *>(take(static_cast<size_t>(rows) * cols));
-    w.d = reinterpret_cast<uint16_t *>(take(static_cast<size_t>(rows) * (cols / 32) * 2));
+    w.q = reinterpret_cast<int8_t *>(take(static_cast<size_t>(kept) * cols));
+    w.d = reinterpret_cast<uint16_t *>(take(static_cast<size_t>(kept) * nb * 2));
     if (gemm_kind_ == 1)
-      w.d32 = reinterpret_cast<float *>(take(static_cast<size_t>(rows) * (cols / 32) * 4));
-    check(cudaMemcpyAsync(staging, base + t->offset, t->size, cudaMemcpyHostToDevice, stream_), "upload weights");
-    launch_repack_p4(staging, rows, cols, w.q, w.d, w.d32, stream_);
-    check(cudaGetLastError(), "repack");
+      w.d32 = reinterpret_cast<float *>(take(static_cast<size_t>(kept) * nb * 4));
+    int64_t at = 0;
+    size_t staged = 0;
+    for (const Rows &range : keep) {
+      const size_t offset = static_cast<size_t>(range.row0 / 4) * nb * kRecordBytes;
+      const size_t bytes = static_cast<size_t>(range.rows / 4) * nb * kRecordBytes;
+      check(cudaMemcpyAsync(staging + staged, base + t->offset + offset, bytes, cudaMemcpyHostToDevice, stream_), "upload weights");
+      launch_repack_p4(staging + staged, range.rows, cols, w.q + at * cols, w.d + at * nb, w.d32 ? w.d32 + at * nb : nullptr, stream_);
+      check(cudaGetLastError(), "repack");
+      at += range.rows;
+      staged += bytes;
+    }
     if (gemm_kind_ >= 2) { // TMA-fed forms: block-major scales, and for the f16 forms the f16-valued plane
-      w.d32t = reinterpret_cast<float *>(take(static_cast<size_t>(rows) * (cols / 32) * 4));
+      w.d32t = reinterpret_cast<float *>(take(static_cast<size_t>(kept) * nb * 4));
       if (gemm_kind_ >= 2 + kGemmF16) {
-        w.h = take(static_cast<size_t>(rows) * cols * 2);
-        launch_weights_to_f16(w.q, w.d, rows, static_cast<int>(cols), w.h, w.d32t, stream_);
+        w.h = take(static_cast<size_t>(kept) * cols * 2);
+        launch_weights_to_f16(w.q, w.d, kept, static_cast<int>(cols), w.h, w.d32t, stream_);
       } else {
-        launch_scales_block_major(w.d, 1, rows, static_cast<int>(cols), rows, w.d32t, stream_);
+        launch_scales_block_major(w.d, 1, kept, static_cast<int>(cols), kept, w.d32t, stream_);
       }
       check(cudaGetLastError(), "GEMM planes");
     }
     return w;
   };
-  auto small = [&](const std::string &name, int64_t elements) {
+  // A BF16 / F32 tensor of which the given ranges of its first dimension are kept (`inner`
+  // elements per index of that dimension).
+  auto small = [&](const std::string &name, int64_t elements, std::vector<Rows> keep = {}, int64_t inner = 1) {
     const TensorEntry *t = manifest.find(name);
     if (!t)
       throw std::runtime_error("missing tensor " + name);
-    SmallTensor s;
-    s.dtype = dtype_of(*t);
+    SmallTensor st;
+    st.dtype = dtype_of(*t);
     uint64_t count = 1;
     for (int64_t d : t->shape)
       count *= static_cast<uint64_t>(d);
     if (static_cast<int64_t>(count) != elements)
       throw std::runtime_error("tensor " + name + " has " + std::to_string(count) + " elements, expected " +
                                std::to_string(elements));
-    s.data = take(t->size);
-    check(cudaMemcpyAsync(s.data, base + t->offset, t->size, cudaMemcpyHostToDevice, stream_), "upload tensor");
-    return s;
+    const size_t width = st.dtype == kBF16 ? 2 : 4;
+    if (keep.empty())
+      keep.push_back({0, elements / inner});
+    size_t kept = 0;
+    for (const Rows &range : keep)
+      kept += static_cast<size_t>(range.rows) * inner * width;
+    st.data = take(kept);
+    size_t at = 0;
+    for (const Rows &range : keep) {
+      const size_t bytes = static_cast<size_t>(range.rows) * inner * width;
+      check(cudaMemcpyAsync(static_cast<uint8_t *>(st.data) + at, base + t->offset + static_cast<size_t>(range.row0) * inner * width,
+                            bytes, cudaMemcpyHostToDevice, stream_), "upload tensor");
+      at += bytes;
+    }
+    return st;
   };
 
   embed_ = q8(root + "embed_tokens.weight", c.vocab, c.hidden);
+  lm_head_ = embed_; // the tied table's rows [vocab_row0_, + vocab_rows_) for the vocabulary projection
+  lm_head_.N = static_cast<int>(vocab_rows_);
+  lm_head_.q = embed_.q + vocab_row0_ * c.hidden;
+  lm_head_.d = embed_.d + vocab_row0_ * (c.hidden / 32);
+  if (embed_.d32)
+    lm_head_.d32 = embed_.d32 + vocab_row0_ * (c.hidden / 32);
+  if (G > 1)
+    lm_head_.h = nullptr, lm_head_.d32t = nullptr; // block-major planes cannot be sliced by rows
+  // This rank's rows of the fused q | k | v projection, of the convolution over them and of the
+  // per-head parameters: its key heads' q and k channels, then its value heads' channels.
+  const int64_t qk = m.lin_k_heads * c.lin_k_dim, vd = m.lin_v_heads * c.lin_v_dim;
+  const std::vector<Rows> qkv_rows = {{r * qk, qk}, {c.lin_k_heads * c.lin_k_dim + r * qk, qk},
+                                      {2 * c.lin_k_heads * c.lin_k_dim + r * vd, vd}};
+  const std::vector<Rows> v_heads = {{r * m.lin_v_heads, m.lin_v_heads}};
   layers_.resize(static_cast<size_t>(c.layers));
   for (int64_t l = 0; l < c.layers; ++l) {
     LayerWeights &L = layers_[static_cast<size_t>(l)];
@@ -321,30 +440,30 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
     L.input_norm = small(p + "input_layernorm.weight", c.hidden);
     L.post_norm = small(p + "post_attention_layernorm.weight", c.hidden);
     if (!L.full) {
-      L.qkv = q8(p + "linear_attn.in_proj_qkv.weight", c.qkv_dim(), c.hidden);
-      L.z = q8(p + "linear_attn.in_proj_z.weight", c.value_dim(), c.hidden);
+      L.qkv = q8(p + "linear_attn.in_proj_qkv.weight", c.qkv_dim(), c.hidden, qkv_rows);
+      L.z = q8(p + "linear_attn.in_proj_z.weight", c.value_dim(), c.hidden, {{r * vd, vd}});
       L.a = q8(p + "linear_attn.in_proj_a.weight", c.lin_v_heads, c.hidden);
       L.b = q8(p + "linear_attn.in_proj_b.weight", c.lin_v_heads, c.hidden);
-      L.conv = small(p + "linear_attn.conv1d.weight", c.qkv_dim() * c.conv_kernel);
+      L.conv = small(p + "linear_attn.conv1d.weight", c.qkv_dim() * c.conv_kernel, qkv_rows, c.conv_kernel);
       if (L.conv.dtype != kBF16)
         throw std::runtime_error("conv1d.weight must be BF16");
-      L.dt_bias = small(p + "linear_attn.dt_bias", c.lin_v_heads);
-      L.a_log = small(p + "linear_attn.A_log", c.lin_v_heads);
+      L.dt_bias = small(p + "linear_attn.dt_bias", c.lin_v_heads, v_heads);
+      L.a_log = small(p + "linear_attn.A_log", c.lin_v_heads, v_heads);
       L.lin_norm = small(p + "linear_attn.norm.weight", c.lin_v_dim);
-      L.out_proj = q8(p + "linear_attn.out_proj.weight", c.hidden, c.value_dim());
+      L.out_proj = q8(p + "linear_attn.out_proj.weight", c.hidden, c.value_dim(), {{r * hidden_rows_, hidden_rows_}});
     } else {
-      L.q_proj = q8(p + "self_attn.q_proj.weight", c.q_out(), c.hidden);
-      L.k_proj = q8(p + "self_attn.k_proj.weight", c.kv_dim(), c.hidden);
-      L.v_proj = q8(p + "self_attn.v_proj.weight", c.kv_dim(), c.hidden);
-      L.o_proj = q8(p + "self_attn.o_proj.weight", c.hidden, c.attn_dim());
+      L.q_proj = q8(p + "self_attn.q_proj.weight", c.q_out(), c.hidden, {{r * m.q_out(), m.q_out()}});
+      L.k_proj = q8(p + "self_attn.k_proj.weight", c.kv_dim(), c.hidden, {{kv_head0_ * c.head_dim, m.kv_dim()}});
+      L.v_proj = q8(p + "self_attn.v_proj.weight", c.kv_dim(), c.hidden, {{kv_head0_ * c.head_dim, m.kv_dim()}});
+      L.o_proj = q8(p + "self_attn.o_proj.weight", c.hidden, c.attn_dim(), {{r * hidden_rows_, hidden_rows_}});
       L.q_norm = small(p + "self_attn.q_norm.weight", c.head_dim);
       L.k_norm = small(p + "self_attn.k_norm.weight", c.head_dim);
       if (L.q_norm.dtype != kBF16 || L.k_norm.dtype != kBF16)
         throw std::runtime_error("q_norm / k_norm must be BF16");
     }
-    L.gate = q8(p + "mlp.gate_proj.weight", c.intermediate, c.hidden);
-    L.up = q8(p + "mlp.up_proj.weight", c.intermediate, c.hidden);
-    L.down = q8(p + "mlp.down_proj.weight", c.hidden, c.intermediate);
+    L.gate = q8(p + "mlp.gate_proj.weight", c.intermediate, c.hidden, {{r * inter_rows_, inter_rows_}});
+    L.up = q8(p + "mlp.up_proj.weight", c.intermediate, c.hidden, {{r * inter_rows_, inter_rows_}});
+    L.down = q8(p + "mlp.down_proj.weight", c.hidden, c.intermediate, {{r * hidden_rows_, hidden_rows_}});
   }
   final_norm_ = small(root + "norm.weight", c.hidden);
   check(cudaStreamSynchronize(stream_), "weight upload");
@@ -353,14 +472,14 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
 }
 
 void Engine::reset_state() {
-  const ModelDims &c = dims_;
+  const ModelDims &c = local_;
   check(cudaMemsetAsync(kv_, 0, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, stream_), "memset");
   check(cudaMemsetAsync(delta_, 0, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, stream_), "memset");
   check(cudaMemsetAsync(conv_, 0, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, stream_), "memset");
 }
 
 void Engine::upload_state(const uint16_t *kv, const float *delta, const uint16_t *conv) {
-  const ModelDims &c = dims_;
+  const ModelDims &c = local_;
   check(cudaMemcpyAsync(kv_, kv, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, cudaMemcpyHostToDevice, stream_), "upload kv");
   check(cudaMemcpyAsync(delta_, delta, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, cudaMemcpyHostToDevice, stream_), "upload delta");
   check(cudaMemcpyAsync(conv_, conv, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, cudaMemcpyHostToDevice, stream_), "upload conv");
@@ -368,7 +487,7 @@ void Engine::upload_state(const uint16_t *kv, const float *delta, const uint16_t
 }
 
 void Engine::download_state(uint16_t *kv, float *delta, uint16_t *conv) {
-  const ModelDims &c = dims_;
+  const ModelDims &c = local_;
   if (kv)
     check(cudaMemcpyAsync(kv, kv_, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, cudaMemcpyDeviceToHost, stream_), "download kv");
   if (delta)
@@ -380,11 +499,15 @@ void Engine::download_state(uint16_t *kv, float *delta, uint16_t *conv) {
 
 void Engine::ensure_workspace(int64_t S, int64_t position) {
   const ModelDims &c = dims_;
+  const ModelDims &m = local_;
   const size_t need_attn =
-      std::max(attn_scratch_bytes(S, static_cast<int>(c.heads), static_cast<int>(c.head_dim), position),
-               attn_fast_scratch_bytes(static_cast<int>(c.heads), static_cast<int>(c.head_dim), position + S - 1));
+      std::max(attn_scratch_bytes(S, static_cast<int>(m.heads), static_cast<int>(m.head_dim), position),
+               attn_fast_scratch_bytes(static_cast<int>(m.heads), static_cast<int>(m.head_dim), position + S - 1));
   if (S <= ws_tokens_ && need_attn <= attn_scratch_bytes_)
     return;
+  if (tp_ && S > max_tokens_)
+    throw std::runtime_error("tensor parallel: a call of " + std::to_string(S) + " tokens exceeds the " +
+                             std::to_string(max_tokens_) + " the exchange slots were sized for");
   check(cudaStreamSynchronize(stream_), "workspace resize");
   if (decode_graph_) { // the captured step points into the buffers that are about to move
     cudaGraphExecDestroy(decode_graph_);
@@ -418,23 +541,53 @@ void Engine::ensure_workspace(int64_t S, int64_t position) {
       ah_ = alloc(r * max_k * 2);
     ast_ = static_cast<float *>(alloc(static_cast<size_t>(gemm_tc16_scale_pitch(rows)) * (max_k / 32) * 4));
   }
-  qkv_ = static_cast<uint16_t *>(alloc(r * c.qkv_dim() * 2));
-  z_ = static_cast<uint16_t *>(alloc(r * c.value_dim() * 2));
+  // Mixer and MLP intermediates hold this rank's heads / rows only; a and b are whole.
+  qkv_ = static_cast<uint16_t *>(alloc(r * m.qkv_dim() * 2));
+  z_ = static_cast<uint16_t *>(alloc(r * m.value_dim() * 2));
   a_ = static_cast<uint16_t *>(alloc(r * c.lin_v_heads * 2));
   b_ = static_cast<uint16_t *>(alloc(r * c.lin_v_heads * 2));
-  convd_ = static_cast<uint16_t *>(alloc(r * c.qkv_dim() * 2));
-  gdn_ = static_cast<uint16_t *>(alloc(r * c.value_dim() * 2));
-  qg_ = static_cast<uint16_t *>(alloc(r * c.q_out() * 2));
-  k_ = static_cast<uint16_t *>(alloc(r * c.kv_dim() * 2));
-  v_ = static_cast<uint16_t *>(alloc(r * c.kv_dim() * 2));
-  attn_ = static_cast<uint16_t *>(alloc(r * c.attn_dim() * 2));
-  gate_ = static_cast<uint16_t *>(alloc(r * c.intermediate * 2));
-  up_ = static_cast<uint16_t *>(alloc(r * c.intermediate * 2));
+  convd_ = static_cast<uint16_t *>(alloc(r * m.qkv_dim() * 2));
+  gdn_ = static_cast<uint16_t *>(alloc(r * m.value_dim() * 2));
+  qg_ = static_cast<uint16_t *>(alloc(r * m.q_out() * 2));
+  k_ = static_cast<uint16_t *>(alloc(r * m.kv_dim() * 2));
+  v_ = static_cast<uint16_t *>(alloc(r * m.kv_dim() * 2));
+  attn_ = static_cast<uint16_t *>(alloc(r * m.attn_dim() * 2));
+  gate_ = static_cast<uint16_t *>(alloc(r * inter_rows_ * 2));
+  up_ = static_cast<uint16_t *>(alloc(r * inter_rows_ * 2));
   gdn_scratch_ = static_cast<float *>(alloc(
-      gdn_scratch_floats(rows, static_cast<int>(c.lin_k_heads), static_cast<int>(c.lin_v_heads), static_cast<int>(c.lin_k_dim)) * 4));
+      gdn_scratch_floats(rows, static_cast<int>(m.lin_k_heads), static_cast<int>(m.lin_v_heads), static_cast<int>(m.lin_k_dim)) * 4));
   attn_scratch_bytes_ = std::max(need_attn, attn_scratch_bytes_);
   attn_scratch_ = alloc(attn_scratch_bytes_);
   ws_tokens_ = rows;
+}
+
+// Tensor parallel: the rows left in aq_ / as_ hold this rank's k_local columns; every rank gets all of
+// them (in a slot of the exchange buffer).  With one rank the local buffers are the result.
+void Engine::gather_quant(int64_t S, int64_t k_local, const int8_t **q, const float **s) {
+  if (!tp_) {
+    *q = aq_;
+    *s = as_;
+    return;
+  }
+  const int slot = exchange_++ & 1;
+  const size_t q_bytes = round_up(static_cast<size_t>(S) * k_local * tp_size_, 256);
+  const TpSegment segments[2] = {{aq_, static_cast<size_t>(k_local), static_cast<size_t>(S), 0},
+                                 {as_, static_cast<size_t>(k_local / 32 * 4), static_cast<size_t>(S), q_bytes}};
+  check(tp_->all_gather(segments, 2, slot, gemm_error_, stream_), "all-gather (quantised rows)");
+  launches_ += 1;
+  *q = reinterpret_cast<const int8_t *>(tp_->slot(slot));
+  *s = reinterpret_cast<const float *>(tp_->slot(slot) + q_bytes);
+}
+
+// The same for bf16 rows of n_local columns per rank.
+const uint16_t *Engine::gather_rows(const uint16_t *src, int64_t S, int64_t n_local) {
+  if (!tp_)
+    return src;
+  const int slot = exchange_++ & 1;
+  const TpSegment segment = {src, static_cast<size_t>(n_local) * 2, static_cast<size_t>(S), 0};
+  check(tp_->all_gather(&segment, 1, slot, gemm_error_, stream_), "all-gather (rows)");
+  launches_ += 1;
+  return reinterpret_cast<const uint16_t *>(tp_->slot(slot));
 }
 
 struct LinearJob {
@@ -531,110 +684,160 @@ void Engine::decode_step() {
   launches_ += decode_graph_launches_;
 }
 
+// First maximum over the ranks' {maximum, index} pairs: the largest value, the lowest index among
+// equal values (what the host argmax of llmcp-benchmark.cpp:51-54 picks over the whole row).
+__global__ void tp_argmax_merge_kernel(const uint8_t *__restrict__ pairs, int size, int64_t *__restrict__ out_index) {
+  grid_dependency_sync();
+  if (threadIdx.x != 0)
+    return;
+  float best = -INFINITY;
+  int64_t index = INT64_MAX;
+  for (int r = 0; r < size; ++r) {
+    const float v = *reinterpret_cast<const float *>(pairs + 16 * r);
+    const int64_t i = *reinterpret_cast<const int64_t *>(pairs + 16 * r + 8);
+    if (v > best || (v == best && i < index)) {
+      best = v;
+      index = i;
+    }
+  }
+  *out_index = index;
+}
+
 void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const float *cos_dev, const float *sin_dev,
                  int rows_from_position) {
   const ModelDims &c = dims_;
+  const ModelDims &m = local_; // this rank's heads
   const int H = static_cast<int>(c.hidden);
   if (S <= 0 || position < 0 || position + S > capacity_)
     throw std::runtime_error("sequence does not fit the cache: position " + std::to_string(position) + " + " +
                              std::to_string(S) + " > capacity " + std::to_string(capacity_));
+  if (tp_ && all_logits_)
+    throw std::runtime_error("all-position logits are not offered under tensor parallelism");
   ensure_workspace(S, position);
+  exchange_ = 0;
   launch_embedding_q8(tokens_dev, S, H, c.vocab, embed_.q, embed_.d, hidden_[0], gemm_error_, stream_);
   launches_ += 1;
   const int gemv_flags = gemv_flags_ | (mode_ == kModeFast ? kGemvFast : 0);
   const F16Planes planes = {ah_, ast_, gemm_kind_ >= 2 ? gemm_kind_ - 2 : -1};
+  int *gemm_status = use_tensor_cores_ ? gemm_error_ : nullptr;
   int cur = 0;
-  bool pending = false;
+  const uint16_t *pending = nullptr; // the MLP output still to be added to the residual stream
   int64_t lin_index = 0, full_index = 0;
   for (int64_t l = 0; l < c.layers; ++l) {
     const LayerWeights &L = layers_[static_cast<size_t>(l)];
     if (pending) {
-      rms_norm(hidden_[cur], mlp_out_, S, L.input_norm, hidden_[cur ^ 1], nullptr);
+      rms_norm(hidden_[cur], pending, S, L.input_norm, hidden_[cur ^ 1], nullptr);
       cur ^= 1;
     } else {
       rms_norm(hidden_[cur], nullptr, S, L.input_norm, nullptr, nullptr);
     }
     launches_ += 1;
+    const int8_t *mixer_q = nullptr; // the mixer's quantised output, all columns
+    const float *mixer_s = nullptr;
     if (!L.full) {
       const LinearJob jobs[4] = {{&L.qkv, qkv_, kBF16, kNone},
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
-      const int C = static_cast<int>(c.qkv_dim());
+      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status);
+      const int C = static_cast<int>(m.qkv_dim());
       uint16_t *conv_state = conv_ + lin_index * (c.conv_kernel - 1) * C;
-      float *delta_state = delta_ + lin_index * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
-      const int nk = static_cast<int>(c.lin_k_heads), nv = static_cast<int>(c.lin_v_heads);
+      float *delta_state = delta_ + lin_index * m.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
+      const int nk = static_cast<int>(m.lin_k_heads), nv = static_cast<int>(m.lin_v_heads);
       const int dk = static_cast<int>(c.lin_k_dim), dv = static_cast<int>(c.lin_v_dim);
+      // a and b are computed for all heads on every rank; this rank's heads start at head0.
+      const int nv_all = static_cast<int>(c.lin_v_heads), head0 = tp_rank_ * nv;
       if (S == 1 && fuse_decode_mixer_ && gdn_decode_supported(static_cast<int>(c.conv_kernel), nk, nv, dk, dv)) {
         check(launch_gdn_decode(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, static_cast<int>(c.conv_kernel),
-                                a_, b_, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype, delta_state, nk, nv, dk,
-                                dv, 1, z_, L.lin_norm.data, L.lin_norm.dtype, c.eps, 1, gdn_scratch_, convd_, nullptr, aq_,
-                                as_, stream_), "gated_delta_net (decode)");
+                                a_ + head0, b_ + head0, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype, delta_state,
+                                nk, nv, dk, dv, 1, z_, L.lin_norm.data, L.lin_norm.dtype, c.eps, 1, gdn_scratch_, convd_, nullptr,
+                                aq_, as_, stream_), "gated_delta_net (decode)");
         launches_ += 2;
       } else {
         check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, S, C,
                                    static_cast<int>(c.conv_kernel), convd_, stream_), "causal_conv1d");
-        check(launch_gated_delta_net(convd_, a_, b_, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype,
-                                     delta_state, S, nk, nv, dk, dv, 1, gdn_scratch_, gdn_, stream_), "gated_delta_net");
-        check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(c.value_dim()), dv,
+        check(launch_gated_delta_net(convd_, a_ + head0, b_ + head0, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype,
+                                     delta_state, S, nk, nv, dk, dv, 1, gdn_scratch_, gdn_, stream_, nv_all), "gated_delta_net");
+        check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(m.value_dim()), dv,
                                     c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
         launches_ += 5;
       }
-      const LinearJob out = {&L.out_proj, branch_, kBF16, kNone};
-      run_linears(planes, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+      gather_quant(S, m.value_dim(), &mixer_q, &mixer_s);
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
-      uint16_t *cache = kv_ + full_index * 2 * c.kv_heads * capacity_ * c.head_dim;
-      if (mode_ == kModeFast && S == 1 &&
-          attention_decode_fast_supported(static_cast<int>(c.heads), static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim))) {
+      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status);
+      uint16_t *cache = kv_ + full_index * 2 * m.kv_heads * capacity_ * c.head_dim;
+      const int nh = static_cast<int>(m.heads), nkv = static_cast<int>(m.kv_heads), hd = static_cast<int>(c.head_dim);
+      if (mode_ == kModeFast && S == 1 && attention_decode_fast_supported(nh, nkv, hd)) {
         check(launch_attention_decode_fast(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                            static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
-                                           cache, position_dev_, position, static_cast<int>(c.heads),
-                                           static_cast<int>(c.kv_heads), static_cast<int>(c.head_dim),
-                                           static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, aq_, as_, stream_),
-              "attention (fast)");
+                                           cache, position_dev_, position, nh, nkv, hd, static_cast<int>(c.rotary), capacity_,
+                                           attn_scratch_, attn_, aq_, as_, stream_), "attention (fast)");
       } else {
         check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position, cache,
-                               position_dev_, position, S, static_cast<int>(c.heads), static_cast<int>(c.kv_heads),
-                               static_cast<int>(c.head_dim), static_cast<int>(c.rotary), capacity_, attn_scratch_, attn_, aq_,
-                               as_, stream_), "attention");
+                               position_dev_, position, S, nh, nkv, hd, static_cast<int>(c.rotary), capacity_, attn_scratch_,
+                               attn_, aq_, as_, stream_), "attention");
       }
       launches_ += 3;
-      const LinearJob out = {&L.o_proj, branch_, kBF16, kNone};
-      run_linears(planes, aq_, as_, S, &out, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
+      gather_quant(S, m.attn_dim(), &mixer_q, &mixer_s);
       ++full_index;
     }
-    rms_norm(hidden_[cur], branch_, S, L.post_norm, hidden_[cur ^ 1], nullptr);
+    // Output projection of the mixer: this rank's rows of the hidden vector, then all of them.
+    const LinearJob out = {L.full ? &L.o_proj : &L.out_proj, branch_, kBF16, kNone};
+    run_linears(planes, mixer_q, mixer_s, S, &out, 1, stream_, &launches_, gemv_flags, gemm_status);
+    const uint16_t *branch = gather_rows(branch_, S, hidden_rows_);
+    rms_norm(hidden_[cur], branch, S, L.post_norm, hidden_[cur ^ 1], nullptr);
     cur ^= 1;
     const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-    run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
-    check(launch_pointwise(gate_, up_, S * c.intermediate, 1, nullptr, aq_, as_, stream_), "mul");
+    run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, gemm_status);
+    check(launch_pointwise(gate_, up_, S * inter_rows_, 1, nullptr, aq_, as_, stream_), "mul");
     launches_ += 2;
+    const int8_t *mlp_q = nullptr;
+    const float *mlp_s = nullptr;
+    gather_quant(S, inter_rows_, &mlp_q, &mlp_s);
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
-    run_linears(planes, aq_, as_, S, &down, 1, stream_, &launches_, gemv_flags, use_tensor_cores_ ? gemm_error_ : nullptr);
-    pending = true;
+    run_linears(planes, mlp_q, mlp_s, S, &down, 1, stream_, &launches_, gemv_flags, gemm_status);
+    pending = gather_rows(mlp_out_, S, hidden_rows_);
   }
   if (all_logits_) {
     // Every position's logits, what the tensor-returning `llmcp_model` function computes
     // (ModelBuilder.cpp:406-438): final norm over all rows, then one S x vocab x hidden contraction.
-    rms_norm(hidden_[cur], pending ? mlp_out_ : nullptr, S, final_norm_, nullptr, branch_);
+    rms_norm(hidden_[cur], pending, S, final_norm_, nullptr, branch_);
     const LinearJob all = {&embed_, all_logits_, kF32, kNone};
     run_linears(planes, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags & kGemvOverlapPrevious,
-                S > 1 && use_tensor_cores_ ? gemm_error_ : nullptr);
+                S > 1 ? gemm_status : nullptr);
     launches_ += 1;
   }
   // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
   const uint16_t *last = hidden_[cur] + (S - 1) * H;
-  rms_norm(last, pending ? mlp_out_ + (S - 1) * H : nullptr, 1, final_norm_, nullptr, final_hidden_);
-  const Q8Weight &table = embed_;
-  const LinearJob head = {&table, logits_, kF32, kNone};
+  rms_norm(last, pending ? pending + (S - 1) * H : nullptr, 1, final_norm_, nullptr, final_hidden_);
+  float *logits_rows = logits_ + vocab_row0_; // this rank's rows of the logits
+  const LinearJob head = {&lm_head_, logits_rows, kF32, kNone};
   run_linears(planes, aq_, as_, 1, &head, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious);
-  launch_argmax(logits_, c.vocab, argmax_v_, argmax_i_, 0, next_token_, nullptr, stream_);
-  launches_ += 3;
+  if (!tp_) {
+    launch_argmax(logits_, c.vocab, argmax_v_, argmax_i_, 0, next_token_, nullptr, stream_);
+    launches_ += 3;
+  } else {
+    // The whole row for the host only when it is asked for (1 / size of it comes from each rank).
+    if (gather_logits_) {
+      const int slot = exchange_++ & 1;
+      const TpSegment segment = {logits_rows, static_cast<size_t>(vocab_rows_) * 4, 1, 0};
+      check(tp_->all_gather(&segment, 1, slot, gemm_error_, stream_), "all-gather (logits)");
+      check(cudaMemcpyAsync(logits_, tp_->slot(slot), static_cast<size_t>(c.vocab) * 4, cudaMemcpyDeviceToDevice, stream_), "logits");
+      launches_ += 1;
+    }
+    // This rank's first maximum with its global index, then the first maximum over the ranks.  The
+    // step's last exchange has a slot of its own, so that the next step's first one never follows
+    // it into the same slot.
+    launch_argmax(logits_rows, vocab_rows_, argmax_v_, argmax_i_, vocab_row0_, reinterpret_cast<int64_t *>(argmax_pair_ + 8),
+                  reinterpret_cast<float *>(argmax_pair_), stream_);
+    const TpSegment pair = {argmax_pair_, 16, 1, 0};
+    check(tp_->all_gather(&pair, 1, 2, gemm_error_, stream_), "all-gather (argmax)");
+    launch_chained(tp_argmax_merge_kernel, dim3(1), dim3(32), 0, stream_, tp_->slot(2), tp_size_, next_token_);
+    launches_ += 6;
+  }
   check(cudaGetLastError(), "forward");
 }
 
@@ -645,6 +848,14 @@ int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position,
   if (S <= 0 || position < 0 || position + S > capacity_)
     throw std::runtime_error("sequence does not fit the cache");
   validate_tokens(tokens, S); // before any copy or launch
+  if (tp_ && gather_logits_ != (logits_host != nullptr)) {
+    // Whether the whole logits row is assembled is part of the captured step.
+    gather_logits_ = logits_host != nullptr;
+    check(cudaStreamSynchronize(stream_), "forward");
+    if (decode_graph_)
+      cudaGraphExecDestroy(decode_graph_);
+    decode_graph_ = nullptr;
+  }
   ensure_workspace(S, position);
   const size_t row_bytes = static_cast<size_t>(c.rotary) * 4;
   if (S == 1) {
@@ -729,6 +940,13 @@ void Engine::generate(int64_t first_token, int64_t position, int64_t steps, int6
   if (c.rotary > 1024)
     throw std::runtime_error("rotary dimension too large");
   validate_tokens(&first_token, 1);
+  if (tp_ && gather_logits_) { // the loop keeps tokens on the device: no rank needs the whole logits row
+    gather_logits_ = false;
+    check(cudaStreamSynchronize(stream_), "generate");
+    if (decode_graph_)
+      cudaGraphExecDestroy(decode_graph_);
+    decode_graph_ = nullptr;
+  }
   set_position(position);
   *token_pinned_ = first_token;
   check(cudaMemcpyAsync(dec_tokens_, token_pinned_, 8, cudaMemcpyHostToDevice, stream_), "first token");

@@ -14,6 +14,8 @@
 
 namespace llmcp_b200 {
 
+class TpComm;
+
 struct Q8Weight {
   int8_t *q = nullptr;   // [N][K]
   uint16_t *d = nullptr; // [N][K/32] f16 bits
@@ -59,12 +61,28 @@ public:
   // `base` points at the first byte of a mapped container (header, arena, manifest).
   // mode: kModeExact, kModeFast, or -1 for default_mode().
   // Throws std::runtime_error with a readable message on any failure.
-  Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode = -1);
+  // tp: exchange context of a tensor-parallel group (null or size 1: the whole model on this GPU).
+  // A rank of size G holds 1/G of every projection's output rows, 1/G of the recurrent and
+  // attention heads (KV heads are duplicated when G exceeds their number) and 1/G of the
+  // vocabulary projection; every rank must make the same calls.  max_tokens bounds the rows of one
+  // call under tensor parallelism (the exchange slots are sized for it).
+  Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode = -1,
+         TpComm *tp = nullptr, int64_t max_tokens = 1024);
+  // Bytes per exchange slot an engine with these dimensions needs for calls of up to max_tokens rows.
+  static size_t tp_slot_bytes(const ModelDims &dims, int64_t max_tokens);
+  // Why these dimensions cannot be split over `size` ranks, or "" if they can.
+  static std::string tp_unsupported(const ModelDims &dims, int size);
   ~Engine();
   Engine(const Engine &) = delete;
   Engine &operator=(const Engine &) = delete;
 
   const ModelDims &dims() const { return dims_; }
+  // Dimensions of this rank's share: head counts divided by the group size (state buffers and
+  // upload_state / download_state use these); hidden, intermediate and vocab stay global.
+  const ModelDims &local_dims() const { return local_; }
+  int64_t kv_head0() const { return kv_head0_; } // first KV head of this rank
+  int tp_rank() const { return tp_rank_; }
+  int tp_size() const { return tp_size_; }
   int64_t capacity() const { return capacity_; }
   int device() const { return device_; }
   int mode() const { return mode_; }
@@ -118,7 +136,21 @@ private:
   void linear(const Q8Weight &w, int64_t S, void *y, int y_dtype, int activation);
   void check(cudaError_t e, const char *what);
 
+  // Tensor parallelism: all-gathers of quantised rows (int8 + scales) and of bf16 rows.
+  void gather_quant(int64_t S, int64_t k_local, const int8_t **q, const float **s);
+  const uint16_t *gather_rows(const uint16_t *src, int64_t S, int64_t n_local);
+
   ModelDims dims_;
+  ModelDims local_;
+  TpComm *tp_ = nullptr;
+  int tp_rank_ = 0, tp_size_ = 1;
+  int64_t max_tokens_ = 1024;
+  int64_t kv_head0_ = 0;   // first KV head of this rank
+  int64_t hidden_rows_ = 0, inter_rows_ = 0, vocab_rows_ = 0, vocab_row0_ = 0; // this rank's output rows
+  int exchange_ = 0;       // exchanges issued so far by the running forward (slot rule of TpComm)
+  bool gather_logits_ = false; // tensor parallel: the next forward also assembles the full logits row
+  Q8Weight lm_head_;       // the rows of the tied table this rank multiplies (a view into embed_)
+  uint8_t *argmax_pair_ = nullptr; // {f32 maximum, pad, i64 index} of this rank's logits
   int64_t capacity_ = 0;
   int device_ = 0;
   int mode_ = kModeExact;

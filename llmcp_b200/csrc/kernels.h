@@ -122,7 +122,7 @@ size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk);
 cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b, const void *a_log,
                                    int a_log_dtype, const void *dt_bias, int dt_dtype, float *state, int64_t S,
                                    int nk, int nv, int dk, int dv, int b_activated, float *scratch,
-                                   uint16_t *out, cudaStream_t stream);
+                                   uint16_t *out, cudaStream_t stream, int ab_stride = 0 /* row pitch of a and b; 0 = nv */);
 // One token of causal_conv1d + gated_delta_net + gated_rms_norm (+ quantisation) in two launches;
 // the same values as the three general launchers above produce.  scratch: gdn_scratch_floats(1, ..).
 bool gdn_decode_supported(int kernel, int nk, int nv, int dk, int dv);

@@ -70,7 +70,7 @@ cudaError_t launch_causal_conv1d(const uint16_t *x, const uint16_t *w, uint16_t 
 __global__ void __launch_bounds__(128)
 gdn_prepare_kernel(const uint16_t *__restrict__ conv, const uint16_t *__restrict__ a,
                    const uint16_t *__restrict__ b, const void *__restrict__ a_log, int a_log_dtype,
-                   const void *__restrict__ dt_bias, int dt_dtype, int64_t S, int nk, int nv, int dk, int dv,
+                   const void *__restrict__ dt_bias, int dt_dtype, int64_t S, int nk, int nv, int ab_stride, int dk, int dv,
                    int b_activated, float *__restrict__ qn, float *__restrict__ kn, float *__restrict__ beta,
                    float *__restrict__ decay) {
   extern __shared__ float prep_all[]; // per warp: q squares [dk], k squares [dk]
@@ -116,11 +116,12 @@ gdn_prepare_kernel(const uint16_t *__restrict__ conv, const uint16_t *__restrict
   const int64_t i = (warp - norm_items) * 32 + lane;
   if (i < S * nv) {
     const int h = static_cast<int>(i % nv);
-    const float bv = bf16_to_f32(b[i]);
+    const int64_t ab = (i / nv) * ab_stride + h; // a and b may be rows of a wider matrix
+    const float bv = bf16_to_f32(b[ab]);
     beta[i] = b_activated ? bv : d_sigmoid(bv);
     // dt_bias is widened from bf16, A_log is read as f32 (LowerGatedDeltaNet.cpp:233-246).
     const float dt = bf16_to_f32(f32_to_bf16(load_as_f32(dt_bias, dt_dtype, h)));
-    const float a_plus_dt = __fadd_rn(bf16_to_f32(a[i]), dt);
+    const float a_plus_dt = __fadd_rn(bf16_to_f32(a[ab]), dt);
     const float softplus = d_log(__fadd_rn(1.0f, d_exp(a_plus_dt)));
     const float g = __fmul_rn(-d_exp(load_as_f32(a_log, a_log_dtype, h)), softplus);
     decay[i] = d_exp(g);
@@ -368,9 +369,11 @@ size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk) {
 cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b,
                                    const void *a_log, int a_log_dtype, const void *dt_bias, int dt_dtype,
                                    float *state, int64_t S, int nk, int nv, int dk, int dv,
-                                   int b_activated, float *scratch, uint16_t *out, cudaStream_t stream) {
+                                   int b_activated, float *scratch, uint16_t *out, cudaStream_t stream, int ab_stride) {
   if (S == 0)
     return cudaSuccess;
+  if (ab_stride <= 0)
+    ab_stride = nv;
   if (nk <= 0 || nv <= 0 || nv % nk != 0)
     return cudaErrorInvalidValue;
   float *qn = scratch;
@@ -379,7 +382,7 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
   float *decay = beta + S * nv;
   const int64_t warps = S * nk + (S * nv + 31) / 32;
   launch_chained(gdn_prepare_kernel, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 4 * 2 * dk * sizeof(float), stream, 
-      conv, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, S, nk, nv, dk, dv, b_activated, qn, kn, beta, decay);
+      conv, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, S, nk, nv, ab_stride, dk, dv, b_activated, qn, kn, beta, decay);
   dim3 grid(nv, (dv + 31) / 32);
   const size_t smem = 2 * static_cast<size_t>(dk) * sizeof(float);
   static const bool pipelined = [] {

@@ -13,6 +13,10 @@ contiguous byte range of the packed weight, every output element is computed by 
 the unsharded arithmetic, and one all-gather assembles the row, so the result is bit-identical
 to the single-GPU product.  A split along K would change the order of the f32 additions and is
 not offered.
+
+(d) ``TensorParallel`` is the whole model split that way inside the engine (C++ / CUDA): this
+module only hands the ranks each other's buffer handles; the exchanges themselves are kernels of
+the library that store into the peers' memory, with no call into ``torch.distributed``.
 """
 import ctypes as C
 
@@ -190,3 +194,54 @@ class ColumnParallelLinear:
 
     def forward(self, x_bf16_bits, group=None):
         return gather_rows(self.local(x_bf16_bits), group=group)
+
+
+class TensorParallel:
+    """A tensor-parallel group of engines, one process per GPU (llmcp_b200_tp_* in
+    include/llmcp_b200.h).  Creating it allocates this rank's exchange buffer and swaps the
+    CUDA IPC handles of all ranks through ``torch.distributed`` (the only use of it: any other
+    channel that moves 64 bytes per rank would do).  Pass it to ``llmcp_b200.Engine(..., tp=group)``.
+    """
+
+    def __init__(self, dims, rank, world, device, max_tokens=1024, group=None):
+        import torch.distributed as dist
+        import llmcp_b200 as L
+        lib = L.lib()
+        self.rank, self.world, self.max_tokens = rank, world, max_tokens
+        slot_bytes = int(lib.llmcp_b200_tp_slot_bytes(C.byref(dims), C.c_int64(max_tokens)))
+        mine = (C.c_uint8 * 64)()
+        handle = lib.llmcp_b200_tp_create(int(rank), int(world), C.c_uint64(slot_bytes), int(device), mine)
+        if not handle:
+            raise L.LlmcpError(L.last_error())
+        self.handle = C.c_void_p(handle)
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(mine), group=group)
+            blob = b"".join(handles)
+            if lib.llmcp_b200_tp_attach(self.handle, blob) != 0:
+                raise L.LlmcpError(L.last_error())
+
+    def all_gather(self, src, slot, stream=0):
+        """The exchange alone (for tests): ``src`` is a torch CUDA tensor [rows, cols] of this rank;
+        returns [rows, world * cols]."""
+        import torch
+        import llmcp_b200 as L
+        rows, cols = src.shape
+        row_bytes = cols * src.element_size()
+        out = torch.empty((rows, self.world * cols), dtype=src.dtype, device=src.device)
+        status = torch.zeros(1, dtype=torch.int32, device=src.device)
+        rc = L.lib().llmcp_b200_tp_all_gather(self.handle, C.c_void_p(src.data_ptr()), C.c_uint64(row_bytes), C.c_uint64(rows),
+                                              int(slot), C.c_void_p(out.data_ptr()), C.c_void_p(status.data_ptr()),
+                                              C.c_void_p(stream or torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise L.LlmcpError(L.last_error())
+        torch.cuda.synchronize()
+        if int(status.item()) != 0:
+            raise L.LlmcpError("all-gather: a peer's flag did not arrive within the wait limit")
+        return out
+
+    def close(self):
+        import llmcp_b200 as L
+        if self.handle:
+            L.lib().llmcp_b200_tp_destroy(self.handle)
+            self.handle = None
