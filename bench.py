@@ -23,8 +23,12 @@ between steps).
          the same 1024-token context; its greedy tokens and logits are also what the GPU arm's
          are compared with (tokens_match_oracle, max_abs_logit_diff, min_top2_margin).
 
-N > 1 (torchrun): every rank holds a full replica and decodes its own sequence; no collective
-on the data path, so scaling is "weak" and value is the sum over ranks.
+N > 1 (torchrun): one sequence decoded by all N GPUs, tensor parallel inside the engine (every
+projection split by output rows, heads and state by head, the vocabulary projection by rows;
+exchanges are the library's own peer-store all-gather kernels, four per layer): scaling is
+"strong" and value is that one sequence's tokens/s.  The replica figure (a full engine and a
+sequence per GPU, no exchange on the data path, sum over ranks) is reported beside it under
+"replicas"; `--parallelism replicas` makes it the headline instead.
 
 `--impl reference` times the CPU oracle alone on the same workload and prints the same line; that
 arm loads no CUDA library.
@@ -372,6 +376,8 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--cpu-steps", type=int, default=16, help="decode steps of the CPU baseline sample")
     parser.add_argument("--mode", default="fast", choices=["fast", "exact"], help="arithmetic mode `value` is measured in")
+    parser.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
+                        help="N > 1: tp = one sequence over N GPUs (strong scaling, the default), replicas = one sequence per GPU")
     parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm", "attn"],
                         help="gemv / gemm / attn: run just that kernel on a small case (what the profiler captures)")
     args = parser.parse_args()
@@ -456,14 +462,23 @@ def main():
     sampler.wait_first_sample()
 
     # ---- device-resident arm, once per arithmetic mode ---------------------------------------
-    def device_arm(mode):
-        engine = L.Engine(arena.data, dims, capacity=capacity, device=local_rank, mode=mode)
+    # N > 1: one sequence decoded by all N GPUs (tensor parallel: every projection split by output
+    # rows, heads split by head, exchanges by the library's peer-store all-gather kernel); the
+    # replica throughput (one sequence per GPU, no exchange) is measured beside it.
+    tp = None
+    if world > 1 and args.parallelism == "tp":
+        from llmcp_b200 import parallel
+        tp = parallel.TensorParallel(dims, rank, world, local_rank, max_tokens=PREFILL)
+
+    def device_arm(mode, group):
+        engine = L.Engine(arena.data, dims, capacity=capacity, device=local_rank, mode=mode, tp=group, max_tokens=PREFILL)
         engine.forward(prompt, 0, want_logits=False)  # warm-up prefill (allocates the workspace)
         engine.reset()
         torch.cuda.synchronize()
+        barrier()
         t0 = time.perf_counter()
         first_logits, first = engine.forward(prompt, 0)
-        prefill_s = time.perf_counter() - t0
+        prefill_s = max_over_ranks(time.perf_counter() - t0)
         warm_tokens, _ = engine.generate(first, PREFILL, warmup)
         before = L.launch_count()
         barrier()
@@ -476,11 +491,26 @@ def main():
                 "tokens": [first] + warm_tokens.tolist() + tokens.tolist(), "first_logits": first_logits, "engine": engine}
 
     other = "exact" if args.mode == "fast" else "fast"
-    main_arm = device_arm(args.mode)
-    side_arm = device_arm(other)
+    main_arm = device_arm(args.mode, tp)
+    if world > 1:
+        main_arm.pop("engine").close()
+    side_arm = device_arm(other, tp)
     side_arm.pop("engine").close()
     device_ms, launches = main_arm["ms"], main_arm["launches"]
-    value = world * steps / (device_ms / 1e3)
+    sequences = 1 if tp is not None else world
+    value = sequences * steps / (device_ms / 1e3)
+    replicas = None
+    if tp is not None:
+        # One full engine per GPU, each with its own sequence: the no-exchange figure, and (exact
+        # mode) the single-GPU tokens the tensor-parallel ones have to equal.
+        replica_arm = device_arm(args.mode, None)
+        replica_arm.pop("engine").close()
+        replica_exact = replica_arm if args.mode == "exact" else device_arm("exact", None)
+        if replica_exact is not replica_arm:
+            replica_exact.pop("engine").close()
+        tp_exact = main_arm if args.mode == "exact" else side_arm
+        replicas = {"value": world * steps / (replica_arm["ms"] / 1e3), "unit": "tokens/s", "ms_per_step": replica_arm["ms"] / steps,
+                    "scaling": "weak", "tp_tokens_equal_single_gpu_exact_mode": tp_exact["tokens"] == replica_exact["tokens"]}
 
     # ---- against the CPU oracle on the same context (rank 0 of a one-GPU run) ----------------
     # The oracle's greedy chain from the same prompt, its logits at every position of the chain and
@@ -520,17 +550,26 @@ def main():
                                   "(OpenMP, all host threads)",
                         "prefill_tokens_per_second": PREFILL / run.prefill_s}
         run.close()
-    main_arm.pop("engine").close()
+    if "engine" in main_arm:
+        main_arm.pop("engine").close()
 
-    # ---- end-to-end arm through the AOT ABI --------------------------------------------------
-    L.set_mode(args.mode)
-    runtime = L.AotRuntime(dims)
-    assert runtime.init(max_sequence=capacity)
-    logits = np.zeros(dims.vocab, dtype=np.float32)  # one host row for every call, as llmcp-benchmark.cpp:84-101 keeps
-    runtime.forward(arena, prompt, 0, PREFILL, logits)
+    # ---- end-to-end arm ----------------------------------------------------------------------
+    # One GPU or replicas: through the AOT ABI entry points with host buffers, as tools/llmcp-benchmark
+    # calls them.  Tensor parallel: the engine's forward call on every rank (token in from the host,
+    # the assembled logits row out to the host, argmax on the host): the AOT ABI has no notion of ranks.
+    if tp is None:
+        L.set_mode(args.mode)
+        runtime = L.AotRuntime(dims)
+        assert runtime.init(max_sequence=capacity)
+        logits = np.zeros(dims.vocab, dtype=np.float32)  # one host row for every call, as llmcp-benchmark.cpp:84-101 keeps
+        step = lambda tokens, position: runtime.forward(arena, tokens, position, position + len(tokens), logits)
+    else:
+        e2e_engine = L.Engine(arena.data, dims, capacity=capacity, device=local_rank, mode=args.mode, tp=tp, max_tokens=PREFILL)
+        step = lambda tokens, position: e2e_engine.forward(tokens, position)[0]
+    logits = step(prompt, 0)
     pos = PREFILL
     for _ in range(warmup):
-        runtime.forward(arena, [int(np.argmax(logits))], pos, pos + 1, logits)
+        logits = step([int(np.argmax(logits))], pos)
         pos += 1
     barrier()
     sampler.open_window()
@@ -538,7 +577,7 @@ def main():
     e2e_tokens = []
     for _ in range(steps):
         e2e_tokens.append(int(np.argmax(logits)))
-        runtime.forward(arena, [e2e_tokens[-1]], pos, pos + 1, logits)
+        logits = step([e2e_tokens[-1]], pos)
         pos += 1
     torch.cuda.synchronize()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
@@ -547,8 +586,11 @@ def main():
     barrier()
     # e2e prefill: a fresh 1024-token call through the same entry point
     t0 = time.perf_counter()
-    runtime.forward(arena, prompt, 0, PREFILL)
+    step(prompt, 0)
     e2e_prefill_s = max_over_ranks(time.perf_counter() - t0)
+    if tp is not None:
+        e2e_engine.close()
+        tp.close()
     L.lib().llmcp_b200_release_all()
     if L.last_error():
         raise SystemExit("library error: " + L.last_error())
@@ -557,25 +599,31 @@ def main():
     bytes_per_step = 4.61e9  # weights 4.468 GB + recurrent state 0.101 GB + KV and logits
     result = {
         "metric": "decode_tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
-        "warmup": warmup, "ms_per_step": device_ms / steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": value / world / M2_DECODE_TOK_S, "dtype": "int8xint8->int32, f32 accumulate", "data": "synthetic",
-        "config": {"workload": workload, "mode": args.mode,
-                   "seed": SEED, "parallelism": f"replica x{world}" if world > 1 else "single GPU",
+        "warmup": warmup, "ms_per_step": device_ms / steps, "higher_is_better": True,
+        "scaling": "strong" if tp is not None else "weak",
+        "vs_baseline": value / sequences / M2_DECODE_TOK_S, "dtype": "int8xint8->int32, f32 accumulate", "data": "synthetic",
+        "config": {"workload": workload if tp is None else workload.replace("batch 1 per GPU", f"batch 1 over {world} GPUs"),
+                   "mode": args.mode, "seed": SEED,
+                   "parallelism": f"tp{world}: rows of every projection, heads and vocabulary split over {world} GPUs; "
+                                  "peer-store all-gather kernels, 4 per layer" if tp is not None
+                   else f"replica x{world}" if world > 1 else "single GPU",
                    "l2": "each step streams the 4.47 GB arena, far larger than L2; no flush needed",
                    "vs_baseline_is": "per-GPU value / 11.39 tok/s published for Apple M2 (reference README.md:140)"},
-        f"{other}_mode": {"value": world * steps / (side_arm["ms"] / 1e3), "unit": "tokens/s",
+        f"{other}_mode": {"value": sequences * steps / (side_arm["ms"] / 1e3), "unit": "tokens/s",
                           "ms_per_step": side_arm["ms"] / steps,
                           "prefill_tokens_per_second": PREFILL / side_arm["prefill_s"]},
-        "e2e": {"value": world * steps / e2e_s, "unit": "tokens/s", # one packet in: position, token, cos row, sin row; logits row, token and status word back
-                "h2d_bytes_per_step": 16 + 2 * dims.rotary * 4,
-                "d2h_bytes_per_step": dims.vocab * 4 + 16, "tokens_match_device_arm": bool(same)},
+        "e2e": {"value": sequences * steps / e2e_s, "unit": "tokens/s", # one packet in: position, token, cos row, sin row; logits row, token and status word back
+                "h2d_bytes_per_step": (16 + 2 * dims.rotary * 4) * world,
+                "d2h_bytes_per_step": (dims.vocab * 4 + 16) * world, "tokens_match_device_arm": bool(same)},
         "gpu_launches": int(launches) * world,
         "clocks": clocks,
         "prefill_tokens_per_second": {"tokens": PREFILL, "engine": PREFILL / main_arm["prefill_s"],
                                       "e2e_abi": PREFILL / e2e_prefill_s},
-        "whole_step_roofline": {"bytes_per_step": bytes_per_step,
-                                "achieved_gbs": bytes_per_step / (device_ms / steps / 1e3) / 1e9},
+        "whole_step_roofline": {"bytes_per_step": bytes_per_step, "gpus_sharing_the_bytes": 1 if tp is None else world,
+                                "achieved_gbs": bytes_per_step / (1 if tp is None else world) / (device_ms / steps / 1e3) / 1e9},
     }
+    if replicas:
+        result["replicas"] = replicas
     if check:
         result["parity"] = check
         result["tokens_match_oracle"] = check["tokens_match_oracle"]

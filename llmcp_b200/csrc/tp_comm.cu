@@ -31,7 +31,10 @@ struct GatherArgs {
 // fenced, before it.
 __global__ void __launch_bounds__(1024)
 tp_all_gather_kernel(const GatherArgs a) {
-  grid_dependency_sync(); // the pieces are written by the kernel in front
+  // The pieces are written by the kernel in front.  The kernel behind (usually a projection that
+  // reads the gathered rows) is released at once: it is placed and requests its weights while the
+  // exchange is under way, and reads the rows only after this kernel has finished.
+  grid_dependency_sync(true);
   const unsigned int number = *a.count_dev + 1;
   const int t = threadIdx.x;
   for (int g = 0; g < a.count; ++g) {
