@@ -249,6 +249,25 @@ void *llmcp_b200_engine_create(const uint8_t *file, uint64_t file_bytes, const l
 /* The same with an explicit arithmetic mode (see llmcp_b200_set_mode). */
 void *llmcp_b200_engine_create_mode(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims,
                                     int64_t capacity, int device, int mode);
+/* A batch of independent sequences (no counterpart in the reference, whose entry points take one
+ * sequence: lib/Model/ModelBuilder.cpp:72-81, 440-526).  The engine keeps recurrent state,
+ * convolution state and KV cache per sequence.  Sequences are prefilled one at a time:
+ * llmcp_b200_engine_select_sequence, then llmcp_b200_engine_forward / _read_state as for one sequence.
+ * Once all stand at the same position they are decoded together, one token each per step: the
+ * projections become one contraction of `batch` rows on the tensor cores (the weights stream
+ * from HBM once per step for all sequences), every other operator runs per sequence with the
+ * arithmetic of the one-sequence path, so each sequence's logits equal its own one-sequence run's
+ * (bit for bit in exact mode).
+ *   llmcp_b200_engine_decode_batch  : tokens[batch] at `position` -> argmax[batch] and, if not
+ *                                     null, logits[batch][vocab].
+ *   llmcp_b200_engine_generate_batch: greedy decoding on the device: out_tokens[steps][batch]. */
+void *llmcp_b200_engine_create_batch(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims, int64_t capacity,
+                                     int device, int mode, int batch);
+int llmcp_b200_engine_select_sequence(void *engine, int sequence);
+int llmcp_b200_engine_decode_batch(void *engine, const int64_t *tokens, int64_t position, float *logits, int64_t *argmax);
+int llmcp_b200_engine_generate_batch(void *engine, const int64_t *first_tokens, int64_t position, int64_t steps,
+                                     int64_t *out_tokens, float *device_ms);
+
 /* Tensor parallelism over the GPUs of one node (no counterpart in the reference, which is one
  * process on one device; what is split are the output rows of the linears that
  * lib/Model/ModelBuilder.cpp:218-319 builds, on the 8-row boundaries of

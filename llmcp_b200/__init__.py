@@ -72,6 +72,7 @@ def lib():
         handle.llmcp_b200_engine_create.restype = C.c_void_p
         handle.llmcp_b200_engine_create_mode.restype = C.c_void_p
         handle.llmcp_b200_engine_create_tp.restype = C.c_void_p
+        handle.llmcp_b200_engine_create_batch.restype = C.c_void_p
         handle.llmcp_b200_tp_create.restype = C.c_void_p
         handle.llmcp_b200_tp_slot_bytes.restype = C.c_uint64
         handle._mlir_ciface_llmcp_model_prefill.restype = None
@@ -476,14 +477,22 @@ class AotRuntime:
 class Engine:
     """Device-resident executor (llmcp_b200_engine_* in include/llmcp_b200.h)."""
 
-    def __init__(self, container, dims=None, capacity=1160, device=0, mode=None, tp=None, max_tokens=1024):
+    def __init__(self, container, dims=None, capacity=1160, device=0, mode=None, tp=None, max_tokens=1024, batch=1):
         """``tp``: a ``parallel.TensorParallel`` group; the engine then holds this rank's share of
-        the model and every rank has to make the same calls (see llmcp_b200_engine_create_tp)."""
+        the model and every rank has to make the same calls (see llmcp_b200_engine_create_tp).
+        ``batch``: number of independent sequences with state of their own (``select_sequence``,
+        ``decode_batch``, ``generate_batch``)."""
         self.dims = dims or default_dims()
         self.container = np.ascontiguousarray(container, dtype=np.uint8)
         self.capacity = capacity
         self.tp = tp
-        if tp is not None:
+        self.batch = int(batch)
+        if self.batch > 1:
+            mode_code = get_mode() if mode is None else mode
+            self.handle = lib().llmcp_b200_engine_create_batch(
+                _p(self.container), C.c_uint64(self.container.size), C.byref(self.dims), _i(capacity), int(device),
+                MODES[mode_code] if isinstance(mode_code, str) else int(mode_code), self.batch)
+        elif tp is not None:
             mode_code = get_mode() if mode is None else mode
             self.handle = lib().llmcp_b200_engine_create_tp(
                 _p(self.container), C.c_uint64(self.container.size), C.byref(self.dims), _i(capacity), int(device),
@@ -517,6 +526,29 @@ class Engine:
         _check(lib().llmcp_b200_engine_forward_all(self.handle, _p(tokens), _i(tokens.shape[0]), _i(position),
                                                    _p(logits)))
         return logits
+
+    def select_sequence(self, sequence):
+        """The sequence of the batch that forward / generate / read_state address from now on."""
+        _check(lib().llmcp_b200_engine_select_sequence(self.handle, int(sequence)))
+
+    def decode_batch(self, tokens, position, want_logits=True):
+        """One token of every sequence at a common position: (logits [batch, vocab] or None, argmax [batch])."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int64)
+        assert tokens.shape == (self.batch,)
+        logits = np.empty((self.batch, self.dims.vocab), dtype=np.float32) if want_logits else None
+        argmax = np.empty(self.batch, dtype=np.int64)
+        _check(lib().llmcp_b200_engine_decode_batch(self.handle, _p(tokens), _i(position), _p(logits), _p(argmax)))
+        return logits, argmax
+
+    def generate_batch(self, first_tokens, position, steps):
+        """Greedy decoding of all sequences on the device: (tokens [steps, batch], milliseconds)."""
+        first_tokens = np.ascontiguousarray(first_tokens, dtype=np.int64)
+        assert first_tokens.shape == (self.batch,)
+        out = np.empty((steps, self.batch), dtype=np.int64)
+        ms = C.c_float(0)
+        _check(lib().llmcp_b200_engine_generate_batch(self.handle, _p(first_tokens), _i(position), _i(steps), _p(out),
+                                                      C.byref(ms)))
+        return out, float(ms.value)
 
     def generate(self, first_token, position, steps):
         out = np.empty(steps, dtype=np.int64)

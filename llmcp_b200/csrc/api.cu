@@ -978,6 +978,43 @@ void *llmcp_b200_engine_create_tp(const uint8_t *file, uint64_t file_bytes, cons
   }
 }
 
+void *llmcp_b200_engine_create_batch(const uint8_t *file, uint64_t file_bytes, const llmcp_b200_dims *dims, int64_t capacity,
+                                     int device, int mode, int batch) {
+  try {
+    const ModelDims d = to_dims(dims);
+    check_dims(d);
+    if (mode != kModeExact && mode != kModeFast)
+      throw std::runtime_error("mode must be 0 (exact) or 1 (fast)");
+    return new Engine(file, file_bytes, d, capacity, device, mode, nullptr, 1024, batch);
+  } catch (const std::exception &e) {
+    set_error(e.what());
+    return nullptr;
+  }
+}
+
+int llmcp_b200_engine_select_sequence(void *engine, int sequence) {
+  return guarded_async([&] { static_cast<Engine *>(engine)->select_sequence(sequence); });
+}
+
+int llmcp_b200_engine_decode_batch(void *engine, const int64_t *tokens, int64_t position, float *logits, int64_t *argmax) {
+  return guarded_async([&] {
+    Engine &e = *static_cast<Engine *>(engine);
+    const uint64_t before = e.launches();
+    e.decode_batch(tokens, position, logits, argmax);
+    g_launches += e.launches() - before;
+  });
+}
+
+int llmcp_b200_engine_generate_batch(void *engine, const int64_t *first_tokens, int64_t position, int64_t steps,
+                                     int64_t *out_tokens, float *device_ms) {
+  return guarded_async([&] {
+    Engine &e = *static_cast<Engine *>(engine);
+    const uint64_t before = e.launches();
+    e.generate_batch(first_tokens, position, steps, out_tokens, device_ms);
+    g_launches += e.launches() - before;
+  });
+}
+
 int llmcp_b200_engine_local_dims(void *engine, llmcp_b200_dims *dims, int64_t *kv_head0) {
   return guarded_async([&] {
     Engine &e = *static_cast<Engine *>(engine);

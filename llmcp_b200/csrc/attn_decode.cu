@@ -52,7 +52,7 @@ template <int HD, int GROUP>
 __global__ void __launch_bounds__(kSplitThreads)
 attn_decode_split_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
                          const int64_t *__restrict__ position_ptr, int nkv, int64_t cap, int chunk, int splits,
-                         float *__restrict__ part_acc, float *__restrict__ part_ml) {
+                         float *__restrict__ part_acc, float *__restrict__ part_ml, int64_t cache_stride) {
   using Lay = SplitLayout<HD, GROUP>;
   constexpr int PD = Lay::PD, QS = Lay::QS, DG = Lay::DG, KG = Lay::KG, KPG = Lay::KPG;
   extern __shared__ __align__(16) float split_sm[];
@@ -63,6 +63,14 @@ attn_decode_split_kernel(const uint16_t *__restrict__ qn, const uint16_t *__rest
   grid_dependency_sync(true);
   const int total = static_cast<int>(*position_ptr) + 1;
   const int split = blockIdx.x, kvh = blockIdx.y;
+  { // blockIdx.z: sequence of a batch (one query token each, a cache per sequence)
+    const int64_t seq = blockIdx.z;
+    const int64_t heads = static_cast<int64_t>(nkv) * GROUP;
+    qn += seq * heads * HD;
+    cache += seq * cache_stride;
+    part_acc += seq * heads * splits * HD;
+    part_ml += seq * heads * splits * 2;
+  }
   const int begin = split * chunk;
   if (begin >= total)
     return; // the merge kernel reads the splits that hold keys only
@@ -209,7 +217,8 @@ attn_decode_merge_kernel(const float *__restrict__ part_acc, const float *__rest
                          const uint16_t *__restrict__ qg, const int64_t *__restrict__ position_ptr, int chunk,
                          int splits, uint16_t *__restrict__ out, int8_t *__restrict__ q_out,
                          float *__restrict__ s_out) {
-  const int h = blockIdx.x, d = threadIdx.x, lane = threadIdx.x & 31;
+  // blockIdx.y: sequence of a batch; its heads follow the previous sequence's in every buffer
+  const int h = blockIdx.y * gridDim.x + blockIdx.x, d = threadIdx.x, lane = threadIdx.x & 31;
   grid_dependency_sync(true);
   const float gate = bf16_to_f32(qg[static_cast<int64_t>(h) * 2 * HD + HD + d]);
   const int total = static_cast<int>(*position_ptr) + 1;
@@ -256,26 +265,28 @@ int fast_chunk(int64_t max_total, int nkv) {
 
 template <int HD, int GROUP>
 cudaError_t launch_split(const uint16_t *qn, const uint16_t *cache, const int64_t *position_dev, int nkv, int64_t cap,
-                         int chunk, int splits, float *part_acc, float *part_ml, cudaStream_t stream) {
+                         int chunk, int splits, float *part_acc, float *part_ml, cudaStream_t stream, int sequences,
+                         int64_t cache_stride) {
   using Lay = SplitLayout<HD, GROUP>;
   if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(attn_decode_split_kernel<HD, GROUP>), Lay::kBytes);
       e != cudaSuccess)
     return e;
-  launch_chained(attn_decode_split_kernel<HD, GROUP>, dim3(splits, nkv), dim3(kSplitThreads), Lay::kBytes, stream, qn, cache,
-                 position_dev, nkv, cap, chunk, splits, part_acc, part_ml);
+  launch_chained(attn_decode_split_kernel<HD, GROUP>, dim3(splits, nkv, sequences), dim3(kSplitThreads), Lay::kBytes, stream, qn,
+                 cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, cache_stride);
   return cudaGetLastError();
 }
 
 template <int HD>
 cudaError_t launch_split_hd(int group, const uint16_t *qn, const uint16_t *cache, const int64_t *position_dev, int nkv,
-                            int64_t cap, int chunk, int splits, float *part_acc, float *part_ml, cudaStream_t stream) {
+                            int64_t cap, int chunk, int splits, float *part_acc, float *part_ml, cudaStream_t stream,
+                            int sequences, int64_t cache_stride) {
   switch (group) {
   case 1:
-    return launch_split<HD, 1>(qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream);
+    return launch_split<HD, 1>(qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream, sequences, cache_stride);
   case 2:
-    return launch_split<HD, 2>(qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream);
+    return launch_split<HD, 2>(qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream, sequences, cache_stride);
   case 4:
-    return launch_split<HD, 4>(qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream);
+    return launch_split<HD, 4>(qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream, sequences, cache_stride);
   default:
     return cudaErrorNotSupported;
   }
@@ -290,12 +301,12 @@ bool attention_decode_fast_supported(int nh, int nkv, int hd) {
   return (hd == 128 || hd == 256) && (group == 1 || group == 2 || group == 4);
 }
 
-size_t attn_fast_scratch_bytes(int nh, int hd, int64_t max_position) {
+size_t attn_fast_scratch_bytes(int nh, int hd, int64_t max_position, int sequences) {
   const int64_t max_total = max_position + 1;
   // nkv is not known here: size for the smallest chunk the launcher can choose.
   const int64_t splits = (max_total + kSplitTile - 1) / kSplitTile;
-  const size_t qn_bytes = (static_cast<size_t>(nh) * hd * sizeof(uint16_t) + 255) / 256 * 256;
-  return qn_bytes + static_cast<size_t>(nh) * splits * (hd + 2) * sizeof(float) + 256;
+  const size_t qn_bytes = (static_cast<size_t>(sequences) * nh * hd * sizeof(uint16_t) + 255) / 256 * 256;
+  return qn_bytes + static_cast<size_t>(sequences) * nh * splits * (hd + 2) * sizeof(float) + 256;
 }
 
 cudaError_t launch_attention_decode_fast(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
@@ -303,33 +314,35 @@ cudaError_t launch_attention_decode_fast(const uint16_t *qg, const uint16_t *k, 
                                          const float *sin, int rows_from_position, uint16_t *cache,
                                          const int64_t *position_dev, int64_t max_position, int nh, int nkv, int hd,
                                          int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out,
-                                         float *s_out, cudaStream_t stream) {
+                                         float *s_out, cudaStream_t stream, int sequences, int64_t cache_stride) {
   if (!attention_decode_fast_supported(nh, nkv, hd))
     return cudaErrorNotSupported;
-  if (rot % 2 != 0 || rot > hd || max_position + 1 > cap)
+  if (rot % 2 != 0 || rot > hd || max_position + 1 > cap || sequences < 1 || (sequences > 1 && cache_stride == 0))
     return cudaErrorInvalidValue;
   const int64_t max_total = max_position + 1;
-  const int chunk = fast_chunk(max_total, nkv);
+  const int chunk = fast_chunk(max_total, nkv * sequences);
   const int splits = static_cast<int>((max_total + chunk - 1) / chunk);
   uint16_t *qn = static_cast<uint16_t *>(scratch);
-  const size_t qn_bytes = (static_cast<size_t>(nh) * hd * sizeof(uint16_t) + 255) / 256 * 256;
+  const size_t qn_bytes = (static_cast<size_t>(sequences) * nh * hd * sizeof(uint16_t) + 255) / 256 * 256;
   float *part_acc = reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + qn_bytes);
-  float *part_ml = part_acc + static_cast<size_t>(nh) * splits * hd;
-  if (cudaError_t e = launch_attention_prepare(qg, k, v, q_norm, k_norm, cos, sin, rows_from_position, cache, position_dev, 1,
-                                               nh, nkv, hd, rot, cap, qn, stream, 1);
+  float *part_ml = part_acc + static_cast<size_t>(sequences) * nh * splits * hd;
+  if (cudaError_t e = launch_attention_prepare(qg, k, v, q_norm, k_norm, cos, sin, rows_from_position, cache, position_dev,
+                                               sequences, nh, nkv, hd, rot, cap, qn, stream, 1, sequences > 1 ? cache_stride : 0);
       e != cudaSuccess)
     return e;
   const int group = nh / nkv;
-  cudaError_t e = hd == 256 ? launch_split_hd<256>(group, qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream)
-                            : launch_split_hd<128>(group, qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream);
+  cudaError_t e = hd == 256 ? launch_split_hd<256>(group, qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream,
+                                                   sequences, cache_stride)
+                            : launch_split_hd<128>(group, qn, cache, position_dev, nkv, cap, chunk, splits, part_acc, part_ml, stream,
+                                                   sequences, cache_stride);
   if (e != cudaSuccess)
     return e;
   if (hd == 256)
-    launch_chained(attn_decode_merge_kernel<256>, dim3(nh), dim3(256), 0, stream, part_acc, part_ml, qg, position_dev, chunk, splits,
-                   out, q_out, s_out);
+    launch_chained(attn_decode_merge_kernel<256>, dim3(nh, sequences), dim3(256), 0, stream, part_acc, part_ml, qg, position_dev, chunk,
+                   splits, out, q_out, s_out);
   else
-    launch_chained(attn_decode_merge_kernel<128>, dim3(nh), dim3(128), 0, stream, part_acc, part_ml, qg, position_dev, chunk, splits,
-                   out, q_out, s_out);
+    launch_chained(attn_decode_merge_kernel<128>, dim3(nh, sequences), dim3(128), 0, stream, part_acc, part_ml, qg, position_dev, chunk,
+                   splits, out, q_out, s_out);
   return cudaGetLastError();
 }
 

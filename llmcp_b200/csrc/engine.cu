@@ -111,11 +111,15 @@ size_t Engine::tp_slot_bytes(const ModelDims &d, int64_t max_tokens) {
 }
 
 Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode,
-               TpComm *tp, int64_t max_tokens)
-    : dims_(dims), local_(dims), tp_(tp), max_tokens_(max_tokens), capacity_(capacity), device_(device),
+               TpComm *tp, int64_t max_tokens, int batch)
+    : dims_(dims), local_(dims), tp_(tp), max_tokens_(max_tokens), batch_(batch), capacity_(capacity), device_(device),
       mode_(mode < 0 ? default_mode() : (mode == kModeFast ? kModeFast : kModeExact)) {
   if (capacity <= 0)
     throw std::runtime_error("capacity must be positive");
+  if (batch < 1 || batch > kArgmaxParts)
+    throw std::runtime_error("batch must be 1 .. " + std::to_string(kArgmaxParts));
+  if (batch > 1 && tp && tp->size() > 1)
+    throw std::runtime_error("a batch of sequences and tensor parallelism are not offered together");
   if (tp && tp->size() > 1) {
     tp_rank_ = tp->rank();
     tp_size_ = tp->size();
@@ -173,9 +177,14 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     allocations_.push_back(p);
     return p;
   };
-  kv_ = static_cast<uint16_t *>(alloc(kv_bytes));
-  delta_ = static_cast<float *>(alloc(delta_bytes));
-  conv_ = static_cast<uint16_t *>(alloc(conv_bytes));
+  kv_seq_ = kv_bytes / 2, delta_seq_ = delta_bytes / 4, conv_seq_ = conv_bytes / 2;
+  kv_ = static_cast<uint16_t *>(alloc(kv_bytes * batch_));
+  delta_ = static_cast<float *>(alloc(delta_bytes * batch_));
+  conv_ = static_cast<uint16_t *>(alloc(conv_bytes * batch_));
+  if (batch_ > 1) {
+    batch_logits_ = static_cast<float *>(alloc(static_cast<size_t>(batch_) * dims_.vocab * 4));
+    batch_tokens_ = static_cast<int64_t *>(alloc(static_cast<size_t>(batch_) * 8));
+  }
   cos_table_ = static_cast<float *>(alloc(static_cast<size_t>(capacity_) * c.rotary * 4));
   sin_table_ = static_cast<float *>(alloc(static_cast<size_t>(capacity_) * c.rotary * 4));
   {
@@ -471,38 +480,44 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   cudaFree(staging);
 }
 
+void Engine::select_sequence(int sequence) {
+  if (sequence < 0 || sequence >= batch_)
+    throw std::runtime_error("sequence " + std::to_string(sequence) + " outside the batch of " + std::to_string(batch_));
+  sequence_ = sequence;
+}
+
+// Clears the state of every sequence.
 void Engine::reset_state() {
-  const ModelDims &c = local_;
-  check(cudaMemsetAsync(kv_, 0, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, stream_), "memset");
-  check(cudaMemsetAsync(delta_, 0, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, stream_), "memset");
-  check(cudaMemsetAsync(conv_, 0, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, stream_), "memset");
+  check(cudaMemsetAsync(kv_, 0, kv_seq_ * 2 * batch_, stream_), "memset");
+  check(cudaMemsetAsync(delta_, 0, delta_seq_ * 4 * batch_, stream_), "memset");
+  check(cudaMemsetAsync(conv_, 0, conv_seq_ * 2 * batch_, stream_), "memset");
 }
 
 void Engine::upload_state(const uint16_t *kv, const float *delta, const uint16_t *conv) {
-  const ModelDims &c = local_;
-  check(cudaMemcpyAsync(kv_, kv, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, cudaMemcpyHostToDevice, stream_), "upload kv");
-  check(cudaMemcpyAsync(delta_, delta, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, cudaMemcpyHostToDevice, stream_), "upload delta");
-  check(cudaMemcpyAsync(conv_, conv, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, cudaMemcpyHostToDevice, stream_), "upload conv");
+  check(cudaMemcpyAsync(kv_ + sequence_ * kv_seq_, kv, kv_seq_ * 2, cudaMemcpyHostToDevice, stream_), "upload kv");
+  check(cudaMemcpyAsync(delta_ + sequence_ * delta_seq_, delta, delta_seq_ * 4, cudaMemcpyHostToDevice, stream_), "upload delta");
+  check(cudaMemcpyAsync(conv_ + sequence_ * conv_seq_, conv, conv_seq_ * 2, cudaMemcpyHostToDevice, stream_), "upload conv");
   check(cudaStreamSynchronize(stream_), "upload state");
 }
 
 void Engine::download_state(uint16_t *kv, float *delta, uint16_t *conv) {
-  const ModelDims &c = local_;
   if (kv)
-    check(cudaMemcpyAsync(kv, kv_, static_cast<size_t>(c.full_layers()) * 2 * c.kv_heads * capacity_ * c.head_dim * 2, cudaMemcpyDeviceToHost, stream_), "download kv");
+    check(cudaMemcpyAsync(kv, kv_ + sequence_ * kv_seq_, kv_seq_ * 2, cudaMemcpyDeviceToHost, stream_), "download kv");
   if (delta)
-    check(cudaMemcpyAsync(delta, delta_, static_cast<size_t>(c.linear_layers()) * c.lin_v_heads * c.lin_k_dim * c.lin_v_dim * 4, cudaMemcpyDeviceToHost, stream_), "download delta");
+    check(cudaMemcpyAsync(delta, delta_ + sequence_ * delta_seq_, delta_seq_ * 4, cudaMemcpyDeviceToHost, stream_), "download delta");
   if (conv)
-    check(cudaMemcpyAsync(conv, conv_, static_cast<size_t>(c.linear_layers()) * (c.conv_kernel - 1) * c.qkv_dim() * 2, cudaMemcpyDeviceToHost, stream_), "download conv");
+    check(cudaMemcpyAsync(conv, conv_ + sequence_ * conv_seq_, conv_seq_ * 2, cudaMemcpyDeviceToHost, stream_), "download conv");
   check(cudaStreamSynchronize(stream_), "download state");
 }
 
 void Engine::ensure_workspace(int64_t S, int64_t position) {
   const ModelDims &c = dims_;
   const ModelDims &m = local_;
+  // sized for tokens of one sequence and for one token each of S sequences (a batched step)
   const size_t need_attn =
       std::max(attn_scratch_bytes(S, static_cast<int>(m.heads), static_cast<int>(m.head_dim), position),
-               attn_fast_scratch_bytes(static_cast<int>(m.heads), static_cast<int>(m.head_dim), position + S - 1));
+               attn_fast_scratch_bytes(static_cast<int>(m.heads), static_cast<int>(m.head_dim), position + S - 1,
+                                       static_cast<int>(std::min<int64_t>(S, batch_))));
   if (S <= ws_tokens_ && need_attn <= attn_scratch_bytes_)
     return;
   if (tp_ && S > max_tokens_)
@@ -704,13 +719,22 @@ __global__ void tp_argmax_merge_kernel(const uint8_t *__restrict__ pairs, int si
 }
 
 void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const float *cos_dev, const float *sin_dev,
-                 int rows_from_position) {
+                 int rows_from_position, bool rows_are_sequences) {
   const ModelDims &c = dims_;
   const ModelDims &m = local_; // this rank's heads
   const int H = static_cast<int>(c.hidden);
-  if (S <= 0 || position < 0 || position + S > capacity_)
+  if (rows_are_sequences && (S != batch_ || all_logits_ || tp_))
+    throw std::runtime_error("a batched step takes one token of each of the engine's sequences");
+  // One-token kernels serve a single token and a batch of single tokens; state of the selected
+  // sequence, or of all of them side by side.
+  const bool one_token = S == 1 || rows_are_sequences;
+  const int sequences = rows_are_sequences ? static_cast<int>(S) : 1;
+  uint16_t *kv_base = kv_ + (rows_are_sequences ? 0 : sequence_ * kv_seq_);
+  float *delta_base = delta_ + (rows_are_sequences ? 0 : sequence_ * delta_seq_);
+  uint16_t *conv_base = conv_ + (rows_are_sequences ? 0 : sequence_ * conv_seq_);
+  if (S <= 0 || position < 0 || position + (rows_are_sequences ? 1 : S) > capacity_)
     throw std::runtime_error("sequence does not fit the cache: position " + std::to_string(position) + " + " +
-                             std::to_string(S) + " > capacity " + std::to_string(capacity_));
+                             std::to_string(rows_are_sequences ? 1 : S) + " > capacity " + std::to_string(capacity_));
   if (tp_ && all_logits_)
     throw std::runtime_error("all-position logits are not offered under tensor parallelism");
   ensure_workspace(S, position);
@@ -741,18 +765,33 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.b, b_, kBF16, kSigmoid}};
       run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status);
       const int C = static_cast<int>(m.qkv_dim());
-      uint16_t *conv_state = conv_ + lin_index * (c.conv_kernel - 1) * C;
-      float *delta_state = delta_ + lin_index * m.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
+      uint16_t *conv_state = conv_base + lin_index * (c.conv_kernel - 1) * C;
+      float *delta_state = delta_base + lin_index * m.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
       const int nk = static_cast<int>(m.lin_k_heads), nv = static_cast<int>(m.lin_v_heads);
       const int dk = static_cast<int>(c.lin_k_dim), dv = static_cast<int>(c.lin_v_dim);
       // a and b are computed for all heads on every rank; this rank's heads start at head0.
       const int nv_all = static_cast<int>(c.lin_v_heads), head0 = tp_rank_ * nv;
-      if (S == 1 && fuse_decode_mixer_ && gdn_decode_supported(static_cast<int>(c.conv_kernel), nk, nv, dk, dv)) {
+      const GdnBatch strides = {static_cast<int64_t>(conv_seq_), nv_all, static_cast<int64_t>(delta_seq_)};
+      if (one_token && fuse_decode_mixer_ && gdn_decode_supported(static_cast<int>(c.conv_kernel), nk, nv, dk, dv)) {
         check(launch_gdn_decode(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, static_cast<int>(c.conv_kernel),
                                 a_ + head0, b_ + head0, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype, delta_state,
                                 nk, nv, dk, dv, 1, z_, L.lin_norm.data, L.lin_norm.dtype, c.eps, 1, gdn_scratch_, convd_, nullptr,
-                                aq_, as_, stream_), "gated_delta_net (decode)");
+                                aq_, as_, stream_, sequences, &strides), "gated_delta_net (decode)");
         launches_ += 2;
+      } else if (rows_are_sequences) {
+        // Shapes the fused one-token kernels do not take: the general kernels, sequence by sequence.
+        const int64_t V = m.value_dim();
+        for (int64_t b = 0; b < S; ++b) {
+          check(launch_causal_conv1d(qkv_ + b * C, static_cast<const uint16_t *>(L.conv.data), conv_state + b * conv_seq_, 1, C,
+                                     static_cast<int>(c.conv_kernel), convd_ + b * C, stream_), "causal_conv1d");
+          check(launch_gated_delta_net(convd_ + b * C, a_ + b * nv_all + head0, b_ + b * nv_all + head0, L.a_log.data, L.a_log.dtype,
+                                       L.dt_bias.data, L.dt_bias.dtype, delta_state + b * delta_seq_, 1, nk, nv, dk, dv, 1,
+                                       gdn_scratch_, gdn_ + b * V, stream_, nv_all), "gated_delta_net");
+          launches_ += 4;
+        }
+        check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(V), dv, c.eps, 1, nullptr, aq_,
+                                    as_, stream_), "gated_rms_norm");
+        launches_ += 1;
       } else {
         check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, S, C,
                                    static_cast<int>(c.conv_kernel), convd_, stream_), "causal_conv1d");
@@ -767,18 +806,19 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
       run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status);
-      uint16_t *cache = kv_ + full_index * 2 * m.kv_heads * capacity_ * c.head_dim;
+      uint16_t *cache = kv_base + full_index * 2 * m.kv_heads * capacity_ * c.head_dim;
       const int nh = static_cast<int>(m.heads), nkv = static_cast<int>(m.kv_heads), hd = static_cast<int>(c.head_dim);
-      if (mode_ == kModeFast && S == 1 && attention_decode_fast_supported(nh, nkv, hd)) {
+      const int64_t cache_stride = rows_are_sequences ? static_cast<int64_t>(kv_seq_) : 0;
+      if (mode_ == kModeFast && one_token && attention_decode_fast_supported(nh, nkv, hd)) {
         check(launch_attention_decode_fast(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                            static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
                                            cache, position_dev_, position, nh, nkv, hd, static_cast<int>(c.rotary), capacity_,
-                                           attn_scratch_, attn_, aq_, as_, stream_), "attention (fast)");
+                                           attn_scratch_, attn_, aq_, as_, stream_, sequences, cache_stride), "attention (fast)");
       } else {
         check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position, cache,
                                position_dev_, position, S, nh, nkv, hd, static_cast<int>(c.rotary), capacity_, attn_scratch_,
-                               attn_, aq_, as_, stream_), "attention");
+                               attn_, aq_, as_, stream_, cache_stride), "attention");
       }
       launches_ += 3;
       gather_quant(S, m.attn_dim(), &mixer_q, &mixer_s);
@@ -809,6 +849,17 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     run_linears(planes, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags & kGemvOverlapPrevious,
                 S > 1 ? gemm_status : nullptr);
     launches_ += 1;
+  }
+  if (rows_are_sequences) {
+    // Every row is a sequence's last position: final norm and vocabulary projection of all rows,
+    // then one first maximum per row.
+    rms_norm(hidden_[cur], pending, S, final_norm_, nullptr, nullptr);
+    const LinearJob heads = {&embed_, batch_logits_, kF32, kNone};
+    run_linears(planes, aq_, as_, S, &heads, 1, stream_, &launches_, gemv_flags & kGemvOverlapPrevious, gemm_status);
+    launch_argmax(batch_logits_, c.vocab, argmax_v_, argmax_i_, 0, batch_tokens_, nullptr, stream_, static_cast<int>(S));
+    launches_ += 3;
+    check(cudaGetLastError(), "forward");
+    return;
   }
   // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
   const uint16_t *last = hidden_[cur] + (S - 1) * H;
@@ -929,6 +980,96 @@ void Engine::forward_all_host(const int64_t *tokens, int64_t S, int64_t position
     throw;
   }
   cudaFree(device_rows);
+  check_status();
+}
+
+namespace {
+
+// After a batched step: every sequence's argmax becomes its next input, is recorded, and the
+// common position advances.
+__global__ void advance_batch_kernel(const int64_t *__restrict__ next, int64_t *__restrict__ tokens, int64_t *__restrict__ generated,
+                                     int64_t *__restrict__ step, int64_t *__restrict__ position, int batch) {
+  grid_dependency_sync();
+  const int b = threadIdx.x;
+  const int64_t at = *step;
+  if (b < batch) {
+    tokens[b] = next[b];
+    generated[at * batch + b] = next[b];
+  }
+  __syncthreads();
+  if (b == 0) {
+    *step = at + 1;
+    *position += 1;
+  }
+}
+
+} // namespace
+
+void Engine::decode_batch(const int64_t *tokens_host, int64_t position, float *logits_host, int64_t *argmax_host) {
+  check(cudaSetDevice(device_), "cudaSetDevice");
+  if (batch_ < 2)
+    throw std::runtime_error("decode_batch needs an engine created with a batch of sequences");
+  if (position < 0 || position + 1 > capacity_)
+    throw std::runtime_error("position does not fit the cache");
+  validate_tokens(tokens_host, batch_);
+  ensure_workspace(batch_, position);
+  set_position(position);
+  check(cudaMemcpyAsync(tokens_, tokens_host, static_cast<size_t>(batch_) * 8, cudaMemcpyHostToDevice, stream_), "tokens");
+  run(tokens_, batch_, position, cos_table_, sin_table_, 1, true);
+  if (logits_host)
+    check(cudaMemcpyAsync(logits_host, batch_logits_, static_cast<size_t>(batch_) * dims_.vocab * 4, cudaMemcpyDeviceToHost, stream_),
+          "logits");
+  if (argmax_host)
+    check(cudaMemcpyAsync(argmax_host, batch_tokens_, static_cast<size_t>(batch_) * 8, cudaMemcpyDeviceToHost, stream_), "argmax");
+  check(cudaMemcpyAsync(token_pinned_, next_token_, 16, cudaMemcpyDeviceToHost, stream_), "status");
+  check(cudaStreamSynchronize(stream_), "decode_batch");
+  check_status();
+}
+
+void Engine::generate_batch(const int64_t *first_tokens_host, int64_t position, int64_t steps, int64_t *out_tokens_host,
+                            float *device_ms) {
+  check(cudaSetDevice(device_), "cudaSetDevice");
+  if (batch_ < 2)
+    throw std::runtime_error("generate_batch needs an engine created with a batch of sequences");
+  if (steps <= 0 || position < 0 || position + steps > capacity_)
+    throw std::runtime_error("generation does not fit the cache");
+  validate_tokens(first_tokens_host, batch_);
+  ensure_workspace(batch_, position + steps - 1);
+  set_position(position);
+  check(cudaMemcpyAsync(tokens_, first_tokens_host, static_cast<size_t>(batch_) * 8, cudaMemcpyHostToDevice, stream_), "tokens");
+  check(cudaMemsetAsync(step_dev_, 0, 8, stream_), "step counter");
+  int64_t *generated = nullptr;
+  check(cudaMalloc(&generated, static_cast<size_t>(steps) * batch_ * 8), "cudaMalloc(generated tokens)");
+  cudaEvent_t begin = nullptr, end = nullptr;
+  try {
+    check(cudaEventCreate(&begin), "event");
+    check(cudaEventCreate(&end), "event");
+    check(cudaEventRecord(begin, stream_), "event");
+    for (int64_t i = 0; i < steps; ++i) {
+      run(tokens_, batch_, position + i, cos_table_, sin_table_, 1, true);
+      launch_chained(advance_batch_kernel, dim3(1), dim3((batch_ + 31) / 32 * 32), 0, stream_, batch_tokens_, tokens_, generated,
+                     step_dev_, position_dev_, batch_);
+      launches_ += 1;
+    }
+    check(cudaEventRecord(end, stream_), "event");
+    check(cudaMemcpyAsync(token_pinned_, next_token_, 16, cudaMemcpyDeviceToHost, stream_), "status");
+    check(cudaStreamSynchronize(stream_), "generate_batch");
+    if (device_ms)
+      check(cudaEventElapsedTime(device_ms, begin, end), "event");
+    if (out_tokens_host)
+      check(cudaMemcpy(out_tokens_host, generated, static_cast<size_t>(steps) * batch_ * 8, cudaMemcpyDeviceToHost), "tokens");
+  } catch (...) {
+    if (begin)
+      cudaEventDestroy(begin);
+    if (end)
+      cudaEventDestroy(end);
+    cudaStreamSynchronize(stream_);
+    cudaFree(generated);
+    throw;
+  }
+  cudaEventDestroy(begin);
+  cudaEventDestroy(end);
+  cudaFree(generated);
   check_status();
 }
 

@@ -66,8 +66,13 @@ public:
   // attention heads (KV heads are duplicated when G exceeds their number) and 1/G of the
   // vocabulary projection; every rank must make the same calls.  max_tokens bounds the rows of one
   // call under tensor parallelism (the exchange slots are sized for it).
+  // batch: number of independent sequences the engine keeps state for (1: the reference's case).
+  // Sequences are prefilled one at a time (forward_host after select_sequence) and can then be
+  // decoded together, one token each per step, at a common position (decode_batch / generate_batch):
+  // the projections then run as one contraction of `batch` rows on the tensor cores, recurrent state,
+  // convolution state and KV cache stay per sequence.
   Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, int64_t capacity, int device, int mode = -1,
-         TpComm *tp = nullptr, int64_t max_tokens = 1024);
+         TpComm *tp = nullptr, int64_t max_tokens = 1024, int batch = 1);
   // Bytes per exchange slot an engine with these dimensions needs for calls of up to max_tokens rows.
   static size_t tp_slot_bytes(const ModelDims &dims, int64_t max_tokens);
   // Why these dimensions cannot be split over `size` ranks, or "" if they can.
@@ -88,6 +93,18 @@ public:
   int mode() const { return mode_; }
   cudaStream_t stream() const { return stream_; }
 
+  int batch() const { return batch_; }
+  // The sequence whose state forward_host / forward_all_host / generate / upload_state /
+  // download_state address (0 after construction).
+  void select_sequence(int sequence);
+  // One token of every sequence, all at `position`: tokens_host[batch] in; the argmax of every
+  // sequence's logits to argmax_host[batch] and, if not null, the logits rows to
+  // logits_host[batch][vocab].
+  void decode_batch(const int64_t *tokens_host, int64_t position, float *logits_host, int64_t *argmax_host);
+  // Greedy decoding of all sequences on the device for `steps` steps from `position`:
+  // out_tokens_host[steps][batch]; device_ms, if not null, the CUDA-event time of the loop.
+  void generate_batch(const int64_t *first_tokens_host, int64_t position, int64_t steps, int64_t *out_tokens_host,
+                      float *device_ms);
   void reset_state();
   // Host <-> device copies of the three state buffers in the reference's layouts:
   // kv [full, 2, kv_heads, capacity, head_dim] bf16, delta [linear, v_heads, k_dim, v_dim] f32,
@@ -127,8 +144,9 @@ private:
   // Enqueues one forward over S tokens whose ids are at tokens_dev.  The start position is read
   // from position_dev_ by the kernels; max_position bounds it (grid and scratch sizing).  cos/sin
   // are the rows of this call, or tables over all positions when rows_from_position is set.
+  // rows_are_sequences: the S rows are one token each of the engine's `batch` sequences (S == batch).
   void run(const int64_t *tokens_dev, int64_t S, int64_t max_position, const float *cos_dev, const float *sin_dev,
-           int rows_from_position);
+           int rows_from_position, bool rows_are_sequences = false);
   void set_position(int64_t position);
   // The single-token forward over the staging buffers (tokens_, cos_, sin_, position_dev_),
   // captured once as a CUDA graph and replayed for every decode step.
@@ -147,6 +165,10 @@ private:
   int64_t max_tokens_ = 1024;
   int64_t kv_head0_ = 0;   // first KV head of this rank
   int64_t hidden_rows_ = 0, inter_rows_ = 0, vocab_rows_ = 0, vocab_row0_ = 0; // this rank's output rows
+  int batch_ = 1, sequence_ = 0;
+  size_t kv_seq_ = 0, delta_seq_ = 0, conv_seq_ = 0; // elements of one sequence's state buffers
+  float *batch_logits_ = nullptr;   // [batch][vocab] logits of a batched step
+  int64_t *batch_tokens_ = nullptr; // [batch] argmax of a batched step (device)
   int exchange_ = 0;       // exchanges issued so far by the running forward (slot rule of TpComm)
   bool gather_logits_ = false; // tensor parallel: the next forward also assembles the full logits row
   Q8Weight lm_head_;       // the rows of the tied table this rank multiplies (a view into embed_)

@@ -97,9 +97,10 @@ cudaError_t launch_gemm_q8_tc16(const void *ah, const float *ast, int M, int K, 
                                 uint32_t spin_limit = 0, int fault = 0);
 void launch_embedding_q8(const int64_t *tokens, int64_t S, int64_t hidden, int64_t vocab, const int8_t *wq,
                          const uint16_t *wd, uint16_t *out, int *status, cudaStream_t stream);
-// scratch_v / scratch_i: kArgmaxParts entries each.
+// scratch_v / scratch_i: kArgmaxParts entries each.  rows > 1: x is [rows, n], one first maximum per
+// row into out_index[row] (out_value[row]); rows <= kArgmaxParts.
 void launch_argmax(const float *x, int64_t n, float *scratch_v, int64_t *scratch_i, int64_t index_base,
-                   int64_t *out_index, float *out_value, cudaStream_t stream);
+                   int64_t *out_index, float *out_value, cudaStream_t stream, int rows = 1);
 
 cudaError_t launch_rms_norm(const uint16_t *a, const uint16_t *b, int64_t M, int H, const void *w, int w_dtype,
                             float eps, int zero_centered, uint16_t *sum_out, uint16_t *y, int8_t *q, float *s,
@@ -123,6 +124,13 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
                                    int a_log_dtype, const void *dt_bias, int dt_dtype, float *state, int64_t S,
                                    int nk, int nv, int dk, int dv, int b_activated, float *scratch,
                                    uint16_t *out, cudaStream_t stream, int ab_stride = 0 /* row pitch of a and b; 0 = nv */);
+// A batch of independent sequences, one token each, through the one-token kernels: element strides
+// between consecutive sequences' buffers (inputs and outputs are rows of a [sequences, width] matrix).
+struct GdnBatch {
+  int64_t conv_state; // convolution state of a layer
+  int64_t ab;         // a and b rows
+  int64_t state;      // recurrent state of a layer
+};
 // One token of causal_conv1d + gated_delta_net + gated_rms_norm (+ quantisation) in two launches;
 // the same values as the three general launchers above produce.  scratch: gdn_scratch_floats(1, ..).
 bool gdn_decode_supported(int kernel, int nk, int nv, int dk, int dv);
@@ -131,17 +139,19 @@ cudaError_t launch_gdn_decode(const uint16_t *qkv, const uint16_t *conv_w, uint1
                               const void *dt_bias, int dt_dtype, float *state, int nk, int nv, int dk, int dv,
                               int b_activated, const uint16_t *gate, const void *norm_w, int norm_w_dtype, float eps,
                               int gate_activated, float *scratch, uint16_t *conv_out, uint16_t *y, int8_t *q_out,
-                              float *s_out, cudaStream_t stream);
+                              float *s_out, cudaStream_t stream, int sequences = 1, const GdnBatch *strides = nullptr);
 // The start position is read from device memory (position_dev) so that a captured launch can be
 // replayed at another position; max_position bounds it (grid and scratch are sized for it).
 // rows_from_position: cos/sin are tables indexed by absolute position instead of the call's rows.
+// cache_stride != 0: the S rows are one token each of S independent sequences, all at the same
+// position, row t using the cache cache_stride elements behind row t - 1's (batched decode).
 // q_out / s_out (optional): int8 quantisation of the output for the linear that follows.
 size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t max_position);
 cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
                              const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
                              uint16_t *cache, const int64_t *position_dev, int64_t max_position, int64_t S, int nh,
                              int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out,
-                             float *s_out, cudaStream_t stream);
+                             float *s_out, cudaStream_t stream, int64_t cache_stride = 0);
 
 // The first of the three attention launches alone: q/k RMSNorm, partial RoPE, q -> qn scratch
 // (bf16 [S, nh, hd]), k and v -> cache rows position .. position + S - 1.  tree_sum (fast mode):
@@ -149,19 +159,20 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
 cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
                                      const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
                                      uint16_t *cache, const int64_t *position_dev, int64_t S, int nh, int nkv, int hd,
-                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream, int tree_sum = 0);
+                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream, int tree_sum = 0,
+                                     int64_t cache_stride = 0);
 // Fast mode of the one-token attention: after the same prepare kernel, the key range is split
 // over CTAs (each keeps a running maximum, denominator and weighted value sum for the query
 // heads of one KV head) and a second kernel merges the splits, applies the sigmoid gate and
 // quantises for o_proj.  The softmax is the same function as the reference's tile-ordered one
 // but sums in another order, so results agree to f32 rounding, not bit for bit.
 bool attention_decode_fast_supported(int nh, int nkv, int hd);
-size_t attn_fast_scratch_bytes(int nh, int hd, int64_t max_position);
+size_t attn_fast_scratch_bytes(int nh, int hd, int64_t max_position, int sequences = 1);
 cudaError_t launch_attention_decode_fast(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
                                          const uint16_t *q_norm, const uint16_t *k_norm, const float *cos,
                                          const float *sin, int rows_from_position, uint16_t *cache,
                                          const int64_t *position_dev, int64_t max_position, int nh, int nkv, int hd,
                                          int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out,
-                                         float *s_out, cudaStream_t stream);
+                                         float *s_out, cudaStream_t stream, int sequences = 1, int64_t cache_stride = 0);
 
 } // namespace llmcp_b200

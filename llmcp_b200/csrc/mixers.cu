@@ -437,13 +437,23 @@ gdn_decode_front_kernel(const uint16_t *__restrict__ x, const uint16_t *__restri
                         const void *__restrict__ a_log, int a_log_dtype, const void *__restrict__ dt_bias,
                         int dt_dtype, int nk, int nv, int dk, int dv, int b_activated, float *__restrict__ qn,
                         float *__restrict__ kn, float *__restrict__ beta, float *__restrict__ decay,
-                        uint16_t *__restrict__ conv_out) {
+                        uint16_t *__restrict__ conv_out, const GdnBatch batch) {
   extern __shared__ __align__(16) float front_sm[]; // dk squares
   __shared__ float scale_sm;
   grid_dependency_sync(true); // the step kernel behind is placed now and fetches its state meanwhile
   const int t = threadIdx.x;
   const int role = blockIdx.x;
   const int C = 2 * nk * dk + nv * dv;
+  { // blockIdx.y: sequence of a batch of independent sequences (one token each)
+    const int64_t seq = blockIdx.y;
+    x += seq * C;
+    conv_out += seq * C;
+    state += seq * batch.conv_state;
+    a += seq * batch.ab;
+    b += seq * batch.ab;
+    const int64_t scratch = seq * (2 * static_cast<int64_t>(nk) * dk + 2 * nv);
+    qn += scratch, kn += scratch, beta += scratch, decay += scratch;
+  }
   const int value_ctas = (nv * dv + dk - 1) / dk;
   if (role < 2 * nk) {
     const bool is_q = role < nk;
@@ -500,12 +510,20 @@ gdn_decode_step_kernel(const uint16_t *__restrict__ conv, const float *__restric
                        const float *__restrict__ beta, const float *__restrict__ decay, float *__restrict__ state,
                        int nk, int nv, int dv, const uint16_t *__restrict__ gate, const void *__restrict__ norm_w,
                        int norm_w_dtype, float eps, int gate_activated, uint16_t *__restrict__ y,
-                       int8_t *__restrict__ q_out, float *__restrict__ s_out) {
+                       int8_t *__restrict__ q_out, float *__restrict__ s_out, const GdnBatch batch) {
   extern __shared__ __align__(16) float step_sm[]; // kn[DK], qn[DK], squares[dv]
   __shared__ float rstd_sm;
   float *k_sm = step_sm, *q_sm = step_sm + DK, *sq_sm = step_sm + 2 * DK;
   const int h = blockIdx.x, v = threadIdx.x;
   const int kh = h / (nv / nk);
+  const int64_t seq = blockIdx.y; // sequence of a batch (one token each)
+  {
+    conv += seq * (2 * static_cast<int64_t>(nk) * DK + static_cast<int64_t>(nv) * dv);
+    const int64_t scratch = seq * (2 * static_cast<int64_t>(nk) * DK + 2 * nv);
+    qn += scratch, kn += scratch, beta += scratch, decay += scratch;
+    state += seq * batch.state;
+    gate += seq * static_cast<int64_t>(nv) * dv;
+  }
   float *col = state + static_cast<int64_t>(h) * DK * dv + v;
   // The recurrent state is this kernel's own (written by the same kernel one token earlier, which
   // finished long ago): it is requested before waiting for the kernel in front.
@@ -564,7 +582,7 @@ gdn_decode_step_kernel(const uint16_t *__restrict__ conv, const float *__restric
     rstd_sm = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(dv)), eps));
   }
   __syncthreads();
-  const int64_t element = static_cast<int64_t>(h) * dv + v;
+  const int64_t element = (seq * nv + h) * dv + v;
   const float silu = gate_activated ? gv : __fmul_rn(gv, d_sigmoid(gv));
   float t = __fmul_rn(xo, silu);
   t = __fmul_rn(t, norm_weight);
@@ -586,19 +604,20 @@ cudaError_t launch_gdn_decode(const uint16_t *qkv, const uint16_t *conv_w, uint1
                               const void *dt_bias, int dt_dtype, float *state, int nk, int nv, int dk, int dv,
                               int b_activated, const uint16_t *gate, const void *norm_w, int norm_w_dtype, float eps,
                               int gate_activated, float *scratch, uint16_t *conv_out, uint16_t *y, int8_t *q_out,
-                              float *s_out, cudaStream_t stream) {
-  if (!gdn_decode_supported(kernel, nk, nv, dk, dv))
+                              float *s_out, cudaStream_t stream, int sequences, const GdnBatch *strides) {
+  if (!gdn_decode_supported(kernel, nk, nv, dk, dv) || sequences < 1 || (sequences > 1 && !strides))
     return cudaErrorInvalidValue;
+  const GdnBatch batch = strides ? *strides : GdnBatch{};
   float *qn = scratch;
   float *kn = qn + nk * dk;
   float *beta = kn + nk * dk;
   float *decay = beta + nv;
   const int ctas = 2 * nk + (nv * dv + dk - 1) / dk + 1;
-  launch_chained(gdn_decode_front_kernel, dim3(ctas), dim3(dk), dk * sizeof(float), stream, qkv, conv_w,
+  launch_chained(gdn_decode_front_kernel, dim3(ctas, sequences), dim3(dk), dk * sizeof(float), stream, qkv, conv_w,
                  conv_state, kernel, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, nk, nv, dk, dv, b_activated, qn, kn, beta,
-                 decay, conv_out);
-  launch_chained(gdn_decode_step_kernel<128>, dim3(nv), dim3(dv), (2 * 128 + dv) * sizeof(float), stream, conv_out, qn, kn,
-                 beta, decay, state, nk, nv, dv, gate, norm_w, norm_w_dtype, eps, gate_activated, y, q_out, s_out);
+                 decay, conv_out, batch);
+  launch_chained(gdn_decode_step_kernel<128>, dim3(nv, sequences), dim3(dv), (2 * 128 + dv) * sizeof(float), stream, conv_out, qn,
+                 kn, beta, decay, state, nk, nv, dv, gate, norm_w, norm_w_dtype, eps, gate_activated, y, q_out, s_out, batch);
   return cudaGetLastError();
 }
 
@@ -616,7 +635,8 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
                                     const uint16_t *__restrict__ k_norm, const float *__restrict__ cos,
                                     const float *__restrict__ sin, uint16_t *__restrict__ cache,
                                     const int64_t *__restrict__ position_ptr, int rows_from_position, int64_t S,
-                                    int nh, int nkv, int hd, int rot, int64_t cap, uint16_t *__restrict__ qn, int tree_sum) {
+                                    int nh, int nkv, int hd, int rot, int64_t cap, uint16_t *__restrict__ qn, int tree_sum,
+                                    int64_t cache_stride) {
   extern __shared__ float prep_sm[]; // per warp: hd values
   grid_dependency_sync();
   const int64_t position = *position_ptr;
@@ -629,6 +649,10 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
   if (item >= S * per_token)
     return;
   const int64_t t = item / per_token;
+  // cache_stride != 0: the rows are one token each of independent sequences at the same position,
+  // row t with a cache of its own cache_stride elements further on; else tokens of one sequence.
+  const int64_t tpos = cache_stride ? 0 : t;
+  cache += t * cache_stride;
   const int which = static_cast<int>(item % per_token);
   const bool is_q = which < nh;
   const int head = is_q ? which : which - nh;
@@ -636,7 +660,7 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
                              : k + t * nkv * hd + static_cast<int64_t>(head) * hd;
   const uint16_t *weight = is_q ? q_norm : k_norm;
   uint16_t *dst = is_q ? qn + (t * nh + head) * hd
-                       : cache + ((0 * static_cast<int64_t>(nkv) + head) * cap + position + t) * hd;
+                       : cache + ((0 * static_cast<int64_t>(nkv) + head) * cap + position + tpos) * hd;
   float *tmp = prep_sm + warp_in_cta * hd;
   // Everything the later passes read from memory (norm weight, rotary rows, the value row to be
   // copied) is requested here, beside the input row, instead of after the serial sum.
@@ -656,8 +680,8 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
         if (!is_q)
           v_reg[i] = vsrc[d];
         if (d < rot) {
-          cos_reg[i] = cos[(row_base + t) * rot + d];
-          sin_reg[i] = sin[(row_base + t) * rot + d];
+          cos_reg[i] = cos[(row_base + tpos) * rot + d];
+          sin_reg[i] = sin[(row_base + tpos) * rot + d];
         }
       }
     }
@@ -713,7 +737,7 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
   }
   __syncwarp();
   const int half = rot / 2;
-  uint16_t *vdst = cache + ((1 * static_cast<int64_t>(nkv) + head) * cap + position + t) * hd;
+  uint16_t *vdst = cache + ((1 * static_cast<int64_t>(nkv) + head) * cap + position + tpos) * hd;
   if (prefetched) {
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
@@ -737,7 +761,7 @@ __global__ void attn_prepare_kernel(const uint16_t *__restrict__ qg, const uint1
     if (d < rot) {
       const bool second = d >= half;
       const float rotated = __fmul_rn(second ? 1.0f : -1.0f, tmp[second ? d - half : d + half]);
-      r = __fadd_rn(__fmul_rn(tmp[d], cos[(row_base + t) * rot + d]), __fmul_rn(rotated, sin[(row_base + t) * rot + d]));
+      r = __fadd_rn(__fmul_rn(tmp[d], cos[(row_base + tpos) * rot + d]), __fmul_rn(rotated, sin[(row_base + tpos) * rot + d]));
     }
     dst[d] = f32_to_bf16(r);
   }
@@ -754,14 +778,15 @@ constexpr int kValueStages = 6; // stages in flight: 6 x 32 x 256 x 2 B = 96 KB 
 // grid: (key tile, kv head, token); block: group * 64 threads (query head x key).
 __global__ void attn_scores_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
                                    const int64_t *__restrict__ position_ptr, int nh, int nkv, int hd, int64_t cap,
-                                   int64_t score_stride, float *__restrict__ scores) {
+                                   int64_t score_stride, float *__restrict__ scores, int64_t cache_stride) {
   extern __shared__ __align__(16) unsigned char att_sm[];
   grid_dependency_sync();
   const int64_t position = *position_ptr;
   const int group = nh / nkv;
   const int64_t t = blockIdx.z;
   const int kvh = blockIdx.y;
-  const int64_t query_end = position + t + 1;
+  cache += t * cache_stride; // rows of independent sequences: a cache per row, every row at `position`
+  const int64_t query_end = position + (cache_stride ? 0 : t) + 1;
   const int64_t start = static_cast<int64_t>(blockIdx.x) * kKeyTile;
   if (start >= query_end)
     return;
@@ -816,14 +841,15 @@ constexpr int kScoreKeys = 32;
 __global__ void __launch_bounds__(256)
 attn_scores_keys32_kernel(const uint16_t *__restrict__ qn, const uint16_t *__restrict__ cache,
                           const int64_t *__restrict__ position_ptr, int nh, int nkv, int hd, int64_t cap,
-                          int64_t score_stride, float *__restrict__ scores) {
+                          int64_t score_stride, float *__restrict__ scores, int64_t cache_stride) {
   extern __shared__ __align__(16) unsigned char att_sm[];
   grid_dependency_sync();
   const int64_t position = *position_ptr;
   const int group = nh / nkv;
   const int64_t t = blockIdx.z;
   const int kvh = blockIdx.y;
-  const int64_t query_end = position + t + 1;
+  cache += t * cache_stride; // rows of independent sequences: a cache per row, every row at `position`
+  const int64_t query_end = position + (cache_stride ? 0 : t) + 1;
   const int64_t start = static_cast<int64_t>(blockIdx.x) * kScoreKeys;
   if (start >= query_end)
     return;
@@ -1019,7 +1045,7 @@ __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint
                                     const uint16_t *__restrict__ qg, const int64_t *__restrict__ position_ptr,
                                     int nh, int nkv, int hd, int64_t cap, int64_t score_stride,
                                     uint16_t *__restrict__ out, int8_t *__restrict__ q_out,
-                                    float *__restrict__ s_out) {
+                                    float *__restrict__ s_out, int64_t cache_stride) {
   extern __shared__ __align__(16) float comb_sm[];
   grid_dependency_sync(true);
   const int64_t position = *position_ptr;
@@ -1028,7 +1054,8 @@ __global__ void attn_combine_kernel(const float *__restrict__ scores, const uint
   const int kvh = h / (nh / nkv);
   const int d = threadIdx.x;
   const bool active = d < hd;
-  const int total = static_cast<int>(position + t + 1);
+  cache += t * cache_stride; // rows of independent sequences: a cache per row, every row at `position`
+  const int total = static_cast<int>(position + (cache_stride ? 0 : t) + 1);
   const int tiles = (total + kKeyTile - 1) / kKeyTile;
   float *p_sm = comb_sm;
   float *m_sm = comb_sm + (static_cast<int>(score_stride) + 3) / 4 * 4;
@@ -1455,12 +1482,12 @@ size_t attn_scratch_bytes(int64_t S, int nh, int hd, int64_t max_position) {
 cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
                                      const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
                                      uint16_t *cache, const int64_t *position_dev, int64_t S, int nh, int nkv, int hd,
-                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream, int tree_sum) {
+                                     int rot, int64_t cap, uint16_t *qn, cudaStream_t stream, int tree_sum, int64_t cache_stride) {
   const int64_t items = S * (nh + nkv);
   const int prepare_warps = items <= 64 ? 1 : 4; // decode: a CTA per head
   launch_chained(attn_prepare_kernel, dim3(static_cast<unsigned>((items + prepare_warps - 1) / prepare_warps)),
                  dim3(32 * prepare_warps), prepare_warps * hd * sizeof(float), stream, qg, k, v, q_norm, k_norm, cos, sin, cache,
-                 position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn, tree_sum);
+                 position_dev, rows_from_position, S, nh, nkv, hd, rot, cap, qn, tree_sum, cache_stride);
   return cudaGetLastError();
 }
 
@@ -1469,12 +1496,12 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
                              const float *sin, int rows_from_position, uint16_t *cache,
                              const int64_t *position_dev, int64_t max_position, int64_t S, int nh, int nkv,
                              int hd, int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out, float *s_out,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, int64_t cache_stride) {
   if (S == 0)
     return cudaSuccess;
   if (q_out && hd % kBlock != 0)
     return cudaErrorInvalidValue;
-  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || rot % 2 != 0 || rot > hd || max_position + S > cap)
+  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || rot % 2 != 0 || rot > hd || max_position + (cache_stride ? 1 : S) > cap)
     return cudaErrorInvalidValue;
   const int group = nh / nkv;
   if (group * kKeyTile > 1024 || hd > 1024)
@@ -1485,7 +1512,7 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   const int64_t score_stride = max_position + S;
 
   if (cudaError_t e = launch_attention_prepare(qg, k, v, q_norm, k_norm, cos, sin, rows_from_position, cache, position_dev, S,
-                                               nh, nkv, hd, rot, cap, qn, stream);
+                                               nh, nkv, hd, rot, cap, qn, stream, 0, cache_stride);
       e != cudaSuccess)
     return e;
 
@@ -1501,7 +1528,7 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   if (smem > 200 * 1024 || csmem > 200 * 1024)
     return cudaErrorInvalidValue; // about 50,000 cached positions
   const size_t block_smem = (static_cast<size_t>(kKeyTile) * (hd + 4) + static_cast<size_t>(kScoreTokens) * group * hd) * sizeof(float);
-  if (S >= 4 && (hd & 7) == 0 && group * kKeyTile <= 256 && block_smem <= 200 * 1024) {
+  if (S >= 4 && cache_stride == 0 && (hd & 7) == 0 && group * kKeyTile <= 256 && block_smem <= 200 * 1024) {
     if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(attn_scores_block_kernel), 200 * 1024); e != cudaSuccess)
       return e;
     dim3 bgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv,
@@ -1512,11 +1539,11 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
     const size_t keys32_smem = (static_cast<size_t>(kScoreKeys) * (hd + 4) + static_cast<size_t>(group) * hd) * sizeof(float);
     dim3 sgrid(static_cast<unsigned>((max_position + S + kScoreKeys - 1) / kScoreKeys), nkv, static_cast<unsigned>(S));
     launch_chained(attn_scores_keys32_kernel, dim3(sgrid), dim3(group * kScoreKeys), keys32_smem, stream, qn, cache, position_dev, nh,
-                   nkv, hd, cap, score_stride, scores);
+                   nkv, hd, cap, score_stride, scores, cache_stride);
   } else {
     dim3 sgrid(static_cast<unsigned>((max_position + S + kKeyTile - 1) / kKeyTile), nkv, static_cast<unsigned>(S));
     launch_chained(attn_scores_kernel, dim3(sgrid), dim3(group * kKeyTile), smem, stream, qn, cache, position_dev, nh, nkv, hd,
-                   cap, score_stride, scores);
+                   cap, score_stride, scores, cache_stride);
   }
   // Prefill: eight tokens of a head per CTA when their probabilities fit in shared memory.
   const int p_stride = static_cast<int>((score_stride + 3) / 4 * 4);
@@ -1524,7 +1551,7 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   const size_t block_csmem = (static_cast<size_t>(kCombineTokens) * (p_stride + 2 * tile_slots + 1)) * sizeof(float) + 16 +
                              static_cast<size_t>(kBlockStages) * kValueTile * hd * sizeof(uint16_t) +
                              kBlockStages * sizeof(uint64_t);
-  if (S >= 4 && hd == 256 && block_csmem <= 200 * 1024) {
+  if (S >= 4 && cache_stride == 0 && hd == 256 && block_csmem <= 200 * 1024) {
     if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(attn_combine_block_kernel), 200 * 1024); e != cudaSuccess)
       return e;
     dim3 bgrid(nh, static_cast<unsigned>((S + kCombineTokens - 1) / kCombineTokens));
@@ -1533,7 +1560,7 @@ cudaError_t launch_attention(const uint16_t *qg, const uint16_t *k, const uint16
   } else {
     dim3 cgrid(nh, static_cast<unsigned>(S));
     launch_chained(attn_combine_kernel, dim3(cgrid), dim3((hd + 31) / 32 * 32), csmem, stream, scores, cache, qg, position_dev, nh,
-                   nkv, hd, cap, score_stride, out, q_out, s_out);
+                   nkv, hd, cap, score_stride, out, q_out, s_out, cache_stride);
   }
   return cudaGetLastError();
 }

@@ -395,11 +395,15 @@ __device__ inline void argmax_merge(float &bv, int64_t &bi, float v, int64_t i) 
   }
 }
 
+// blockIdx.y: row of a [rows, n] matrix (one argmax per row).
 __global__ void argmax_partial_kernel(const float *__restrict__ x, int64_t n, float *__restrict__ pv,
                                       int64_t *__restrict__ pi) {
   __shared__ float sv[32];
   __shared__ int64_t si[32];
   grid_dependency_sync();
+  x += static_cast<int64_t>(blockIdx.y) * n;
+  pv += blockIdx.y * gridDim.x;
+  pi += blockIdx.y * gridDim.x;
   float bv = -INFINITY;
   int64_t bi = INT64_MAX;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -435,6 +439,11 @@ __global__ void argmax_final_kernel(const float *__restrict__ pv, const int64_t 
                                     int64_t index_base, int64_t *__restrict__ out_index,
                                     float *__restrict__ out_value) {
   grid_dependency_sync();
+  pv += blockIdx.x * parts; // blockIdx.x: row
+  pi += blockIdx.x * parts;
+  out_index += blockIdx.x;
+  if (out_value)
+    out_value += blockIdx.x;
   float bv = -INFINITY;
   int64_t bi = INT64_MAX;
   for (int i = threadIdx.x; i < parts; i += 32)
@@ -452,10 +461,11 @@ __global__ void argmax_final_kernel(const float *__restrict__ pv, const int64_t 
 }
 
 void launch_argmax(const float *x, int64_t n, float *scratch_v, int64_t *scratch_i, int64_t index_base,
-                   int64_t *out_index, float *out_value, cudaStream_t stream) {
-  const int parts = static_cast<int>(std::min<int64_t>((n + 1023) / 1024, kArgmaxParts));
-  launch_chained(argmax_partial_kernel, dim3(parts), dim3(256), 0, stream, x, n, scratch_v, scratch_i);
-  launch_chained(argmax_final_kernel, dim3(1), dim3(32), 0, stream, scratch_v, scratch_i, parts, index_base, out_index, out_value);
+                   int64_t *out_index, float *out_value, cudaStream_t stream, int rows) {
+  const int parts = static_cast<int>(std::min<int64_t>((n + 1023) / 1024, kArgmaxParts / std::max(1, rows)));
+  launch_chained(argmax_partial_kernel, dim3(std::max(parts, 1), rows), dim3(256), 0, stream, x, n, scratch_v, scratch_i);
+  launch_chained(argmax_final_kernel, dim3(rows), dim3(32), 0, stream, scratch_v, scratch_i, std::max(parts, 1), index_base, out_index,
+                 out_value);
 }
 
 } // namespace llmcp_b200
