@@ -368,6 +368,53 @@ def attention_alone(L, repeats=4, position=1030):
     return out[0]
 
 
+def decode_timeline(L, torch, mode):
+    """Prints the device timeline of one decode step at 1032 cached positions: per kernel family its
+    launches, summed duration and the summed distance from the previous kernel's end to its own start
+    (negative = it started while the previous one ran), then start -> end of every kernel of the first
+    four layers and of the step's tail.  Stamps come from the PyTorch profiler (CUPTI activity
+    records of a plain CUDA-graph replay: kernels overlap as they do in the bench)."""
+    import collections
+    import tempfile
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.zeros(1, device="cuda")
+    arena = L.Arena().load(ensure_container(0))
+    engine = L.Engine(arena.data, L.default_dims(), capacity=PREFILL + 136, mode=mode)
+    _, token = engine.forward([TOKEN] * PREFILL, 0)
+    out, _ = engine.generate(token, PREFILL, 8)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        out, ms = engine.generate(int(out[-1]), PREFILL + 8, 4)
+        torch.cuda.synchronize()
+    with tempfile.TemporaryDirectory() as folder:
+        trace = os.path.join(folder, "trace.json")
+        prof.export_chrome_trace(trace)
+        events = [e for e in json.load(open(trace))["traceEvents"] if e.get("cat") == "kernel"]
+    events.sort(key=lambda e: e["ts"])
+    starts = [i for i, e in enumerate(events) if "embedding" in e["name"]]
+    step = events[starts[1]:starts[2]]
+    t0 = step[0]["ts"]
+
+    def short(name):
+        name = name.split("(")[0].replace("llmcp_b200::", "").replace("(anonymous namespace)::", "").replace("void ", "")
+        return name or "gemv_q8_*"  # the GEMV templates' names are cut at their first parenthesis
+
+    families = collections.defaultdict(lambda: [0, 0.0, 0.0])
+    previous_end = None
+    for e in step:
+        entry = families[short(e["name"])]
+        entry[0] += 1
+        entry[1] += e["dur"]
+        entry[2] += 0.0 if previous_end is None else e["ts"] - previous_end
+        previous_end = e["ts"] + e["dur"]
+    span = step[-1]["ts"] + step[-1]["dur"] - t0
+    print(f"mode {mode}: {ms / 4 * 1e3:.1f} us per token over 4 steps; this step spans {span:.1f} us in {len(step)} kernels")
+    for name, (n, dur, gap) in sorted(families.items(), key=lambda kv: -kv[1][1]):
+        print(f"{name[:56]:56s} n={n:4d} dur={dur:8.1f} us  start-after-previous-end={gap:8.1f} us  avg={dur / n:6.2f}")
+    for e in step[:42] + step[-6:]:
+        print(f"{e['ts'] - t0:8.2f} -> {e['ts'] - t0 + e['dur']:8.2f} (+{e['dur']:6.2f})  {short(e['name'])[:64]}")
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -378,8 +425,10 @@ def main():
     parser.add_argument("--mode", default="fast", choices=["fast", "exact"], help="arithmetic mode `value` is measured in")
     parser.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
                         help="N > 1: tp = one sequence over N GPUs (strong scaling, the default), replicas = one sequence per GPU")
-    parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm", "attn"],
-                        help="gemv / gemm / attn: run just that kernel on a small case (what the profiler captures)")
+    parser.add_argument("--batch", type=int, default=64, help="sequences of the batched-decode measurement (0 = skip it)")
+    parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm", "attn", "timeline"],
+                        help="gemv / gemm / attn: run just that kernel on a small case (what the profiler captures); "
+                             "timeline: kernel start / end stamps of one decode step (CUDA-graph replay) as text")
     args = parser.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
@@ -435,6 +484,9 @@ def main():
     if args.only == "gemm":
         us, tops = gemm_alone(L, torch)
         print(json.dumps({"only": "gemm", "shape": [GEMM_M, GEMM_N, GEMM_K], "us_per_launch": us, "int8_tops": tops}))
+        return
+    if args.only == "timeline":
+        decode_timeline(L, torch, args.mode)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -653,6 +705,35 @@ def main():
                                    "epilogue_bound_us": epilogue_us,
                                    "epilogue_bound_tops": 2.0 * GEMM_M * GEMM_N * GEMM_K / epilogue_us / 1e6,
                                    "frac_of_epilogue_bound": epilogue_us / gemm_us}
+    if rank == 0 and world == 1 and args.batch > 1:
+        # Batch of independent sequences (the batched configuration of the benchmark list): every
+        # sequence prefilled with its own 1024 tokens, then all decoded together, one token each per
+        # step.  Two prompt sets: all 1024 x token 9419, and ids drawn per sequence.
+        batch, batch_steps = args.batch, 16
+        engine = L.Engine(arena.data, dims, capacity=PREFILL + 2 * batch_steps + 8, device=local_rank, mode=args.mode, batch=batch)
+        rng = np.random.default_rng(SEED + 5)
+        sets = {}
+        for name in ("all_9419", "per_sequence_random"):
+            engine.reset()
+            firsts = []
+            t0 = time.perf_counter()
+            for b in range(batch):
+                ids = prompt if name == "all_9419" else rng.integers(0, dims.vocab, PREFILL).tolist()
+                engine.select_sequence(b)
+                firsts.append(engine.forward(ids, 0, want_logits=False)[1])
+            batch_prefill_s = time.perf_counter() - t0
+            warm, _ = engine.generate_batch(firsts, PREFILL, 4)
+            tokens_b, ms_b = engine.generate_batch(warm[-1], PREFILL + 4, batch_steps)
+            sets[name] = {"value": batch * batch_steps / (ms_b / 1e3), "unit": "tokens/s", "ms_per_step": ms_b / batch_steps,
+                          "prefill_tokens_per_second": batch * PREFILL / batch_prefill_s,
+                          "distinct_sequences": len({tuple(col) for col in tokens_b.T.tolist()})}
+        engine.close()
+        # per step: weights once, and per sequence the recurrent state (read and written) and the KV cache
+        step_bytes = 4.47e9 + batch * (2 * 100.7e6 + 8 * 4096 * (PREFILL + 4 + batch_steps // 2))
+        result["batch"] = {"sequences": batch, "steps": batch_steps, "mode": args.mode, "sets": sets,
+                           "bytes_per_step": step_bytes,
+                           "achieved_gbs": step_bytes / (sets["all_9419"]["ms_per_step"] / 1e3) / 1e9,
+                           "parity": "each sequence against its own one-sequence oracle run: tests/test_gpu_batch.py"}
     if cpu_baseline:
         result["cpu_baseline"] = cpu_baseline
     if rank == 0:
