@@ -396,8 +396,8 @@ def decode_timeline(L, torch, mode):
     t0 = step[0]["ts"]
 
     def short(name):
-        name = name.split("(")[0].replace("llmcp_b200::", "").replace("(anonymous namespace)::", "").replace("void ", "")
-        return name or "gemv_q8_*"  # the GEMV templates' names are cut at their first parenthesis
+        name = name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
+        return name.split("(")[0].replace("llmcp_b200::", "").replace("void ", "")
 
     families = collections.defaultdict(lambda: [0, 0.0, 0.0])
     previous_end = None

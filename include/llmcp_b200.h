@@ -167,6 +167,14 @@ int llmcp_dev_repack_q8(const uint8_t *records, int64_t N, int64_t K, int8_t *q,
 int llmcp_dev_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *scales, void *stream);
 int llmcp_dev_gemv_q8(const int8_t *aq, const float *as, int64_t K, const int8_t *wq, const uint16_t *wd, int64_t N,
                       void *y, int y_dtype, int activation, int rows_per_warp, int flags, void *stream);
+/* The MLP's gate and up projections of one token with their product in one launch (K = 2560,
+ * N % 32 == 0): product[i] = bf16(bf16(silu(gate_i . x)) * bf16(up_i . x)) (optional output) and its
+ * int8 quantisation q_out [N], s_out [N/32] for the down projection -- the fused form of
+ * lib/Dialect/LLMCP/Transforms/FuseLinearActivations.cpp:27-77 + the `mul` of LowerToLinalg.cpp:312-427
+ * + Q8Decode.cpp:83-120.  flags: 1 and 16 as for llmcp_dev_gemv_q8.  q_out/s_out must not alias aq/as. */
+int llmcp_dev_gemv_q8_swiglu(const int8_t *aq, const float *as, int64_t K, const int8_t *gate_q, const uint16_t *gate_d,
+                             const int8_t *up_q, const uint16_t *up_d, int64_t N, uint16_t *product, int8_t *q_out,
+                             float *s_out, int flags, void *stream);
 int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
                       int64_t N, void *y, int y_dtype, int activation, void *stream);
 int llmcp_dev_gemm_q8_tc(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const float *wd32,
@@ -217,6 +225,28 @@ uint64_t llmcp_b200_synthetic_bytes(const llmcp_b200_dims *dims);
 int llmcp_b200_synthetic_fill(const llmcp_b200_dims *dims, uint64_t seed, uint8_t *file, uint64_t file_bytes);
 int llmcp_b200_pack_q8_0_p4(const float *values, int64_t rows, int64_t cols, uint8_t *dst);
 int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes);
+/* Token ids -> text, the output half of llmcp-run (tools/llmcp-run/llmcp-run.cpp:657-690).  Host only.
+ *   llmcp_b200_vocab_create   : from the text of a tokenizer.json (model.vocab + added_tokens, ByteLevel
+ *                               decoder) or of a bare {"token": id} object; NULL + last_error on failure.
+ *   llmcp_b200_vocab_decode   : the tokenizer's Decode(ids): GPT-2 byte alphabet back to bytes, then
+ *                               lossy UTF-8 (ill-formed subsequences become U+FFFD); ids without a
+ *                               token are skipped.  Text functions copy at most capacity - 1 bytes
+ *                               and a terminating 0 into `out` and return the full length.
+ *   llmcp_b200_stream_*       : ByteLevelStreamingDecoder of tools/llmcp-run/StreamingDecoder.cpp:13-29:
+ *                               append returns a complete chunk, or nothing while the decoded tail is
+ *                               U+FFFD (bytes the next token may complete); finish emits the rest.
+ *                               The vocabulary must outlive the stream.
+ *   llmcp_b200_chat_prompt    : makeChatPrompt of tools/llmcp-run/llmcp-run.cpp:608-624. */
+void *llmcp_b200_vocab_create(const char *json, uint64_t length);
+void llmcp_b200_vocab_destroy(void *vocab);
+int64_t llmcp_b200_vocab_size(const void *vocab);
+int32_t llmcp_b200_vocab_token_to_id(const void *vocab, const char *token);
+uint64_t llmcp_b200_vocab_decode(const void *vocab, const int32_t *ids, uint64_t count, char *out, uint64_t capacity);
+void *llmcp_b200_stream_create(const void *vocab);
+void llmcp_b200_stream_destroy(void *stream);
+uint64_t llmcp_b200_stream_append(void *stream, int32_t token, char *out, uint64_t capacity);
+uint64_t llmcp_b200_stream_finish(void *stream, char *out, uint64_t capacity);
+uint64_t llmcp_b200_chat_prompt(const char *user, const char *system, int thinking, char *out, uint64_t capacity);
 /* Checkpoint → container, the job of llmcp's offline packer:
  *   llmcp_b200_parse_config     : model dimensions from the text of config.json, with the
  *                                 checks of lib/Model/ModelConfig.cpp:78-283.

@@ -75,6 +75,12 @@ def lib():
         handle.llmcp_b200_engine_create_batch.restype = C.c_void_p
         handle.llmcp_b200_tp_create.restype = C.c_void_p
         handle.llmcp_b200_tp_slot_bytes.restype = C.c_uint64
+        handle.llmcp_b200_vocab_create.restype = C.c_void_p
+        handle.llmcp_b200_vocab_size.restype = C.c_int64
+        handle.llmcp_b200_vocab_token_to_id.restype = C.c_int32
+        handle.llmcp_b200_stream_create.restype = C.c_void_p
+        for name in ("vocab_decode", "stream_append", "stream_finish", "chat_prompt"):
+            getattr(handle, "llmcp_b200_" + name).restype = C.c_uint64
         handle._mlir_ciface_llmcp_model_prefill.restype = None
         handle._mlir_ciface_llmcp_model_decode.restype = None
         _lib = handle
@@ -307,6 +313,74 @@ def pack_checkpoint(model_dir, output_path=None, quant="none", dry_run=False, ve
         os.fsencode(str(model_dir)), os.fsencode(str(output_path)) if output_path else None, quant.encode(),
         int(bool(dry_run)), int(bool(verbose)), *[C.byref(c) for c in counters]))
     return tuple(int(c.value) for c in counters)
+
+
+def _text_call(fn, *args):
+    """Calls a C function that fills (out, capacity) and returns the full length; returns bytes."""
+    size = int(fn(*args, None, C.c_uint64(0)))
+    buf = C.create_string_buffer(size + 1)
+    fn(*args, buf, C.c_uint64(size + 1))
+    return buf.raw[:size]
+
+
+class Vocab:
+    """Token ids -> text of a ByteLevel tokenizer: what llmcp-run gets from ``tokenizers::Tokenizer``
+    (``Decode``, ``TokenToId``; tools/llmcp-run/llmcp-run.cpp:635-690).  ``json`` is the text of a
+    tokenizer.json or of a bare ``{"token": id}`` object."""
+
+    def __init__(self, json):
+        raw = json.encode() if isinstance(json, str) else bytes(json)
+        self._handle = lib().llmcp_b200_vocab_create(raw, C.c_uint64(len(raw)))
+        if not self._handle:
+            raise LlmcpError(last_error())
+
+    def __len__(self):
+        return int(lib().llmcp_b200_vocab_size(C.c_void_p(self._handle)))
+
+    def token_to_id(self, token):
+        return int(lib().llmcp_b200_vocab_token_to_id(C.c_void_p(self._handle), token.encode()))
+
+    def decode(self, ids):
+        arr = (C.c_int32 * len(ids))(*ids)
+        return _text_call(lib().llmcp_b200_vocab_decode, C.c_void_p(self._handle), arr, C.c_uint64(len(ids))).decode()
+
+    def close(self):
+        if self._handle:
+            lib().llmcp_b200_vocab_destroy(C.c_void_p(self._handle))
+            self._handle = None
+
+
+class StreamingDecoder:
+    """``ByteLevelStreamingDecoder`` of tools/llmcp-run/StreamingDecoder.h: ``append`` returns a
+    complete chunk or "" while a character's bytes are incomplete; ``finish`` emits the rest."""
+
+    def __init__(self, vocab):
+        self._vocab = vocab  # must outlive the stream
+        self._handle = lib().llmcp_b200_stream_create(C.c_void_p(vocab._handle))
+
+    def _once(self, fn, *args):
+        # these calls consume the pending ids, so they are made once, with a buffer no chunk outgrows
+        buf = C.create_string_buffer(1 << 16)
+        size = int(fn(C.c_void_p(self._handle), *args, buf, C.c_uint64(len(buf))))
+        if size >= len(buf):
+            raise LlmcpError("a streamed chunk longer than 64 KiB was cut")
+        return buf.raw[:size].decode()
+
+    def append(self, token):
+        return self._once(lib().llmcp_b200_stream_append, C.c_int32(token))
+
+    def finish(self):
+        return self._once(lib().llmcp_b200_stream_finish)
+
+    def close(self):
+        if self._handle:
+            lib().llmcp_b200_stream_destroy(C.c_void_p(self._handle))
+            self._handle = None
+
+
+def chat_prompt(user, system="", thinking=True):
+    """``makeChatPrompt`` of tools/llmcp-run/llmcp-run.cpp:608-624."""
+    return _text_call(lib().llmcp_b200_chat_prompt, user.encode(), system.encode(), int(bool(thinking))).decode()
 
 
 class Arena:

@@ -16,6 +16,7 @@
 #include "checkpoint.h"
 #include "engine.h"
 #include "kernels.h"
+#include "text.h"
 #include "tp_comm.h"
 
 using namespace llmcp_b200;
@@ -694,6 +695,21 @@ int llmcp_dev_gemv_q8(const int8_t *aq, const float *as, int64_t K, const int8_t
   });
 }
 
+int llmcp_dev_gemv_q8_swiglu(const int8_t *aq, const float *as, int64_t K, const int8_t *gate_q, const uint16_t *gate_d,
+                             const int8_t *up_q, const uint16_t *up_d, int64_t N, uint16_t *product, int8_t *q_out,
+                             float *s_out, int flags, void *stream) {
+  return guarded_async([&] {
+    check_q8_shape(N, K);
+    if (!gemv_swiglu_supported(static_cast<int>(K), N))
+      throw std::runtime_error("llmcp_dev_gemv_q8_swiglu takes K = 2560 and N % 32 == 0");
+    if (static_cast<const void *>(aq) == q_out || static_cast<const void *>(as) == s_out)
+      throw std::runtime_error("llmcp_dev_gemv_q8_swiglu: the quantised product must not overwrite the quantised input");
+    cuda_check(launch_gemv_q8_swiglu(aq, as, static_cast<int>(K), gate_q, gate_d, up_q, up_d, N, product, q_out, s_out, flags,
+                                     static_cast<cudaStream_t>(stream)), "gate/up GEMV");
+    g_launches += 1;
+  });
+}
+
 int llmcp_dev_gemm_q8(const int8_t *aq, const float *as, int64_t M, int64_t K, const int8_t *wq, const uint16_t *wd,
                       int64_t N, void *y, int y_dtype, int activation, void *stream) {
   return guarded_async([&] {
@@ -824,6 +840,59 @@ int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes) {
     if (!error.empty())
       throw std::runtime_error(error);
   });
+}
+
+// ---- token ids -> text (text.h) ----------------------------------------------------------------
+namespace {
+uint64_t copy_text(const std::string &text, char *out, uint64_t capacity) {
+  if (out && capacity) {
+    const uint64_t n = std::min<uint64_t>(text.size(), capacity - 1);
+    std::memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return text.size();
+}
+} // namespace
+
+void *llmcp_b200_vocab_create(const char *json, uint64_t length) {
+  auto *vocab = new ByteLevelVocab();
+  const std::string error = vocab->load(json, length);
+  if (!error.empty()) {
+    set_error(error);
+    delete vocab;
+    return nullptr;
+  }
+  return vocab;
+}
+
+void llmcp_b200_vocab_destroy(void *vocab) { delete static_cast<ByteLevelVocab *>(vocab); }
+
+int64_t llmcp_b200_vocab_size(const void *vocab) { return static_cast<const ByteLevelVocab *>(vocab)->size(); }
+
+int32_t llmcp_b200_vocab_token_to_id(const void *vocab, const char *token) {
+  return static_cast<const ByteLevelVocab *>(vocab)->token_to_id(token ? token : "");
+}
+
+uint64_t llmcp_b200_vocab_decode(const void *vocab, const int32_t *ids, uint64_t count, char *out, uint64_t capacity) {
+  return copy_text(static_cast<const ByteLevelVocab *>(vocab)->decode(ids, count), out, capacity);
+}
+
+void *llmcp_b200_stream_create(const void *vocab) {
+  return new ByteLevelStreamingDecoder(*static_cast<const ByteLevelVocab *>(vocab));
+}
+
+void llmcp_b200_stream_destroy(void *stream) { delete static_cast<ByteLevelStreamingDecoder *>(stream); }
+
+uint64_t llmcp_b200_stream_append(void *stream, int32_t token, char *out, uint64_t capacity) {
+  return copy_text(static_cast<ByteLevelStreamingDecoder *>(stream)->append(token), out, capacity);
+}
+
+uint64_t llmcp_b200_stream_finish(void *stream, char *out, uint64_t capacity) {
+  return copy_text(static_cast<ByteLevelStreamingDecoder *>(stream)->finish(), out, capacity);
+}
+
+uint64_t llmcp_b200_chat_prompt(const char *user, const char *system, int thinking, char *out, uint64_t capacity) {
+  return copy_text(make_chat_prompt(user ? user : "", system ? system : "", thinking != 0), out, capacity);
 }
 
 int llmcp_b200_parse_config(const char *json, uint64_t length, llmcp_b200_dims *dims) {

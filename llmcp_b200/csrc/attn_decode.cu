@@ -210,43 +210,66 @@ attn_decode_split_kernel(const uint16_t *__restrict__ qn, const uint16_t *__rest
   }
 }
 
-// grid: query head; block: HD threads (one head dimension each).
+// grid: query head; block: kMergeGroups x HD threads.  Thread (g, d) folds splits g, g + 4, ... of head
+// dimension d (every load of a round issued before the first use: the partial sums come from L2
+// and a dependent chain over 30-70 splits would cost a round trip each); group 0 adds the four
+// partial results in group order.
+constexpr int kMergeGroups = 4;
+constexpr int kMergeUnroll = 8;
+
 template <int HD>
-__global__ void __launch_bounds__(HD)
+__global__ void __launch_bounds__(kMergeGroups *HD)
 attn_decode_merge_kernel(const float *__restrict__ part_acc, const float *__restrict__ part_ml,
                          const uint16_t *__restrict__ qg, const int64_t *__restrict__ position_ptr, int chunk,
                          int splits, uint16_t *__restrict__ out, int8_t *__restrict__ q_out,
                          float *__restrict__ s_out) {
+  __shared__ float group_l[kMergeGroups];
+  __shared__ float group_o[kMergeGroups][HD];
   // blockIdx.y: sequence of a batch; its heads follow the previous sequence's in every buffer
-  const int h = blockIdx.y * gridDim.x + blockIdx.x, d = threadIdx.x, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * gridDim.x + blockIdx.x;
+  const int d = threadIdx.x % HD, g = threadIdx.x / HD, lane = threadIdx.x & 31;
   grid_dependency_sync(true);
-  const float gate = bf16_to_f32(qg[static_cast<int64_t>(h) * 2 * HD + HD + d]);
+  const float gate = g == 0 ? bf16_to_f32(qg[static_cast<int64_t>(h) * 2 * HD + HD + d]) : 0.0f;
   const int total = static_cast<int>(*position_ptr) + 1;
   const int active = (total + chunk - 1) / chunk;
   const float *ml = part_ml + static_cast<size_t>(h) * splits * 2;
   const float *pa = part_acc + static_cast<size_t>(h) * splits * HD + d;
+  // maximum over the splits: every warp folds all of them (lane-strided), so no second barrier
   float m = -1.0e30f;
-  for (int s = 0; s < active; ++s)
+  for (int s = lane; s < active; s += 32)
     m = fmaxf(m, ml[2 * s]);
-  float l = 0.0f, o = 0.0f;
-  int s = 0;
-  for (; s + 4 <= active; s += 4) {
-    float w[4], a[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      a[u] = pa[static_cast<size_t>(s + u) * HD];
-      w[u] = expf(__fsub_rn(ml[2 * (s + u)], m));
+  for (int o = 16; o > 0; o >>= 1)
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float l = 0.0f, o = 0.0f;
+  for (int s0 = g; s0 < active; s0 += kMergeGroups * kMergeUnroll) {
+    float w[kMergeUnroll], a[kMergeUnroll], ls[kMergeUnroll];
+#pragma unroll
+    for (int u = 0; u < kMergeUnroll; ++u) {
+      const int s = s0 + u * kMergeGroups;
+      const bool on = s < active;
+      a[u] = on ? pa[static_cast<size_t>(s) * HD] : 0.0f;
+      w[u] = on ? ml[2 * s] : -1.0e30f;
+      ls[u] = on ? ml[2 * s + 1] : 0.0f;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      l = __fmaf_rn(w[u], ml[2 * (s + u) + 1], l);
-      o = __fmaf_rn(w[u], a[u], o);
+    for (int u = 0; u < kMergeUnroll; ++u) {
+      const float e = expf(__fsub_rn(w[u], m));
+      l = __fmaf_rn(e, ls[u], l);
+      o = __fmaf_rn(e, a[u], o);
     }
   }
-  for (; s < active; ++s) {
-    const float w = expf(__fsub_rn(ml[2 * s], m));
-    l = __fmaf_rn(w, ml[2 * s + 1], l);
-    o = __fmaf_rn(w, pa[static_cast<size_t>(s) * HD], o);
+  group_o[g][d] = o;
+  if (d == 0)
+    group_l[g] = l;
+  __syncthreads();
+  if (g != 0)
+    return;
+  l = group_l[0], o = group_o[0][d];
+#pragma unroll
+  for (int k = 1; k < kMergeGroups; ++k) {
+    l = __fadd_rn(l, group_l[k]);
+    o = __fadd_rn(o, group_o[k][d]);
   }
   const float sigmoid = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gate)));
   const uint16_t bits = f32_to_bf16(__fmul_rn(__fdiv_rn(o, l), sigmoid));
@@ -338,10 +361,10 @@ cudaError_t launch_attention_decode_fast(const uint16_t *qg, const uint16_t *k, 
   if (e != cudaSuccess)
     return e;
   if (hd == 256)
-    launch_chained(attn_decode_merge_kernel<256>, dim3(nh, sequences), dim3(256), 0, stream, part_acc, part_ml, qg, position_dev, chunk,
+    launch_chained(attn_decode_merge_kernel<256>, dim3(nh, sequences), dim3(kMergeGroups * 256), 0, stream, part_acc, part_ml, qg, position_dev, chunk,
                    splits, out, q_out, s_out);
   else
-    launch_chained(attn_decode_merge_kernel<128>, dim3(nh, sequences), dim3(128), 0, stream, part_acc, part_ml, qg, position_dev, chunk,
+    launch_chained(attn_decode_merge_kernel<128>, dim3(nh, sequences), dim3(kMergeGroups * 128), 0, stream, part_acc, part_ml, qg, position_dev, chunk,
                    splits, out, q_out, s_out);
   return cudaGetLastError();
 }

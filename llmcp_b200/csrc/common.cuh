@@ -129,6 +129,21 @@ __device__ __forceinline__ void grid_dependency_sync(bool release_early = false)
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// Barrier over all threads of the thread-block cluster; shared-memory stores made before it (to
+// any CTA of the cluster) are visible after it.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Stores v at the place of `local` (an address in this CTA's shared memory) in the shared memory
+// of CTA `rank` of the cluster.
+__device__ __forceinline__ void store_shared_cluster(float *local, int rank, float v) {
+  const uint32_t mine = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 // Raises a kernel's dynamic shared-memory limit once per (kernel, device).  The attribute belongs
 // to the device that is current when it is set, so a process that drives several GPUs has to make
 // the opt-in on each of them; the record of what has been done is guarded by a mutex.
@@ -174,6 +189,27 @@ inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 blo
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = overlap_launches_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// The same with thread-block clusters of cluster_x CTAs along x (grid.x a multiple of it).
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                          int cluster_x, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = overlap_launches_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 

@@ -218,7 +218,9 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   if (const char *flag = std::getenv("LLMCP_B200_GEMV_FLAGS"))
     gemv_flags_ = std::atoi(flag);
   if (const char *flag = std::getenv("LLMCP_B200_FUSE_MIXER"))
-    fuse_decode_mixer_ = std::atoi(flag) != 0;
+    fuse_decode_mixer_ = std::atoi(flag);
+  if (const char *flag = std::getenv("LLMCP_B200_FUSE_SWIGLU"))
+    fuse_swiglu_ = std::atoi(flag) != 0;
   check(cudaMemsetAsync(gemm_error_, 0, 4, stream_), "memset");
   generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
   check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
@@ -578,16 +580,19 @@ void Engine::ensure_workspace(int64_t S, int64_t position) {
 
 // Tensor parallel: the rows left in aq_ / as_ hold this rank's k_local columns; every rank gets all of
 // them (in a slot of the exchange buffer).  With one rank the local buffers are the result.
-void Engine::gather_quant(int64_t S, int64_t k_local, const int8_t **q, const float **s) {
+void Engine::gather_quant(int64_t S, int64_t k_local, const int8_t **q, const float **s, const int8_t *src_q,
+                          const float *src_s) {
+  if (!src_q)
+    src_q = aq_, src_s = as_;
   if (!tp_) {
-    *q = aq_;
-    *s = as_;
+    *q = src_q;
+    *s = src_s;
     return;
   }
   const int slot = exchange_++ & 1;
   const size_t q_bytes = round_up(static_cast<size_t>(S) * k_local * tp_size_, 256);
-  const TpSegment segments[2] = {{aq_, static_cast<size_t>(k_local), static_cast<size_t>(S), 0},
-                                 {as_, static_cast<size_t>(k_local / 32 * 4), static_cast<size_t>(S), q_bytes}};
+  const TpSegment segments[2] = {{src_q, static_cast<size_t>(k_local), static_cast<size_t>(S), 0},
+                                 {src_s, static_cast<size_t>(k_local / 32 * 4), static_cast<size_t>(S), q_bytes}};
   check(tp_->all_gather(segments, 2, slot, gemm_error_, stream_), "all-gather (quantised rows)");
   launches_ += 1;
   *q = reinterpret_cast<const int8_t *>(tp_->slot(slot));
@@ -773,11 +778,12 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       const int nv_all = static_cast<int>(c.lin_v_heads), head0 = tp_rank_ * nv;
       const GdnBatch strides = {static_cast<int64_t>(conv_seq_), nv_all, static_cast<int64_t>(delta_seq_)};
       if (one_token && fuse_decode_mixer_ && gdn_decode_supported(static_cast<int>(c.conv_kernel), nk, nv, dk, dv)) {
+        const int single = fuse_decode_mixer_ >= 2 && gdn_decode_single_kernel_supported(static_cast<int>(c.conv_kernel), nk, nv, dk, dv);
         check(launch_gdn_decode(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, static_cast<int>(c.conv_kernel),
                                 a_ + head0, b_ + head0, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype, delta_state,
                                 nk, nv, dk, dv, 1, z_, L.lin_norm.data, L.lin_norm.dtype, c.eps, 1, gdn_scratch_, convd_, nullptr,
-                                aq_, as_, stream_, sequences, &strides), "gated_delta_net (decode)");
-        launches_ += 2;
+                                aq_, as_, stream_, sequences, &strides, single, mode_ == kModeFast ? 1 : 0), "gated_delta_net (decode)");
+        launches_ += single ? 1 : 2;
       } else if (rows_are_sequences) {
         // Shapes the fused one-token kernels do not take: the general kernels, sequence by sequence.
         const int64_t V = m.value_dim();
@@ -830,13 +836,25 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     const uint16_t *branch = gather_rows(branch_, S, hidden_rows_);
     rms_norm(hidden_[cur], branch, S, L.post_norm, hidden_[cur ^ 1], nullptr);
     cur ^= 1;
-    const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-    run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, gemm_status);
-    check(launch_pointwise(gate_, up_, S * inter_rows_, 1, nullptr, aq_, as_, stream_), "mul");
-    launches_ += 2;
     const int8_t *mlp_q = nullptr;
     const float *mlp_s = nullptr;
-    gather_quant(S, inter_rows_, &mlp_q, &mlp_s);
+    if (S == 1 && fuse_swiglu_ && L.gate.K == L.up.K && L.gate.N == L.up.N && gemv_swiglu_supported(L.gate.K, L.gate.N)) {
+      // One token: both projections, the product and its quantisation in one launch.  The launch
+      // reads the quantised input while it writes the quantised product, so the product goes to
+      // the (otherwise unused) rows of the separate projections' outputs.
+      int8_t *product_q = reinterpret_cast<int8_t *>(gate_);
+      float *product_s = reinterpret_cast<float *>(up_);
+      check(launch_gemv_q8_swiglu(aq_, as_, L.gate.K, L.gate.q, L.gate.d, L.up.q, L.up.d, L.gate.N, nullptr, product_q, product_s,
+                                  gemv_flags, stream_), "gate/up (one launch)");
+      launches_ += 1;
+      gather_quant(S, inter_rows_, &mlp_q, &mlp_s, product_q, product_s);
+    } else {
+      const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
+      run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, gemm_status);
+      check(launch_pointwise(gate_, up_, S * inter_rows_, 1, nullptr, aq_, as_, stream_), "mul");
+      launches_ += 2;
+      gather_quant(S, inter_rows_, &mlp_q, &mlp_s);
+    }
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
     run_linears(planes, mlp_q, mlp_s, S, &down, 1, stream_, &launches_, gemv_flags, gemm_status);
     pending = gather_rows(mlp_out_, S, hidden_rows_);

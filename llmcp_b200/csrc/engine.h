@@ -155,7 +155,8 @@ private:
   void check(cudaError_t e, const char *what);
 
   // Tensor parallelism: all-gathers of quantised rows (int8 + scales) and of bf16 rows.
-  void gather_quant(int64_t S, int64_t k_local, const int8_t **q, const float **s);
+  void gather_quant(int64_t S, int64_t k_local, const int8_t **q, const float **s, const int8_t *src_q = nullptr,
+                    const float *src_s = nullptr);
   const uint16_t *gather_rows(const uint16_t *src, int64_t S, int64_t n_local);
 
   ModelDims dims_;
@@ -232,7 +233,10 @@ private:
   float *ast_ = nullptr;  // [max K / 32][pitch] their scales, block-major
   int *gemm_error_ = nullptr; // device flag raised by a timed-out wait in the GEMM
   int gemv_flags_ = 3; // kGemvOverlapPrevious | kGemvPrefetchL2
-  bool fuse_decode_mixer_ = true; // one-token gated-delta-net layers in two launches instead of five
+  bool fuse_swiglu_ = true;   // one-token MLP: gate, up, product and quantisation in one launch
+  // one-token gated-delta-net layers: 0 five launches, 1 two, 2 one (a cluster per key head; measured
+  // slower than two: the recurrent state can then be fetched only after the projections have finished)
+  int fuse_decode_mixer_ = 1;
 };
 
 } // namespace llmcp_b200

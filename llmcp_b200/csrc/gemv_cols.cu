@@ -291,6 +291,120 @@ cudaError_t launch_cols80(const int8_t *aq, const float *as, GemvJobs jobs, int3
   return cudaLaunchKernelEx(&config, gemv_q8_cols80_kernel<false, false>, aq, as, jobs, sets, no_dots);
 }
 
+// gate and up projections of the MLP with their product in one launch (K = 2560):
+//   h = bf16(bf16(silu(gate . x)) * bf16(up . x)),  then the int8 quantisation of h that the down
+// projection reads (Q8Decode.cpp:83-120).  A cluster of two CTAs owns one quantisation block of h:
+// CTA 0 takes rows [32 u, 32 u + 32) of the gate matrix, CTA 1 the same rows of the up matrix, each
+// as two sets of 16 rows through the registers -> shared memory -> row sums path of
+// gemv_q8_cols80_kernel (so the launch streams like that kernel: 4 CTAs per SM, one set in flight
+// per CTA).  CTA 1 then stores its 32 results into CTA 0's shared memory, and CTA 0's first warp
+// forms the 32 products, their maximum and the int8 values.  Every value has the arithmetic of the
+// separate linear, linear, multiply launches (FuseLinearActivations.cpp:27-77,
+// LowerToLinalg.cpp:312-427).
+template <bool FAST>
+__global__ void __launch_bounds__(160, 4)
+gemv_q8_swiglu80_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const int8_t *__restrict__ gate_q,
+                        const uint16_t *__restrict__ gate_d, const int8_t *__restrict__ up_q,
+                        const uint16_t *__restrict__ up_d, uint16_t *__restrict__ product, int8_t *__restrict__ q_out,
+                        float *__restrict__ s_out) {
+  constexpr int NB = 80, K = 2560, kHalf = kSetRows / 2;
+  constexpr int kStride = NB + 2;
+  constexpr int kFastStride = 88;
+  __shared__ __align__(16) float2 slab[kSetRows * kStride];
+  __shared__ float results[4 * kSetRows]; // silu(gate) rows 0..31, then up rows 0..31, each rounded to bf16
+  const int t = threadIdx.x;
+  const int kb = t % NB, half = t / NB;
+  const int rank = blockIdx.x & 1, unit = blockIdx.x >> 1; // clusters of two along x
+  const int row_base = unit * 32;
+  const int8_t *wq = rank ? up_q : gate_q;
+  const uint16_t *wd = rank ? up_d : gate_d;
+  const int activation = rank ? kNone : kSilu;
+
+  ColsBlock w[kHalf];
+  uint16_t scale_bits[kHalf];
+  auto load = [&](int set) {
+#pragma unroll
+    for (int i = 0; i < kHalf; ++i) {
+      const size_t row = static_cast<size_t>(row_base + set * kSetRows + half * kHalf + i);
+      w[i] = ld_cols_block(wq + row * K + kb * 32);
+      scale_bits[i] = __ldg(wd + row * NB + kb);
+    }
+  };
+  load(0);
+  // first half of a cluster barrier: by the time CTA 1 stores into CTA 0's shared memory both have started
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  // The weights are on their way; the input row belongs to the kernel in front.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint4 lo = reinterpret_cast<const uint4 *>(aq)[2 * kb];
+  const uint4 hi = reinterpret_cast<const uint4 *>(aq)[2 * kb + 1];
+  const float a_scale = as[kb];
+#pragma unroll
+  for (int set = 0; set < 2; ++set) {
+#pragma unroll
+    for (int i = 0; i < kHalf; ++i) {
+      int dot = dp4a(static_cast<int>(w[i].v[0]), static_cast<int>(lo.x), 0);
+      dot = dp4a(static_cast<int>(w[i].v[1]), static_cast<int>(lo.y), dot);
+      dot = dp4a(static_cast<int>(w[i].v[2]), static_cast<int>(lo.z), dot);
+      dot = dp4a(static_cast<int>(w[i].v[3]), static_cast<int>(lo.w), dot);
+      dot = dp4a(static_cast<int>(w[i].v[4]), static_cast<int>(hi.x), dot);
+      dot = dp4a(static_cast<int>(w[i].v[5]), static_cast<int>(hi.y), dot);
+      dot = dp4a(static_cast<int>(w[i].v[6]), static_cast<int>(hi.z), dot);
+      dot = dp4a(static_cast<int>(w[i].v[7]), static_cast<int>(hi.w), dot);
+      const int row = half * kHalf + i;
+      const float factor = __fmul_rn(a_scale, f16_bits_to_f32(scale_bits[i]));
+      if (FAST)
+        reinterpret_cast<float *>(slab)[row * kFastStride + kb] = __fmul_rn(static_cast<float>(dot), factor);
+      else
+        slab[row * kStride + kb] = make_float2(static_cast<float>(dot), factor);
+    }
+    __syncthreads();
+    if (set == 0)
+      load(1); // travels while the sums below run
+    float *mine_out = results + rank * 2 * kSetRows + set * kSetRows;
+    if (FAST) {
+      if (t < kSetRows * 8) {
+        const int row = t >> 3, j = t & 7;
+        const float *mine = reinterpret_cast<const float *>(slab) + row * kFastStride + j;
+        float acc = 0.0f;
+#pragma unroll
+        for (int p = 0; p < NB / 8; ++p)
+          acc = __fadd_rn(acc, mine[8 * p]);
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+        if (j == 0)
+          mine_out[row] = bf16_to_f32(f32_to_bf16(apply_activation(acc, activation)));
+      }
+    } else if (t < kSetRows) {
+      const float4 *mine = reinterpret_cast<const float4 *>(slab + t * kStride);
+      float acc = 0.0f;
+      for (int p = 0; p < NB / 2; p += 8) {
+        float4 pairs[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          pairs[u] = mine[p + u];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc = __fmaf_rn(pairs[u].x, pairs[u].y, acc);
+          acc = __fmaf_rn(pairs[u].z, pairs[u].w, acc);
+        }
+      }
+      mine_out[t] = bf16_to_f32(f32_to_bf16(apply_activation(acc, activation)));
+    }
+    __syncthreads(); // the slab is free again; after the second set this CTA's 32 results are complete
+  }
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (rank == 1 && t < 2 * kSetRows)
+    store_shared_cluster(results + 2 * kSetRows + t, 0, results[2 * kSetRows + t]);
+  cluster_sync_all();
+  if (rank == 0 && t < 32) {
+    const uint16_t bits = f32_to_bf16(__fmul_rn(results[t], results[2 * kSetRows + t]));
+    if (product)
+      product[row_base + t] = bits;
+    warp_quant_block(bf16_to_f32(bits), q_out, s_out, row_base + t, unit, t);
+  }
+}
+
 } // namespace
 
 // K = 2560: up to four matrices of the layer.  K = 4096 or 9216: one matrix with few enough rows
@@ -321,6 +435,32 @@ cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const 
   if (K == 4096)
     return launch_cols<128, 8>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
   return launch_cols<288, 9>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
+}
+
+bool gemv_swiglu_supported(int K, int64_t N) { return K == 2560 && N > 0 && N % 32 == 0; }
+
+cudaError_t launch_gemv_q8_swiglu(const int8_t *aq, const float *as, int K, const int8_t *gate_q, const uint16_t *gate_d,
+                                  const int8_t *up_q, const uint16_t *up_d, int64_t N, uint16_t *product, int8_t *q_out,
+                                  float *s_out, int flags, cudaStream_t stream) {
+  if (!gemv_swiglu_supported(K, N) || !q_out || !s_out)
+    return cudaErrorInvalidValue;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(N / 32 * 2));
+  config.blockDim = dim3(160);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = 2;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (flags & kGemvOverlapPrevious) ? 2 : 1;
+  if (flags & kGemvFast)
+    return cudaLaunchKernelEx(&config, gemv_q8_swiglu80_kernel<true>, aq, as, gate_q, gate_d, up_q, up_d, product, q_out, s_out);
+  return cudaLaunchKernelEx(&config, gemv_q8_swiglu80_kernel<false>, aq, as, gate_q, gate_d, up_q, up_d, product, q_out, s_out);
 }
 
 } // namespace llmcp_b200

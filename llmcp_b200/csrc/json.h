@@ -61,19 +61,49 @@ struct JsonReader {
         case 'r': out += '\r'; break;
         case 'b': out += '\b'; break;
         case 'f': out += '\f'; break;
-        case 'u':
-          if (p + 4 < end) {
-            unsigned code = 0;
-            for (int i = 1; i <= 4; ++i) {
-              char c = p[i];
-              code = code * 16 + (c >= '0' && c <= '9' ? c - '0' : (c | 32) >= 'a' && (c | 32) <= 'f' ? (c | 32) - 'a' + 10 : 0);
+        case 'u': {
+          // \uXXXX, a surrogate pair included, as UTF-8
+          auto hex4 = [&](const char *q, unsigned *code) {
+            *code = 0;
+            for (int i = 0; i < 4; ++i) {
+              const char c = q[i];
+              const int digit = c >= '0' && c <= '9' ? c - '0' : (c | 32) >= 'a' && (c | 32) <= 'f' ? (c | 32) - 'a' + 10 : -1;
+              if (digit < 0)
+                return false;
+              *code = *code * 16 + static_cast<unsigned>(digit);
             }
-            out += code < 128 ? static_cast<char>(code) : '?';
-            p += 4;
-          } else {
+            return true;
+          };
+          unsigned code = 0;
+          if (p + 4 >= end || !hex4(p + 1, &code)) {
             ok = false;
+            break;
+          }
+          p += 4;
+          if (code >= 0xd800 && code <= 0xdbff && p + 6 < end && p[1] == '\\' && p[2] == 'u') {
+            unsigned low = 0;
+            if (hex4(p + 3, &low) && low >= 0xdc00 && low <= 0xdfff) {
+              code = 0x10000 + ((code - 0xd800) << 10) + (low - 0xdc00);
+              p += 6;
+            }
+          }
+          if (code < 0x80) {
+            out += static_cast<char>(code);
+          } else if (code < 0x800) {
+            out += static_cast<char>(0xc0 | (code >> 6));
+            out += static_cast<char>(0x80 | (code & 0x3f));
+          } else if (code < 0x10000) {
+            out += static_cast<char>(0xe0 | (code >> 12));
+            out += static_cast<char>(0x80 | ((code >> 6) & 0x3f));
+            out += static_cast<char>(0x80 | (code & 0x3f));
+          } else {
+            out += static_cast<char>(0xf0 | (code >> 18));
+            out += static_cast<char>(0x80 | ((code >> 12) & 0x3f));
+            out += static_cast<char>(0x80 | ((code >> 6) & 0x3f));
+            out += static_cast<char>(0x80 | (code & 0x3f));
           }
           break;
+        }
         default: out += *p;
         }
         ++p;

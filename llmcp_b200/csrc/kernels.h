@@ -55,6 +55,13 @@ cudaError_t launch_gemv_q8_rows(const int8_t *aq, const float *as, int K, const 
 bool gemv_cols_supported(int K, const GemvJobs &jobs);
 cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const GemvJobs &jobs, int32_t *dots_out,
                                 cudaStream_t stream);
+// gate and up projections of the MLP (K = 2560, N % 32 == 0 rows each), SiLU on the gate, their
+// product rounded to bf16 (product, optional) and quantised to int8 blocks (q_out, s_out) in one
+// launch; the values of launch_gemv_q8 x 2 + launch_pointwise(mul).  flags: kGemvOverlapPrevious, kGemvFast.
+bool gemv_swiglu_supported(int K, int64_t N);
+cudaError_t launch_gemv_q8_swiglu(const int8_t *aq, const float *as, int K, const int8_t *gate_q, const uint16_t *gate_d,
+                                  const int8_t *up_q, const uint16_t *up_d, int64_t N, uint16_t *product, int8_t *q_out,
+                                  float *s_out, int flags, cudaStream_t stream);
 cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K, const int8_t *wq,
                                 const uint16_t *wd, int N, void *y, int y_dtype, int activation,
                                 int32_t *dots_out, cudaStream_t stream);
@@ -131,15 +138,21 @@ struct GdnBatch {
   int64_t ab;         // a and b rows
   int64_t state;      // recurrent state of a layer
 };
-// One token of causal_conv1d + gated_delta_net + gated_rms_norm (+ quantisation) in two launches;
-// the same values as the three general launchers above produce.  scratch: gdn_scratch_floats(1, ..).
+// One token of causal_conv1d + gated_delta_net + gated_rms_norm (+ quantisation) in two launches,
+// or in one (single_kernel, where gdn_decode_single_kernel_supported: a thread-block cluster per
+// key head exchanges the normalised q and k through distributed shared memory; conv_out is not
+// written then); the same values as the three general launchers above produce.  tree_sum (single
+// kernel only): the three 128-term sums as shuffle trees instead of in index order.
+// scratch: gdn_scratch_floats(1, ..).
 bool gdn_decode_supported(int kernel, int nk, int nv, int dk, int dv);
+bool gdn_decode_single_kernel_supported(int kernel, int nk, int nv, int dk, int dv);
 cudaError_t launch_gdn_decode(const uint16_t *qkv, const uint16_t *conv_w, uint16_t *conv_state, int kernel,
                               const uint16_t *a, const uint16_t *b, const void *a_log, int a_log_dtype,
                               const void *dt_bias, int dt_dtype, float *state, int nk, int nv, int dk, int dv,
                               int b_activated, const uint16_t *gate, const void *norm_w, int norm_w_dtype, float eps,
                               int gate_activated, float *scratch, uint16_t *conv_out, uint16_t *y, int8_t *q_out,
-                              float *s_out, cudaStream_t stream, int sequences = 1, const GdnBatch *strides = nullptr);
+                              float *s_out, cudaStream_t stream, int sequences = 1, const GdnBatch *strides = nullptr,
+                              int single_kernel = 0, int tree_sum = 0);
 // The start position is read from device memory (position_dev) so that a captured launch can be
 // replayed at another position; max_position bounds it (grid and scratch are sized for it).
 // rows_from_position: cos/sin are tables indexed by absolute position instead of the call's rows.

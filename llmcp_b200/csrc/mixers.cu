@@ -594,6 +594,226 @@ gdn_decode_step_kernel(const uint16_t *__restrict__ conv, const float *__restric
     warp_quant_block(bf16_to_f32(r), q_out, s_out, element, element / kBlock, v & 31);
 }
 
+// The same convolution in two halves: what does not depend on the kernel in front (the channel's
+// state rows and taps' weights) is fetched first, the new row is applied after the wait.
+struct ConvChannel {
+  uint16_t taps[kMaxConvKernel];
+  uint16_t weights[kMaxConvKernel];
+};
+
+__device__ __forceinline__ void conv_fetch(const uint16_t *__restrict__ w, const uint16_t *__restrict__ state, int C, int kernel,
+                                           int c, ConvChannel &ch) {
+#pragma unroll
+  for (int k = 0; k < kMaxConvKernel; ++k)
+    if (k < kernel) {
+      ch.weights[k] = w[c * kernel + k];
+      if (k < kernel - 1)
+        ch.taps[k] = state[static_cast<int64_t>(k) * C + c];
+    }
+}
+
+__device__ __forceinline__ float conv_apply(ConvChannel &ch, uint16_t x_new, uint16_t *__restrict__ state, int C, int kernel, int c) {
+  const int state_len = kernel - 1;
+#pragma unroll
+  for (int k = 0; k < kMaxConvKernel; ++k)
+    if (k == state_len)
+      ch.taps[k] = x_new;
+  float acc = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kMaxConvKernel; ++k)
+    if (k < kernel)
+      acc = __fadd_rn(acc, __fmul_rn(bf16_to_f32(ch.taps[k]), bf16_to_f32(ch.weights[k])));
+#pragma unroll
+  for (int k = 0; k + 1 < kMaxConvKernel; ++k)
+    if (k < state_len)
+      state[static_cast<int64_t>(k) * C + c] = ch.taps[k + 1];
+  return bf16_to_f32(f32_to_bf16(__fmul_rn(acc, d_sigmoid(acc))));
+}
+
+// Sum of `count` floats of shared memory as every thread of the CTA sees it afterwards:
+// ordered (thread 0 adds them in index order, the reference's order) or, with tree_sum, a
+// shuffle tree per warp and the warps' results in warp order.  count = blockDim.x = 128.
+__device__ __forceinline__ float cta_sum_128(float *values, float *result, int tree_sum) {
+  const int t = threadIdx.x;
+  if (tree_sum) {
+    float part = values[t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+    __syncthreads(); // every thread has read its value
+    if ((t & 31) == 0)
+      values[t >> 5] = part;
+    __syncthreads();
+    return __fadd_rn(__fadd_rn(values[0], values[1]), __fadd_rn(values[2], values[3]));
+  }
+  if (t == 0) {
+    float sum = 0.0f;
+    for (int d = 0; d < 128; d += 16) {
+      float4 sq[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        sq[u] = *reinterpret_cast<const float4 *>(values + d + 4 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        sum = __fadd_rn(sum, sq[u].x);
+        sum = __fadd_rn(sum, sq[u].y);
+        sum = __fadd_rn(sum, sq[u].z);
+        sum = __fadd_rn(sum, sq[u].w);
+      }
+    }
+    *result = sum;
+  }
+  __syncthreads();
+  return *result;
+}
+
+// The whole one-token mixer in one launch: a thread-block cluster per key head, one CTA per value
+// head of it, 128 threads (dk = dv = 128).  CTA 0 of the cluster convolves and normalises the key
+// head's q channels, CTA 1 its k channels (a single CTA does both when a key head serves one value
+// head), and each stores its 128 results into the shared memory of every CTA of the cluster; every
+// CTA convolves its own value channels and computes its head's beta and decay, then runs the
+// recurrence step, the gated RMSNorm and the quantisation as gdn_decode_step_kernel does.  The
+// arithmetic of every value is that of the two-kernel form (bit-identical when tree_sum == 0).
+template <int RATIO_MIN2>
+__global__ void __launch_bounds__(128)
+gdn_decode_fused_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ w, uint16_t *__restrict__ conv_state,
+                        int kernel, const uint16_t *__restrict__ a, const uint16_t *__restrict__ b,
+                        const void *__restrict__ a_log, int a_log_dtype, const void *__restrict__ dt_bias, int dt_dtype,
+                        int nk, int nv, int b_activated, float *__restrict__ state, const uint16_t *__restrict__ gate,
+                        const void *__restrict__ norm_w, int norm_w_dtype, float eps, int gate_activated, int tree_sum,
+                        uint16_t *__restrict__ y, int8_t *__restrict__ q_out, float *__restrict__ s_out,
+                        const GdnBatch batch) {
+  constexpr int DK = 128, DV = 128;
+  __shared__ __align__(16) float k_sm[DK];
+  __shared__ __align__(16) float q_sm[DK];
+  __shared__ __align__(16) float sq_sm[DV];
+  __shared__ float sum_sm;
+  const int h = blockIdx.x, t = threadIdx.x;
+  const int ratio = nv / nk;
+  const int kh = h / ratio, rank = h % ratio;
+  const int C = 2 * nk * DK + nv * DV;
+  const int64_t seq = blockIdx.y;
+  x += seq * C;
+  conv_state += seq * batch.conv_state;
+  a += seq * batch.ab;
+  b += seq * batch.ab;
+  state += seq * batch.state;
+  gate += seq * static_cast<int64_t>(nv) * DV;
+  // Nothing below up to the wait depends on the kernel in front: the head's state column, the
+  // channels' convolution state and weights, the norm weight, the per-head constants.
+  float *col = state + static_cast<int64_t>(h) * DK * DV + t;
+  float s[DK];
+#pragma unroll
+  for (int k = 0; k < DK; ++k)
+    s[k] = col[static_cast<int64_t>(k) * DV];
+  const float norm_weight = load_as_f32(norm_w, norm_w_dtype, t);
+  // channels of this thread: one or two of the key head's (by cluster rank), one value channel
+  const bool does_q = RATIO_MIN2 ? rank == 0 : true, does_k = RATIO_MIN2 ? rank == 1 : true;
+  const int cq = kh * DK + t, ck = nk * DK + kh * DK + t, cv = 2 * nk * DK + h * DV + t;
+  ConvChannel chq, chk, chv;
+  if (does_q)
+    conv_fetch(w, conv_state, C, kernel, cq, chq);
+  if (does_k)
+    conv_fetch(w, conv_state, C, kernel, ck, chk);
+  conv_fetch(w, conv_state, C, kernel, cv, chv);
+  const float dt = bf16_to_f32(f32_to_bf16(load_as_f32(dt_bias, dt_dtype, h)));
+  const float minus_exp_a = -d_exp(load_as_f32(a_log, a_log_dtype, h));
+  if (RATIO_MIN2) // every CTA of the cluster is running before anyone stores into its shared memory
+    cluster_sync_all();
+  grid_dependency_sync(true);
+  const float gv = bf16_to_f32(gate[static_cast<int64_t>(h) * DV + t]);
+  const uint16_t xq = does_q ? x[cq] : uint16_t(0), xk = does_k ? x[ck] : uint16_t(0), xv = x[cv];
+  const float bv = bf16_to_f32(b[h]), av = bf16_to_f32(a[h]);
+  if (does_q) {
+    const float v = conv_apply(chq, xq, conv_state, C, kernel, cq);
+    sq_sm[t] = __fmul_rn(v, v);
+    __syncthreads();
+    const float sum = cta_sum_128(sq_sm, &sum_sm, tree_sum);
+    float scale = d_rsqrt(__fadd_rn(sum, 1.0e-6f));
+    scale = __fmul_rn(scale, static_cast<float>(1.0 / sqrt(static_cast<double>(DK))));
+    const float n = __fmul_rn(v, scale);
+    if (RATIO_MIN2) {
+      for (int r = 0; r < ratio; ++r)
+        store_shared_cluster(q_sm + t, r, n);
+    } else {
+      q_sm[t] = n;
+    }
+  }
+  if (does_k) {
+    if (does_q)
+      __syncthreads(); // sq_sm and sum_sm are reused
+    const float v = conv_apply(chk, xk, conv_state, C, kernel, ck);
+    sq_sm[t] = __fmul_rn(v, v);
+    __syncthreads();
+    const float sum = cta_sum_128(sq_sm, &sum_sm, tree_sum);
+    const float n = __fmul_rn(v, d_rsqrt(__fadd_rn(sum, 1.0e-6f)));
+    if (RATIO_MIN2) {
+      for (int r = 0; r < ratio; ++r)
+        store_shared_cluster(k_sm + t, r, n);
+    } else {
+      k_sm[t] = n;
+    }
+  }
+  const float value = conv_apply(chv, xv, conv_state, C, kernel, cv);
+  const float bt = b_activated ? bv : d_sigmoid(bv);
+  // dt_bias is widened from bf16, A_log is read as f32 (LowerGatedDeltaNet.cpp:233-246).
+  const float softplus = d_log(__fadd_rn(1.0f, d_exp(__fadd_rn(av, dt))));
+  const float dc = d_exp(__fmul_rn(minus_exp_a, softplus));
+  if (RATIO_MIN2)
+    cluster_sync_all(); // q and k of the key head have arrived from the cluster's first two CTAs
+  else
+    __syncthreads();
+  float kv = 0.0f;
+#pragma unroll
+  for (int k4 = 0; k4 < DK; k4 += 4) {
+    const float4 kk = *reinterpret_cast<const float4 *>(k_sm + k4);
+    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s[k4 + u] = __fmul_rn(s[k4 + u], dc);
+      kv = __fadd_rn(kv, __fmul_rn(s[k4 + u], kv4[u]));
+    }
+  }
+  const float delta = __fmul_rn(__fsub_rn(value, kv), bt);
+  float o = 0.0f;
+#pragma unroll
+  for (int k4 = 0; k4 < DK; k4 += 4) {
+    const float4 kk = *reinterpret_cast<const float4 *>(k_sm + k4);
+    const float4 qq = *reinterpret_cast<const float4 *>(q_sm + k4);
+    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+    const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s[k4 + u] = __fadd_rn(s[k4 + u], __fmul_rn(kv4[u], delta));
+      o = __fadd_rn(o, __fmul_rn(s[k4 + u], qv4[u]));
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < DK; ++k)
+    col[static_cast<int64_t>(k) * DV] = s[k];
+  // gated RMSNorm over the head (LowerToLinalg.cpp:655-718, DecodeNormalization.cpp:118-131)
+  const float xo = bf16_to_f32(f32_to_bf16(o));
+  __syncthreads(); // sq_sm may still be read by a slower warp of the q/k norm
+  sq_sm[t] = __fmul_rn(xo, xo);
+  __syncthreads();
+  const float sum = cta_sum_128(sq_sm, &sum_sm, tree_sum);
+  const float rstd = d_rsqrt(__fadd_rn(__fdiv_rn(sum, static_cast<float>(DV)), eps));
+  const int64_t element = (seq * nv + h) * DV + t;
+  const float silu = gate_activated ? gv : __fmul_rn(gv, d_sigmoid(gv));
+  float r = __fmul_rn(xo, silu);
+  r = __fmul_rn(r, norm_weight);
+  r = __fmul_rn(r, rstd);
+  const uint16_t bits = f32_to_bf16(r);
+  if (y)
+    y[element] = bits;
+  if (q_out)
+    warp_quant_block(bf16_to_f32(bits), q_out, s_out, element, element / kBlock, t & 31);
+}
+
+bool gdn_decode_single_kernel_supported(int kernel, int nk, int nv, int dk, int dv) {
+  return kernel >= 1 && kernel <= kMaxConvKernel && dk == 128 && dv == 128 && nk > 0 && nv % nk == 0 && nv / nk <= 8;
+}
+
 bool gdn_decode_supported(int kernel, int nk, int nv, int dk, int dv) {
   return kernel >= 1 && kernel <= kMaxConvKernel && dk == 128 && dv % 32 == 0 && dv >= 32 && dv <= 256 && nk > 0 &&
          nv % nk == 0;
@@ -604,10 +824,23 @@ cudaError_t launch_gdn_decode(const uint16_t *qkv, const uint16_t *conv_w, uint1
                               const void *dt_bias, int dt_dtype, float *state, int nk, int nv, int dk, int dv,
                               int b_activated, const uint16_t *gate, const void *norm_w, int norm_w_dtype, float eps,
                               int gate_activated, float *scratch, uint16_t *conv_out, uint16_t *y, int8_t *q_out,
-                              float *s_out, cudaStream_t stream, int sequences, const GdnBatch *strides) {
+                              float *s_out, cudaStream_t stream, int sequences, const GdnBatch *strides, int single_kernel,
+                              int tree_sum) {
   if (!gdn_decode_supported(kernel, nk, nv, dk, dv) || sequences < 1 || (sequences > 1 && !strides))
     return cudaErrorInvalidValue;
   const GdnBatch batch = strides ? *strides : GdnBatch{};
+  if (single_kernel && gdn_decode_single_kernel_supported(kernel, nk, nv, dk, dv)) {
+    const int ratio = nv / nk;
+    if (ratio == 1)
+      launch_chained(gdn_decode_fused_kernel<0>, dim3(nv, sequences), dim3(128), 0, stream, qkv, conv_w, conv_state, kernel, a, b,
+                     a_log, a_log_dtype, dt_bias, dt_dtype, nk, nv, b_activated, state, gate, norm_w, norm_w_dtype, eps,
+                     gate_activated, tree_sum, y, q_out, s_out, batch);
+    else
+      launch_chained_cluster(gdn_decode_fused_kernel<1>, dim3(nv, sequences), dim3(128), 0, stream, ratio, qkv, conv_w, conv_state,
+                             kernel, a, b, a_log, a_log_dtype, dt_bias, dt_dtype, nk, nv, b_activated, state, gate, norm_w,
+                             norm_w_dtype, eps, gate_activated, tree_sum, y, q_out, s_out, batch);
+    return cudaGetLastError();
+  }
   float *qn = scratch;
   float *kn = qn + nk * dk;
   float *beta = kn + nk * dk;

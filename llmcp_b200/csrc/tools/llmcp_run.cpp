@@ -1,0 +1,171 @@
+// llmcp-run, AOT half: the generation driver of tools/llmcp-run/llmcp-run.cpp:626-704 for AOT ABI v2
+// libraries (prefill, greedy decode until --max-new-tokens or the end-of-turn token, text streamed
+// through the ByteLevel streaming decoder, then the `tokens:` line; without new tokens the
+// `aot logits: N next T` line), on top of this repository's container reader.
+//
+//   llmcp-run --weights weights.bin --aot libllmcp_b200.so [--tokens ID | --token-ids a,b,c]
+//             [--tokenizer tokenizer.json] [--max-new-tokens N] [--eos-token ID] [--dump-logits]
+//             [--synthetic SEED]
+//   llmcp-run --text 'Hello' [--chat] [--system S] [--no-thinking] --print-prompt
+//
+// Prompts are token ids: encoding text needs the tokenizer's BPE merges and pre-tokeniser, which
+// are not part of this build (the reference's `--tokenize-only` prints the ids of a text).
+// --print-prompt writes the text that would be encoded (with --chat: the Qwen chat template around
+// --text, llmcp-run.cpp:608-624) and exits.  The reference's interpreter half (no --aot) is not here.
+
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+
+#include "../text.h"
+#include "aot_host.h"
+
+using namespace llmcp_b200;
+using namespace llmcp_b200::host;
+
+int main(int argc, char **argv) {
+  std::string weights = "build/weights.bin", aot, tokenizer_path, text, system_prompt, ids_text;
+  int64_t token = 9419, max_new_tokens = 0, eos_override = -2;
+  bool chat = false, no_thinking = false, dump_logits = false, print_prompt = false, synthetic = false;
+  uint64_t seed = 0;
+  for (int i = 1; i < argc; ++i) {
+    const std::string a = argv[i];
+    auto value = [&](const char *name) -> const char * {
+      const std::string eq = std::string(name) + "=";
+      if (a.rfind(eq, 0) == 0)
+        return argv[i] + eq.size();
+      if (a == name && i + 1 < argc)
+        return argv[++i];
+      return nullptr;
+    };
+    if (const char *v = value("--weights")) weights = v;
+    else if (const char *v = value("--aot")) aot = v;
+    else if (const char *v = value("--tokenizer")) tokenizer_path = v;
+    else if (const char *v = value("--tokens")) token = std::atoll(v);
+    else if (const char *v = value("--token-ids")) ids_text = v;
+    else if (const char *v = value("--text")) text = v;
+    else if (const char *v = value("--system")) system_prompt = v;
+    else if (const char *v = value("--max-new-tokens")) max_new_tokens = std::atoll(v);
+    else if (const char *v = value("--eos-token")) eos_override = std::atoll(v);
+    else if (const char *v = value("--synthetic")) { synthetic = true; seed = std::strtoull(v, nullptr, 10); }
+    else if (a == "--chat") chat = true;
+    else if (a == "--no-thinking") no_thinking = true;
+    else if (a == "--dump-logits") dump_logits = true;
+    else if (a == "--print-prompt") print_prompt = true;
+    else { std::fprintf(stderr, "llmcp-run: unknown option %s\n", a.c_str()); return 1; }
+  }
+  if (print_prompt) {
+    const std::string prompt = chat ? make_chat_prompt(text, system_prompt, !no_thinking) : text;
+    std::fwrite(prompt.data(), 1, prompt.size(), stdout);
+    return 0;
+  }
+  if (!text.empty()) {
+    std::fprintf(stderr, "llmcp-run: text prompts need the tokenizer's encoder, which this build does not have; "
+                         "pass --token-ids (see --print-prompt)\n");
+    return 1;
+  }
+  if (aot.empty()) {
+    std::fprintf(stderr, "llmcp-run: --aot is required (the interpreter half is not part of this build)\n");
+    return 1;
+  }
+  std::vector<int64_t> tokens;
+  if (!ids_text.empty()) {
+    std::stringstream stream(ids_text);
+    std::string item;
+    while (std::getline(stream, item, ',')) {
+      char *end = nullptr;
+      const long long id = std::strtoll(item.c_str(), &end, 10);
+      if (item.empty() || *end) {
+        std::fprintf(stderr, "llmcp-run: --token-ids wants comma-separated integers\n");
+        return 1;
+      }
+      tokens.push_back(id);
+    }
+  } else {
+    tokens.push_back(token);
+  }
+  if (max_new_tokens < 0) {
+    std::fprintf(stderr, "llmcp-run: max-new-tokens must be >= 0\n");
+    return 1;
+  }
+
+  ByteLevelVocab vocab;
+  bool have_vocab = false;
+  int64_t eos = -1;
+  if (!tokenizer_path.empty()) {
+    std::ifstream file(tokenizer_path, std::ios::binary);
+    std::stringstream blob;
+    blob << file.rdbuf();
+    if (!file) {
+      std::fprintf(stderr, "llmcp-run: cannot read %s\n", tokenizer_path.c_str());
+      return 1;
+    }
+    const std::string json = blob.str();
+    if (const std::string error = vocab.load(json.data(), json.size()); !error.empty()) {
+      std::fprintf(stderr, "llmcp-run: %s\n", error.c_str());
+      return 1;
+    }
+    have_vocab = true;
+    eos = vocab.token_to_id("<|im_end|>");
+  }
+  if (eos_override != -2)
+    eos = eos_override;
+
+  Runtime runtime;
+  if (synthetic && access(weights.c_str(), R_OK) != 0) {
+    const uint64_t bytes = synthetic_container_bytes(runtime.dims, nullptr);
+    std::vector<uint8_t> file(bytes);
+    const std::string error = fill_synthetic_container(runtime.dims, seed, file.data(), bytes);
+    FILE *out = error.empty() ? std::fopen(weights.c_str(), "wb") : nullptr;
+    if (!out || std::fwrite(file.data(), 1, bytes, out) != bytes) {
+      std::fprintf(stderr, "llmcp-run: cannot write %s %s\n", weights.c_str(), error.c_str());
+      return 1;
+    }
+    std::fclose(out);
+  }
+  Arena arena;
+  if (const std::string error = arena.load(weights); !error.empty()) {
+    std::fprintf(stderr, "llmcp-run: %s\n", error.c_str());
+    return 1;
+  }
+  const int64_t prompt_tokens = static_cast<int64_t>(tokens.size());
+  if (!runtime.init(aot, prompt_tokens + max_new_tokens + 16))
+    return 1;
+  std::vector<float> logits;
+  if (!runtime.forward(arena, tokens, 0, prompt_tokens, logits))
+    return 1;
+  std::vector<int64_t> generated;
+  ByteLevelStreamingDecoder decoder(vocab);
+  auto emit = [&](const std::string &chunk) {
+    std::fwrite(chunk.data(), 1, chunk.size(), stdout);
+    std::fflush(stdout);
+  };
+  if (max_new_tokens > 0)
+    emit("output: ");
+  for (int64_t i = 0; i < max_new_tokens; ++i) {
+    const int64_t next = argmax(logits);
+    if (next == eos)
+      break;
+    generated.push_back(next);
+    if (have_vocab)
+      emit(decoder.append(static_cast<int32_t>(next)));
+    const int64_t position = prompt_tokens + static_cast<int64_t>(generated.size()) - 1;
+    if (!runtime.forward(arena, {next}, position, position + 1, logits))
+      return 1;
+  }
+  if (have_vocab)
+    emit(decoder.finish());
+  if (!generated.empty()) {
+    std::printf("\ntokens:");
+    for (int64_t id : generated)
+      std::printf(" %lld", static_cast<long long>(id));
+    std::printf("\n");
+  } else {
+    std::printf("aot logits: %zu next %lld\n", logits.size(), static_cast<long long>(argmax(logits)));
+  }
+  if (dump_logits)
+    for (float v : logits)
+      std::printf("%g\n", v);
+  return 0;
+}

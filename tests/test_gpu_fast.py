@@ -131,7 +131,11 @@ def test_attention_decode_fast_long_context(fast_mode):
     got, _ = L.ops.attention(qg, k, v, norm, norm, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
     want, _ = oracle.attention(qg, k, v, norm, norm, cos[None], sin[None], cache, position, nh, nkv, hd, rot)
     ulps = bf16_ulps(got, want)
-    assert ulps.max() <= 2 and (ulps != 0).mean() < 0.05, (ulps.max(), (ulps != 0).mean())
+    # 65 partial results per head are merged in another order than the key order: a bf16 step or two
+    # where that moves a rounding; more steps only on outputs that cancel to nearly zero
+    error, scale = np.abs(f(got) - f(want)), np.abs(f(want)).max()
+    assert ((ulps <= 2) | (error <= scale * 2.0 ** -9)).all(), (ulps.max(), error.max(), scale)
+    assert (ulps != 0).mean() < 0.05, (ulps != 0).mean()
 
 
 SMALL = dict(hidden=256, intermediate=512, vocab=2048, layers=8, full_interval=4, heads=4, kv_heads=2,

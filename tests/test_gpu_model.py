@@ -89,6 +89,37 @@ def test_engine_matches_aot_and_oracle_state():
     engine.close()
 
 
+@pytest.mark.parametrize("heads", [(2, 8), (4, 8), (8, 8)])
+def test_one_launch_recurrent_layer_matches_oracle(monkeypatch, heads):
+    """LLMCP_B200_FUSE_MIXER=2: convolution, q/k norms, recurrence step, gated norm and quantisation
+    of a one-token gated-delta-net layer in one launch (a thread-block cluster per key head: 4, 2
+    and 1 value heads per key head).  Same tokens and state as the oracle."""
+    nk, nv = heads
+    d = L.default_dims().copy(**dict(SMALL, lin_k_heads=nk, lin_v_heads=nv))
+    prompt = [17, 5, 900, 2047, 0, 33, 33]
+    data = L.synthetic_container(d, 5)
+    arena = L.Arena().from_buffer(data)
+    model = oracle.Model(data, arena.manifest, oracle_dims(d))
+    state = model.new_state(16)
+
+    def cos_sin(pos, n):
+        rows = [L.make_cos_sin(pos + t, d.rotary, d.rope_theta) for t in range(n)]
+        return dict(cos=np.stack([r[0] for r in rows]), sin=np.stack([r[1] for r in rows]))
+
+    want = [oracle.argmax(model.forward(state, prompt, 0, **cos_sin(0, len(prompt))))]
+    for step in range(5):
+        want.append(oracle.argmax(model.forward(state, [want[-1]], len(prompt) + step, **cos_sin(len(prompt) + step, 1))))
+    monkeypatch.setenv("LLMCP_B200_FUSE_MIXER", "2")
+    engine = L.Engine(data, d, capacity=16)
+    _, token = engine.forward(prompt, 0)
+    generated, _ = engine.generate(token, len(prompt), 5)
+    assert [token] + generated.tolist() == want
+    dev = engine.read_state()
+    assert np.array_equal(dev["delta"].view(np.uint32), state["delta"].view(np.uint32))
+    assert np.array_equal(dev["conv"], state["conv"])
+    engine.close()
+
+
 def test_packed_checkpoint_matches_oracle(tmp_path):
     """A checkpoint packed by this repository's llmcp-pack, with random norm gains, A_log and
     dt_bias (the synthetic model has them at their neutral values), through the AOT entries."""

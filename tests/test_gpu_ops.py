@@ -335,6 +335,59 @@ def test_gemv_kernel_variants(N, K):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"flags {flags}"
 
 
+@pytest.mark.parametrize("N", [9216, 1152, 64])
+def test_gemv_swiglu_one_launch(N):
+    """gate and up projections, SiLU, product and the product's int8 quantisation in one launch:
+    bit for bit what the oracle's linear(silu) x linear -> mul -> act_quant chain gives (exact form),
+    and within the fast form's bar (a bf16 step of the product on near-ties)."""
+    import ctypes as C
+    torch = pytest.importorskip("torch")
+    K = 2560
+    rng = np.random.default_rng(N)
+    packed = [oracle.pack_q8_0_p4((rng.standard_normal((N, K)) * 0.02).astype(np.float32)) for _ in range(2)]
+    x = rand_bf16(rng, 1, K)
+    gate = oracle.linear_q8(x, packed[0], N, activation="silu")
+    up = oracle.linear_q8(x, packed[1], N)
+    want = oracle.pointwise(gate, up, "mul")
+    want_q, want_s = oracle.act_quant(want)
+    lib = L.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    planes = []
+    for records in packed:
+        wq = torch.empty((N, K), dtype=torch.int8, device="cuda")
+        wd = torch.empty((N, K // 32), dtype=torch.float16, device="cuda")
+        assert lib.llmcp_dev_repack_q8(ptr(torch.from_numpy(records).cuda()), C.c_int64(N), C.c_int64(K), ptr(wq), ptr(wd), stream) == 0
+        planes += [wq, wd]
+    xd = torch.from_numpy(x.view(np.int16)).cuda()
+    aq = torch.empty(K, dtype=torch.int8, device="cuda")
+    scales = torch.empty(K // 32, dtype=torch.float32, device="cuda")
+    assert lib.llmcp_dev_act_quant(ptr(xd), 1, C.c_int64(1), C.c_int64(K), ptr(aq), ptr(scales), stream) == 0
+    for flags in (0, 1, 16, 17):
+        product = torch.zeros(N, dtype=torch.int16, device="cuda")
+        q = torch.zeros(N, dtype=torch.int8, device="cuda")
+        s = torch.zeros(N // 32, dtype=torch.float32, device="cuda")
+        rc = lib.llmcp_dev_gemv_q8_swiglu(ptr(aq), ptr(scales), C.c_int64(K), ptr(planes[0]), ptr(planes[1]), ptr(planes[2]),
+                                          ptr(planes[3]), C.c_int64(N), ptr(product), ptr(q), ptr(s), flags, stream)
+        assert rc == 0, L.last_error()
+        torch.cuda.synchronize()
+        got = product.cpu().numpy().view(np.uint16)[None]
+        if flags & 16:
+            steps = np.abs(got.astype(np.int32) - want.astype(np.int32))
+            assert steps.max() <= 2 and (steps != 0).mean() < 0.05, (flags, steps.max(), (steps != 0).mean())
+            again_q, again_s = oracle.act_quant(got)  # the quantisation itself is exact on the kernel's own product
+            assert np.array_equal(q.cpu().numpy()[None], again_q) and np.array_equal(s.cpu().numpy()[None], again_s)
+        else:
+            assert np.array_equal(got, want), flags
+            assert np.array_equal(q.cpu().numpy()[None], want_q), flags
+            assert np.array_equal(s.cpu().numpy()[None].view(np.uint32), want_s.view(np.uint32)), flags
+    # refusals: the product may not overwrite the input, other K
+    assert lib.llmcp_dev_gemv_q8_swiglu(ptr(aq), ptr(scales), C.c_int64(K), ptr(planes[0]), ptr(planes[1]), ptr(planes[2]),
+                                        ptr(planes[3]), C.c_int64(N), None, ptr(aq), ptr(s), 0, stream) != 0
+    assert lib.llmcp_dev_gemv_q8_swiglu(ptr(aq), ptr(scales), C.c_int64(4096), ptr(planes[0]), ptr(planes[1]), ptr(planes[2]),
+                                        ptr(planes[3]), C.c_int64(N), None, ptr(q), ptr(s), 0, stream) != 0
+
+
 def _tma_gemm_setup(torch, M, N, K, seed):
     """Operand and scale planes of the TMA-fed tensor-core GEMM on the device, and the oracle's result."""
     import ctypes as C
