@@ -620,7 +620,8 @@ int llmcp_op_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint
         scratch(gdn_scratch_floats(S, static_cast<int>(nk), static_cast<int>(nv), static_cast<int>(dk)) * 4);
     cuda_check(launch_gated_delta_net(dc.as<uint16_t>(), da.as<uint16_t>(), db.as<uint16_t>(), dl.p, kF32, dt.p, kBF16,
                                       ds.as<float>(), S, static_cast<int>(nk), static_cast<int>(nv), static_cast<int>(dk),
-                                      static_cast<int>(dv), b_activated, scratch.as<float>(), dout.as<uint16_t>(), nullptr),
+                                      static_cast<int>(dv), b_activated, scratch.as<float>(), dout.as<uint16_t>(), nullptr, 0,
+                                      default_mode() == kModeFast ? 1 : 0),
                "gated_delta_net");
     g_launches += 2;
     cuda_check(cudaDeviceSynchronize(), "gated_delta_net");
@@ -644,9 +645,20 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
         dqn(static_cast<size_t>(hd) * 2, q_norm), dkn(static_cast<size_t>(hd) * 2, k_norm), dcos(static_cast<size_t>(S) * rot * 4, cos),
         dsin(static_cast<size_t>(S) * rot * 4, sin), dcache(static_cast<size_t>(2) * nkv * cap * hd * 2, cache),
         dout(static_cast<size_t>(S) * nh * hd * 2),
-        scratch(std::max(attn_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(hd), position),
-                         attn_fast_scratch_bytes(static_cast<int>(nh), static_cast<int>(hd), position + S - 1))),
-        dpos(8, &position);
+        scratch(std::max({attn_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(hd), position),
+                          attn_fast_scratch_bytes(static_cast<int>(nh), static_cast<int>(hd), position + S - 1),
+                          attention_prefill_tc_scratch_bytes(S, static_cast<int>(nh), static_cast<int>(nkv), cap)})),
+        dpos(8, &position), dstatus(4);
+    const bool tensor_cores = default_mode() == kModeFast && S > 1 &&
+                              attention_prefill_tc_supported(static_cast<int>(nh), static_cast<int>(nkv), static_cast<int>(hd));
+    if (tensor_cores) {
+      cuda_check(cudaMemset(dstatus.p, 0, 4), "memset");
+      cuda_check(launch_attention_prefill_tc(dqg.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(), dqn.as<uint16_t>(),
+                                             dkn.as<uint16_t>(), dcos.as<float>(), dsin.as<float>(), 0, dcache.as<uint16_t>(),
+                                             dpos.as<int64_t>(), position, S, static_cast<int>(nh), static_cast<int>(nkv),
+                                             static_cast<int>(hd), static_cast<int>(rot), cap, scratch.p, dout.as<uint16_t>(),
+                                             nullptr, nullptr, dstatus.as<int>(), nullptr), "attention (tensor cores)");
+    } else
     if (default_mode() == kModeFast && S == 1 &&
         attention_decode_fast_supported(static_cast<int>(nh), static_cast<int>(nkv), static_cast<int>(hd))) {
       cuda_check(launch_attention_decode_fast(dqg.as<uint16_t>(), dk.as<uint16_t>(), dv.as<uint16_t>(), dqn.as<uint16_t>(),
@@ -662,6 +674,12 @@ int llmcp_op_attention(const uint16_t *qg, const uint16_t *k, const uint16_t *v,
                                 scratch.p, dout.as<uint16_t>(), nullptr, nullptr, nullptr), "attention");
     g_launches += 3;
     cuda_check(cudaDeviceSynchronize(), "attention");
+    if (tensor_cores) {
+      int status = 0;
+      dstatus.to_host(&status, 4);
+      if (status)
+        throw std::runtime_error("attention: a bounded wait inside the tensor-core kernel ran out");
+    }
     dout.to_host(out, dout.bytes);
     dcache.to_host(cache, dcache.bytes);
   });

@@ -219,6 +219,8 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     gemv_flags_ = std::atoi(flag);
   if (const char *flag = std::getenv("LLMCP_B200_FUSE_MIXER"))
     fuse_decode_mixer_ = std::atoi(flag);
+  if (const char *flag = std::getenv("LLMCP_B200_TC_ATTENTION"))
+    tc_prefill_attention_ = std::atoi(flag) != 0;
   if (const char *flag = std::getenv("LLMCP_B200_FUSE_SWIGLU"))
     fuse_swiglu_ = std::atoi(flag) != 0;
   check(cudaMemsetAsync(gemm_error_, 0, 4, stream_), "memset");
@@ -516,10 +518,12 @@ void Engine::ensure_workspace(int64_t S, int64_t position) {
   const ModelDims &c = dims_;
   const ModelDims &m = local_;
   // sized for tokens of one sequence and for one token each of S sequences (a batched step)
-  const size_t need_attn =
+  size_t need_attn =
       std::max(attn_scratch_bytes(S, static_cast<int>(m.heads), static_cast<int>(m.head_dim), position),
                attn_fast_scratch_bytes(static_cast<int>(m.heads), static_cast<int>(m.head_dim), position + S - 1,
                                        static_cast<int>(std::min<int64_t>(S, batch_))));
+  if (attention_prefill_tc_supported(static_cast<int>(m.heads), static_cast<int>(m.kv_heads), static_cast<int>(m.head_dim)))
+    need_attn = std::max(need_attn, attention_prefill_tc_scratch_bytes(S, static_cast<int>(m.heads), static_cast<int>(m.kv_heads), capacity_));
   if (S <= ws_tokens_ && need_attn <= attn_scratch_bytes_)
     return;
   if (tp_ && S > max_tokens_)
@@ -802,7 +806,8 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
         check(launch_causal_conv1d(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, S, C,
                                    static_cast<int>(c.conv_kernel), convd_, stream_), "causal_conv1d");
         check(launch_gated_delta_net(convd_, a_ + head0, b_ + head0, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype,
-                                     delta_state, S, nk, nv, dk, dv, 1, gdn_scratch_, gdn_, stream_, nv_all), "gated_delta_net");
+                                     delta_state, S, nk, nv, dk, dv, 1, gdn_scratch_, gdn_, stream_, nv_all, mode_ == kModeFast ? 1 : 0),
+              "gated_delta_net");
         check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(m.value_dim()), dv,
                                     c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
         launches_ += 5;
@@ -820,6 +825,12 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                            static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
                                            cache, position_dev_, position, nh, nkv, hd, static_cast<int>(c.rotary), capacity_,
                                            attn_scratch_, attn_, aq_, as_, stream_, sequences, cache_stride), "attention (fast)");
+      } else if (mode_ == kModeFast && S > 1 && !rows_are_sequences && tc_prefill_attention_ &&
+                 attention_prefill_tc_supported(nh, nkv, hd)) {
+        check(launch_attention_prefill_tc(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
+                                          static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position, cache,
+                                          position_dev_, position, S, nh, nkv, hd, static_cast<int>(c.rotary), capacity_,
+                                          attn_scratch_, attn_, aq_, as_, gemm_error_, stream_), "attention (tensor cores)");
       } else {
         check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position, cache,

@@ -233,6 +233,7 @@ private:
   float *ast_ = nullptr;  // [max K / 32][pitch] their scales, block-major
   int *gemm_error_ = nullptr; // device flag raised by a timed-out wait in the GEMM
   int gemv_flags_ = 3; // kGemvOverlapPrevious | kGemvPrefetchL2
+  bool tc_prefill_attention_ = true; // fast mode, more than one token: attention contractions on the tensor cores
   bool fuse_swiglu_ = true;   // one-token MLP: gate, up, product and quantisation in one launch
   // one-token gated-delta-net layers: 0 five launches, 1 two, 2 one (a cluster per key head; measured
   // slower than two: the recurrent state can then be fetched only after the projections have finished)

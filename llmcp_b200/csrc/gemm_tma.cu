@@ -40,10 +40,13 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace llmcp_b200 {
 
 namespace {
+
+using namespace tc;
 
 constexpr int kTileM = 128;
 constexpr int kTileN = 128;
@@ -64,72 +67,6 @@ template <bool F16> struct Form {
   static constexpr int kStageBytes = 2 * kOperandBytes + 2 * kScaleBytes; // 34 KB / 36 KB, multiples of 1024
   static constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + kBarrierBytes;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-  asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-
-// Waits for the phase with the given parity; gives up when `abort_flag` is raised or after `limit`
-// polls (and then raises it).  Returns false on failure.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t limit) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < limit; ++spin) {
-    uint32_t done;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(done)
-                 : "r"(addr), "r"(parity)
-                 : "memory");
-    if (done)
-      return true;
-    if ((spin & 63) == 63 && *abort_flag)
-      return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-// The same wait without the abort protocol (used while leaving after an abort).
-__device__ __forceinline__ bool mbar_wait_quiet(uint64_t *bar, uint32_t parity, uint32_t limit) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < limit; ++spin) {
-    uint32_t done;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(done)
-                 : "r"(addr), "r"(parity)
-                 : "memory");
-    if (done)
-      return true;
-  }
-  return false;
-}
-
-// Tiled 2-D load of one box; completion is counted in bytes on `bar`.
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                   smem_u32(dst)),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-               : "memory");
-}
-
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_address) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_address & 0x3ffffu) >> 4); // start address
-  d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused with swizzle)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset: next 8-row group
-  d |= static_cast<uint64_t>(1) << 46;                        // descriptor version for sm_100
-  d |= static_cast<uint64_t>(2) << 61;                        // SWIZZLE_128B
-  return d;
-}
 
 // kind::f16: f16 x f16 -> f32, both operands K-major, M = 128, N = 128, K = 16 per instruction.
 constexpr uint32_t kInstructionF16 = (1u << 4) | ((kTileN >> 3) << 17) | ((kTileM >> 4) << 24);
@@ -162,27 +99,6 @@ __device__ __forceinline__ void fma2(float &c0, float &c1, float a0, float a1, f
   asm("{ .reg .b64 a, b, c; mov.b64 a, {%2, %3}; mov.b64 b, {%4, %5}; mov.b64 c, {%0, %1}; fma.rn.f32x2 c, a, b, c; mov.b64 {%0, %1}, c; }"
       : "+f"(c0), "+f"(c1)
       : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-
-__device__ __forceinline__ void mma_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// 32 consecutive 32-bit columns of this thread's lane.
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 struct Barriers {
@@ -443,25 +359,6 @@ __global__ void weights_to_f16_kernel(const int8_t *__restrict__ wq, const uint1
       wst[b * N + n] = f16_bits_to_f32(wd[i]);
     }
   }
-}
-
-using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled through the runtime's driver entry point table (no link against libcuda).
-EncodeTiled encode_tiled() {
-  static std::mutex mutex;
-  static EncodeTiled fn = nullptr;
-  std::lock_guard<std::mutex> lock(mutex);
-  if (!fn) {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiled>(p);
-  }
-  return fn;
 }
 
 // rows x K operand plane, K contiguous: boxes of 128 rows x 128 bytes of K (64 f16 or 128 int8),

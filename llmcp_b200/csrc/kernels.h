@@ -130,7 +130,8 @@ size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk);
 cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b, const void *a_log,
                                    int a_log_dtype, const void *dt_bias, int dt_dtype, float *state, int64_t S,
                                    int nk, int nv, int dk, int dv, int b_activated, float *scratch,
-                                   uint16_t *out, cudaStream_t stream, int ab_stride = 0 /* row pitch of a and b; 0 = nv */);
+                                   uint16_t *out, cudaStream_t stream, int ab_stride = 0 /* row pitch of a and b; 0 = nv */,
+                                   int fast = 0 /* S > 1, dk = 128: row quarters per lane, fused multiply-adds */);
 // A batch of independent sequences, one token each, through the one-token kernels: element strides
 // between consecutive sequences' buffers (inputs and outputs are rows of a [sequences, width] matrix).
 struct GdnBatch {
@@ -179,6 +180,17 @@ cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, cons
 // heads of one KV head) and a second kernel merges the splits, applies the sigmoid gate and
 // quantises for o_proj.  The softmax is the same function as the reference's tile-ordered one
 // but sums in another order, so results agree to f32 rounding, not bit for bit.
+// Fast mode of the prefill attention (S > 1, head_dim 256): the same prepare kernel, then both
+// contractions on the tensor cores with the softmax weights rounded to bf16 (attn_prefill.cu).
+// scratch: attention_prefill_tc_scratch_bytes.  error_flag (device int, optional) is set to 1 if a
+// bounded wait inside the kernel ran out; three launches.
+bool attention_prefill_tc_supported(int nh, int nkv, int hd);
+size_t attention_prefill_tc_scratch_bytes(int64_t S, int nh, int nkv, int64_t cap);
+cudaError_t launch_attention_prefill_tc(const uint16_t *qg, const uint16_t *k, const uint16_t *v, const uint16_t *q_norm,
+                                        const uint16_t *k_norm, const float *cos, const float *sin, int rows_from_position,
+                                        uint16_t *cache, const int64_t *position_dev, int64_t max_position, int64_t S, int nh,
+                                        int nkv, int hd, int rot, int64_t cap, void *scratch, uint16_t *out, int8_t *q_out,
+                                        float *s_out, int *error_flag, cudaStream_t stream, uint32_t spin_limit = 0);
 bool attention_decode_fast_supported(int nh, int nkv, int hd);
 size_t attn_fast_scratch_bytes(int nh, int hd, int64_t max_position, int sequences = 1);
 cudaError_t launch_attention_decode_fast(const uint16_t *qg, const uint16_t *k, const uint16_t *v,

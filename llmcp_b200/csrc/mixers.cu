@@ -362,6 +362,133 @@ gdn_recurrence_pipelined_kernel(const uint16_t *__restrict__ conv, const float *
   }
 }
 
+// Fast form of the recurrence for calls of more than one token: the same two-tokens-in-flight loop,
+// but a warp owns 8 value columns and each column's 128 state rows are shared by four lanes (32 rows
+// each), so the two dependent chains per token are 32 long instead of 128 and end in two shuffles;
+// multiply and add are fused.  The sums therefore differ from the reference's order (row quarters
+// are added as a tree) and from its roundings (fused multiply-adds): results agree with the exact
+// kernels to f32 rounding noise, not bit for bit.  grid (value head, dv / 8), 32 threads.
+template <int DK>
+__global__ void __launch_bounds__(32)
+gdn_recurrence_split_kernel(const uint16_t *__restrict__ conv, const float *__restrict__ qn,
+                            const float *__restrict__ kn, const float *__restrict__ beta,
+                            const float *__restrict__ decay, float *__restrict__ state, int64_t S, int nk,
+                            int nv, int dv, uint16_t *__restrict__ out) {
+  constexpr int kRows = DK / 4; // state rows per lane
+  grid_dependency_sync();
+  const int h = blockIdx.x;
+  const int lane = threadIdx.x, c = lane & 7, quarter = lane >> 3;
+  const int v = blockIdx.y * 8 + c;
+  const int kh = h / (nv / nk);
+  const int64_t channels = 2 * static_cast<int64_t>(nk) * DK + static_cast<int64_t>(nv) * dv;
+  float *col = state + static_cast<int64_t>(h) * DK * dv + static_cast<int64_t>(quarter) * kRows * dv + v;
+  __shared__ __align__(16) float kq_sm[2][2 * DK]; // per token parity: kn[DK], qn[DK]
+
+  float s[kRows];
+#pragma unroll
+  for (int k = 0; k < kRows; ++k)
+    s[k] = col[static_cast<int64_t>(k) * dv];
+
+  constexpr int kPre = DK / 32;
+  float k_next[kPre], q_next[kPre];
+  float dc_next = 0.0f, bt_next = 0.0f;
+  uint16_t value_next = 0;
+  auto fetch = [&](int64_t t) {
+#pragma unroll
+    for (int u = 0; u < kPre; ++u) {
+      k_next[u] = kn[(t * nk + kh) * DK + u * 32 + lane];
+      q_next[u] = qn[(t * nk + kh) * DK + u * 32 + lane];
+    }
+    dc_next = decay[t * nv + h];
+    bt_next = beta[t * nv + h];
+    value_next = conv[t * channels + 2 * static_cast<int64_t>(nk) * DK + h * dv + v];
+  };
+  auto publish = [&](int parity) {
+#pragma unroll
+    for (int u = 0; u < kPre; ++u) {
+      kq_sm[parity][u * 32 + lane] = k_next[u];
+      kq_sm[parity][DK + u * 32 + lane] = q_next[u];
+    }
+  };
+  auto over_quarters = [](float x) { // the four lanes of a column hold the quarters' partial sums
+    x += __shfl_xor_sync(0xffffffffu, x, 8);
+    x += __shfl_xor_sync(0xffffffffu, x, 16);
+    return x;
+  };
+  const int row0 = quarter * kRows;
+
+  fetch(0);
+  publish(0);
+  float dc = dc_next, bt = bt_next, value = bf16_to_f32(value_next);
+  if (S > 1)
+    fetch(1);
+  __syncwarp();
+  float kv = 0.0f;
+#pragma unroll
+  for (int k4 = 0; k4 < kRows; k4 += 4) {
+    const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[0][row0 + k4]);
+    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s[k4 + u] *= dc;
+      kv = __fmaf_rn(s[k4 + u], kv4[u], kv);
+    }
+  }
+  kv = over_quarters(kv);
+  for (int64_t t = 0; t < S; ++t) {
+    const int cur = static_cast<int>(t & 1);
+    const float delta = (value - kv) * bt;
+    float o = 0.0f;
+    if (t + 1 < S) {
+      publish(cur ^ 1);
+      const float dc1 = dc_next;
+      bt = bt_next;
+      value = bf16_to_f32(value_next);
+      if (t + 2 < S)
+        fetch(t + 2);
+      __syncwarp();
+      float kv1 = 0.0f;
+#pragma unroll
+      for (int k4 = 0; k4 < kRows; k4 += 4) {
+        const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[cur][row0 + k4]);
+        const float4 qq = *reinterpret_cast<const float4 *>(&kq_sm[cur][DK + row0 + k4]);
+        const float4 kn1 = *reinterpret_cast<const float4 *>(&kq_sm[cur ^ 1][row0 + k4]);
+        const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+        const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
+        const float kw4[4] = {kn1.x, kn1.y, kn1.z, kn1.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[k4 + u] = __fmaf_rn(kv4[u], delta, s[k4 + u]);
+          o = __fmaf_rn(s[k4 + u], qv4[u], o);
+          s[k4 + u] *= dc1;
+          kv1 = __fmaf_rn(s[k4 + u], kw4[u], kv1);
+        }
+      }
+      kv = over_quarters(kv1);
+    } else {
+#pragma unroll
+      for (int k4 = 0; k4 < kRows; k4 += 4) {
+        const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[cur][row0 + k4]);
+        const float4 qq = *reinterpret_cast<const float4 *>(&kq_sm[cur][DK + row0 + k4]);
+        const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+        const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[k4 + u] = __fmaf_rn(kv4[u], delta, s[k4 + u]);
+          o = __fmaf_rn(s[k4 + u], qv4[u], o);
+        }
+      }
+    }
+    o = over_quarters(o);
+    if (quarter == 0)
+      out[t * nv * dv + h * dv + v] = f32_to_bf16(o);
+    __syncwarp();
+  }
+#pragma unroll
+  for (int k = 0; k < kRows; ++k)
+    col[static_cast<int64_t>(k) * dv] = s[k];
+}
+
 size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk) {
   return static_cast<size_t>(S) * (2 * static_cast<size_t>(nk) * dk + 2 * static_cast<size_t>(nv));
 }
@@ -369,7 +496,8 @@ size_t gdn_scratch_floats(int64_t S, int nk, int nv, int dk) {
 cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, const uint16_t *b,
                                    const void *a_log, int a_log_dtype, const void *dt_bias, int dt_dtype,
                                    float *state, int64_t S, int nk, int nv, int dk, int dv,
-                                   int b_activated, float *scratch, uint16_t *out, cudaStream_t stream, int ab_stride) {
+                                   int b_activated, float *scratch, uint16_t *out, cudaStream_t stream, int ab_stride,
+                                   int fast) {
   if (S == 0)
     return cudaSuccess;
   if (ab_stride <= 0)
@@ -389,7 +517,10 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
     const char *flag = std::getenv("LLMCP_B200_GDN_PIPELINE");
     return !(flag && flag[0] == '0');
   }();
-  if (dk == 128 && S > 1 && pipelined)
+  if (dk == 128 && S > 1 && fast && dv % 8 == 0)
+    launch_chained(gdn_recurrence_split_kernel<128>, dim3(nv, dv / 8), dim3(32), 0, stream, conv, qn, kn, beta, decay, state, S, nk, nv,
+                   dv, out);
+  else if (dk == 128 && S > 1 && pipelined)
     launch_chained(gdn_recurrence_pipelined_kernel<128>, dim3(grid), dim3(32), 0, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dv, out);
   else if (dk == 128)
     launch_chained(gdn_recurrence_kernel<128>, dim3(grid), dim3(32), smem, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dk, dv, out);

@@ -1,0 +1,123 @@
+// Pieces shared by the kernels that drive the fifth-generation tensor cores directly: mbarriers with
+// bounded waits, tiled TMA loads (no multicast), shared-memory operand descriptors for K-major tiles
+// with 128-byte swizzle, tcgen05 commit / fences / tensor-memory loads, and the host-side tensor-map
+// encoder.  Everything here is for operands in this GPU's own memory.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+
+namespace llmcp_b200 {
+namespace tc {
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+// Waits for the phase with the given parity; gives up when `abort_flag` is raised or after `limit`
+// polls (and then raises it).  Returns false on failure.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t limit) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < limit; ++spin) {
+    uint32_t done;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(done)
+                 : "r"(addr), "r"(parity)
+                 : "memory");
+    if (done)
+      return true;
+    if ((spin & 63) == 63 && *abort_flag)
+      return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+// The same wait without the abort protocol (used while leaving after an abort).
+__device__ __forceinline__ bool mbar_wait_quiet(uint64_t *bar, uint32_t parity, uint32_t limit) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < limit; ++spin) {
+    uint32_t done;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(done)
+                 : "r"(addr), "r"(parity)
+                 : "memory");
+    if (done)
+      return true;
+  }
+  return false;
+}
+
+// Tiled 2-D load of one box; completion is counted in bytes on `bar`.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_address) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_address & 0x3ffffu) >> 4); // start address
+  d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset: next 8-row group
+  d |= static_cast<uint64_t>(1) << 46;                        // descriptor version for sm_100
+  d |= static_cast<uint64_t>(2) << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive 32-bit columns of this thread's lane.
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (no link against libcuda).
+inline EncodeTiled encode_tiled() {
+  static std::mutex mutex;
+  static EncodeTiled fn = nullptr;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  }
+  return fn;
+}
+
+} // namespace tc
+} // namespace llmcp_b200

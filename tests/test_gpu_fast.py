@@ -138,6 +138,57 @@ def test_attention_decode_fast_long_context(fast_mode):
     assert (ulps != 0).mean() < 0.05, (ulps != 0).mean()
 
 
+@pytest.mark.parametrize("S,position", [(130, 0), (64, 0), (2, 0), (300, 0), (70, 64), (129, 7), (1024, 0)])
+def test_attention_prefill_on_tensor_cores(fast_mode, S, position):
+    """More than one query token in fast mode: Q K^T and P V on the tensor cores with the softmax
+    weights rounded to bf16.  Against the oracle (f32 weights, key-ordered sums): every output within
+    2^-7 of the largest one, nearly all within two bf16 steps; the cache as in the one-token test."""
+    rng = np.random.default_rng(S * 31 + position)
+    nh, nkv, hd, rot = 16, 4, 256, 64
+    cap = position + S + 5
+    qg = bf16(rng.standard_normal((S, nh * 2 * hd)))
+    k = bf16(rng.standard_normal((S, nkv * hd)))
+    v = bf16(rng.standard_normal((S, nkv * hd)))
+    qn = bf16(rng.standard_normal(hd) * 0.1)
+    kn = bf16(rng.standard_normal(hd) * 0.1)
+    rows = [L.make_cos_sin(position + t, rot, 1e7) for t in range(S)]
+    cos, sin = np.stack([r[0] for r in rows]), np.stack([r[1] for r in rows])
+    cache = bf16(rng.standard_normal((2, nkv, cap, hd)))
+    got, got_cache = L.ops.attention(qg, k, v, qn, kn, cos, sin, cache, position, nh, nkv, hd, rot)
+    want, want_cache = oracle.attention(qg, k, v, qn, kn, cos, sin, cache, position, nh, nkv, hd, rot)
+    cache_ulps = bf16_ulps(got_cache, want_cache)
+    assert cache_ulps.max() <= 1 and np.count_nonzero(cache_ulps) <= S * nkv * hd // 20
+    assert np.array_equal(got_cache[1], want_cache[1])
+    assert np.isfinite(f(got)).all()
+    error, scale = np.abs(f(got) - f(want)), np.abs(f(want)).max()
+    ulps = bf16_ulps(got, want)
+    assert error.max() <= scale * 2.0 ** -7, (error.max(), scale)
+    assert ((ulps <= 2) | (error <= scale * 2.0 ** -9)).mean() > 0.999, ((ulps > 2).mean(), error.max(), scale)
+
+
+@pytest.mark.parametrize("S,nk,nv", [(64, 16, 32), (1024, 16, 32), (33, 16, 16), (2, 2, 8)])
+def test_gated_delta_net_prefill_fast(fast_mode, S, nk, nv):
+    """Prefill recurrence with the state rows of a column split over four lanes and fused multiply-adds:
+    against the oracle, outputs within a bf16 step or two, the final state to f32 rounding noise, and
+    the golden vectors within the reference's own tolerance."""
+    dk = dv = 128
+    rng = np.random.default_rng(S + nv)
+    channels = 2 * nk * dk + nv * dv
+    conv, a = bf16(rng.standard_normal((S, channels))), bf16(rng.standard_normal((S, nv)))
+    b = bf16(rng.standard_normal((S, nv)))
+    a_log = (rng.standard_normal(nv) * 0.2).astype(np.float32)
+    dt = bf16(rng.standard_normal(nv) * 0.2)
+    state = (rng.standard_normal((nv, dk, dv)) * 0.1).astype(np.float32)
+    got, got_state = L.ops.gated_delta_net(conv, a, b, a_log, dt, state, nk, nv, dk, dv)
+    want, want_state = oracle.gated_delta_net(conv, a, b, a_log, dt, state, nk, nv, dk, dv)
+    assert np.isfinite(f(got)).all() and np.isfinite(got_state).all()
+    ulps = bf16_ulps(got, want)
+    error, scale = np.abs(f(got) - f(want)), np.abs(f(want)).max()
+    assert ((ulps <= 2) | (error <= scale * 2.0 ** -9)).all(), (ulps.max(), error.max(), scale)
+    assert (ulps != 0).mean() < 0.05, (ulps != 0).mean()
+    assert np.abs(got_state - want_state).max() <= 1e-4 * np.abs(want_state).max()
+
+
 SMALL = dict(hidden=256, intermediate=512, vocab=2048, layers=8, full_interval=4, heads=4, kv_heads=2,
              head_dim=256, rotary=64, lin_k_heads=2, lin_v_heads=8, lin_k_dim=128, lin_v_dim=128, conv_kernel=4)
 

@@ -263,3 +263,56 @@ def test_llmcp_benchmark_binary_against_oracle(tmp_path):
         pos += 1
     assert generated == want
     model.close()
+
+
+@pytest.mark.slow
+def test_llmcp_run_binary_against_oracle(tmp_path):
+    """The C++ generation driver (the AOT half of the reference's llmcp-run) on the full-size synthetic
+    container through libllmcp_b200.so: `output: <streamed text>`, then `tokens: ...`, which must be the
+    oracle's greedy tokens; generation stops in front of the end-of-turn token; without new tokens the
+    `aot logits: N next T` line."""
+    import json
+    import pathlib
+    import subprocess
+    tool = L._PACKAGE / "bin" / "llmcp-run"
+    assert tool.exists(), "run python -m llmcp_b200.build"
+    d = L.default_dims()
+    # a ByteLevel vocabulary of the model's size: the 256 bytes, then "<n>" for every other id
+    alphabet, nxt = [], 256
+    for byte in range(256):
+        direct = 33 <= byte <= 126 or 161 <= byte <= 172 or byte >= 174
+        alphabet.append(chr(byte if direct else nxt))
+        nxt += 0 if direct else 1
+    vocab = {alphabet[b]: b for b in range(256)}
+    vocab.update({f"<{i}>": i for i in range(256, d.vocab)})
+    blob = json.dumps({"model": {"type": "BPE", "vocab": vocab, "merges": []}, "added_tokens": [], "decoder": {"type": "ByteLevel"}})
+    (tmp_path / "tokenizer.json").write_text(blob)
+    weights = pathlib.Path("/dev/shm") / "llmcp_b200_synth_20261125.bin"
+    prompt = [9419] * 8
+    base = [str(tool), "--weights", str(weights), "--aot", str(L.LIBRARY_PATH), "--synthetic", "20261125",
+            "--token-ids", ",".join(map(str, prompt)), "--tokenizer", str(tmp_path / "tokenizer.json")]
+    run = subprocess.run(base + ["--max-new-tokens", "6"], capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stderr
+    out_line, tokens_line = run.stdout.strip().split("\n")
+    generated = [int(v) for v in tokens_line.removeprefix("tokens:").split()]
+    data = np.fromfile(weights, dtype=np.uint8)
+    arena = L.Arena().from_buffer(data)
+    model = oracle.Model(data, arena.manifest, oracle_dims(d))
+    state = model.new_state(40)
+    logits = model.forward(state, prompt, 0)
+    want = []
+    for step in range(6):
+        want.append(oracle.argmax(logits))
+        logits = model.forward(state, [want[-1]], len(prompt) + step)
+    model.close()
+    assert generated == want
+    v = L.Vocab(blob)
+    assert out_line == "output: " + v.decode(generated)
+    v.close()
+    # the third token as end-of-turn token: two tokens come out
+    if want[2] not in want[:2]:
+        run = subprocess.run(base + ["--max-new-tokens", "6", "--eos-token", str(want[2])], capture_output=True, text=True, timeout=900)
+        assert run.returncode == 0, run.stderr
+        assert [int(x) for x in run.stdout.strip().split("\n")[-1].removeprefix("tokens:").split()] == want[:2]
+    run = subprocess.run(base, capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0 and run.stdout.strip() == f"aot logits: {d.vocab} next {want[0]}", run.stdout
