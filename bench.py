@@ -415,6 +415,47 @@ def decode_timeline(L, torch, mode):
         print(f"{e['ts'] - t0:8.2f} -> {e['ts'] - t0 + e['dur']:8.2f} (+{e['dur']:6.2f})  {short(e['name'])[:64]}")
 
 
+def prefill_timeline(L, torch, mode):
+    """Per kernel family of one 1024-token prefill: launches and summed device time (PyTorch
+    profiler, CUPTI activity records of a plain run; kernels of a prefill run back to back)."""
+    import collections
+    import tempfile
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.zeros(1, device="cuda")
+    arena = L.Arena().load(ensure_container(0))
+    engine = L.Engine(arena.data, L.default_dims(), capacity=PREFILL + 16, mode=mode)
+    for _ in range(2):
+        engine.reset()
+        engine.forward([TOKEN] * PREFILL, 0, want_logits=False)
+    engine.reset()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        engine.forward([TOKEN] * PREFILL, 0, want_logits=False)
+        torch.cuda.synchronize()
+    with tempfile.TemporaryDirectory() as folder:
+        trace = os.path.join(folder, "trace.json")
+        prof.export_chrome_trace(trace)
+        events = [e for e in json.load(open(trace))["traceEvents"] if e.get("cat") == "kernel"]
+    events.sort(key=lambda e: e["ts"])
+    first = max(i for i, e in enumerate(events) if "embedding" in e["name"])
+    events = events[first:]
+
+    def short(name):
+        name = name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
+        return name.split("(")[0].replace("llmcp_b200::", "").replace("void ", "")
+
+    families = collections.defaultdict(lambda: [0, 0.0])
+    for e in events:
+        entry = families[short(e["name"])]
+        entry[0] += 1
+        entry[1] += e["dur"]
+    span = events[-1]["ts"] + events[-1]["dur"] - events[0]["ts"]
+    total = sum(v[1] for v in families.values())
+    print(f"mode {mode}: prefill of {PREFILL} tokens spans {span / 1e3:.2f} ms in {len(events)} kernels (sum of durations {total / 1e3:.2f} ms)")
+    for name, (n, dur) in sorted(families.items(), key=lambda kv: -kv[1][1]):
+        print(f"{name[:64]:64s} n={n:4d} total={dur / 1e3:8.3f} ms  share={dur / total:6.1%}  avg={dur / n:8.1f} us")
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -426,9 +467,10 @@ def main():
     parser.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
                         help="N > 1: tp = one sequence over N GPUs (strong scaling, the default), replicas = one sequence per GPU")
     parser.add_argument("--batch", type=int, default=64, help="sequences of the batched-decode measurement (0 = skip it)")
-    parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm", "attn", "timeline"],
+    parser.add_argument("--only", default="all", choices=["all", "gemv", "gemm", "attn", "timeline", "prefill-timeline"],
                         help="gemv / gemm / attn: run just that kernel on a small case (what the profiler captures); "
-                             "timeline: kernel start / end stamps of one decode step (CUDA-graph replay) as text")
+                             "timeline: kernel start / end stamps of one decode step (CUDA-graph replay) as text; "
+                             "prefill-timeline: device time per kernel family of one 1024-token prefill")
     args = parser.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
@@ -487,6 +529,9 @@ def main():
         return
     if args.only == "timeline":
         decode_timeline(L, torch, args.mode)
+        return
+    if args.only == "prefill-timeline":
+        prefill_timeline(L, torch, args.mode)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))

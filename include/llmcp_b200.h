@@ -88,6 +88,14 @@ int llmcp_op_act_quant(const void *x, int x_dtype, int64_t M, int64_t K, int8_t 
 int llmcp_op_linear_q8(const void *x, int x_dtype, int64_t M, int64_t K, const uint8_t *weight, int64_t N,
                        void *y, int y_dtype, int activation, int32_t *block_dots);
 
+/* llmcp.linear on the bf16 matrix of an unquantised arena (lib/Dialect/LLMCP/Transforms/
+ * MatmulLoweringCommon.cpp:186-251,509-527): y = act(x w^T), x [M, K] and w [N, K] bf16, products and
+ * sums in f32, y bf16 or f32.  One row runs a streaming GEMV, more rows the tensor cores; the order of
+ * the f32 additions is this library's (the reference's differs by target), so results agree with the
+ * reference to f32 rounding, as its own tests require (tests/numeric/run_numeric.py:676-688). */
+int llmcp_op_linear_bf16(const uint16_t *x, int64_t M, int64_t K, const uint16_t *weight, int64_t N, void *y, int y_dtype,
+                         int activation);
+
 /* llmcp.lm_head (LLMCPOps.td:103-110, LowerToLinalg.cpp:729-765) followed by the host
  * argmax of tools/llmcp-benchmark/llmcp-benchmark.cpp:51-54 (first maximum).
  * hidden: [M, K] bf16; logits: [M, vocab] f32 (may be NULL); argmax: [M] (may be NULL). */

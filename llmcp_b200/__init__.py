@@ -168,6 +168,19 @@ class ops:
         return (y, dots) if want_dots else y
 
     @staticmethod
+    def linear_bf16(x, w, y_bf16=True, activation="none"):
+        """llmcp.linear on the bf16 matrix ``w`` [N, K] of an unquantised arena; ``x`` [M, K] bf16."""
+        x = np.ascontiguousarray(x, dtype=np.uint16)
+        w = np.ascontiguousarray(w, dtype=np.uint16)
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise LlmcpError("the weight's second dimension must equal the input's")
+        y = np.empty((M, N), dtype=np.uint16 if y_bf16 else np.float32)
+        _check(lib().llmcp_op_linear_bf16(_p(x), _i(M), _i(K), _p(w), _i(N), _p(y), int(y_bf16), ACTIVATIONS[activation]))
+        return y
+
+    @staticmethod
     def lm_head_q8(hidden, packed, vocab):
         hidden = np.ascontiguousarray(hidden, dtype=np.uint16)
         packed = np.ascontiguousarray(packed, dtype=np.uint8)

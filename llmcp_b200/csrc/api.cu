@@ -480,6 +480,33 @@ int llmcp_op_linear_q8(const void *x, int x_dtype, int64_t M, int64_t K, const u
   });
 }
 
+int llmcp_op_linear_bf16(const uint16_t *x, int64_t M, int64_t K, const uint16_t *weight, int64_t N, void *y, int y_dtype,
+                         int activation) {
+  return guarded([&] {
+    require_device();
+    if (N <= 0 || K <= 0 || K % 16 != 0 || (M > 1 && N % 8 != 0))
+      throw std::runtime_error("bf16 linear: K must be a multiple of 16 (and N of 8 for more than one row)");
+    if (M <= 0)
+      return;
+    Buf dx(static_cast<size_t>(M) * K * 2, x), dw(static_cast<size_t>(N) * K * 2, weight), dy(static_cast<size_t>(M) * N * elem(y_dtype)),
+        dstatus(4);
+    cuda_check(cudaMemset(dstatus.p, 0, 4), "memset");
+    if (M == 1)
+      cuda_check(launch_gemv_bf16(dx.as<uint16_t>(), static_cast<int>(K), dw.as<uint16_t>(), N, dy.p, y_dtype, activation, nullptr),
+                 "bf16 GEMV");
+    else
+      cuda_check(launch_gemm_bf16_tc(dx.as<uint16_t>(), static_cast<int>(M), static_cast<int>(K), dw.as<uint16_t>(),
+                                     static_cast<int>(N), dy.p, y_dtype, activation, dstatus.as<int>(), nullptr), "bf16 GEMM");
+    g_launches += 1;
+    cuda_check(cudaDeviceSynchronize(), "bf16 linear");
+    int status = 0;
+    dstatus.to_host(&status, 4);
+    if (status)
+      throw std::runtime_error("bf16 linear: a bounded wait inside the tensor-core kernel ran out");
+    dy.to_host(y, dy.bytes);
+  });
+}
+
 int llmcp_op_lm_head_q8(const uint16_t *hidden, int64_t M, int64_t K, const uint8_t *table, int64_t vocab,
                         float *logits, int64_t *argmax) {
   return guarded([&] {

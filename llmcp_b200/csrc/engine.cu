@@ -163,8 +163,12 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   const std::string error = parse_container(base, file_bytes, &manifest);
   if (!error.empty())
     throw std::runtime_error(error);
-  if (manifest.quantization != "q8_0")
-    throw std::runtime_error("only q8_0 arenas are supported (quantization = " + manifest.quantization + ")");
+  if (manifest.quantization == "none")
+    bf16_weights_ = true; // bf16 matrices (llmcp-pack --quant none): MatmulLoweringCommon.cpp:509-527
+  else if (manifest.quantization != "q8_0")
+    throw std::runtime_error("only q8_0 and unquantised arenas are supported (quantization = " + manifest.quantization + ")");
+  if (bf16_weights_ && (tp_ || batch_ > 1))
+    throw std::runtime_error("an unquantised (bf16) arena runs one sequence on one GPU");
   load_weights(base, manifest);
 
   const ModelDims &c = local_; // state is per rank: this rank's heads
@@ -293,14 +297,19 @@ void Engine::check_status() {
 // mode takes the tree-reduced kernel where the row length allows.
 void Engine::rms_norm(const uint16_t *a, const uint16_t *b, int64_t S, const SmallTensor &w, uint16_t *sum_out, uint16_t *y) {
   const int H = static_cast<int>(dims_.hidden);
+  // bf16 arena: the next linear reads the normalised rows themselves, not a quantised copy
+  int8_t *q = bf16_weights_ ? nullptr : aq_;
+  float *qs = bf16_weights_ ? nullptr : as_;
+  if (bf16_weights_ && !y)
+    y = xb_;
   if (mode_ == kModeFast) {
-    const cudaError_t e = launch_rms_norm_fast(a, b, S, H, w.data, w.dtype, dims_.eps, 1, sum_out, y, aq_, as_, stream_);
+    const cudaError_t e = launch_rms_norm_fast(a, b, S, H, w.data, w.dtype, dims_.eps, 1, sum_out, y, q, qs, stream_);
     if (e == cudaSuccess)
       return;
     if (e != cudaErrorNotSupported)
       check(e, "rms_norm (fast)");
   }
-  check(launch_rms_norm(a, b, S, H, w.data, w.dtype, dims_.eps, 1, sum_out, y, aq_, as_, stream_), "rms_norm");
+  check(launch_rms_norm(a, b, S, H, w.data, w.dtype, dims_.eps, 1, sum_out, y, q, qs, stream_), "rms_norm");
 }
 
 void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
@@ -357,6 +366,17 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
     const TensorEntry *t = manifest.find(name);
     if (!t)
       throw std::runtime_error("missing tensor " + name);
+    if (bf16_weights_) { // the matrix as it is in the arena
+      if (t->dtype != "BF16" || t->shape.size() != 2 || t->shape[0] != rows || t->shape[1] != cols)
+        throw std::runtime_error("tensor " + name + " is not BF16 [" + std::to_string(rows) + ", " + std::to_string(cols) + "]");
+      Q8Weight w;
+      w.N = static_cast<int>(rows);
+      w.K = static_cast<int>(cols);
+      uint8_t *dst = take(static_cast<size_t>(rows) * cols * 2);
+      check(cudaMemcpyAsync(dst, base + t->offset, static_cast<size_t>(rows) * cols * 2, cudaMemcpyHostToDevice, stream_), "upload weights");
+      w.bf = reinterpret_cast<const uint16_t *>(dst);
+      return w;
+    }
     if (t->dtype != "Q8_0" || t->shape.size() != 2 || t->shape[0] != rows || t->shape[1] != cols)
       throw std::runtime_error("tensor " + name + " is not Q8_0 [" + std::to_string(rows) + ", " +
                                std::to_string(cols) + "]");
@@ -433,8 +453,10 @@ void Engine::load_weights(const uint8_t *base, const Manifest &manifest) {
   embed_ = q8(root + "embed_tokens.weight", c.vocab, c.hidden);
   lm_head_ = embed_; // the tied table's rows [vocab_row0_, + vocab_rows_) for the vocabulary projection
   lm_head_.N = static_cast<int>(vocab_rows_);
-  lm_head_.q = embed_.q + vocab_row0_ * c.hidden;
-  lm_head_.d = embed_.d + vocab_row0_ * (c.hidden / 32);
+  if (!bf16_weights_) {
+    lm_head_.q = embed_.q + vocab_row0_ * c.hidden;
+    lm_head_.d = embed_.d + vocab_row0_ * (c.hidden / 32);
+  }
   if (embed_.d32)
     lm_head_.d32 = embed_.d32 + vocab_row0_ * (c.hidden / 32);
   if (G > 1)
@@ -553,6 +575,7 @@ void Engine::ensure_workspace(int64_t S, int64_t position) {
   hidden_[1] = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
   branch_ = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
   mlp_out_ = static_cast<uint16_t *>(alloc(r * c.hidden * 2));
+  xb_ = bf16_weights_ ? static_cast<uint16_t *>(alloc(r * max_k * 2)) : nullptr;
   aq_ = static_cast<int8_t *>(alloc(r * max_k));
   as_ = static_cast<float *>(alloc(r * (max_k / 32) * 4));
   ah_ = nullptr;
@@ -629,7 +652,20 @@ struct F16Planes {
 };
 
 static void run_linears(const F16Planes &planes, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
-                        cudaStream_t stream, uint64_t *launches, int flags, int *gemm_error = nullptr) {
+                        cudaStream_t stream, uint64_t *launches, int flags, int *gemm_error = nullptr,
+                        const uint16_t *xb = nullptr, int *status = nullptr) {
+  if (jobs[0].w->bf) { // bf16 matrices: the input rows are bf16 (xb), one launch per matrix
+    for (int i = 0; i < count; ++i) {
+      const Q8Weight &w = *jobs[i].w;
+      const cudaError_t e = S == 1 ? launch_gemv_bf16(xb, w.K, w.bf, w.N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, stream)
+                                   : launch_gemm_bf16_tc(xb, static_cast<int>(S), w.K, w.bf, w.N, jobs[i].y, jobs[i].y_dtype,
+                                                         jobs[i].activation, status, stream);
+      if (e != cudaSuccess)
+        throw std::runtime_error(std::string("bf16 linear: ") + cudaGetErrorString(e));
+      *launches += 1;
+    }
+    return;
+  }
   if (S == 1) {
     GemvJobs g{};
     g.count = count;
@@ -748,7 +784,15 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     throw std::runtime_error("all-position logits are not offered under tensor parallelism");
   ensure_workspace(S, position);
   exchange_ = 0;
-  launch_embedding_q8(tokens_dev, S, H, c.vocab, embed_.q, embed_.d, hidden_[0], gemm_error_, stream_);
+  // bf16 arena: operators hand bf16 rows to the next linear (act_y) instead of int8 blocks (act_q, act_s)
+  const bool bf = bf16_weights_;
+  int8_t *act_q = bf ? nullptr : aq_;
+  float *act_s = bf ? nullptr : as_;
+  uint16_t *act_y = bf ? xb_ : nullptr;
+  if (bf)
+    check(launch_embedding_bf16(tokens_dev, S, H, c.vocab, embed_.bf, hidden_[0], gemm_error_, stream_), "embedding");
+  else
+    launch_embedding_q8(tokens_dev, S, H, c.vocab, embed_.q, embed_.d, hidden_[0], gemm_error_, stream_);
   launches_ += 1;
   const int gemv_flags = gemv_flags_ | (mode_ == kModeFast ? kGemvFast : 0);
   const F16Planes planes = {ah_, ast_, gemm_kind_ >= 2 ? gemm_kind_ - 2 : -1};
@@ -772,7 +816,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status);
+      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
       const int C = static_cast<int>(m.qkv_dim());
       uint16_t *conv_state = conv_base + lin_index * (c.conv_kernel - 1) * C;
       float *delta_state = delta_base + lin_index * m.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
@@ -785,8 +829,8 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
         const int single = fuse_decode_mixer_ >= 2 && gdn_decode_single_kernel_supported(static_cast<int>(c.conv_kernel), nk, nv, dk, dv);
         check(launch_gdn_decode(qkv_, static_cast<const uint16_t *>(L.conv.data), conv_state, static_cast<int>(c.conv_kernel),
                                 a_ + head0, b_ + head0, L.a_log.data, L.a_log.dtype, L.dt_bias.data, L.dt_bias.dtype, delta_state,
-                                nk, nv, dk, dv, 1, z_, L.lin_norm.data, L.lin_norm.dtype, c.eps, 1, gdn_scratch_, convd_, nullptr,
-                                aq_, as_, stream_, sequences, &strides, single, mode_ == kModeFast ? 1 : 0), "gated_delta_net (decode)");
+                                nk, nv, dk, dv, 1, z_, L.lin_norm.data, L.lin_norm.dtype, c.eps, 1, gdn_scratch_, convd_, act_y,
+                                act_q, act_s, stream_, sequences, &strides, single, mode_ == kModeFast ? 1 : 0), "gated_delta_net (decode)");
         launches_ += single ? 1 : 2;
       } else if (rows_are_sequences) {
         // Shapes the fused one-token kernels do not take: the general kernels, sequence by sequence.
@@ -809,14 +853,15 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                      delta_state, S, nk, nv, dk, dv, 1, gdn_scratch_, gdn_, stream_, nv_all, mode_ == kModeFast ? 1 : 0),
               "gated_delta_net");
         check(launch_gated_rms_norm(gdn_, z_, L.lin_norm.data, L.lin_norm.dtype, S, static_cast<int>(m.value_dim()), dv,
-                                    c.eps, 1, nullptr, aq_, as_, stream_), "gated_rms_norm");
+                                    c.eps, 1, act_y, act_q, act_s, stream_), "gated_rms_norm");
         launches_ += 5;
       }
-      gather_quant(S, m.value_dim(), &mixer_q, &mixer_s);
+      if (!bf)
+        gather_quant(S, m.value_dim(), &mixer_q, &mixer_s);
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status);
+      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
       uint16_t *cache = kv_base + full_index * 2 * m.kv_heads * capacity_ * c.head_dim;
       const int nh = static_cast<int>(m.heads), nkv = static_cast<int>(m.kv_heads), hd = static_cast<int>(c.head_dim);
       const int64_t cache_stride = rows_are_sequences ? static_cast<int64_t>(kv_seq_) : 0;
@@ -824,32 +869,33 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
         check(launch_attention_decode_fast(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                            static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position,
                                            cache, position_dev_, position, nh, nkv, hd, static_cast<int>(c.rotary), capacity_,
-                                           attn_scratch_, attn_, aq_, as_, stream_, sequences, cache_stride), "attention (fast)");
+                                           attn_scratch_, attn_, act_q, act_s, stream_, sequences, cache_stride), "attention (fast)");
       } else if (mode_ == kModeFast && S > 1 && !rows_are_sequences && tc_prefill_attention_ &&
                  attention_prefill_tc_supported(nh, nkv, hd)) {
         check(launch_attention_prefill_tc(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                           static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position, cache,
                                           position_dev_, position, S, nh, nkv, hd, static_cast<int>(c.rotary), capacity_,
-                                          attn_scratch_, attn_, aq_, as_, gemm_error_, stream_), "attention (tensor cores)");
+                                          attn_scratch_, attn_, act_q, act_s, gemm_error_, stream_), "attention (tensor cores)");
       } else {
         check(launch_attention(qg_, k_, v_, static_cast<const uint16_t *>(L.q_norm.data),
                                static_cast<const uint16_t *>(L.k_norm.data), cos_dev, sin_dev, rows_from_position, cache,
                                position_dev_, position, S, nh, nkv, hd, static_cast<int>(c.rotary), capacity_, attn_scratch_,
-                               attn_, aq_, as_, stream_, cache_stride), "attention");
+                               attn_, act_q, act_s, stream_, cache_stride), "attention");
       }
       launches_ += 3;
-      gather_quant(S, m.attn_dim(), &mixer_q, &mixer_s);
+      if (!bf)
+        gather_quant(S, m.attn_dim(), &mixer_q, &mixer_s);
       ++full_index;
     }
     // Output projection of the mixer: this rank's rows of the hidden vector, then all of them.
     const LinearJob out = {L.full ? &L.o_proj : &L.out_proj, branch_, kBF16, kNone};
-    run_linears(planes, mixer_q, mixer_s, S, &out, 1, stream_, &launches_, gemv_flags, gemm_status);
+    run_linears(planes, mixer_q, mixer_s, S, &out, 1, stream_, &launches_, gemv_flags, gemm_status, L.full ? attn_ : xb_, gemm_error_);
     const uint16_t *branch = gather_rows(branch_, S, hidden_rows_);
     rms_norm(hidden_[cur], branch, S, L.post_norm, hidden_[cur ^ 1], nullptr);
     cur ^= 1;
     const int8_t *mlp_q = nullptr;
     const float *mlp_s = nullptr;
-    if (S == 1 && fuse_swiglu_ && L.gate.K == L.up.K && L.gate.N == L.up.N && gemv_swiglu_supported(L.gate.K, L.gate.N)) {
+    if (!bf && S == 1 && fuse_swiglu_ && L.gate.K == L.up.K && L.gate.N == L.up.N && gemv_swiglu_supported(L.gate.K, L.gate.N)) {
       // One token: both projections, the product and its quantisation in one launch.  The launch
       // reads the quantised input while it writes the quantised product, so the product goes to
       // the (otherwise unused) rows of the separate projections' outputs.
@@ -861,13 +907,14 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       gather_quant(S, inter_rows_, &mlp_q, &mlp_s, product_q, product_s);
     } else {
       const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-      run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, gemm_status);
-      check(launch_pointwise(gate_, up_, S * inter_rows_, 1, nullptr, aq_, as_, stream_), "mul");
+      run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
+      check(launch_pointwise(gate_, up_, S * inter_rows_, 1, act_y, act_q, act_s, stream_), "mul");
       launches_ += 2;
-      gather_quant(S, inter_rows_, &mlp_q, &mlp_s);
+      if (!bf)
+        gather_quant(S, inter_rows_, &mlp_q, &mlp_s);
     }
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
-    run_linears(planes, mlp_q, mlp_s, S, &down, 1, stream_, &launches_, gemv_flags, gemm_status);
+    run_linears(planes, mlp_q, mlp_s, S, &down, 1, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
     pending = gather_rows(mlp_out_, S, hidden_rows_);
   }
   if (all_logits_) {
@@ -876,7 +923,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     rms_norm(hidden_[cur], pending, S, final_norm_, nullptr, branch_);
     const LinearJob all = {&embed_, all_logits_, kF32, kNone};
     run_linears(planes, aq_, as_, S, &all, 1, stream_, &launches_, gemv_flags & kGemvOverlapPrevious,
-                S > 1 ? gemm_status : nullptr);
+                S > 1 ? gemm_status : nullptr, branch_, gemm_error_);
     launches_ += 1;
   }
   if (rows_are_sequences) {
@@ -895,7 +942,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
   rms_norm(last, pending ? pending + (S - 1) * H : nullptr, 1, final_norm_, nullptr, final_hidden_);
   float *logits_rows = logits_ + vocab_row0_; // this rank's rows of the logits
   const LinearJob head = {&lm_head_, logits_rows, kF32, kNone};
-  run_linears(planes, aq_, as_, 1, &head, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious);
+  run_linears(planes, aq_, as_, 1, &head, 1, stream_, &launches_, gemv_flags_ & kGemvOverlapPrevious, nullptr, final_hidden_, gemm_error_);
   if (!tp_) {
     launch_argmax(logits_, c.vocab, argmax_v_, argmax_i_, 0, next_token_, nullptr, stream_);
     launches_ += 3;

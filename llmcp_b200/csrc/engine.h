@@ -22,6 +22,7 @@ struct Q8Weight {
   float *d32 = nullptr;  // [N][K/32] the same scales as f32 (tensor-core GEMM, int8 form)
   void *h = nullptr;     // [N][K] the integers as f16 values (tensor-core GEMM, f16 form)
   float *d32t = nullptr; // [K/32][N] the scales as f32, block-major (tensor-core GEMM, f16 form)
+  const uint16_t *bf = nullptr; // [N][K] bf16: the matrix of an unquantised arena (q, d unused then)
   int N = 0, K = 0;
 };
 
@@ -233,6 +234,8 @@ private:
   float *ast_ = nullptr;  // [max K / 32][pitch] their scales, block-major
   int *gemm_error_ = nullptr; // device flag raised by a timed-out wait in the GEMM
   int gemv_flags_ = 3; // kGemvOverlapPrevious | kGemvPrefetchL2
+  bool bf16_weights_ = false;   // unquantised arena: bf16 matrices, bf16 activations between operators
+  uint16_t *xb_ = nullptr;      // bf16 input rows of the next linear (bf16 arenas)
   bool tc_prefill_attention_ = true; // fast mode, more than one token: attention contractions on the tensor cores
   bool fuse_swiglu_ = true;   // one-token MLP: gate, up, product and quantisation in one launch
   // one-token gated-delta-net layers: 0 five launches, 1 two, 2 one (a cluster per key head; measured

@@ -180,6 +180,15 @@ cudaError_t launch_attention_prepare(const uint16_t *qg, const uint16_t *k, cons
 // heads of one KV head) and a second kernel merges the splits, applies the sigmoid gate and
 // quantises for o_proj.  The softmax is the same function as the reference's tile-ordered one
 // but sums in another order, so results agree to f32 rounding, not bit for bit.
+// bf16 weights [N][K] of an unquantised arena (MatmulLoweringCommon.cpp:186-251): y = act(x w^T) with
+// f32 accumulation; one row through a streaming GEMV, more rows on the tensor cores (bf16 operands by
+// TMA; error_flag as for the Q8 GEMM).  GEMV: K % 16 == 0; GEMM: K % 8 == 0 and N % 8 == 0.
+cudaError_t launch_gemv_bf16(const uint16_t *x, int K, const uint16_t *w, int64_t N, void *y, int y_dtype, int activation,
+                             cudaStream_t stream);
+cudaError_t launch_gemm_bf16_tc(const uint16_t *x, int M, int K, const uint16_t *w, int N, void *y, int y_dtype, int activation,
+                                int *error_flag, cudaStream_t stream, uint32_t spin_limit = 0);
+cudaError_t launch_embedding_bf16(const int64_t *tokens, int64_t S, int H, int64_t vocab, const uint16_t *table, uint16_t *out,
+                                  int *status, cudaStream_t stream);
 // Fast mode of the prefill attention (S > 1, head_dim 256): the same prepare kernel, then both
 // contractions on the tensor cores with the softmax weights rounded to bf16 (attn_prefill.cu).
 // scratch: attention_prefill_tc_scratch_bytes.  error_flag (device int, optional) is set to 1 if a

@@ -15,7 +15,8 @@ _HERE = pathlib.Path(__file__).resolve().parent
 _LIB = None
 
 ACT = {"none": 0, "silu": 1, "sigmoid": 2, "softplus": 3}
-MODE = {"fma": 0, "muladd": 1}
+# bf16 / bf16-pairs: an unquantised arena (bf16 matrices), portable lowering / the aarch64 lowering's order
+MODE = {"fma": 0, "muladd": 1, "bf16": 2, "bf16-pairs": 3}
 
 
 def build(force=False):
@@ -129,6 +130,17 @@ def linear_q8(x, packed, N, x_bf16=True, y_bf16=True, activation="none", mode="f
     fn = lib().orc_linear_q8_direct if direct else lib().orc_linear_q8
     fn(_p(x), int(x_bf16), _i(M), _i(K), _p(packed), _i(N), _p(y), int(y_bf16),
        ACT[activation], MODE[mode])
+    return y
+
+
+def linear_bf16(x, w, x_bf16=True, y_bf16=True, activation="none"):
+    """bf16 weights [N][K] (an unquantised arena): MatmulLoweringCommon.cpp:186-251, the portable lowering."""
+    x = np.ascontiguousarray(x, dtype=np.uint16 if x_bf16 else np.float32)
+    w = np.ascontiguousarray(w, dtype=np.uint16)
+    M, K = x.shape
+    N = w.shape[0]
+    y = np.empty((M, N), dtype=np.uint16 if y_bf16 else np.float32)
+    lib().orc_linear_bf16(_p(x), int(x_bf16), _i(M), _i(K), _p(w), _i(N), _p(y), int(y_bf16), ACT[activation])
     return y
 
 

@@ -174,6 +174,7 @@ struct Unpacked {
   int64_t N = 0, K = 0;
   std::vector<int8_t> q;
   std::vector<float> d;
+  const uint16_t *bf = nullptr; // a bf16 [N][K] matrix of an unquantised arena (mode 2): nothing to unpack
 };
 
 void unpack(const uint8_t *w, int64_t N, int64_t K, Unpacked &out) {
@@ -207,9 +208,54 @@ inline int32_t block_dot(const int8_t *a, const int8_t *w) {
 
 // Q8Decode.cpp:131-225 / Q8Matmul.cpp:143-289 (mode 0, fused multiply-add)
 // Q8Scalar.cpp:65-212 (mode 1, multiply then add)
+// The bf16 linear of an unquantised arena, portable lowering
+// (MatmulLoweringCommon.cpp:186-251): per 32-wide tile of K the f32 products are
+// added in lane order starting from zero (an ordered vector reduction), and the
+// tile's sum is added to the running f32 sum; activation, then the output type.
+// pairs != 0: the order of the aarch64 lowering instead (MatmulLoweringCommon.cpp:253-322): four f32
+// lanes, lane j of every 8-wide block receives the sum of the products 2j and 2j+1 (one rounding,
+// as the two-way bf16 dot instruction forms it), and the lanes are added in order at the end.
+void linear_bf16(const void *x, int x_bf16, int64_t M, int64_t K,
+                 const uint16_t *w, int64_t N, void *y, int y_bf16,
+                 int activation, int pairs = 0) {
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < N; ++n) {
+    const uint16_t *row = w + n * K;
+    for (int64_t m = 0; m < M; ++m) {
+      float acc = 0.0f;
+      if (pairs) {
+        float lanes[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int64_t k0 = 0; k0 < K; k0 += 8)
+          for (int64_t j = 0; j < 4; ++j) {
+            const double p0 = static_cast<double>(load_act(x, x_bf16, m * K + k0 + 2 * j)) * bf16_to_f32(row[k0 + 2 * j]);
+            const double p1 = static_cast<double>(load_act(x, x_bf16, m * K + k0 + 2 * j + 1)) * bf16_to_f32(row[k0 + 2 * j + 1]);
+            lanes[j] = lanes[j] + static_cast<float>(p0 + p1);
+          }
+        for (int64_t j = 0; j < 4; ++j)
+          acc = acc + lanes[j];
+      }
+      for (int64_t k0 = 0; k0 < K && !pairs; k0 += kBlock) {
+        float dot = 0.0f;
+        for (int64_t i = 0; i < kBlock; ++i)
+          dot = dot + load_act(x, x_bf16, m * K + k0 + i) * bf16_to_f32(row[k0 + i]);
+        acc = acc + dot;
+      }
+      float v = apply_activation(acc, activation);
+      if (y_bf16)
+        static_cast<uint16_t *>(y)[m * N + n] = f32_to_bf16(v);
+      else
+        static_cast<float *>(y)[m * N + n] = v;
+    }
+  }
+}
+
 void linear_unpacked(const void *x, int x_bf16, int64_t M, int64_t K,
                      const Unpacked &w, void *y, int y_bf16, int activation,
                      int mode) {
+  if (w.bf) {
+    linear_bf16(x, x_bf16, M, K, w.bf, w.N, y, y_bf16, activation, mode == 3);
+    return;
+  }
   const int64_t N = w.N, blocks = K / kBlock;
   std::vector<int8_t> aq(static_cast<size_t>(M * K));
   std::vector<float> as(static_cast<size_t>(M * blocks));
@@ -642,6 +688,13 @@ void orc_linear_q8_direct(const void *x, int x_bf16, int64_t M, int64_t K,
   }
 }
 
+// bf16 weights [N][K] (an unquantised arena), portable lowering.
+void orc_linear_bf16(const void *x, int x_bf16, int64_t M, int64_t K,
+                     const uint16_t *w, int64_t N, void *y, int y_bf16,
+                     int activation) {
+  linear_bf16(x, x_bf16, M, K, w, N, y, y_bf16, activation);
+}
+
 // ---- a6: embedding gather ---------------------------------------------------
 // LowerToLinalg.cpp:435-531
 void orc_embedding_q8(const int64_t *tokens, int64_t S, const uint8_t *table,
@@ -782,8 +835,15 @@ namespace {
 const Unpacked &weight(OrcModel &m, int64_t layer, int slot, uint64_t offset,
                        int64_t N, int64_t K) {
   Unpacked &u = m.cache[static_cast<size_t>(layer * 16 + slot)];
-  if (u.N == 0)
-    unpack(m.arena + offset, N, K, u);
+  if (u.N == 0) {
+    if (m.cfg.mode >= 2) { // unquantised arena: bf16 [N][K] in place
+      u.N = N;
+      u.K = K;
+      u.bf = reinterpret_cast<const uint16_t *>(m.arena + offset);
+    } else {
+      unpack(m.arena + offset, N, K, u);
+    }
+  }
   return u;
 }
 
@@ -834,7 +894,13 @@ void orc_model_forward(void *handle, const int64_t *tokens, int64_t S,
 
   std::vector<uint16_t> hidden(S * H), norm(S * H), residual(S * H),
       branch(S * H);
-  orc_embedding_q8(tokens, S, m.arena + m.embed, H, hidden.data());
+  if (c.mode >= 2) { // bf16 table: the rows themselves (LowerToLinalg.cpp:435-531)
+    const uint16_t *table = reinterpret_cast<const uint16_t *>(m.arena + m.embed);
+    for (int64_t r = 0; r < S; ++r)
+      std::memcpy(hidden.data() + r * H, table + tokens[r] * H, static_cast<size_t>(H) * 2);
+  } else {
+    orc_embedding_q8(tokens, S, m.arena + m.embed, H, hidden.data());
+  }
 
   int64_t linear_index = 0, full_index = 0;
   for (int64_t layer = 0; layer < c.layers; ++layer) {
@@ -915,7 +981,13 @@ void orc_model_forward(void *handle, const int64_t *tokens, int64_t S,
   if (hidden_out)
     std::memcpy(hidden_out, norm.data(), static_cast<size_t>(S * H) * 2);
   if (!m.embed_ready) {
-    unpack(m.arena + m.embed, c.vocab, H, m.embed_unpacked);
+    if (c.mode >= 2) {
+      m.embed_unpacked.N = c.vocab;
+      m.embed_unpacked.K = H;
+      m.embed_unpacked.bf = reinterpret_cast<const uint16_t *>(m.arena + m.embed);
+    } else {
+      unpack(m.arena + m.embed, c.vocab, H, m.embed_unpacked);
+    }
     m.embed_ready = true;
   }
   linear_unpacked(norm.data() + (S - 1) * H, 1, 1, H, m.embed_unpacked, logits,
