@@ -363,113 +363,156 @@ gdn_recurrence_pipelined_kernel(const uint16_t *__restrict__ conv, const float *
 }
 
 // Fast form of the recurrence for calls of more than one token: the same two-tokens-in-flight loop,
-// but a warp owns 8 value columns and each column's 128 state rows are shared by four lanes (32 rows
-// each), so the two dependent chains per token are 32 long instead of 128 and end in two shuffles;
-// multiply and add are fused.  The sums therefore differ from the reference's order (row quarters
-// are added as a tree) and from its roundings (fused multiply-adds): results agree with the exact
-// kernels to f32 rounding noise, not bit for bit.  grid (value head, dv / 8), 32 threads.
+// but a warp owns 4 value columns and each column's 128 state rows are shared by eight lanes (16
+// rows each), so the two dependent chains per token are 16 long instead of 128 and end in three
+// shuffles; multiply and add are fused.  What bounds the exact kernel, and still bounds this one, is
+// how fast ONE warp can walk its dependent instructions (about one every two cycles), so the work of
+// a head is spread over 32 independent warps instead of 4.  A token then takes a few hundred cycles,
+// less than a trip to L2, so the inputs (k, q, decay, beta, the 4 values) arrive by cp.async in
+// chunks of 8 tokens, three chunks in shared memory per warp: the one in use, the next (token
+// t + 1's k is needed beside token t) and the one in flight.  The sums differ from the reference's
+// order (row groups are added as a tree) and from its roundings (fused multiply-adds): results
+// agree with the exact kernels to f32 rounding noise, not bit for bit.
+// grid (value head, dv / 16), 128 threads: four independent warps that share nothing.
+constexpr int kSplitChunk = 8; // tokens per chunk
+constexpr int kSplitWarps = 4;
+constexpr int kSplitCols = 8;  // value columns per warp
+constexpr int kSplitLanes = 32 / kSplitCols; // lanes per column
+
+// A lane reads its 16-byte pieces of k and q at the same offset inside its own row group; the groups
+// are kept 16 bytes out of step (rows + 4 floats apart) so that those reads fall into different banks.
+template <int DK> struct SplitChunk {
+  static constexpr int kRows = DK / kSplitLanes, kPitch = kRows + 4;
+  float kq[kSplitChunk][2][kSplitLanes][kPitch]; // per token: kn and qn, by row group
+  uint16_t value[kSplitChunk][kSplitCols];
+  float dc[kSplitChunk], bt[kSplitChunk];
+};
+
 template <int DK>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(32 * kSplitWarps)
 gdn_recurrence_split_kernel(const uint16_t *__restrict__ conv, const float *__restrict__ qn,
                             const float *__restrict__ kn, const float *__restrict__ beta,
-                            const float *__restrict__ decay, float *__restrict__ state, int64_t S, int nk,
+                            const float *__restrict__ decay, float *__restrict__ state, int S, int nk,
                             int nv, int dv, uint16_t *__restrict__ out) {
-  constexpr int kRows = DK / 4; // state rows per lane
+  constexpr int kRows = DK / kSplitLanes; // state rows per lane
+  using Chunk = SplitChunk<DK>;
+  extern __shared__ __align__(16) unsigned char split_sm[]; // Chunk [kSplitWarps][3]
   grid_dependency_sync();
   const int h = blockIdx.x;
-  const int lane = threadIdx.x, c = lane & 7, quarter = lane >> 3;
-  const int v = blockIdx.y * 8 + c;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, c = lane % kSplitCols, part = lane / kSplitCols;
+  const int v0 = (blockIdx.y * kSplitWarps + warp) * kSplitCols, v = v0 + c;
+  if (v0 >= dv) // the column groups need not fill the last CTA
+    return;
+  Chunk *chunks = reinterpret_cast<Chunk *>(split_sm) + warp * 3;
   const int kh = h / (nv / nk);
   const int64_t channels = 2 * static_cast<int64_t>(nk) * DK + static_cast<int64_t>(nv) * dv;
-  float *col = state + static_cast<int64_t>(h) * DK * dv + static_cast<int64_t>(quarter) * kRows * dv + v;
-  __shared__ __align__(16) float kq_sm[2][2 * DK]; // per token parity: kn[DK], qn[DK]
+  float *col = state + static_cast<int64_t>(h) * DK * dv + static_cast<int64_t>(part) * kRows * dv + v;
 
   float s[kRows];
 #pragma unroll
   for (int k = 0; k < kRows; ++k)
     s[k] = col[static_cast<int64_t>(k) * dv];
 
-  constexpr int kPre = DK / 32;
-  float k_next[kPre], q_next[kPre];
-  float dc_next = 0.0f, bt_next = 0.0f;
-  uint16_t value_next = 0;
-  auto fetch = [&](int64_t t) {
-#pragma unroll
-    for (int u = 0; u < kPre; ++u) {
-      k_next[u] = kn[(t * nk + kh) * DK + u * 32 + lane];
-      q_next[u] = qn[(t * nk + kh) * DK + u * 32 + lane];
-    }
-    dc_next = decay[t * nv + h];
-    bt_next = beta[t * nv + h];
-    value_next = conv[t * channels + 2 * static_cast<int64_t>(nk) * DK + h * dv + v];
+  auto copy = [](void *dst, const void *src, auto bytes) {
+    if (decltype(bytes)::value == 16)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src)
+                   : "memory");
+    else
+      asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src),
+                   "n"(decltype(bytes)::value)
+                   : "memory");
   };
-  auto publish = [&](int parity) {
-#pragma unroll
-    for (int u = 0; u < kPre; ++u) {
-      kq_sm[parity][u * 32 + lane] = k_next[u];
-      kq_sm[parity][DK + u * 32 + lane] = q_next[u];
+  // Requests chunk `index` (tokens 8 index .. 8 index + 7, those below S) and closes the copy group.
+  auto request = [&](int index) {
+    Chunk &ch = chunks[index % 3];
+    const int t0 = index * kSplitChunk;
+    for (int i = lane; i < kSplitChunk * (2 * DK / 4); i += 32) { // 16-byte pieces of k and q
+      const int token = i / (2 * DK / 4), piece = i % (2 * DK / 4);
+      if (t0 + token < S) {
+        const int which = piece / (DK / 4), row = (piece % (DK / 4)) * 4;
+        const float *src = (which ? qn : kn) + (static_cast<int64_t>(t0 + token) * nk + kh) * DK + row;
+        copy(&ch.kq[token][which][row / kRows][row % kRows], src, std::integral_constant<int, 16>());
+      }
     }
+    if (lane < kSplitChunk && t0 + lane < S) {
+      copy(&ch.value[lane][0], conv + (t0 + lane) * channels + 2 * static_cast<int64_t>(nk) * DK + h * dv + v0,
+           std::integral_constant<int, 2 * kSplitCols>());
+      copy(&ch.dc[lane], decay + static_cast<int64_t>(t0 + lane) * nv + h, std::integral_constant<int, 4>());
+      copy(&ch.bt[lane], beta + static_cast<int64_t>(t0 + lane) * nv + h, std::integral_constant<int, 4>());
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  auto over_quarters = [](float x) { // the four lanes of a column hold the quarters' partial sums
-    x += __shfl_xor_sync(0xffffffffu, x, 8);
-    x += __shfl_xor_sync(0xffffffffu, x, 16);
+  auto over_parts = [](float x) { // the lanes of a column hold its row groups' partial sums
+#pragma unroll
+    for (int o = kSplitCols; o < 32; o <<= 1)
+      x += __shfl_xor_sync(0xffffffffu, x, o);
     return x;
   };
-  const int row0 = quarter * kRows;
+  uint16_t *out_col = out + static_cast<int64_t>(h) * dv + v;
+  const int64_t out_stride = static_cast<int64_t>(nv) * dv;
 
-  fetch(0);
-  publish(0);
-  float dc = dc_next, bt = bt_next, value = bf16_to_f32(value_next);
-  if (S > 1)
-    fetch(1);
-  __syncwarp();
-  float kv = 0.0f;
-#pragma unroll
-  for (int k4 = 0; k4 < kRows; k4 += 4) {
-    const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[0][row0 + k4]);
-    const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      s[k4 + u] *= dc;
-      kv = __fmaf_rn(s[k4 + u], kv4[u], kv);
-    }
-  }
-  kv = over_quarters(kv);
-  for (int64_t t = 0; t < S; ++t) {
-    const int cur = static_cast<int>(t & 1);
-    const float delta = (value - kv) * bt;
-    float o = 0.0f;
-    if (t + 1 < S) {
-      publish(cur ^ 1);
-      const float dc1 = dc_next;
-      bt = bt_next;
-      value = bf16_to_f32(value_next);
-      if (t + 2 < S)
-        fetch(t + 2);
+  request(0);
+  request(1);
+  float kv = 0.0f, bt = 0.0f, value = 0.0f;
+  int slot = 0, cur_index = 0; // token t is slot `slot` of chunk `cur_index` (buffer cur_index % 3)
+  const Chunk *cur = chunks;
+  for (int t = 0; t < S; ++t) {
+    if (slot == 0) { // chunk index + 2 goes into the buffer of the chunk that has just been left
       __syncwarp();
-      float kv1 = 0.0f;
+      request(cur_index + 2);
+      asm volatile("cp.async.wait_group 1;" ::: "memory"); // all but the newest group: this chunk and the next
+      __syncwarp();
+    }
+    if (t == 0) { // the first token's decay and first chain on their own
+      const float dc = cur->dc[0];
+      bt = cur->bt[0];
+      value = bf16_to_f32(cur->value[0][c]);
 #pragma unroll
       for (int k4 = 0; k4 < kRows; k4 += 4) {
-        const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[cur][row0 + k4]);
-        const float4 qq = *reinterpret_cast<const float4 *>(&kq_sm[cur][DK + row0 + k4]);
-        const float4 kn1 = *reinterpret_cast<const float4 *>(&kq_sm[cur ^ 1][row0 + k4]);
+        const float4 kk = *reinterpret_cast<const float4 *>(&cur->kq[0][0][part][k4]);
+        const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[k4 + u] *= dc;
+          kv = __fmaf_rn(s[k4 + u], kv4[u], kv);
+        }
+      }
+      kv = over_parts(kv);
+    }
+    const float delta = (value - kv) * bt;
+    float o = 0.0f;
+    // where token t + 1 lives
+    const int nslot = slot + 1 == kSplitChunk ? 0 : slot + 1;
+    const int nindex = nslot == 0 ? cur_index + 1 : cur_index;
+    const Chunk *nxt = nslot == 0 ? chunks + nindex % 3 : cur;
+    if (t + 1 < S) {
+      const float dc1 = nxt->dc[nslot];
+      bt = nxt->bt[nslot];
+      value = bf16_to_f32(nxt->value[nslot][c]);
+      float kv1[2] = {0.0f, 0.0f}, o2[2] = {0.0f, 0.0f}; // two interleaved partial sums per chain
+#pragma unroll
+      for (int k4 = 0; k4 < kRows; k4 += 4) {
+        const float4 kk = *reinterpret_cast<const float4 *>(&cur->kq[slot][0][part][k4]);
+        const float4 qq = *reinterpret_cast<const float4 *>(&cur->kq[slot][1][part][k4]);
+        const float4 kn1 = *reinterpret_cast<const float4 *>(&nxt->kq[nslot][0][part][k4]);
         const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
         const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
         const float kw4[4] = {kn1.x, kn1.y, kn1.z, kn1.w};
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          s[k4 + u] = __fmaf_rn(kv4[u], delta, s[k4 + u]);
-          o = __fmaf_rn(s[k4 + u], qv4[u], o);
-          s[k4 + u] *= dc1;
-          kv1 = __fmaf_rn(s[k4 + u], kw4[u], kv1);
+          s[k4 + u] = __fmaf_rn(kv4[u], delta, s[k4 + u]); // row k as token t leaves it
+          o2[u & 1] = __fmaf_rn(s[k4 + u], qv4[u], o2[u & 1]);
+          s[k4 + u] *= dc1;                                // decayed for token t + 1
+          kv1[u & 1] = __fmaf_rn(s[k4 + u], kw4[u], kv1[u & 1]);
         }
       }
-      kv = over_quarters(kv1);
+      o = o2[0] + o2[1];
+      kv = over_parts(kv1[0] + kv1[1]);
     } else {
 #pragma unroll
       for (int k4 = 0; k4 < kRows; k4 += 4) {
-        const float4 kk = *reinterpret_cast<const float4 *>(&kq_sm[cur][row0 + k4]);
-        const float4 qq = *reinterpret_cast<const float4 *>(&kq_sm[cur][DK + row0 + k4]);
+        const float4 kk = *reinterpret_cast<const float4 *>(&cur->kq[slot][0][part][k4]);
+        const float4 qq = *reinterpret_cast<const float4 *>(&cur->kq[slot][1][part][k4]);
         const float kv4[4] = {kk.x, kk.y, kk.z, kk.w};
         const float qv4[4] = {qq.x, qq.y, qq.z, qq.w};
 #pragma unroll
@@ -479,11 +522,12 @@ gdn_recurrence_split_kernel(const uint16_t *__restrict__ conv, const float *__re
         }
       }
     }
-    o = over_quarters(o);
-    if (quarter == 0)
-      out[t * nv * dv + h * dv + v] = f32_to_bf16(o);
-    __syncwarp();
+    o = over_parts(o);
+    if (part == 0)
+      out_col[t * out_stride] = f32_to_bf16(o);
+    slot = nslot, cur_index = nindex, cur = nxt;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
   for (int k = 0; k < kRows; ++k)
     col[static_cast<int64_t>(k) * dv] = s[k];
@@ -517,9 +561,15 @@ cudaError_t launch_gated_delta_net(const uint16_t *conv, const uint16_t *a, cons
     const char *flag = std::getenv("LLMCP_B200_GDN_PIPELINE");
     return !(flag && flag[0] == '0');
   }();
-  if (dk == 128 && S > 1 && fast && dv % 8 == 0)
-    launch_chained(gdn_recurrence_split_kernel<128>, dim3(nv, dv / 8), dim3(32), 0, stream, conv, qn, kn, beta, decay, state, S, nk, nv,
-                   dv, out);
+  if (dk == 128 && S > 1 && fast && dv % kSplitCols == 0 && S < (1 << 30)) {
+    constexpr size_t split_bytes = kSplitWarps * 3 * sizeof(SplitChunk<128>);
+    if (cudaError_t e = opt_in_shared_memory(reinterpret_cast<const void *>(gdn_recurrence_split_kernel<128>), split_bytes);
+        e != cudaSuccess)
+      return e;
+    const int groups = dv / kSplitCols;
+    launch_chained(gdn_recurrence_split_kernel<128>, dim3(nv, (groups + kSplitWarps - 1) / kSplitWarps), dim3(32 * kSplitWarps),
+                   split_bytes, stream, conv, qn, kn, beta, decay, state, static_cast<int>(S), nk, nv, dv, out);
+  }
   else if (dk == 128 && S > 1 && pipelined)
     launch_chained(gdn_recurrence_pipelined_kernel<128>, dim3(grid), dim3(32), 0, stream, conv, qn, kn, beta, decay, state, S, nk, nv, dv, out);
   else if (dk == 128)
