@@ -49,31 +49,43 @@ namespace {
 using namespace tc;
 
 constexpr int kTileM = 128;
-constexpr int kTileN = 128;
-constexpr int kTmemBuffers = 4;             // 4 x 128 columns of 32-bit accumulators
+// Output tiles are 128 rows by TN columns, TN = 128 (four tensor-memory buffers) or 160 (three): the
+// wider tile exists for matrices whose 128-wide tiles would leave a nearly empty last wave (N = 2560 at
+// 1024 rows: 160 tiles on 148 SMs, against 128 tiles of 160 columns in one wave).
+template <int TN> struct Tile {
+  static_assert(TN == 128 || TN == 160, "tile widths with a tensor-memory plan");
+  static constexpr int kBuffers = TN == 128 ? 4 : 3;  // TN columns of 32-bit accumulators each, 512 in all
+  static constexpr int kStages = TN == 128 ? 6 : 5;
+  static constexpr int kWarpColumns = TN / 4;         // columns per epilogue warp: 32, or 32 + 8
+  static constexpr int kOperandBytesB = TN * 128;
+};
+constexpr int kMaxBuffers = 4, kMaxStages = 6;
 constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueWarps = 16;
 constexpr int kThreads = 32 * (kEpilogueWarp0 + kEpilogueWarps);
 constexpr int kOperandBytes = kTileM * 128;  // 16 KB per operand per stage: rows of 128 bytes of K
-constexpr int kStages = 6;
 constexpr int kBarrierBytes = 256;
 
 // F16: operands are f16 values (64 per 128-byte row = 2 quantisation blocks per stage);
 // otherwise int8 (128 per row = 4 blocks per stage).
-template <bool F16> struct Form {
+template <bool F16, int TN = 128> struct Form {
   static constexpr int kStageBlocks = F16 ? 2 : 4;
   static constexpr int kStageK = kStageBlocks * 32;                 // elements of K per stage
-  static constexpr int kScaleBytes = kStageBlocks * kTileM * 4;     // per operand per stage
-  static constexpr int kStageBytes = 2 * kOperandBytes + 2 * kScaleBytes; // 34 KB / 36 KB, multiples of 1024
-  static constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + kBarrierBytes;
+  static constexpr int kScaleBytesA = kStageBlocks * kTileM * 4;    // the rows' scales of a stage
+  static constexpr int kScaleBytesB = kStageBlocks * TN * 4;        // the columns' scales
+  static constexpr int kScaleBytes = (kScaleBytesA + kScaleBytesB + 1023) / 1024 * 1024;
+  static constexpr int kStageBytes = kOperandBytes + Tile<TN>::kOperandBytesB + kScaleBytes; // multiples of 1024
+  static constexpr size_t kSmemBytes = 1024 + Tile<TN>::kStages * kStageBytes + kBarrierBytes;
 };
 
-// kind::f16: f16 x f16 -> f32, both operands K-major, M = 128, N = 128, K = 16 per instruction.
-constexpr uint32_t kInstructionF16 = (1u << 4) | ((kTileN >> 3) << 17) | ((kTileM >> 4) << 24);
-// kind::i8: s8 x s8 -> s32, both operands K-major, M = 128, N = 128, K = 32 per instruction.
-constexpr uint32_t kInstructionI8 = (2u << 4) | (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | ((kTileM >> 4) << 24);
+// kind::f16: f16 x f16 -> f32, both operands K-major, M = 128, N = TN, K = 16 per instruction.
+// kind::i8: s8 x s8 -> s32, both operands K-major, M = 128, N = TN, K = 32 per instruction.
+template <int TN> struct Instruction {
+  static constexpr uint32_t kF16 = (1u << 4) | ((TN >> 3) << 17) | ((kTileM >> 4) << 24);
+  static constexpr uint32_t kI8 = (2u << 4) | (1u << 7) | (1u << 10) | ((TN >> 3) << 17) | ((kTileM >> 4) << 24);
+};
 
-__device__ __forceinline__ void mma_f16(uint32_t tmem, uint64_t a, uint64_t b, uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16(uint32_t tmem, uint64_t a, uint64_t b, uint32_t accumulate, uint32_t kInstructionF16) {
   asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p; }"
                :
@@ -81,7 +93,7 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem, uint64_t a, uint64_t b, u
                : "memory");
 }
 
-__device__ __forceinline__ void mma_i8(uint32_t tmem, uint64_t a, uint64_t b) {
+__device__ __forceinline__ void mma_i8(uint32_t tmem, uint64_t a, uint64_t b, uint32_t kInstructionI8) {
   asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p; }"
                :
@@ -102,10 +114,10 @@ __device__ __forceinline__ void fma2(float &c0, float &c1, float a0, float a1, f
 }
 
 struct Barriers {
-  uint64_t full[kStages];        // stage landed in shared memory (one arrival + the copies' bytes)
-  uint64_t empty[kStages];       // stage no longer needed: MMA done (1) + every epilogue warp (scales read)
-  uint64_t tfull[kTmemBuffers];  // a block's dot products are in the tensor-memory buffer
-  uint64_t tempty[kTmemBuffers]; // the buffer has been read by all epilogue warps
+  uint64_t full[kMaxStages];     // stage landed in shared memory (one arrival + the copies' bytes)
+  uint64_t empty[kMaxStages];    // stage no longer needed: MMA done (1) + every epilogue warp (scales read)
+  uint64_t tfull[kMaxBuffers];   // a block's dot products are in the tensor-memory buffer
+  uint64_t tempty[kMaxBuffers];  // the buffer has been read by all epilogue warps
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -113,14 +125,16 @@ struct Barriers {
 // fault (test hook): 1 = the loader announces the first stage's bytes but never issues its copies,
 // so the barrier of that stage cannot complete and every wait behind it has to run out.
 // PACKED: the epilogue's multiplies and fmas as two-lane f32x2 instructions (same roundings).
-template <bool F16, bool PACKED, bool DOTS>
+template <bool F16, bool PACKED, bool DOTS, int TN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_as, const __grid_constant__ CUtensorMap map_bs, int M, int K,
                     int N, void *__restrict__ y, int y_dtype, int activation, int32_t *__restrict__ dots_out,
                     int *__restrict__ error_out, uint32_t spin_limit, int fault) {
-  constexpr int kStageBlocks = Form<F16>::kStageBlocks, kStageK = Form<F16>::kStageK, kScaleBytes = Form<F16>::kScaleBytes,
-                kStageBytes = Form<F16>::kStageBytes;
+  using F = Form<F16, TN>;
+  constexpr int kStageBlocks = F::kStageBlocks, kStageK = F::kStageK, kStageBytes = F::kStageBytes;
+  constexpr int kTileN = TN, kTmemBuffers = Tile<TN>::kBuffers, kStages = Tile<TN>::kStages, kWarpColumns = Tile<TN>::kWarpColumns;
+  constexpr int kOperandBytesB = Tile<TN>::kOperandBytesB;
   extern __shared__ uint8_t raw_smem[];
   uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   Barriers *bars = reinterpret_cast<Barriers *>(base + kStages * kStageBytes);
@@ -145,7 +159,7 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
-                 "r"(kTmemBuffers * kTileN)
+                 "r"(512)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -164,15 +178,15 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (it >= kStages && !mbar_wait(&bars->empty[s], ((it / kStages) - 1) & 1, abort_flag, spin_limit))
           break;
         uint8_t *stage = base + s * kStageBytes;
-        mbar_expect_tx(&bars->full[s], kStageBytes);
+        mbar_expect_tx(&bars->full[s], kOperandBytes + kOperandBytesB + F::kScaleBytesA + F::kScaleBytesB);
         issued = it + 1;
         if (fault == 1 && it == 0)
           continue;
         const int k0 = it * kStageK, kb0 = it * kStageBlocks;
         tma_load_2d(stage, &map_a, k0, m0, &bars->full[s]);
         tma_load_2d(stage + kOperandBytes, &map_b, k0, n0, &bars->full[s]);
-        tma_load_2d(stage + 2 * kOperandBytes, &map_as, m0, kb0, &bars->full[s]);
-        tma_load_2d(stage + 2 * kOperandBytes + kScaleBytes, &map_bs, n0, kb0, &bars->full[s]);
+        tma_load_2d(stage + kOperandBytes + kOperandBytesB, &map_as, m0, kb0, &bars->full[s]);
+        tma_load_2d(stage + kOperandBytes + kOperandBytesB + F::kScaleBytesA, &map_bs, n0, kb0, &bars->full[s]);
       }
       // Leaving after a failed wait: the copies already requested still write into this CTA's
       // shared memory, so each of them gets one more bounded wait before the CTA may exit.
@@ -205,10 +219,10 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           }
           const uint32_t d = tmem_base + buf * kTileN;
           if (F16) { // two K = 16 instructions per block: the first overwrites, the second accumulates
-            mma_f16(d, operand_descriptor(a_addr + j * 64), operand_descriptor(b_addr + j * 64), 0u);
-            mma_f16(d, operand_descriptor(a_addr + j * 64 + 32), operand_descriptor(b_addr + j * 64 + 32), 1u);
+            mma_f16(d, operand_descriptor(a_addr + j * 64), operand_descriptor(b_addr + j * 64), 0u, Instruction<TN>::kF16);
+            mma_f16(d, operand_descriptor(a_addr + j * 64 + 32), operand_descriptor(b_addr + j * 64 + 32), 1u, Instruction<TN>::kF16);
           } else {
-            mma_i8(d, operand_descriptor(a_addr + j * 32), operand_descriptor(b_addr + j * 32));
+            mma_i8(d, operand_descriptor(a_addr + j * 32), operand_descriptor(b_addr + j * 32), Instruction<TN>::kI8);
           }
           mma_commit(&bars->tfull[buf]);
         }
@@ -218,12 +232,12 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   } else {
     // ---- epilogue ---------------------------------------------------------------------------
     const int quarter = warp & 3;                  // tensor-memory lanes 32*quarter .. +31 (fixed by the warp number)
-    const int colq = (warp - kEpilogueWarp0) >> 2; // columns 32*colq .. +31
+    const int colq = (warp - kEpilogueWarp0) >> 2; // columns kWarpColumns * colq .. + kWarpColumns - 1
     const int row = quarter * 32 + lane;
     const int gm = m0 + row;
-    float acc[32];
+    float acc[kWarpColumns];
 #pragma unroll
-    for (int c = 0; c < 32; ++c)
+    for (int c = 0; c < kWarpColumns; ++c)
       acc[c] = 0.0f;
     bool ok = true;
     for (int kb = 0; kb < nb && ok; ++kb) {
@@ -239,23 +253,30 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         ok = false;
         break;
       }
-      const float *scales = reinterpret_cast<const float *>(base + s * kStageBytes + 2 * kOperandBytes);
+      const float *scales = reinterpret_cast<const float *>(base + s * kStageBytes + kOperandBytes + kOperandBytesB);
       const float a_scale = scales[j * kTileM + row];
-      const float4 *w_scale = reinterpret_cast<const float4 *>(scales + kStageBlocks * kTileM + j * kTileN + colq * 32);
-      uint32_t raw[32];
-      tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kTileN + colq * 32, raw);
+      const float4 *w_scale = reinterpret_cast<const float4 *>(scales + kStageBlocks * kTileM + j * kTileN + colq * kWarpColumns);
+      uint32_t raw[kWarpColumns];
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kTileN + colq * kWarpColumns;
+      if (kWarpColumns == 32) {
+        tmem_load32(taddr, *reinterpret_cast<uint32_t(*)[32]>(raw));
+      } else { // 32 + 8 columns, one wait for both loads
+        tmem_issue32(taddr, *reinterpret_cast<uint32_t(*)[32]>(raw));
+        tmem_issue8(taddr + 32, *reinterpret_cast<uint32_t(*)[8]>(raw + 32));
+        tmem_wait_loads();
+      }
       // The buffer is handed back before any arithmetic, so that the MMA of a later block can
       // reuse it while this one is still being folded in.
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&bars->tempty[buf]);
-      float v[32];
+      float v[kWarpColumns];
 #pragma unroll
-      for (int u = 0; u < 32; ++u)
+      for (int u = 0; u < kWarpColumns; ++u)
         v[u] = F16 ? __uint_as_float(raw[u]) : __int2float_rn(static_cast<int>(raw[u]));
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+      for (int g = 0; g < kWarpColumns / 4; ++g) {
         const float4 w4 = w_scale[g];
         if (PACKED) {
           float f0, f1, f2, f3;
@@ -273,8 +294,8 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (DOTS) {
         if (gm < M) {
 #pragma unroll
-          for (int u = 0; u < 32; ++u) {
-            const int gn = n0 + colq * 32 + u;
+          for (int u = 0; u < kWarpColumns; ++u) {
+            const int gn = n0 + colq * kWarpColumns + u;
             if (gn < N)
               dots_out[(static_cast<size_t>(gm) * N + gn) * nb + kb] = F16 ? __float2int_rn(v[u]) : static_cast<int>(raw[u]);
           }
@@ -288,8 +309,8 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     if (ok && gm < M) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const int gn = n0 + colq * 32 + g * 8;
+      for (int g = 0; g < kWarpColumns / 8; ++g) {
+        const int gn = n0 + colq * kWarpColumns + g * 8;
         if (gn < N) { // N is a multiple of 8, so a group of eight is entirely inside or outside
           float o[8];
 #pragma unroll
@@ -316,7 +337,7 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemBuffers * kTileN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
   if (tid == 0 && bars->abort_flag && error_out)
     atomicExch(error_out, 1);
@@ -363,13 +384,13 @@ __global__ void weights_to_f16_kernel(const int8_t *__restrict__ wq, const uint1
 
 // rows x K operand plane, K contiguous: boxes of 128 rows x 128 bytes of K (64 f16 or 128 int8),
 // 128-byte swizzle; out-of-range parts read as zero.
-bool operand_map(CUtensorMap *map, const void *plane, int64_t rows, int K, bool f16) {
+bool operand_map(CUtensorMap *map, const void *plane, int64_t rows, int K, bool f16, int box_rows = kTileM) {
   EncodeTiled encode = encode_tiled();
   if (!encode)
     return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * (f16 ? 2 : 1)};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(f16 ? 64 : 128), kTileM};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(f16 ? 64 : 128), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   return encode(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(plane), dims,
                 strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -377,41 +398,67 @@ bool operand_map(CUtensorMap *map, const void *plane, int64_t rows, int K, bool 
 }
 
 // nb x ld f32, block-major: boxes of a stage's blocks x 128 entries.
-bool scale_map(CUtensorMap *map, const void *plane, int64_t entries, int64_t ld, int nb, int stage_blocks) {
+bool scale_map(CUtensorMap *map, const void *plane, int64_t entries, int64_t ld, int nb, int stage_blocks, int box_entries = kTileM) {
   EncodeTiled encode = encode_tiled();
   if (!encode)
     return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(entries), static_cast<cuuint64_t>(nb)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
-  const cuuint32_t box[2] = {kTileM, static_cast<cuuint32_t>(stage_blocks)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_entries), static_cast<cuuint32_t>(stage_blocks)};
   const cuuint32_t elem[2] = {1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(plane), dims, strides, box, elem,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <bool F16, bool PACKED, int TN>
+cudaError_t launch_tile(const void *a, const float *ast, int M, int K, const void *w, const float *wst, int N, void *y,
+                        int y_dtype, int activation, int32_t *dots_out, int *error_flag, cudaStream_t stream, uint32_t spin_limit,
+                        int fault) {
+  using F = Form<F16, TN>;
+  const int nb = K / kBlock;
+  CUtensorMap map_a, map_b, map_as, map_bs;
+  if (!operand_map(&map_a, a, M, K, F16) || !operand_map(&map_b, w, N, K, F16, TN) ||
+      !scale_map(&map_as, ast, M, gemm_tc16_scale_pitch(M), nb, F::kStageBlocks) ||
+      !scale_map(&map_bs, wst, N, N, nb, F::kStageBlocks, TN))
+    return cudaErrorNotSupported;
+  const void *kernel = dots_out ? reinterpret_cast<const void *>(gemm_q8_tma_kernel<F16, PACKED, true, TN>)
+                                : reinterpret_cast<const void *>(gemm_q8_tma_kernel<F16, PACKED, false, TN>);
+  if (cudaError_t e = opt_in_shared_memory(kernel, F::kSmemBytes); e != cudaSuccess)
+    return e;
+  dim3 grid((N + TN - 1) / TN, (M + kTileM - 1) / kTileM);
+  if (dots_out)
+    launch_chained(gemm_q8_tma_kernel<F16, PACKED, true, TN>, grid, dim3(kThreads), F::kSmemBytes, stream, map_a, map_b, map_as,
+                   map_bs, M, K, N, y, y_dtype, activation, dots_out, error_flag, spin_limit, fault);
+  else
+    launch_chained(gemm_q8_tma_kernel<F16, PACKED, false, TN>, grid, dim3(kThreads), F::kSmemBytes, stream, map_a, map_b, map_as,
+                   map_bs, M, K, N, y, y_dtype, activation, dots_out, error_flag, spin_limit, fault);
+  return cudaGetLastError();
+}
+
+// Tile width for an M x N output: every wave of tiles costs about the same whatever it holds, a
+// 160-wide tile a quarter more than a 128-wide one; LLMCP_B200_GEMM_TILE=128|160 overrides.
+int choose_tile(int M, int N) {
+  const char *flag = std::getenv("LLMCP_B200_GEMM_TILE");
+  const int forced = flag ? std::atoi(flag) : 0;
+  if (forced == 128 || forced == 160)
+    return forced;
+  int sm_count = 148;
+  if (current_sm_count(&sm_count) != cudaSuccess || sm_count <= 0)
+    sm_count = 148;
+  const int64_t sms = sm_count;
+  const int64_t rows = (M + kTileM - 1) / kTileM;
+  const int64_t waves128 = (rows * ((N + 127) / 128) + sms - 1) / sms, waves160 = (rows * ((N + 159) / 160) + sms - 1) / sms;
+  return waves160 * 5 < waves128 * 4 ? 160 : 128;
+}
+
 template <bool F16, bool PACKED>
 cudaError_t launch_form(const void *a, const float *ast, int M, int K, const void *w, const float *wst, int N, void *y,
                         int y_dtype, int activation, int32_t *dots_out, int *error_flag, cudaStream_t stream, uint32_t spin_limit,
                         int fault) {
-  const int nb = K / kBlock;
-  CUtensorMap map_a, map_b, map_as, map_bs;
-  if (!operand_map(&map_a, a, M, K, F16) || !operand_map(&map_b, w, N, K, F16) ||
-      !scale_map(&map_as, ast, M, gemm_tc16_scale_pitch(M), nb, Form<F16>::kStageBlocks) ||
-      !scale_map(&map_bs, wst, N, N, nb, Form<F16>::kStageBlocks))
-    return cudaErrorNotSupported;
-  const void *kernel = dots_out ? reinterpret_cast<const void *>(gemm_q8_tma_kernel<F16, PACKED, true>)
-                                : reinterpret_cast<const void *>(gemm_q8_tma_kernel<F16, PACKED, false>);
-  if (cudaError_t e = opt_in_shared_memory(kernel, Form<F16>::kSmemBytes); e != cudaSuccess)
-    return e;
-  dim3 grid((N + kTileN - 1) / kTileN, (M + kTileM - 1) / kTileM);
-  if (dots_out)
-    launch_chained(gemm_q8_tma_kernel<F16, PACKED, true>, grid, dim3(kThreads), Form<F16>::kSmemBytes, stream, map_a, map_b,
-                   map_as, map_bs, M, K, N, y, y_dtype, activation, dots_out, error_flag, spin_limit, fault);
-  else
-    launch_chained(gemm_q8_tma_kernel<F16, PACKED, false>, grid, dim3(kThreads), Form<F16>::kSmemBytes, stream, map_a, map_b,
-                   map_as, map_bs, M, K, N, y, y_dtype, activation, dots_out, error_flag, spin_limit, fault);
-  return cudaGetLastError();
+  if (choose_tile(M, N) == 160)
+    return launch_tile<F16, PACKED, 160>(a, ast, M, K, w, wst, N, y, y_dtype, activation, dots_out, error_flag, stream, spin_limit, fault);
+  return launch_tile<F16, PACKED, 128>(a, ast, M, K, w, wst, N, y, y_dtype, activation, dots_out, error_flag, stream, spin_limit, fault);
 }
 
 // [rows][K/32] scales -> block-major f32 [K/32][ld]; scales are f32 (activations) or f16 bits (weights).

@@ -485,3 +485,35 @@ def test_linear_q8_every_gemm_form(monkeypatch):
         y, dots = L.ops.linear_q8(x, packed, N, y_bf16=False, want_dots=True)
         assert np.array_equal(y.view(np.uint32), want.view(np.uint32)), form
         assert np.array_equal(dots, want_dots), form
+
+
+def test_linear_q8_both_tile_widths(monkeypatch):
+    """The TMA-fed GEMM with 128- and with 160-column tiles (the second exists for matrices whose
+    128-wide tiles would leave a nearly empty last wave): every form exact, block dots included, a
+    partial last tile in both directions, bf16 output with an activation; and the automatic choice on
+    a 1024 x 2560 output (160 tiles of 128 columns against 128 tiles of 160 in one wave)."""
+    rng = np.random.default_rng(33)
+    M, N, K = 130, 264, 2560
+    packed = oracle.pack_q8_0_p4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    x = rand_bf16(rng, M, K)
+    want = oracle.linear_q8(x, packed, N, y_bf16=False)
+    want_silu = oracle.linear_q8(x, packed, N, activation="silu")
+    q, _ = oracle.act_quant(x)
+    want_dots = oracle.block_dots(q, packed, N)
+    for tile in ("128", "160"):
+        monkeypatch.setenv("LLMCP_B200_GEMM_TILE", tile)
+        for form in ("i8", "i8x2", "f16", "f16x2"):
+            monkeypatch.setenv("LLMCP_B200_GEMM", form)
+            y, dots = L.ops.linear_q8(x, packed, N, y_bf16=False, want_dots=True)
+            assert np.array_equal(y.view(np.uint32), want.view(np.uint32)), (tile, form)
+            assert np.array_equal(dots, want_dots), (tile, form)
+            assert np.array_equal(L.ops.linear_q8(x, packed, N, activation="silu"), want_silu), (tile, form)
+    monkeypatch.delenv("LLMCP_B200_GEMM_TILE")
+    monkeypatch.delenv("LLMCP_B200_GEMM")
+    M, N, K = 1024, 2560, 256
+    packed = oracle.pack_q8_0_p4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    x = rand_bf16(rng, M, K)
+    y, dots = L.ops.linear_q8(x, packed, N, y_bf16=False, want_dots=True)
+    assert np.array_equal(y.view(np.uint32), oracle.linear_q8(x, packed, N, y_bf16=False).view(np.uint32))
+    assert np.array_equal(dots, oracle.block_dots(oracle.act_quant(x)[0], packed, N))
+
