@@ -153,6 +153,13 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   // here, so that a failed create leaves no device or pinned memory behind.
   try {
   check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+  for (int i = 0; i < kSideStreams; ++i) {
+    check(cudaStreamCreateWithFlags(&side_streams_[i], cudaStreamNonBlocking), "cudaStreamCreate");
+    check(cudaEventCreateWithFlags(&join_events_[i], cudaEventDisableTiming), "cudaEventCreate");
+  }
+  check(cudaEventCreateWithFlags(&fork_event_, cudaEventDisableTiming), "cudaEventCreate");
+  if (const char *flag = std::getenv("LLMCP_B200_CONCURRENT_GEMMS"))
+    concurrent_gemms_ = std::atoi(flag) != 0;
 
   // Prefill GEMM form: decides which weight planes load_weights() builds.
   if (const char *flag = std::getenv("LLMCP_B200_GEMM")) {
@@ -270,6 +277,17 @@ void Engine::release() noexcept {
   logits_pinned_ = nullptr;
   token_pinned_ = nullptr;
   position_pinned_ = nullptr;
+  for (int i = 0; i < kSideStreams; ++i) {
+    if (side_streams_[i])
+      cudaStreamDestroy(side_streams_[i]);
+    if (join_events_[i])
+      cudaEventDestroy(join_events_[i]);
+    side_streams_[i] = nullptr;
+    join_events_[i] = nullptr;
+  }
+  if (fork_event_)
+    cudaEventDestroy(fork_event_);
+  fork_event_ = nullptr;
   if (stream_)
     cudaStreamDestroy(stream_);
   stream_ = nullptr;
@@ -637,6 +655,13 @@ const uint16_t *Engine::gather_rows(const uint16_t *src, int64_t S, int64_t n_lo
   return reinterpret_cast<const uint16_t *>(tp_->slot(slot));
 }
 
+// Streams and events for independent GEMMs that share an input (Engine::side_streams_).
+struct SideStreams {
+  cudaStream_t *streams;
+  cudaEvent_t fork, *joins;
+  int count;
+};
+
 struct LinearJob {
   const Q8Weight *w;
   void *y;
@@ -653,7 +678,7 @@ struct F16Planes {
 
 static void run_linears(const F16Planes &planes, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
                         cudaStream_t stream, uint64_t *launches, int flags, int *gemm_error = nullptr,
-                        const uint16_t *xb = nullptr, int *status = nullptr) {
+                        const uint16_t *xb = nullptr, int *status = nullptr, const SideStreams *side = nullptr) {
   if (jobs[0].w->bf) { // bf16 matrices: the input rows are bf16 (xb), one launch per matrix
     for (int i = 0; i < count; ++i) {
       const Q8Weight &w = *jobs[i].w;
@@ -694,11 +719,23 @@ static void run_linears(const F16Planes &planes, const int8_t *aq, const float *
       launch_scales_block_major(as, 0, S, jobs[0].w->K, gemm_tc16_scale_pitch(S), planes.ast, stream);
     *launches += 1;
   }
+  // Matrices that share the input are independent: the first stays on the stream, the others go to
+  // side streams behind a fork event, and the stream waits for all of them afterwards.  Their tiles
+  // then fill the SMs together instead of ending in a partly empty wave each.
+  const bool fork = side && count > 1 && tma;
+  if (fork && cudaEventRecord(side->fork, stream) != cudaSuccess)
+    throw std::runtime_error("gemm: cudaEventRecord");
   for (int i = 0; i < count; ++i) {
+    cudaStream_t stream_i = stream;
+    if (fork && i > 0) {
+      stream_i = side->streams[(i - 1) % side->count];
+      if (i - 1 < side->count && cudaStreamWaitEvent(stream_i, side->fork, 0) != cudaSuccess)
+        throw std::runtime_error("gemm: cudaStreamWaitEvent");
+    }
     cudaError_t e =
         tma ? launch_gemm_q8_tma(planes.form, f16 ? planes.ah : static_cast<const void *>(aq), planes.ast, static_cast<int>(S),
                                  jobs[i].w->K, f16 ? jobs[i].w->h : static_cast<const void *>(jobs[i].w->q), jobs[i].w->d32t,
-                                 jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, gemm_error, stream)
+                                 jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, gemm_error, stream_i)
         : gemm_error ? launch_gemm_q8_tc(aq, as, static_cast<int>(S), jobs[i].w->K, jobs[i].w->q, jobs[i].w->d32,
                                          jobs[i].w->N, jobs[i].y, jobs[i].y_dtype, jobs[i].activation, nullptr, gemm_error,
                                          stream)
@@ -707,6 +744,12 @@ static void run_linears(const F16Planes &planes, const int8_t *aq, const float *
     if (e != cudaSuccess)
       throw std::runtime_error(std::string("gemm: ") + cudaGetErrorString(e));
     *launches += 1;
+  }
+  if (fork) {
+    const int used = std::min(count - 1, side->count);
+    for (int i = 0; i < used; ++i)
+      if (cudaEventRecord(side->joins[i], side->streams[i]) != cudaSuccess || cudaStreamWaitEvent(stream, side->joins[i], 0) != cudaSuccess)
+        throw std::runtime_error("gemm: joining the side streams failed");
   }
 }
 
@@ -797,6 +840,8 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
   const int gemv_flags = gemv_flags_ | (mode_ == kModeFast ? kGemvFast : 0);
   const F16Planes planes = {ah_, ast_, gemm_kind_ >= 2 ? gemm_kind_ - 2 : -1};
   int *gemm_status = use_tensor_cores_ ? gemm_error_ : nullptr;
+  SideStreams side_streams = {side_streams_, fork_event_, join_events_, kSideStreams};
+  const SideStreams *side = concurrent_gemms_ && S > 1 ? &side_streams : nullptr;
   int cur = 0;
   const uint16_t *pending = nullptr; // the MLP output still to be added to the residual stream
   int64_t lin_index = 0, full_index = 0;
@@ -816,7 +861,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
+      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, side);
       const int C = static_cast<int>(m.qkv_dim());
       uint16_t *conv_state = conv_base + lin_index * (c.conv_kernel - 1) * C;
       float *delta_state = delta_base + lin_index * m.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
@@ -861,7 +906,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
+      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, side);
       uint16_t *cache = kv_base + full_index * 2 * m.kv_heads * capacity_ * c.head_dim;
       const int nh = static_cast<int>(m.heads), nkv = static_cast<int>(m.kv_heads), hd = static_cast<int>(c.head_dim);
       const int64_t cache_stride = rows_are_sequences ? static_cast<int64_t>(kv_seq_) : 0;
@@ -907,7 +952,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       gather_quant(S, inter_rows_, &mlp_q, &mlp_s, product_q, product_s);
     } else {
       const LinearJob mlp[2] = {{&L.gate, gate_, kBF16, kSilu}, {&L.up, up_, kBF16, kNone}};
-      run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
+      run_linears(planes, aq_, as_, S, mlp, 2, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, side);
       check(launch_pointwise(gate_, up_, S * inter_rows_, 1, act_y, act_q, act_s, stream_), "mul");
       launches_ += 2;
       if (!bf)

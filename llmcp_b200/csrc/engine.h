@@ -179,6 +179,12 @@ private:
   int device_ = 0;
   int mode_ = kModeExact;
   cudaStream_t stream_ = nullptr;
+  // Independent GEMMs of a prefill (the projections that share an input) run side by side: a fork
+  // event on stream_, one side stream and one join event per extra matrix.
+  static constexpr int kSideStreams = 3;
+  cudaStream_t side_streams_[kSideStreams] = {};
+  cudaEvent_t fork_event_ = nullptr, join_events_[kSideStreams] = {};
+  bool concurrent_gemms_ = true;
   uint64_t launches_ = 0;
 
   std::vector<void *> allocations_;

@@ -118,6 +118,7 @@ struct Barriers {
   uint64_t empty[kMaxStages];    // stage no longer needed: MMA done (1) + every epilogue warp (scales read)
   uint64_t tfull[kMaxBuffers];   // a block's dot products are in the tensor-memory buffer
   uint64_t tempty[kMaxBuffers];  // the buffer has been read by all epilogue warps
+  uint64_t done;                 // the last commit of the MMA lane has arrived (see the end of its loop)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -154,6 +155,7 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       mbar_init(&bars->tfull[i], 1);
       mbar_init(&bars->tempty[i], kEpilogueWarps);
     }
+    mbar_init(&bars->done, 1);
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -228,6 +230,12 @@ gemm_q8_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         mma_commit(&bars->empty[s]);
       }
+      // A commit's arrival is asynchronous, and nothing else waits for the last ones on `empty`: the
+      // CTA must not end (and hand its shared memory to the next CTA on this SM, possibly of another
+      // kernel with its barriers elsewhere) while an arrival is still on its way.  Commits arrive in
+      // order, so seeing this one means all have.
+      mma_commit(&bars->done);
+      mbar_wait_quiet(&bars->done, 0, spin_limit);
     }
   } else {
     // ---- epilogue ---------------------------------------------------------------------------
