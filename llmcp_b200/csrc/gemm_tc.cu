@@ -145,6 +145,7 @@ struct Barriers {
   uint64_t empty[kStages];         // stage no longer needed: MMA done (1) + every epilogue warp
   uint64_t tfull[kTmemBuffers];    // a block's dot products are in the tensor-memory buffer
   uint64_t tempty[kTmemBuffers];   // the buffer has been read by all epilogue warps
+  uint64_t done;                   // the MMA lane's last commit has arrived
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -170,6 +171,8 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
     }
     for (int i = 0; i < kTmemBuffers; ++i) {
       mbar_init(&bars->tfull[i], 1);
+      if (i == 0)
+        mbar_init(&bars->done, 1);
       mbar_init(&bars->tempty[i], kEpilogueThreads / 32);
     }
     bars->abort_flag = 0;
@@ -258,6 +261,10 @@ gemm_q8_tc_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, i
         }
         mma_commit(&bars->empty[s]);
       }
+      // Nothing else waits for the last arrivals on `empty`; commits arrive in order, so once this
+      // one is in, none is still on its way into shared memory that the next CTA on this SM owns.
+      mma_commit(&bars->done);
+      mbar_wait(&bars->done, 0, abort_flag);
     }
   } else if (warp >= kEpilogueWarp0) {
     // ---- epilogue ---------------------------------------------------------------------------

@@ -119,6 +119,14 @@ __device__ __forceinline__ void tmem_issue8(uint32_t taddr, uint32_t (&r)[8]) {
                : "memory");
 }
 __device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The wait as the point where the registers of loads issued earlier become defined: the compiler
+// must not read (or reuse a copy of) them from before this statement.
+template <int N> __device__ __forceinline__ void tmem_wait_loads_into(uint32_t (&r)[N]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+    asm volatile("" : "+r"(r[i])::"memory");
+}
 
 using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,

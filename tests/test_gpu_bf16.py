@@ -92,6 +92,7 @@ def test_bf16_arena_through_engine_and_aot_entries(tmp_path, mode):
     model.close()
     other.close()
     # the drop-in entry points take the same container
+    L.lib().llmcp_b200_clear_error()  # a message left by an earlier, deliberately failing call
     runtime = L.AotRuntime(d)
     assert runtime.init(max_sequence=24)
     got = runtime.forward(arena, prompt, 0, len(prompt))
