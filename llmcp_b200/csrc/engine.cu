@@ -153,11 +153,6 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   // here, so that a failed create leaves no device or pinned memory behind.
   try {
   check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
-  for (int i = 0; i < kSideStreams; ++i) {
-    check(cudaStreamCreateWithFlags(&side_streams_[i], cudaStreamNonBlocking), "cudaStreamCreate");
-    check(cudaEventCreateWithFlags(&join_events_[i], cudaEventDisableTiming), "cudaEventCreate");
-  }
-  check(cudaEventCreateWithFlags(&fork_event_, cudaEventDisableTiming), "cudaEventCreate");
   if (const char *flag = std::getenv("LLMCP_B200_CONCURRENT_GEMMS"))
     concurrent_gemms_ = std::atoi(flag) != 0;
 
@@ -277,9 +272,29 @@ void Engine::release() noexcept {
   logits_pinned_ = nullptr;
   token_pinned_ = nullptr;
   position_pinned_ = nullptr;
+  drop_side_streams();
+  if (stream_)
+    cudaStreamDestroy(stream_);
+  stream_ = nullptr;
+  cudaGetLastError();
+}
+
+// The side streams exist only while a call of more than one token runs.
+void Engine::make_side_streams() {
+  for (int i = 0; i < kSideStreams; ++i) {
+    if (!side_streams_[i])
+      check(cudaStreamCreateWithFlags(&side_streams_[i], cudaStreamNonBlocking), "cudaStreamCreate");
+    if (!join_events_[i])
+      check(cudaEventCreateWithFlags(&join_events_[i], cudaEventDisableTiming), "cudaEventCreate");
+  }
+  if (!fork_event_)
+    check(cudaEventCreateWithFlags(&fork_event_, cudaEventDisableTiming), "cudaEventCreate");
+}
+
+void Engine::drop_side_streams() noexcept {
   for (int i = 0; i < kSideStreams; ++i) {
     if (side_streams_[i])
-      cudaStreamDestroy(side_streams_[i]);
+      cudaStreamDestroy(side_streams_[i]); // returns at once; the stream goes when its work is done
     if (join_events_[i])
       cudaEventDestroy(join_events_[i]);
     side_streams_[i] = nullptr;
@@ -288,10 +303,6 @@ void Engine::release() noexcept {
   if (fork_event_)
     cudaEventDestroy(fork_event_);
   fork_event_ = nullptr;
-  if (stream_)
-    cudaStreamDestroy(stream_);
-  stream_ = nullptr;
-  cudaGetLastError();
 }
 
 void Engine::validate_tokens(const int64_t *tokens, int64_t S) const {
@@ -840,8 +851,11 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
   const int gemv_flags = gemv_flags_ | (mode_ == kModeFast ? kGemvFast : 0);
   const F16Planes planes = {ah_, ast_, gemm_kind_ >= 2 ? gemm_kind_ - 2 : -1};
   int *gemm_status = use_tensor_cores_ ? gemm_error_ : nullptr;
+  const bool use_side_streams = concurrent_gemms_ && S > 1 && !bf16_weights_;
+  if (use_side_streams)
+    make_side_streams();
   SideStreams side_streams = {side_streams_, fork_event_, join_events_, kSideStreams};
-  const SideStreams *side = concurrent_gemms_ && S > 1 ? &side_streams : nullptr;
+  const SideStreams *side = use_side_streams ? &side_streams : nullptr;
   int cur = 0;
   const uint16_t *pending = nullptr; // the MLP output still to be added to the residual stream
   int64_t lin_index = 0, full_index = 0;
@@ -980,6 +994,8 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     launch_argmax(batch_logits_, c.vocab, argmax_v_, argmax_i_, 0, batch_tokens_, nullptr, stream_, static_cast<int>(S));
     launches_ += 3;
     check(cudaGetLastError(), "forward");
+    if (use_side_streams)
+      drop_side_streams();
     return;
   }
   // Final norm and vocabulary projection of the last position only (ModelBuilder.cpp:489-512).
@@ -1011,6 +1027,8 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     launches_ += 6;
   }
   check(cudaGetLastError(), "forward");
+  if (use_side_streams)
+    drop_side_streams();
 }
 
 int64_t Engine::forward_host(const int64_t *tokens, int64_t S, int64_t position, const float *cos, const float *sin,

@@ -363,17 +363,18 @@ gdn_recurrence_pipelined_kernel(const uint16_t *__restrict__ conv, const float *
 }
 
 // Fast form of the recurrence for calls of more than one token: the same two-tokens-in-flight loop,
-// but a warp owns 4 value columns and each column's 128 state rows are shared by eight lanes (16
-// rows each), so the two dependent chains per token are 16 long instead of 128 and end in three
+// but a warp owns 8 value columns and each column's 128 state rows are shared by four lanes (32
+// rows each), so the two dependent chains per token are 32 long instead of 128 and end in two
 // shuffles; multiply and add are fused.  What bounds the exact kernel, and still bounds this one, is
-// how fast ONE warp can walk its dependent instructions (about one every two cycles), so the work of
-// a head is spread over 32 independent warps instead of 4.  A token then takes a few hundred cycles,
-// less than a trip to L2, so the inputs (k, q, decay, beta, the 4 values) arrive by cp.async in
-// chunks of 8 tokens, three chunks in shared memory per warp: the one in use, the next (token
-// t + 1's k is needed beside token t) and the one in flight.  The sums differ from the reference's
-// order (row groups are added as a tree) and from its roundings (fused multiply-adds): results
-// agree with the exact kernels to f32 rounding noise, not bit for bit.
-// grid (value head, dv / 16), 128 threads: four independent warps that share nothing.
+// how fast ONE warp can walk its dependent instructions, so a head is spread over 16 independent
+// warps instead of 4.  A token then takes a few hundred cycles, less than a trip to L2, so the
+// inputs (k, q, decay, beta, the 8 values) arrive by cp.async in chunks of 8 tokens, three chunks in
+// shared memory per warp: the one in use, the next (token t + 1's k is needed beside token t) and
+// the one in flight.  The sums differ from the reference's order (row groups are added as a tree)
+// and from its roundings (fused multiply-adds): results agree with the exact kernels to f32
+// rounding noise, not bit for bit.  Measured with 4 columns and eight lanes per column instead:
+// slower (twice the shared memory per column, so half the CTAs fit).
+// grid (value head, dv / 32), 128 threads: four independent warps that share nothing.
 constexpr int kSplitChunk = 8; // tokens per chunk
 constexpr int kSplitWarps = 4;
 constexpr int kSplitCols = 8;  // value columns per warp
