@@ -153,6 +153,9 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
   // here, so that a failed create leaves no device or pinned memory behind.
   try {
   check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+  // On for engines that hold a batch of sequences (their steps are GEMMs of a few tiles each), off
+  // for a single sequence (see engine.h); the switch overrides both.
+  concurrent_gemms_ = batch_ > 1;
   if (const char *flag = std::getenv("LLMCP_B200_CONCURRENT_GEMMS"))
     concurrent_gemms_ = std::atoi(flag) != 0;
 

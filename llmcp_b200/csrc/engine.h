@@ -181,9 +181,10 @@ private:
   cudaStream_t stream_ = nullptr;
   // Independent GEMMs of a prefill (the projections that share an input) can run side by side: a
   // fork event on stream_, one side stream and one join event per extra matrix
-  // (LLMCP_B200_CONCURRENT_GEMMS=1).  Off by default: it takes 3 ms off a 1024-token prefill, but in
-  // fast mode every decode step that follows in the same process then measured 75 us longer, also
-  // when the streams are destroyed right after the prefill; the cause was not found.
+  // (LLMCP_B200_CONCURRENT_GEMMS=0|1).  On for a batch of sequences; off for a single sequence: it
+  // takes 3 ms off a 1024-token prefill, but in fast mode every decode step that follows in the same
+  // process then measured 75 us longer, also when the streams are destroyed right after the
+  // prefill; the cause was not found.
   static constexpr int kSideStreams = 3;
   cudaStream_t side_streams_[kSideStreams] = {};
   cudaEvent_t fork_event_ = nullptr, join_events_[kSideStreams] = {};

@@ -393,7 +393,11 @@ cudaError_t launch_rms_norm_fast(const uint16_t *a, const uint16_t *b, int64_t M
     return cudaSuccess;
   if (H % 8 != 0 || H > 8192 || (q && H % kBlock != 0))
     return cudaErrorNotSupported;
-  if (H <= 4096) {
+  static const int wide = [] { // LLMCP_B200_NORM_EPT=8: eight elements per thread for every row length
+    const char *flag = std::getenv("LLMCP_B200_NORM_EPT");
+    return flag && std::atoi(flag) == 8 ? 1 : 0;
+  }();
+  if (H <= 4096 && !wide) {
     const int threads = (H / 4 + 31) / 32 * 32;
     launch_chained(rms_norm_fast_kernel<4>, dim3(static_cast<unsigned>(M)), dim3(threads), 0, stream, a, b, H, w, w_dtype, eps,
                    zero_centered, sum_out, y, q, s);
