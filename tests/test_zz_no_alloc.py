@@ -5,7 +5,8 @@ process that has given the whole GPU to its own memory pool, a decode loop that 
 an allocation's synchronisation).  Its working memory is one array inside the library shared by
 all calls, so the test makes two calls in a row with different inputs: the second must not be
 disturbed by what the first left in the array.  Outputs and the updated recurrent state have to
-be bit-identical to the allocating entry point's.  This file is collected last on purpose.
+be bit-identical to the allocating entry point's and to the CPU oracle's.  This file is collected
+last on purpose.
 """
 import ctypes as C
 
@@ -13,6 +14,7 @@ import numpy as np
 import pytest
 
 import llmcp_b200 as L
+import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -52,6 +54,11 @@ def test_noalloc_matches_allocating_entry_point_twice():
         assert rc == 0, L.last_error()
         assert np.array_equal(out, want_out)
         assert np.array_equal(state.view(np.uint32), want_state.view(np.uint32))
+        # and against the CPU oracle directly, not only through the allocating entry point
+        oracle_out, oracle_state = oracle.gated_delta_net(x["conv"], x["a"], x["b"], x["a_log"], x["dt_bias"], x["state"],
+                                                          nk, nv, dk, dv)
+        assert np.array_equal(out, oracle_out)
+        assert np.array_equal(state.view(np.uint32), oracle_state.view(np.uint32))
 
 
 def test_noalloc_rejects_oversized_calls():
