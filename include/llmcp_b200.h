@@ -57,6 +57,9 @@ int llmcp_b200_device_count(void);
 int llmcp_b200_set_device(int device);
 /* Releases every engine created by the AOT entries. */
 void llmcp_b200_release_all(void);
+/* Engines currently held by the AOT entry points: one per distinct (arena, kv, delta, conv) set of the
+ * caller, at most LLMCP_B200_MAX_SESSIONS (default 4; the least recently used one is released beyond that). */
+int llmcp_b200_session_count(void);
 /* Kernel launches issued by this library since it was loaded. */
 uint64_t llmcp_b200_launch_count(void);
 /* Arithmetic mode (no counterpart in the reference, which has one order of operations).

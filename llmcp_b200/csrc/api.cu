@@ -215,10 +215,22 @@ struct Session {
   uint64_t arena_bytes = 0;
   const void *kv = nullptr, *delta = nullptr, *conv = nullptr;
   int64_t capacity = 0;
+  uint64_t last_use = 0;
   std::unique_ptr<Engine> engine;
 };
 
+// Sessions are keyed by the caller's arena and state buffers, so a caller that reallocates its state
+// vectors (AotRuntime::init does, AotRuntime.cpp:41-43) makes a new one each time while the old one
+// still holds a copy of the weights.  The list is therefore bounded: beyond
+// LLMCP_B200_MAX_SESSIONS (default 4) the least recently used session is released.
 std::vector<std::unique_ptr<Session>> g_sessions;
+uint64_t g_session_clock = 0;
+
+size_t max_sessions() {
+  const char *flag = std::getenv("LLMCP_B200_MAX_SESSIONS");
+  const long v = flag ? std::atol(flag) : 4;
+  return static_cast<size_t>(v < 1 ? 1 : v);
+}
 
 bool contiguous(const int64_t *sizes, const int64_t *strides, int rank) {
   int64_t expect = 1;
@@ -262,6 +274,8 @@ void aot_entry(void *tokens_p, void *cos_p, void *sin_p, void *start_pos, void *
         if (s->arena == base && s->arena_bytes == static_cast<uint64_t>(arena->sizes[0]) &&
             s->kv == kv->data && s->delta == delta->data && s->conv == conv->data && s->capacity == kv->sizes[3])
           session = s.get();
+      if (session)
+        session->last_use = ++g_session_clock;
     }
     if (!session) {
       // Dimensions the generated code has baked in come from the descriptors and the
@@ -318,6 +332,14 @@ void aot_entry(void *tokens_p, void *cos_p, void *sin_p, void *start_pos, void *
       fresh->capacity = kv->sizes[3];
       fresh->engine = std::make_unique<Engine>(base, 0, d, kv->sizes[3], device);
       std::lock_guard<std::mutex> lock(g_mutex);
+      while (g_sessions.size() >= max_sessions()) { // the engine's destructor waits for its stream and frees its memory
+        size_t oldest = 0;
+        for (size_t i = 1; i < g_sessions.size(); ++i)
+          if (g_sessions[i]->last_use < g_sessions[oldest]->last_use)
+            oldest = i;
+        g_sessions.erase(g_sessions.begin() + static_cast<std::ptrdiff_t>(oldest));
+      }
+      fresh->last_use = ++g_session_clock;
       g_sessions.push_back(std::move(fresh));
       session = g_sessions.back().get();
     }
@@ -423,6 +445,11 @@ int llmcp_b200_set_device(int device) {
 void llmcp_b200_release_all(void) {
   std::lock_guard<std::mutex> lock(g_mutex);
   g_sessions.clear();
+}
+
+int llmcp_b200_session_count(void) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return static_cast<int>(g_sessions.size());
 }
 
 uint64_t llmcp_b200_launch_count(void) { return g_launches.load(); }

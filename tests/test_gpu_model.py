@@ -316,3 +316,32 @@ def test_llmcp_run_binary_against_oracle(tmp_path):
         assert [int(x) for x in run.stdout.strip().split("\n")[-1].removeprefix("tokens:").split()] == want[:2]
     run = subprocess.run(base, capture_output=True, text=True, timeout=900)
     assert run.returncode == 0 and run.stdout.strip() == f"aot logits: {d.vocab} next {want[0]}", run.stdout
+
+
+def test_aot_sessions_are_bounded(monkeypatch):
+    """A caller that reallocates its state buffers (as the reference's AotRuntime::init does) gets a new
+    engine each time; beyond LLMCP_B200_MAX_SESSIONS the least recently used one is released, and a
+    released session's caller simply gets a fresh engine on its next call (state starts at position 0)."""
+    monkeypatch.setenv("LLMCP_B200_MAX_SESSIONS", "2")
+    lib = L.lib()
+    lib.llmcp_b200_release_all()
+    d = L.default_dims().copy(**TINY)
+    data = L.synthetic_container(d, 9)
+    arena = L.Arena().from_buffer(data)
+    prompt = [1, 2, 3, 4]
+    runtimes, first = [], None
+    for _ in range(3):
+        runtime = L.AotRuntime(d)
+        assert runtime.init(max_sequence=16)
+        logits = runtime.forward(arena, prompt, 0, len(prompt))
+        assert logits is not None and not L.last_error()
+        first = logits if first is None else first
+        assert np.array_equal(logits.view(np.uint32), first.view(np.uint32))
+        runtimes.append(runtime)
+        assert lib.llmcp_b200_session_count() <= 2
+    assert lib.llmcp_b200_session_count() == 2
+    # the first runtime's session was released: a call at position 0 builds it again
+    again = runtimes[0].forward(arena, prompt, 0, len(prompt))
+    assert np.array_equal(again.view(np.uint32), first.view(np.uint32)) and lib.llmcp_b200_session_count() == 2
+    lib.llmcp_b200_release_all()
+    assert lib.llmcp_b200_session_count() == 0
