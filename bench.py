@@ -32,6 +32,11 @@ sequence per GPU, no exchange on the data path, sum over ranks) is reported besi
 
 `--impl reference` times the CPU oracle alone on the same workload and prints the same line; that
 arm loads no CUDA library.
+
+Other keys: `batch` (64 sequences decoded together, two prompt sets; `--batch 0` skips it),
+`prefill_tokens_per_second`, `parity`, `whole_step_roofline`.  `--only gemv|gemm|attn` run one kernel on
+a small case (what a profiler captures); `--only timeline` and `--only prefill-timeline` print the
+device timeline of a decode step and the time per kernel family of a 1024-token prefill.
 """
 import argparse
 import ctypes as C
