@@ -236,13 +236,22 @@ uint64_t llmcp_b200_synthetic_bytes(const llmcp_b200_dims *dims);
 int llmcp_b200_synthetic_fill(const llmcp_b200_dims *dims, uint64_t seed, uint8_t *file, uint64_t file_bytes);
 int llmcp_b200_pack_q8_0_p4(const float *values, int64_t rows, int64_t cols, uint8_t *dst);
 int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes);
-/* Token ids -> text, the output half of llmcp-run (tools/llmcp-run/llmcp-run.cpp:657-690).  Host only.
+/* Text <-> token ids, the two ends of llmcp-run (tools/llmcp-run/llmcp-run.cpp:626-690).  Host only.
  *   llmcp_b200_vocab_create   : from the text of a tokenizer.json (model.vocab + added_tokens, ByteLevel
  *                               decoder) or of a bare {"token": id} object; NULL + last_error on failure.
  *   llmcp_b200_vocab_decode   : the tokenizer's Decode(ids): GPT-2 byte alphabet back to bytes, then
  *                               lossy UTF-8 (ill-formed subsequences become U+FFFD); ids without a
  *                               token are skipped.  Text functions copy at most capacity - 1 bytes
  *                               and a terminating 0 into `out` and return the full length.
+ *   llmcp_b200_vocab_encode   : the tokenizer's Encode(text) of tools/llmcp-run/llmcp-run.cpp:641 (tokenizers-cpp
+ *                               over the Hugging Face byte-level BPE): added tokens are cut out whole, the
+ *                               rest is split by the Qwen pre-tokenisation pattern, each piece is mapped to
+ *                               the byte alphabet and merged by rank.  Writes at most `capacity` ids and
+ *                               returns the full count; -1 + last_error when the tokenizer.json asks for a
+ *                               pre-tokeniser, normaliser or added-token option this code does not restate
+ *                               (nothing is approximated).
+ *   llmcp_b200_pretokenize    : the split step of that encoder alone: byte offsets at which the pieces of
+ *                               `text` end (at most `capacity` written); returns the number of pieces.
  *   llmcp_b200_stream_*       : ByteLevelStreamingDecoder of tools/llmcp-run/StreamingDecoder.cpp:13-29:
  *                               append returns a complete chunk, or nothing while the decoded tail is
  *                               U+FFFD (bytes the next token may complete); finish emits the rest.
@@ -253,6 +262,8 @@ void llmcp_b200_vocab_destroy(void *vocab);
 int64_t llmcp_b200_vocab_size(const void *vocab);
 int32_t llmcp_b200_vocab_token_to_id(const void *vocab, const char *token);
 uint64_t llmcp_b200_vocab_decode(const void *vocab, const int32_t *ids, uint64_t count, char *out, uint64_t capacity);
+int64_t llmcp_b200_vocab_encode(const void *vocab, const char *text, uint64_t length, int32_t *ids, uint64_t capacity);
+int64_t llmcp_b200_pretokenize(const char *text, uint64_t length, int64_t *ends, uint64_t capacity);
 void *llmcp_b200_stream_create(const void *vocab);
 void llmcp_b200_stream_destroy(void *stream);
 uint64_t llmcp_b200_stream_append(void *stream, int32_t token, char *out, uint64_t capacity);

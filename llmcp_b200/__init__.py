@@ -78,6 +78,8 @@ def lib():
         handle.llmcp_b200_vocab_create.restype = C.c_void_p
         handle.llmcp_b200_vocab_size.restype = C.c_int64
         handle.llmcp_b200_vocab_token_to_id.restype = C.c_int32
+        handle.llmcp_b200_vocab_encode.restype = C.c_int64
+        handle.llmcp_b200_pretokenize.restype = C.c_int64
         handle.llmcp_b200_stream_create.restype = C.c_void_p
         for name in ("vocab_decode", "stream_append", "stream_finish", "chat_prompt"):
             getattr(handle, "llmcp_b200_" + name).restype = C.c_uint64
@@ -337,8 +339,8 @@ def _text_call(fn, *args):
 
 
 class Vocab:
-    """Token ids -> text of a ByteLevel tokenizer: what llmcp-run gets from ``tokenizers::Tokenizer``
-    (``Decode``, ``TokenToId``; tools/llmcp-run/llmcp-run.cpp:635-690).  ``json`` is the text of a
+    """Text <-> token ids of a ByteLevel tokenizer: what llmcp-run gets from ``tokenizers::Tokenizer``
+    (``Encode``, ``Decode``, ``TokenToId``; tools/llmcp-run/llmcp-run.cpp:635-690).  ``json`` is the text of a
     tokenizer.json or of a bare ``{"token": id}`` object."""
 
     def __init__(self, json):
@@ -357,10 +359,31 @@ class Vocab:
         arr = (C.c_int32 * len(ids))(*ids)
         return _text_call(lib().llmcp_b200_vocab_decode, C.c_void_p(self._handle), arr, C.c_uint64(len(ids))).decode()
 
+    def encode(self, text):
+        """``Encode(text)`` of the same tokenizer (llmcp-run.cpp:641): byte-level BPE after the Qwen
+        pre-tokenisation split; raises when the tokenizer.json describes anything else."""
+        raw = text.encode() if isinstance(text, str) else bytes(text)
+        capacity = len(raw) + 16  # a piece never yields more ids than it has bytes
+        ids = (C.c_int32 * capacity)()
+        n = int(lib().llmcp_b200_vocab_encode(C.c_void_p(self._handle), raw, C.c_uint64(len(raw)), ids, C.c_uint64(capacity)))
+        if n < 0:
+            raise LlmcpError(last_error())
+        return list(ids[:n])
+
     def close(self):
         if self._handle:
             lib().llmcp_b200_vocab_destroy(C.c_void_p(self._handle))
             self._handle = None
+
+
+def pretokenize(text):
+    """The pieces the Qwen pre-tokenisation pattern cuts ``text`` into (the Split step in front of
+    the byte-level BPE), as a list of strings."""
+    raw = text.encode()
+    ends = (C.c_int64 * (len(raw) + 1))()
+    n = int(lib().llmcp_b200_pretokenize(raw, C.c_uint64(len(raw)), ends, C.c_uint64(len(raw) + 1)))
+    cuts = [0] + list(ends[:n])
+    return [raw[a:b].decode() for a, b in zip(cuts, cuts[1:])]
 
 
 class StreamingDecoder:

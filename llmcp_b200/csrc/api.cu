@@ -949,6 +949,29 @@ uint64_t llmcp_b200_vocab_decode(const void *vocab, const int32_t *ids, uint64_t
   return copy_text(static_cast<const ByteLevelVocab *>(vocab)->decode(ids, count), out, capacity);
 }
 
+int64_t llmcp_b200_vocab_encode(const void *vocab, const char *text, uint64_t length, int32_t *ids, uint64_t capacity) {
+  std::vector<int32_t> out;
+  const std::string error = static_cast<const ByteLevelVocab *>(vocab)->encode(std::string(text ? text : "", text ? length : 0), &out);
+  if (!error.empty()) {
+    set_error(error);
+    return -1;
+  }
+  if (ids)
+    std::memcpy(ids, out.data(), std::min<uint64_t>(out.size(), capacity) * sizeof(int32_t));
+  return static_cast<int64_t>(out.size());
+}
+
+int64_t llmcp_b200_pretokenize(const char *text, uint64_t length, int64_t *ends, uint64_t capacity) {
+  const std::vector<std::string> pieces = pretokenize(std::string(text ? text : "", text ? length : 0));
+  int64_t end = 0;
+  for (size_t i = 0; i < pieces.size(); ++i) {
+    end += static_cast<int64_t>(pieces[i].size());
+    if (ends && i < capacity)
+      ends[i] = end;
+  }
+  return static_cast<int64_t>(pieces.size());
+}
+
 void *llmcp_b200_stream_create(const void *vocab) {
   return new ByteLevelStreamingDecoder(*static_cast<const ByteLevelVocab *>(vocab));
 }

@@ -1,6 +1,11 @@
 #include "text.h"
 
+#include <algorithm>
+#include <climits>
+#include <cstdio>
+
 #include "json.h"
+#include "unicode_tables.h"
 
 namespace llmcp_b200 {
 
@@ -63,6 +68,80 @@ int well_formed(const unsigned char *p, size_t left, int *valid_prefix) {
   }
   return length;
 }
+
+bool in_ranges(const detail::CodeRange *ranges, size_t count, uint32_t cp) {
+  size_t lo = 0, hi = count;
+  while (lo < hi) {
+    const size_t mid = (lo + hi) / 2;
+    if (cp > ranges[mid].last)
+      lo = mid + 1;
+    else if (cp < ranges[mid].first)
+      hi = mid;
+    else
+      return true;
+  }
+  return false;
+}
+bool is_letter(uint32_t cp) { return in_ranges(detail::kLetterRanges, sizeof(detail::kLetterRanges) / sizeof(detail::CodeRange), cp); }
+bool is_number(uint32_t cp) { return in_ranges(detail::kNumberRanges, sizeof(detail::kNumberRanges) / sizeof(detail::CodeRange), cp); }
+// \s of a Unicode-aware pattern: the White_Space property.
+bool is_space(uint32_t cp) {
+  return (cp >= 9 && cp <= 13) || cp == 0x20 || cp == 0x85 || cp == 0xa0 || cp == 0x1680 || (cp >= 0x2000 && cp <= 0x200a) ||
+         cp == 0x2028 || cp == 0x2029 || cp == 0x202f || cp == 0x205f || cp == 0x3000;
+}
+bool is_newline(uint32_t cp) { return cp == '\r' || cp == '\n'; }
+
+// Code points of a text with the byte offset of each (one more offset at the end); an ill-formed
+// byte stands for itself as a character outside every category.
+void decode_points(const std::string &text, std::vector<uint32_t> *points, std::vector<size_t> *offsets) {
+  const unsigned char *p = reinterpret_cast<const unsigned char *>(text.data());
+  size_t i = 0;
+  while (i < text.size()) {
+    int prefix = 1;
+    const int length = well_formed(p + i, text.size() - i, &prefix);
+    uint32_t cp;
+    if (length == 1)
+      cp = p[i];
+    else if (length == 2)
+      cp = (static_cast<uint32_t>(p[i] & 0x1f) << 6) | (p[i + 1] & 0x3f);
+    else if (length == 3)
+      cp = (static_cast<uint32_t>(p[i] & 0x0f) << 12) | (static_cast<uint32_t>(p[i + 1] & 0x3f) << 6) | (p[i + 2] & 0x3f);
+    else if (length == 4)
+      cp = (static_cast<uint32_t>(p[i] & 0x07) << 18) | (static_cast<uint32_t>(p[i + 1] & 0x3f) << 12) |
+           (static_cast<uint32_t>(p[i + 2] & 0x3f) << 6) | (p[i + 3] & 0x3f);
+    else
+      cp = 0xfffd;
+    points->push_back(cp);
+    offsets->push_back(i);
+    i += static_cast<size_t>(length > 0 ? length : 1);
+  }
+  offsets->push_back(text.size());
+}
+
+// Byte -> the UTF-8 text of its character in the GPT-2 byte alphabet.
+struct ByteText {
+  std::string text[256];
+  ByteText() {
+    int next = 256;
+    for (int byte = 0; byte < 256; ++byte) {
+      const bool direct = (byte >= 33 && byte <= 126) || (byte >= 161 && byte <= 172) || byte >= 174;
+      const int cp = direct ? byte : next++;
+      if (cp < 128) {
+        text[byte] = std::string(1, static_cast<char>(cp));
+      } else {
+        text[byte] += static_cast<char>(0xc0 | (cp >> 6));
+        text[byte] += static_cast<char>(0x80 | (cp & 0x3f));
+      }
+    }
+  }
+};
+const ByteText &byte_text() {
+  static const ByteText table;
+  return table;
+}
+
+const char *const kSupportedPattern =
+    "(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\r\\n\\p{L}\\p{N}]?\\p{L}+|\\p{N}| ?[^\\s\\p{L}\\p{N}]+[\\r\\n]*|\\s*[\\r\\n]+|\\s+(?!\\S)|\\s+";
 
 } // namespace
 
@@ -133,6 +212,66 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
   }
   if (tokens_.empty())
     return "tokenizer: empty vocabulary";
+  // text -> ids: merges by rank, added tokens, and the one pre-tokeniser this code restates
+  merge_rank_.clear();
+  added_.clear();
+  encoder_ready_ = nfc_ = added_options_ = ignore_merges_ = false;
+  encode_refusal_ = "the tokenizer has no merges";
+  const detail::Json *model = root.get("model");
+  const detail::Json *merges = model ? model->get("merges") : nullptr;
+  if (merges && merges->kind == detail::Json::Array) {
+    int32_t rank = 0;
+    for (const detail::Json &m : merges->items) {
+      if (m.kind == detail::Json::String)
+        merge_rank_.emplace(m.text, rank++);
+      else if (m.kind == detail::Json::Array && m.items.size() == 2 && m.items[0].kind == detail::Json::String &&
+               m.items[1].kind == detail::Json::String)
+        merge_rank_.emplace(m.items[0].text + " " + m.items[1].text, rank++);
+      else
+        return "tokenizer: malformed merges entry";
+    }
+    if (const detail::Json *flag = model->get("ignore_merges"))
+      ignore_merges_ = flag->kind == detail::Json::Bool && flag->boolean;
+    if (added && added->kind == detail::Json::Array)
+      for (const detail::Json &entry : added->items) {
+        added_.push_back(entry.get("content")->text);
+        for (const char *option : {"lstrip", "rstrip", "single_word"})
+          if (const detail::Json *flag = entry.get(option))
+            if (flag->kind == detail::Json::Bool && flag->boolean)
+              added_options_ = true;
+      }
+    std::sort(added_.begin(), added_.end(), [](const std::string &a, const std::string &b) { return a.size() > b.size(); });
+    // pre_tokenizer: Sequence[Split(the supported pattern, Isolated), ByteLevel(use_regex = false)]
+    encode_refusal_ = "its pre_tokenizer is not Split(<the Qwen pattern>, Isolated) followed by ByteLevel without its own pattern";
+    const detail::Json *pre = root.get("pre_tokenizer");
+    const detail::Json *list = pre ? pre->get("pretokenizers") : nullptr;
+    if (list && list->kind == detail::Json::Array && list->items.size() == 2) {
+      const detail::Json &split = list->items[0], &bytes = list->items[1];
+      const detail::Json *pattern = split.get("pattern");
+      const detail::Json *regex = pattern ? pattern->get("Regex") : nullptr;
+      const detail::Json *behavior = split.get("behavior"), *invert = split.get("invert");
+      const detail::Json *use_regex = bytes.get("use_regex"), *prefix = bytes.get("add_prefix_space");
+      const detail::Json *kind0 = split.get("type"), *kind1 = bytes.get("type");
+      encoder_ready_ = kind0 && kind0->text == "Split" && kind1 && kind1->text == "ByteLevel" && regex &&
+                       regex->text == kSupportedPattern && behavior && behavior->text == "Isolated" &&
+                       !(invert && invert->boolean) && use_regex && !use_regex->boolean && !(prefix && prefix->boolean);
+    }
+    if (encoder_ready_ && added_options_) {
+      encoder_ready_ = false;
+      encode_refusal_ = "an added token asks for lstrip, rstrip or single_word matching";
+    }
+    if (encoder_ready_)
+      if (const detail::Json *normalizer = root.get("normalizer"))
+        if (normalizer->kind == detail::Json::Object) {
+          const detail::Json *type = normalizer->get("type");
+          if (type && type->text == "NFC") {
+            nfc_ = true;
+          } else {
+            encoder_ready_ = false;
+            encode_refusal_ = "its normalizer is neither absent nor NFC";
+          }
+        }
+  }
   return "";
 }
 
@@ -189,6 +328,168 @@ std::string ByteLevelStreamingDecoder::finish() {
   std::string text = vocab_.decode(pending_.data(), pending_.size());
   pending_.clear();
   return text;
+}
+
+std::vector<std::string> pretokenize(const std::string &text) {
+  std::vector<uint32_t> cp;
+  std::vector<size_t> at;
+  decode_points(text, &cp, &at);
+  const size_t n = cp.size();
+  std::vector<std::string> pieces;
+  auto fold = [](uint32_t c) { return c == 0x17f ? uint32_t('s') : c == 0x212a ? uint32_t('k') : (c >= 'A' && c <= 'Z') ? c + 32 : c; };
+  auto punct = [](uint32_t c) { return !is_space(c) && !is_letter(c) && !is_number(c); };
+  size_t p = 0;
+  while (p < n) {
+    size_t end = 0;
+    // 1. contractions, case-insensitive, in the pattern's order
+    if (cp[p] == '\'' && p + 1 < n) {
+      const uint32_t a = fold(cp[p + 1]), b = p + 2 < n ? fold(cp[p + 2]) : 0;
+      if (a == 's' || a == 't')
+        end = p + 2;
+      else if ((a == 'r' && b == 'e') || (a == 'v' && b == 'e'))
+        end = p + 3;
+      else if (a == 'm')
+        end = p + 2;
+      else if (a == 'l' && b == 'l')
+        end = p + 3;
+      else if (a == 'd')
+        end = p + 2;
+    }
+    // 2. an optional character that is no letter, number, CR or LF, then letters
+    if (!end) {
+      size_t q = p;
+      if (!is_letter(cp[q]) && !is_number(cp[q]) && !is_newline(cp[q]) && q + 1 < n && is_letter(cp[q + 1]))
+        ++q;
+      if (is_letter(cp[q])) {
+        while (q < n && is_letter(cp[q]))
+          ++q;
+        end = q;
+      }
+    }
+    // 3. one number character
+    if (!end && is_number(cp[p]))
+      end = p + 1;
+    // 4. an optional space, characters that are no space, letter or number, then CRs and LFs
+    if (!end) {
+      size_t q = p;
+      if (cp[q] == ' ' && q + 1 < n && punct(cp[q + 1]))
+        ++q;
+      if (punct(cp[q])) {
+        while (q < n && punct(cp[q]))
+          ++q;
+        while (q < n && is_newline(cp[q]))
+          ++q;
+        end = q;
+      }
+    }
+    if (!end && is_space(cp[p])) {
+      size_t run = p;
+      while (run < n && is_space(cp[run]))
+        ++run;
+      // 5. white space up to and including its last CR or LF
+      size_t last_newline = n;
+      for (size_t i = p; i < run; ++i)
+        if (is_newline(cp[i]))
+          last_newline = i;
+      if (last_newline != n)
+        end = last_newline + 1;
+      else if (run == n)      // 6. white space not followed by anything else ...
+        end = run;
+      else if (run - p >= 2)  //    ... or all of it but the last character
+        end = run - 1;
+      else                    // 7. white space
+        end = run;
+    }
+    if (!end)
+      end = p + 1; // not reachable: every character is a letter, a number, white space or none of them
+    pieces.emplace_back(text, at[p], at[end] - at[p]);
+    p = end;
+  }
+  return pieces;
+}
+
+void ByteLevelVocab::encode_piece(const std::string &piece, std::vector<int32_t> *ids) const {
+  const ByteText &alphabet = byte_text();
+  std::vector<std::string> symbols;
+  std::string whole;
+  for (unsigned char byte : piece) {
+    symbols.push_back(alphabet.text[byte]);
+    whole += alphabet.text[byte];
+  }
+  if (ignore_merges_) {
+    const auto it = ids_.find(whole);
+    if (it != ids_.end()) {
+      ids->push_back(it->second);
+      return;
+    }
+  }
+  // the adjacent pair of lowest rank, leftmost among equals, until none is left
+  while (symbols.size() > 1) {
+    int32_t best_rank = INT32_MAX;
+    size_t best = 0;
+    for (size_t i = 0; i + 1 < symbols.size(); ++i) {
+      const auto it = merge_rank_.find(symbols[i] + " " + symbols[i + 1]);
+      if (it != merge_rank_.end() && it->second < best_rank) {
+        best_rank = it->second;
+        best = i;
+      }
+    }
+    if (best_rank == INT32_MAX)
+      break;
+    symbols[best] += symbols[best + 1];
+    symbols.erase(symbols.begin() + static_cast<std::ptrdiff_t>(best) + 1);
+  }
+  for (const std::string &symbol : symbols) {
+    const auto it = ids_.find(symbol);
+    if (it != ids_.end())
+      ids->push_back(it->second);
+  }
+}
+
+std::string ByteLevelVocab::encode(const std::string &text, std::vector<int32_t> *ids) const {
+  if (!encoder_ready_)
+    return "tokenizer: cannot encode text: " + encode_refusal_;
+  {
+    // Ill-formed UTF-8 has no encoding (the reference hands the text to a library that takes UTF-8
+    // only).  Under an NFC normaliser the text must be in NFC already: normalisation is not built,
+    // so a text that NFC could change is refused, not encoded as it stands.
+    std::vector<uint32_t> points;
+    std::vector<size_t> offsets;
+    decode_points(text, &points, &offsets);
+    for (size_t i = 0; i < points.size(); ++i) {
+      const size_t bytes = offsets[i + 1] - offsets[i];
+      if (points[i] == 0xfffd && bytes == 1)
+        return "tokenizer: cannot encode text: ill-formed UTF-8 at byte " + std::to_string(offsets[i]);
+      if (nfc_ && in_ranges(detail::kNfcUnsafeRanges, sizeof(detail::kNfcUnsafeRanges) / sizeof(detail::kNfcUnsafeRanges[0]), points[i])) {
+        char name[16];
+        std::snprintf(name, sizeof(name), "U+%04X", static_cast<unsigned>(points[i]));
+        return std::string("tokenizer: cannot encode text: ") + name + " at byte " + std::to_string(offsets[i]) +
+               " may change under the tokenizer's NFC normalisation, which is not built; pass text in NFC without combining marks";
+      }
+    }
+  }
+  size_t p = 0;
+  while (p < text.size()) {
+    // the leftmost added token; the longest of those that start there (added_ is sorted by length)
+    size_t where = std::string::npos;
+    const std::string *which = nullptr;
+    for (const std::string &token : added_) {
+      const size_t found = text.find(token, p);
+      if (found != std::string::npos && (found < where)) {
+        where = found;
+        which = &token;
+      }
+    }
+    const size_t stop = which ? where : text.size();
+    if (stop > p)
+      for (const std::string &piece : pretokenize(text.substr(p, stop - p)))
+        encode_piece(piece, ids);
+    if (!which)
+      break;
+    ids->push_back(ids_.at(*which));
+    p = where + which->size();
+  }
+  return "";
 }
 
 std::string make_chat_prompt(const std::string &user, const std::string &system, bool thinking) {

@@ -1,11 +1,17 @@
-// Token ids -> text for the interactive driver: the ByteLevel decoding that the reference gets from
+// Text <-> token ids for the interactive driver: the ByteLevel decoding that the reference gets from
 // its tokenizer dependency (tokenizers-cpp, a wrapper of the HuggingFace `tokenizers` crate, pinned
 // as the submodule third_party/tokenizers-cpp and absent from the reference tree), restated from
 // the published algorithm, the streaming decoder of tools/llmcp-run/StreamingDecoder.{h,cpp} and
 // the chat template of tools/llmcp-run/llmcp-run.cpp:608-624.  Host-only C++.
 //
-// What is not here: text -> ids (the BPE merges and the Unicode-class pre-tokeniser regex);
-// prompts reach the driver as ids.
+// Text -> ids (Tokenizer::Encode) is restated for the tokenizer the model ships with: added tokens cut
+// out first, then the pre-tokenisation pattern of its tokenizer.json (the Qwen / GPT-4 style pattern,
+// matched by a hand-written scanner over Unicode categories L, N and White_Space), the ByteLevel
+// alphabet, and byte-pair merges by rank.  Unicode normalisation is not built: where the tokenizer
+// normalises to NFC, a text that NFC could change (a combining mark, a decomposable character, an
+// unassigned code point) is refused with an error, so every id sequence returned is the tokenizer's.
+// A tokenizer.json with any other pre-tokeniser, normaliser or added-token matching option loads for
+// decoding and refuses to encode.
 #pragma once
 
 #include <cstdint>
@@ -33,11 +39,31 @@ public:
   // its own UTF-8 bytes), then the lossy conversion over all bytes together.
   std::string decode(const int32_t *ids, size_t count) const;
 
+  // Encode of the tokenizer (no special tokens are added around the text).  Needs a tokenizer.json
+  // with merges and the supported pre-tokeniser; returns an error text or "".
+  std::string encode(const std::string &text, std::vector<int32_t> *ids) const;
+  bool can_encode() const { return encoder_ready_; }
+  const std::string &encode_refusal() const { return encode_refusal_; }
+
 private:
+  void encode_piece(const std::string &piece, std::vector<int32_t> *ids) const;
+
   std::vector<std::string> tokens_; // id -> token text ("" + present_[id] == 0: no such id)
   std::vector<uint8_t> present_;
   std::unordered_map<std::string, int32_t> ids_;
+  std::unordered_map<std::string, int32_t> merge_rank_; // "left right" -> rank
+  std::vector<std::string> added_;                       // added tokens, longest first
+  bool ignore_merges_ = false;
+  bool encoder_ready_ = false;
+  bool nfc_ = false;           // the tokenizer normalises to NFC: encode() takes text that is in NFC already
+  bool added_options_ = false; // an added token with lstrip / rstrip / single_word: not restated, encode() refuses
+  std::string encode_refusal_ = "the tokenizer has no merges";
 };
+
+// The pieces the pre-tokenisation pattern
+//   (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+
+// cuts a text into (byte ranges, in order; ill-formed bytes count as one character each).
+std::vector<std::string> pretokenize(const std::string &text);
 
 // tools/llmcp-run/StreamingDecoder.cpp:13-29: text is held back while the decoded tail is U+FFFD
 // (the bytes of a character may be completed by the next token).

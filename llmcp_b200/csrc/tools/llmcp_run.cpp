@@ -3,15 +3,16 @@
 // through the ByteLevel streaming decoder, then the `tokens:` line; without new tokens the
 // `aot logits: N next T` line), on top of this repository's container reader.
 //
-//   llmcp-run --weights weights.bin --aot libllmcp_b200.so [--tokens ID | --token-ids a,b,c]
-//             [--tokenizer tokenizer.json] [--max-new-tokens N] [--eos-token ID] [--dump-logits]
-//             [--synthetic SEED]
+//   llmcp-run --weights weights.bin --aot libllmcp_b200.so --tokenizer tokenizer.json
+//             [--text 'Hello' [--chat] [--system S] [--no-thinking] | --tokens ID | --token-ids a,b,c]
+//             [--max-new-tokens N] [--eos-token ID] [--dump-logits] [--synthetic SEED]
+//   llmcp-run --tokenizer tokenizer.json --text 'Hello' --tokenize-only [--expect-token ID]
 //   llmcp-run --text 'Hello' [--chat] [--system S] [--no-thinking] --print-prompt
 //
-// Prompts are token ids: encoding text needs the tokenizer's BPE merges and pre-tokeniser, which
-// are not part of this build (the reference's `--tokenize-only` prints the ids of a text).
-// --print-prompt writes the text that would be encoded (with --chat: the Qwen chat template around
-// --text, llmcp-run.cpp:608-624) and exits.  The reference's interpreter half (no --aot) is not here.
+// --text is encoded with the tokenizer's own pre-tokenisation pattern and merges (text.h); with
+// --chat the Qwen chat template goes around it first (llmcp-run.cpp:608-624).  --tokenize-only
+// prints the ids, comma-separated, and exits (llmcp-run.cpp:646-653).  --print-prompt writes the text
+// that would be encoded and exits.  The reference's interpreter half (no --aot) is not here.
 
 #include <cstdlib>
 #include <cstring>
@@ -26,8 +27,8 @@ using namespace llmcp_b200::host;
 
 int main(int argc, char **argv) {
   std::string weights = "build/weights.bin", aot, tokenizer_path, text, system_prompt, ids_text;
-  int64_t token = 9419, max_new_tokens = 0, eos_override = -2;
-  bool chat = false, no_thinking = false, dump_logits = false, print_prompt = false, synthetic = false;
+  int64_t token = 9419, max_new_tokens = 0, eos_override = -2, expect_token = -1;
+  bool chat = false, no_thinking = false, dump_logits = false, print_prompt = false, synthetic = false, tokenize_only = false;
   uint64_t seed = 0;
   for (int i = 1; i < argc; ++i) {
     const std::string a = argv[i];
@@ -52,38 +53,15 @@ int main(int argc, char **argv) {
     else if (a == "--chat") chat = true;
     else if (a == "--no-thinking") no_thinking = true;
     else if (a == "--dump-logits") dump_logits = true;
+    else if (const char *v = value("--expect-token")) expect_token = std::atoll(v);
     else if (a == "--print-prompt") print_prompt = true;
+    else if (a == "--tokenize-only") tokenize_only = true;
     else { std::fprintf(stderr, "llmcp-run: unknown option %s\n", a.c_str()); return 1; }
   }
   if (print_prompt) {
     const std::string prompt = chat ? make_chat_prompt(text, system_prompt, !no_thinking) : text;
     std::fwrite(prompt.data(), 1, prompt.size(), stdout);
     return 0;
-  }
-  if (!text.empty()) {
-    std::fprintf(stderr, "llmcp-run: text prompts need the tokenizer's encoder, which this build does not have; "
-                         "pass --token-ids (see --print-prompt)\n");
-    return 1;
-  }
-  if (aot.empty()) {
-    std::fprintf(stderr, "llmcp-run: --aot is required (the interpreter half is not part of this build)\n");
-    return 1;
-  }
-  std::vector<int64_t> tokens;
-  if (!ids_text.empty()) {
-    std::stringstream stream(ids_text);
-    std::string item;
-    while (std::getline(stream, item, ',')) {
-      char *end = nullptr;
-      const long long id = std::strtoll(item.c_str(), &end, 10);
-      if (item.empty() || *end) {
-        std::fprintf(stderr, "llmcp-run: --token-ids wants comma-separated integers\n");
-        return 1;
-      }
-      tokens.push_back(id);
-    }
-  } else {
-    tokens.push_back(token);
   }
   if (max_new_tokens < 0) {
     std::fprintf(stderr, "llmcp-run: max-new-tokens must be >= 0\n");
@@ -111,6 +89,49 @@ int main(int argc, char **argv) {
   }
   if (eos_override != -2)
     eos = eos_override;
+
+  std::vector<int64_t> tokens;
+  if (!text.empty()) {
+    if (!have_vocab) {
+      std::fprintf(stderr, "llmcp-run: --text needs --tokenizer\n");
+      return 1;
+    }
+    std::vector<int32_t> ids;
+    const std::string prompt = chat ? make_chat_prompt(text, system_prompt, !no_thinking) : text;
+    if (const std::string error = vocab.encode(prompt, &ids); !error.empty()) {
+      std::fprintf(stderr, "llmcp-run: %s\n", error.c_str());
+      return 1;
+    }
+    tokens.assign(ids.begin(), ids.end());
+  } else if (!ids_text.empty()) {
+    std::stringstream stream(ids_text);
+    std::string item;
+    while (std::getline(stream, item, ',')) {
+      char *end = nullptr;
+      const long long id = std::strtoll(item.c_str(), &end, 10);
+      if (item.empty() || *end) {
+        std::fprintf(stderr, "llmcp-run: --token-ids wants comma-separated integers\n");
+        return 1;
+      }
+      tokens.push_back(id);
+    }
+  } else {
+    tokens.push_back(token);
+  }
+  if (tokenize_only) {
+    for (size_t i = 0; i < tokens.size(); ++i)
+      std::printf("%s%lld", i ? "," : "", static_cast<long long>(tokens[i]));
+    std::printf("\n");
+    return expect_token >= 0 && (tokens.empty() || tokens[0] != expect_token) ? 1 : 0;
+  }
+  if (tokens.empty()) {
+    std::fprintf(stderr, "llmcp-run: the prompt has no tokens\n");
+    return 1;
+  }
+  if (aot.empty()) {
+    std::fprintf(stderr, "llmcp-run: --aot is required (the interpreter half is not part of this build)\n");
+    return 1;
+  }
 
   Runtime runtime;
   if (synthetic && access(weights.c_str(), R_OK) != 0) {

@@ -1,9 +1,13 @@
-"""Token ids -> text of the llmcp-run driver: ByteLevel decoding, the streaming decoder and the chat
-template.  The cases are those of the reference's tests/unittests/StreamingDecoderTest.cpp (same
+"""Text <-> token ids of the llmcp-run driver: ByteLevel decoding, the streaming decoder, the chat
+template, and the byte-level BPE encoder behind --text.  The cases are those of the reference's tests/unittests/StreamingDecoderTest.cpp (same
 vocabulary construction, same id sequences and expectations); the HuggingFace `tokenizers` package,
 which the reference's tokenizer dependency wraps, is the independent check where it is installed.
+The encoder is held to that package's own answers: a committed fixture (tests/golden/bpe_encoder.json,
+written by tests/golden/make_bpe_golden.py) and, where the package is installed, live comparisons.
 Host-only: no GPU."""
 import json
+import pathlib
+import random
 import subprocess
 
 import numpy as np
@@ -150,6 +154,150 @@ def test_llmcp_run_prompt_only_paths():
     run = subprocess.run([str(tool), "--text", "Hello", "--chat", "--no-thinking", "--print-prompt"], capture_output=True, text=True)
     assert run.returncode == 0 and run.stdout == L.chat_prompt("Hello", thinking=False)
     run = subprocess.run([str(tool), "--text", "Hello", "--aot", "x.so"], capture_output=True, text=True)
-    assert run.returncode == 1 and "--token-ids" in run.stderr
+    assert run.returncode == 1 and "--tokenizer" in run.stderr
     run = subprocess.run([str(tool), "--tokens", "5"], capture_output=True, text=True)
     assert run.returncode == 1 and "--aot" in run.stderr
+
+
+# ---- text -> ids ---------------------------------------------------------------------------------
+GOLDEN = pathlib.Path(__file__).parent / "golden" / "bpe_encoder.json"
+QWEN_PATTERN = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*"
+                r"|\s*[\r\n]+|\s+(?!\S)|\s+")
+
+
+@pytest.fixture(scope="module")
+def golden():
+    return json.loads(GOLDEN.read_text())
+
+
+def test_pretokenize_against_the_committed_pieces(golden):
+    for case in golden["cases"]:
+        assert L.pretokenize(case["text"]) == case["pieces"], case["text"]
+    assert L.pretokenize("") == []
+
+
+def test_encode_against_the_committed_ids(golden):
+    v = L.Vocab(golden["tokenizer"])
+    for case in golden["cases"]:
+        ids = v.encode(case["text"])
+        assert ids == case["ids"], case["text"]
+        if "\u0301" not in case["text"]:  # decode(encode(text)) is the text (the byte alphabet loses nothing)
+            assert v.decode(ids) == case["text"]
+    assert v.encode("") == []
+    # the chat template's markers come out as single ids, the text between them as pieces
+    prompt = L.chat_prompt("What's 2+2?", thinking=False)
+    ids = v.encode(prompt)
+    assert ids[0] == v.token_to_id("<|im_start|>") and ids.count(v.token_to_id("<|im_end|>")) == 1
+    assert v.token_to_id("<think>") in ids and v.decode(ids) == prompt
+    v.close()
+
+
+def test_pretokenize_every_code_point_against_the_package():
+    """Each code point, in the positions where its class matters (inside a word, after a space, after
+    an apostrophe, doubled), against the regular-expression engine of the `tokenizers` package."""
+    tokenizers = pytest.importorskip("tokenizers")
+    split = tokenizers.pre_tokenizers.Split(tokenizers.Regex(QWEN_PATTERN), behavior="isolated", invert=False)
+    points = [cp for cp in range(0x110000) if not 0xD800 <= cp <= 0xDFFF]
+    for start in range(0, len(points), 4096):
+        text = "".join("x" + chr(cp) + "y" + chr(cp) + chr(cp) + " " + chr(cp) + "'" + chr(cp) + "\n" for cp in points[start:start + 4096])
+        assert L.pretokenize(text) == [p for p, _ in split.pre_tokenize_str(text)], hex(points[start])
+
+
+def test_encode_random_texts_against_the_package(golden):
+    tokenizers = pytest.importorskip("tokenizers")
+    tok = tokenizers.Tokenizer.from_str(golden["tokenizer"])
+    v = L.Vocab(golden["tokenizer"])
+    rng = random.Random(11)
+    alphabet = list("abcXYZ'sStTrReEvVmMlLdD  \t\n\r.,!?-_()123") + ["\r\n", "\u017f", "\u212a", "é", "你", "好", "😀", "\u00a0", "\u3000", "\u200b",
+                                                                  "\x85", "\x1c", "<|im_start|>", "<think>", "<|im_end|>", "<", "|", ">"]
+    for _ in range(3000):
+        text = "".join(rng.choice(alphabet) for _ in range(rng.randint(1, 40)))
+        assert v.encode(text) == tok.encode(text, add_special_tokens=False).ids, repr(text)
+    v.close()
+
+
+def test_ignore_merges_and_string_merges(golden):
+    """`ignore_merges` (a piece that is a token is taken whole) and merges written as "left right"
+    strings (tokenizer.json files written before the pair form)."""
+    tokenizers = pytest.importorskip("tokenizers")
+    blob = json.loads(golden["tokenizer"])
+    blob["model"]["merges"] = [m if isinstance(m, str) else " ".join(m) for m in blob["model"]["merges"]]
+    blob["model"]["ignore_merges"] = True
+    a = byte_alphabet()
+    whole = a[ord(" ")] + "zzqq"  # a token no merge sequence reaches
+    blob["model"]["vocab"][whole] = max(blob["model"]["vocab"].values()) + 10
+    text = json.dumps(blob)
+    tok, v = tokenizers.Tokenizer.from_str(text), L.Vocab(text)
+    for sample in [" zzqq", "a zzqq zzqq!", "zzqq", "Hello world, it's a fine day."]:
+        assert v.encode(sample) == tok.encode(sample, add_special_tokens=False).ids
+    assert v.encode(" zzqq") == [blob["model"]["vocab"][whole]]
+    v.close()
+
+
+def test_encoder_refuses_what_it_does_not_restate(golden):
+    blob = json.loads(golden["tokenizer"])
+    # another pattern: decoding still works, encoding says why not
+    other = json.loads(golden["tokenizer"])
+    other["pre_tokenizer"]["pretokenizers"][0]["pattern"]["Regex"] = r"\w+|\s+"
+    v = L.Vocab(json.dumps(other))
+    assert v.decode([v.token_to_id("<|im_end|>")]) == "<|im_end|>"
+    with pytest.raises(L.LlmcpError, match="pre_tokenizer"):
+        v.encode("hello")
+    v.close()
+    # a bare vocabulary has no merges
+    v = L.Vocab(json.dumps(make_vocab()))
+    with pytest.raises(L.LlmcpError, match="merges"):
+        v.encode("hello")
+    v.close()
+    # an added token with whitespace stripping
+    other = json.loads(golden["tokenizer"])
+    other["added_tokens"][0]["lstrip"] = True
+    v = L.Vocab(json.dumps(other))
+    with pytest.raises(L.LlmcpError, match="lstrip"):
+        v.encode("hello")
+    v.close()
+    # a normaliser other than NFC
+    other = json.loads(golden["tokenizer"])
+    other["normalizer"] = {"type": "Lowercase"}
+    v = L.Vocab(json.dumps(other))
+    with pytest.raises(L.LlmcpError, match="normalizer"):
+        v.encode("hello")
+    v.close()
+    # ill-formed UTF-8
+    v = L.Vocab(json.dumps(blob))
+    with pytest.raises(L.LlmcpError, match="ill-formed"):
+        v.encode(b"ab\xffcd")
+    v.close()
+
+
+def test_nfc_tokenizer_takes_only_text_that_is_in_nfc(golden):
+    """Under an NFC normaliser (the shipped Qwen tokenizer.json has one) text that NFC leaves alone is
+    encoded as the package encodes it; text NFC could change is refused, never encoded unnormalised."""
+    tokenizers = pytest.importorskip("tokenizers")
+    blob = json.loads(golden["tokenizer"])
+    blob["normalizer"] = {"type": "NFC"}
+    text = json.dumps(blob)
+    tok, v = tokenizers.Tokenizer.from_str(text), L.Vocab(text)
+    for sample in ["Hello, world!", "café Größe 你好 😀 한국어", "x = 1;\n\n  y = 2\t// ok"]:
+        assert v.encode(sample) == tok.encode(sample, add_special_tokens=False).ids
+    for sample in ["cafe\u0301", "\u212b", "\u1112\u1161", "\U000e0fff"]:  # combining mark, singleton, jamo, unassigned
+        with pytest.raises(L.LlmcpError, match="NFC"):
+            v.encode(sample)
+    v.close()
+
+
+def test_llmcp_run_tokenize_only(tmp_path, golden):
+    """llmcp-run.cpp:646-653: --tokenize-only prints the ids of --text and --expect-token checks the first."""
+    tool = L._PACKAGE / "bin" / "llmcp-run"
+    path = tmp_path / "tokenizer.json"
+    path.write_text(golden["tokenizer"])
+    v = L.Vocab(golden["tokenizer"])
+    want = v.encode(L.chat_prompt("Hello world", system="Be brief", thinking=False))
+    base = [str(tool), "--tokenizer", str(path), "--text", "Hello world", "--chat", "--system", "Be brief", "--no-thinking", "--tokenize-only"]
+    run = subprocess.run(base, capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.strip() == ",".join(map(str, want)), run.stderr
+    assert subprocess.run(base + ["--expect-token", str(want[0])], capture_output=True).returncode == 0
+    assert subprocess.run(base + ["--expect-token", str(want[0] + 1)], capture_output=True).returncode == 1
+    run = subprocess.run([str(tool), "--tokenize-only", "--tokens", "77"], capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.strip() == "77"
+    v.close()
