@@ -248,10 +248,12 @@ int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes);
  *                               rest is split by the Qwen pre-tokenisation pattern, each piece is mapped to
  *                               the byte alphabet and merged by rank.  Writes at most `capacity` ids and
  *                               returns the full count; -1 + last_error when the tokenizer.json asks for a
- *                               pre-tokeniser, normaliser or added-token option this code does not restate
- *                               (nothing is approximated).
+ *                               pre-tokeniser, normaliser (other than NFC) or added-token option this code
+ *                               does not restate, or the text is ill-formed UTF-8 (nothing is approximated).
  *   llmcp_b200_pretokenize    : the split step of that encoder alone: byte offsets at which the pieces of
  *                               `text` end (at most `capacity` written); returns the number of pieces.
+ *   llmcp_b200_normalize_nfc  : Unicode Normalization Form C of a UTF-8 text, the normaliser the encoder
+ *                               applies when the tokenizer.json names it.
  *   llmcp_b200_stream_*       : ByteLevelStreamingDecoder of tools/llmcp-run/StreamingDecoder.cpp:13-29:
  *                               append returns a complete chunk, or nothing while the decoded tail is
  *                               U+FFFD (bytes the next token may complete); finish emits the rest.
@@ -264,6 +266,7 @@ int32_t llmcp_b200_vocab_token_to_id(const void *vocab, const char *token);
 uint64_t llmcp_b200_vocab_decode(const void *vocab, const int32_t *ids, uint64_t count, char *out, uint64_t capacity);
 int64_t llmcp_b200_vocab_encode(const void *vocab, const char *text, uint64_t length, int32_t *ids, uint64_t capacity);
 int64_t llmcp_b200_pretokenize(const char *text, uint64_t length, int64_t *ends, uint64_t capacity);
+uint64_t llmcp_b200_normalize_nfc(const char *text, uint64_t length, char *out, uint64_t capacity);
 void *llmcp_b200_stream_create(const void *vocab);
 void llmcp_b200_stream_destroy(void *stream);
 uint64_t llmcp_b200_stream_append(void *stream, int32_t token, char *out, uint64_t capacity);

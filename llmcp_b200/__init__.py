@@ -81,7 +81,7 @@ def lib():
         handle.llmcp_b200_vocab_encode.restype = C.c_int64
         handle.llmcp_b200_pretokenize.restype = C.c_int64
         handle.llmcp_b200_stream_create.restype = C.c_void_p
-        for name in ("vocab_decode", "stream_append", "stream_finish", "chat_prompt"):
+        for name in ("vocab_decode", "stream_append", "stream_finish", "chat_prompt", "normalize_nfc"):
             getattr(handle, "llmcp_b200_" + name).restype = C.c_uint64
         handle._mlir_ciface_llmcp_model_prefill.restype = None
         handle._mlir_ciface_llmcp_model_decode.restype = None
@@ -384,6 +384,14 @@ def pretokenize(text):
     n = int(lib().llmcp_b200_pretokenize(raw, C.c_uint64(len(raw)), ends, C.c_uint64(len(raw) + 1)))
     cuts = [0] + list(ends[:n])
     return [raw[a:b].decode() for a, b in zip(cuts, cuts[1:])]
+
+
+def normalize_nfc(text):
+    """Unicode Normalization Form C, as the encoder applies it under an NFC tokenizer."""
+    raw = text.encode()
+    out = C.create_string_buffer(3 * len(raw) + 16)  # NFC never grows a UTF-8 text threefold
+    n = int(lib().llmcp_b200_normalize_nfc(raw, C.c_uint64(len(raw)), out, C.c_uint64(len(out))))
+    return out.raw[:n].decode()
 
 
 class StreamingDecoder:

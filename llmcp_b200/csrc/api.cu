@@ -972,6 +972,10 @@ int64_t llmcp_b200_pretokenize(const char *text, uint64_t length, int64_t *ends,
   return static_cast<int64_t>(pieces.size());
 }
 
+uint64_t llmcp_b200_normalize_nfc(const char *text, uint64_t length, char *out, uint64_t capacity) {
+  return copy_text(normalize_nfc(std::string(text ? text : "", text ? length : 0)), out, capacity);
+}
+
 void *llmcp_b200_stream_create(const void *vocab) {
   return new ByteLevelStreamingDecoder(*static_cast<const ByteLevelVocab *>(vocab));
 }

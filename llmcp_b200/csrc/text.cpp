@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <climits>
+#include <cstddef>
 #include <cstdio>
 
 #include "json.h"
@@ -118,6 +119,85 @@ void decode_points(const std::string &text, std::vector<uint32_t> *points, std::
   offsets->push_back(text.size());
 }
 
+void append_utf8(uint32_t cp, std::string *out) {
+  if (cp < 0x80) {
+    *out += static_cast<char>(cp);
+  } else if (cp < 0x800) {
+    *out += static_cast<char>(0xc0 | (cp >> 6));
+    *out += static_cast<char>(0x80 | (cp & 0x3f));
+  } else if (cp < 0x10000) {
+    *out += static_cast<char>(0xe0 | (cp >> 12));
+    *out += static_cast<char>(0x80 | ((cp >> 6) & 0x3f));
+    *out += static_cast<char>(0x80 | (cp & 0x3f));
+  } else {
+    *out += static_cast<char>(0xf0 | (cp >> 18));
+    *out += static_cast<char>(0x80 | ((cp >> 12) & 0x3f));
+    *out += static_cast<char>(0x80 | ((cp >> 6) & 0x3f));
+    *out += static_cast<char>(0x80 | (cp & 0x3f));
+  }
+}
+
+// ---- Unicode Normalization Form C (UAX #15), on the tables of unicode_tables.h ------------------
+constexpr uint32_t kHangulS = 0xac00, kHangulL = 0x1100, kHangulV = 0x1161, kHangulT = 0x11a7;
+constexpr uint32_t kHangulLCount = 19, kHangulVCount = 21, kHangulTCount = 28;
+constexpr uint32_t kHangulNCount = kHangulVCount * kHangulTCount, kHangulSCount = kHangulLCount * kHangulNCount;
+
+uint32_t combining_class(uint32_t cp) {
+  constexpr size_t count = sizeof(detail::kCombiningClasses) / sizeof(detail::kCombiningClasses[0]);
+  const detail::CombiningClass *end = detail::kCombiningClasses + count;
+  const detail::CombiningClass *it =
+      std::upper_bound(detail::kCombiningClasses, end, cp, [](uint32_t v, const detail::CombiningClass &r) { return v < r.first; });
+  if (it == detail::kCombiningClasses)
+    return 0;
+  --it;
+  return cp <= it->last ? it->value : 0;
+}
+
+const detail::Decomposition *find_decomposition(uint32_t cp) {
+  constexpr size_t count = sizeof(detail::kDecompositions) / sizeof(detail::kDecompositions[0]);
+  const detail::Decomposition *end = detail::kDecompositions + count;
+  const detail::Decomposition *it =
+      std::lower_bound(detail::kDecompositions, end, cp, [](const detail::Decomposition &r, uint32_t v) { return r.point < v; });
+  return it != end && it->point == cp ? it : nullptr;
+}
+
+// Full canonical decomposition of one code point, appended to out.
+void decompose(uint32_t cp, std::vector<uint32_t> *out) {
+  if (cp >= kHangulS && cp < kHangulS + kHangulSCount) {
+    const uint32_t s = cp - kHangulS;
+    out->push_back(kHangulL + s / kHangulNCount);
+    out->push_back(kHangulV + (s % kHangulNCount) / kHangulTCount);
+    if (s % kHangulTCount)
+      out->push_back(kHangulT + s % kHangulTCount);
+    return;
+  }
+  const detail::Decomposition *d = cp < 0xc0 ? nullptr : find_decomposition(cp);
+  if (!d) {
+    out->push_back(cp);
+    return;
+  }
+  decompose(d->first, out);
+  if (d->second)
+    decompose(d->second, out);
+}
+
+// The primary composite of a pair, or 0.
+uint32_t compose(uint32_t a, uint32_t b) {
+  if (a >= kHangulL && a < kHangulL + kHangulLCount && b >= kHangulV && b < kHangulV + kHangulVCount)
+    return kHangulS + ((a - kHangulL) * kHangulVCount + (b - kHangulV)) * kHangulTCount;
+  if (a >= kHangulS && a < kHangulS + kHangulSCount && (a - kHangulS) % kHangulTCount == 0 && b > kHangulT && b < kHangulT + kHangulTCount)
+    return a + (b - kHangulT);
+  static const std::unordered_map<uint64_t, uint32_t> pairs = [] {
+    std::unordered_map<uint64_t, uint32_t> map;
+    for (const detail::Decomposition &d : detail::kDecompositions)
+      if (d.composes)
+        map.emplace((static_cast<uint64_t>(d.first) << 32) | d.second, d.point);
+    return map;
+  }();
+  const auto it = pairs.find((static_cast<uint64_t>(a) << 32) | b);
+  return it == pairs.end() ? 0 : it->second;
+}
+
 // Byte -> the UTF-8 text of its character in the GPT-2 byte alphabet.
 struct ByteText {
   std::string text[256];
@@ -215,7 +295,7 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
   // text -> ids: merges by rank, added tokens, and the one pre-tokeniser this code restates
   merge_rank_.clear();
   added_.clear();
-  encoder_ready_ = nfc_ = added_options_ = ignore_merges_ = false;
+  encoder_ready_ = nfc_ = added_options_ = added_normalized_ = ignore_merges_ = false;
   encode_refusal_ = "the tokenizer has no merges";
   const detail::Json *model = root.get("model");
   const detail::Json *merges = model ? model->get("merges") : nullptr;
@@ -235,6 +315,9 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
     if (added && added->kind == detail::Json::Array)
       for (const detail::Json &entry : added->items) {
         added_.push_back(entry.get("content")->text);
+        if (const detail::Json *flag = entry.get("normalized"))
+          if (flag->kind == detail::Json::Bool && flag->boolean)
+            added_normalized_ = true;
         for (const char *option : {"lstrip", "rstrip", "single_word"})
           if (const detail::Json *flag = entry.get(option))
             if (flag->kind == detail::Json::Bool && flag->boolean)
@@ -264,8 +347,11 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
       if (const detail::Json *normalizer = root.get("normalizer"))
         if (normalizer->kind == detail::Json::Object) {
           const detail::Json *type = normalizer->get("type");
-          if (type && type->text == "NFC") {
+          if (type && type->text == "NFC" && !added_normalized_) {
             nfc_ = true;
+          } else if (type && type->text == "NFC") {
+            encoder_ready_ = false;
+            encode_refusal_ = "an added token is matched in normalised text (normalized = true) under the NFC normaliser";
           } else {
             encoder_ready_ = false;
             encode_refusal_ = "its normalizer is neither absent nor NFC";
@@ -328,6 +414,53 @@ std::string ByteLevelStreamingDecoder::finish() {
   std::string text = vocab_.decode(pending_.data(), pending_.size());
   pending_.clear();
   return text;
+}
+
+std::string normalize_nfc(const std::string &text) {
+  bool ascii = true;
+  for (unsigned char c : text)
+    ascii = ascii && c < 0x80;
+  if (ascii)
+    return text;
+  std::vector<uint32_t> points, parts;
+  std::vector<size_t> offsets;
+  decode_points(text, &points, &offsets);
+  for (uint32_t cp : points)
+    decompose(cp, &parts);
+  // canonical ordering: marks of a run between starters, by class, order among equals kept
+  std::vector<uint32_t> classes(parts.size());
+  for (size_t i = 0; i < parts.size(); ++i)
+    classes[i] = combining_class(parts[i]);
+  for (size_t i = 1; i < parts.size(); ++i)
+    for (size_t j = i; j > 0 && classes[j] != 0 && classes[j - 1] > classes[j]; --j) {
+      std::swap(parts[j], parts[j - 1]);
+      std::swap(classes[j], classes[j - 1]);
+    }
+  // canonical composition: a character joins the last starter unless something between them has
+  // its class or a higher one (or is a starter itself)
+  std::vector<uint32_t> out;
+  size_t starter = SIZE_MAX;
+  int64_t between = -1; // class of the last character kept after the starter; -1: none
+  for (size_t i = 0; i < parts.size(); ++i) {
+    const int64_t cc = classes[i];
+    if (starter != SIZE_MAX && (between < 0 || between < cc)) {
+      if (const uint32_t joined = compose(out[starter], parts[i])) {
+        out[starter] = joined;
+        continue;
+      }
+    }
+    if (cc == 0) {
+      starter = out.size();
+      between = -1;
+    } else {
+      between = cc;
+    }
+    out.push_back(parts[i]);
+  }
+  std::string result;
+  for (uint32_t cp : out)
+    append_utf8(cp, &result);
+  return result;
 }
 
 std::vector<std::string> pretokenize(const std::string &text) {
@@ -450,23 +583,13 @@ std::string ByteLevelVocab::encode(const std::string &text, std::vector<int32_t>
   if (!encoder_ready_)
     return "tokenizer: cannot encode text: " + encode_refusal_;
   {
-    // Ill-formed UTF-8 has no encoding (the reference hands the text to a library that takes UTF-8
-    // only).  Under an NFC normaliser the text must be in NFC already: normalisation is not built,
-    // so a text that NFC could change is refused, not encoded as it stands.
+    // Ill-formed UTF-8 has no encoding (the reference hands the text to a library that takes UTF-8 only).
     std::vector<uint32_t> points;
     std::vector<size_t> offsets;
     decode_points(text, &points, &offsets);
-    for (size_t i = 0; i < points.size(); ++i) {
-      const size_t bytes = offsets[i + 1] - offsets[i];
-      if (points[i] == 0xfffd && bytes == 1)
+    for (size_t i = 0; i < points.size(); ++i)
+      if (points[i] == 0xfffd && offsets[i + 1] - offsets[i] == 1)
         return "tokenizer: cannot encode text: ill-formed UTF-8 at byte " + std::to_string(offsets[i]);
-      if (nfc_ && in_ranges(detail::kNfcUnsafeRanges, sizeof(detail::kNfcUnsafeRanges) / sizeof(detail::kNfcUnsafeRanges[0]), points[i])) {
-        char name[16];
-        std::snprintf(name, sizeof(name), "U+%04X", static_cast<unsigned>(points[i]));
-        return std::string("tokenizer: cannot encode text: ") + name + " at byte " + std::to_string(offsets[i]) +
-               " may change under the tokenizer's NFC normalisation, which is not built; pass text in NFC without combining marks";
-      }
-    }
   }
   size_t p = 0;
   while (p < text.size()) {
@@ -481,9 +604,11 @@ std::string ByteLevelVocab::encode(const std::string &text, std::vector<int32_t>
       }
     }
     const size_t stop = which ? where : text.size();
-    if (stop > p)
-      for (const std::string &piece : pretokenize(text.substr(p, stop - p)))
+    if (stop > p) {
+      const std::string segment = text.substr(p, stop - p);
+      for (const std::string &piece : pretokenize(nfc_ ? normalize_nfc(segment) : segment))
         encode_piece(piece, ids);
+    }
     if (!which)
       break;
     ids->push_back(ids_.at(*which));

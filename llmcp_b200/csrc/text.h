@@ -7,9 +7,9 @@
 // Text -> ids (Tokenizer::Encode) is restated for the tokenizer the model ships with: added tokens cut
 // out first, then the pre-tokenisation pattern of its tokenizer.json (the Qwen / GPT-4 style pattern,
 // matched by a hand-written scanner over Unicode categories L, N and White_Space), the ByteLevel
-// alphabet, and byte-pair merges by rank.  Unicode normalisation is not built: where the tokenizer
-// normalises to NFC, a text that NFC could change (a combining mark, a decomposable character, an
-// unassigned code point) is refused with an error, so every id sequence returned is the tokenizer's.
+// alphabet, and byte-pair merges by rank.  Where the tokenizer normalises to NFC, the text between
+// added tokens is normalised first (UAX #15 on generated tables that hold what that library's own
+// normaliser knows: its Unicode data is older than its regular-expression engine's).
 // A tokenizer.json with any other pre-tokeniser, normaliser or added-token matching option loads for
 // decoding and refuses to encode.
 #pragma once
@@ -55,10 +55,16 @@ private:
   std::vector<std::string> added_;                       // added tokens, longest first
   bool ignore_merges_ = false;
   bool encoder_ready_ = false;
-  bool nfc_ = false;           // the tokenizer normalises to NFC: encode() takes text that is in NFC already
+  bool nfc_ = false;           // the tokenizer normalises to NFC: encode() normalises what lies between added tokens
+  bool added_normalized_ = false; // an added token with normalized = true (matched after normalisation)
   bool added_options_ = false; // an added token with lstrip / rstrip / single_word: not restated, encode() refuses
   std::string encode_refusal_ = "the tokenizer has no merges";
 };
+
+// Unicode Normalization Form C of a UTF-8 text (canonical decomposition, canonical ordering,
+// canonical composition; Hangul by arithmetic), with the tokenizer library's view of which code
+// points combine or decompose.
+std::string normalize_nfc(const std::string &text);
 
 // The pieces the pre-tokenisation pattern
 //   (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+

@@ -51,30 +51,67 @@ def ranges(prefix):
         return unicodedata_ranges(prefix), f"Unicode {unicodedata.unidata_version}"
 
 
-def nfc_unsafe_ranges():
-    """Code points whose presence means a text may change under NFC: a non-zero combining class, a
-    canonical decomposition that NFC applies, the second half of a canonical composition (the
-    NFC_Quick_Check values No and Maybe), and everything this interpreter's Unicode version leaves
-    unassigned.  A text without any of them is in NFC already."""
-    second = set(range(0x1161, 0x1176)) | set(range(0x11A8, 0x11C3))  # Hangul vowels and trailing consonants
+def package_normalizers():
+    """(NFD, NFC) of the `tokenizers` package, or None.  Its normalisation tables are older than this
+    interpreter's (combining marks added since Unicode 10 are starters to it), and the encoder has to
+    normalise as that package does, so the tables below keep only what the package knows."""
+    try:
+        from tokenizers import normalizers
+
+        return normalizers.NFD().normalize_str, normalizers.NFC().normalize_str
+    except ImportError:
+        return None
+
+
+def combining_classes():
+    """(first, last, canonical combining class) for every run of code points with a non-zero class."""
+    package = package_normalizers()
+    out = []
+    for cp in range(sys.maxunicode + 1):
+        c = chr(cp)
+        cc = unicodedata.combining(c)
+        if cc and cc < 240 and package:  # known to the package: it moves the mark in front of U+0345 (class 240)
+            nfd = package[0]
+            if nfd("a\u0345" + c) != "a" + nfd(c) + "\u0345":
+                cc = 0
+        if cc:
+            if out and out[-1][1] == cp - 1 and out[-1][2] == cc:
+                out[-1][1] = cp
+            else:
+                out.append([cp, cp, cc])
+    return out
+
+
+def decompositions():
+    """(code point, first, second or 0, 1 if NFC composes the pair back) for every canonical
+    decomposition mapping (one level; Hangul syllables are algorithmic and not listed)."""
+    package = package_normalizers()
+    out = []
     for cp in range(sys.maxunicode + 1):
         parts = unicodedata.decomposition(chr(cp)).split()
-        if len(parts) == 2 and not parts[0].startswith("<"):
-            pair = chr(int(parts[0], 16)) + chr(int(parts[1], 16))
-            if unicodedata.normalize("NFC", pair) == chr(cp):
-                second.add(int(parts[1], 16))
-    out, start = [], None
-    for cp in range(sys.maxunicode + 2):
-        c = chr(cp) if cp <= sys.maxunicode else None
-        inside = c is not None and not 0xD800 <= cp <= 0xDFFF and (
-            unicodedata.combining(c) != 0 or unicodedata.normalize("NFC", c) != c or cp in second
-            or unicodedata.category(c) == "Cn")
-        if inside and start is None:
-            start = cp
-        elif not inside and start is not None:
-            out.append((start, cp - 1))
-            start = None
+        if not parts or parts[0].startswith("<"):
+            continue
+        a, b = int(parts[0], 16), int(parts[1], 16) if len(parts) == 2 else 0
+        if package and package[0](chr(cp)) == chr(cp):
+            continue  # the package leaves it alone
+        nfc = package[1] if package else (lambda t: unicodedata.normalize("NFC", t))
+        composes = int(b != 0 and nfc(chr(a) + chr(b)) == chr(cp))
+        out.append((cp, a, b, composes))
     return out
+
+
+def rows(name, kind, items, fmt):
+    lines = [f"constexpr {kind} {name}[] = {{"]
+    row = "   "
+    for item in items:
+        cell = " " + fmt(item) + ","
+        if len(row) + len(cell) > 118:
+            lines.append(row)
+            row = "   "
+        row += cell
+    lines.append(row)
+    lines.append("};")
+    return "\n".join(lines)
 
 
 def table(name, items):
@@ -111,8 +148,21 @@ struct CodeRange {{
 
 {table("kNumberRanges", numbers)}
 
-// Code points that can change under NFC, or that Unicode {unicodedata.unidata_version} leaves unassigned: a text without them is in NFC.
-{table("kNfcUnsafeRanges", nfc_unsafe_ranges())}
+// Normalisation data: Unicode {unicodedata.unidata_version} (this interpreter's `unicodedata`), less what the NFC
+// normaliser of {source.split(" of ")[-1]} does not know (it treats those code points as inert).
+struct CombiningClass {{
+  uint32_t first, last, value;
+}};
+
+{rows("kCombiningClasses", "CombiningClass", combining_classes(), lambda r: "{0x%X, 0x%X, %d}" % tuple(r))}
+
+// One level of canonical decomposition: code point -> first, second (0: none); composes = 1 where
+// NFC puts the pair together again (no composition exclusion).  Sorted by code point.
+struct Decomposition {{
+  uint32_t point, first, second, composes;
+}};
+
+{rows("kDecompositions", "Decomposition", decompositions(), lambda r: "{0x%X, 0x%X, 0x%X, %d}" % r)}
 
 }} // namespace detail
 }} // namespace llmcp_b200

@@ -318,6 +318,29 @@ def test_llmcp_run_binary_against_oracle(tmp_path):
     assert run.returncode == 0 and run.stdout.strip() == f"aot logits: {d.vocab} next {want[0]}", run.stdout
 
 
+def test_llmcp_run_text_prompt(tmp_path):
+    """`llmcp-run --text ... --chat`: the driver encodes the chat-wrapped prompt itself and generates
+    the same tokens as a run that is handed the ids (ids from the package-checked encoder)."""
+    import json
+    import pathlib
+    import subprocess
+    tool = L._PACKAGE / "bin" / "llmcp-run"
+    golden = json.loads((pathlib.Path(__file__).parent / "golden" / "bpe_encoder.json").read_text())
+    (tmp_path / "tokenizer.json").write_text(golden["tokenizer"])
+    v = L.Vocab(golden["tokenizer"])
+    ids = v.encode(L.chat_prompt("Hello world, it's 12 o'clock", thinking=False))
+    assert len(ids) > 8 and ids[0] == v.token_to_id("<|im_start|>")
+    weights = pathlib.Path("/dev/shm") / "llmcp_b200_synth_20261125.bin"
+    base = [str(tool), "--weights", str(weights), "--aot", str(L.LIBRARY_PATH), "--synthetic", "20261125",
+            "--tokenizer", str(tmp_path / "tokenizer.json"), "--max-new-tokens", "4", "--eos-token", "-1"]
+    by_text = subprocess.run(base + ["--text", "Hello world, it's 12 o'clock", "--chat", "--no-thinking"], capture_output=True, text=True, timeout=900)
+    by_ids = subprocess.run(base + ["--token-ids", ",".join(map(str, ids))], capture_output=True, text=True, timeout=900)
+    assert by_text.returncode == 0 and by_ids.returncode == 0, by_text.stderr + by_ids.stderr
+    assert by_text.stdout == by_ids.stdout and by_text.stdout.strip().split("\n")[-1].startswith("tokens:")
+    assert len(by_text.stdout.strip().split("\n")[-1].split()) == 5
+    v.close()
+
+
 def test_aot_sessions_are_bounded(monkeypatch):
     """A caller that reallocates its state buffers (as the reference's AotRuntime::init does) gets a new
     engine each time; beyond LLMCP_B200_MAX_SESSIONS the least recently used one is released, and a

@@ -270,19 +270,58 @@ def test_encoder_refuses_what_it_does_not_restate(golden):
     v.close()
 
 
-def test_nfc_tokenizer_takes_only_text_that_is_in_nfc(golden):
-    """Under an NFC normaliser (the shipped Qwen tokenizer.json has one) text that NFC leaves alone is
-    encoded as the package encodes it; text NFC could change is refused, never encoded unnormalised."""
-    tokenizers = pytest.importorskip("tokenizers")
+def nfc_tokenizer(golden):
     blob = json.loads(golden["tokenizer"])
+    assert blob["normalizer"] is None
     blob["normalizer"] = {"type": "NFC"}
-    text = json.dumps(blob)
+    return json.dumps(blob)
+
+
+def test_nfc_against_the_committed_forms(golden):
+    """Under an NFC normaliser (the shipped Qwen tokenizer.json has one) the text between added tokens is
+    normalised before it is split: marks put into canonical order, pairs composed, Hangul by arithmetic."""
+    v = L.Vocab(nfc_tokenizer(golden))
+    for case in golden["nfc_cases"]:
+        if "<|" not in case["text"]:
+            assert L.normalize_nfc(case["text"]) == case["nfc"], case["text"].encode("unicode_escape")
+        assert v.encode(case["text"]) == case["ids"], case["text"].encode("unicode_escape")
+    assert L.normalize_nfc("") == "" and L.normalize_nfc("plain ascii") == "plain ascii"
+    # an added token is cut out of the raw text: the mark behind <|im_end|> does not reach into it
+    ids = v.encode("<|im_end|>\u0301")
+    assert ids[0] == v.token_to_id("<|im_end|>") and len(ids) > 1
+    v.close()
+    # an added token that is matched after normalisation is not restated
+    blob = json.loads(nfc_tokenizer(golden))
+    blob["added_tokens"][-1]["normalized"] = True
+    v = L.Vocab(json.dumps(blob))
+    with pytest.raises(L.LlmcpError, match="normalized"):
+        v.encode("hello")
+    v.close()
+
+
+def test_nfc_every_code_point_against_the_package(golden):
+    """Each code point alone, after a base, in front of two marks and behind a mark of the highest class,
+    against the package's normaliser (its tables are older than Unicode 15: what it does not know
+    stays as it is, here too); then random mixtures of marks, jamo and decomposable characters, and the
+    NFC tokenizer's ids on them."""
+    tokenizers = pytest.importorskip("tokenizers")
+    import unicodedata
+    nfc = tokenizers.normalizers.NFC().normalize_str
+    points = [cp for cp in range(0x110000) if not 0xD800 <= cp <= 0xDFFF]
+    for start in range(0, len(points), 4096):
+        text = "".join(chr(c) + "|a" + chr(c) + "|" + chr(c) + "\u0323\u0301|a\u0345" + chr(c) + "|" for c in points[start:start + 4096])
+        assert L.normalize_nfc(text) == nfc(text), hex(points[start])
+    rng = random.Random(5)
+    special = [c for c in points if unicodedata.combining(chr(c))] + list(range(0x1100, 0x1200)) + list(range(0xAC00, 0xAC40))
+    special += [c for c in points if unicodedata.decomposition(chr(c)) and not unicodedata.decomposition(chr(c)).startswith("<")]
+    text = nfc_tokenizer(golden)
     tok, v = tokenizers.Tokenizer.from_str(text), L.Vocab(text)
-    for sample in ["Hello, world!", "café Größe 你好 😀 한국어", "x = 1;\n\n  y = 2\t// ok"]:
-        assert v.encode(sample) == tok.encode(sample, add_special_tokens=False).ids
-    for sample in ["cafe\u0301", "\u212b", "\u1112\u1161", "\U000e0fff"]:  # combining mark, singleton, jamo, unassigned
-        with pytest.raises(L.LlmcpError, match="NFC"):
-            v.encode(sample)
+    for _ in range(20000):
+        sample = "".join(chr(rng.choice(special if rng.random() < 0.8 else points)) for _ in range(rng.randint(1, 10)))
+        assert L.normalize_nfc(sample) == nfc(sample), sample.encode("unicode_escape")
+    for _ in range(2000):
+        sample = "".join(rng.choice(["a", "e", " ", "\n", "<|im_end|>", "'s"]) if rng.random() < 0.5 else chr(rng.choice(special)) for _ in range(rng.randint(1, 16)))
+        assert v.encode(sample) == tok.encode(sample, add_special_tokens=False).ids, sample.encode("unicode_escape")
     v.close()
 
 
