@@ -2,6 +2,8 @@
 
 #include <algorithm>
 #include <climits>
+#include <functional>
+#include <queue>
 #include <cstddef>
 #include <cstdio>
 
@@ -301,20 +303,32 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
   const detail::Json *merges = model ? model->get("merges") : nullptr;
   if (merges && merges->kind == detail::Json::Array) {
     int32_t rank = 0;
+    bool outside = false;
     for (const detail::Json &m : merges->items) {
-      if (m.kind == detail::Json::String)
-        merge_rank_.emplace(m.text, rank++);
-      else if (m.kind == detail::Json::Array && m.items.size() == 2 && m.items[0].kind == detail::Json::String &&
-               m.items[1].kind == detail::Json::String)
-        merge_rank_.emplace(m.items[0].text + " " + m.items[1].text, rank++);
-      else
+      std::string left, right;
+      if (m.kind == detail::Json::String && m.text.find(' ') != std::string::npos) {
+        left = m.text.substr(0, m.text.find(' '));
+        right = m.text.substr(m.text.find(' ') + 1);
+      } else if (m.kind == detail::Json::Array && m.items.size() == 2 && m.items[0].kind == detail::Json::String &&
+                 m.items[1].kind == detail::Json::String) {
+        left = m.items[0].text;
+        right = m.items[1].text;
+      } else {
         return "tokenizer: malformed merges entry";
+      }
+      const auto a = ids_.find(left), b = ids_.find(right), joined = ids_.find(left + right);
+      if (a == ids_.end() || b == ids_.end() || joined == ids_.end())
+        outside = true;
+      else
+        merge_rank_.emplace(pair_key(a->second, b->second), Merge{rank, joined->second});
+      ++rank;
     }
     if (const detail::Json *flag = model->get("ignore_merges"))
       ignore_merges_ = flag->kind == detail::Json::Bool && flag->boolean;
     if (added && added->kind == detail::Json::Array)
       for (const detail::Json &entry : added->items) {
-        added_.push_back(entry.get("content")->text);
+        if (!entry.get("content")->text.empty())
+          added_.push_back(entry.get("content")->text);
         if (const detail::Json *flag = entry.get("normalized"))
           if (flag->kind == detail::Json::Bool && flag->boolean)
             added_normalized_ = true;
@@ -338,6 +352,10 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
       encoder_ready_ = kind0 && kind0->text == "Split" && kind1 && kind1->text == "ByteLevel" && regex &&
                        regex->text == kSupportedPattern && behavior && behavior->text == "Isolated" &&
                        !(invert && invert->boolean) && use_regex && !use_regex->boolean && !(prefix && prefix->boolean);
+    }
+    if (encoder_ready_ && outside) {
+      encoder_ready_ = false;
+      encode_refusal_ = "a merge names a token outside the vocabulary";
     }
     if (encoder_ready_ && added_options_) {
       encoder_ready_ = false;
@@ -543,40 +561,65 @@ std::vector<std::string> pretokenize(const std::string &text) {
 
 void ByteLevelVocab::encode_piece(const std::string &piece, std::vector<int32_t> *ids) const {
   const ByteText &alphabet = byte_text();
-  std::vector<std::string> symbols;
-  std::string whole;
-  for (unsigned char byte : piece) {
-    symbols.push_back(alphabet.text[byte]);
-    whole += alphabet.text[byte];
-  }
   if (ignore_merges_) {
+    std::string whole;
+    for (unsigned char byte : piece)
+      whole += alphabet.text[byte];
     const auto it = ids_.find(whole);
     if (it != ids_.end()) {
       ids->push_back(it->second);
       return;
     }
   }
-  // the adjacent pair of lowest rank, leftmost among equals, until none is left
-  while (symbols.size() > 1) {
-    int32_t best_rank = INT32_MAX;
-    size_t best = 0;
-    for (size_t i = 0; i + 1 < symbols.size(); ++i) {
-      const auto it = merge_rank_.find(symbols[i] + " " + symbols[i + 1]);
-      if (it != merge_rank_.end() && it->second < best_rank) {
-        best_rank = it->second;
-        best = i;
-      }
-    }
-    if (best_rank == INT32_MAX)
-      break;
-    symbols[best] += symbols[best + 1];
-    symbols.erase(symbols.begin() + static_cast<std::ptrdiff_t>(best) + 1);
+  // One symbol per byte, in a doubly linked list; candidates in a heap ordered by (rank, position):
+  // the adjacent pair of lowest rank, leftmost among equals, is merged until none is left.
+  struct Symbol {
+    int32_t id, prev, next;
+  };
+  struct Candidate {
+    int32_t rank, at;
+    bool operator>(const Candidate &o) const { return rank != o.rank ? rank > o.rank : at > o.at; }
+  };
+  const int32_t n = static_cast<int32_t>(piece.size());
+  std::vector<Symbol> symbols(piece.size());
+  for (int32_t i = 0; i < n; ++i) {
+    const auto it = ids_.find(alphabet.text[static_cast<unsigned char>(piece[static_cast<size_t>(i)])]);
+    symbols[static_cast<size_t>(i)] = {it == ids_.end() ? -1 : it->second, i - 1, i + 1 < n ? i + 1 : -1};
   }
-  for (const std::string &symbol : symbols) {
-    const auto it = ids_.find(symbol);
-    if (it != ids_.end())
-      ids->push_back(it->second);
+  std::priority_queue<Candidate, std::vector<Candidate>, std::greater<Candidate>> heap;
+  auto offer = [&](int32_t at) {
+    if (at < 0 || symbols[static_cast<size_t>(at)].next < 0)
+      return;
+    const Symbol &l = symbols[static_cast<size_t>(at)], &r = symbols[static_cast<size_t>(l.next)];
+    if (l.id < 0 || r.id < 0)
+      return;
+    const auto it = merge_rank_.find(pair_key(l.id, r.id));
+    if (it != merge_rank_.end())
+      heap.push({it->second.rank, at});
+  };
+  for (int32_t i = 0; i + 1 < n; ++i)
+    offer(i);
+  while (!heap.empty()) {
+    const Candidate top = heap.top();
+    heap.pop();
+    Symbol &l = symbols[static_cast<size_t>(top.at)];
+    if (l.id < 0 || l.next < 0)
+      continue; // the left symbol was merged away, or lost its neighbour
+    Symbol &r = symbols[static_cast<size_t>(l.next)];
+    const auto it = merge_rank_.find(pair_key(l.id, r.id));
+    if (it == merge_rank_.end() || it->second.rank != top.rank)
+      continue; // the pair at this position is no longer the one that was offered
+    l.id = it->second.id;
+    r.id = -2; // gone
+    l.next = r.next;
+    if (l.next >= 0)
+      symbols[static_cast<size_t>(l.next)].prev = top.at;
+    offer(l.prev);
+    offer(top.at);
   }
+  for (int32_t i = n ? 0 : -1; i >= 0; i = symbols[static_cast<size_t>(i)].next)
+    if (symbols[static_cast<size_t>(i)].id >= 0)
+      ids->push_back(symbols[static_cast<size_t>(i)].id);
 }
 
 std::string ByteLevelVocab::encode(const std::string &text, std::vector<int32_t> *ids) const {
@@ -592,15 +635,20 @@ std::string ByteLevelVocab::encode(const std::string &text, std::vector<int32_t>
         return "tokenizer: cannot encode text: ill-formed UTF-8 at byte " + std::to_string(offsets[i]);
   }
   size_t p = 0;
+  std::vector<size_t> next(added_.size(), 0); // where each added token occurs next (searched again once passed)
+  std::vector<uint8_t> searched(added_.size(), 0);
   while (p < text.size()) {
     // the leftmost added token; the longest of those that start there (added_ is sorted by length)
     size_t where = std::string::npos;
     const std::string *which = nullptr;
-    for (const std::string &token : added_) {
-      const size_t found = text.find(token, p);
-      if (found != std::string::npos && (found < where)) {
-        where = found;
-        which = &token;
+    for (size_t t = 0; t < added_.size(); ++t) {
+      if (!searched[t] || (next[t] != std::string::npos && next[t] < p)) {
+        next[t] = text.find(added_[t], p);
+        searched[t] = 1;
+      }
+      if (next[t] != std::string::npos && next[t] < where) {
+        where = next[t];
+        which = &added_[t];
       }
     }
     const size_t stop = which ? where : text.size();

@@ -51,7 +51,13 @@ private:
   std::vector<std::string> tokens_; // id -> token text ("" + present_[id] == 0: no such id)
   std::vector<uint8_t> present_;
   std::unordered_map<std::string, int32_t> ids_;
-  std::unordered_map<std::string, int32_t> merge_rank_; // "left right" -> rank
+  struct Merge {
+    int32_t rank, id; // position in the merges list; id of the joined token
+  };
+  static uint64_t pair_key(int32_t left, int32_t right) {
+    return (static_cast<uint64_t>(static_cast<uint32_t>(left)) << 32) | static_cast<uint32_t>(right);
+  }
+  std::unordered_map<uint64_t, Merge> merge_rank_; // (left id, right id) -> merge
   std::vector<std::string> added_;                       // added tokens, longest first
   bool ignore_merges_ = false;
   bool encoder_ready_ = false;
