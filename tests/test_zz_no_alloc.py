@@ -28,15 +28,24 @@ def _inputs(rng, S, nk, nv, dk, dv):
                 state=(rng.standard_normal((nv, dk, dv)) * 0.1).astype(np.float32))
 
 
-def _noalloc(torch, x, S, nk, nv, dk, dv):
+def _upload(torch, x, S, nv, dv):
     dev = {k: torch.from_numpy(v.view(np.int16) if v.dtype == np.uint16 else v).cuda() for k, v in x.items()}
-    out = torch.empty((S, nv * dv), dtype=torch.int16, device="cuda")
+    return dev, torch.empty((S, nv * dv), dtype=torch.int16, device="cuda")
+
+
+def _call(torch, dev, out, S, nk, nv, dk, dv):
     ptr = lambda t: C.c_void_p(t.data_ptr())
     stream = torch.cuda.current_stream().cuda_stream
     rc = L.lib().llmcp_dev_gated_delta_net_noalloc(
         ptr(dev["conv"]), ptr(dev["a"]), ptr(dev["b"]), ptr(dev["a_log"]), ptr(dev["dt_bias"]), ptr(dev["state"]),
         C.c_int64(S), C.c_int64(nk), C.c_int64(nv), C.c_int64(dk), C.c_int64(dv), 0, ptr(out), C.c_void_p(stream))
     torch.cuda.synchronize()
+    return rc
+
+
+def _noalloc(torch, x, S, nk, nv, dk, dv):
+    dev, out = _upload(torch, x, S, nv, dv)
+    rc = _call(torch, dev, out, S, nk, nv, dk, dv)
     return rc, out.cpu().numpy().view(np.uint16), dev["state"].cpu().numpy()
 
 
@@ -59,6 +68,27 @@ def test_noalloc_matches_allocating_entry_point_twice():
                                                           nk, nv, dk, dv)
         assert np.array_equal(out, oracle_out)
         assert np.array_equal(state.view(np.uint32), oracle_state.view(np.uint32))
+
+
+def test_noalloc_leaves_free_device_memory_unchanged():
+    """After one call per kernel (one token, several tokens) further calls take no device memory: the
+    free byte count of the GPU is the same before and after them (inputs and output are uploaded
+    before the first reading, so nothing else allocates in between)."""
+    torch = pytest.importorskip("torch")
+    torch.cuda.set_device(0)
+    L.set_device(0)
+    rng = np.random.default_rng(3)
+    shapes = ((1, 16, 32, 128, 128), (7, 16, 32, 128, 128))
+    held = []
+    for S, nk, nv, dk, dv in shapes:
+        dev, out = _upload(torch, _inputs(rng, S, nk, nv, dk, dv), S, nv, dv)
+        assert _call(torch, dev, out, S, nk, nv, dk, dv) == 0, L.last_error()  # the start-up call of this kernel
+        held.append((dev, out))
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        for (S, nk, nv, dk, dv), (dev, out) in zip(shapes, held):
+            assert _call(torch, dev, out, S, nk, nv, dk, dv) == 0
+    assert torch.cuda.mem_get_info()[0] == free_before
 
 
 def test_noalloc_rejects_oversized_calls():
