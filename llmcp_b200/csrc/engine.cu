@@ -232,6 +232,8 @@ Engine::Engine(const uint8_t *base, uint64_t file_bytes, const ModelDims &dims, 
     tc_prefill_attention_ = std::atoi(flag) != 0;
   if (const char *flag = std::getenv("LLMCP_B200_FUSE_SWIGLU"))
     fuse_swiglu_ = std::atoi(flag) != 0;
+  if (const char *flag = std::getenv("LLMCP_B200_PREFETCH_NEXT"))
+    prefetch_next_ = std::atoi(flag) != 0;
   check(cudaMemsetAsync(gemm_error_, 0, 4, stream_), "memset");
   generated_ = static_cast<int64_t *>(alloc(static_cast<size_t>(capacity_) * 8));
   check(cudaMallocHost(&logits_pinned_, static_cast<size_t>(c.vocab) * 4), "cudaMallocHost");
@@ -690,9 +692,24 @@ struct F16Planes {
   int form; // GemmForm, or -1: not a TMA-fed form
 };
 
+// The matrix and the scales of a projection, as ranges for the GEMV in front of it to ask for in L2.
+static void add_weight(PrefetchList *list, const Q8Weight &w) {
+  auto add = [&](const void *p, uint64_t bytes) {
+    if (p && bytes && bytes <= 0xffffffffull && bytes % 16 == 0 && reinterpret_cast<uintptr_t>(p) % 16 == 0 &&
+        list->count < kMaxPrefetchRanges) {
+      list->ptr[list->count] = p;
+      list->bytes[list->count] = static_cast<uint32_t>(bytes);
+      ++list->count;
+    }
+  };
+  add(w.q, static_cast<uint64_t>(w.N) * static_cast<uint64_t>(w.K));
+  add(w.d, static_cast<uint64_t>(w.N) * static_cast<uint64_t>(w.K / 32) * 2);
+}
+
 static void run_linears(const F16Planes &planes, const int8_t *aq, const float *as, int64_t S, const LinearJob *jobs, int count,
                         cudaStream_t stream, uint64_t *launches, int flags, int *gemm_error = nullptr,
-                        const uint16_t *xb = nullptr, int *status = nullptr, const SideStreams *side = nullptr) {
+                        const uint16_t *xb = nullptr, int *status = nullptr, const SideStreams *side = nullptr,
+                        const PrefetchList *next = nullptr) {
   if (jobs[0].w->bf) { // bf16 matrices: the input rows are bf16 (xb), one launch per matrix
     for (int i = 0; i < count; ++i) {
       const Q8Weight &w = *jobs[i].w;
@@ -718,6 +735,8 @@ static void run_linears(const F16Planes &planes, const int8_t *aq, const float *
       g.job[i].activation = jobs[i].activation;
       g.job[i].y_dtype = jobs[i].y_dtype;
     }
+    if (next)
+      g.next = *next;
     cudaError_t e = launch_gemv_q8(aq, as, jobs[0].w->K, g, nullptr, stream);
     if (e != cudaSuccess)
       throw std::runtime_error(std::string("gemv: ") + cudaGetErrorString(e));
@@ -859,6 +878,15 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     make_side_streams();
   SideStreams side_streams = {side_streams_, fork_event_, join_events_, kSideStreams};
   const SideStreams *side = use_side_streams ? &side_streams : nullptr;
+  // One token: every GEMV asks for the next GEMV's weights in L2 while it runs (PrefetchList in kernels.h).
+  const bool prefetch_next = prefetch_next_ && S == 1 && !rows_are_sequences && !bf && !tp_;
+  auto input_weights = [&](const LayerWeights &L, PrefetchList *list) {
+    if (L.full) {
+      add_weight(list, L.q_proj), add_weight(list, L.k_proj), add_weight(list, L.v_proj);
+    } else {
+      add_weight(list, L.qkv), add_weight(list, L.z), add_weight(list, L.a), add_weight(list, L.b);
+    }
+  };
   int cur = 0;
   const uint16_t *pending = nullptr; // the MLP output still to be added to the residual stream
   int64_t lin_index = 0, full_index = 0;
@@ -873,12 +901,20 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     launches_ += 1;
     const int8_t *mixer_q = nullptr; // the mixer's quantised output, all columns
     const float *mixer_s = nullptr;
+    PrefetchList after_input{}, after_out{}, after_mlp{}, after_down{};
+    if (prefetch_next) {
+      add_weight(&after_input, L.full ? L.o_proj : L.out_proj);
+      add_weight(&after_out, L.gate), add_weight(&after_out, L.up);
+      add_weight(&after_mlp, L.down);
+      if (l + 1 < c.layers)
+        input_weights(layers_[static_cast<size_t>(l + 1)], &after_down);
+    }
     if (!L.full) {
       const LinearJob jobs[4] = {{&L.qkv, qkv_, kBF16, kNone},
                                  {&L.z, z_, kBF16, kSilu},
                                  {&L.a, a_, kBF16, kNone},
                                  {&L.b, b_, kBF16, kSigmoid}};
-      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, side);
+      run_linears(planes, aq_, as_, S, jobs, 4, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, side, &after_input);
       const int C = static_cast<int>(m.qkv_dim());
       uint16_t *conv_state = conv_base + lin_index * (c.conv_kernel - 1) * C;
       float *delta_state = delta_base + lin_index * m.lin_v_heads * c.lin_k_dim * c.lin_v_dim;
@@ -923,7 +959,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       ++lin_index;
     } else {
       const LinearJob jobs[3] = {{&L.q_proj, qg_, kBF16, kNone}, {&L.k_proj, k_, kBF16, kNone}, {&L.v_proj, v_, kBF16, kNone}};
-      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, side);
+      run_linears(planes, aq_, as_, S, jobs, 3, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, side, &after_input);
       uint16_t *cache = kv_base + full_index * 2 * m.kv_heads * capacity_ * c.head_dim;
       const int nh = static_cast<int>(m.heads), nkv = static_cast<int>(m.kv_heads), hd = static_cast<int>(c.head_dim);
       const int64_t cache_stride = rows_are_sequences ? static_cast<int64_t>(kv_seq_) : 0;
@@ -951,7 +987,8 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
     }
     // Output projection of the mixer: this rank's rows of the hidden vector, then all of them.
     const LinearJob out = {L.full ? &L.o_proj : &L.out_proj, branch_, kBF16, kNone};
-    run_linears(planes, mixer_q, mixer_s, S, &out, 1, stream_, &launches_, gemv_flags, gemm_status, L.full ? attn_ : xb_, gemm_error_);
+    run_linears(planes, mixer_q, mixer_s, S, &out, 1, stream_, &launches_, gemv_flags, gemm_status, L.full ? attn_ : xb_, gemm_error_,
+                nullptr, &after_out);
     const uint16_t *branch = gather_rows(branch_, S, hidden_rows_);
     rms_norm(hidden_[cur], branch, S, L.post_norm, hidden_[cur ^ 1], nullptr);
     cur ^= 1;
@@ -964,7 +1001,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
       int8_t *product_q = reinterpret_cast<int8_t *>(gate_);
       float *product_s = reinterpret_cast<float *>(up_);
       check(launch_gemv_q8_swiglu(aq_, as_, L.gate.K, L.gate.q, L.gate.d, L.up.q, L.up.d, L.gate.N, nullptr, product_q, product_s,
-                                  gemv_flags, stream_), "gate/up (one launch)");
+                                  gemv_flags, stream_, &after_mlp), "gate/up (one launch)");
       launches_ += 1;
       gather_quant(S, inter_rows_, &mlp_q, &mlp_s, product_q, product_s);
     } else {
@@ -976,7 +1013,7 @@ void Engine::run(const int64_t *tokens_dev, int64_t S, int64_t position, const f
         gather_quant(S, inter_rows_, &mlp_q, &mlp_s);
     }
     const LinearJob down = {&L.down, mlp_out_, kBF16, kNone};
-    run_linears(planes, mlp_q, mlp_s, S, &down, 1, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_);
+    run_linears(planes, mlp_q, mlp_s, S, &down, 1, stream_, &launches_, gemv_flags, gemm_status, xb_, gemm_error_, nullptr, &after_down);
     pending = gather_rows(mlp_out_, S, hidden_rows_);
   }
   if (all_logits_) {

@@ -250,6 +250,7 @@ private:
   uint16_t *xb_ = nullptr;      // bf16 input rows of the next linear (bf16 arenas)
   bool tc_prefill_attention_ = true; // fast mode, more than one token: attention contractions on the tensor cores
   bool fuse_swiglu_ = true;   // one-token MLP: gate, up, product and quantisation in one launch
+  bool prefetch_next_ = true; // one token: a GEMV asks for the next GEMV's weights in L2 while it runs
   // one-token gated-delta-net layers: 0 five launches, 1 two, 2 one (a cluster per key head; measured
   // slower than two: the recurrent state can then be fetched only after the projections have finished)
   int fuse_decode_mixer_ = 1;

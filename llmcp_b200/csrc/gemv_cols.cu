@@ -28,13 +28,45 @@ __device__ inline ColsBlock ld_cols_block(const void *p) {
   return r;
 }
 
+// Asks for the ranges of `next` in L2, 2 KB per request; request c of the concatenated ranges goes to
+// thread c of the grid (most threads issue one request or none).  The ranges are indexed with
+// constants only, so the list stays in the kernel's parameter space.
+__device__ __forceinline__ void prefetch_next_weights(const PrefetchList &next, unsigned thread, unsigned threads) {
+  constexpr uint32_t kShift = 11, kChunk = 1u << kShift;
+  if (next.count == 0)
+    return;
+  uint32_t total = 0;
+#pragma unroll
+  for (int r = 0; r < kMaxPrefetchRanges; ++r)
+    total += r < next.count ? (next.bytes[r] + kChunk - 1) >> kShift : 0u;
+  for (uint32_t c = thread; c < total; c += threads) {
+    uint32_t local = c, bytes = 0;
+    const char *base = nullptr;
+#pragma unroll
+    for (int r = 0; r < kMaxPrefetchRanges; ++r) {
+      const uint32_t chunks = r < next.count ? (next.bytes[r] + kChunk - 1) >> kShift : 0u;
+      if (base == nullptr && local < chunks) {
+        base = static_cast<const char *>(next.ptr[r]);
+        bytes = next.bytes[r];
+      } else if (base == nullptr) {
+        local -= chunks;
+      }
+    }
+    if (base != nullptr) {
+      const uint32_t offset = local << kShift;
+      const uint32_t size = min(kChunk, bytes - offset);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + offset), "r"(size) : "memory");
+    }
+  }
+}
+
 // FAST: the row's block products  float(dot) * (a_scale * w_scale)  are added by a warp (lane-strided
 // partial sums, then shuffles) instead of the ascending fma chain.
 template <int NB, int R, bool DOTS, bool FAST>
-__global__ void __launch_bounds__(NB)
+__global__ void __launch_bounds__(NB, NB == 288 ? 2 : 5) // resident CTAs per SM that gemv_cols_supported counts on
 gemv_q8_cols_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const int8_t *__restrict__ wq,
                     const uint16_t *__restrict__ wd, void *__restrict__ y, int N, int activation, int y_dtype,
-                    int32_t *__restrict__ dots_out) {
+                    int32_t *__restrict__ dots_out, const PrefetchList next) {
   constexpr int K = NB * 32;
   constexpr int kStride = NB + 2; // float2 units: rows start 16-byte aligned on distinct banks
   __shared__ __align__(16) float2 slab[R * kStride];
@@ -51,6 +83,7 @@ gemv_q8_cols_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
       scale_bits[i] = __ldg(wd + static_cast<size_t>(row0 + i) * NB + t);
     }
   }
+  prefetch_next_weights(next, blockIdx.x * NB + t, gridDim.x * NB);
   // The weights are on their way; the input row belongs to the kernel in front.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint4 lo = reinterpret_cast<const uint4 *>(aq)[2 * t];
@@ -113,7 +146,7 @@ gemv_q8_cols_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
 
 template <int NB, int R>
 cudaError_t launch_cols(const int8_t *aq, const float *as, const GemvJob &job, int flags, int32_t *dots_out,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const PrefetchList &next) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((job.N + R - 1) / R);
   config.blockDim = dim3(NB);
@@ -126,13 +159,13 @@ cudaError_t launch_cols(const int8_t *aq, const float *as, const GemvJob &job, i
   config.numAttrs = (flags & kGemvOverlapPrevious) ? 1 : 0;
   if (dots_out)
     return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, true, false>, aq, as, job.wq, job.wd, job.y, job.N,
-                              job.activation, job.y_dtype, dots_out);
+                              job.activation, job.y_dtype, dots_out, next);
   int32_t *no_dots = nullptr;
   if (flags & kGemvFast)
     return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, false, true>, aq, as, job.wq, job.wd, job.y, job.N,
-                              job.activation, job.y_dtype, no_dots);
+                              job.activation, job.y_dtype, no_dots, next);
   return cudaLaunchKernelEx(&config, gemv_q8_cols_kernel<NB, R, false, false>, aq, as, job.wq, job.wd, job.y, job.N,
-                            job.activation, job.y_dtype, no_dots);
+                            job.activation, job.y_dtype, no_dots, next);
 }
 
 // K = 2560 (80 blocks per row), up to four matrices that share the input row.  160 threads: thread
@@ -202,6 +235,7 @@ gemv_q8_cols80_kernel(const int8_t *__restrict__ aq, const float *__restrict__ a
                      : "memory");
     }
   }
+  prefetch_next_weights(jobs.next, blockIdx.x * 160 + t, gridDim.x * 160);
   // The weights are on their way; the input row belongs to the kernel in front.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint4 lo = reinterpret_cast<const uint4 *>(aq)[2 * kb];
@@ -306,7 +340,7 @@ __global__ void __launch_bounds__(160, 4)
 gemv_q8_swiglu80_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as, const int8_t *__restrict__ gate_q,
                         const uint16_t *__restrict__ gate_d, const int8_t *__restrict__ up_q,
                         const uint16_t *__restrict__ up_d, uint16_t *__restrict__ product, int8_t *__restrict__ q_out,
-                        float *__restrict__ s_out) {
+                        float *__restrict__ s_out, const PrefetchList next) {
   constexpr int NB = 80, K = 2560, kHalf = kSetRows / 2;
   constexpr int kStride = NB + 2;
   constexpr int kFastStride = 88;
@@ -331,6 +365,7 @@ gemv_q8_swiglu80_kernel(const int8_t *__restrict__ aq, const float *__restrict__
     }
   };
   load(0);
+  prefetch_next_weights(next, blockIdx.x * 160 + t, gridDim.x * 160);
   // first half of a cluster barrier: by the time CTA 1 stores into CTA 0's shared memory both have started
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   // The weights are on their way; the input row belongs to the kernel in front.
@@ -433,17 +468,18 @@ cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const 
   if (K == 2560)
     return launch_cols80(aq, as, jobs, dots_out, stream);
   if (K == 4096)
-    return launch_cols<128, 8>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
-  return launch_cols<288, 9>(aq, as, jobs.job[0], jobs.flags, dots_out, stream);
+    return launch_cols<128, 8>(aq, as, jobs.job[0], jobs.flags, dots_out, stream, jobs.next);
+  return launch_cols<288, 9>(aq, as, jobs.job[0], jobs.flags, dots_out, stream, jobs.next);
 }
 
 bool gemv_swiglu_supported(int K, int64_t N) { return K == 2560 && N > 0 && N % 32 == 0; }
 
 cudaError_t launch_gemv_q8_swiglu(const int8_t *aq, const float *as, int K, const int8_t *gate_q, const uint16_t *gate_d,
                                   const int8_t *up_q, const uint16_t *up_d, int64_t N, uint16_t *product, int8_t *q_out,
-                                  float *s_out, int flags, cudaStream_t stream) {
+                                  float *s_out, int flags, cudaStream_t stream, const PrefetchList *next) {
   if (!gemv_swiglu_supported(K, N) || !q_out || !s_out)
     return cudaErrorInvalidValue;
+  const PrefetchList ranges = next ? *next : PrefetchList{};
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(N / 32 * 2));
   config.blockDim = dim3(160);
@@ -459,8 +495,8 @@ cudaError_t launch_gemv_q8_swiglu(const int8_t *aq, const float *as, int K, cons
   config.attrs = attribute;
   config.numAttrs = (flags & kGemvOverlapPrevious) ? 2 : 1;
   if (flags & kGemvFast)
-    return cudaLaunchKernelEx(&config, gemv_q8_swiglu80_kernel<true>, aq, as, gate_q, gate_d, up_q, up_d, product, q_out, s_out);
-  return cudaLaunchKernelEx(&config, gemv_q8_swiglu80_kernel<false>, aq, as, gate_q, gate_d, up_q, up_d, product, q_out, s_out);
+    return cudaLaunchKernelEx(&config, gemv_q8_swiglu80_kernel<true>, aq, as, gate_q, gate_d, up_q, up_d, product, q_out, s_out, ranges);
+  return cudaLaunchKernelEx(&config, gemv_q8_swiglu80_kernel<false>, aq, as, gate_q, gate_d, up_q, up_d, product, q_out, s_out, ranges);
 }
 
 } // namespace llmcp_b200

@@ -34,11 +34,22 @@ constexpr int kGemvFast = 16;           // fast mode: a row's block products are
                                         // instead of the reference's ascending fma chain (the int32 block
                                         // dots are unchanged; the f32 sum differs by rounding only)
 
+// Memory that the GEMV launch behind this one will stream (its weight matrices and scales): this
+// launch asks for it in L2 while it runs, so that HBM keeps streaming under the small kernels
+// between two GEMVs and the next GEMV reads from L2.  Addresses 16-byte aligned, sizes multiples of 16.
+constexpr int kMaxPrefetchRanges = 8;
+struct PrefetchList {
+  const void *ptr[kMaxPrefetchRanges];
+  uint32_t bytes[kMaxPrefetchRanges];
+  int count;
+};
+
 struct GemvJobs {
   GemvJob job[kMaxGemvJobs];
   int count;
   int flags;
   int *error_flag; // device int (optional): set to 1 if a bounded wait for a copy ran out
+  PrefetchList next; // K in {2560, 4096, 9216} block-column kernels only
 };
 
 // d32 (optional): the same scales widened to f32, [N][K/32], for the tensor-core GEMM.
@@ -61,7 +72,7 @@ cudaError_t launch_gemv_q8_cols(const int8_t *aq, const float *as, int K, const 
 bool gemv_swiglu_supported(int K, int64_t N);
 cudaError_t launch_gemv_q8_swiglu(const int8_t *aq, const float *as, int K, const int8_t *gate_q, const uint16_t *gate_d,
                                   const int8_t *up_q, const uint16_t *up_d, int64_t N, uint16_t *product, int8_t *q_out,
-                                  float *s_out, int flags, cudaStream_t stream);
+                                  float *s_out, int flags, cudaStream_t stream, const PrefetchList *next = nullptr);
 cudaError_t launch_gemm_q8_dp4a(const int8_t *aq, const float *as, int M, int K, const int8_t *wq,
                                 const uint16_t *wd, int N, void *y, int y_dtype, int activation,
                                 int32_t *dots_out, cudaStream_t stream);
