@@ -252,6 +252,12 @@ int llmcp_b200_validate(const uint8_t *file, uint64_t file_bytes);
  *                               does not restate, or the text is ill-formed UTF-8 (nothing is approximated).
  *   llmcp_b200_pretokenize    : the split step of that encoder alone: byte offsets at which the pieces of
  *                               `text` end (at most `capacity` written); returns the number of pieces.
+ *   llmcp_b200_regex_split    : a Split pre-tokeniser on its own: `pattern` in the regular-expression subset the
+ *                               library restates (csrc/text_regex.h), `behavior` one of removed, isolated,
+ *                               merged_with_previous, merged_with_next, contiguous.  The pieces are written
+ *                               one after the other into `out` (never more than `length` bytes) and their
+ *                               byte lengths into `lengths`; returns their number, or -1 + last_error for
+ *                               a pattern with a construct outside the subset.
  *   llmcp_b200_normalize_nfc  : Unicode Normalization Form C of a UTF-8 text, the normaliser the encoder
  *                               applies when the tokenizer.json names it.
  *   llmcp_b200_stream_*       : ByteLevelStreamingDecoder of tools/llmcp-run/StreamingDecoder.cpp:13-29:
@@ -267,6 +273,8 @@ uint64_t llmcp_b200_vocab_decode(const void *vocab, const int32_t *ids, uint64_t
 int64_t llmcp_b200_vocab_encode(const void *vocab, const char *text, uint64_t length, int32_t *ids, uint64_t capacity);
 int64_t llmcp_b200_pretokenize(const char *text, uint64_t length, int64_t *ends, uint64_t capacity);
 uint64_t llmcp_b200_normalize_nfc(const char *text, uint64_t length, char *out, uint64_t capacity);
+int64_t llmcp_b200_regex_split(const char *pattern, const char *text, uint64_t length, const char *behavior, int invert,
+                               char *out, uint64_t out_capacity, int64_t *lengths, uint64_t capacity);
 void *llmcp_b200_stream_create(const void *vocab);
 void llmcp_b200_stream_destroy(void *stream);
 uint64_t llmcp_b200_stream_append(void *stream, int32_t token, char *out, uint64_t capacity);

@@ -80,6 +80,7 @@ def lib():
         handle.llmcp_b200_vocab_token_to_id.restype = C.c_int32
         handle.llmcp_b200_vocab_encode.restype = C.c_int64
         handle.llmcp_b200_pretokenize.restype = C.c_int64
+        handle.llmcp_b200_regex_split.restype = C.c_int64
         handle.llmcp_b200_stream_create.restype = C.c_void_p
         for name in ("vocab_decode", "stream_append", "stream_finish", "chat_prompt", "normalize_nfc"):
             getattr(handle, "llmcp_b200_" + name).restype = C.c_uint64
@@ -384,6 +385,23 @@ def pretokenize(text):
     n = int(lib().llmcp_b200_pretokenize(raw, C.c_uint64(len(raw)), ends, C.c_uint64(len(raw) + 1)))
     cuts = [0] + list(ends[:n])
     return [raw[a:b].decode() for a, b in zip(cuts, cuts[1:])]
+
+
+def regex_split(pattern, text, behavior="isolated", invert=False):
+    """The pieces a ``Split`` pre-tokeniser with this pattern cuts ``text`` into (the library's own
+    regular-expression matcher; raises for a pattern with a construct it does not restate)."""
+    raw = text.encode()
+    out = C.create_string_buffer(len(raw) + 1)
+    lengths = (C.c_int64 * (len(raw) + 1))()
+    n = int(lib().llmcp_b200_regex_split(pattern.encode(), raw, C.c_uint64(len(raw)), behavior.encode(), int(bool(invert)), out,
+                                         C.c_uint64(len(raw) + 1), lengths, C.c_uint64(len(raw) + 1)))
+    if n < 0:
+        raise LlmcpError(last_error())
+    pieces, at, data = [], 0, out.raw
+    for size in lengths[:n]:
+        pieces.append(data[at:at + size].decode())
+        at += size
+    return pieces
 
 
 def normalize_nfc(text):

@@ -17,9 +17,9 @@ ROOT = PACKAGE.parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libllmcp_b200.so"
 
-SOURCES = ["q8_linear.cu", "gemv_rows.cu", "gemv_cols.cu", "gemm_tc.cu", "gemm_tma.cu", "norms.cu", "mixers.cu", "attn_decode.cu", "attn_prefill.cu", "bf16_linear.cu", "engine.cu", "api.cu", "tp_comm.cu", "noalloc.cu", "format.cpp", "checkpoint.cpp", "text.cpp"]
+SOURCES = ["q8_linear.cu", "gemv_rows.cu", "gemv_cols.cu", "gemm_tc.cu", "gemm_tma.cu", "norms.cu", "mixers.cu", "attn_decode.cu", "attn_prefill.cu", "bf16_linear.cu", "engine.cu", "api.cu", "tp_comm.cu", "noalloc.cu", "format.cpp", "checkpoint.cpp", "text.cpp", "text_regex.cpp"]
 TOOLS = {"llmcp-benchmark": ["tools/llmcp_benchmark.cpp"], "llmcp-pack": ["tools/llmcp_pack.cpp"],
-         "llmcp-run": ["tools/llmcp_run.cpp", "text.cpp"]}
+         "llmcp-run": ["tools/llmcp_run.cpp", "text.cpp", "text_regex.cpp"]}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -17,6 +17,7 @@
 #include "engine.h"
 #include "kernels.h"
 #include "text.h"
+#include "text_regex.h"
 #include "tp_comm.h"
 
 using namespace llmcp_b200;
@@ -968,6 +969,31 @@ int64_t llmcp_b200_pretokenize(const char *text, uint64_t length, int64_t *ends,
     end += static_cast<int64_t>(pieces[i].size());
     if (ends && i < capacity)
       ends[i] = end;
+  }
+  return static_cast<int64_t>(pieces.size());
+}
+
+int64_t llmcp_b200_regex_split(const char *pattern, const char *text, uint64_t length, const char *behavior, int invert,
+                               char *out, uint64_t out_capacity, int64_t *lengths, uint64_t capacity) {
+  detail::Regex regex;
+  detail::SplitBehavior how = detail::SplitBehavior::kIsolated;
+  std::string error = regex.compile(pattern ? pattern : "");
+  if (error.empty())
+    error = detail::parse_split_behavior(behavior ? behavior : "isolated", &how);
+  std::vector<std::string> pieces;
+  if (error.empty())
+    error = detail::regex_split(regex, std::string(text ? text : "", text ? length : 0), how, invert != 0, &pieces);
+  if (!error.empty()) {
+    set_error(error);
+    return -1;
+  }
+  uint64_t at = 0;
+  for (size_t i = 0; i < pieces.size(); ++i) {
+    if (out && at + pieces[i].size() <= out_capacity)
+      std::memcpy(out + at, pieces[i].data(), pieces[i].size());
+    at += pieces[i].size();
+    if (lengths && i < capacity)
+      lengths[i] = static_cast<int64_t>(pieces[i].size());
   }
   return static_cast<int64_t>(pieces.size());
 }

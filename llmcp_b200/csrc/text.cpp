@@ -227,6 +227,12 @@ const char *const kSupportedPattern =
 
 } // namespace
 
+namespace detail {
+void utf8_points(const std::string &text, std::vector<uint32_t> *points, std::vector<size_t> *offsets) {
+  decode_points(text, points, offsets);
+}
+} // namespace detail
+
 std::string utf8_lossy(const std::string &bytes) {
   std::string out;
   out.reserve(bytes.size());
@@ -338,21 +344,11 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
               added_options_ = true;
       }
     std::sort(added_.begin(), added_.end(), [](const std::string &a, const std::string &b) { return a.size() > b.size(); });
-    // pre_tokenizer: Sequence[Split(the supported pattern, Isolated), ByteLevel(use_regex = false)]
-    encode_refusal_ = "its pre_tokenizer is not Split(<the Qwen pattern>, Isolated) followed by ByteLevel without its own pattern";
-    const detail::Json *pre = root.get("pre_tokenizer");
-    const detail::Json *list = pre ? pre->get("pretokenizers") : nullptr;
-    if (list && list->kind == detail::Json::Array && list->items.size() == 2) {
-      const detail::Json &split = list->items[0], &bytes = list->items[1];
-      const detail::Json *pattern = split.get("pattern");
-      const detail::Json *regex = pattern ? pattern->get("Regex") : nullptr;
-      const detail::Json *behavior = split.get("behavior"), *invert = split.get("invert");
-      const detail::Json *use_regex = bytes.get("use_regex"), *prefix = bytes.get("add_prefix_space");
-      const detail::Json *kind0 = split.get("type"), *kind1 = bytes.get("type");
-      encoder_ready_ = kind0 && kind0->text == "Split" && kind1 && kind1->text == "ByteLevel" && regex &&
-                       regex->text == kSupportedPattern && behavior && behavior->text == "Isolated" &&
-                       !(invert && invert->boolean) && use_regex && !use_regex->boolean && !(prefix && prefix->boolean);
-    }
+    // pre_tokenizer: ByteLevel, or a Sequence of Split steps that ends in ByteLevel
+    steps_.clear();
+    prefix_space_ = false;
+    encode_refusal_ = parse_pre_tokenizer(root.get("pre_tokenizer"));
+    encoder_ready_ = encode_refusal_.empty();
     if (encoder_ready_ && outside) {
       encoder_ready_ = false;
       encode_refusal_ = "a merge names a token outside the vocabulary";
@@ -432,6 +428,95 @@ std::string ByteLevelStreamingDecoder::finish() {
   std::string text = vocab_.decode(pending_.data(), pending_.size());
   pending_.clear();
   return text;
+}
+
+// The pre-tokenisation pattern the ByteLevel pre-tokeniser applies when it is asked to (use_regex).
+static const char *const kByteLevelPattern =
+    "'s|'t|'re|'ve|'m|'ll|'d| ?\\p{L}+| ?\\p{N}+| ?[^\\s\\p{L}\\p{N}]+|\\s+(?!\\S)|\\s+";
+
+std::string ByteLevelVocab::parse_pre_tokenizer(const detail::Json *pre) {
+  if (!pre || pre->kind != detail::Json::Object)
+    return "it has no pre_tokenizer (a byte-level vocabulary needs the ByteLevel step)";
+  std::vector<const detail::Json *> list;
+  const detail::Json *type = pre->get("type");
+  if (type && type->text == "Sequence") {
+    const detail::Json *items = pre->get("pretokenizers");
+    if (!items || items->kind != detail::Json::Array)
+      return "its pre_tokenizer Sequence has no list";
+    for (const detail::Json &item : items->items)
+      list.push_back(&item);
+  } else {
+    list.push_back(pre);
+  }
+  bool byte_level = false;
+  for (size_t i = 0; i < list.size(); ++i) {
+    const detail::Json *kind = list[i]->get("type");
+    const std::string name = kind ? kind->text : "";
+    if (byte_level)
+      return "its pre_tokenizer has a step behind ByteLevel";
+    PreStep step;
+    std::string pattern;
+    if (name == "Split") {
+      const detail::Json *p = list[i]->get("pattern");
+      const detail::Json *regex = p ? p->get("Regex") : nullptr, *literal = p ? p->get("String") : nullptr;
+      if (regex && regex->kind == detail::Json::String) {
+        pattern = regex->text;
+      } else if (literal && literal->kind == detail::Json::String && !literal->text.empty()) {
+        for (unsigned char c : literal->text) { // the literal as a pattern: punctuation escaped
+          if (c < 0x80 && !((c >= '0' && c <= '9') || (c >= 'a' && c <= 'z') || (c >= 'A' && c <= 'Z') || c == ' '))
+            pattern += '\\';
+          pattern += static_cast<char>(c);
+        }
+      } else {
+        return "a Split step of its pre_tokenizer has neither a Regex nor a String pattern";
+      }
+      const detail::Json *behavior = list[i]->get("behavior"), *invert = list[i]->get("invert");
+      if (const std::string error = detail::parse_split_behavior(behavior ? behavior->text : "", &step.behavior); !error.empty())
+        return "a Split step of its pre_tokenizer: " + error;
+      step.invert = invert && invert->kind == detail::Json::Bool && invert->boolean;
+    } else if (name == "ByteLevel") {
+      byte_level = true;
+      const detail::Json *use_regex = list[i]->get("use_regex"), *prefix = list[i]->get("add_prefix_space");
+      if (prefix && prefix->kind == detail::Json::Bool && prefix->boolean) {
+        if (i != 0)
+          return "its ByteLevel step adds a prefix space behind other steps";
+        prefix_space_ = true;
+      }
+      if (use_regex && use_regex->kind == detail::Json::Bool && !use_regex->boolean)
+        continue; // only the byte mapping
+      pattern = kByteLevelPattern;
+      step.behavior = detail::SplitBehavior::kIsolated;
+    } else {
+      return "its pre_tokenizer has a step of type '" + name + "' (Split and ByteLevel are restated)";
+    }
+    step.scanner = pattern == kSupportedPattern && step.behavior == detail::SplitBehavior::kIsolated && !step.invert;
+    if (const std::string error = step.regex.compile(pattern); !error.empty())
+      return "a pattern of its pre_tokenizer is outside what is restated: " + error;
+    steps_.push_back(std::move(step));
+  }
+  if (!byte_level)
+    return "its pre_tokenizer does not end in ByteLevel";
+  return "";
+}
+
+std::string ByteLevelVocab::split_pieces(const std::string &segment, std::vector<std::string> *pieces) const {
+  std::vector<std::string> current;
+  if (!segment.empty())
+    current.push_back(prefix_space_ && segment[0] != ' ' ? " " + segment : segment);
+  for (const PreStep &step : steps_) {
+    std::vector<std::string> next;
+    for (const std::string &piece : current) {
+      if (step.scanner) {
+        for (std::string &part : pretokenize(piece))
+          next.push_back(std::move(part));
+      } else if (const std::string error = detail::regex_split(step.regex, piece, step.behavior, step.invert, &next); !error.empty()) {
+        return "tokenizer: cannot encode text: " + error;
+      }
+    }
+    current.swap(next);
+  }
+  pieces->swap(current);
+  return "";
 }
 
 std::string normalize_nfc(const std::string &text) {
@@ -654,7 +739,10 @@ std::string ByteLevelVocab::encode(const std::string &text, std::vector<int32_t>
     const size_t stop = which ? where : text.size();
     if (stop > p) {
       const std::string segment = text.substr(p, stop - p);
-      for (const std::string &piece : pretokenize(nfc_ ? normalize_nfc(segment) : segment))
+      std::vector<std::string> pieces;
+      if (const std::string error = split_pieces(nfc_ ? normalize_nfc(segment) : segment, &pieces); !error.empty())
+        return error;
+      for (const std::string &piece : pieces)
         encode_piece(piece, ids);
     }
     if (!which)

@@ -4,14 +4,14 @@
 // the published algorithm, the streaming decoder of tools/llmcp-run/StreamingDecoder.{h,cpp} and
 // the chat template of tools/llmcp-run/llmcp-run.cpp:608-624.  Host-only C++.
 //
-// Text -> ids (Tokenizer::Encode) is restated for the tokenizer the model ships with: added tokens cut
-// out first, then the pre-tokenisation pattern of its tokenizer.json (the Qwen / GPT-4 style pattern,
-// matched by a hand-written scanner over Unicode categories L, N and White_Space), the ByteLevel
-// alphabet, and byte-pair merges by rank.  Where the tokenizer normalises to NFC, the text between
-// added tokens is normalised first (UAX #15 on generated tables that hold what that library's own
-// normaliser knows: its Unicode data is older than its regular-expression engine's).
-// A tokenizer.json with any other pre-tokeniser, normaliser or added-token matching option loads for
-// decoding and refuses to encode.
+// Text -> ids (Tokenizer::Encode) is restated for byte-level BPE tokenizers: added tokens are cut out
+// first; where the tokenizer normalises to NFC, the text between them is normalised (UAX #15 on
+// generated tables that hold what that library's own normaliser knows); the pre_tokenizer's Split
+// steps and ByteLevel's own pattern run on the matcher of text_regex.h (the Qwen pattern on a
+// hand-written scanner over the same character classes); then the ByteLevel alphabet and the
+// byte-pair merges by rank.  A tokenizer.json with any other pre-tokeniser step, a pattern outside
+// the matcher's subset, another normaliser or an added-token matching option loads for decoding
+// and refuses to encode, with the reason.
 #pragma once
 
 #include <cstdint>
@@ -19,7 +19,13 @@
 #include <unordered_map>
 #include <vector>
 
+#include "text_regex.h"
+
 namespace llmcp_b200 {
+
+namespace detail {
+struct Json;
+}
 
 // Bytes -> UTF-8 text with every maximal ill-formed subsequence replaced by U+FFFD (the lossy
 // conversion the ByteLevel decoder ends with).
@@ -46,7 +52,19 @@ public:
   const std::string &encode_refusal() const { return encode_refusal_; }
 
 private:
+  // One splitting step of the pre_tokenizer (a Split, or the pattern ByteLevel applies itself).
+  struct PreStep {
+    detail::Regex regex;
+    detail::SplitBehavior behavior = detail::SplitBehavior::kIsolated;
+    bool invert = false;
+    bool scanner = false; // the Qwen pattern, isolated: pretokenize() below does the same without backtracking
+  };
+  std::string parse_pre_tokenizer(const detail::Json *pre); // "" or why encode() will refuse
+  std::string split_pieces(const std::string &segment, std::vector<std::string> *pieces) const;
   void encode_piece(const std::string &piece, std::vector<int32_t> *ids) const;
+
+  std::vector<PreStep> steps_;
+  bool prefix_space_ = false; // ByteLevel's add_prefix_space
 
   std::vector<std::string> tokens_; // id -> token text ("" + present_[id] == 0: no such id)
   std::vector<uint8_t> present_;

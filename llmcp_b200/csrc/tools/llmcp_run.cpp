@@ -9,7 +9,7 @@
 //   llmcp-run --tokenizer tokenizer.json --text 'Hello' --tokenize-only [--expect-token ID]
 //   llmcp-run --text 'Hello' [--chat] [--system S] [--no-thinking] --print-prompt
 //
-// --text is encoded with the tokenizer's own pre-tokenisation pattern and merges (text.h); with
+// --text is encoded with the tokenizer's own pre-tokeniser, normaliser and merges (text.h); with
 // --chat the Qwen chat template goes around it first (llmcp-run.cpp:608-624).  --tokenize-only
 // prints the ids, comma-separated, and exits (llmcp-run.cpp:646-653).  --print-prompt writes the text
 // that would be encoded and exits.  The reference's interpreter half (no --aot) is not here.

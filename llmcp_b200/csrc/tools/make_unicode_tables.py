@@ -28,6 +28,46 @@ def engine_ranges(prefix):
     return out
 
 
+CATEGORIES = "Lu Ll Lt Lm Lo Mn Mc Me Nd Nl No Pc Pd Ps Pe Pi Pf Po Sm Sc Sk So Zs Zl Zp Cc Cf Co".split()  # Cn, Cs: the rest
+SCRIPTS = "Han Hiragana Katakana Hangul Latin Cyrillic Greek Arabic Hebrew Thai Devanagari".split()
+
+
+def engine_class_ranges(pattern):
+    """Ranges of a one-character pattern (\\w, \\p{Han}, ...) according to the tokenizers package."""
+    from tokenizers import Regex, pre_tokenizers
+
+    points = [cp for cp in range(sys.maxunicode + 1) if not 0xD800 <= cp <= 0xDFFF]
+    text = "".join(map(chr, points))
+    split = pre_tokenizers.Split(Regex("(?:%s)+" % pattern), behavior="removed", invert=False)
+    kept = [span for _, span in split.pre_tokenize_str(text)]
+    out, at = [], 0
+    for start, end in kept + [(len(points), len(points))]:
+        if start > at:
+            out.append((points[at], points[start - 1]))
+        at = end
+    return out
+
+
+def category_rows():
+    """(first, last, index into CATEGORIES) over all code points that have one of those categories."""
+    try:
+        import tokenizers  # noqa: F401
+
+        found = [(a, b, i) for i, name in enumerate(CATEGORIES) for a, b in engine_class_ranges("\\p{%s}" % name)]
+    except ImportError:
+        found = [(a, b, i) for i, name in enumerate(CATEGORIES) for a, b in unicodedata_ranges(name)]
+    return sorted(found)
+
+
+def class_ranges(pattern, fallback):
+    try:
+        import tokenizers  # noqa: F401
+
+        return engine_class_ranges(pattern)
+    except ImportError:
+        return fallback()
+
+
 def unicodedata_ranges(prefix):
     out, start = [], None
     for cp in range(sys.maxunicode + 1):
@@ -147,6 +187,32 @@ struct CodeRange {{
 {table("kLetterRanges", letters)}
 
 {table("kNumberRanges", numbers)}
+
+// General category of every assigned code point (what is not listed is Cn, or a surrogate), for
+// the \\p{{..}} classes of a tokenizer's pre-tokenisation patterns.  Sorted by first code point.
+constexpr const char *kCategoryNames[] = {{{", ".join('"%s"' % c for c in CATEGORIES)}}};
+
+struct CategoryRange {{
+  uint32_t first, last, category; // index into kCategoryNames
+}};
+
+{rows("kCategoryRanges", "CategoryRange", category_rows(), lambda r: "{0x%X, 0x%X, %d}" % r)}
+
+// \\w and \\s of that engine; \\w inside a bracketed class is a slightly smaller set there.
+{table("kWordRanges", class_ranges("\\w", lambda: []))}
+
+{table("kWordClassRanges", class_ranges("[\\w]", lambda: []))}
+
+{table("kSpaceRanges", class_ranges("\\s", lambda: []))}
+
+// Scripts that pre-tokenisation patterns name.
+constexpr const char *kScriptNames[] = {{{", ".join('"%s"' % c for c in SCRIPTS)}}};
+
+struct ScriptRange {{
+  uint32_t first, last, script; // index into kScriptNames
+}};
+
+{rows("kScriptRanges", "ScriptRange", sorted((a, b, i) for i, name in enumerate(SCRIPTS) for a, b in class_ranges("\\p{%s}" % name, lambda: [])), lambda r: "{0x%X, 0x%X, %d}" % r)}
 
 // Normalisation data: Unicode {unicodedata.unidata_version} (this interpreter's `unicodedata`), less what the NFC
 // normaliser of {source.split(" of ")[-1]} does not know (it treats those code points as inert).

@@ -238,10 +238,23 @@ def test_encoder_refuses_what_it_does_not_restate(golden):
     blob = json.loads(golden["tokenizer"])
     # another pattern: decoding still works, encoding says why not
     other = json.loads(golden["tokenizer"])
-    other["pre_tokenizer"]["pretokenizers"][0]["pattern"]["Regex"] = r"\w+|\s+"
+    other["pre_tokenizer"]["pretokenizers"][0]["pattern"]["Regex"] = r"(?<=\s)\w+|\s+"  # look-behind
     v = L.Vocab(json.dumps(other))
     assert v.decode([v.token_to_id("<|im_end|>")]) == "<|im_end|>"
-    with pytest.raises(L.LlmcpError, match="pre_tokenizer"):
+    with pytest.raises(L.LlmcpError, match="look-behind"):
+        v.encode("hello")
+    v.close()
+    # a pre-tokeniser step that is not restated, and a step behind ByteLevel
+    other = json.loads(golden["tokenizer"])
+    other["pre_tokenizer"]["pretokenizers"].insert(0, {"type": "Digits", "individual_digits": True})
+    v = L.Vocab(json.dumps(other))
+    with pytest.raises(L.LlmcpError, match="Digits"):
+        v.encode("hello")
+    v.close()
+    other = json.loads(golden["tokenizer"])
+    other["pre_tokenizer"]["pretokenizers"].reverse()
+    v = L.Vocab(json.dumps(other))
+    with pytest.raises(L.LlmcpError, match="behind ByteLevel"):
         v.encode("hello")
     v.close()
     # a bare vocabulary has no merges
@@ -340,3 +353,103 @@ def test_llmcp_run_tokenize_only(tmp_path, golden):
     run = subprocess.run([str(tool), "--tokenize-only", "--tokens", "77"], capture_output=True, text=True)
     assert run.returncode == 0 and run.stdout.strip() == "77"
     v.close()
+
+
+# ---- the regular-expression matcher behind Split and ByteLevel -----------------------------------
+# Patterns in the styles byte-level tokenizers use: contractions, optional leading character, digit
+# groups, possessive and lazy quantifiers, case classes with marks, look-ahead, scripts, explicit ranges.
+SPLIT_PATTERNS = [
+    QWEN_PATTERN,
+    r"'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+",
+    r"'(?i:[sdmt]|ll|ve|re)|[^\r\n\p{L}\p{N}]?+\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]++[\r\n]*|\s*[\r\n]|\s+(?!\S)|\s+",
+    r"[^\r\n\p{L}\p{N}]?[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]*[\p{Ll}\p{Lm}\p{Lo}\p{M}]+(?i:'s|'t|'re|'ve|'m|'ll|'d)?"
+    r"|[^\r\n\p{L}\p{N}]?[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]+[\p{Ll}\p{Lm}\p{Lo}\p{M}]*(?i:'s|'t|'re|'ve|'m|'ll|'d)?"
+    r"|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n/]*|\s*[\r\n]+|\s+(?!\S)|\s+",
+    r"\p{N}{1,3}", r"[\u4e00-\u9fa5\u3040-\u309f\u30a0-\u30ff]+", r"\s?\p{L}+|\s?\p{P}+|\d", r"\w+|[^\w\s]+", r" ",
+    r"a|b*?c|[^abc]{2,}?d", r"(?:ab)+|(?>a+)b|x(?=y)|\bfoo\b", r"(?i)hello|WORLD", r"x(?i)a|B", r"[\x41-\x5a]+|\x{1F600}",
+    r"\p{Han}+|\p{Hiragana}+|\p{Katakana}+", r"[\p{L}\p{M}]+|[\p{P}\p{S}]|\p{Zs}+|\P{L}", r"\S+\s*",
+]
+FUZZ_ALPHABET = list("abcXYZ'sStTrReEvVmMlLdD  \t\n\r.,!?-_()/12345foo") + [
+    "\r\n", "\u017f", "\u212a", "é", "É", "ß", "你", "好", "ひ", "カ", "😀", "\u00a0", "\u3000", "\u0301", "\u200b", "\x85", "\u01c5",
+    "\u02b0", "\u2177", "«", "$", "+", "²", "½", "٣", "hello", "WORLD", "World", "xa", "xB"]
+
+
+def fuzz_texts(count, seed):
+    rng = random.Random(seed)
+    fixed = ["", " ", "Hello world, it's 12345 o'clock!!\n\n  x", "fooBarBaz foo's FOO'S 1234567 a\r\n\r\n b"]
+    return fixed + ["".join(rng.choice(FUZZ_ALPHABET) for _ in range(rng.randint(1, 30))) for _ in range(count)]
+
+
+def test_regex_split_against_the_package():
+    tokenizers = pytest.importorskip("tokenizers")
+    texts = fuzz_texts(250, 2)
+    for pattern in SPLIT_PATTERNS:
+        for behavior in ("isolated", "removed", "merged_with_previous", "merged_with_next", "contiguous"):
+            for invert in (False, True):
+                split = tokenizers.pre_tokenizers.Split(tokenizers.Regex(pattern), behavior=behavior, invert=invert)
+                for text in texts if (behavior, invert) == ("isolated", False) else texts[:60]:
+                    want = [piece for piece, _ in split.pre_tokenize_str(text)]
+                    assert L.regex_split(pattern, text, behavior, invert) == want, (pattern, behavior, invert, text)
+
+
+def test_regex_classes_on_every_code_point():
+    """Each class on the string of all code points: what a Split with behaviour "removed" leaves."""
+    tokenizers = pytest.importorskip("tokenizers")
+    text = "".join(chr(cp) for cp in range(0x110000) if not 0xD800 <= cp <= 0xDFFF)
+    for cls in (r"\w", r"[\w]", r"\W", r"[^\w]", r"\s", r"\S", r"\d", r"\D", r".", r"\p{L}", r"\P{L}", r"\p{Lu}", r"\p{Ll}", r"\p{Lt}", r"\p{Lm}",
+                r"\p{Lo}", r"\p{M}", r"\p{Mn}", r"\p{N}", r"\p{Nd}", r"\p{P}", r"\p{S}", r"\p{Z}", r"\p{Zs}", r"\p{C}", r"\p{Cn}", r"\p{Cf}",
+                r"\p{Han}", r"\p{Hangul}", r"\p{Latin}", r"\p{Cyrillic}", r"[^\s\p{L}\p{N}]", r"\p{Letter}", r"\p{^L}"):
+        pattern = "(?:%s)+" % cls
+        split = tokenizers.pre_tokenizers.Split(tokenizers.Regex(pattern), behavior="removed", invert=False)
+        assert L.regex_split(pattern, text, "removed") == [piece for piece, _ in split.pre_tokenize_str(text)], cls
+
+
+def test_regex_refuses_what_it_does_not_restate():
+    for pattern, word in ((r"(?<=a)b", "look-behind"), (r"(a)\1", "back-references"), (r"[a&&[b]]", "intersections"), (r"[a[:alpha:]]", "nested"), (r"\p{Greekish}", "unknown property"),
+                          (r"(?i)é", "non-ASCII"), (r"(a*)*", "can be empty"), (r"(?m)a", "flag"), (r"a{2,1}", "quantifier"), (r"(a", "missing"),
+                          (r"a)", "unmatched"), (r"\h", "escape")):
+        with pytest.raises(L.LlmcpError, match=word):
+            L.regex_split(pattern, "abc")
+    with pytest.raises(L.LlmcpError, match="empty string"):
+        L.regex_split(r"a?", "bbb")
+    with pytest.raises(L.LlmcpError, match="behaviour"):
+        L.regex_split(r"a", "bbb", behavior="sideways")
+
+
+def trained(tokenizers, pre_tokenizer, normalizer=None):
+    tok = tokenizers.Tokenizer(tokenizers.models.BPE())
+    tok.pre_tokenizer = pre_tokenizer
+    if normalizer is not None:
+        tok.normalizer = normalizer
+    tok.decoder = tokenizers.decoders.ByteLevel()
+    corpus = ["Hello world, it's a fine day. I'll say they've done 12345 things!\n\n  indented\tcode();\r\n",
+              "Größe naïve café — «quotes» … 你好世界 こんにちは カタカナ мир", "def f(x):\n    return x**2 + 1  # comment 2024-01-31\n",
+              "   spaces   everywhere   \n \n\t\n", "emoji 😀😃 and ½ ² ٣ numbers"] * 20
+    trainer = tokenizers.trainers.BpeTrainer(vocab_size=480, special_tokens=["<|endoftext|>", "<|im_end|>"],
+                                             initial_alphabet=tokenizers.pre_tokenizers.ByteLevel.alphabet(), show_progress=False)
+    tok.train_from_iterator(corpus, trainer)
+    return tok
+
+
+def test_encode_with_other_pre_tokenizers():
+    """Tokenizers set up the way other byte-level BPE models ship them: ByteLevel with its own pattern
+    (with and without the prefix space), several Split steps in a row, a literal-string Split."""
+    tokenizers = pytest.importorskip("tokenizers")
+    P, R = tokenizers.pre_tokenizers, tokenizers.Regex
+    setups = [
+        P.ByteLevel(add_prefix_space=False, use_regex=True),
+        P.ByteLevel(add_prefix_space=True, use_regex=True),
+        P.Sequence([P.Split(R(SPLIT_PATTERNS[2]), behavior="isolated"), P.ByteLevel(add_prefix_space=False, use_regex=False)]),
+        P.Sequence([P.Split(R(r"\p{N}{1,3}"), behavior="isolated"), P.Split(R(SPLIT_PATTERNS[5]), behavior="isolated"),
+                    P.Split(R(SPLIT_PATTERNS[3]), behavior="isolated"), P.ByteLevel(add_prefix_space=False, use_regex=False)]),
+        P.Sequence([P.Split(" ", behavior="merged_with_next"), P.Split(R(r"\d"), behavior="isolated"),
+                    P.ByteLevel(add_prefix_space=False, use_regex=False)]),
+        P.Sequence([P.Split(R(r"\s+"), behavior="removed"), P.ByteLevel(add_prefix_space=False, use_regex=True)]),
+    ]
+    texts = fuzz_texts(400, 4) + ["<|im_end|>x<|im_end|> y", "a<|endoftext|>"]
+    for number, setup in enumerate(setups):
+        tok = trained(tokenizers, setup, tokenizers.normalizers.NFC() if number == 3 else None)
+        v = L.Vocab(tok.to_str())
+        for text in texts:
+            assert v.encode(text) == tok.encode(text, add_special_tokens=False).ids, (number, text)
+        v.close()
