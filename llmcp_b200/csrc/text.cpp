@@ -361,6 +361,9 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
       if (const detail::Json *normalizer = root.get("normalizer"))
         if (normalizer->kind == detail::Json::Object) {
           const detail::Json *type = normalizer->get("type");
+          const detail::Json *members = normalizer->get("normalizers");
+          if (type && type->text == "Sequence" && members && members->kind == detail::Json::Array && members->items.size() == 1)
+            type = members->items[0].get("type"); // a Sequence of one normaliser is that normaliser
           if (type && type->text == "NFC" && !added_normalized_) {
             nfc_ = true;
           } else if (type && type->text == "NFC") {

@@ -299,6 +299,12 @@ def test_nfc_against_the_committed_forms(golden):
             assert L.normalize_nfc(case["text"]) == case["nfc"], case["text"].encode("unicode_escape")
         assert v.encode(case["text"]) == case["ids"], case["text"].encode("unicode_escape")
     assert L.normalize_nfc("") == "" and L.normalize_nfc("plain ascii") == "plain ascii"
+    # a Sequence that holds only NFC is NFC
+    blob = json.loads(nfc_tokenizer(golden))
+    blob["normalizer"] = {"type": "Sequence", "normalizers": [{"type": "NFC"}]}
+    w = L.Vocab(json.dumps(blob))
+    assert w.encode("cafe\u0301 \u1112\u1161") == v.encode("cafe\u0301 \u1112\u1161")
+    w.close()
     # an added token is cut out of the raw text: the mark behind <|im_end|> does not reach into it
     ids = v.encode("<|im_end|>\u0301")
     assert ids[0] == v.token_to_id("<|im_end|>") and len(ids) > 1
