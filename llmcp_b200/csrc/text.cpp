@@ -353,6 +353,28 @@ std::string ByteLevelVocab::load(const char *json, size_t bytes) {
       encoder_ready_ = false;
       encode_refusal_ = "a merge names a token outside the vocabulary";
     }
+    if (encoder_ready_) { // model options that change what Encode returns
+      auto refuse = [&](const char *why) {
+        encoder_ready_ = false;
+        encode_refusal_ = why;
+      };
+      const detail::Json *kind = model->get("type"), *dropout = model->get("dropout"), *fallback = model->get("byte_fallback");
+      const detail::Json *prefix = model->get("continuing_subword_prefix"), *suffix = model->get("end_of_word_suffix");
+      if (kind && kind->kind == detail::Json::String && kind->text != "BPE")
+        refuse("its model is not BPE");
+      else if (dropout && dropout->kind == detail::Json::Number && dropout->number > 0)
+        refuse("its model drops merges at random (dropout)");
+      else if (fallback && fallback->kind == detail::Json::Bool && fallback->boolean)
+        refuse("its model falls back to byte tokens (byte_fallback)");
+      else if ((prefix && !prefix->text.empty()) || (suffix && !suffix->text.empty()))
+        refuse("its model has a subword prefix or an end-of-word suffix");
+      else
+        for (int byte = 0; byte < 256; ++byte)
+          if (ids_.find(byte_text().text[byte]) == ids_.end()) {
+            refuse("its vocabulary lacks a symbol of the byte alphabet");
+            break;
+          }
+    }
     if (encoder_ready_ && added_options_) {
       encoder_ready_ = false;
       encode_refusal_ = "an added token asks for lstrip, rstrip or single_word matching";

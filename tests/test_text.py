@@ -276,6 +276,20 @@ def test_encoder_refuses_what_it_does_not_restate(golden):
     with pytest.raises(L.LlmcpError, match="normalizer"):
         v.encode("hello")
     v.close()
+    # model options that change the result
+    for key, value, word in (("dropout", 0.1, "dropout"), ("byte_fallback", True, "byte_fallback"), ("end_of_word_suffix", "</w>", "suffix")):
+        other = json.loads(golden["tokenizer"])
+        other["model"][key] = value
+        v = L.Vocab(json.dumps(other))
+        with pytest.raises(L.LlmcpError, match=word):
+            v.encode("hello")
+        v.close()
+    other = json.loads(golden["tokenizer"])
+    del other["model"]["vocab"][byte_alphabet()[0x41]]  # "A"
+    v = L.Vocab(json.dumps(other))
+    with pytest.raises(L.LlmcpError, match="merge names|byte alphabet"):
+        v.encode("hello")
+    v.close()
     # ill-formed UTF-8
     v = L.Vocab(json.dumps(blob))
     with pytest.raises(L.LlmcpError, match="ill-formed"):
