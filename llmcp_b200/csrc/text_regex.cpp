@@ -112,7 +112,7 @@ void add_digits(std::vector<R> *set) { add_property("Nd", set); }
 
 // ---- syntax tree ---------------------------------------------------------------------------------
 struct Regex::Node {
-  enum Kind { kEmpty, kChar, kSeq, kAlt, kRepeat, kLookahead, kAtomicGroup, kStart, kEnd, kBoundary, kNotBoundary } kind = kEmpty;
+  enum Kind { kEmpty, kChar, kSeq, kAlt, kRepeat, kLookahead, kAtomicGroup, kStart, kEnd, kTextStart, kTextEnd, kBoundary, kNotBoundary } kind = kEmpty;
   int set = -1;
   std::vector<Node> kids;
   int min = 0, max = -1, mode = 0;
@@ -147,6 +147,7 @@ struct Regex::Parser {
   size_t at = 0;
   std::vector<Set> *sets;
   std::string error;
+  int depth = 0; // of nested groups
 
   bool done() const { return at >= p.size(); }
   uint32_t peek(size_t ahead = 0) const { return at + ahead < p.size() ? p[at + ahead] : 0; }
@@ -337,6 +338,7 @@ struct Regex::Parser {
 
   bool quantifier(Node *atom) {
     int min = 0, max = -1;
+    bool braces = false, exact = false;
     if (take('?'))
       min = 0, max = 1;
     else if (take('*'))
@@ -355,7 +357,9 @@ struct Regex::Parser {
       if (!number(&min))
         return fail("malformed { } quantifier");
       max = min;
+      braces = exact = true;
       if (take(',')) {
+        exact = false;
         max = -1;
         if (peek() != '}' && !number(&max))
           return fail("malformed { } quantifier");
@@ -366,12 +370,21 @@ struct Regex::Parser {
       return true; // no quantifier
     }
     int mode = 0;
-    if (take('?'))
+    bool optional_group = false;
+    if (braces) { // in this syntax X{n}? is (?:X{n})? and X{n,m}+ repeats the repetition
+      if (exact && take('?'))
+        optional_group = true;
+      else if (take('?'))
+        mode = 1;
+      else if (peek() == '+')
+        return fail("a + behind a { } quantifier is not supported");
+    } else if (take('?')) {
       mode = 1;
-    else if (take('+'))
+    } else if (take('+')) {
       mode = 2;
-    if (atom->kind == Node::kStart || atom->kind == Node::kEnd || atom->kind == Node::kLookahead || atom->kind == Node::kBoundary ||
-        atom->kind == Node::kNotBoundary)
+    }
+    if (atom->kind == Node::kStart || atom->kind == Node::kEnd || atom->kind == Node::kTextStart || atom->kind == Node::kTextEnd ||
+        atom->kind == Node::kLookahead || atom->kind == Node::kBoundary || atom->kind == Node::kNotBoundary)
       return fail("a quantifier on an anchor or a look-ahead is not supported");
     if (max == -1 && atom->nullable())
       return fail("an unbounded repetition of something that can be empty is not supported");
@@ -380,6 +393,13 @@ struct Regex::Parser {
     repeat.min = min, repeat.max = max, repeat.mode = mode;
     repeat.kids.push_back(*atom);
     *atom = repeat;
+    if (optional_group) {
+      Node outer;
+      outer.kind = Node::kRepeat;
+      outer.min = 0, outer.max = 1, outer.mode = 0;
+      outer.kids.push_back(*atom);
+      *atom = outer;
+    }
     if (peek() == '?' || peek() == '*' || peek() == '+' || (peek() == '{' && peek(1) >= '0' && peek(1) <= '9'))
       return fail("a quantifier on a quantifier is not supported");
     return true;
@@ -428,8 +448,11 @@ struct Regex::Parser {
         }
       }
       Node inner;
+      if (++depth > 100)
+        return fail("groups nested more than 100 deep");
       if (!alternation(inner_fold, &inner))
         return false;
+      --depth;
       if (!take(')'))
         return fail("missing )");
       if (kind == Node::kSeq) {
@@ -459,11 +482,11 @@ struct Regex::Parser {
         return true;
       }
       if (peek() == 'A') {
-        ++at, out->kind = Node::kStart;
+        ++at, out->kind = Node::kTextStart;
         return true;
       }
       if (peek() == 'z') {
-        ++at, out->kind = Node::kEnd;
+        ++at, out->kind = Node::kTextEnd;
         return true;
       }
       std::vector<R> ranges;
@@ -637,6 +660,12 @@ int Regex::emit(const Node &node, std::string *error) {
   case Node::kEnd:
     add(Inst{kEol});
     return 0;
+  case Node::kTextStart:
+    add(Inst{kTextBegin});
+    return 0;
+  case Node::kTextEnd:
+    add(Inst{kTextFinish});
+    return 0;
   case Node::kBoundary:
     add(Inst{kWordBoundary});
     return 0;
@@ -653,7 +682,7 @@ std::string Regex::compile(const std::string &pattern) {
   std::vector<uint32_t> points;
   std::vector<size_t> offsets;
   utf8_points(pattern, &points, &offsets);
-  Parser parser{points, 0, &sets_, ""};
+  Parser parser{points, 0, &sets_, "", 0};
   Node root;
   if (!parser.alternation(false, &root))
     return "regular expression: " + parser.error;
@@ -771,13 +800,25 @@ size_t Regex::run(int pc, size_t pos, const std::vector<uint32_t> &text, int64_t
           failed = true;
         break;
       }
-      case kBol:
-        if (pos == 0)
+      case kBol: // ^ and $ are line anchors in the syntax the tokenizers' engine reads
+        if (pos == 0 || (text[pos - 1] == '\n' && pos < n)) // not behind a newline that ends the text
           ++pc;
         else
           failed = true;
         break;
       case kEol:
+        if (pos == n || text[pos] == '\n')
+          ++pc;
+        else
+          failed = true;
+        break;
+      case kTextBegin:
+        if (pos == 0)
+          ++pc;
+        else
+          failed = true;
+        break;
+      case kTextFinish:
         if (pos == n)
           ++pc;
         else

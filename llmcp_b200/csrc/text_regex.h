@@ -4,7 +4,7 @@
 // constructs those patterns are written in:
 //
 //   alternation, groups ( ) (?: ) (?i: ) (?i) (?> ), look-ahead (?= ) (?! ), classes [ ] [^ ] with
-//   ranges and escapes, . ^ $ \b \B, \s \S \d \D \w \W, \p{..} \P{..} with general categories (one-
+//   ranges and escapes, . ^ $ (line anchors) \A \z \b \B, \s \S \d \D \w \W, \p{..} \P{..} with general categories (one-
 //   and two-letter names) and a few scripts, \r \n \t \f \v \xHH \uHHHH \x{H..}, quantifiers ? * + {m}
 //   {m,} {m,n}, each greedy, lazy (?) or possessive (+).
 //
@@ -36,7 +36,7 @@ private:
     uint32_t first, last;
   };
   using Set = std::vector<Range>; // sorted, disjoint
-  enum Op { kSet, kSpan, kSplit, kJump, kMatch, kLook, kAtomic, kBol, kEol, kWordBoundary, kNotWordBoundary };
+  enum Op { kSet, kSpan, kSplit, kJump, kMatch, kLook, kAtomic, kBol, kEol, kTextBegin, kTextFinish, kWordBoundary, kNotWordBoundary };
   struct Inst {
     Op op;
     int x = 0, y = 0; // kSplit: first and second continuation; kJump: x; kLook / kAtomic: y = continuation, body at pc + 1

@@ -388,6 +388,7 @@ SPLIT_PATTERNS = [
     r"\p{N}{1,3}", r"[\u4e00-\u9fa5\u3040-\u309f\u30a0-\u30ff]+", r"\s?\p{L}+|\s?\p{P}+|\d", r"\w+|[^\w\s]+", r" ",
     r"a|b*?c|[^abc]{2,}?d", r"(?:ab)+|(?>a+)b|x(?=y)|\bfoo\b", r"(?i)hello|WORLD", r"x(?i)a|B", r"[\x41-\x5a]+|\x{1F600}",
     r"\p{Han}+|\p{Hiragana}+|\p{Katakana}+", r"[\p{L}\p{M}]+|[\p{P}\p{S}]|\p{Zs}+|\P{L}", r"\S+\s*",
+    r"^\w+|\w+$|\n^", r"\A\s+|\s+\z|a{2}?b",
 ]
 FUZZ_ALPHABET = list("abcXYZ'sStTrReEvVmMlLdD  \t\n\r.,!?-_()/12345foo") + [
     "\r\n", "\u017f", "\u212a", "é", "É", "ß", "你", "好", "ひ", "カ", "😀", "\u00a0", "\u3000", "\u0301", "\u200b", "\x85", "\u01c5",
@@ -410,6 +411,32 @@ def test_regex_split_against_the_package():
                 for text in texts if (behavior, invert) == ("isolated", False) else texts[:60]:
                     want = [piece for piece, _ in split.pre_tokenize_str(text)]
                     assert L.regex_split(pattern, text, behavior, invert) == want, (pattern, behavior, invert, text)
+
+
+def test_random_patterns_against_the_package():
+    """Patterns thrown together from the constructs the matcher takes: where both it and the package
+    accept one, the pieces are the same (a pattern the matcher refuses is not an error here)."""
+    tokenizers = pytest.importorskip("tokenizers")
+    rng = random.Random(21)
+    atoms = ["a", "b", "c", " ", r"\s", r"\S", r"\d", r"\w", r"\p{L}", r"\p{N}", r"\P{L}", "[ab]", r"[^a\s]", "[a-c]", ".", r"\r", r"\n", "(?:", "(", ")",
+             "|", "?", "*", "+", "{1,2}", "{2}", "?+", "*?", "+?", "(?i:", "(?=", "(?!", "(?>", "^", "$", r"\b", "'", "x", "é", "你", "{2}?", "{1,}?",
+             r"\A", r"\z", r"\B", "(?i)", "A", "S", r"[^\r\n\p{L}]", r"[\w-]", "[]a]", r"[a\]]", r"\.", r"\x41", "\u212a", "\u017f", "-", "{", "}", ",", "1"]
+    texts = ["", "a", "ab cab  abc\n", "aab b\r\nc", "x'a é你 1a2", "   ", "abcabcabc", "AbS\u017f\u212a-a]1{2}, A.a", "\n\na\n"]
+    compared = 0
+    for _ in range(6000):
+        pattern = "".join(rng.choice(atoms) for _ in range(rng.randint(1, 8)))
+        try:
+            ours = [L.regex_split(pattern, text) for text in texts]
+        except L.LlmcpError:
+            continue
+        try:
+            split = tokenizers.pre_tokenizers.Split(tokenizers.Regex(pattern), behavior="isolated")
+            theirs = [[piece for piece, _ in split.pre_tokenize_str(text)] for text in texts]
+        except Exception:
+            continue
+        assert ours == theirs, pattern
+        compared += 1
+    assert compared > 1500
 
 
 def test_regex_classes_on_every_code_point():
