@@ -4,9 +4,10 @@
 // constructs those patterns are written in:
 //
 //   alternation, groups ( ) (?: ) (?i: ) (?i) (?> ), look-ahead (?= ) (?! ), classes [ ] [^ ] with
-//   ranges and escapes, . ^ $ (line anchors) \A \z \b \B, \s \S \d \D \w \W, \p{..} \P{..} with general categories (one-
-//   and two-letter names) and a few scripts, \r \n \t \f \v \xHH \uHHHH \x{H..}, quantifiers ? * + {m}
-//   {m,} {m,n}, each greedy, lazy (?) or possessive (+).
+//   ranges and escapes, . ^ $ (line anchors) \A \z \b \B, \s \S \d \D \w \W, \p{..} \P{..} with
+//   general categories (one- and two-letter names) and a few scripts, \r \n \t \f \v \xHH \uHHHH
+//   \x{H..}, quantifiers ? * + {m} {m,} {m,n}, greedy, lazy (?) or, for ? * +, possessive (+); X{m}?
+//   is (?:X{m})? as in the engine this follows.
 //
 // Anything else (look-behind, back-references, named groups, class intersections, case-insensitive
 // matching of non-ASCII text, unknown property names) is refused when the pattern is compiled, with
